@@ -1,0 +1,422 @@
+"""Typed configuration objects and architecture presets.
+
+The reference plugin receives its configuration from upstream vLLM
+(``VllmConfig``) and only mutates it in
+``vllm_kunlun/platforms/kunlun.py:147-245`` (block size 16 by default, 64 for
+MLA / sparse MLA, eager fallbacks) and ``vllm_kunlun/models/config.py:619-643``
+(per-architecture fix-ups).  This framework is standalone, so it owns the whole
+configuration surface; the same fix-ups live in :meth:`EngineConfig.finalize`.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+
+@dataclass
+class RopeScaling:
+    """YaRN parameters (``models/deepseek_v2.py:311-316,889-903`` in the reference)."""
+
+    type: str = "none"  # "none" | "yarn" | "linear" | "llama3"
+    factor: float = 1.0
+    original_max_position: int = 4096
+    beta_fast: float = 32.0
+    beta_slow: float = 1.0
+    mscale: float = 1.0
+    mscale_all_dim: float = 0.0
+    low_freq_factor: float = 1.0
+    high_freq_factor: float = 4.0
+
+
+@dataclass
+class ModelConfig:
+    """Architecture description shared by every model family."""
+
+    architecture: str = "LlamaForCausalLM"
+    name: str = "unnamed"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 11008
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: RopeScaling = field(default_factory=RopeScaling)
+    rope_neox: bool = True
+    rotary_dim: Optional[int] = None
+    max_position: int = 8192
+    tie_word_embeddings: bool = False
+    qkv_bias: bool = False
+    o_bias: bool = False
+    mlp_bias: bool = False
+    qk_norm: bool = False  # per-head q/k RMSNorm (Qwen3)
+    hidden_act: str = "silu"  # "silu" | "swigluoai" | "gelu_tanh"
+    gemma_norm: bool = False  # (1 + w) RMSNorm
+    # sliding window / sinks (GPT-OSS, MiMo-V2, Gemma)
+    sliding_window: Optional[int] = None
+    sliding_window_pattern: int = 0  # every n-th layer is full attention; 0 = none sliding
+    attention_sinks: bool = False
+    v_head_dim: Optional[int] = None  # asymmetric V (MiMo-V2-Flash)
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    num_shared_experts: int = 0
+    shared_expert_gate: bool = False  # Qwen3-Next sigmoid gate on the shared expert
+    first_dense_layers: int = 0
+    moe_layer_freq: int = 1
+    scoring_func: str = "softmax"  # "softmax" | "sigmoid"
+    norm_topk_prob: bool = True
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    router_bias: bool = False  # e_score_correction_bias
+    moe_bias: bool = False  # GPT-OSS experts carry biases
+    # MLA
+    use_mla: bool = False
+    q_lora_rank: Optional[int] = None
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    # DeepSeek-V3.2 lightning indexer
+    index_topk: int = 0
+    index_n_heads: int = 0
+    index_head_dim: int = 0
+    # MTP
+    num_mtp_layers: int = 0
+    # Gated DeltaNet (Qwen3-Next) hybrid
+    linear_attn_pattern: int = 0  # every n-th layer is full attention, others GDN; 0 = none
+    gdn_num_k_heads: int = 0
+    gdn_num_v_heads: int = 0
+    gdn_head_k_dim: int = 0
+    gdn_head_v_dim: int = 0
+    gdn_conv_kernel: int = 4
+    # quantization of the checkpoint
+    quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq"
+    weight_block_size: tuple = (128, 128)
+    dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        if self.v_head_dim is None:
+            self.v_head_dim = self.head_dim
+        if self.rotary_dim is None:
+            self.rotary_dim = self.qk_rope_head_dim if self.use_mla else self.head_dim
+
+    # ---- derived ----
+    @property
+    def q_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def mla_cache_dim(self) -> int:
+        return self.kv_lora_rank + self.qk_rope_head_dim
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_dense_layers and (i % self.moe_layer_freq == 0)
+
+    def layer_is_sliding(self, i: int) -> bool:
+        if self.sliding_window is None:
+            return False
+        if self.sliding_window_pattern <= 0:
+            return True
+        return (i + 1) % self.sliding_window_pattern != 0
+
+    def layer_is_linear_attn(self, i: int) -> bool:
+        if self.linear_attn_pattern <= 0:
+            return False
+        return (i + 1) % self.linear_attn_pattern != 0
+
+    def num_params(self) -> int:
+        """Rough parameter count (used for memory planning)."""
+        h = self.hidden_size
+        per_attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        if self.use_mla:
+            qk = self.qk_nope_head_dim + self.qk_rope_head_dim
+            qa = self.q_lora_rank or 0
+            per_attn = (h * (qa + self.kv_lora_rank + self.qk_rope_head_dim)
+                        + qa * self.num_heads * qk
+                        + self.kv_lora_rank * self.num_heads * (self.qk_nope_head_dim + self.v_head_dim)
+                        + self.num_heads * self.v_head_dim * h)
+        total = self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        for i in range(self.num_layers):
+            total += per_attn
+            if self.layer_is_moe(i):
+                total += self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+                total += self.num_shared_experts * 3 * h * self.moe_intermediate_size
+            else:
+                total += 3 * h * self.intermediate_size
+        return total
+
+    @classmethod
+    def from_hf_config(cls, cfg: dict) -> "ModelConfig":
+        """Build from a Hugging Face ``config.json`` dict (same checkpoints the reference serves)."""
+        arch = (cfg.get("architectures") or ["LlamaForCausalLM"])[0]
+        h = cfg["hidden_size"]
+        nh = cfg["num_attention_heads"]
+        rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}
+        rope = RopeScaling()
+        rtype = rs.get("type", rs.get("rope_type", "none")) if rs else "none"
+        if rtype in ("yarn", "deepseek_yarn"):
+            rope = RopeScaling(
+                type="yarn", factor=float(rs.get("factor", 1.0)),
+                original_max_position=int(rs.get("original_max_position_embeddings", 4096)),
+                beta_fast=float(rs.get("beta_fast", 32)), beta_slow=float(rs.get("beta_slow", 1)),
+                mscale=float(rs.get("mscale", 1.0)), mscale_all_dim=float(rs.get("mscale_all_dim", 0.0)))
+        elif rtype == "llama3":
+            rope = RopeScaling(
+                type="llama3", factor=float(rs.get("factor", 8.0)),
+                original_max_position=int(rs.get("original_max_position_embeddings", 8192)),
+                low_freq_factor=float(rs.get("low_freq_factor", 1.0)),
+                high_freq_factor=float(rs.get("high_freq_factor", 4.0)))
+        elif rtype == "linear":
+            rope = RopeScaling(type="linear", factor=float(rs.get("factor", 1.0)))
+        qc = cfg.get("quantization_config") or {}
+        quant = None
+        wbs = (128, 128)
+        if qc:
+            method = qc.get("quant_method")
+            if method == "fp8":
+                quant = "fp8"
+                wbs = tuple(qc.get("weight_block_size") or (128, 128))
+            elif method in ("awq", "gptq"):
+                quant = method
+            elif method == "compressed-tensors":
+                quant = "int8"
+        use_mla = "kv_lora_rank" in cfg and cfg.get("kv_lora_rank")
+        kw: dict[str, Any] = dict(
+            architecture=arch, name=cfg.get("_name_or_path", arch),
+            vocab_size=cfg["vocab_size"], hidden_size=h, num_layers=cfg["num_hidden_layers"],
+            num_heads=nh, num_kv_heads=cfg.get("num_key_value_heads", nh),
+            head_dim=cfg.get("head_dim") or h // nh,
+            intermediate_size=cfg.get("intermediate_size", 4 * h),
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
+            rope_theta=float(cfg.get("rope_theta", 10000.0)), rope_scaling=rope,
+            max_position=cfg.get("max_position_embeddings", 8192),
+            tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+            qkv_bias=bool(cfg.get("attention_bias", arch.startswith("Qwen2"))),
+            qk_norm=arch.startswith("Qwen3"),
+            sliding_window=cfg.get("sliding_window") if cfg.get("use_sliding_window", True) else None,
+            quantization=quant, weight_block_size=wbs,
+            dtype=str(cfg.get("torch_dtype", "bfloat16")),
+        )
+        if arch.startswith("Qwen2") or arch.startswith("Qwen3"):
+            kw["sliding_window"] = None
+        n_exp = cfg.get("num_experts") or cfg.get("n_routed_experts") or cfg.get("num_local_experts") or 0
+        if n_exp:
+            kw.update(
+                num_experts=n_exp,
+                num_experts_per_tok=cfg.get("num_experts_per_tok", 8),
+                moe_intermediate_size=cfg.get("moe_intermediate_size", cfg.get("intermediate_size")),
+                num_shared_experts=cfg.get("n_shared_experts", 0) or 0,
+                first_dense_layers=cfg.get("first_k_dense_replace", 0),
+                moe_layer_freq=cfg.get("moe_layer_freq", 1) or 1,
+                scoring_func=cfg.get("scoring_func", "softmax"),
+                norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
+                n_group=cfg.get("n_group", 1) or 1, topk_group=cfg.get("topk_group", 1) or 1,
+                routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0)),
+                router_bias=cfg.get("topk_method") == "noaux_tc",
+            )
+        if use_mla:
+            kw.update(
+                use_mla=True, q_lora_rank=cfg.get("q_lora_rank"), kv_lora_rank=cfg["kv_lora_rank"],
+                qk_nope_head_dim=cfg["qk_nope_head_dim"], qk_rope_head_dim=cfg["qk_rope_head_dim"],
+                v_head_dim=cfg["v_head_dim"], head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
+                rope_neox=False, index_topk=cfg.get("index_topk", 0) or 0,
+                index_n_heads=cfg.get("index_n_heads", 0) or 0,
+                index_head_dim=cfg.get("index_head_dim", 0) or 0,
+                num_mtp_layers=cfg.get("num_nextn_predict_layers", 0) or 0,
+            )
+        if arch == "GptOssForCausalLM":
+            kw.update(attention_sinks=True, sliding_window_pattern=2, hidden_act="swigluoai",
+                      moe_bias=True, qkv_bias=True, o_bias=True,
+                      sliding_window=cfg.get("sliding_window", 128))
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_hf_config(json.load(f))
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 16
+    num_blocks: Optional[int] = None  # None = derive from memory budget
+    gpu_memory_utilization: float = 0.9
+    cache_dtype: str = "auto"  # "auto" | "bfloat16" | "fp8_ds_mla"
+    enable_prefix_caching: bool = False
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    use_sequence_parallel_moe: bool = False
+    fused_collectives: bool = True  # GEMM+reduce-scatter / all-gather+GEMM kernels when peers are mapped
+
+    @property
+    def world_size(self) -> int:
+        return self.tensor_parallel_size * self.pipeline_parallel_size
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 8192
+    enable_chunked_prefill: bool = True
+
+
+@dataclass
+class SpeculativeConfig:
+    method: Optional[str] = None  # None | "mtp" | "eagle" | "eagle3" | "ngram"
+    num_speculative_tokens: int = 0
+    ngram_n: int = 3
+
+
+@dataclass
+class CompilationConfig:
+    """CUDA-graph settings.  The reference only supports piecewise graphs
+    (``docs/source/developer_guide/feature_guide/Kunlun_Graph.md:58-75``); here the
+    decode step is captured whole, and ``piecewise`` keeps attention outside."""
+
+    mode: str = "full_decode"  # "none" | "piecewise" | "full_decode"
+    capture_sizes: tuple = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig
+    cache: CacheConfig = field(default_factory=CacheConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
+    compilation: CompilationConfig = field(default_factory=CompilationConfig)
+    device: str = "cpu"
+    seed: int = 0
+    weights_path: Optional[str] = None
+    init_std: float = 0.02
+
+    def finalize(self) -> "EngineConfig":
+        """Apply the platform fix-ups the reference performs in
+        ``check_and_update_config`` (``platforms/kunlun.py:147-245``)."""
+        m = self.model
+        if m.use_mla and self.cache.block_size not in (64,):
+            self.cache.block_size = 64
+        if m.index_topk and self.cache.cache_dtype == "auto":
+            self.cache.cache_dtype = "bfloat16"
+        if self.device == "cpu":
+            self.compilation.mode = "none"
+        if self.speculative.method == "mtp" and not m.num_mtp_layers:
+            raise ValueError("MTP speculative decoding needs a model with MTP layers")
+        self.scheduler.max_num_batched_tokens = max(
+            self.scheduler.max_num_batched_tokens, self.cache.block_size)
+        return self
+
+
+# --------------------------------------------------------------------------------------
+# Presets: the architectures named by the benchmark configurations.
+# --------------------------------------------------------------------------------------
+
+def qwen2_0_5b() -> ModelConfig:
+    return ModelConfig(
+        architecture="Qwen2ForCausalLM", name="qwen2-0.5b", vocab_size=151936, hidden_size=896,
+        num_layers=24, num_heads=14, num_kv_heads=2, head_dim=64, intermediate_size=4864,
+        rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, qkv_bias=True,
+        max_position=32768, dtype="float32")
+
+
+def llama_3_1_8b() -> ModelConfig:
+    return ModelConfig(
+        architecture="LlamaForCausalLM", name="llama-3.1-8b", vocab_size=128256, hidden_size=4096,
+        num_layers=32, num_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=14336,
+        rms_norm_eps=1e-5, rope_theta=5e5, max_position=131072)
+
+
+def qwen3_8b() -> ModelConfig:
+    return ModelConfig(
+        architecture="Qwen3ForCausalLM", name="qwen3-8b", vocab_size=151936, hidden_size=4096,
+        num_layers=36, num_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=12288,
+        rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, max_position=40960)
+
+
+def qwen3_30b_a3b(fp8: bool = True) -> ModelConfig:
+    return ModelConfig(
+        architecture="Qwen3MoeForCausalLM", name="qwen3-30b-a3b", vocab_size=151936, hidden_size=2048,
+        num_layers=48, num_heads=32, num_kv_heads=4, head_dim=128, intermediate_size=6144,
+        rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, num_experts=128, num_experts_per_tok=8,
+        moe_intermediate_size=768, scoring_func="softmax", norm_topk_prob=True,
+        max_position=40960, quantization="fp8" if fp8 else None)
+
+
+def deepseek_v3(fp8: bool = True, sparse: bool = False) -> ModelConfig:
+    return ModelConfig(
+        architecture="DeepseekV32ForCausalLM" if sparse else "DeepseekV3ForCausalLM",
+        name="deepseek-v3.2" if sparse else "deepseek-v3", vocab_size=129280, hidden_size=7168,
+        num_layers=61, num_heads=128, num_kv_heads=128, head_dim=192, v_head_dim=128,
+        intermediate_size=18432, rms_norm_eps=1e-6, rope_theta=10000.0, rope_neox=False,
+        rope_scaling=RopeScaling(type="yarn", factor=40.0, original_max_position=4096,
+                                 beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0),
+        use_mla=True, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64,
+        num_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048, num_shared_experts=1,
+        first_dense_layers=3, scoring_func="sigmoid", norm_topk_prob=True, n_group=8, topk_group=4,
+        routed_scaling_factor=2.5, router_bias=True, num_mtp_layers=1, max_position=163840,
+        index_topk=2048 if sparse else 0, index_n_heads=64 if sparse else 0,
+        index_head_dim=128 if sparse else 0, quantization="fp8" if fp8 else None)
+
+
+def gpt_oss_20b() -> ModelConfig:
+    return ModelConfig(
+        architecture="GptOssForCausalLM", name="gpt-oss-20b", vocab_size=201088, hidden_size=2880,
+        num_layers=24, num_heads=64, num_kv_heads=8, head_dim=64, intermediate_size=2880,
+        rms_norm_eps=1e-5, rope_theta=150000.0, qkv_bias=True, o_bias=True, num_experts=32,
+        num_experts_per_tok=4, moe_intermediate_size=2880, scoring_func="softmax_after_topk",
+        hidden_act="swigluoai", moe_bias=True, attention_sinks=True, sliding_window=128,
+        sliding_window_pattern=2, max_position=131072)
+
+
+PRESETS = {
+    "qwen2-0.5b": qwen2_0_5b,
+    "llama-3.1-8b": llama_3_1_8b,
+    "qwen3-8b": qwen3_8b,
+    "qwen3-30b-a3b": qwen3_30b_a3b,
+    "deepseek-v3": deepseek_v3,
+    "deepseek-v3.2": lambda: deepseek_v3(sparse=True),
+    "gpt-oss-20b": gpt_oss_20b,
+}
+
+
+def tiny(base: ModelConfig, **overrides) -> ModelConfig:
+    """Shrink a preset for tests while keeping its structure."""
+    return dataclasses.replace(base, **overrides)
+
+
+def cdiv(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def round_up(a: int, b: int) -> int:
+    return cdiv(a, b) * b
+
+
+def yarn_mscale(scale: float, mscale: float) -> float:
+    if scale <= 1.0:
+        return 1.0
+    return 0.1 * mscale * math.log(scale) + 1.0

@@ -1,0 +1,204 @@
+"""``LLM``: the user-facing offline entry point (``LLM(...).generate(...)`` as in the reference's
+quick start, ``docs/source/quick_start.md:77-106``) and the step loop behind the server.
+
+Every rank of a tensor-/pipeline-parallel job runs the same loop on the same requests (SPMD); the
+schedule is a pure function of the request set, and sampled tokens are identical on all ranks
+(greedy on all-gathered logits, or a shared seed), so no per-step control messages are needed.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Iterable, Optional, Sequence, Union
+
+import torch
+
+from ..config import (CacheConfig, CompilationConfig, EngineConfig, ModelConfig, ParallelConfig, PRESETS,
+                      SchedulerConfig, SpeculativeConfig)
+from ..parallel import state as pstate_mod
+from .request import Request, RequestOutput, SamplingParams
+from .runner import ModelRunner, StepHandle
+from .scheduler import BlockPool, Scheduler
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig):
+        self.cfg = cfg.finalize()
+        if cfg.parallel.world_size > 1 or cfg.parallel.data_parallel_size > 1:
+            pstate_mod.init_distributed()
+        self.pstate = pstate_mod.initialize_model_parallel(
+            tp=cfg.parallel.tensor_parallel_size, pp=cfg.parallel.pipeline_parallel_size,
+            dp=cfg.parallel.data_parallel_size, ep=cfg.parallel.enable_expert_parallel,
+            dcp=cfg.parallel.decode_context_parallel_size, device=cfg.device,
+            fused_collectives=cfg.parallel.fused_collectives) \
+            if torch.distributed.is_initialized() else pstate_mod.get_state()
+        self.runner = ModelRunner(self.cfg, self.pstate)
+        self.pool = BlockPool(self.runner.num_blocks, self.cfg.cache.block_size, self.cfg.cache.enable_prefix_caching)
+        self.scheduler = Scheduler(
+            self.pool, self.cfg.scheduler.max_num_seqs, self.cfg.scheduler.max_num_batched_tokens,
+            self.cfg.scheduler.max_model_len, self.cfg.scheduler.enable_chunked_prefill,
+            self.cfg.speculative.num_speculative_tokens, getattr(self.runner, "num_state_slots", 0))
+        self.spec = None
+        if self.cfg.speculative.method:
+            from .spec_decode import build_proposer
+            self.spec = build_proposer(self)
+        # async scheduling: launch step i+1 before reading step i's tokens (not with speculation,
+        # whose accepted length decides the next step's inputs)
+        self.async_scheduling = self.runner.is_cuda and self.spec is None
+        self._inflight: Optional[StepHandle] = None
+        self._ids = itertools.count()
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
+                      "spec_proposed": 0, "spec_accepted": 0}
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_token_ids: Sequence[int], sampling: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, eos_token_id: Optional[int] = None, lora_id: int = -1):
+        rid = request_id or f"req-{next(self._ids)}"
+        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), eos_token_id, lora_id=lora_id)
+        self.scheduler.add(req)
+        return req
+
+    def abort(self, request_id: str) -> bool:
+        return self.scheduler.abort(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work() or self._inflight is not None
+
+    # ------------------------------------------------------------------ stepping
+    def _process(self, h: StepHandle) -> list:
+        """Append sampled tokens, run stop checks, free finished requests."""
+        toks = h.wait().tolist()
+        now = time.perf_counter()
+        finished = []
+        row = 0
+        for req, rows in zip(h.sample_reqs, h.rows_per_req):
+            vals = toks[row:row + rows]
+            row += rows
+            req.num_pending = max(0, req.num_pending - 1)
+            if req.status.finished:
+                continue  # finished while this step was in flight: drop the extra token
+            if self.spec is not None and rows > 1:
+                vals = self.spec.accept(req, vals, self.stats)
+            for v in vals:
+                req.append_token(v, now)
+                if req.check_stop():
+                    self.scheduler.finish(req)
+                    finished.append(req)
+                    break
+        return finished
+
+    def step(self) -> list:
+        """Run one engine iteration; returns requests that finished."""
+        sched = self.scheduler.schedule()
+        self.stats["preemptions"] += len(sched.preempted)
+        finished = []
+        if sched.empty:
+            if self._inflight is not None:
+                finished = self._process(self._inflight)
+                self._inflight = None
+            return finished
+        h = self.runner.execute(sched)
+        self.stats["steps"] += 1
+        for sr in sched.scheduled:
+            self.stats["decode_tokens" if sr.is_decode else "prefill_tokens"] += sr.num_new_tokens
+            if sr.samples:
+                sr.req.num_pending += 1
+        if self.async_scheduling:
+            prev, self._inflight = self._inflight, h
+            if prev is not None:
+                finished = self._process(prev)
+            # a request that will hit max_tokens with its pending token must not be scheduled again
+            for sr in sched.scheduled:
+                r = sr.req
+                if sr.samples and len(r.output_token_ids) + r.num_pending >= r.sampling.max_tokens:
+                    self._drain()
+                    finished += self._finished_since
+                    break
+        else:
+            finished = self._process(h)
+            if self.spec is not None:
+                self.spec.propose(h, self.stats)
+        return finished
+
+    _finished_since: list = []
+
+    def _drain(self):
+        self._finished_since = []
+        if self._inflight is not None:
+            self._finished_since = self._process(self._inflight)
+            self._inflight = None
+
+    def run_until_done(self) -> list:
+        done = []
+        while self.has_unfinished():
+            done += self.step()
+        return done
+
+
+class LLM:
+    """Offline inference front-end.
+
+    ``model`` is a preset name (random-init weights of that architecture), a :class:`ModelConfig`,
+    or a directory with ``config.json`` + safetensors (the checkpoint format the reference loads,
+    including fp8 block-128 ``weight_scale_inv`` tensors)."""
+
+    def __init__(self, model: Union[str, ModelConfig], tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1,
+                 enable_expert_parallel: bool = False, device: Optional[str] = None, dtype: Optional[str] = None,
+                 block_size: int = 16, max_model_len: int = 8192, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.9,
+                 num_gpu_blocks: Optional[int] = None, enable_prefix_caching: bool = False,
+                 enforce_eager: bool = False, speculative_config: Optional[dict] = None, seed: int = 0,
+                 enable_chunked_prefill: bool = True, kv_cache_dtype: str = "auto",
+                 fused_collectives: bool = True, tokenizer=None):
+        import os
+        weights = None
+        if isinstance(model, ModelConfig):
+            mc = model
+        elif model in PRESETS:
+            mc = PRESETS[model]()
+        elif os.path.isdir(model):
+            mc = ModelConfig.from_pretrained(model)
+            weights = model
+        else:
+            raise ValueError(f"unknown model {model!r}")
+        if dtype:
+            mc.dtype = dtype
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        if device == "cuda":
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
+            torch.cuda.set_device(device)
+        spec = SpeculativeConfig(**(speculative_config or {}))
+        cfg = EngineConfig(
+            model=mc,
+            cache=CacheConfig(block_size=block_size, num_blocks=num_gpu_blocks,
+                              gpu_memory_utilization=gpu_memory_utilization, cache_dtype=kv_cache_dtype,
+                              enable_prefix_caching=enable_prefix_caching),
+            parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size,
+                                    enable_expert_parallel=enable_expert_parallel,
+                                    fused_collectives=fused_collectives),
+            scheduler=SchedulerConfig(max_num_seqs, max_num_batched_tokens, max_model_len, enable_chunked_prefill),
+            speculative=spec,
+            compilation=CompilationConfig(mode="none" if enforce_eager else "full_decode"),
+            device=device, seed=seed, weights_path=weights)
+        self.engine = LLMEngine(cfg)
+        self.tokenizer = tokenizer
+        self.eos_token_id = getattr(tokenizer, "eos_token_id", None)
+
+    def generate(self, prompt_token_ids: Iterable[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
+        prompts = list(prompt_token_ids)
+        if isinstance(prompts[0], str):
+            assert self.tokenizer is not None, "string prompts need a tokenizer"
+            prompts = [self.tokenizer.encode(p) for p in prompts]
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        import copy
+        reqs = [self.engine.add_request(p, copy.copy(sp), eos_token_id=self.eos_token_id)
+                for p, sp in zip(prompts, sampling_params)]
+        self.engine.run_until_done()
+        outs = [RequestOutput.from_request(r) for r in reqs]
+        if self.tokenizer is not None:
+            for o in outs:
+                o.text = self.tokenizer.decode(o.token_ids)
+        return outs

@@ -1,0 +1,317 @@
+"""Model runner: owns the model shard, the KV cache, per-step input staging and CUDA graphs.
+
+Counterpart of upstream's ``GPUModelRunner`` that the reference plugs into (call stack in
+``v1/attention/backends/kunlun_attn.py:587-670``: per-step host metadata with several small H2D
+copies).  Here all integer metadata of a step is packed into two pinned staging buffers and moved
+with two async copies into persistent device buffers, so that the same tensors can be bound into a
+captured decode graph.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..attention.metadata import AttentionMetadata, ForwardContext, set_forward_context
+from ..config import EngineConfig, cdiv, round_up
+from ..models import build_model
+from ..parallel.state import ParallelState, get_state
+from ..sample.sampler import Sampler
+from .scheduler import SchedulerOutput
+
+
+@dataclass
+class StepHandle:
+    """Result of one launched step.  ``tokens`` stays on the device; ``tokens_cpu`` is filled by an
+    async copy guarded by ``event`` (CUDA) or immediately (CPU)."""
+
+    sched: SchedulerOutput
+    sample_reqs: list  # requests in the row order of ``tokens``
+    rows_per_req: list  # number of sampled rows per request (1, or 1 + drafts)
+    tokens: torch.Tensor
+    tokens_cpu: torch.Tensor
+    event: Optional[object]
+    hidden: Optional[torch.Tensor] = None  # last hidden states of sampled rows (MTP input)
+    launch_time: float = 0.0
+
+    def wait(self) -> torch.Tensor:
+        if self.event is not None:
+            self.event.synchronize()
+        return self.tokens_cpu
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, pstate: Optional[ParallelState] = None):
+        self.cfg = cfg
+        self.pstate = pstate or get_state()
+        self.device = torch.device(cfg.device)
+        self.is_cuda = self.device.type == "cuda"
+        m = cfg.model
+        with torch.inference_mode():
+            self.model = build_model(m, device=cfg.device)
+            if cfg.weights_path:
+                from ..models.loader import load_safetensors
+                self.model.load_weights(load_safetensors(cfg.weights_path))
+            else:
+                self.model.init_random(cfg.seed, cfg.init_std)
+        self.block_size = cfg.cache.block_size
+        self.max_bs = cfg.scheduler.max_num_seqs
+        self.max_tokens = cfg.scheduler.max_num_batched_tokens
+        self.max_blocks_per_seq = cdiv(cfg.scheduler.max_model_len, self.block_size)
+        self.num_spec = cfg.speculative.num_speculative_tokens
+        self.sampler = Sampler(m.vocab_size, self.device, seed=cfg.seed)
+        self.num_blocks = self._plan_num_blocks()
+        self.kv_caches = self._alloc_kv()
+        self._alloc_staging()
+        self.graphs = None
+        self.last_tokens: Optional[torch.Tensor] = None  # previous step's sampled tokens (device)
+        self.last_rows: dict = {}  # request_id -> row in last_tokens of its newest token
+        self.kernel_launches = 0
+        if self.is_cuda and cfg.compilation.mode != "none":
+            from ..compilation.cuda_graph import DecodeGraphs
+            self.graphs = DecodeGraphs(self)
+
+    # ------------------------------------------------------------------ memory
+    def _bytes_per_block(self) -> int:
+        total = 0
+        for _, (shape, dtype) in self.model.kv_cache_spec(self.block_size).items():
+            shapes = shape if isinstance(shape, list) else [(shape, dtype)]
+            for shp, dt in shapes:
+                total += int(np.prod(shp)) * torch.empty((), dtype=dt).element_size()
+        return total
+
+    def _plan_num_blocks(self) -> int:
+        if self.cfg.cache.num_blocks is not None:
+            return self.cfg.cache.num_blocks
+        per = max(1, self._bytes_per_block())
+        if self.is_cuda:
+            free, total = torch.cuda.mem_get_info(self.device)
+            reserve = int(total * (1 - self.cfg.cache.gpu_memory_utilization))
+            # activations for the largest step: a few [T, max(inter, vocab-shard)] buffers
+            act = self.max_tokens * 16 * self.cfg.model.hidden_size * 2 + (2 << 30)
+            budget = max(0, free - reserve - act)
+            need = self.max_bs * self.max_blocks_per_seq
+            return int(max(16, min(budget // per, need + 64)))
+        return min(self.max_bs * self.max_blocks_per_seq + 8, 4096)
+
+    def _alloc_kv(self):
+        caches = {}
+        for i, (shape, dtype) in self.model.kv_cache_spec(self.block_size).items():
+            if isinstance(shape, list):  # several tensors per layer (e.g. MLA + indexer, GDN states)
+                caches[i] = tuple(torch.zeros((self.num_blocks if lead else n0, *shp), dtype=dt, device=self.device)
+                                  for (shp, dt), (lead, n0) in zip(shape, dtype))
+            else:
+                caches[i] = torch.zeros((self.num_blocks, *shape), dtype=dtype, device=self.device)
+        return caches
+
+    def _alloc_staging(self):
+        T, B, MB = self.max_tokens, self.max_bs, self.max_blocks_per_seq
+        pin = self.is_cuda
+        self.n64 = 3 * T
+        self.n32 = 2 * B + 2 + B * MB + T + T
+        # Two staging sets used alternately: the host may fill step i+1 while the copies of step i
+        # are still queued (the engine runs at most one step ahead of the device).
+        self._h64s = [torch.zeros(self.n64, dtype=torch.int64, pin_memory=pin) for _ in range(2)]
+        self._h32s = [torch.zeros(self.n32, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.d64 = torch.zeros(self.n64, dtype=torch.int64, device=self.device)
+        self.d32 = torch.zeros(self.n32, dtype=torch.int32, device=self.device)
+        self._tok_hosts = [torch.zeros(max(T, B * (1 + self.num_spec)), dtype=torch.int64, pin_memory=pin)
+                           for _ in range(2)]
+        self.step_idx = 0
+        self._bind_staging()
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def _bind_staging(self):
+        k = self.step_idx & 1
+        self.h64, self.h32, self.tokens_host = self._h64s[k], self._h32s[k], self._tok_hosts[k]
+        self.h64_np, self.h32_np = self.h64.numpy(), self.h32.numpy()
+
+    # ------------------------------------------------------------------ input preparation
+    def prepare(self, sched: SchedulerOutput, pad_reqs: int = 0):
+        """Fill the staging buffers for this step; returns ``(AttentionMetadata, input_ids, info)``."""
+        bs = self.block_size
+        srs = sched.scheduled
+        B = len(srs)
+        Bp = max(B, pad_reqs)
+        T = sched.num_tokens
+        Tp = T + (Bp - B)  # padded decode rows carry one dummy token each
+        ids = self.h64_np[0:Tp]
+        pos = self.h64_np[self.max_tokens:self.max_tokens + Tp]
+        slots = self.h64_np[2 * self.max_tokens:2 * self.max_tokens + Tp]
+        seq_lens = self.h32_np[0:Bp]
+        qsl = self.h32_np[self.max_bs:self.max_bs + Bp + 1]
+        o_bt = 2 * self.max_bs + 2
+        max_seq = 0
+        max_q = 0
+        nblk = 1
+        for sr in srs:
+            nblk = max(nblk, len(sr.req.block_ids))
+        nblk = min(self.max_blocks_per_seq, round_up(nblk, 8))
+        if pad_reqs:
+            nblk = self.max_blocks_per_seq  # graph buffers have a fixed row stride
+        bt = self.h32_np[o_bt:o_bt + Bp * nblk].reshape(Bp, nblk)
+        o_li = o_bt + self.max_bs * self.max_blocks_per_seq
+        logits_idx = self.h32_np[o_li:o_li + self.max_tokens]
+        o_rq = o_li + self.max_tokens
+        req_of_tok = self.h32_np[o_rq:o_rq + Tp]
+        t = 0
+        n_logits = 0
+        sample_reqs, rows_per_req = [], []
+        pending_dst, pending_src = [], []
+        num_decodes = num_decode_tokens = 0
+        qsl[0] = 0
+        for b, sr in enumerate(srs):
+            r, n = sr.req, sr.num_new_tokens
+            c = r.num_computed_tokens
+            known = r.all_token_ids
+            n_spec = len(r.spec_token_ids) if sr.is_decode else 0
+            n_known = n - n_spec
+            chunk = known[c:c + n_known]
+            if len(chunk) < n_known:  # newest token still on the device (async scheduling)
+                assert len(chunk) == n_known - 1 and r.request_id in self.last_rows
+                pending_dst.append(t + n_known - 1)
+                pending_src.append(self.last_rows[r.request_id])
+                chunk = chunk + [0]
+            ids[t:t + n_known] = chunk
+            if n_spec:
+                ids[t + n_known:t + n] = r.spec_token_ids
+            p = np.arange(c, c + n)
+            pos[t:t + n] = p
+            blocks = np.asarray(r.block_ids, dtype=np.int64)
+            slots[t:t + n] = blocks[p // bs] * bs + p % bs
+            bt[b, :len(r.block_ids)] = r.block_ids
+            bt[b, len(r.block_ids):] = 0
+            seq_lens[b] = c + n
+            qsl[b + 1] = t + n
+            req_of_tok[t:t + n] = b
+            max_seq = max(max_seq, c + n)
+            max_q = max(max_q, n)
+            if sr.is_decode:
+                num_decodes += 1
+                num_decode_tokens += n
+            if sr.samples:
+                rows = n if (sr.is_decode and n_spec) else 1
+                logits_idx[n_logits:n_logits + rows] = np.arange(t + n - rows, t + n)
+                n_logits += rows
+                sample_reqs.append(r)
+                rows_per_req.append(rows)
+            t += n
+        for b in range(B, Bp):  # padding rows for a captured batch size
+            ids[t] = 0
+            pos[t] = 0
+            slots[t] = -1
+            bt[b, :] = 0
+            seq_lens[b] = 0
+            qsl[b + 1] = t + 1
+            req_of_tok[t] = b
+            logits_idx[n_logits] = t
+            n_logits += 1
+            t += 1
+        # ---- host -> device
+        if self.is_cuda:
+            MT_ = self.max_tokens
+            if Tp * 8 < MT_:  # small step: three short copies beat one long one
+                for o in (0, MT_, 2 * MT_):
+                    self.d64[o:o + Tp].copy_(self.h64[o:o + Tp], non_blocking=True)
+            else:
+                self.d64.copy_(self.h64, non_blocking=True)
+            n32_used = o_rq + Tp
+            self.d32[:n32_used].copy_(self.h32[:n32_used], non_blocking=True)
+            self.h2d_bytes += Tp * 8 * 3 + (Bp * 2 + 1 + Bp * nblk + n_logits + Tp) * 4
+            src64, src32 = self.d64, self.d32
+        else:
+            src64, src32 = self.h64.clone(), self.h32.clone()
+        MT = self.max_tokens
+        input_ids = src64[0:Tp]
+        md = AttentionMetadata(
+            num_tokens=Tp, num_reqs=Bp, positions=src64[MT:MT + Tp], slot_mapping=src64[2 * MT:2 * MT + Tp],
+            block_tables=src32[o_bt:o_bt + Bp * nblk].view(Bp, nblk), seq_lens=src32[0:Bp],
+            query_start_loc=src32[self.max_bs:self.max_bs + Bp + 1], max_query_len=max(max_q, 1),
+            max_seq_len=max(max_seq, 1), num_decodes=num_decodes, num_decode_tokens=num_decode_tokens,
+            num_prefills=B - num_decodes, req_id_per_token=src32[o_rq:o_rq + Tp],
+            logits_indices=src32[o_li:o_li + n_logits], num_spec_tokens=self.num_spec)
+        if not self.is_cuda:
+            md.seq_lens_cpu, md.query_start_loc_cpu = md.seq_lens, md.query_start_loc
+        else:
+            md.seq_lens_cpu = torch.from_numpy(seq_lens.copy())
+            md.query_start_loc_cpu = torch.from_numpy(qsl.copy())
+        if pending_dst:
+            dst = torch.tensor(pending_dst, dtype=torch.int64)
+            src = torch.tensor(pending_src, dtype=torch.int64)
+            if self.is_cuda:
+                dst, src = dst.to(self.device, non_blocking=True), src.to(self.device, non_blocking=True)
+            input_ids.index_copy_(0, dst, self.last_tokens.index_select(0, src))
+        return md, input_ids, (sample_reqs, rows_per_req, n_logits)
+
+    # ------------------------------------------------------------------ execution
+    @torch.inference_mode()
+    def execute(self, sched: SchedulerOutput) -> StepHandle:
+        t0 = time.perf_counter()
+        self.step_idx += 1
+        self._bind_staging()
+        srs = sched.scheduled
+        use_graph = (self.graphs is not None and all(s.is_decode for s in srs)
+                     and self.graphs.supports(len(srs), sched.num_tokens))
+        pad = self.graphs.padded_batch(len(srs)) if use_graph else 0
+        md, input_ids, (sample_reqs, rows_per_req, n_logits) = self.prepare(sched, pad)
+        sp = self.sampler.make_params([r.sampling for r in sample_reqs], rows_per_req, n_logits)
+        if use_graph:
+            tokens, hidden = self.graphs.run(md, input_ids, sp)
+        else:
+            tokens, hidden = self.forward_and_sample(md, input_ids, sp)
+        n_real = sum(rows_per_req)
+        tokens = tokens[:n_real]
+        # bookkeeping at launch time: the KV of these tokens is (being) written
+        row = 0
+        self.last_rows = {}
+        for r, rows in zip(sample_reqs, rows_per_req):
+            self.last_rows[r.request_id] = row + rows - 1
+            row += rows
+        for sr in srs:
+            sr.req.num_computed_tokens += sr.num_new_tokens
+        self.last_tokens = tokens
+        ev = None
+        if self.is_cuda:
+            tokens_cpu = self.tokens_host[:n_real]
+            tokens_cpu.copy_(tokens, non_blocking=True)
+            self.d2h_bytes += n_real * 8
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            tokens_cpu = tokens
+        return StepHandle(sched, sample_reqs, rows_per_req, tokens, tokens_cpu, ev, hidden, t0)
+
+    def forward_and_sample(self, md: AttentionMetadata, input_ids, sp, capturing: bool = False):
+        ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing)
+        with set_forward_context(ctx):
+            hidden = self.run_model(input_ids, md)
+            if hidden is None:  # not the last pipeline stage
+                return torch.zeros(md.logits_indices.shape[0], dtype=torch.int64, device=self.device), None
+            sel = hidden.index_select(0, md.logits_indices.long()) if md.logits_indices is not None else hidden
+            logits = self.model.compute_logits(sel)
+            tokens = self.sampler(logits, sp)
+        return tokens, sel
+
+    def run_model(self, input_ids, md):
+        """One pipeline stage: receive from the previous stage, run, send on (NCCL p2p)."""
+        st = self.pstate
+        hidden = residual = None
+        if st.pp_size > 1 and not st.is_first_pp:
+            shape = (md.num_tokens, self.cfg.model.hidden_size)
+            hidden = st.pp_comm.recv(shape, self.model.dtype, st.pp_rank - 1)
+            residual = st.pp_comm.recv(shape, self.model.dtype, st.pp_rank - 1)
+        hidden, residual = self.model(input_ids, hidden, residual)
+        if st.pp_size > 1 and not st.is_last_pp:
+            st.pp_comm.isend_side_stream(hidden, st.pp_rank + 1)
+            st.pp_comm.isend_side_stream(residual, st.pp_rank + 1)
+            return None
+        return hidden
+
+    def profile_run(self, num_tokens: int):
+        """Dummy forward to size activations (``attn_metadata is None`` path of the reference,
+        ``kunlun_attn.py:770-772``)."""
+        raise NotImplementedError

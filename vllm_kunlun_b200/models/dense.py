@@ -1,0 +1,252 @@
+"""Dense GQA decoders: Llama / Qwen2 / Qwen3 / InternLM2 / Seed-OSS / Mistral shapes.
+
+In the reference these run on upstream model files and the plugin only contributes OOT layers, the
+attention backend and the communicator (``vllm_kunlun/models/__init__.py:24-31``); ``seed_oss.py``
+and ``internlm2.py`` are plain dense decoders on the plugin's ``Attention``.  One decode-step call
+chain (``v1/attention/backends/kunlun_attn.py:751-949``): add+RMSNorm -> qkv GEMM -> (q/k norm) ->
+RoPE -> cache write -> attention -> o_proj (all-reduce) -> add+RMSNorm -> gate_up -> SiLU*up -> down.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..attention.metadata import get_forward_context
+from ..config import ModelConfig
+from ..parallel.state import get_state
+from .layers import (DTYPES, ColumnParallelLinear, ParallelLMHead, RMSNorm, RowParallelLinear,
+                     VocabParallelEmbedding, get_cos_sin_cache, param)
+
+
+class GQAAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        super().__init__()
+        st = get_state()
+        tp = st.tp_size
+        self.layer_idx = layer_idx
+        self.cfg = cfg
+        self.head_dim = cfg.head_dim
+        self.v_head_dim = cfg.v_head_dim
+        assert cfg.num_heads % tp == 0
+        self.num_heads = cfg.num_heads // tp
+        self.kv_replicated = tp > cfg.num_kv_heads
+        self.num_kv_heads = max(1, cfg.num_kv_heads // tp)
+        kv_total = cfg.num_kv_heads * cfg.head_dim
+        v_total = cfg.num_kv_heads * cfg.v_head_dim
+        if self.kv_replicated:
+            # each rank keeps one KV head; the checkpoint slice is chosen at load time
+            sizes = [cfg.q_size, self.head_dim, self.v_head_dim]
+            repl = [False, True, True]
+        else:
+            sizes, repl = [cfg.q_size, kv_total, v_total], [False, False, False]
+        self.qkv_proj = ColumnParallelLinear(cfg.hidden_size, sizes, bias=cfg.qkv_bias, dtype=dtype,
+                                             device=device, quant=cfg.quantization, replicate=repl)
+        self.o_proj = RowParallelLinear(cfg.num_heads * cfg.v_head_dim, cfg.hidden_size, bias=cfg.o_bias,
+                                        dtype=dtype, device=device, quant=cfg.quantization)
+        self.q_norm = self.k_norm = None
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
+            self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
+        self.scale = cfg.head_dim ** -0.5
+        self.window = cfg.sliding_window if cfg.layer_is_sliding(layer_idx) else None
+        self.sinks = param(self.num_heads, dtype=torch.float32, device=device) if cfg.attention_sinks else None
+        self.cos_sin = get_cos_sin_cache(cfg.rotary_dim, cfg.max_position, cfg.rope_theta, cfg.rope_scaling, device)
+
+    def kv_head_for_rank(self, part: int) -> int:
+        """Row offset in the checkpoint K (part 1) / V (part 2) tensor for a replicated KV head."""
+        st = get_state()
+        head = st.tp_rank * self.cfg.num_kv_heads // st.tp_size
+        return head * (self.head_dim if part == 1 else self.v_head_dim)
+
+    def forward(self, hidden):
+        ctx = get_forward_context()
+        md = ctx.attn
+        qkv = self.qkv_proj(hidden)
+        kv_cache = ctx.kv_caches[self.layer_idx]
+        if self.v_head_dim != self.head_dim:
+            raise NotImplementedError("asymmetric V head dim goes through models.mimo")
+        q = ops.qkv_split_norm_rope_cache(
+            qkv, md.positions, self.cos_sin,
+            None if self.q_norm is None else self.q_norm.weight,
+            None if self.k_norm is None else self.k_norm.weight,
+            self.cfg.rms_norm_eps, self.num_heads, self.num_kv_heads, self.head_dim, self.cfg.rope_neox,
+            kv_cache, md.slot_mapping, self.cfg.gemma_norm)
+        T = q.shape[0]
+        o = ops.paged_attention(
+            q.view(T, self.num_heads, self.head_dim), kv_cache, md.block_tables, md.seq_lens,
+            md.query_start_loc, self.scale, md.max_query_len, md.max_seq_len, self.window, self.sinks,
+            md.seq_lens_cpu, md.query_start_loc_cpu, workspace=md.workspace)
+        return self.o_proj(o.reshape(T, self.num_heads * self.head_dim))
+
+
+class GatedMLP(nn.Module):
+    def __init__(self, hidden, inter, dtype, device, quant=None, act="silu", bias=False, reduce_results=True,
+                 tp_size=None, tp_rank=None):
+        super().__init__()
+        self.gate_up_proj = ColumnParallelLinear(hidden, [inter, inter], bias=bias, dtype=dtype, device=device,
+                                                 quant=quant, tp_size=tp_size, tp_rank=tp_rank)
+        self.down_proj = RowParallelLinear(inter, hidden, bias=bias, dtype=dtype, device=device, quant=quant,
+                                           reduce_results=reduce_results, tp_size=tp_size, tp_rank=tp_rank)
+        self.act = act
+
+    def forward(self, x):
+        return self.down_proj(ops.act_and_mul(self.gate_up_proj(x), self.act))
+
+
+class DenseDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
+        self.self_attn = GQAAttention(cfg, layer_idx, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
+        self.mlp = self.build_mlp(cfg, layer_idx, dtype, device)
+
+    def build_mlp(self, cfg, layer_idx, dtype, device):
+        return GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization,
+                        cfg.hidden_act, cfg.mlp_bias)
+
+    def forward(self, hidden, residual):
+        if residual is None:
+            residual = hidden
+            hidden = self.input_layernorm(hidden)
+        else:
+            hidden, residual = self.input_layernorm(hidden, residual)
+        hidden = self.self_attn(hidden)
+        hidden, residual = self.post_attention_layernorm(hidden, residual)
+        hidden = self.mlp(hidden)
+        return hidden, residual
+
+
+# checkpoint name fragment -> (fused param fragment, shard id)
+STACKED = [
+    (".q_proj.", ".qkv_proj.", 0), (".k_proj.", ".qkv_proj.", 1), (".v_proj.", ".qkv_proj.", 2),
+    (".gate_proj.", ".gate_up_proj.", 0), (".up_proj.", ".gate_up_proj.", 1),
+]
+
+
+class DenseForCausalLM(nn.Module):
+    """Pipeline-parallel aware causal LM (``SupportsPP`` pattern: each stage owns a layer slice and
+    passes ``(hidden, residual)`` on, ``models/deepseek_v2.py:1102-1158``)."""
+
+    layer_cls = DenseDecoderLayer
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        super().__init__()
+        self.cfg = cfg
+        self.dtype = dtype or DTYPES[cfg.dtype]
+        self.device = torch.device(device)
+        st = get_state()
+        per = -(-cfg.num_layers // st.pp_size)
+        self.first_layer = st.pp_rank * per
+        self.last_layer = min(cfg.num_layers, self.first_layer + per)
+        self.embed_tokens = (VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, self.dtype, device)
+                             if st.is_first_pp or cfg.tie_word_embeddings else None)
+        self.layers = nn.ModuleDict({
+            str(i): self.layer_cls(cfg, i, self.dtype, device) for i in range(self.first_layer, self.last_layer)})
+        self.norm = self.lm_head = None
+        if st.is_last_pp:
+            self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, self.dtype, device, cfg.gemma_norm)
+            self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, self.dtype, device)
+            if cfg.tie_word_embeddings and self.embed_tokens is not None:
+                self.lm_head.weight = self.embed_tokens.weight
+
+    # ---- forward ----
+    def forward(self, input_ids, hidden=None, residual=None):
+        if hidden is None:
+            hidden = self.embed_tokens(input_ids)
+        for i in range(self.first_layer, self.last_layer):
+            hidden, residual = self.layers[str(i)](hidden, residual)
+        if self.norm is None:
+            return hidden, residual
+        hidden, _ = self.norm(hidden, residual)
+        return hidden, None
+
+    def compute_logits(self, hidden):
+        return self.lm_head.logits(hidden)
+
+    # ---- KV cache ----
+    def kv_cache_spec(self, block_size: int):
+        """Per-layer ``(shape_per_block, dtype)`` for layers this stage owns."""
+        st = get_state()
+        kvh = max(1, self.cfg.num_kv_heads // st.tp_size)
+        return {i: ((2, kvh, block_size, self.cfg.head_dim), self.dtype)
+                for i in range(self.first_layer, self.last_layer)}
+
+    # ---- weights ----
+    def init_random(self, seed: int = 0, std: float = 0.02):
+        """Seeded ``N(0, std)`` weights, norm weights = 1, biases/sinks ~ N(0, std)."""
+        g = torch.Generator(device=self.device).manual_seed(seed + 1000 * get_state().tp_rank)
+        for name, p in self.named_parameters():
+            if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                continue
+            if name.endswith("norm.weight") or "layernorm.weight" in name:
+                p.data.fill_(0.0 if self.cfg.gemma_norm else 1.0)
+            else:
+                p.data.copy_((torch.randn(p.shape, generator=g, device=self.device, dtype=torch.float32) * std)
+                             .to(p.dtype))
+        self.finish_loading()
+
+    def finish_loading(self):
+        for m in self.modules():
+            meth = getattr(m, "method", None)
+            if meth is not None:
+                meth.process_weights_after_loading(m)
+
+    def _resolve(self, name: str):
+        """Checkpoint tensor name -> (module, param name, shard id) or None when not on this stage."""
+        name = name.removeprefix("model.")
+        shard = None
+        for ck, fused, sid in STACKED:
+            if ck in name:
+                name, shard = name.replace(ck, fused), sid
+                break
+        parts = name.split(".")
+        mod = self
+        for i, p in enumerate(parts[:-1]):
+            if p == "layers":
+                continue
+            if i > 0 and parts[i - 1] == "layers":
+                if p not in self.layers:
+                    return None
+                mod = self.layers[p]
+                continue
+            if not hasattr(mod, p) or getattr(mod, p) is None:
+                return None
+            mod = getattr(mod, p)
+        return mod, parts[-1], shard
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
+        loaded = set()
+        for name, w in weights:
+            if "rotary_emb.inv_freq" in name:
+                continue
+            if name == "lm_head.weight" and self.cfg.tie_word_embeddings:
+                continue
+            r = self._resolve(name)
+            if r is None:
+                continue
+            mod, pname, shard = r
+            if not hasattr(mod, pname) or getattr(mod, pname) is None:
+                continue
+            kw = {}
+            attn = None
+            if isinstance(mod, ColumnParallelLinear) and any(mod.replicate):
+                attn = self._attn_owner(name)
+                if attn is not None:
+                    kw["kv_head_shard"] = attn.kv_head_for_rank
+            if hasattr(mod, "load"):
+                mod.load(pname, w, shard, **kw) if kw else mod.load(pname, w, shard)
+            else:
+                getattr(mod, pname).data.copy_(w)
+            loaded.add(name)
+        self.finish_loading()
+        return loaded
+
+    def _attn_owner(self, ckpt_name: str):
+        parts = ckpt_name.removeprefix("model.").split(".")
+        if len(parts) > 2 and parts[0] == "layers" and parts[1] in self.layers:
+            return getattr(self.layers[parts[1]], "self_attn", None)
+        return None

@@ -1,0 +1,243 @@
+"""Tensor-parallel building blocks: linears, embedding, norms, rotary caches.
+
+Parity targets in the reference: ``ops/linear.py`` (merged-column / QKV weight loaders with
+block-scale shard arithmetic ``:91-96``), ``ops/vocab_parallel_embedding.py:94-118``,
+``ops/layernorm.py:71-167`` and ``ops/rotary_embedding/*``.  Weight tensors keep the checkpoint
+layout ``[out_features, in_features]``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..config import cdiv
+from ..parallel.state import get_state
+
+DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32,
+          "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16, "torch.float32": torch.float32}
+
+
+def param(*shape, dtype, device) -> nn.Parameter:
+    return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device), requires_grad=False)
+
+
+# --------------------------------------------------------------------------- quant method plumbing
+
+class UnquantizedLinearMethod:
+    """bf16 / fp16 / fp32 weights, GEMM through :func:`ops.linear` (tcgen05 on CUDA)."""
+
+    name = None
+
+    def create_weights(self, layer: "LinearBase", out_local: int, in_local: int, dtype, device):
+        layer.weight = param(out_local, in_local, dtype=dtype, device=device)
+
+    def apply(self, layer: "LinearBase", x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, layer.weight, layer.bias)
+
+    def process_weights_after_loading(self, layer):
+        pass
+
+    # rows/cols of every quant-aux tensor that shard with the weight: name -> (row_div, col_div)
+    def aux_params(self):
+        return {}
+
+
+_QUANT_METHODS = {None: UnquantizedLinearMethod}
+
+
+def register_linear_method(name: str, cls) -> None:
+    _QUANT_METHODS[name] = cls
+
+
+def get_linear_method(name: Optional[str], **kw):
+    if name not in _QUANT_METHODS:
+        from .. import quantization  # noqa: F401  (registers the methods)
+    return _QUANT_METHODS[name](**kw)
+
+
+class LinearBase(nn.Module):
+    def __init__(self, in_features, out_features, bias, dtype, device, quant: Optional[str], quant_kw=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.method = get_linear_method(quant, **(quant_kw or {}))
+        self.bias = None
+        self._dtype, self._device = dtype, device
+
+    def forward(self, x):
+        return self.method.apply(self, x)
+
+
+class ReplicatedLinear(LinearBase):
+    def __init__(self, in_features, out_features, bias=False, dtype=torch.bfloat16, device="cpu", quant=None,
+                 quant_kw=None):
+        super().__init__(in_features, out_features, bias, dtype, device, quant, quant_kw)
+        self.method.create_weights(self, out_features, in_features, dtype, device)
+        if bias:
+            self.bias = param(out_features, dtype=dtype, device=device)
+
+    def load(self, name: str, w: torch.Tensor, shard_id=None):
+        getattr(self, name).data.copy_(w)
+
+
+class ColumnParallelLinear(LinearBase):
+    """Output dimension sharded over TP.  ``output_sizes`` lists the logical partitions of a merged
+    projection (e.g. ``[q, k, v]`` or ``[gate, up]``); each is sharded separately so a rank holds the
+    matching slices of all of them (``MergedColumnParallelLinear`` / ``QKVParallelLinear``)."""
+
+    def __init__(self, in_features, output_sizes: Sequence[int], bias=False, dtype=torch.bfloat16,
+                 device="cpu", quant=None, tp_size=None, tp_rank=None, replicate: Sequence[bool] = (),
+                 quant_kw=None):
+        st = get_state()
+        self.tp_size = st.tp_size if tp_size is None else tp_size
+        self.tp_rank = st.tp_rank if tp_rank is None else tp_rank
+        self.output_sizes = list(output_sizes)
+        # a partition marked "replicate" is kept whole on every rank (KV heads when tp > kv_heads)
+        self.replicate = list(replicate) or [False] * len(self.output_sizes)
+        self.local_sizes = [s if r else s // self.tp_size for s, r in zip(self.output_sizes, self.replicate)]
+        super().__init__(in_features, sum(self.output_sizes), bias, dtype, device, quant, quant_kw)
+        self.out_local = sum(self.local_sizes)
+        self.method.create_weights(self, self.out_local, in_features, dtype, device)
+        if bias:
+            self.bias = param(self.out_local, dtype=dtype, device=device)
+
+    def _shard_rows(self, shard_id: Optional[int], row_div: int = 1):
+        """(dst_start, dst_len, src_start) in units of ``row_div`` rows for partition ``shard_id``."""
+        ids = range(len(self.output_sizes)) if shard_id is None else [shard_id]
+        out = []
+        for i in ids:
+            dst0 = sum(self.local_sizes[:i])
+            ln = self.local_sizes[i]
+            src0 = 0 if self.replicate[i] else self.tp_rank * ln
+            # block-scale tensors: ceil-divide, as ``adjust_block_scale_shard`` does (ops/linear.py:91-96)
+            out.append((cdiv(dst0, row_div) if row_div > 1 else dst0,
+                        cdiv(ln, row_div) if row_div > 1 else ln,
+                        src0 // row_div, i))
+        return out
+
+    def load(self, name: str, w: torch.Tensor, shard_id: Optional[int] = None, kv_head_shard=None):
+        p = getattr(self, name)
+        aux = self.method.aux_params().get(name)
+        row_div = aux[0] if aux else 1
+        if shard_id is None and len(self.output_sizes) > 1:
+            # fused checkpoint tensor: split along rows by logical partition first
+            offs = 0
+            for i, s in enumerate(self.output_sizes):
+                n = cdiv(s, row_div)
+                self.load(name, w[offs:offs + n], i)
+                offs += n
+            return
+        for dst0, ln, src0, i in self._shard_rows(shard_id if shard_id is not None else 0, row_div):
+            if kv_head_shard is not None and self.replicate[i]:
+                src0 = kv_head_shard(i) // row_div
+            if p.dim() == 0:
+                p.data.copy_(w.reshape(()))
+            else:
+                p.data[dst0:dst0 + ln].copy_(w[src0:src0 + ln])
+
+
+class RowParallelLinear(LinearBase):
+    """Input dimension sharded over TP; partial sums are combined by all-reduce
+    (call site C1/C2 of the reference: ``models/deepseek_v2.py:126-134,399-405``) unless
+    ``reduce_results`` is False (the caller fuses the reduction)."""
+
+    def __init__(self, in_features, out_features, bias=False, dtype=torch.bfloat16, device="cpu",
+                 quant=None, reduce_results=True, tp_size=None, tp_rank=None, quant_kw=None):
+        st = get_state()
+        self.tp_size = st.tp_size if tp_size is None else tp_size
+        self.tp_rank = st.tp_rank if tp_rank is None else tp_rank
+        super().__init__(in_features, out_features, bias, dtype, device, quant, quant_kw)
+        self.in_local = in_features // self.tp_size
+        self.reduce_results = reduce_results
+        self.method.create_weights(self, out_features, self.in_local, dtype, device)
+        if bias:
+            self.bias = param(out_features, dtype=dtype, device=device)
+
+    def forward(self, x):
+        bias = self.bias
+        if self.tp_rank != 0:
+            self.bias = None  # add the bias once
+        try:
+            y = self.method.apply(self, x)
+        finally:
+            self.bias = bias
+        if self.reduce_results and self.tp_size > 1:
+            y = get_state().tp_comm.all_reduce(y)
+        return y
+
+    def load(self, name: str, w: torch.Tensor, shard_id=None):
+        p = getattr(self, name)
+        if name == "bias" or p.dim() < 2:
+            p.data.copy_(w.reshape(p.shape))
+            return
+        aux = self.method.aux_params().get(name)
+        col_div = aux[1] if aux else 1
+        n = p.shape[1]
+        s0 = (self.tp_rank * self.in_local) // col_div
+        p.data.copy_(w[:, s0:s0 + n])
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Rows sharded over TP; lookups outside the shard give zeros, then all-reduce (C4)."""
+
+    def __init__(self, vocab_size, hidden, dtype=torch.bfloat16, device="cpu", pad_to: int = 64):
+        super().__init__()
+        st = get_state()
+        self.tp_size, self.tp_rank = st.tp_size, st.tp_rank
+        self.vocab_size = vocab_size
+        self.padded = cdiv(vocab_size, pad_to * self.tp_size) * pad_to * self.tp_size
+        self.rows = self.padded // self.tp_size
+        self.start = self.tp_rank * self.rows
+        self.weight = param(self.rows, hidden, dtype=dtype, device=device)
+
+    def forward(self, ids):
+        out = ops.embedding(ids, self.weight, self.start)
+        if self.tp_size > 1:
+            out = get_state().tp_comm.all_reduce(out)
+        return out
+
+    def load(self, name, w, shard_id=None):
+        n = max(0, min(self.rows, w.shape[0] - self.start))
+        self.weight.data.zero_()
+        if n > 0:
+            self.weight.data[:n].copy_(w[self.start:self.start + n])
+
+
+class ParallelLMHead(VocabParallelEmbedding):
+    """Logits = hidden @ W.T on the local vocab shard, then all-gather (C5)."""
+
+    def logits(self, hidden, weight=None):
+        w = self.weight if weight is None else weight
+        lg = ops.linear(hidden, w)
+        if self.tp_size > 1:
+            lg = get_state().tp_comm.all_gather(lg, dim=-1)
+        return lg[..., : self.vocab_size]
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, size, eps, dtype=torch.bfloat16, device="cpu", gemma=False):
+        super().__init__()
+        self.weight = param(size, dtype=dtype, device=device)
+        self.eps, self.gemma = eps, gemma
+
+    def forward(self, x, residual=None):
+        if residual is None:
+            return ops.rmsnorm(x, self.weight, self.eps, self.gemma)
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps, self.gemma)
+
+    def load(self, name, w, shard_id=None):
+        self.weight.data.copy_(w)
+
+
+_ROPE_CACHE: dict = {}
+
+
+def get_cos_sin_cache(rotary_dim, max_pos, theta, scaling, device) -> torch.Tensor:
+    """Process-wide cache of cos/sin tables (``get_rope`` registry, ``ops/rotary_embedding/rope_ext.py:67-108``)."""
+    key = (rotary_dim, max_pos, theta, None if scaling is None else tuple(vars(scaling).items()), str(device))
+    if key not in _ROPE_CACHE:
+        from ..ops.reference.basic import build_cos_sin_cache
+        _ROPE_CACHE[key] = build_cos_sin_cache(rotary_dim, max_pos, theta, scaling).to(device)
+    return _ROPE_CACHE[key]

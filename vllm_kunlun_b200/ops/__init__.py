@@ -1,0 +1,240 @@
+"""Functional op layer.
+
+Every function takes tensors and dispatches on their device: CUDA tensors go to the hand-written
+sm_100a kernels in the in-tree extension (and fail loudly if it is missing); CPU tensors go to the
+fp32 oracles in :mod:`vllm_kunlun_b200.ops.reference`.  This replaces the reference's two binding
+layers (``vllm_kunlun/ops/_custom_ops.py`` - 54 ``torch.library.custom_op`` shims - and
+``vllm_kunlun/ops/_kunlun_ops.py`` - the ``KunlunOps`` facade), which forward to closed libraries.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _ext
+from .reference import attention as _ra
+from .reference import basic as _rb
+from .reference import misc as _rx
+from .reference import moe as _rm
+
+reference_basic = _rb
+reference_attention = _ra
+reference_moe = _rm
+reference_misc = _rx
+
+
+def _c():
+    return _ext.C()
+
+
+# ----------------------------------------------------------------------------- norms / activations
+
+def rmsnorm(x, weight, eps: float, gemma: bool = False):
+    if x.is_cuda:
+        out = torch.empty_like(x)
+        _c().rmsnorm(out, x, weight, eps, gemma)
+        return out
+    return _rb.rmsnorm(x, weight, eps, gemma)
+
+
+def add_rmsnorm(x, residual, weight, eps: float, gemma: bool = False):
+    """Returns ``(normed, new_residual)``.  On CUDA both are written in place
+    (``x`` becomes the normed output, ``residual`` the sum)."""
+    if x.is_cuda:
+        _c().add_rmsnorm(x, residual, weight, eps, gemma)
+        return x, residual
+    return _rb.add_rmsnorm(x, residual, weight, eps, gemma)
+
+
+def rms_norm_gated(x, z, weight, eps, norm_before_gate=True, group_size=None):
+    if x.is_cuda:
+        out = torch.empty_like(x)
+        _c().rms_norm_gated(out, x, z, weight, eps, norm_before_gate, group_size or x.shape[-1])
+        return out
+    return _rb.rms_norm_gated(x, z, weight, eps, norm_before_gate, group_size)
+
+
+def l2norm(x, eps: float = 1e-6):
+    if x.is_cuda:
+        out = torch.empty_like(x)
+        _c().l2norm(out, x, eps)
+        return out
+    return _rb.l2norm(x, eps)
+
+
+_ACT_CODES = {"silu": 0, "gelu_tanh": 1, "swigluoai": 2}
+
+
+def act_and_mul(x, act: str = "silu"):
+    if x.is_cuda:
+        d = x.shape[-1] // 2
+        out = torch.empty(*x.shape[:-1], d, dtype=x.dtype, device=x.device)
+        _c().act_and_mul(out, x, _ACT_CODES[act])
+        return out
+    if act == "silu":
+        return _rb.silu_and_mul(x)
+    if act == "swigluoai":
+        return _rb.swigluoai_and_mul(x)
+    return _rb.gelu_tanh_and_mul(x)
+
+
+def silu_and_mul(x):
+    return act_and_mul(x, "silu")
+
+
+def quick_gelu(x):
+    if x.is_cuda:
+        out = torch.empty_like(x)
+        _c().quick_gelu(out, x)
+        return out
+    return _rb.quick_gelu(x)
+
+
+# ----------------------------------------------------------------------------- rotary / cache
+
+def rope(q, k, positions, cos_sin_cache, head_dim: int, neox: bool = True):
+    """In-place style rotary on ``q [T, Hq*D]`` and ``k [T, Hkv*D]``; returns ``(q, k)``."""
+    if q.is_cuda:
+        _c().rope(q, k, positions, cos_sin_cache, head_dim, neox)
+        return q, k
+    rd = cos_sin_cache.shape[-1]
+    return (_rb.apply_rope(q, positions, cos_sin_cache, head_dim, neox, rd),
+            _rb.apply_rope(k, positions, cos_sin_cache, head_dim, neox, rd))
+
+
+def mrope(q, k, positions3, cos_sin_cache, head_dim, sections, interleaved=False):
+    if q.is_cuda:
+        _c().mrope(q, k, positions3, cos_sin_cache, head_dim, list(sections), interleaved)
+        return q, k
+    return (_rb.apply_mrope(q, positions3, cos_sin_cache, head_dim, sections, interleaved),
+            _rb.apply_mrope(k, positions3, cos_sin_cache, head_dim, sections, interleaved))
+
+
+def reshape_and_cache(k, v, kv_cache, slot_mapping):
+    if k.is_cuda:
+        _c().reshape_and_cache(k, v, kv_cache, slot_mapping)
+    else:
+        _ra.reshape_and_cache(k, v, kv_cache, slot_mapping)
+
+
+def qkv_split_norm_rope_cache(qkv, positions, cos_sin_cache, q_weight, k_weight, eps: float,
+                              num_heads: int, num_kv_heads: int, head_dim: int, neox: bool,
+                              kv_cache, slot_mapping, gemma: bool = False):
+    """One pass over a fused qkv row: split, optional per-head q/k RMSNorm, RoPE, and the K/V
+    scatter into the paged cache (``_C::split_norm_rope_neox`` + ``reshape_and_cache_flash`` of the
+    reference in a single kernel).  Returns the rotated ``q [T, Hq*D]``."""
+    T = qkv.shape[0]
+    if qkv.is_cuda:
+        q = torch.empty(T, num_heads * head_dim, dtype=qkv.dtype, device=qkv.device)
+        _c().qkv_split_norm_rope_cache(q, qkv, positions, cos_sin_cache, q_weight, k_weight, eps,
+                                       num_heads, num_kv_heads, head_dim, neox, gemma, kv_cache, slot_mapping)
+        return q
+    q, k, v = _rb.split_qknorm_rope(qkv, positions, cos_sin_cache, q_weight, k_weight, eps,
+                                    num_heads, num_kv_heads, head_dim, neox, gemma)
+    if kv_cache is not None:
+        _ra.reshape_and_cache(k.reshape(T, num_kv_heads, head_dim), v.reshape(T, num_kv_heads, head_dim),
+                              kv_cache, slot_mapping)
+    return q
+
+
+def concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping):
+    if kv_c.is_cuda:
+        _c().concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping)
+    elif kv_cache.dtype == torch.uint8:
+        _ra.concat_and_cache_mla_fp8(kv_c, k_pe, kv_cache, slot_mapping)
+    else:
+        _ra.concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping)
+
+
+def indexer_k_quant_and_cache(k, k_cache, slot_mapping, ue8m0: bool = True):
+    if k.is_cuda:
+        _c().indexer_k_quant_and_cache(k, k_cache, slot_mapping, ue8m0)
+    else:
+        _ra.indexer_k_quant_and_cache(k, k_cache, slot_mapping, ue8m0)
+
+
+def convert_req_index_to_global_index(req_id, block_table, token_indices, block_size: int):
+    if token_indices.is_cuda:
+        out = torch.empty_like(token_indices, dtype=torch.int32)
+        _c().convert_req_index_to_global_index(out, req_id, block_table, token_indices, block_size)
+        return out
+    return _ra.convert_req_index_to_global_index(req_id, block_table, token_indices, block_size)
+
+
+def copy_blocks(caches, mapping):
+    if caches and caches[0].is_cuda:
+        src = torch.tensor([m[0] for m in mapping], dtype=torch.int64, device=caches[0].device)
+        dst = torch.tensor([m[1] for m in mapping], dtype=torch.int64, device=caches[0].device)
+        for c in caches:
+            _c().copy_blocks(c, src, dst)
+    else:
+        _ra.copy_blocks(caches, mapping)
+
+
+def swap_blocks(src, dst, mapping):
+    """Host<->device or device<->device block moves: one async copy per block."""
+    for s, d in mapping:
+        dst[d].copy_(src[s], non_blocking=True)
+
+
+# ----------------------------------------------------------------------------- attention
+
+def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
+                    max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
+                    seq_lens_cpu=None, query_start_loc_cpu=None, out=None, workspace=None):
+    """Unified varlen paged GQA attention (prefill with prefix, decode, spec-verify)."""
+    if q.is_cuda:
+        if out is None:
+            out = torch.empty(q.shape[0], q.shape[1], kv_cache.shape[-1], dtype=q.dtype, device=q.device)
+        from .attention_cuda import paged_attention_cuda
+        return paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
+                                    max_query_len, max_seq_len, window, sinks, workspace)
+    sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
+    ql = query_start_loc if query_start_loc_cpu is None else query_start_loc_cpu
+    return _ra.paged_attention(q, kv_cache, block_tables, sl, ql, scale, window, sinks)
+
+
+def merge_attn_states(o1, lse1, o2, lse2):
+    if o1.is_cuda:
+        out = torch.empty_like(o1)
+        lse = torch.empty_like(lse1)
+        _c().merge_attn_states(out, lse, o1, lse1, o2, lse2)
+        return out, lse
+    return _ra.merge_attn_states(o1, lse1, o2, lse2)
+
+
+# ----------------------------------------------------------------------------- GEMM
+
+def linear(x, weight, bias=None, out=None):
+    """``y = x @ W.T (+ b)``, ``W [N, K]`` as stored in checkpoints.  CUDA: the tcgen05 GEMM."""
+    if x.is_cuda:
+        from .gemm_cuda import gemm_bf16
+        return gemm_bf16(x, weight, bias, out)
+    return _rb.linear(x, weight, bias)
+
+
+def embedding(ids, weight, vocab_start: int = 0):
+    """Vocab-parallel gather: rows outside ``[vocab_start, vocab_start + rows)`` yield zeros
+    (``ops/vocab_parallel_embedding.py:94-118``)."""
+    if ids.is_cuda:
+        out = torch.empty(ids.shape[0], weight.shape[1], dtype=weight.dtype, device=weight.device)
+        _c().embedding(out, ids, weight, vocab_start)
+        return out
+    local = ids.long() - vocab_start
+    ok = (local >= 0) & (local < weight.shape[0])
+    out = weight[local.clamp(0, weight.shape[0] - 1)]
+    return out * ok.unsqueeze(-1).to(out.dtype)
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def argmax(logits):
+    if logits.is_cuda:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+        _c().argmax(out, logits)
+        return out
+    return logits.float().argmax(-1)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]
