@@ -1,0 +1,79 @@
+// C ABI of the sm_100a kernel library.  Kernel sources include only this header and CUDA headers
+// (no libtorch), so they compile in seconds; bindings.cpp adapts torch tensors to these calls.
+// Every launcher returns 0 on success, a cudaError_t value or a small positive code on bad arguments.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// dtype codes: 0 = float32, 1 = bfloat16, 2 = float16
+
+// ---- GEMM (tcgen05) -------------------------------------------------------------------------
+typedef struct GemmArgs {
+  void* out;          // [T, ldo] bf16/fp16
+  const void* bias;   // [N] or null
+  float* ws;          // split-K partial tiles (tiles * splits * bn * 128 floats)
+  int* counters;      // per-tile arrival tickets, zero on entry, zero again on exit
+  int* status;        // device status word: 0 = ok, otherwise the code of the wait that timed out
+  int T, N, K;
+  int n_tiles, t_tiles, splits, kb_per_split;
+  int fmt;            // 1 = bf16, 0 = fp16
+  int ldo;            // row stride of out (elements)
+  int bn;             // token tile: 16 / 32 / 64 / 128 / 256
+  int num_sms;
+} GemmArgs;
+int b200_gemm_pick_bn(int T);
+int b200_gemm_launch(const GemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
+
+// Encodes a 2-D row-major [rows, cols] tensor map with a [box_rows, box_cols] box and 128-byte
+// swizzle into `out` (128 bytes).  elem_bytes = 1 or 2.
+int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                        uint32_t box_rows, uint32_t box_cols, int elem_bytes);
+
+// ---- elementwise ----------------------------------------------------------------------------
+int b200_rmsnorm(void* out, const void* x, void* residual, const void* w, int64_t rows, int H, float eps, int gemma,
+                 int64_t x_stride, int64_t out_stride, int dtype, cudaStream_t st);
+int b200_rownorm(void* out, const void* x, const void* z, const void* w, int64_t rows, int D, float eps, int mode,
+                 int dtype, cudaStream_t st);
+int b200_act_and_mul(void* out, const void* x, int64_t rows, int d, int act, int dtype, cudaStream_t st);
+int b200_quick_gelu(void* out, const void* x, int64_t n, int dtype, cudaStream_t st);
+int b200_embedding(void* out, const int64_t* ids, const void* w, int64_t T, int H, int64_t rows, int64_t vocab_start,
+                   int dtype, cudaStream_t st);
+int b200_argmax(int64_t* out, const void* logits, int64_t rows, int V, int64_t stride, int dtype, cudaStream_t st);
+
+// ---- rotary / cache -------------------------------------------------------------------------
+int b200_qkv_split_norm_rope_cache(void* q_out, const void* qkv, const int64_t* positions, const float* cos_sin,
+                                   const void* q_w, const void* k_w, float eps, int64_t T, int Hq, int Hkv, int D,
+                                   int rot_dim, int neox, int gemma, void* kv_cache, const int64_t* slots,
+                                   int block_size, int64_t num_blocks, int64_t max_pos, int64_t qkv_stride, int dtype,
+                                   cudaStream_t st);
+int b200_rope(void* q, void* k, const int64_t* positions, const float* cos_sin, int64_t T, int Hq, int Hk, int D,
+              int rot_dim, int neox, int64_t max_pos, int64_t q_stride, int64_t k_stride, const int64_t* positions3,
+              int sec0, int sec1, int interleaved, int dtype, cudaStream_t st);
+int b200_reshape_and_cache(const void* k, const void* v, void* kv_cache, const int64_t* slots, int64_t T, int Hkv,
+                           int D, int block_size, int64_t num_blocks, int64_t k_stride, int64_t v_stride, int dtype,
+                           cudaStream_t st);
+int b200_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* cache, const int64_t* slots, int64_t T,
+                              int rank, int rope, int64_t total_slots, int64_t kvc_stride, int64_t kpe_stride, int fp8,
+                              int dtype, cudaStream_t st);
+int b200_indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slots, int64_t T, int64_t total_slots,
+                                   int ue8m0, int64_t k_stride, int dtype, cudaStream_t st);
+int b200_convert_req_index(int32_t* out, const int32_t* req_id, const int32_t* block_table, const int32_t* idx,
+                           int64_t T, int topk, int block_size, int max_blocks, int num_reqs, cudaStream_t st);
+int b200_copy_blocks(void* cache, const int64_t* src, const int64_t* dst, int64_t n_pairs, int64_t bytes_per_block,
+                     int64_t num_blocks, cudaStream_t st);
+int b200_merge_attn_states(void* out, float* lse_out, const void* o1, const float* lse1, const void* o2,
+                           const float* lse2, int64_t rows, int D, int dtype, cudaStream_t st);
+
+// ---- attention ------------------------------------------------------------------------------
+int b200_paged_attention(void* out, const void* q, const void* kv_cache, const int* block_tables, const int* seq_lens,
+                         const int* qsl, const float* sinks, float* ws_o, float* ws_lse, int64_t T, int B, int Hq,
+                         int Hkv, int D, int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
+                         int num_splits, int window, float scale, int decode_layout, int dtype, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

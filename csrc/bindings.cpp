@@ -1,0 +1,315 @@
+// Python bindings: torch tensors -> the C ABI in api.h.  Also hosts the small C++ runtime pieces
+// (weak_ref_tensor, tensor-map cache, GEMM workspace).
+//
+// weak_ref_tensor mirrors the one native function of the reference (vllm_kunlun/csrc/utils.cpp:4-32):
+// an alias of a CUDA tensor that does not own its storage, used to hold CUDA-graph outputs without
+// keeping the allocation alive.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+
+namespace {
+
+int dtype_code(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return 0;
+    case at::kBFloat16: return 1;
+    case at::kHalf: return 2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+  }
+}
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+at::Tensor weak_ref_tensor(const at::Tensor& t) {
+  TORCH_CHECK(t.is_cuda(), "weak_ref_tensor expects a CUDA tensor");
+  return torch::from_blob(t.data_ptr(), t.sizes(), t.strides(), t.options());
+}
+
+// ---------------------------------------------------------------------------------------- GEMM
+struct TmapKey {
+  const void* p; int64_t rows, cols, stride; int box_rows;
+  bool operator==(const TmapKey& o) const {
+    return p == o.p && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows;
+  }
+};
+struct TmapHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = std::hash<const void*>()(k.p);
+    h ^= std::hash<int64_t>()(k.rows * 1315423911u + k.cols) + 0x9e3779b9 + (h << 6) + (h >> 2);
+    h ^= std::hash<int64_t>()(k.stride * 31 + k.box_rows) + 0x9e3779b9 + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+struct alignas(64) Tmap { unsigned char b[128]; };
+
+struct GemmState {
+  std::mutex mu;
+  std::unordered_map<TmapKey, Tmap, TmapHash> cache;
+  at::Tensor ws, counters, status;
+  int num_sms = 0;
+  int64_t launches = 0;
+};
+GemmState& gemm_state() { static GemmState s; return s; }
+
+const Tmap& get_tmap(GemmState& gs, const at::Tensor& t, int box_rows, int elem_bytes) {
+  TmapKey key{t.data_ptr(), t.size(0), t.size(1), t.stride(0), box_rows};
+  auto it = gs.cache.find(key);
+  if (it != gs.cache.end()) return it->second;
+  if (gs.cache.size() > 4096) gs.cache.clear();
+  Tmap tm;
+  int rc = b200_encode_tmap_2d(tm.b, t.data_ptr(), t.size(0), t.size(1), t.stride(0) * elem_bytes, box_rows,
+                               128 / elem_bytes, elem_bytes);
+  TORCH_CHECK(rc == 0, "tensor map encode failed: ", rc);
+  return gs.cache.emplace(key, tm).first->second;
+}
+
+// out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  splits <= 0 lets the library choose.
+void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+          int64_t splits, int64_t bn_override) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda());
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2);
+  TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == out.scalar_type());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "gemm: bf16/fp16 only");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1);
+  const int T = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == T && out.size(1) == N);
+  TORCH_CHECK(K % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0, "gemm: K and row strides must be multiples of 8");
+  if (T == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(x.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, x.options().dtype(at::kFloat));        // 64 MiB of split-K partials
+    gs.counters = at::zeros({1 << 16}, x.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, x.options().dtype(at::kInt));
+  }
+  GemmArgs a;
+  a.bn = bn_override > 0 ? (int)bn_override : b200_gemm_pick_bn(T);
+  a.T = T; a.N = N; a.K = K;
+  a.n_tiles = (N + 127) / 128;
+  a.t_tiles = (T + a.bn - 1) / a.bn;
+  const int total_kb = (K + 63) / 64;
+  int tiles = a.n_tiles * a.t_tiles;
+  int sp = (int)splits;
+  if (sp <= 0) {
+    // choose the split count that fills the SMs best; each split must keep >= 4 k-blocks
+    sp = 1;
+    double best = 0;
+    int max_sp = std::max(1, std::min(16, total_kb / 4));
+    if (tiles >= 2 * gs.num_sms) max_sp = 1;
+    for (int s = 1; s <= max_sp; ++s) {
+      int items = tiles * s;
+      int waves = (items + gs.num_sms - 1) / gs.num_sms;
+      double eff = (double)items / (waves * gs.num_sms) * (1.0 - 0.015 * (s - 1));
+      if (eff > best + 1e-9) { best = eff; sp = s; }
+    }
+  }
+  a.kb_per_split = (total_kb + sp - 1) / sp;
+  sp = (total_kb + a.kb_per_split - 1) / a.kb_per_split;  // no empty split
+  if ((int64_t)tiles * sp * a.bn * 128 > gs.ws.numel() || tiles > gs.counters.numel()) {
+    sp = 1;
+    a.kb_per_split = total_kb;
+  }
+  a.splits = sp;
+  a.out = out.data_ptr();
+  a.bias = opt_ptr(bias);
+  a.ws = gs.ws.data_ptr<float>();
+  a.counters = gs.counters.data_ptr<int>();
+  a.status = gs.status.data_ptr<int>();
+  a.fmt = x.scalar_type() == at::kBFloat16 ? 1 : 0;
+  a.ldo = out.stride(0);
+  a.num_sms = gs.num_sms;
+  const Tmap& tw = get_tmap(gs, w, 128, 2);
+  const Tmap& tx = get_tmap(gs, x, a.bn, 2);
+  check(b200_gemm_launch(&a, tw.b, tx.b, stream()), "gemm launch");
+  gs.launches++;
+}
+
+int64_t gemm_status() {
+  GemmState& gs = gemm_state();
+  if (!gs.status.defined()) return 0;
+  return gs.status.item<int>();
+}
+void gemm_clear_tmap_cache() { gemm_state().cache.clear(); }
+
+// ---------------------------------------------------------------------------------------- elementwise
+void rmsnorm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, double eps, bool gemma) {
+  int H = x.size(-1);
+  int64_t rows = x.numel() / H;
+  TORCH_CHECK(x.stride(-1) == 1 && out.is_contiguous());
+  int64_t xs = x.dim() >= 2 ? x.stride(-2) : H;
+  if (x.dim() > 2) TORCH_CHECK(x.is_contiguous());
+  check(b200_rmsnorm(out.data_ptr(), x.data_ptr(), nullptr, w.data_ptr(), rows, H, (float)eps, gemma, xs, H,
+                     dtype_code(x), stream()), "rmsnorm");
+}
+void add_rmsnorm(at::Tensor x, at::Tensor residual, const at::Tensor& w, double eps, bool gemma) {
+  int H = x.size(-1);
+  int64_t rows = x.numel() / H;
+  TORCH_CHECK(x.is_contiguous() && residual.is_contiguous());
+  check(b200_rmsnorm(x.data_ptr(), x.data_ptr(), residual.data_ptr(), w.data_ptr(), rows, H, (float)eps, gemma, H, H,
+                     dtype_code(x), stream()), "add_rmsnorm");
+}
+void rownorm(at::Tensor out, const at::Tensor& x, const c10::optional<at::Tensor>& z,
+             const c10::optional<at::Tensor>& w, double eps, int64_t mode) {
+  int D = x.size(-1);
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous());
+  check(b200_rownorm(out.data_ptr(), x.data_ptr(), opt_ptr(z), opt_ptr(w), x.numel() / D, D, (float)eps, (int)mode,
+                     dtype_code(x), stream()), "rownorm");
+}
+void act_and_mul(at::Tensor out, const at::Tensor& x, int64_t act) {
+  int d = x.size(-1) / 2;
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous());
+  check(b200_act_and_mul(out.data_ptr(), x.data_ptr(), x.numel() / (2 * d), d, (int)act, dtype_code(x), stream()),
+        "act_and_mul");
+}
+void quick_gelu(at::Tensor out, const at::Tensor& x) {
+  TORCH_CHECK(x.is_contiguous());
+  check(b200_quick_gelu(out.data_ptr(), x.data_ptr(), x.numel(), dtype_code(x), stream()), "quick_gelu");
+}
+void embedding(at::Tensor out, const at::Tensor& ids, const at::Tensor& w, int64_t vocab_start) {
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && w.is_contiguous());
+  check(b200_embedding(out.data_ptr(), ids.data_ptr<int64_t>(), w.data_ptr(), ids.numel(), w.size(1), w.size(0),
+                       vocab_start, dtype_code(w), stream()), "embedding");
+}
+void argmax(at::Tensor out, const at::Tensor& logits) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong);
+  check(b200_argmax(out.data_ptr<int64_t>(), logits.data_ptr(), logits.size(0), logits.size(1), logits.stride(0),
+                    dtype_code(logits), stream()), "argmax");
+}
+
+// ---------------------------------------------------------------------------------------- rotary / cache
+void qkv_split_norm_rope_cache(at::Tensor q_out, const at::Tensor& qkv, const at::Tensor& positions,
+                               const at::Tensor& cos_sin, const c10::optional<at::Tensor>& q_w,
+                               const c10::optional<at::Tensor>& k_w, double eps, int64_t Hq, int64_t Hkv, int64_t D,
+                               bool neox, bool gemma, const c10::optional<at::Tensor>& kv_cache,
+                               const at::Tensor& slots) {
+  TORCH_CHECK(qkv.stride(1) == 1 && cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous());
+  TORCH_CHECK(positions.scalar_type() == at::kLong && slots.scalar_type() == at::kLong);
+  int block_size = 0;
+  int64_t num_blocks = 0;
+  if (kv_cache.has_value()) {
+    TORCH_CHECK(kv_cache->is_contiguous() && kv_cache->dim() == 5 && kv_cache->size(2) == Hkv && kv_cache->size(4) == D);
+    block_size = kv_cache->size(3);
+    num_blocks = kv_cache->size(0);
+  }
+  check(b200_qkv_split_norm_rope_cache(q_out.data_ptr(), qkv.data_ptr(), positions.data_ptr<int64_t>(),
+                                       cos_sin.data_ptr<float>(), opt_ptr(q_w), opt_ptr(k_w), (float)eps,
+                                       qkv.size(0), Hq, Hkv, D, cos_sin.size(1), neox, gemma,
+                                       kv_cache.has_value() ? kv_cache->data_ptr() : nullptr,
+                                       slots.data_ptr<int64_t>(), block_size, num_blocks, cos_sin.size(0),
+                                       qkv.stride(0), dtype_code(qkv), stream()), "qkv_split_norm_rope_cache");
+}
+void rope(at::Tensor q, at::Tensor k, const at::Tensor& positions, const at::Tensor& cos_sin, int64_t D, bool neox) {
+  TORCH_CHECK(q.stride(-1) == 1 && k.stride(-1) == 1 && q.dim() == 2 && k.dim() == 2);
+  check(b200_rope(q.data_ptr(), k.data_ptr(), positions.data_ptr<int64_t>(), cos_sin.data_ptr<float>(), q.size(0),
+                  q.size(1) / D, k.size(1) / D, D, cos_sin.size(1), neox, cos_sin.size(0), q.stride(0), k.stride(0),
+                  nullptr, 0, 0, 0, dtype_code(q), stream()), "rope");
+}
+void mrope(at::Tensor q, at::Tensor k, const at::Tensor& positions3, const at::Tensor& cos_sin, int64_t D,
+           std::vector<int64_t> sections, bool interleaved) {
+  TORCH_CHECK(positions3.is_contiguous() && positions3.size(0) == 3 && sections.size() == 3);
+  check(b200_rope(q.data_ptr(), k.data_ptr(), nullptr, cos_sin.data_ptr<float>(), q.size(0), q.size(1) / D,
+                  k.size(1) / D, D, cos_sin.size(1), 1, cos_sin.size(0), q.stride(0), k.stride(0),
+                  positions3.data_ptr<int64_t>(), sections[0], sections[1], interleaved, dtype_code(q), stream()),
+        "mrope");
+}
+void reshape_and_cache(const at::Tensor& k, const at::Tensor& v, at::Tensor kv_cache, const at::Tensor& slots) {
+  TORCH_CHECK(kv_cache.is_contiguous() && kv_cache.dim() == 5);
+  int Hkv = kv_cache.size(2), D = kv_cache.size(4);
+  auto k2 = k.reshape({k.size(0), -1}), v2 = v.reshape({v.size(0), -1});
+  TORCH_CHECK(k2.stride(1) == 1 && v2.stride(1) == 1 && k2.size(1) == Hkv * D);
+  check(b200_reshape_and_cache(k2.data_ptr(), v2.data_ptr(), kv_cache.data_ptr(), slots.data_ptr<int64_t>(),
+                               k2.size(0), Hkv, D, kv_cache.size(3), kv_cache.size(0), k2.stride(0), v2.stride(0),
+                               dtype_code(k), stream()), "reshape_and_cache");
+}
+void concat_and_cache_mla(const at::Tensor& kv_c, const at::Tensor& k_pe, at::Tensor cache, const at::Tensor& slots) {
+  TORCH_CHECK(cache.is_contiguous() && cache.dim() == 3 && kv_c.stride(-1) == 1 && k_pe.stride(-1) == 1);
+  bool fp8 = cache.scalar_type() == at::kByte;
+  auto pe = k_pe.reshape({k_pe.size(0), -1});
+  check(b200_concat_and_cache_mla(kv_c.data_ptr(), pe.data_ptr(), cache.data_ptr(), slots.data_ptr<int64_t>(),
+                                  kv_c.size(0), kv_c.size(1), pe.size(1), cache.size(0) * cache.size(1),
+                                  kv_c.stride(0), pe.stride(0), fp8, dtype_code(kv_c), stream()),
+        "concat_and_cache_mla");
+}
+void indexer_k_quant_and_cache(const at::Tensor& k, at::Tensor cache, const at::Tensor& slots, bool ue8m0) {
+  TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte && cache.size(-1) == 132 && k.size(1) == 128);
+  check(b200_indexer_k_quant_and_cache(k.data_ptr(), cache.data_ptr(), slots.data_ptr<int64_t>(), k.size(0),
+                                       cache.size(0) * cache.size(1), ue8m0, k.stride(0), dtype_code(k), stream()),
+        "indexer_k_quant_and_cache");
+}
+void convert_req_index_to_global_index(at::Tensor out, const at::Tensor& req_id, const at::Tensor& block_table,
+                                       const at::Tensor& idx, int64_t block_size) {
+  TORCH_CHECK(req_id.scalar_type() == at::kInt && block_table.scalar_type() == at::kInt && idx.scalar_type() == at::kInt);
+  TORCH_CHECK(block_table.is_contiguous() && idx.is_contiguous());
+  check(b200_convert_req_index(out.data_ptr<int32_t>(), req_id.data_ptr<int32_t>(), block_table.data_ptr<int32_t>(),
+                               idx.data_ptr<int32_t>(), idx.size(0), idx.size(1), block_size, block_table.size(1),
+                               block_table.size(0), stream()), "convert_req_index");
+}
+void copy_blocks(at::Tensor cache, const at::Tensor& src, const at::Tensor& dst) {
+  TORCH_CHECK(cache.is_contiguous());
+  int64_t bytes = cache.numel() / cache.size(0) * cache.element_size();
+  check(b200_copy_blocks(cache.data_ptr(), src.data_ptr<int64_t>(), dst.data_ptr<int64_t>(), src.numel(), bytes,
+                         cache.size(0), stream()), "copy_blocks");
+}
+void merge_attn_states(at::Tensor out, c10::optional<at::Tensor> lse_out, const at::Tensor& o1, const at::Tensor& lse1,
+                       const at::Tensor& o2, const at::Tensor& lse2) {
+  TORCH_CHECK(o1.is_contiguous() && o2.is_contiguous() && lse1.is_contiguous() && lse2.is_contiguous());
+  int D = o1.size(-1);
+  check(b200_merge_attn_states(out.data_ptr(), lse_out.has_value() ? lse_out->data_ptr<float>() : nullptr,
+                               o1.data_ptr(), lse1.data_ptr<float>(), o2.data_ptr(), lse2.data_ptr<float>(),
+                               o1.numel() / D, D, dtype_code(o1), stream()), "merge_attn_states");
+}
+
+// ---------------------------------------------------------------------------------------- attention
+void paged_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_cache, const at::Tensor& block_tables,
+                     const at::Tensor& seq_lens, const at::Tensor& qsl, const c10::optional<at::Tensor>& sinks,
+                     const c10::optional<at::Tensor>& ws_o, const c10::optional<at::Tensor>& ws_lse,
+                     int64_t max_query_len, int64_t num_splits, int64_t window, double scale, bool decode_layout) {
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && kv_cache.is_contiguous() && q.dim() == 3);
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
+  TORCH_CHECK(block_tables.stride(1) == 1);
+  if (num_splits > 1) TORCH_CHECK(ws_o.has_value() && ws_lse.has_value());
+  int B = seq_lens.size(0);
+  check(b200_paged_attention(out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(), block_tables.data_ptr<int>(),
+                             seq_lens.data_ptr<int>(), qsl.data_ptr<int>(),
+                             sinks.has_value() ? sinks->data_ptr<float>() : nullptr,
+                             ws_o.has_value() ? ws_o->data_ptr<float>() : nullptr,
+                             ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, q.size(0), B, q.size(1),
+                             kv_cache.size(2), q.size(2), kv_cache.size(3), block_tables.stride(0), kv_cache.size(0),
+                             max_query_len, num_splits, window, (float)scale, decode_layout, dtype_code(q), stream()),
+        "paged_attention");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("weak_ref_tensor", &weak_ref_tensor);
+  m.def("gemm", &gemm);
+  m.def("gemm_status", &gemm_status);
+  m.def("gemm_clear_tmap_cache", &gemm_clear_tmap_cache);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("add_rmsnorm", &add_rmsnorm);
+  m.def("rownorm", &rownorm);
+  m.def("act_and_mul", &act_and_mul);
+  m.def("quick_gelu", &quick_gelu);
+  m.def("embedding", &embedding);
+  m.def("argmax", &argmax);
+  m.def("qkv_split_norm_rope_cache", &qkv_split_norm_rope_cache);
+  m.def("rope", &rope);
+  m.def("mrope", &mrope);
+  m.def("reshape_and_cache", &reshape_and_cache);
+  m.def("concat_and_cache_mla", &concat_and_cache_mla);
+  m.def("indexer_k_quant_and_cache", &indexer_k_quant_and_cache);
+  m.def("convert_req_index_to_global_index", &convert_req_index_to_global_index);
+  m.def("copy_blocks", &copy_blocks);
+  m.def("merge_attn_states", &merge_attn_states);
+  m.def("paged_attention", &paged_attention);
+}

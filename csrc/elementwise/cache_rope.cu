@@ -1,0 +1,336 @@
+// Rotary embedding and KV-cache movement kernels.
+//
+// Cache layouts (see vllm_kunlun_b200/ops/reference/attention.py):
+//   GQA     kv_cache[block][2][kv_head][slot_in_block][head_dim]
+//   MLA     kv_cache[block][slot_in_block][576]   (bf16) or uint8 [..][656] (512 e4m3 | 4 f32 | 64 bf16)
+//   indexer k_cache[block][slot_in_block][132]    (128 e4m3 | 1 f32)
+// Slot ids < 0 mark padding rows and are skipped.  Every index read from a table is range-checked
+// against the tensor bounds before it is used as an address.
+#include <cuda_fp8.h>
+#include <math.h>
+
+#include "../api.h"
+#include "../common/utils.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ void rope_pair(float& a, float& b, float c, float s) {
+  float x = a, y = b;
+  a = x * c - y * s;
+  b = y * c + x * s;
+}
+
+// One warp per (token, head).  Heads [0, Hq) are queries, [Hq, Hq+Hkv) keys, the rest values.
+template <typename T>
+__global__ void qkv_split_norm_rope_cache_kernel(
+    T* __restrict__ q_out, const T* __restrict__ qkv, const int64_t* __restrict__ positions,
+    const float* __restrict__ cos_sin, const T* __restrict__ q_w, const T* __restrict__ k_w, float eps, int Hq,
+    int Hkv, int D, int rot_dim, int neox, int gemma, T* __restrict__ kv_cache, const int64_t* __restrict__ slots,
+    int block_size, int64_t num_blocks, int64_t max_pos, int64_t qkv_stride) {
+  extern __shared__ float sm[];
+  const int warps = blockDim.x >> 5;
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = blockIdx.x;
+  const int head = blockIdx.y * warps + wid;
+  const int total_heads = Hq + 2 * Hkv;
+  if (head >= total_heads) return;
+  float* buf = sm + wid * D;
+  const T* src = qkv + t * qkv_stride + (int64_t)head * D;
+  const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
+  for (int i = lane; i < D; i += 32) buf[i] = to_f(src[i]);
+  __syncwarp();
+  if (is_q || is_k) {
+    const T* w = is_q ? q_w : k_w;
+    if (w != nullptr) {
+      float ss = 0.f;
+      for (int i = lane; i < D; i += 32) ss += buf[i] * buf[i];
+      ss = warp_sum(ss);
+      float inv = rsqrtf(ss / D + eps);
+      // round to T between norm and rotary, as two separate kernels would
+      for (int i = lane; i < D; i += 32) buf[i] = to_f(from_f<T>(buf[i] * inv * (to_f(w[i]) + (gemma ? 1.f : 0.f))));
+      __syncwarp();
+    }
+    int64_t pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + pos * rot_dim;
+    const int half = rot_dim >> 1;
+    for (int j = lane; j < half; j += 32) {
+      float c = cs[j], s = cs[half + j];
+      if (neox) rope_pair(buf[j], buf[j + half], c, s);
+      else rope_pair(buf[2 * j], buf[2 * j + 1], c, s);
+    }
+    __syncwarp();
+  }
+  if (is_q) {
+    T* dst = q_out + (t * Hq + head) * (int64_t)D;
+    for (int i = lane; i < D; i += 32) dst[i] = from_f<T>(buf[i]);
+  } else if (kv_cache != nullptr) {
+    int64_t slot = slots[t];
+    if (slot < 0 || slot >= num_blocks * block_size) return;
+    int kvh = is_k ? head - Hq : head - Hq - Hkv;
+    int64_t blk = slot / block_size, off = slot % block_size;
+    T* dst = kv_cache + ((((blk * 2 + (is_k ? 0 : 1)) * Hkv + kvh) * block_size + off) * (int64_t)D);
+    for (int i = lane; i < D; i += 32) dst[i] = from_f<T>(buf[i]);
+  }
+}
+
+// In-place rotary on separate q [T, Hq*D] and k [T, Hk*D] (rows may be strided).
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ q, T* __restrict__ k, const int64_t* __restrict__ positions,
+                            const float* __restrict__ cos_sin, int Hq, int Hk, int D, int rot_dim, int neox,
+                            int64_t max_pos, int64_t q_stride, int64_t k_stride, const int64_t* positions3,
+                            int sec0, int sec1, int interleaved, int64_t T_) {
+  const int warps = blockDim.x >> 5;
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = blockIdx.x;
+  const int head = blockIdx.y * warps + wid;
+  if (head >= Hq + Hk) return;
+  T* p = head < Hq ? q + t * q_stride + (int64_t)head * D : k + t * k_stride + (int64_t)(head - Hq) * D;
+  const int half = rot_dim >> 1;
+  for (int j = lane; j < half; j += 32) {
+    int64_t pos;
+    if (positions3 != nullptr) {  // M-RoPE: frequency slot j takes the temporal / height / width position
+      int axis;
+      if (interleaved) axis = (j % 3 == 1 && j < sec1 * 3) ? 1 : ((j % 3 == 2 && j < (rot_dim / 2 - sec0 - sec1) * 3) ? 2 : 0);
+      else axis = j < sec0 ? 0 : (j < sec0 + sec1 ? 1 : 2);
+      pos = positions3[axis * T_ + t];
+    } else {
+      pos = positions[t];
+    }
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + pos * rot_dim;
+    float c = cs[j], s = cs[half + j];
+    int ia = neox ? j : 2 * j, ib = neox ? j + half : 2 * j + 1;
+    float a = to_f(p[ia]), b = to_f(p[ib]);
+    rope_pair(a, b, c, s);
+    p[ia] = from_f<T>(a);
+    p[ib] = from_f<T>(b);
+  }
+}
+
+template <typename T>
+__global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ kv_cache,
+                                         const int64_t* __restrict__ slots, int Hkv, int D, int block_size,
+                                         int64_t num_blocks, int64_t k_stride, int64_t v_stride) {
+  const int64_t t = blockIdx.x;
+  int64_t slot = slots[t];
+  if (slot < 0 || slot >= num_blocks * block_size) return;
+  int64_t blk = slot / block_size, off = slot % block_size;
+  for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
+    int h = i / D, d = i % D;
+    kv_cache[(((blk * 2 + 0) * Hkv + h) * block_size + off) * (int64_t)D + d] = k[t * k_stride + i];
+    kv_cache[(((blk * 2 + 1) * Hkv + h) * block_size + off) * (int64_t)D + d] = v[t * v_stride + i];
+  }
+}
+
+template <typename T>
+__global__ void concat_and_cache_mla_kernel(const T* __restrict__ kv_c, const T* __restrict__ k_pe,
+                                            T* __restrict__ cache, const int64_t* __restrict__ slots, int rank,
+                                            int rope, int64_t total_slots, int64_t kvc_stride, int64_t kpe_stride) {
+  const int64_t t = blockIdx.x;
+  int64_t slot = slots[t];
+  if (slot < 0 || slot >= total_slots) return;
+  T* dst = cache + slot * (int64_t)(rank + rope);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = kv_c[t * kvc_stride + i];
+  for (int i = threadIdx.x; i < rope; i += blockDim.x) dst[rank + i] = k_pe[t * kpe_stride + i];
+}
+
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// 656-byte rows: 4 x (128 e4m3) | 4 x f32 scale | 64 bf16.  One block of 128 threads per token:
+// warp g quantises group g.
+template <typename T>
+__global__ void __launch_bounds__(128) concat_and_cache_mla_fp8_kernel(
+    const T* __restrict__ kv_c, const T* __restrict__ k_pe, uint8_t* __restrict__ cache,
+    const int64_t* __restrict__ slots, int64_t total_slots, int64_t kvc_stride, int64_t kpe_stride) {
+  const int64_t t = blockIdx.x;
+  int64_t slot = slots[t];
+  if (slot < 0 || slot >= total_slots) return;
+  uint8_t* row = cache + slot * 656;
+  int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = to_f(kv_c[t * kvc_stride + g * 128 + lane * 4 + j]);
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  float scale = amax / 448.f;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) packed |= (uint32_t)to_e4m3(v[j] / scale) << (8 * j);
+  reinterpret_cast<uint32_t*>(row)[g * 32 + lane] = packed;
+  if (lane == 0) reinterpret_cast<float*>(row + 512)[g] = scale;
+  if (threadIdx.x < 64) reinterpret_cast<__nv_bfloat16*>(row + 528)[threadIdx.x] =
+      __float2bfloat16(to_f(k_pe[t * kpe_stride + threadIdx.x]));
+}
+
+// 132-byte rows: 128 e4m3 | f32 scale (power of two when ue8m0).  One warp per token.
+template <typename T>
+__global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_t* __restrict__ cache,
+                                                 const int64_t* __restrict__ slots, int64_t T_, int64_t total_slots,
+                                                 int ue8m0, int64_t k_stride) {
+  int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T_) return;
+  int lane = threadIdx.x & 31;
+  int64_t slot = slots[t];
+  if (slot < 0 || slot >= total_slots) return;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = to_f(k[t * k_stride + lane * 4 + j]); amax = fmaxf(amax, fabsf(v[j])); }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  float scale = amax / 448.f;
+  if (ue8m0) scale = exp2f(ceilf(log2f(scale)));
+  uint8_t* row = cache + slot * 132;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) packed |= (uint32_t)to_e4m3(v[j] / scale) << (8 * j);
+  reinterpret_cast<uint32_t*>(row)[lane] = packed;
+  if (lane == 0) *reinterpret_cast<float*>(row + 128) = scale;
+}
+
+__global__ void convert_req_index_kernel(int32_t* __restrict__ out, const int32_t* __restrict__ req_id,
+                                         const int32_t* __restrict__ block_table, const int32_t* __restrict__ idx,
+                                         int64_t T_, int topk, int block_size, int max_blocks, int num_reqs) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T_ * topk) return;
+  int64_t t = i / topk;
+  int v = idx[i];
+  int r = req_id[t];
+  int o = -1;
+  if (v >= 0 && r >= 0 && r < num_reqs) {
+    int b = v / block_size;
+    if (b < max_blocks) o = block_table[(int64_t)r * max_blocks + b] * block_size + v % block_size;
+  }
+  out[i] = o;
+}
+
+__global__ void copy_blocks_kernel(uint4* __restrict__ cache, const int64_t* __restrict__ src,
+                                   const int64_t* __restrict__ dst, int64_t vec_per_block, int64_t num_blocks) {
+  int64_t s = src[blockIdx.x], d = dst[blockIdx.x];
+  if (s < 0 || d < 0 || s >= num_blocks || d >= num_blocks) return;
+  for (int64_t i = threadIdx.x; i < vec_per_block; i += blockDim.x) cache[d * vec_per_block + i] = cache[s * vec_per_block + i];
+}
+
+// out = merge of two partial attention results by log-sum-exp.  o [T,H,D], lse [T,H].
+template <typename T>
+__global__ void merge_attn_states_kernel(T* __restrict__ out, float* __restrict__ lse_out, const T* __restrict__ o1,
+                                         const float* __restrict__ lse1, const T* __restrict__ o2,
+                                         const float* __restrict__ lse2, int64_t rows, int D) {
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  int lane = threadIdx.x & 31;
+  float a = lse1[row], b = lse2[row];
+  float m = fmaxf(a, b);
+  if (isinf(m)) m = 0.f;
+  float w1 = __expf(a - m), w2 = __expf(b - m);
+  float den = fmaxf(w1 + w2, 1e-30f);
+  for (int i = lane; i < D; i += 32)
+    out[row * D + i] = from_f<T>((to_f(o1[row * D + i]) * w1 + to_f(o2[row * D + i]) * w2) / den);
+  if (lane == 0 && lse_out != nullptr) lse_out[row] = m + __logf(den);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_qkv_split_norm_rope_cache(void* q_out, const void* qkv, const int64_t* positions,
+                                               const float* cos_sin, const void* q_w, const void* k_w, float eps,
+                                               int64_t T_, int Hq, int Hkv, int D, int rot_dim, int neox, int gemma,
+                                               void* kv_cache, const int64_t* slots, int block_size,
+                                               int64_t num_blocks, int64_t max_pos, int64_t qkv_stride, int dtype,
+                                               cudaStream_t st) {
+  if (T_ == 0) return 0;
+  const int warps = 4;
+  dim3 grid((unsigned)T_, (Hq + 2 * Hkv + warps - 1) / warps);
+  B200_DISPATCH_DTYPE(dtype, {
+    qkv_split_norm_rope_cache_kernel<T><<<grid, warps * 32, warps * D * sizeof(float), st>>>(
+        (T*)q_out, (const T*)qkv, positions, cos_sin, (const T*)q_w, (const T*)k_w, eps, Hq, Hkv, D, rot_dim, neox,
+        gemma, (T*)kv_cache, slots, block_size, num_blocks, max_pos, qkv_stride);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_rope(void* q, void* k, const int64_t* positions, const float* cos_sin, int64_t T_, int Hq, int Hk,
+                         int D, int rot_dim, int neox, int64_t max_pos, int64_t q_stride, int64_t k_stride,
+                         const int64_t* positions3, int sec0, int sec1, int interleaved, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  const int warps = 4;
+  dim3 grid((unsigned)T_, (Hq + Hk + warps - 1) / warps);
+  B200_DISPATCH_DTYPE(dtype, {
+    rope_kernel<T><<<grid, warps * 32, 0, st>>>((T*)q, (T*)k, positions, cos_sin, Hq, Hk, D, rot_dim, neox, max_pos,
+                                               q_stride, k_stride, positions3, sec0, sec1, interleaved, T_);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_reshape_and_cache(const void* k, const void* v, void* kv_cache, const int64_t* slots, int64_t T_,
+                                      int Hkv, int D, int block_size, int64_t num_blocks, int64_t k_stride,
+                                      int64_t v_stride, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    reshape_and_cache_kernel<T><<<T_, 256, 0, st>>>((const T*)k, (const T*)v, (T*)kv_cache, slots, Hkv, D, block_size,
+                                                   num_blocks, k_stride, v_stride);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* cache, const int64_t* slots,
+                                         int64_t T_, int rank, int rope, int64_t total_slots, int64_t kvc_stride,
+                                         int64_t kpe_stride, int fp8, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    if (fp8) {
+      if (rank != 512 || rope != 64) return 2;
+      concat_and_cache_mla_fp8_kernel<T><<<T_, 128, 0, st>>>((const T*)kv_c, (const T*)k_pe, (uint8_t*)cache, slots,
+                                                            total_slots, kvc_stride, kpe_stride);
+    } else {
+      concat_and_cache_mla_kernel<T><<<T_, 128, 0, st>>>((const T*)kv_c, (const T*)k_pe, (T*)cache, slots, rank, rope,
+                                                        total_slots, kvc_stride, kpe_stride);
+    }
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slots, int64_t T_,
+                                              int64_t total_slots, int ue8m0, int64_t k_stride, int dtype,
+                                              cudaStream_t st) {
+  if (T_ == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    indexer_k_quant_and_cache_kernel<T><<<(T_ + 3) / 4, 128, 0, st>>>((const T*)k, (uint8_t*)cache, slots, T_,
+                                                                     total_slots, ue8m0, k_stride);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_convert_req_index(int32_t* out, const int32_t* req_id, const int32_t* block_table,
+                                      const int32_t* idx, int64_t T_, int topk, int block_size, int max_blocks,
+                                      int num_reqs, cudaStream_t st) {
+  int64_t n = T_ * topk;
+  if (n == 0) return 0;
+  convert_req_index_kernel<<<(n + 255) / 256, 256, 0, st>>>(out, req_id, block_table, idx, T_, topk, block_size,
+                                                           max_blocks, num_reqs);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_copy_blocks(void* cache, const int64_t* src, const int64_t* dst, int64_t n_pairs,
+                                int64_t bytes_per_block, int64_t num_blocks, cudaStream_t st) {
+  if (n_pairs == 0) return 0;
+  if (bytes_per_block % 16) return 2;
+  copy_blocks_kernel<<<n_pairs, 256, 0, st>>>((uint4*)cache, src, dst, bytes_per_block / 16, num_blocks);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_merge_attn_states(void* out, float* lse_out, const void* o1, const float* lse1, const void* o2,
+                                      const float* lse2, int64_t rows, int D, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    merge_attn_states_kernel<T><<<(rows + 7) / 8, 256, 0, st>>>((T*)out, lse_out, (const T*)o1, lse1, (const T*)o2,
+                                                               lse2, rows, D);
+  });
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,345 @@
+// bf16/fp16 GEMM for sm_100a:  out[T, N] = x[T, K] . W[N, K]^T (+ bias[N]),  fp32 accumulation.
+//
+// Orientation: the weight rows are the UMMA "M" side (128 output features per tile, one per TMEM
+// lane) and the tokens are the UMMA "N" side (BN = 16..256 columns).  A decode batch of 16 tokens
+// therefore wastes no tensor-core rows and the kernel streams the weight matrix once at HBM rate;
+// a prefill chunk uses BN = 256.  The same kernel serves both.
+//
+// Structure (192 threads, persistent over work items):
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D tiles (128B swizzle) into a ring of stages
+//   warp 1      allocates TMEM, issues tcgen05.mma (one elected thread), commits to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (double-buffered in TMEM so the next tile's
+//               main loop overlaps), add bias, convert, store; or write split-K partials
+// Split-K: partial tiles go to an fp32 workspace; the last CTA to arrive for a tile (atomic ticket)
+// sums the partials in a fixed order and writes the output, so results are deterministic.
+// Every mbarrier wait is bounded; on time-out the CTA records a code in `status`, drains its
+// outstanding copies, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../api.h"
+#include "../common/ptx.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128;      // features per tile (TMEM lanes)
+constexpr int BK = 64;       // K elements per stage (one 128-byte swizzle row of bf16)
+constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit inputs
+constexpr int kGemmThreads = 192;
+constexpr int kSmemBudget = 200 * 1024;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStageBytesA = BM * BK * 2;
+  static constexpr int kStageBytesB = BN * BK * 2;
+  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct Abort {
+  int* status;
+  volatile int* flag;  // shared-memory abort flag
+  __device__ __forceinline__ bool aborted() const { return *flag != 0; }
+  __device__ __forceinline__ void raise(int code) {
+    *flag = 1;
+    atomicCAS(status, 0, code);
+  }
+};
+
+// Bounded wait that also leaves early once another role of this CTA has given up.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Abort& ab, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < (1u << 20); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255) == 255 && ab.aborted()) return false;
+  }
+  ab.raise(code);
+  return false;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT from_float(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half(v); }
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+               OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
+               int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
+               int t_tiles, int splits, int kb_per_split, int fmt, int ldo) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;                       // [kStages]
+  uint64_t* empty_bar = bars + Cfg::kStages;       // [kStages]
+  uint64_t* tmem_full = bars + 2 * Cfg::kStages;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;            // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  int* ticket_slot = reinterpret_cast<int*>(tmem_base_slot + 2);
+  volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 3);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_kb = (K + BK - 1) / BK;
+  const int total_items = n_tiles * t_tiles * splits;
+  Abort ab{status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmW);
+    prefetch_tmap(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  // item -> (n_tile, t_tile, split).  Splits of one tile are adjacent so they run concurrently;
+  // without split-K, groups of 8 token tiles sweep the feature tiles so that concurrently
+  // resident CTAs share x and W tiles in L2.
+  auto decode = [&](int item, int& nt, int& tt, int& sp) {
+    sp = item % splits;
+    int tile = item / splits;
+    constexpr int G = 8;
+    int group_sz = G * n_tiles;
+    int g = tile / group_sz;
+    int rem = tile - g * group_sz;
+    int g_rows = min(G, t_tiles - g * G);
+    nt = rem / g_rows;
+    tt = g * G + rem % g_rows;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      const uint64_t pol_w = (t_tiles <= 2) ? policy_evict_first() : policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int nt, tt, sp;
+        decode(item, nt, tt, sp);
+        int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 101)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kStageBytesA;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d_hint(sa, &tmW, &full_bar[stage], kb * BK, nt * BM, pol_w);
+          tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
+          ++issued;
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Drain: copies already issued must land before this CTA's shared memory is released.
+        int pending = issued < Cfg::kStages ? issued : Cfg::kStages;
+        for (int i = 0; i < pending; ++i) {
+          int s = (stage - 1 - i + 2 * Cfg::kStages) % Cfg::kStages;
+          uint32_t ph = (s < stage) ? phase : (phase ^ 1);
+          for (uint32_t p = 0; p < (1u << 16); ++p)
+            if (mbar_try_wait(&full_bar[s], ph)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc(BM, BN, fmt, fmt);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
+        int nt, tt, sp;
+        decode(item, nt, tt, sp);
+        int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
+        int buf = local & 1;
+        uint32_t acc_phase = (local >> 1) & 1;
+        if (!wait_or_abort(&tmem_empty[buf], acc_phase ^ 1, ab, 102)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&full_bar[stage], phase, ab, 103)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          uint32_t sb = sa + Cfg::kStageBytesA;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da = umma_desc_k_sw128(sa + k * UMMA_K * 2);
+            uint64_t db = umma_desc_k_sw128(sb + k * UMMA_K * 2);
+            umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    const int ep_tid = (warp - 2) * 32 + lane;
+    int local = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
+      int nt, tt, sp;
+      decode(item, nt, tt, sp);
+      int buf = local & 1;
+      uint32_t acc_phase = (local >> 1) & 1;
+      // One thread does the bounded wait and publishes the verdict, so that the 128 epilogue
+      // threads always agree and none is left alone at a named barrier.
+      if (ep_tid == 0) *ep_ok_slot = wait_or_abort(&tmem_full[buf], acc_phase, ab, 104) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*ep_ok_slot == 0) { ok = false; break; }
+      while (!mbar_try_wait(&tmem_full[buf], acc_phase)) {}  // phase is complete: returns at once
+      tc_fence_after_sync();
+      const int n = nt * BM + quarter * 32 + lane;
+      const int t0 = tt * BN;
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      const bool n_ok = n < N;
+      if (splits == 1) {
+        float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          tmem_ld_x16(taddr + c, r);
+          tmem_ld_wait();
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              int t = t0 + c + j;
+              if (t < T) out[(size_t)t * ldo + n] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      } else {
+        // partial tile -> workspace [tile][split][BN][128]
+        const int tile = item / splits;
+        float* wtile = ws + ((size_t)tile * splits + sp) * (BN * BM);
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          tmem_ld_x16(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) wtile[(c + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ep_tid == 0) {
+          int prev = atomicAdd(&counters[tile], 1);
+          if (prev == splits - 1) counters[tile] = 0;  // re-arm for the next launch / graph replay
+          *ticket_slot = prev;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*ticket_slot == splits - 1) {
+          __threadfence();
+          const float* wbase = ws + (size_t)tile * splits * (BN * BM);
+          float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
+          for (int c = 0; c < BN; ++c) {
+            int t = t0 + c;
+            if (t >= T) break;
+            float acc = bv;
+            for (int s = 0; s < splits; ++s) acc += __ldcg(wbase + (size_t)s * (BN * BM) + c * BM + quarter * 32 + lane);
+            if (n_ok) out[(size_t)t * ldo + n] = from_float<OutT>(acc);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_slot is reused by the next item
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, typename OutT>
+static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CUtensorMap& tmX, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_tn_kernel<BN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  int items = a.n_tiles * a.t_tiles * a.splits;
+  int grid = items < a.num_sms ? items : a.num_sms;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.ws, a.counters,
+                                                   a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.splits,
+                                                   a.kb_per_split, a.fmt, a.ldo);
+  return cudaGetLastError();
+}
+
+}  // namespace b200
+
+extern "C" int b200_gemm_pick_bn(int T) {
+  if (T <= 16) return 16;
+  if (T <= 32) return 32;
+  if (T <= 64) return 64;
+  if (T <= 128) return 128;
+  if (T <= 256) return 256;
+  int pad128 = (T + 127) / 128 * 128, pad256 = (T + 255) / 256 * 256;
+  return (pad128 < pad256) ? 128 : 256;
+}
+
+extern "C" int b200_gemm_launch(const GemmArgs* a, const void* tmW, const void* tmX, cudaStream_t st) {
+  using namespace b200;
+  const CUtensorMap& w = *reinterpret_cast<const CUtensorMap*>(tmW);
+  const CUtensorMap& x = *reinterpret_cast<const CUtensorMap*>(tmX);
+  cudaError_t e = cudaErrorInvalidValue;
+#define B200_BN_CASE(BN_)                                                                              \
+  case BN_:                                                                                            \
+    e = (a->fmt == 1) ? launch_bn<BN_, __nv_bfloat16>(*a, w, x, st) : launch_bn<BN_, __half>(*a, w, x, st); \
+    break;
+  switch (a->bn) {
+    B200_BN_CASE(16)
+    B200_BN_CASE(32)
+    B200_BN_CASE(64)
+    B200_BN_CASE(128)
+    B200_BN_CASE(256)
+    default: break;
+  }
+#undef B200_BN_CASE
+  return (int)e;
+}

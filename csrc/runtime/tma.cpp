@@ -1,0 +1,45 @@
+// Host-side TMA descriptor encoding.  cuTensorMapEncodeTiled is resolved through the runtime's
+// driver-entry-point lookup, so the library does not link against libcuda directly.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "../api.h"
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+extern "C" int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols,
+                                   uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return 1001;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15)) return 1002;
+  if ((uint64_t)box_cols * elem_bytes != 128 || box_rows > 256) return 1003;
+  CUtensorMap tm;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(&tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 2000 + (int)r;
+  memcpy(out, &tm, sizeof(tm));
+  return 0;
+}

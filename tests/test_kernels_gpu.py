@@ -1,0 +1,227 @@
+"""CUDA kernels vs the fp32 PyTorch oracles (run with ``-m gpu`` on a B200)."""
+import math
+
+import pytest
+import torch
+
+from vllm_kunlun_b200 import ops
+from vllm_kunlun_b200.ops.reference import attention as ra
+from vllm_kunlun_b200.ops.reference import basic as rb
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol, name=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).float().mean().item()
+    assert bad < 1e-3, f"{name}: {bad:.4%} elements off, max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 4096, 4096), (17, 384, 512), (64, 200, 256),
+                                   (200, 1024, 1024), (512, 2048, 768), (1000, 640, 4096), (16, 6144, 4096),
+                                   (16, 4096, 14336), (3, 128256 // 8, 512)])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_gemm_bf16(T, N, K, splits):
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status, gemm_bf16
+    g = torch.Generator(device=DEV).manual_seed(T * 7 + N + K)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, device=DEV, generator=g).to(torch.bfloat16)
+    y = gemm_bf16(x, w, b, splits=splits)
+    torch.cuda.synchronize()
+    check_status()
+    ref = x.float() @ w.float().T + b.float()
+    _close(y, ref, atol=0.02 * math.sqrt(K / 64), rtol=0.02, name=f"gemm {T}x{N}x{K}/{splits}")
+
+
+def test_gemm_fp16_strided_out():
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status, gemm_bf16
+    x = torch.randn(40, 320, device=DEV).half()
+    w = (torch.randn(256, 320, device=DEV) * 0.05).half()
+    y = gemm_bf16(x, w)
+    torch.cuda.synchronize()
+    check_status()
+    _close(y, x.float() @ w.float().T, 0.03, 0.02, "gemm fp16")
+
+
+def test_gemm_deterministic():
+    from vllm_kunlun_b200.ops.gemm_cuda import gemm_bf16
+    x = torch.randn(16, 4096, device=DEV).bfloat16()
+    w = (torch.randn(4096, 4096, device=DEV) * 0.02).bfloat16()
+    a = gemm_bf16(x, w, splits=4).clone()
+    for _ in range(3):
+        assert torch.equal(a, gemm_bf16(x, w, splits=4))
+
+
+@pytest.mark.parametrize("T,H", [(1, 896), (16, 4096), (33, 7168), (5, 16384)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rmsnorm(T, H, dtype):
+    x = torch.randn(T, H, device=DEV).to(dtype)
+    r = torch.randn(T, H, device=DEV).to(dtype)
+    w = torch.randn(H, device=DEV).to(dtype)
+    _close(ops.rmsnorm(x, w, 1e-5), rb.rmsnorm(x.cpu(), w.cpu(), 1e-5), 1e-2, 1e-2, "rmsnorm")
+    eo, er = rb.add_rmsnorm(x.cpu(), r.cpu(), w.cpu(), 1e-5)
+    xo, ro = ops.add_rmsnorm(x.clone(), r.clone(), w, 1e-5)
+    _close(xo, eo, 2e-2, 2e-2, "add_rmsnorm out")
+    _close(ro, er, 1e-2, 1e-2, "add_rmsnorm residual")
+    _close(ops.rmsnorm(x, w, 1e-6, gemma=True), rb.rmsnorm(x.cpu(), w.cpu(), 1e-6, True), 2e-2, 2e-2, "gemma")
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh", "swigluoai"])
+def test_act_and_mul(act):
+    x = torch.randn(19, 2 * 1536, device=DEV).bfloat16()
+    ref = {"silu": rb.silu_and_mul, "gelu_tanh": rb.gelu_tanh_and_mul, "swigluoai": rb.swigluoai_and_mul}[act](x.cpu())
+    _close(ops.act_and_mul(x, act), ref, 2e-2, 2e-2, act)
+
+
+def test_rownorm_variants():
+    x = torch.randn(7, 12, 128, device=DEV).bfloat16()
+    z = torch.randn(7, 12, 128, device=DEV).bfloat16()
+    w = torch.randn(128, device=DEV).bfloat16()
+    _close(ops.l2norm(x), rb.l2norm(x.cpu()), 1e-2, 1e-2, "l2norm")
+    for nbg in (True, False):
+        _close(ops.rms_norm_gated(x, z, w, 1e-6, nbg), rb.rms_norm_gated(x.cpu(), z.cpu(), w.cpu(), 1e-6, nbg),
+               3e-2, 3e-2, f"gated {nbg}")
+    _close(ops.quick_gelu(x), rb.quick_gelu(x.cpu()), 1e-2, 1e-2, "quick_gelu")
+
+
+def test_embedding_argmax():
+    w = torch.randn(1000, 256, device=DEV).bfloat16()
+    ids = torch.tensor([0, 5, 999, 1200, 400], device=DEV)
+    out = ops.embedding(ids, w, 0)
+    assert torch.equal(out[:3], w[ids[:3]]) and out[3].abs().sum() == 0
+    out2 = ops.embedding(ids, w[400:], 400)
+    assert torch.equal(out2[2], w[999]) and out2[0].abs().sum() == 0 and torch.equal(out2[4], w[400])
+    lg = torch.randn(9, 151936, device=DEV).bfloat16()
+    assert torch.equal(ops.argmax(lg).cpu(), lg.float().argmax(-1).cpu())
+    lg32 = torch.randn(3, 1000, device=DEV)
+    assert torch.equal(ops.argmax(lg32), lg32.argmax(-1))
+
+
+@pytest.mark.parametrize("qk_norm,neox,D", [(False, True, 128), (True, True, 128), (False, False, 64), (True, True, 64)])
+def test_qkv_split_norm_rope_cache(qk_norm, neox, D):
+    T, Hq, Hkv, bs, nblk = 23, 8, 2, 16, 12
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    pos = torch.randint(0, 500, (T,), device=DEV)
+    cs = rb.build_cos_sin_cache(D, 512, 10000.0).to(DEV)
+    qw = torch.randn(D, device=DEV).bfloat16() if qk_norm else None
+    kw = torch.randn(D, device=DEV).bfloat16() if qk_norm else None
+    slots = torch.randperm(bs * nblk, device=DEV)[:T]
+    slots[3] = -1
+    cache = torch.zeros(nblk, 2, Hkv, bs, D, device=DEV, dtype=torch.bfloat16)
+    q = ops.qkv_split_norm_rope_cache(qkv, pos, cs, qw, kw, 1e-6, Hq, Hkv, D, neox, cache, slots)
+    cache_ref = torch.zeros(nblk, 2, Hkv, bs, D, dtype=torch.bfloat16)
+    q_ref = ops.qkv_split_norm_rope_cache(qkv.cpu(), pos.cpu(), cs.cpu(), None if qw is None else qw.cpu(),
+                                          None if kw is None else kw.cpu(), 1e-6, Hq, Hkv, D, neox, cache_ref, slots.cpu())
+    _close(q, q_ref, 3e-2, 3e-2, "q")
+    _close(cache, cache_ref, 3e-2, 3e-2, "cache")
+
+
+def _make_paged(B, seq_lens, Hkv, D, bs, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    max_blocks = max(-(-s // bs) for s in seq_lens) + 1
+    nblk = sum(-(-s // bs) for s in seq_lens) + 3
+    perm = torch.randperm(nblk, generator=g)
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32)
+    k = 0
+    for b, s in enumerate(seq_lens):
+        n = -(-s // bs)
+        bt[b, :n] = perm[k:k + n]
+        k += n
+    cache = (torch.randn(nblk, 2, Hkv, bs, D, generator=g) * 0.5).to(dtype)
+    return cache, bt
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,bs", [(128, 32, 8, 16), (128, 8, 1, 64), (64, 14, 2, 16), (128, 16, 16, 32)])
+@pytest.mark.parametrize("q_len", [1, 2])
+def test_paged_attention_decode(D, Hq, Hkv, bs, q_len):
+    seq_lens = [1 + q_len, 17, 64, 65, 300, 1000, 2049]
+    B = len(seq_lens)
+    cache, bt = _make_paged(B, seq_lens, Hkv, D, bs)
+    qsl = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32)
+    q = (torch.randn(B * q_len, Hq, D) * 0.5).bfloat16()
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    scale = D ** -0.5
+    ref = ra.paged_attention(q, cache, bt, sl, qsl, scale)
+    for splits in (None, 1, 5):
+        from vllm_kunlun_b200.ops.attention_cuda import paged_attention_cuda
+        out = torch.empty(B * q_len, Hq, D, device=DEV, dtype=torch.bfloat16)
+        paged_attention_cuda(out, q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), scale, q_len,
+                             max(seq_lens), num_splits=splits)
+        _close(out, ref, 2e-2, 2e-2, f"decode splits={splits}")
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,bs", [(128, 8, 2, 16), (64, 4, 4, 64), (128, 4, 1, 32)])
+def test_paged_attention_prefill(D, Hq, Hkv, bs):
+    # (q_len, seq_len): fresh prompts, chunked continuation with cached prefix, one decode row mixed in
+    spec = [(1, 40), (37, 37), (128, 128), (70, 200), (300, 300), (5, 133)]
+    B = len(spec)
+    seq_lens = [s for _, s in spec]
+    cache, bt = _make_paged(B, seq_lens, Hkv, D, bs, seed=1)
+    qsl = torch.tensor([0] + list(torch.tensor([q for q, _ in spec]).cumsum(0)), dtype=torch.int32)
+    T = int(qsl[-1])
+    q = (torch.randn(T, Hq, D) * 0.5).bfloat16()
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    scale = D ** -0.5
+    ref = ra.paged_attention(q, cache, bt, sl, qsl, scale)
+    out = ops.paged_attention(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), scale,
+                              max(qq for qq, _ in spec), max(seq_lens), num_decodes=1)
+    _close(out, ref, 2e-2, 2e-2, "prefill")
+
+
+def test_paged_attention_window_sinks():
+    D, Hq, Hkv, bs = 64, 8, 2, 16
+    spec = [(1, 300), (1, 100), (150, 150), (40, 260)]
+    B = len(spec)
+    seq_lens = [s for _, s in spec]
+    cache, bt = _make_paged(B, seq_lens, Hkv, D, bs, seed=2)
+    qsl = torch.tensor([0] + list(torch.tensor([q for q, _ in spec]).cumsum(0)), dtype=torch.int32)
+    q = (torch.randn(int(qsl[-1]), Hq, D) * 0.5).bfloat16()
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    sinks = torch.randn(Hq)
+    ref = ra.paged_attention(q, cache, bt, sl, qsl, 0.125, window=128, sinks=sinks)
+    out = ops.paged_attention(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), 0.125, 150, 300,
+                              window=128, sinks=sinks.to(DEV), num_decodes=2)
+    _close(out, ref, 2e-2, 2e-2, "window+sinks")
+
+
+def test_cache_ops():
+    T, bs, nblk = 11, 64, 4
+    kvc = torch.randn(T, 512, device=DEV).bfloat16()
+    kpe = torch.randn(T, 64, device=DEV).bfloat16()
+    slots = torch.randperm(bs * nblk, device=DEV)[:T]
+    cache = torch.zeros(nblk, bs, 576, device=DEV, dtype=torch.bfloat16)
+    ops.concat_and_cache_mla(kvc, kpe, cache, slots)
+    ref = torch.zeros(nblk, bs, 576, dtype=torch.bfloat16)
+    ra.concat_and_cache_mla(kvc.cpu(), kpe.cpu(), ref, slots.cpu())
+    assert torch.equal(cache.cpu(), ref)
+    c8 = torch.zeros(nblk, bs, 656, device=DEV, dtype=torch.uint8)
+    ops.concat_and_cache_mla(kvc, kpe, c8, slots)
+    r8 = torch.zeros(nblk, bs, 656, dtype=torch.uint8)
+    ra.concat_and_cache_mla_fp8(kvc.cpu(), kpe.cpu(), r8, slots.cpu())
+    _close(ra.dequant_mla_fp8_rows(c8.cpu()), ra.dequant_mla_fp8_rows(r8), 0.08, 0.08, "fp8_ds_mla")
+    k = torch.randn(T, 128, device=DEV).bfloat16()
+    ck = torch.zeros(nblk, bs, 132, device=DEV, dtype=torch.uint8)
+    ops.indexer_k_quant_and_cache(k, ck, slots)
+    rk = torch.zeros(nblk, bs, 132, dtype=torch.uint8)
+    ra.indexer_k_quant_and_cache(k.cpu(), rk, slots.cpu())
+    assert torch.equal(ck.cpu()[..., 128:], rk[..., 128:])
+    a = ck.cpu()[..., :128].contiguous().view(torch.float8_e4m3fn).float()
+    b = rk[..., :128].contiguous().view(torch.float8_e4m3fn).float()
+    assert (a - b).abs().max() <= 32  # at most one e4m3 step apart
+    idx = torch.randint(-1, 200, (T, 64), device=DEV, dtype=torch.int32)
+    req = torch.randint(0, 3, (T,), device=DEV, dtype=torch.int32)
+    btab = torch.randint(0, 50, (3, 4), device=DEV, dtype=torch.int32)
+    got = ops.convert_req_index_to_global_index(req, btab, idx, 64)
+    want = ra.convert_req_index_to_global_index(req.cpu(), btab.cpu(), idx.cpu(), 64)
+    assert torch.equal(got.cpu(), want)
+    o1, o2 = torch.randn(5, 4, 128, device=DEV).bfloat16(), torch.randn(5, 4, 128, device=DEV).bfloat16()
+    l1, l2 = torch.randn(5, 4, device=DEV), torch.randn(5, 4, device=DEV)
+    l2[0, 0] = float("-inf")
+    mo, ml = ops.merge_attn_states(o1, l1, o2, l2)
+    ro, rl = ra.merge_attn_states(o1.cpu(), l1.cpu(), o2.cpu(), l2.cpu())
+    _close(mo, ro, 2e-2, 2e-2, "merge o")
+    _close(ml, rl, 1e-3, 1e-3, "merge lse")

@@ -1,0 +1,87 @@
+"""CUDA-graph capture and replay of decode steps.
+
+The reference supports piecewise graphs only: the model is split at the attention op, each piece is
+captured, and attention runs eagerly between pieces, one host launch sequence per layer
+(``docs/source/developer_guide/feature_guide/Kunlun_Graph.md:58-75``; platform hooks
+``platforms/kunlun.py:100-106,366-378``).  The attention kernels here read all per-step state from
+device tensors at fixed addresses (block tables, lengths, slot mapping live in the runner's
+persistent staging buffers), so a whole decode step - embedding to logits - is captured as ONE graph
+per padded batch size and replayed with no per-layer host work.  ``mode="piecewise"`` keeps the
+reference's behaviour (attention outside the graphs) for backends that cannot be captured.
+"""
+from __future__ import annotations
+
+import bisect
+from typing import Optional
+
+import torch
+
+from ..attention.metadata import AttentionMetadata
+
+
+class DecodeGraphs:
+    def __init__(self, runner):
+        self.runner = runner
+        cfg = runner.cfg
+        self.tokens_per_req = 1 + cfg.speculative.num_speculative_tokens
+        self.sizes = sorted(s for s in cfg.compilation.capture_sizes if s <= runner.max_bs)
+        if runner.max_bs not in self.sizes and runner.max_bs <= 512:
+            self.sizes.append(runner.max_bs)
+        self.graphs: dict = {}
+        self.logits: dict = {}
+        self.hidden: dict = {}
+        self.pool = None
+        self.hits = 0
+        self.misses = 0
+
+    def supports(self, num_reqs: int, num_tokens: int) -> bool:
+        ok = (num_reqs > 0 and num_tokens == num_reqs * self.tokens_per_req and self.sizes
+              and num_reqs <= self.sizes[-1])
+        if not ok:
+            self.misses += 1
+        return bool(ok)
+
+    def padded_batch(self, num_reqs: int) -> int:
+        return self.sizes[bisect.bisect_left(self.sizes, num_reqs)]
+
+    def _forward(self, md: AttentionMetadata, input_ids):
+        from ..attention.metadata import ForwardContext, set_forward_context
+        r = self.runner
+        ctx = ForwardContext(attn=md, kv_caches=r.kv_caches, pstate=r.pstate, capturing=True)
+        with set_forward_context(ctx):
+            hidden = r.run_model(input_ids, md)
+            sel = hidden.index_select(0, md.logits_indices.long())
+            return r.model.compute_logits(sel), sel
+
+    def _capture(self, md: AttentionMetadata, input_ids):
+        key = md.num_reqs
+        # plan attention splits for the longest context this graph may ever see
+        md.max_seq_len = self.runner.cfg.scheduler.max_model_len
+        md.max_query_len = self.tokens_per_req
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):  # warm-up: lazy allocations, tensor-map cache, function attributes
+                self._forward(md, input_ids)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self.pool):
+            logits, sel = self._forward(md, input_ids)
+        if self.pool is None:
+            self.pool = g.pool()
+        self.graphs[key], self.logits[key], self.hidden[key] = g, logits, sel
+
+    @torch.inference_mode()
+    def run(self, md: AttentionMetadata, input_ids, sp):
+        key = md.num_reqs
+        if key not in self.graphs:
+            self._capture(md, input_ids)
+        self.hits += 1
+        self.graphs[key].replay()
+        tokens = self.runner.sampler(self.logits[key], sp)
+        return tokens, self.hidden[key]
+
+    def capture_all(self):
+        """Eagerly capture every configured size with a synthetic batch (server warm-up)."""
+        raise NotImplementedError

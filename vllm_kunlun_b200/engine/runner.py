@@ -67,6 +67,7 @@ class ModelRunner:
         self.kv_caches = self._alloc_kv()
         self._alloc_staging()
         self.graphs = None
+        self.attn_workspace = self._alloc_attn_workspace()
         self.last_tokens: Optional[torch.Tensor] = None  # previous step's sampled tokens (device)
         self.last_rows: dict = {}  # request_id -> row in last_tokens of its newest token
         self.kernel_launches = 0
@@ -106,6 +107,14 @@ class ModelRunner:
             else:
                 caches[i] = torch.zeros((self.num_blocks, *shape), dtype=dtype, device=self.device)
         return caches
+
+    def _alloc_attn_workspace(self):
+        if not self.is_cuda or self.cfg.model.use_mla:
+            return None
+        from ..ops.attention_cuda import AttnWorkspace
+        m = self.cfg.model
+        heads = m.num_heads // self.pstate.tp_size
+        return AttnWorkspace(self.max_bs * (1 + self.num_spec), heads, m.head_dim, 16, self.device)
 
     def _alloc_staging(self):
         T, B, MB = self.max_tokens, self.max_bs, self.max_blocks_per_seq
@@ -211,6 +220,8 @@ class ModelRunner:
             logits_idx[n_logits] = t
             n_logits += 1
             t += 1
+        if pad_reqs:  # a padded (graph) batch is decode-shaped throughout
+            num_decodes, num_decode_tokens = Bp, Tp
         # ---- host -> device
         if self.is_cuda:
             MT_ = self.max_tokens
@@ -232,7 +243,7 @@ class ModelRunner:
             block_tables=src32[o_bt:o_bt + Bp * nblk].view(Bp, nblk), seq_lens=src32[0:Bp],
             query_start_loc=src32[self.max_bs:self.max_bs + Bp + 1], max_query_len=max(max_q, 1),
             max_seq_len=max(max_seq, 1), num_decodes=num_decodes, num_decode_tokens=num_decode_tokens,
-            num_prefills=B - num_decodes, req_id_per_token=src32[o_rq:o_rq + Tp],
+            num_prefills=Bp - num_decodes, workspace=self.attn_workspace, req_id_per_token=src32[o_rq:o_rq + Tp],
             logits_indices=src32[o_li:o_li + n_logits], num_spec_tokens=self.num_spec)
         if not self.is_cuda:
             md.seq_lens_cpu, md.query_start_loc_cpu = md.seq_lens, md.query_start_loc

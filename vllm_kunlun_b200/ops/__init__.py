@@ -49,16 +49,21 @@ def add_rmsnorm(x, residual, weight, eps: float, gemma: bool = False):
 
 def rms_norm_gated(x, z, weight, eps, norm_before_gate=True, group_size=None):
     if x.is_cuda:
-        out = torch.empty_like(x)
-        _c().rms_norm_gated(out, x, z, weight, eps, norm_before_gate, group_size or x.shape[-1])
-        return out
+        gs = group_size or x.shape[-1]
+        xs, zs = x.reshape(-1, gs).contiguous(), z.reshape(-1, gs).contiguous()
+        if gs != x.shape[-1]:
+            return _rb.rms_norm_gated(x, z, weight, eps, norm_before_gate, group_size)
+        out = torch.empty_like(xs)
+        _c().rownorm(out, xs, zs, weight, eps, 2 if norm_before_gate else 3)
+        return out.reshape(x.shape)
     return _rb.rms_norm_gated(x, z, weight, eps, norm_before_gate, group_size)
 
 
 def l2norm(x, eps: float = 1e-6):
     if x.is_cuda:
-        out = torch.empty_like(x)
-        _c().l2norm(out, x, eps)
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        _c().rownorm(out, xc, None, None, eps, 1)
         return out
     return _rb.l2norm(x, eps)
 
@@ -182,12 +187,26 @@ def swap_blocks(src, dst, mapping):
 
 def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
                     max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
-                    seq_lens_cpu=None, query_start_loc_cpu=None, out=None, workspace=None):
-    """Unified varlen paged GQA attention (prefill with prefix, decode, spec-verify)."""
+                    seq_lens_cpu=None, query_start_loc_cpu=None, out=None, workspace=None,
+                    num_decodes: int = 0, decode_query_len: int = 1):
+    """Unified varlen paged GQA attention (prefill with prefix, decode, spec-verify).
+
+    The batch is decode-first: the first ``num_decodes`` requests have at most ``decode_query_len``
+    query tokens each.  On CUDA a mixed batch is served by two launches (decode layout with
+    split-KV, then the prefill layout) over views of the same tensors."""
     if q.is_cuda:
         if out is None:
             out = torch.empty(q.shape[0], q.shape[1], kv_cache.shape[-1], dtype=q.dtype, device=q.device)
         from .attention_cuda import paged_attention_cuda
+        B = seq_lens.shape[0]
+        if 0 < num_decodes < B:
+            paged_attention_cuda(out, q, kv_cache, block_tables[:num_decodes], seq_lens[:num_decodes],
+                                 query_start_loc[:num_decodes + 1], scale, decode_query_len, max_seq_len,
+                                 window, sinks, workspace)
+            paged_attention_cuda(out, q, kv_cache, block_tables[num_decodes:], seq_lens[num_decodes:],
+                                 query_start_loc[num_decodes:], scale, max_query_len, max_seq_len,
+                                 window, sinks, workspace)
+            return out
         return paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
                                     max_query_len, max_seq_len, window, sinks, workspace)
     sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
@@ -199,7 +218,7 @@ def merge_attn_states(o1, lse1, o2, lse2):
     if o1.is_cuda:
         out = torch.empty_like(o1)
         lse = torch.empty_like(lse1)
-        _c().merge_attn_states(out, lse, o1, lse1, o2, lse2)
+        _c().merge_attn_states(out, lse, o1.contiguous(), lse1.contiguous(), o2.contiguous(), lse2.contiguous())
         return out, lse
     return _ra.merge_attn_states(o1, lse1, o2, lse2)
 

@@ -1,0 +1,65 @@
+"""CUDA paged attention entry (``csrc/attention/paged_attention.cu``).
+
+Batches are decode-first; a decode-only batch uses the decode warp layout with split-KV sized to
+fill the SMs, a prefill batch uses the 64-row layout.  Split-KV partials live in a workspace that
+the caller may pre-allocate (needed under CUDA-graph capture).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _ext
+
+_SM_COUNT: dict = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+class AttnWorkspace:
+    """Split-KV scratch: ``ws_o [splits, T, Hq, D]`` fp32 and ``ws_lse [splits, T, Hq]``."""
+
+    def __init__(self, max_tokens: int, num_heads: int, head_dim: int, max_splits: int, device):
+        self.max_splits = max_splits
+        self.max_tokens = max_tokens
+        self.o = torch.empty(max_splits * max_tokens * num_heads * head_dim, dtype=torch.float32, device=device)
+        self.lse = torch.empty(max_splits * max_tokens * num_heads, dtype=torch.float32, device=device)
+
+
+def plan_splits(num_reqs: int, num_kv_heads: int, q_tiles: int, max_seq_len: int, device, max_splits: int = 32) -> int:
+    """Enough KV splits for ~2 CTAs per SM, each split at least 256 keys."""
+    base = max(1, num_reqs * num_kv_heads * q_tiles)
+    want = -(-2 * sm_count(device) // base)
+    by_len = max(1, max_seq_len // 256)
+    return int(max(1, min(want, by_len, max_splits)))
+
+
+def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
+                         max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
+                         workspace: Optional[AttnWorkspace] = None, num_splits: Optional[int] = None):
+    T, Hq, D = q.shape
+    Hkv = kv_cache.shape[2]
+    g = Hq // Hkv
+    B = seq_lens.shape[0]
+    decode_layout = max_query_len * g <= 16
+    if num_splits is None:
+        if decode_layout:
+            num_splits = plan_splits(B, Hkv, 1, max_seq_len, q.device,
+                                     workspace.max_splits if workspace is not None else 32)
+        else:
+            num_splits = 1
+    ws_o = ws_lse = None
+    if num_splits > 1:
+        if workspace is None:
+            workspace = AttnWorkspace(T, Hq, D, num_splits, q.device)
+        assert T <= workspace.max_tokens and num_splits <= workspace.max_splits
+        ws_o, ws_lse = workspace.o, workspace.lse
+    _ext.C().paged_attention(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, ws_o, ws_lse,
+                             max_query_len, num_splits, window or 0, scale, decode_layout)
+    return out

@@ -1,0 +1,34 @@
+"""CUDA GEMM entry: ``y = x @ W.T (+ b)`` on the tcgen05 kernel (``csrc/gemm/gemm_bf16.cu``).
+
+The reference runs dense linears through ``F.linear`` on the vendor BLAS
+(``fc_cdnn_infer`` in its profiles, ``docs/.../profiling.md:420``); no library GEMM is used here.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+
+LAUNCHES = 0
+
+
+def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits: int = 0, bn: int = 0):
+    global LAUNCHES
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    N = weight.shape[0]
+    if out is None:
+        out = torch.empty(x2.shape[0], N, dtype=x.dtype, device=x.device)
+    out2 = out.reshape(-1, N)
+    _ext.C().gemm(out2, x2, weight, bias, splits, bn)
+    LAUNCHES += 1
+    return out.reshape(*lead, N)
+
+
+def check_status() -> None:
+    """Raise if any GEMM CTA gave up on a bounded wait (a device-side status word, read on demand)."""
+    code = _ext.C().gemm_status()
+    if code:
+        raise RuntimeError(f"tcgen05 GEMM reported a timed-out wait, code {code}")
