@@ -1,0 +1,222 @@
+"""Headline benchmark: output tok/s at 16-way concurrency, 2048-token prompts, 2048 generated tokens.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model llama-3.1-8b]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+One *step* is one complete serving round: 16 concurrent requests, each a 2048-token prompt of
+uniform random ids, greedy generation of 2048 tokens with ignore_eos, run through the framework's
+own engine (scheduler, paged KV cache, chunked prefill, CUDA-graph decode).  Weights are random-init
+N(0, 0.02) of the named architecture; N GPUs = tensor parallel over N ranks (strong scaling: the
+request set is fixed).
+
+Two measurements, each of exactly K steps after W warm-up steps:
+  value  device time: CUDA events on the launching stream around the K steps, barrier +
+         synchronize on both sides, max over ranks;
+  e2e    the public API (``LLM.generate`` on host token lists): wall clock around the call,
+         including every step's host->device copy of its inputs from pinned memory and the
+         device->host read of the sampled tokens.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOK_S = {  # published by the reference (Kunlun3 P800), 16-way, 2048/2048
+    "llama-3.1-8b": 1779.8,   # closest published analogue: Qwen3-8B, TP=1
+    "qwen3-8b": 1779.8,
+    "qwen3-30b-a3b": 1927.4,  # Qwen3-30B-A3B, TP=2
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama-3.1-8b")
+    ap.add_argument("--concurrency", type=int, default=16)
+    ap.add_argument("--in-len", type=int, default=2048)
+    ap.add_argument("--out-len", type=int, default=2048)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region (read-only queries)."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "200", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, pw = [], [], []
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2])); pw.append(float(parts[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.f.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    # The reference is a Kunlun-XPU plugin: `pip install --no-index ... /root/reference` fails offline
+    # (build backend `hatchling` is not in the wheelhouse) and, installed or not, it imports closed
+    # vendor wheels (kunlun_ops, xspeedgate_ops, cocopod) at module top level.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference needs closed Kunlun wheels (kunlun_ops/xspeedgate_ops/cocopod) and its hatchling "
+                      "build backend is absent offline; baseline/_ref could not be installed"}))
+    return 0
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import torch
+    import torch.distributed as dist
+
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    from vllm_kunlun_b200.ops import _ext
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local)
+    C, IN, OUT = args.concurrency, args.in_len, args.out_len
+    llm = LLM(args.model, tensor_parallel_size=world, device="cuda", block_size=64, max_model_len=IN + OUT + 64,
+              max_num_seqs=C, max_num_batched_tokens=8192, gpu_memory_utilization=0.9, seed=0)
+    eng = llm.engine
+    vocab = eng.cfg.model.vocab_size
+    g = torch.Generator().manual_seed(1234)
+    # prompts live in pinned host memory; every round draws a fresh set so nothing is cached
+    n_rounds = args.warmup + 2 * args.steps
+    prompt_bank = torch.randint(0, vocab, (n_rounds, C, IN), generator=g, dtype=torch.int64).pin_memory()
+    sp = SamplingParams(max_tokens=OUT, temperature=0.0, ignore_eos=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+
+    ttfts, tpots = [], []
+
+    def one_round(i, collect=False):
+        outs = llm.generate([prompt_bank[i, c].tolist() for c in range(C)], sp)
+        assert all(len(o.token_ids) == OUT for o in outs)
+        if collect:
+            ttfts.extend(o.ttft for o in outs)
+            tpots.extend(o.tpot for o in outs)
+        return outs
+
+    r = 0
+    for _ in range(args.warmup):
+        one_round(r); r += 1
+    # ---------------- device-timed region
+    sampler = ClockSampler(local)
+    barrier()
+    k0 = _ext.C().launch_count()
+    g0 = eng.runner.graphs.replayed_kernels if eng.runner.graphs else 0
+    h0, d0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one_round(r, collect=True); r += 1
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    dev_ms = e0.elapsed_time(e1)
+    launches = (_ext.C().launch_count() - k0) + ((eng.runner.graphs.replayed_kernels - g0) if eng.runner.graphs else 0)
+    h2d = (eng.runner.h2d_bytes - h0) / args.steps
+    d2h = (eng.runner.d2h_bytes - d0) / args.steps
+    # ---------------- end-to-end region (public API, wall clock)
+    e2e_ms = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            one_round(r); r += 1
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([dev_ms, e2e_ms or 0.0], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_max = t.tolist()
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    check_status()
+    if rank == 0:
+        tokens = C * OUT * args.steps
+        value = tokens / (dev_ms / 1e3)
+        base = BASELINE_TOK_S.get(args.model)
+        out = {
+            "metric": "output tok/s at 16 concurrency, 2048 in/2048 out", "value": round(value, 1), "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 2),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": round(value / base, 3) if base else None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+            "impl": "ours",
+            "config": {"model": args.model, "global_batch": C, "seq_len": IN + OUT, "in_len": IN, "out_len": OUT,
+                       "parallelism": f"tp{world}", "step": "one full serving round of 16 requests",
+                       "l2": "inputs larger than L2: every decode step streams the whole weight set (16 GB bf16) "
+                             "and the KV cache",
+                       "baseline_ref": "Qwen3-8B TP=1 on Kunlun3 P800 (closest published analogue)"},
+            "p50_ttft_ms": round(statistics.median(ttfts) * 1e3, 1) if ttfts else None,
+            "p50_tpot_ms": round(statistics.median(tpots) * 1e3, 3) if tpots else None,
+            "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e_ms is not None:
+            out["e2e"] = {"value": round(tokens / (e2e_max / 1e3), 1), "unit": "tok/s",
+                          "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                          "ms_per_step": round(e2e_max / args.steps, 2)}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier(device_ids=[local])
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -72,6 +72,23 @@ def bench_gemm(iters):
                           "frac_hbm": round(gbs / hbm, 3), "frac_tensor": round(tfl / tf, 3), "peaks": src}), flush=True)
 
 
+def bench_gemm_sweep(iters):
+    """Decode-shaped GEMMs over split-K factor and CTAs per SM (tuning aid for the launch heuristic)."""
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status, gemm_bf16
+    hbm, _, src = peaks()
+    for T, N, K in [(16, 6144, 4096), (16, 4096, 4096), (16, 28672, 4096), (16, 4096, 14336), (64, 28672, 4096)]:
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        for cps in (1, 2, 3):
+            for sp in (0, 1, 2, 3, 4, 5, 6, 8, 12):
+                ms = timeit(lambda: gemm_bf16(x, w, out=out, splits=sp, ctas_per_sm=cps), iters)
+                byt = (T * K + N * K + T * N) * 2
+                print(json.dumps({"kernel": "gemm_sweep", "T": T, "N": N, "K": K, "ctas_per_sm": cps, "splits": sp,
+                                  "ms": round(ms, 4), "frac_hbm": round(byt / ms / 1e6 / hbm, 3), "peaks": src}), flush=True)
+        check_status()
+
+
 def bench_attn(iters):
     from vllm_kunlun_b200.ops.attention_cuda import AttnWorkspace, paged_attention_cuda
     hbm, tf, src = peaks()
@@ -132,4 +149,4 @@ if __name__ == "__main__":
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     for w in a.what.split(","):
-        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[w](a.iters)
+        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "gemm_sweep": bench_gemm_sweep}[w](a.iters)

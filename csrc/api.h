@@ -24,6 +24,8 @@ typedef struct GemmArgs {
   int ldo;            // row stride of out (elements)
   int bn;             // token tile: 16 / 32 / 64 / 128 / 256
   int num_sms;
+  int stages;         // 0 = choose from the shared-memory budget
+  int ctas_per_sm;    // 0 = choose (2 for small token tiles)
 } GemmArgs;
 int b200_gemm_pick_bn(int T);
 int b200_gemm_launch(const GemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);

@@ -8,6 +8,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -24,7 +25,12 @@ int dtype_code(const at::Tensor& t) {
   }
 }
 cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
-void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+std::atomic<int64_t> g_launches{0};
+void check(int rc, const char* what, int n_kernels = 1) {
+  TORCH_CHECK(rc == 0, what, " failed with code ", rc);
+  g_launches += n_kernels;
+}
+int64_t launch_count() { return g_launches.load(); }
 const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 
 at::Tensor weak_ref_tensor(const at::Tensor& t) {
@@ -72,7 +78,7 @@ const Tmap& get_tmap(GemmState& gs, const at::Tensor& t, int box_rows, int elem_
 
 // out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  splits <= 0 lets the library choose.
 void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
-          int64_t splits, int64_t bn_override) {
+          int64_t splits, int64_t bn_override, int64_t stages, int64_t ctas_per_sm) {
   TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda());
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2);
   TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == out.scalar_type());
@@ -104,11 +110,13 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
     sp = 1;
     double best = 0;
     int max_sp = std::max(1, std::min(16, total_kb / 4));
-    if (tiles >= 2 * gs.num_sms) max_sp = 1;
+    int cps = ctas_per_sm > 0 ? (int)ctas_per_sm : ((a.bn <= 64 && a.t_tiles == 1) ? 2 : 1);
+    int slots = gs.num_sms * cps;
+    if (tiles >= 4 * gs.num_sms) max_sp = 1;
     for (int s = 1; s <= max_sp; ++s) {
       int items = tiles * s;
-      int waves = (items + gs.num_sms - 1) / gs.num_sms;
-      double eff = (double)items / (waves * gs.num_sms) * (1.0 - 0.015 * (s - 1));
+      int waves = (items + slots - 1) / slots;
+      double eff = (double)items / (waves * slots) * (1.0 - 0.015 * (s - 1));
       if (eff > best + 1e-9) { best = eff; sp = s; }
     }
   }
@@ -127,6 +135,8 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
   a.fmt = x.scalar_type() == at::kBFloat16 ? 1 : 0;
   a.ldo = out.stride(0);
   a.num_sms = gs.num_sms;
+  a.stages = (int)stages;
+  a.ctas_per_sm = (int)ctas_per_sm;
   const Tmap& tw = get_tmap(gs, w, 128, 2);
   const Tmap& tx = get_tmap(gs, x, a.bn, 2);
   check(b200_gemm_launch(&a, tw.b, tx.b, stream()), "gemm launch");
@@ -285,13 +295,14 @@ void paged_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_c
                              ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, q.size(0), B, q.size(1),
                              kv_cache.size(2), q.size(2), kv_cache.size(3), block_tables.stride(0), kv_cache.size(0),
                              max_query_len, num_splits, window, (float)scale, decode_layout, dtype_code(q), stream()),
-        "paged_attention");
+        "paged_attention", num_splits > 1 ? 2 : 1);
 }
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("weak_ref_tensor", &weak_ref_tensor);
+  m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
   m.def("gemm_clear_tmap_cache", &gemm_clear_tmap_cache);

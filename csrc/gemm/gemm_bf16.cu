@@ -35,9 +35,7 @@ struct GemmCfg {
   static constexpr int kStageBytesB = BN * BK * 2;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct Abort {
@@ -75,18 +73,18 @@ template <>
 __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
 
 template <int BN, typename OutT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
                int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
-               int t_tiles, int splits, int kb_per_split, int fmt, int ldo) {
+               int t_tiles, int splits, int kb_per_split, int fmt, int ldo, int num_stages) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + num_stages * Cfg::kStageBytes);
   uint64_t* full_bar = bars;                       // [kStages]
-  uint64_t* empty_bar = bars + Cfg::kStages;       // [kStages]
-  uint64_t* tmem_full = bars + 2 * Cfg::kStages;   // [2]
+  uint64_t* empty_bar = bars + num_stages;         // [kStages]
+  uint64_t* tmem_full = bars + 2 * num_stages;     // [2]
   uint64_t* tmem_empty = tmem_full + 2;            // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
@@ -101,7 +99,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < num_stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -157,14 +155,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tma_load_2d_hint(sa, &tmW, &full_bar[stage], kb * BK, nt * BM, pol_w);
           tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
           ++issued;
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == num_stages) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
         // Drain: copies already issued must land before this CTA's shared memory is released.
-        int pending = issued < Cfg::kStages ? issued : Cfg::kStages;
+        int pending = issued < num_stages ? issued : num_stages;
         for (int i = 0; i < pending; ++i) {
-          int s = (stage - 1 - i + 2 * Cfg::kStages) % Cfg::kStages;
+          int s = (stage - 1 - i + 2 * num_stages) % num_stages;
           uint32_t ph = (s < stage) ? phase : (phase ^ 1);
           for (uint32_t p = 0; p < (1u << 16); ++p)
             if (mbar_try_wait(&full_bar[s], ph)) break;
@@ -200,7 +198,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == num_stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tmem_full[buf]);
       }
@@ -270,14 +268,28 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*ticket_slot == splits - 1) {
           __threadfence();
-          const float* wbase = ws + (size_t)tile * splits * (BN * BM);
+          const float* wbase = ws + (size_t)tile * splits * (BN * BM) + quarter * 32 + lane;
           float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
-          for (int c = 0; c < BN; ++c) {
-            int t = t0 + c;
-            if (t >= T) break;
-            float acc = bv;
-            for (int s = 0; s < splits; ++s) acc += __ldcg(wbase + (size_t)s * (BN * BM) + c * BM + quarter * 32 + lane);
-            if (n_ok) out[(size_t)t * ldo + n] = from_float<OutT>(acc);
+          // 16 columns at a time: the 16 loads of one split are independent, so their L2
+          // latencies overlap; splits are summed in index order (deterministic).
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (t0 + c0 >= T) break;
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = bv;
+            for (int s = 0; s < splits; ++s) {
+              const float* wp = wbase + (size_t)s * (BN * BM) + c0 * BM;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] += __ldcg(wp + j * BM);
+            }
+            if (n_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                int t = t0 + c0 + j;
+                if (t < T) out[(size_t)t * ldo + n] = from_float<OutT>(acc[j]);
+              }
+            }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_slot is reused by the next item
@@ -299,15 +311,26 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   auto kern = gemm_tn_kernel<BN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kStagesRaw * Cfg::kStageBytes + 1024 + 512);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
+  // Shared memory per CTA decides how many CTAs share an SM: small token tiles run two CTAs per SM
+  // so one CTA's prologue / split-K epilogue overlaps the other's main loop.
+  int ctas_per_sm = a.ctas_per_sm > 0 ? a.ctas_per_sm : ((BN <= 64 && a.t_tiles == 1) ? 2 : 1);
+  int budget = (kSmemBudget + 16 * 1024) / ctas_per_sm - 2048;
+  int stages = a.stages > 0 ? a.stages : budget / Cfg::kStageBytes;
+  if (stages > 12) stages = 12;
+  if (stages > Cfg::kStagesRaw) stages = Cfg::kStagesRaw;
+  if (stages < 2) stages = 2;
+  int smem = stages * Cfg::kStageBytes + 1024 + 512;
   int items = a.n_tiles * a.t_tiles * a.splits;
-  int grid = items < a.num_sms ? items : a.num_sms;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.ws, a.counters,
-                                                   a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.splits,
-                                                   a.kb_per_split, a.fmt, a.ldo);
+  int slots = a.num_sms * ctas_per_sm;
+  int grid = items < slots ? items : slots;
+  kern<<<grid, kGemmThreads, smem, st>>>(tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.ws, a.counters, a.status,
+                                         a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.splits, a.kb_per_split, a.fmt,
+                                         a.ldo, stages);
   return cudaGetLastError();
 }
 

@@ -5,13 +5,13 @@ import pytest
 import torch
 
 from vllm_kunlun_b200 import LLM, SamplingParams
-from vllm_kunlun_b200.config import llama_3_1_8b
+from vllm_kunlun_b200.config import llama_3_1_8b, tiny
 
 pytestmark = pytest.mark.gpu
 
 
 def _tiny():
-    return dataclasses.replace(llama_3_1_8b(), num_layers=2, vocab_size=2048, hidden_size=512, num_heads=8,
+    return tiny(llama_3_1_8b(), num_layers=2, vocab_size=2048, hidden_size=512, num_heads=8,
                                num_kv_heads=2, head_dim=64, intermediate_size=1024, max_position=4096)
 
 
@@ -22,7 +22,8 @@ def test_gpu_logits_match_cpu_oracle():
     cpu_cfg = dataclasses.replace(cfg, dtype="float32")
     cpu = LLM(cpu_cfg, device="cpu", block_size=16, max_model_len=512, max_num_seqs=8, num_gpu_blocks=256)
     sd = {k: v.float().cpu() for k, v in gpu.engine.runner.model.state_dict().items()}
-    cpu.engine.runner.model.load_state_dict(sd)
+    with torch.inference_mode():
+        cpu.engine.runner.model.load_state_dict(sd)
     prompt = torch.randint(0, 2048, (150,), generator=torch.Generator().manual_seed(0)).tolist()
 
     def first_logits(llm):

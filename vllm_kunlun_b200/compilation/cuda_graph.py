@@ -32,6 +32,8 @@ class DecodeGraphs:
         self.hidden: dict = {}
         self.pool = None
         self.hits = 0
+        self.kernels_per_graph: dict = {}
+        self.replayed_kernels = 0
         self.misses = 0
 
     def supports(self, num_reqs: int, num_tokens: int) -> bool:
@@ -65,9 +67,12 @@ class DecodeGraphs:
                 self._forward(md, input_ids)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        from ..ops import _ext
         g = torch.cuda.CUDAGraph()
+        n0 = _ext.C().launch_count()
         with torch.cuda.graph(g, pool=self.pool):
             logits, sel = self._forward(md, input_ids)
+        self.kernels_per_graph[key] = _ext.C().launch_count() - n0
         if self.pool is None:
             self.pool = g.pool()
         self.graphs[key], self.logits[key], self.hidden[key] = g, logits, sel
@@ -79,6 +84,7 @@ class DecodeGraphs:
             self._capture(md, input_ids)
         self.hits += 1
         self.graphs[key].replay()
+        self.replayed_kernels += self.kernels_per_graph[key]
         tokens = self.runner.sampler(self.logits[key], sp)
         return tokens, self.hidden[key]
 

@@ -404,7 +404,10 @@ PRESETS = {
 
 
 def tiny(base: ModelConfig, **overrides) -> ModelConfig:
-    """Shrink a preset for tests while keeping its structure."""
+    """Shrink a preset for tests while keeping its structure (derived head sizes are re-derived)."""
+    if "head_dim" in overrides and not base.use_mla:
+        overrides.setdefault("v_head_dim", None)
+        overrides.setdefault("rotary_dim", None)
     return dataclasses.replace(base, **overrides)
 
 

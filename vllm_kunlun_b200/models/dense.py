@@ -79,7 +79,8 @@ class GQAAttention(nn.Module):
             q.view(T, self.num_heads, self.head_dim), kv_cache, md.block_tables, md.seq_lens,
             md.query_start_loc, self.scale, md.max_query_len, md.max_seq_len, self.window, self.sinks,
             md.seq_lens_cpu, md.query_start_loc_cpu, workspace=md.workspace,
-            num_decodes=md.num_decodes, decode_query_len=1 + md.num_spec_tokens)
+            num_decodes=md.num_decodes, decode_query_len=1 + md.num_spec_tokens,
+            num_decode_tokens=md.num_decode_tokens)
         return self.o_proj(o.reshape(T, self.num_heads * self.head_dim))
 
 

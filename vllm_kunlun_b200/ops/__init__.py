@@ -188,7 +188,7 @@ def swap_blocks(src, dst, mapping):
 def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
                     max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
                     seq_lens_cpu=None, query_start_loc_cpu=None, out=None, workspace=None,
-                    num_decodes: int = 0, decode_query_len: int = 1):
+                    num_decodes: int = 0, decode_query_len: int = 1, num_decode_tokens: int = 0):
     """Unified varlen paged GQA attention (prefill with prefix, decode, spec-verify).
 
     The batch is decode-first: the first ``num_decodes`` requests have at most ``decode_query_len``
@@ -200,7 +200,8 @@ def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale:
         from .attention_cuda import paged_attention_cuda
         B = seq_lens.shape[0]
         if 0 < num_decodes < B:
-            paged_attention_cuda(out, q, kv_cache, block_tables[:num_decodes], seq_lens[:num_decodes],
+            ndt = num_decode_tokens or num_decodes * decode_query_len
+            paged_attention_cuda(out[:ndt], q[:ndt], kv_cache, block_tables[:num_decodes], seq_lens[:num_decodes],
                                  query_start_loc[:num_decodes + 1], scale, decode_query_len, max_seq_len,
                                  window, sinks, workspace)
             paged_attention_cuda(out, q, kv_cache, block_tables[num_decodes:], seq_lens[num_decodes:],

@@ -32,12 +32,22 @@ class AttnWorkspace:
         self.lse = torch.empty(max_splits * max_tokens * num_heads, dtype=torch.float32, device=device)
 
 
-def plan_splits(num_reqs: int, num_kv_heads: int, q_tiles: int, max_seq_len: int, device, max_splits: int = 32) -> int:
-    """Enough KV splits for ~2 CTAs per SM, each split at least 256 keys."""
+def plan_splits(num_reqs: int, num_kv_heads: int, q_tiles: int, max_seq_len: int, device, max_splits: int = 16,
+                ctas_per_sm: int = 2, warps: int = 4, tile: int = 16) -> int:
+    """Split count for decode: fill the resident CTA slots in whole waves while every warp keeps
+    enough 16-key tiles to amortise its pipeline prologue."""
     base = max(1, num_reqs * num_kv_heads * q_tiles)
-    want = -(-2 * sm_count(device) // base)
-    by_len = max(1, max_seq_len // 256)
-    return int(max(1, min(want, by_len, max_splits)))
+    slots = sm_count(device) * ctas_per_sm
+    best, best_score = 1, -1.0
+    for s in range(1, max_splits + 1):
+        ctas = base * s
+        waves = -(-ctas // slots)
+        eff = ctas / (waves * slots)
+        tiles_per_warp = max_seq_len / tile / warps / s
+        score = eff * tiles_per_warp / (tiles_per_warp + 3.0)
+        if score > best_score + 1e-9:
+            best, best_score = s, score
+    return best
 
 
 def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
@@ -51,7 +61,7 @@ def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_l
     if num_splits is None:
         if decode_layout:
             num_splits = plan_splits(B, Hkv, 1, max_seq_len, q.device,
-                                     workspace.max_splits if workspace is not None else 32)
+                                     workspace.max_splits if workspace is not None else 16)
         else:
             num_splits = 1
     ws_o = ws_lse = None

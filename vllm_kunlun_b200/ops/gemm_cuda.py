@@ -12,7 +12,8 @@ from . import _ext
 LAUNCHES = 0
 
 
-def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits: int = 0, bn: int = 0):
+def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits: int = 0, bn: int = 0,
+              stages: int = 0, ctas_per_sm: int = 0):
     global LAUNCHES
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -22,7 +23,7 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits
     if out is None:
         out = torch.empty(x2.shape[0], N, dtype=x.dtype, device=x.device)
     out2 = out.reshape(-1, N)
-    _ext.C().gemm(out2, x2, weight, bias, splits, bn)
+    _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm)
     LAUNCHES += 1
     return out.reshape(*lead, N)
 
