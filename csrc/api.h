@@ -15,11 +15,14 @@ extern "C" {
 typedef struct GemmArgs {
   void* out;          // [T, ldo] bf16/fp16
   const void* bias;   // [N] or null
-  float* ws;          // split-K partial tiles (tiles * splits * bn * 128 floats)
+  float* ws;          // stream-K partial tiles (tiles * max_contrib * bn * 128 floats)
   int* counters;      // per-tile arrival tickets, zero on entry, zero again on exit
   int* status;        // device status word: 0 = ok, otherwise the code of the wait that timed out
   int T, N, K;
-  int n_tiles, t_tiles, splits, kb_per_split;
+  int n_tiles, t_tiles;
+  int per_cta;        // stream-K: k-block units per CTA; 0 = whole tiles, strided over the grid
+  int max_contrib;    // stream-K: workspace slots per tile
+  int grid;
   int fmt;            // 1 = bf16, 0 = fp16
   int ldo;            // row stride of out (elements)
   int bn;             // token tile: 16 / 32 / 64 / 128 / 256
@@ -75,6 +78,14 @@ int b200_paged_attention(void* out, const void* q, const void* kv_cache, const i
                          const int* qsl, const float* sinks, float* ws_o, float* ws_lse, int64_t T, int B, int Hq,
                          int Hkv, int D, int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
                          int num_splits, int window, float scale, int decode_layout, int dtype, cudaStream_t st);
+
+// ---- communication over NVLink peer memory ----------------------------------------------------
+int b200_allreduce_max_ctas();
+int64_t b200_allreduce_flag_bytes();
+int b200_oneshot_allreduce(void* const* bufs, const void* in, void* out, void* residual, const void* weight,
+                           uint32_t* epochs, int* status, int64_t parity_bytes, int64_t flags_offset, int rank,
+                           int nranks, int rows, int H, float eps, int gemma, int grid, uint32_t spin_limit, int dtype,
+                           cudaStream_t st);
 
 #ifdef __cplusplus
 }

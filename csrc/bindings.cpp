@@ -103,30 +103,31 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
   a.n_tiles = (N + 127) / 128;
   a.t_tiles = (T + a.bn - 1) / a.bn;
   const int total_kb = (K + 63) / 64;
-  int tiles = a.n_tiles * a.t_tiles;
-  int sp = (int)splits;
-  if (sp <= 0) {
-    // choose the split count that fills the SMs best; each split must keep >= 4 k-blocks
-    sp = 1;
-    double best = 0;
-    int max_sp = std::max(1, std::min(16, total_kb / 4));
-    int cps = ctas_per_sm > 0 ? (int)ctas_per_sm : ((a.bn <= 64 && a.t_tiles == 1) ? 2 : 1);
-    int slots = gs.num_sms * cps;
-    if (tiles >= 4 * gs.num_sms) max_sp = 1;
-    for (int s = 1; s <= max_sp; ++s) {
-      int items = tiles * s;
-      int waves = (items + slots - 1) / slots;
-      double eff = (double)items / (waves * slots) * (1.0 - 0.015 * (s - 1));
-      if (eff > best + 1e-9) { best = eff; sp = s; }
-    }
+  const int tiles = a.n_tiles * a.t_tiles;
+  const int cps = ctas_per_sm > 0 ? (int)ctas_per_sm : 1;
+  const int slots = gs.num_sms * cps;
+  const int64_t units = (int64_t)tiles * total_kb;
+  // splits == 1 forces whole tiles; splits > 1 forces ceil(total_kb / splits) units per CTA;
+  // otherwise whole tiles when there are many of them per SM, stream-K when there are few.
+  int per = 0;
+  if (splits > 1) {
+    per = (total_kb + (int)splits - 1) / (int)splits;
+  } else if (splits <= 0) {
+    // Whole tiles cost nothing extra; stream-K pays a fix-up (partials through L2 + an atomic
+    // ticket, a few microseconds) and wins only when whole tiles would leave most SMs idle or
+    // make the slowest SM stream at least twice its fair share of the weights.
+    int64_t fair = std::max<int64_t>(4, (units + slots - 1) / slots);
+    int64_t whole_path = (int64_t)((tiles + slots - 1) / slots) * total_kb;
+    if (tiles < slots / 4 || whole_path >= 2 * fair) per = (int)fair;
+    if (tiles >= 2 * slots) per = 0;
   }
-  a.kb_per_split = (total_kb + sp - 1) / sp;
-  sp = (total_kb + a.kb_per_split - 1) / a.kb_per_split;  // no empty split
-  if ((int64_t)tiles * sp * a.bn * 128 > gs.ws.numel() || tiles > gs.counters.numel()) {
-    sp = 1;
-    a.kb_per_split = total_kb;
+  if (per > 0) {
+    int max_contrib = (total_kb + per - 1) / per + 1;
+    int64_t grid = (units + per - 1) / per;
+    if ((int64_t)tiles * max_contrib * a.bn * 128 > gs.ws.numel() || tiles > gs.counters.numel()) per = 0;
+    else { a.per_cta = per; a.max_contrib = max_contrib; a.grid = (int)grid; }
   }
-  a.splits = sp;
+  if (per == 0) { a.per_cta = 0; a.max_contrib = 1; a.grid = std::min(tiles, slots); }
   a.out = out.data_ptr();
   a.bias = opt_ptr(bias);
   a.ws = gs.ws.data_ptr<float>();
@@ -298,6 +299,53 @@ void paged_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_c
         "paged_attention", num_splits > 1 ? 2 : 1);
 }
 
+// ---------------------------------------------------------------------------------------- peer memory
+// Symmetric buffers are plain cudaMalloc allocations shared between the ranks of one node with CUDA
+// IPC handles (exchanged by the Python side over the process group).
+int64_t peer_alloc(int64_t bytes) {
+  void* p = nullptr;
+  TORCH_CHECK(cudaMalloc(&p, bytes) == cudaSuccess, "cudaMalloc of the symmetric buffer failed");
+  TORCH_CHECK(cudaMemset(p, 0, bytes) == cudaSuccess);
+  TORCH_CHECK(cudaDeviceSynchronize() == cudaSuccess);
+  return reinterpret_cast<int64_t>(p);
+}
+void peer_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
+py::bytes peer_export(int64_t ptr) {
+  cudaIpcMemHandle_t h;
+  TORCH_CHECK(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr)) == cudaSuccess, "cudaIpcGetMemHandle failed");
+  return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+int64_t peer_open(const std::string& handle) {
+  TORCH_CHECK(handle.size() == sizeof(cudaIpcMemHandle_t));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle.data(), sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  TORCH_CHECK(e == cudaSuccess, "cudaIpcOpenMemHandle failed: ", cudaGetErrorString(e));
+  return reinterpret_cast<int64_t>(p);
+}
+void peer_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+int64_t allreduce_max_ctas() { return b200_allreduce_max_ctas(); }
+int64_t allreduce_flag_bytes() { return b200_allreduce_flag_bytes(); }
+
+// out = sum over ranks of `in`; with `residual` + `weight`: residual += sum, out = rmsnorm(residual) * w.
+void oneshot_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tensor out,
+                       const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& weight,
+                       at::Tensor epochs, at::Tensor status, int64_t parity_bytes, int64_t flags_offset, int64_t rank,
+                       double eps, bool gemma, int64_t grid, int64_t spin_limit) {
+  TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.dim() == 2);
+  TORCH_CHECK(in.numel() * in.element_size() <= parity_bytes, "all-reduce payload exceeds the symmetric buffer");
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && weight.has_value());
+  void* ptrs[8] = {nullptr};
+  TORCH_CHECK(bufs.size() <= 8);
+  for (size_t i = 0; i < bufs.size(); ++i) ptrs[i] = reinterpret_cast<void*>(bufs[i]);
+  check(b200_oneshot_allreduce(ptrs, in.data_ptr(), out.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
+                               opt_ptr(weight), reinterpret_cast<uint32_t*>(epochs.data_ptr<int>()),
+                               status.data_ptr<int>(), parity_bytes, flags_offset, rank, bufs.size(), in.size(0),
+                               in.size(1), (float)eps, gemma, grid, (uint32_t)spin_limit, dtype_code(in), stream()),
+        "oneshot_allreduce");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -323,4 +371,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("copy_blocks", &copy_blocks);
   m.def("merge_attn_states", &merge_attn_states);
   m.def("paged_attention", &paged_attention);
+  m.def("peer_alloc", &peer_alloc);
+  m.def("peer_free", &peer_free);
+  m.def("peer_export", &peer_export);
+  m.def("peer_open", &peer_open);
+  m.def("peer_close", &peer_close);
+  m.def("allreduce_max_ctas", &allreduce_max_ctas);
+  m.def("allreduce_flag_bytes", &allreduce_flag_bytes);
+  m.def("oneshot_allreduce", &oneshot_allreduce);
 }

@@ -1,0 +1,191 @@
+// One-shot all-reduce over NVLink peer memory, optionally fused with residual add + RMSNorm.
+//
+// Every rank owns a symmetric buffer (same layout on all ranks, mapped into every peer):
+//     [ data parity 0 | data parity 1 | flags[kMaxRanks][kMaxCtas] ]
+// CTA c of every rank handles the same rows c, c + G, ...:
+//   1. copy its rows of the local input into this rank's data[parity]          (local stores)
+//   2. publish  flags(peer)[my_rank][c] = epoch  on every peer                 (st.release.sys)
+//   3. wait until flags(me)[p][c] == epoch for every peer p                     (ld.acquire.sys, bounded)
+//   4. read the rows from all ranks' data[parity] (plain peer loads), sum in rank order in fp32 -
+//      every rank adds in the same order, so all ranks hold bit-identical results -
+//      then either store, or add the residual, store it back and RMS-normalise the row.
+// Two data parities make one barrier per call enough: a rank can only reach call k+2 (which
+// reuses parity k) after every peer has entered call k+1, i.e. finished reading call k.
+// Epochs live in device memory and are advanced by the kernel itself, so CUDA-graph replays
+// need no host-side reset.  The wait is bounded; on time-out the status word is set and the
+// kernel completes (with wrong data) instead of hanging the GPU.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../api.h"
+#include "../common/utils.cuh"
+
+namespace b200 {
+
+constexpr int kArMaxRanks = 8;
+constexpr int kArMaxCtas = 128;
+constexpr int kArThreads = 512;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+struct ArParams {
+  void* bufs[kArMaxRanks];   // symmetric buffers of all ranks, as mapped in this process
+  const void* in;            // [rows, H] local partial sums
+  void* out;                 // [rows, H]
+  void* residual;            // [rows, H] (fused norm) or null
+  const void* weight;        // [H] (fused norm) or null
+  uint32_t* epochs;          // [kArMaxCtas] local per-CTA call counters
+  int* status;
+  int64_t parity_bytes;      // size of one data parity
+  int64_t flags_offset;      // byte offset of the flag block inside a symmetric buffer
+  int rank, nranks, rows, H;
+  float eps;
+  int gemma;
+  uint32_t spin_limit;
+};
+
+template <typename T, bool kNorm>
+__global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams p) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[32];
+  const int c = blockIdx.x, G = gridDim.x;
+  const int tid = threadIdx.x;
+  const uint32_t epoch = p.epochs[c] + 1;
+  const int parity = epoch & 1;
+  const int nvec = p.H / V;
+  T* my_data = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p.bufs[p.rank]) + parity * p.parity_bytes);
+
+  // 1. stage my partial rows
+  for (int row = c; row < p.rows; row += G) {
+    const T* src = reinterpret_cast<const T*>(p.in) + (int64_t)row * p.H;
+    T* dst = my_data + (int64_t)row * p.H;
+    for (int i = tid; i < nvec; i += kArThreads) st_vec(dst + i * V, ld_vec(src + i * V));
+  }
+  __threadfence_system();
+  __syncthreads();
+  // 2./3. signal every peer, then wait for every peer
+  if (tid < p.nranks) {
+    uint32_t* peer_flags = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.bufs[tid]) + p.flags_offset);
+    st_release_sys(peer_flags + p.rank * kArMaxCtas + c, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(reinterpret_cast<uint8_t*>(p.bufs[p.rank]) + p.flags_offset) +
+                           tid * kArMaxCtas + c;
+    bool ok = false;
+    for (uint32_t i = 0; i < p.spin_limit; ++i) {
+      if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) { ok = true; break; }
+      if (i > 64) __nanosleep(64);
+    }
+    if (!ok) atomicCAS(p.status, 0, 200 + tid);
+  }
+  __syncthreads();
+  if (tid == 0) p.epochs[c] = epoch;
+
+  // 4. reduce (and normalise)
+  for (int row = c; row < p.rows; row += G) {
+    float ss = 0.f;
+    // each thread owns the vectors tid, tid + 512, ... of the row; H <= 512 * V * kMaxKeep keeps them in registers
+    constexpr int kMaxKeep = 4;
+    float keep[kMaxKeep][V];
+    int k = 0;
+    for (int i = tid; i < nvec; i += kArThreads, ++k) {
+      float acc[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+      for (int r = 0; r < p.nranks; ++r) {
+        const T* src = reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(p.bufs[r]) + parity * p.parity_bytes) +
+                       (int64_t)row * p.H + i * V;
+        uint4 raw = ld_relaxed_sys_v4(src);
+        const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += to_f(v[j]);
+      }
+      if (kNorm) {
+        T* rr = reinterpret_cast<T*>(p.residual) + (int64_t)row * p.H + i * V;
+        Vec16<T> res = ld_vec(rr);
+        Vec16<T> sum;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          // round the all-reduced value to T first (what a separate all-reduce would hand to add+norm)
+          float s = to_f(from_f<T>(acc[j])) + to_f(res.v[j]);
+          sum.v[j] = from_f<T>(s);
+          float f = to_f(sum.v[j]);
+          ss += f * f;
+          if (k < kMaxKeep) keep[k][j] = f;
+        }
+        st_vec(rr, sum);
+      } else {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(acc[j]);
+        st_vec(reinterpret_cast<T*>(p.out) + (int64_t)row * p.H + i * V, o);
+      }
+    }
+    if (kNorm) {
+      ss = block_sum(ss, red);
+      const float inv = rsqrtf(ss / p.H + p.eps);
+      k = 0;
+      for (int i = tid; i < nvec; i += kArThreads, ++k) {
+        Vec16<T> w = ld_vec(reinterpret_cast<const T*>(p.weight) + i * V);
+        Vec16<T> o;
+        if (k < kMaxKeep) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(keep[k][j] * inv * (to_f(w.v[j]) + (p.gemma ? 1.f : 0.f)));
+        } else {
+          Vec16<T> s = ld_vec(reinterpret_cast<const T*>(p.residual) + (int64_t)row * p.H + i * V);
+#pragma unroll
+          for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(to_f(s.v[j]) * inv * (to_f(w.v[j]) + (p.gemma ? 1.f : 0.f)));
+        }
+        st_vec(reinterpret_cast<T*>(p.out) + (int64_t)row * p.H + i * V, o);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_allreduce_max_ctas() { return kArMaxCtas; }
+extern "C" int64_t b200_allreduce_flag_bytes() { return (int64_t)kArMaxRanks * kArMaxCtas * sizeof(uint32_t); }
+
+extern "C" int b200_oneshot_allreduce(void* const* bufs, const void* in, void* out, void* residual, const void* weight,
+                                      uint32_t* epochs, int* status, int64_t parity_bytes, int64_t flags_offset,
+                                      int rank, int nranks, int rows, int H, float eps, int gemma, int grid,
+                                      uint32_t spin_limit, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (nranks > kArMaxRanks || grid > kArMaxCtas || grid < 1) return 2;
+  ArParams p;
+  for (int i = 0; i < kArMaxRanks; ++i) p.bufs[i] = i < nranks ? bufs[i] : nullptr;
+  p.in = in; p.out = out; p.residual = residual; p.weight = weight; p.epochs = epochs; p.status = status;
+  p.parity_bytes = parity_bytes; p.flags_offset = flags_offset; p.rank = rank; p.nranks = nranks; p.rows = rows;
+  p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit;
+  if (dtype == kBF16) {
+    if (H % 8) return 2;
+    if (residual) oneshot_allreduce_kernel<__nv_bfloat16, true><<<grid, kArThreads, 0, st>>>(p);
+    else oneshot_allreduce_kernel<__nv_bfloat16, false><<<grid, kArThreads, 0, st>>>(p);
+  } else if (dtype == kF16) {
+    if (H % 8) return 2;
+    if (residual) oneshot_allreduce_kernel<__half, true><<<grid, kArThreads, 0, st>>>(p);
+    else oneshot_allreduce_kernel<__half, false><<<grid, kArThreads, 0, st>>>(p);
+  } else if (dtype == kF32) {
+    if (H % 4) return 2;
+    if (residual) oneshot_allreduce_kernel<float, true><<<grid, kArThreads, 0, st>>>(p);
+    else oneshot_allreduce_kernel<float, false><<<grid, kArThreads, 0, st>>>(p);
+  } else {
+    return 1;
+  }
+  return (int)cudaGetLastError();
+}

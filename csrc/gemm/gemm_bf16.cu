@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(kGemmThreads)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
                int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
-               int t_tiles, int splits, int kb_per_split, int fmt, int ldo, int num_stages) {
+               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,7 +94,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_kb = (K + BK - 1) / BK;
-  const int total_items = n_tiles * t_tiles * splits;
+  const int num_tiles = n_tiles * t_tiles;
   Abort ab{status, abort_flag};
 
   if (threadIdx.x == 0) {
@@ -120,12 +120,44 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  // item -> (n_tile, t_tile, split).  Splits of one tile are adjacent so they run concurrently;
-  // without split-K, groups of 8 token tiles sweep the feature tiles so that concurrently
+  // Work decomposition.  per_cta == 0: whole tiles, CTA b takes tiles b, b + grid, ... (prefill:
+  // many tiles per SM).  per_cta > 0 ("stream-K"): the k-blocks of all tiles form one sequence of
+  // num_tiles * total_kb units and CTA b owns units [b * per_cta, (b + 1) * per_cta), so every SM
+  // streams the same number of weight bytes whatever the tile count; a tile cut by a CTA boundary
+  // is finished through the fp32 workspace by the last CTA to arrive.
+  struct Work {
+    int cur, end, stride, total_kb, num_tiles;
+    bool streamk;
+    __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1) {
+      if (!streamk) {
+        if (cur >= num_tiles) return false;
+        tile = cur; kb0 = 0; kb1 = total_kb; cur += stride;
+        return true;
+      }
+      if (cur >= end) return false;
+      tile = cur / total_kb;
+      kb0 = cur - tile * total_kb;
+      int len = min(total_kb - kb0, end - cur);
+      kb1 = kb0 + len;
+      cur += len;
+      return true;
+    }
+  };
+  auto make_work = [&]() {
+    Work w;
+    w.total_kb = total_kb; w.num_tiles = num_tiles; w.streamk = per_cta > 0;
+    if (per_cta > 0) {
+      w.cur = blockIdx.x * per_cta;
+      w.end = min(num_tiles * total_kb, w.cur + per_cta);
+      w.stride = 0;
+    } else {
+      w.cur = blockIdx.x; w.end = 0; w.stride = gridDim.x;
+    }
+    return w;
+  };
+  // tile -> (n_tile, t_tile): groups of 8 token tiles sweep the feature tiles so that concurrently
   // resident CTAs share x and W tiles in L2.
-  auto decode = [&](int item, int& nt, int& tt, int& sp) {
-    sp = item % splits;
-    int tile = item / splits;
+  auto tile_coords = [&](int tile, int& nt, int& tt) {
     constexpr int G = 8;
     int group_sz = G * n_tiles;
     int g = tile / group_sz;
@@ -143,10 +175,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        int nt, tt, sp;
-        decode(item, nt, tt, sp);
-        int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
+      Work work = make_work();
+      int tile, kb0, kb1;
+      while (ok && work.next(tile, kb0, kb1)) {
+        int nt, tt;
+        tile_coords(tile, nt, tt);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 101)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
@@ -177,10 +210,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
-        int nt, tt, sp;
-        decode(item, nt, tt, sp);
-        int kb0 = sp * kb_per_split, kb1 = min(total_kb, kb0 + kb_per_split);
+      Work work = make_work();
+      int tile, kb0, kb1;
+      for (; ok && work.next(tile, kb0, kb1); ++local) {
         int buf = local & 1;
         uint32_t acc_phase = (local >> 1) & 1;
         if (!wait_or_abort(&tmem_empty[buf], acc_phase ^ 1, ab, 102)) { ok = false; break; }
@@ -209,23 +241,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int ep_tid = (warp - 2) * 32 + lane;
     int local = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
-      int nt, tt, sp;
-      decode(item, nt, tt, sp);
+    Work work = make_work();
+    int tile, kb0, kb1;
+    for (; ok && work.next(tile, kb0, kb1); ++local) {
+      int nt, tt;
+      tile_coords(tile, nt, tt);
       int buf = local & 1;
       uint32_t acc_phase = (local >> 1) & 1;
       // One thread does the bounded wait and publishes the verdict, so that the 128 epilogue
       // threads always agree and none is left alone at a named barrier.
-      if (ep_tid == 0) *ep_ok_slot = wait_or_abort(&tmem_full[buf], acc_phase, ab, 104) ? 1 : 0;
+      // (two flag slots: thread 0 may already be publishing for the next item while a slow thread reads)
+      if (ep_tid == 0) ep_ok_slot[local & 1] = wait_or_abort(&tmem_full[buf], acc_phase, ab, 104) ? 1 : 0;
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*ep_ok_slot == 0) { ok = false; break; }
+      if (ep_ok_slot[local & 1] == 0) { ok = false; break; }
       while (!mbar_try_wait(&tmem_full[buf], acc_phase)) {}  // phase is complete: returns at once
       tc_fence_after_sync();
       const int n = nt * BM + quarter * 32 + lane;
       const int t0 = tt * BN;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
       const bool n_ok = n < N;
-      if (splits == 1) {
+      if (kb0 == 0 && kb1 == total_kb) {
         float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
 #pragma unroll
         for (int c = 0; c < BN; c += 16) {
@@ -244,9 +279,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       } else {
-        // partial tile -> workspace [tile][split][BN][128]
-        const int tile = item / splits;
-        float* wtile = ws + ((size_t)tile * splits + sp) * (BN * BM);
+        // partial tile -> workspace [tile][slot][BN][128]; slot = rank of this CTA among the CTAs
+        // whose unit ranges intersect the tile (ascending K order)
+        const int first_cta = (tile * total_kb) / per_cta;
+        const int last_cta = ((tile + 1) * total_kb - 1) / per_cta;
+        const int contrib = last_cta - first_cta + 1;
+        const int slot = (int)blockIdx.x - first_cta;
+        float* wtile = ws + ((size_t)tile * max_contrib + slot) * (BN * BM);
 #pragma unroll
         for (int c = 0; c < BN; c += 16) {
           uint32_t r[16];
@@ -262,23 +301,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ep_tid == 0) {
           int prev = atomicAdd(&counters[tile], 1);
-          if (prev == splits - 1) counters[tile] = 0;  // re-arm for the next launch / graph replay
+          if (prev == contrib - 1) counters[tile] = 0;  // re-arm for the next launch / graph replay
           *ticket_slot = prev;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*ticket_slot == splits - 1) {
+        if (*ticket_slot == contrib - 1) {
           __threadfence();
-          const float* wbase = ws + (size_t)tile * splits * (BN * BM) + quarter * 32 + lane;
+          const float* wbase = ws + (size_t)tile * max_contrib * (BN * BM) + quarter * 32 + lane;
           float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
-          // 16 columns at a time: the 16 loads of one split are independent, so their L2
-          // latencies overlap; splits are summed in index order (deterministic).
+          // 16 columns x 2 slots per round: 32 independent loads are in flight before the first add,
+          // and slots are summed in ascending K order (deterministic).
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) {
             if (t0 + c0 >= T) break;
             float acc[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] = bv;
-            for (int s = 0; s < splits; ++s) {
+            int s = 0;
+            for (; s + 2 <= contrib; s += 2) {
+              const float* wp = wbase + (size_t)s * (BN * BM) + c0 * BM;
+              float v0[16], v1[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) { v0[j] = __ldcg(wp + j * BM); v1[j] = __ldcg(wp + BN * BM + j * BM); }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] = (acc[j] + v0[j]) + v1[j];
+            }
+            if (s < contrib) {
               const float* wp = wbase + (size_t)s * (BN * BM) + c0 * BM;
 #pragma unroll
               for (int j = 0; j < 16; ++j) acc[j] += __ldcg(wp + j * BM);
@@ -318,19 +366,16 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   }
   // Shared memory per CTA decides how many CTAs share an SM: small token tiles run two CTAs per SM
   // so one CTA's prologue / split-K epilogue overlaps the other's main loop.
-  int ctas_per_sm = a.ctas_per_sm > 0 ? a.ctas_per_sm : ((BN <= 64 && a.t_tiles == 1) ? 2 : 1);
+  int ctas_per_sm = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
   int budget = (kSmemBudget + 16 * 1024) / ctas_per_sm - 2048;
   int stages = a.stages > 0 ? a.stages : budget / Cfg::kStageBytes;
   if (stages > 12) stages = 12;
   if (stages > Cfg::kStagesRaw) stages = Cfg::kStagesRaw;
   if (stages < 2) stages = 2;
   int smem = stages * Cfg::kStageBytes + 1024 + 512;
-  int items = a.n_tiles * a.t_tiles * a.splits;
-  int slots = a.num_sms * ctas_per_sm;
-  int grid = items < slots ? items : slots;
-  kern<<<grid, kGemmThreads, smem, st>>>(tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.ws, a.counters, a.status,
-                                         a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.splits, a.kb_per_split, a.fmt,
-                                         a.ldo, stages);
+  kern<<<a.grid, kGemmThreads, smem, st>>>(tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.ws, a.counters, a.status,
+                                           a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta, a.max_contrib, a.fmt,
+                                           a.ldo, stages);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,103 @@
+"""Tensor / pipeline parallel plumbing on CPU ranks (gloo): TP=2 and PP=2 reproduce the single-rank tokens."""
+import dataclasses
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from vllm_kunlun_b200.config import qwen2_0_5b
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _cfg():
+    return dataclasses.replace(qwen2_0_5b(), num_layers=2, vocab_size=512, hidden_size=128, num_heads=4, num_kv_heads=2,
+                               head_dim=32, v_head_dim=32, rotary_dim=32, intermediate_size=256, max_position=1024)
+
+
+def _prompts():
+    g = torch.Generator().manual_seed(0)
+    return [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 40, 7)]
+
+
+def _full_state(cfg):
+    """Deterministic full (unsharded) checkpoint in HF naming."""
+    g = torch.Generator().manual_seed(7)
+    sd = {}
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    r = lambda *s: torch.randn(*s, generator=g) * 0.05
+    sd["model.embed_tokens.weight"] = r(cfg.vocab_size, H)
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        sd[p + "input_layernorm.weight"] = 1 + r(H)
+        sd[p + "post_attention_layernorm.weight"] = 1 + r(H)
+        sd[p + "self_attn.q_proj.weight"] = r(cfg.q_size, H)
+        sd[p + "self_attn.k_proj.weight"] = r(cfg.kv_size, H)
+        sd[p + "self_attn.v_proj.weight"] = r(cfg.kv_size, H)
+        sd[p + "self_attn.q_proj.bias"] = r(cfg.q_size)
+        sd[p + "self_attn.k_proj.bias"] = r(cfg.kv_size)
+        sd[p + "self_attn.v_proj.bias"] = r(cfg.kv_size)
+        sd[p + "self_attn.o_proj.weight"] = r(H, cfg.q_size)
+        sd[p + "mlp.gate_proj.weight"] = r(I, H)
+        sd[p + "mlp.up_proj.weight"] = r(I, H)
+        sd[p + "mlp.down_proj.weight"] = r(H, I)
+    sd["model.norm.weight"] = 1 + r(H)
+    return sd
+
+
+def _run(rank, world, port, tp, pp, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    cfg = _cfg()
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, pipeline_parallel_size=pp, block_size=16, max_model_len=128,
+              max_num_seqs=4, num_gpu_blocks=64)
+    with torch.inference_mode():
+        llm.engine.runner.model.load_weights(_full_state(cfg).items())
+    outs = llm.generate(_prompts(), SamplingParams(max_tokens=8, ignore_eos=True))
+    if rank == world - 1:
+        q.put([o.token_ids for o in outs])
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+def _launch(tp, pp):
+    world = tp * pp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_run, args=(r, world, port, tp, pp, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    import queue as _q
+    import time
+    out, t0 = None, time.time()
+    while out is None:
+        try:
+            out = q.get(timeout=2)
+        except _q.Empty:
+            dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+            if dead or time.time() - t0 > 300:
+                for p in procs:
+                    p.kill()
+                raise AssertionError(f"ranks failed or timed out: exit codes {[p.exitcode for p in procs]}")
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return out
+
+
+@pytest.mark.parametrize("tp,pp", [(2, 1), (1, 2), (4, 1)])
+def test_parallel_matches_single(tp, pp):
+    ref = _launch(1, 1)
+    assert _launch(tp, pp) == ref

@@ -300,11 +300,16 @@ class ModelRunner:
         ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing)
         with set_forward_context(ctx):
             hidden = self.run_model(input_ids, md)
-            if hidden is None:  # not the last pipeline stage
-                return torch.zeros(md.logits_indices.shape[0], dtype=torch.int64, device=self.device), None
-            sel = hidden.index_select(0, md.logits_indices.long()) if md.logits_indices is not None else hidden
-            logits = self.model.compute_logits(sel)
-            tokens = self.sampler(logits, sp)
+            st = self.pstate
+            if hidden is None:  # not the last pipeline stage: sampled ids arrive from the last one
+                tokens = torch.zeros(md.logits_indices.shape[0], dtype=torch.int64, device=self.device)
+                sel = None
+            else:
+                sel = hidden.index_select(0, md.logits_indices.long()) if md.logits_indices is not None else hidden
+                logits = self.model.compute_logits(sel)
+                tokens = self.sampler(logits, sp)
+            if st.pp_size > 1:
+                st.pp_comm.broadcast(tokens, src=st.pp_size - 1)
         return tokens, sel
 
     def run_model(self, input_ids, md):

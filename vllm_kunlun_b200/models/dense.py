@@ -18,7 +18,7 @@ from ..attention.metadata import get_forward_context
 from ..config import ModelConfig
 from ..parallel.state import get_state
 from .layers import (DTYPES, ColumnParallelLinear, ParallelLMHead, RMSNorm, RowParallelLinear,
-                     VocabParallelEmbedding, get_cos_sin_cache, param)
+                     VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm)
 
 
 class GQAAttention(nn.Module):
@@ -44,8 +44,9 @@ class GQAAttention(nn.Module):
             sizes, repl = [cfg.q_size, kv_total, v_total], [False, False, False]
         self.qkv_proj = ColumnParallelLinear(cfg.hidden_size, sizes, bias=cfg.qkv_bias, dtype=dtype,
                                              device=device, quant=cfg.quantization, replicate=repl)
+        # the all-reduce of o_proj is fused into the add+RMSNorm that follows (reduce_add_rmsnorm)
         self.o_proj = RowParallelLinear(cfg.num_heads * cfg.v_head_dim, cfg.hidden_size, bias=cfg.o_bias,
-                                        dtype=dtype, device=device, quant=cfg.quantization)
+                                        dtype=dtype, device=device, quant=cfg.quantization, reduce_results=False)
         self.q_norm = self.k_norm = None
         if cfg.qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
@@ -108,16 +109,14 @@ class DenseDecoderLayer(nn.Module):
 
     def build_mlp(self, cfg, layer_idx, dtype, device):
         return GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization,
-                        cfg.hidden_act, cfg.mlp_bias)
+                        cfg.hidden_act, cfg.mlp_bias, reduce_results=False)
 
-    def forward(self, hidden, residual):
-        if residual is None:
-            residual = hidden
-            hidden = self.input_layernorm(hidden)
-        else:
-            hidden, residual = self.input_layernorm(hidden, residual)
+    def forward(self, hidden, residual, partial: bool = False):
+        """``hidden`` is a row-parallel partial sum when ``partial`` (previous layer's MLP output);
+        the returned hidden is again a partial (tp > 1) to be reduced by the next norm."""
+        hidden, residual = reduce_add_rmsnorm(hidden, residual, self.input_layernorm, partial)
         hidden = self.self_attn(hidden)
-        hidden, residual = self.post_attention_layernorm(hidden, residual)
+        hidden, residual = reduce_add_rmsnorm(hidden, residual, self.post_attention_layernorm, True)
         hidden = self.mlp(hidden)
         return hidden, residual
 
@@ -159,11 +158,16 @@ class DenseForCausalLM(nn.Module):
     def forward(self, input_ids, hidden=None, residual=None):
         if hidden is None:
             hidden = self.embed_tokens(input_ids)
+        partial = False
         for i in range(self.first_layer, self.last_layer):
-            hidden, residual = self.layers[str(i)](hidden, residual)
+            hidden, residual = self.layers[str(i)](hidden, residual, partial)
+            partial = True
         if self.norm is None:
+            st = get_state()
+            if st.tp_size > 1:  # hand a fully reduced activation to the next pipeline stage
+                hidden = st.tp_comm.all_reduce(hidden)
             return hidden, residual
-        hidden, _ = self.norm(hidden, residual)
+        hidden, _ = reduce_add_rmsnorm(hidden, residual, self.norm, partial)
         return hidden, None
 
     def compute_logits(self, hidden):

@@ -231,6 +231,24 @@ class RMSNorm(nn.Module):
         self.weight.data.copy_(w)
 
 
+def reduce_add_rmsnorm(x, residual, norm: "RMSNorm", partial: bool):
+    """``residual += all_reduce(x); out = norm(residual)`` for a row-parallel partial ``x``.
+
+    With mapped peer memory and a decode-sized payload this is ONE kernel (peer loads + add + norm,
+    replacing all-reduce call sites C1 / C2 of the reference plus the ``add_rmsnorm`` that follows
+    them); otherwise a collective followed by the fused add+norm kernel."""
+    st = get_state()
+    if partial and st.tp_size > 1:
+        comm = st.tp_comm
+        if (residual is not None and comm.peer is not None and not comm.disabled
+                and comm.peer.can_one_shot(x)):
+            return comm.peer.all_reduce_add_rmsnorm(x, residual, norm.weight, norm.eps, norm.gemma)
+        x = comm.all_reduce(x)
+    if residual is None:
+        return norm(x), x
+    return norm(x, residual)
+
+
 _ROPE_CACHE: dict = {}
 
 

@@ -55,11 +55,11 @@ class DeviceCommunicator:
         if dim < 0:
             dim += x.dim()
         x = x.contiguous()
-        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x, group=self.group)
+        flat = torch.empty((self.world_size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x, group=self.group)
         if dim == 0:
-            return out.reshape(self.world_size * x.shape[0], *x.shape[1:])
-        out = out.movedim(0, dim)
+            return flat
+        out = flat.reshape((self.world_size,) + tuple(x.shape)).movedim(0, dim)
         shp = list(x.shape)
         shp[dim] *= self.world_size
         return out.reshape(shp)
