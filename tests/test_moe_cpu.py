@@ -1,0 +1,78 @@
+"""MoE routing / fused MoE oracles and the MoE engine path on CPU."""
+import dataclasses
+
+import pytest
+import torch
+
+from vllm_kunlun_b200 import LLM, SamplingParams, ops
+from vllm_kunlun_b200.config import qwen3_30b_a3b, tiny
+from vllm_kunlun_b200.ops.reference import basic as rb
+from vllm_kunlun_b200.ops.reference import moe as rm
+
+
+def test_routing_variants():
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(7, 16, generator=g)
+    w, ids = rm.route_softmax_topk(logits, 4, True)
+    assert torch.allclose(w.sum(-1), torch.ones(7)) and ids.shape == (7, 4)
+    p = logits.softmax(-1)
+    assert torch.equal(ids.long(), p.topk(4).indices)
+    bias = torch.randn(16, generator=g) * 0.1
+    w2, ids2 = rm.route_sigmoid_group_topk(logits, bias, 4, n_group=4, topk_group=2, renormalize=True, scale=2.5)
+    assert torch.allclose(w2.sum(-1), torch.full((7,), 2.5), atol=1e-5)
+    # chosen experts come from at most topk_group groups
+    assert all(len(set((ids2[t] // 4).tolist())) <= 2 for t in range(7))
+    w3, ids3 = rm.route_topk_then_softmax(logits, 3)
+    assert torch.allclose(w3.sum(-1), torch.ones(7))
+
+
+def test_fused_moe_matches_dense_loop():
+    g = torch.Generator().manual_seed(1)
+    T, H, I, E, k = 9, 64, 32, 6, 2
+    x = torch.randn(T, H, generator=g)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.1
+    w2 = torch.randn(E, H, I, generator=g) * 0.1
+    tw, ids = rm.route_softmax_topk(torch.randn(T, E, generator=g), k)
+    out = rm.fused_moe(x, w13, w2, tw, ids)
+    ref = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            e = int(ids[t, j])
+            h = rb.silu_and_mul((x[t] @ w13[e].T).unsqueeze(0))
+            ref[t] += tw[t, j] * (h @ w2[e].T).squeeze(0)
+    assert torch.allclose(out, ref, atol=1e-4)
+    # expert-parallel halves sum to the whole
+    emap0 = torch.tensor([0, 1, 2, -1, -1, -1], dtype=torch.int32)
+    emap1 = torch.tensor([-1, -1, -1, 0, 1, 2], dtype=torch.int32)
+    a = rm.fused_moe(x, w13[:3], w2[:3], tw, ids, expert_map=emap0)
+    b = rm.fused_moe(x, w13[3:], w2[3:], tw, ids, expert_map=emap1)
+    assert torch.allclose(a + b, ref, atol=1e-4)
+
+
+def test_fp8_block_quant_roundtrip_and_gemm():
+    g = torch.Generator().manual_seed(2)
+    w = torch.randn(200, 384, generator=g) * 0.02
+    q, s = rb.quant_fp8_block(w)
+    assert s.shape == (2, 3)
+    assert (rb.dequant_fp8_block(q, s) - w).abs().max() < 0.07 * w.abs().max()
+    x = torch.randn(5, 384, generator=g)
+    y = ops.fp8_linear(x, q, s, out_dtype=torch.float32)
+    assert torch.allclose(y, x @ w.T, atol=0.05, rtol=0.1)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_moe_engine_cpu(fp8):
+    cfg = tiny(qwen3_30b_a3b(fp8=fp8), num_layers=2, vocab_size=256, hidden_size=128, num_heads=4, num_kv_heads=2,
+               head_dim=32, intermediate_size=256, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+               max_position=512, dtype="float32")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (12, 30)]
+    a = llm.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))
+    # chunked prefill must not change the result
+    llm2 = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32,
+               max_num_batched_tokens=16)
+    with torch.inference_mode():
+        llm2.engine.runner.model.load_state_dict(llm.engine.runner.model.state_dict())
+    b = llm2.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]

@@ -1,0 +1,206 @@
+"""Sparse-MoE decoders with GQA attention: Qwen3-MoE / Qwen2-MoE / Mixtral / GPT-OSS shapes.
+
+Reference behaviour being replaced: ``UnquantizedFusedMoEMethod.apply_monolithic`` hands router
+logits to ``KunlunOps.fused_moe`` (``ops/fused_moe/layer.py:36-81``, stage graph
+``ops/_kunlun_ops.py:397-637``); with expert parallelism it runs a Python loop over local experts
+with boolean masks on TP-replicated tokens and lets the layer's all-reduce combine the result
+(``fused_moe_ep``, ``ops/_kunlun_ops.py:639-696``; note it ignores sigmoid / grouped routing there).
+
+Parallel layouts here:
+* TP experts (default): every rank holds all experts with the intermediate dim sharded.
+* EP: every rank holds ``E / ep`` whole experts.  Tokens are replicated after attention, each rank
+  computes its local experts for the tokens routed to them, and the partial outputs are summed by
+  the all-reduce fused into the next norm - or, with mapped peer memory, tokens travel through the
+  dispatch / combine kernels of :mod:`vllm_kunlun_b200.parallel.ep_a2a`.
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..config import ModelConfig
+from ..parallel.state import get_state
+from .dense import STACKED, DenseDecoderLayer, DenseForCausalLM, GatedMLP
+from .layers import ReplicatedLinear, param
+
+
+class FusedExperts(nn.Module):
+    """Stacked expert weights ``w13 [E_local, 2*I_local, H]`` and ``w2 [E_local, H, I_local]``."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        st = get_state()
+        self.cfg = cfg
+        E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        self.use_ep = st.ep_size > 1
+        if self.use_ep:
+            assert E % st.ep_size == 0
+            self.num_local = E // st.ep_size
+            self.first = st.ep_rank * self.num_local
+            self.i_local = I
+            self.i_rank, self.i_size = 0, 1
+            emap = torch.full((E,), -1, dtype=torch.int32)
+            emap[self.first:self.first + self.num_local] = torch.arange(self.num_local, dtype=torch.int32)
+            self.register_buffer("expert_map", emap.to(device), persistent=False)
+        else:
+            self.num_local, self.first = E, 0
+            self.i_local = I // st.tp_size
+            self.i_rank, self.i_size = st.tp_rank, st.tp_size
+            self.expert_map = None
+        self.fp8 = cfg.quantization == "fp8"
+        wdt = torch.float8_e4m3fn if self.fp8 else dtype
+        self.w13 = param(self.num_local, 2 * self.i_local, H, dtype=wdt, device=device)
+        self.w2 = param(self.num_local, H, self.i_local, dtype=wdt, device=device)
+        self.block = tuple(cfg.weight_block_size)
+        if self.fp8:
+            bn, bk = self.block
+            self.w13_scale = param(self.num_local, -(-2 * self.i_local // bn), -(-H // bk), dtype=torch.float32,
+                                   device=device)
+            self.w2_scale = param(self.num_local, -(-H // bn), -(-self.i_local // bk), dtype=torch.float32,
+                                  device=device)
+        else:
+            self.w13_scale = self.w2_scale = None
+        self.b13 = self.b2 = None
+        if cfg.moe_bias:
+            self.b13 = param(self.num_local, 2 * self.i_local, dtype=dtype, device=device)
+            self.b2 = param(self.num_local, H, dtype=dtype, device=device)
+        self.act = cfg.hidden_act
+
+    def forward(self, x, topk_w, topk_ids):
+        return ops.fused_moe(x, self.w13, self.w2, topk_w, topk_ids, self.act, self.b13, self.b2, self.w13_scale,
+                             self.w2_scale, self.block, self.expert_map)
+
+    # ---- checkpoint loading: ``experts.{e}.{gate,up,down}_proj.{weight,weight_scale_inv}`` ----
+    def load_expert(self, e: int, which: str, pname: str, w: torch.Tensor):
+        le = e - self.first
+        if not (0 <= le < self.num_local):
+            return
+        scale = pname == "weight_scale_inv"
+        I = self.i_local
+        if which in ("gate_proj", "up_proj", "w1", "w3"):
+            dst = self.w13_scale if scale else self.w13
+            div = self.block[0] if scale else 1
+            off = 0 if which in ("gate_proj", "w1") else -(-I // div)
+            n = -(-I // div)
+            src0 = (self.i_rank * I) // div
+            dst.data[le, off:off + n].copy_(w[src0:src0 + n])
+        else:
+            dst = self.w2_scale if scale else self.w2
+            div = self.block[1] if scale else 1
+            n = -(-I // div)
+            src0 = (self.i_rank * I) // div
+            dst.data[le].copy_(w[:, src0:src0 + n])
+
+
+class SparseMoEBlock(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.gate = ReplicatedLinear(cfg.hidden_size, cfg.num_experts, bias=cfg.moe_bias, dtype=dtype, device=device)
+        self.e_score_correction_bias = (param(cfg.num_experts, dtype=torch.float32, device=device)
+                                        if cfg.router_bias else None)
+        self.experts = FusedExperts(cfg, dtype, device)
+        self.shared_experts = None
+        if cfg.num_shared_experts:
+            self.shared_experts = GatedMLP(cfg.hidden_size, cfg.moe_intermediate_size * cfg.num_shared_experts, dtype,
+                                           device, cfg.quantization, "silu", reduce_results=False)
+        self.shared_expert_gate = (ReplicatedLinear(cfg.hidden_size, 1, dtype=dtype, device=device)
+                                   if cfg.shared_expert_gate else None)
+
+    def forward(self, x):
+        cfg = self.cfg
+        logits = self.gate(x)
+        w, ids = ops.moe_route(logits, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
+                               self.e_score_correction_bias, cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor)
+        out = self.experts(x, w, ids)
+        if self.shared_experts is not None:
+            sh = self.shared_experts(x)
+            if self.shared_expert_gate is not None:
+                sh = sh * torch.sigmoid(self.shared_expert_gate(x).float()).to(sh.dtype)
+            st = get_state()
+            if self.experts.use_ep and st.tp_size > 1:
+                # routed part is complete per rank only after the EP sum; shared part is a TP partial:
+                # both are partial sums over the same ranks, so they add before the fused reduction
+                pass
+            out = out + sh
+        return out  # partial over TP / EP ranks; reduced by the next norm
+
+
+class MoEDecoderLayer(DenseDecoderLayer):
+    def build_mlp(self, cfg, layer_idx, dtype, device):
+        if cfg.layer_is_moe(layer_idx):
+            return SparseMoEBlock(cfg, dtype, device)
+        return GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization, cfg.hidden_act,
+                        cfg.mlp_bias, reduce_results=False)
+
+
+class MoEForCausalLM(DenseForCausalLM):
+    layer_cls = MoEDecoderLayer
+
+    def init_random(self, seed: int = 0, std: float = 0.02):
+        """fp8 checkpoints: draw N(0, std) in fp32 and quantise per 128x128 absmax block."""
+        from ..quantization.fp8 import Fp8BlockLinearMethod
+        g = torch.Generator(device=self.device).manual_seed(seed + 1000 * get_state().tp_rank)
+
+        def draw(shape):
+            return torch.randn(shape, generator=g, device=self.device, dtype=torch.float32) * std
+
+        done = set()
+        for mname, m in self.named_modules():
+            if isinstance(getattr(m, "method", None), Fp8BlockLinearMethod):
+                q, s = _quant_block_device(draw(m.weight.shape), m.method.block)
+                m.weight.data.copy_(q)
+                m.weight_scale_inv.data.copy_(s)
+                done.update({f"{mname}.weight", f"{mname}.weight_scale_inv"})
+            elif isinstance(m, FusedExperts) and m.fp8:
+                for wn, sn in (("w13", "w13_scale"), ("w2", "w2_scale")):
+                    wt = getattr(m, wn)
+                    for e in range(wt.shape[0]):
+                        q, s = _quant_block_device(draw(wt.shape[1:]), m.block)
+                        wt.data[e].copy_(q)
+                        getattr(m, sn).data[e].copy_(s)
+                    done.update({f"{mname}.{wn}", f"{mname}.{sn}"})
+        for name, p in self.named_parameters():
+            if name in done or p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                continue
+            if name.endswith("norm.weight") or "layernorm.weight" in name:
+                p.data.fill_(0.0 if self.cfg.gemma_norm else 1.0)
+            elif name.endswith("e_score_correction_bias"):
+                p.data.zero_()
+            else:
+                p.data.copy_(draw(p.shape).to(p.dtype))
+        self.finish_loading()
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
+        rest = []
+        loaded = set()
+        for name, w in weights:
+            if ".mlp.experts." in name and ".shared" not in name:
+                # model.layers.L.mlp.experts.E.{gate,up,down}_proj.{weight,weight_scale_inv}
+                parts = name.removeprefix("model.").split(".")
+                li, e, which, pname = parts[1], int(parts[4]), parts[5], parts[6]
+                if li in self.layers and isinstance(self.layers[li].mlp, SparseMoEBlock):
+                    self.layers[li].mlp.experts.load_expert(e, which, pname, w)
+                    loaded.add(name)
+                continue
+            name = name.replace(".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias")
+            name = name.replace(".block_sparse_moe.", ".mlp.")
+            rest.append((name, w))
+        loaded |= super().load_weights(rest)
+        return loaded
+
+
+def _quant_block_device(w: torch.Tensor, block=(128, 128)):
+    """128x128 absmax e4m3 quantisation on the tensor's own device."""
+    N, K = w.shape
+    bn, bk = block
+    Np, Kp = -(-N // bn) * bn, -(-K // bk) * bk
+    wp = torch.zeros(Np, Kp, dtype=torch.float32, device=w.device)
+    wp[:N, :K] = w
+    v = wp.reshape(Np // bn, bn, Kp // bk, bk)
+    scale = v.abs().amax(dim=(1, 3), keepdim=True).clamp(min=1e-10) / 448.0
+    q = (v / scale).clamp(-448, 448).reshape(Np, Kp)[:N, :K].to(torch.float8_e4m3fn)
+    return q, scale.reshape(Np // bn, Kp // bk)

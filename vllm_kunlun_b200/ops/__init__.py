@@ -258,3 +258,71 @@ def argmax(logits):
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]
+
+
+# ----------------------------------------------------------------------------- quantised linears
+
+def quant_fp8_per_group(x, group: int = 128, ue8m0: bool = False):
+    """Dynamic 1 x ``group`` e4m3 quantisation: ``(q, scale [..., K/group])``."""
+    if x.is_cuda:
+        from .quant_cuda import quant_fp8_group_cuda
+        return quant_fp8_group_cuda(x, group, ue8m0)
+    return _rb.quant_fp8_per_group(x, group, ue8m0)
+
+
+def fp8_linear(x, w_fp8, w_scale_inv, bias=None, block=(128, 128), out_dtype=torch.bfloat16):
+    """``y = x @ dequant(W).T`` with activations quantised per 1x128 group on the fly."""
+    if x.is_cuda:
+        from .quant_cuda import fp8_linear_cuda
+        return fp8_linear_cuda(x, w_fp8, w_scale_inv, bias, block, out_dtype)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    q, s = _rb.quant_fp8_per_group(x2, block[1])
+    y = _rb.fp8_block_gemm(q, s, w_fp8, w_scale_inv, block, torch.float32)
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype if out_dtype != torch.float8_e4m3fn else torch.bfloat16).reshape(*lead, -1)
+
+
+def int8_linear(x, w_q, w_scale, bias=None, input_scale=None, out_dtype=torch.bfloat16):
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x.is_cuda:
+        from .quant_cuda import int8_linear_cuda
+        return int8_linear_cuda(x2, w_q, w_scale, bias, input_scale, out_dtype).reshape(*lead, -1)
+    if input_scale is None:
+        q, s = _rb.quant_int8_per_token(x2)
+    else:
+        q, s = _rb.quant_int8_static(x2, input_scale.float()), input_scale.float().reshape(1, 1)
+    return _rb.int8_scaled_mm(q, s, w_q, w_scale.reshape(-1), bias, out_dtype).reshape(*lead, -1)
+
+
+# ----------------------------------------------------------------------------- MoE
+
+def moe_route(logits, k: int, scoring: str = "softmax", renormalize: bool = True, bias=None, n_group: int = 1,
+              topk_group: int = 1, scale: float = 1.0):
+    """Router: ``(weights [T, k] fp32, ids [T, k] int32)``.
+
+    ``softmax`` = softmax -> top-k (-> renormalise) (``_C::moe_softmax_topk(_norm)``);
+    ``sigmoid`` = DeepSeek-V3 group-limited routing with a selection bias
+    (``_C::moe_sigmoid_group_topk_norm``); ``softmax_after_topk`` = GPT-OSS."""
+    if logits.is_cuda:
+        from .moe_cuda import moe_route_cuda
+        return moe_route_cuda(logits, k, scoring, renormalize, bias, n_group, topk_group, scale)
+    if scoring == "softmax":
+        w, ids = _rm.route_softmax_topk(logits, k, renormalize)
+        return w * scale, ids
+    if scoring == "softmax_after_topk":
+        return _rm.route_topk_then_softmax(logits, k)
+    return _rm.route_sigmoid_group_topk(logits, bias, k, n_group, topk_group, renormalize, scale)
+
+
+def fused_moe(x, w13, w2, topk_weights, topk_ids, act: str = "silu", b13=None, b2=None, w13_scale=None,
+              w2_scale=None, block=(128, 128), expert_map=None, num_local_experts=None):
+    """Routed experts: permute -> grouped GEMM(w13) -> act*mul -> grouped GEMM(w2) -> weighted un-permute.
+    ``expert_map`` (global id -> local id or -1) restricts the work to this rank's experts."""
+    if x.is_cuda:
+        from .moe_cuda import fused_moe_cuda
+        return fused_moe_cuda(x, w13, w2, topk_weights, topk_ids, act, b13, b2, w13_scale, w2_scale, block,
+                              expert_map)
+    return _rm.fused_moe(x, w13, w2, topk_weights, topk_ids, act, b13, b2, w13_scale, w2_scale, block, expert_map)
