@@ -213,8 +213,12 @@ def main():
                           "ms_per_step": round(e2e_max / args.steps, 2)}
         print(json.dumps(out), flush=True)
     if world > 1:
+        # leave together; captured graphs still reference the NCCL communicator, so the process
+        # exits without an explicit communicator teardown
+        torch.cuda.synchronize()
         dist.barrier(device_ids=[local])
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        os._exit(0)
     return 0
 
 

@@ -75,12 +75,12 @@ if __name__ == "__main__":
         code = 1
     with open(f"{out}.rank{rank}.json", "w") as f:
         json.dump(res, f)
+    # Orderly exit: every rank reaches the barrier, then leaves without tearing NCCL down (captured
+    # CUDA graphs may still reference the communicator; process exit releases everything).
     try:
-        from vllm_kunlun_b200.parallel import state as ps
         if code == 0:
-            ps.destroy_model_parallel()
+            torch.cuda.synchronize()
             dist.barrier(device_ids=[torch.cuda.current_device()])
-            dist.destroy_process_group()
     finally:
         sys.stdout.flush()
         os._exit(code)

@@ -95,7 +95,13 @@ class ModelRunner:
             act = self.max_tokens * 16 * self.cfg.model.hidden_size * 2 + (2 << 30)
             budget = max(0, free - reserve - act)
             need = self.max_bs * self.max_blocks_per_seq
-            return int(max(16, min(budget // per, need + 64)))
+            n = int(max(16, min(budget // per, need + 64)))
+            if torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+                # every rank must plan the same pool or the (replicated) schedulers would diverge
+                t = torch.tensor([n], device=self.device, dtype=torch.int64)
+                torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+                n = int(t.item())
+            return n
         return min(self.max_bs * self.max_blocks_per_seq + 8, 4096)
 
     def _alloc_kv(self):
