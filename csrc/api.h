@@ -33,6 +33,23 @@ typedef struct GemmArgs {
 int b200_gemm_pick_bn(int T);
 int b200_gemm_launch(const GemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
 
+// Grouped (rows sorted by expert) and/or fp8 block-scaled GEMM; lod == null -> one group of M rows.
+typedef struct GroupedGemmArgs {
+  void* out;             // [M, ldo] bf16/fp16
+  const void* bias;      // [E, N] or null
+  const int* lod;        // [E + 1] device, or null
+  const float* a_scale;  // fp8: [ceil(K/128), a_stride] transposed activation scales
+  const float* w_scale;  // fp8: [E, ceil(N/128), ceil(K/128)]
+  int* status;
+  int M, N, K, E, ldo, a_stride;
+  int fp8;               // 1 = e4m3 inputs
+  int fmt;               // 16-bit inputs: 1 = bf16, 0 = fp16
+  int out_fmt;           // 1 = bf16, 0 = fp16
+  int bn;                // token tile 16 / 32 / 64 / 128
+  int grid;
+} GroupedGemmArgs;
+int b200_grouped_gemm_launch(const GroupedGemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
+
 // Encodes a 2-D row-major [rows, cols] tensor map with a [box_rows, box_cols] box and 128-byte
 // swizzle into `out` (128 bytes).  elem_bytes = 1 or 2.
 int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
@@ -47,7 +64,9 @@ int b200_act_and_mul(void* out, const void* x, int64_t rows, int d, int act, int
 int b200_quick_gelu(void* out, const void* x, int64_t n, int dtype, cudaStream_t st);
 int b200_embedding(void* out, const int64_t* ids, const void* w, int64_t T, int H, int64_t rows, int64_t vocab_start,
                    int dtype, cudaStream_t st);
-int b200_argmax(int64_t* out, const void* logits, int64_t rows, int V, int64_t stride, int dtype, cudaStream_t st);
+// scratch_val / scratch_idx: rows * chunks entries each (partial maxima)
+int b200_argmax(int64_t* out, const void* logits, int64_t rows, int V, int64_t stride, int dtype, float* scratch_val,
+                int* scratch_idx, int chunks, cudaStream_t st);
 
 // ---- rotary / cache -------------------------------------------------------------------------
 int b200_qkv_split_norm_rope_cache(void* q_out, const void* qkv, const int64_t* positions, const float* cos_sin,
@@ -78,6 +97,17 @@ int b200_paged_attention(void* out, const void* q, const void* kv_cache, const i
                          const int* qsl, const float* sinks, float* ws_o, float* ws_lse, int64_t T, int B, int Hq,
                          int Hkv, int D, int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
                          int num_splits, int window, float scale, int decode_layout, int dtype, cudaStream_t st);
+
+// ---- MoE / fp8 activation quantisation --------------------------------------------------------
+int b200_moe_route(float* out_w, int* out_ids, const void* logits, const float* bias, int64_t T, int E, int k, int mode,
+                   int renorm, int n_group, int topk_group, float scale, int64_t stride, int dtype, cudaStream_t st);
+int b200_moe_permute(void* x_sorted, int* pos_of_pair, int* lod, int* counts, int* cursor, const void* x, const int* ids,
+                     const int* emap, int64_t T, int k, int H, int E_local, int E_global, int64_t x_stride,
+                     int64_t max_rows, int dtype, cudaStream_t st);
+int b200_moe_unpermute(void* out, const void* y_sorted, const int* pos_of_pair, const float* w, int64_t T, int k, int H,
+                       int dtype, cudaStream_t st);
+int b200_quant_fp8_group(void* q, float* scale_t, const void* x, int64_t rows, int K, int64_t x_stride, int64_t s_stride,
+                         int ue8m0, const int* rows_valid_ptr, int dtype, cudaStream_t st);
 
 // ---- communication over NVLink peer memory ----------------------------------------------------
 int b200_allreduce_max_ctas();

@@ -18,6 +18,7 @@
 #include <math.h>
 
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "attn_common.cuh"
 
 namespace b200 {
@@ -328,6 +329,8 @@ template <typename T>
 __global__ void merge_splits_kernel(T* __restrict__ out, float* __restrict__ lse_out, const float* __restrict__ ws_o,
                                     const float* __restrict__ ws_lse, const float* __restrict__ sinks, int64_t rows,
                                     int Hq, int D, int splits, int64_t T_, const int* __restrict__ qsl, int B) {
+  griddep_launch();
+  griddep_wait();
   int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   int lane = threadIdx.x & 31;
@@ -408,11 +411,11 @@ extern "C" int b200_paged_attention(void* out, const void* q, const void* kv_cac
   if (num_splits > 1) {
     int64_t rows = T_ * Hq;
     if (dtype == kBF16)
-      merge_splits_kernel<__nv_bfloat16><<<(rows + 7) / 8, 256, 0, st>>>((__nv_bfloat16*)out, nullptr, ws_o, ws_lse,
-                                                                        sinks, rows, Hq, D, num_splits, T_, qsl, B);
+      launch_pdl(merge_splits_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, st, (__nv_bfloat16*)out,
+                 (float*)nullptr, (const float*)ws_o, (const float*)ws_lse, sinks, rows, Hq, D, num_splits, T_, qsl, B);
     else
-      merge_splits_kernel<__half><<<(rows + 7) / 8, 256, 0, st>>>((__half*)out, nullptr, ws_o, ws_lse, sinks, rows, Hq,
-                                                                 D, num_splits, T_, qsl, B);
+      launch_pdl(merge_splits_kernel<__half>, dim3((rows + 7) / 8), dim3(256), 0, st, (__half*)out, (float*)nullptr,
+                 (const float*)ws_o, (const float*)ws_lse, sinks, rows, Hq, D, num_splits, T_, qsl, B);
     return (int)cudaGetLastError();
   }
   return 0;

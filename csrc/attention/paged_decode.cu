@@ -8,6 +8,7 @@
 // The per-warp states are merged through shared memory at the end; split partials go to the
 // fp32 workspace consumed by merge_splits_kernel.
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "attn_common.cuh"
 
 namespace b200 {
@@ -25,6 +26,8 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(AttnParams p)
   T* sQ = reinterpret_cast<T*>(smem_dec);  // [16][D]
   T* sKV = sQ + 16 * D;                    // [kWarps][kStages][2][16][D]
 
+  griddep_launch();
+  griddep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = p.Hq / p.Hkv;
   const int kvh = blockIdx.y;
@@ -285,8 +288,7 @@ static int launch_decode(const AttnParams& p, int B, int max_q_rows, cudaStream_
     attr_set = true;
   }
   dim3 grid((max_q_rows + 15) / 16, p.Hkv, B * p.num_splits);
-  kern<<<grid, kWarps * 32, smem, st>>>(p);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, grid, dim3(kWarps * 32), smem, st, p);
 }
 
 int paged_decode_dispatch(const AttnParams& p, int B, int max_q_rows, int D, int dtype, cudaStream_t st) {

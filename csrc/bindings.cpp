@@ -151,6 +151,109 @@ int64_t gemm_status() {
 }
 void gemm_clear_tmap_cache() { gemm_state().cache.clear(); }
 
+// out[M, N] = x[M, K] @ w[e(row)]^T for rows sorted by expert (lod), or one group when lod is absent.
+// fp8: x / w are uint8 views of e4m3 data, a_scale_t [K/128, stride], w_scale [E, N/128, K/128].
+void grouped_gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& lod,
+                  const c10::optional<at::Tensor>& bias, const c10::optional<at::Tensor>& a_scale_t,
+                  const c10::optional<at::Tensor>& w_scale, int64_t bn) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && (w.dim() == 3 || w.dim() == 2));
+  TORCH_CHECK(x.stride(1) == 1 && w.is_contiguous() && out.stride(1) == 1);
+  const bool fp8 = x.element_size() == 1;
+  TORCH_CHECK(w.element_size() == x.element_size());
+  const int E = w.dim() == 3 ? w.size(0) : 1;
+  const int N = w.size(-2), K = w.size(-1), M = x.size(0);
+  TORCH_CHECK(x.size(1) == K && out.size(0) == M && out.size(1) == N);
+  TORCH_CHECK((K * x.element_size()) % 16 == 0 && (x.stride(0) * x.element_size()) % 16 == 0);
+  if (M == 0) return;
+  if (fp8) TORCH_CHECK(a_scale_t.has_value() && w_scale.has_value() && a_scale_t->stride(1) == 1 && w_scale->is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, x.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, x.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, x.options().dtype(at::kInt));
+  }
+  GroupedGemmArgs a;
+  a.out = out.data_ptr(); a.bias = opt_ptr(bias);
+  a.lod = lod.has_value() ? lod->data_ptr<int>() : nullptr;
+  a.a_scale = fp8 ? a_scale_t->data_ptr<float>() : nullptr;
+  a.w_scale = fp8 ? w_scale->data_ptr<float>() : nullptr;
+  a.status = gs.status.data_ptr<int>();
+  a.M = M; a.N = N; a.K = K; a.E = E; a.ldo = out.stride(0);
+  a.a_stride = fp8 ? a_scale_t->stride(0) : 0;
+  a.fp8 = fp8; a.fmt = x.scalar_type() == at::kBFloat16 ? 1 : 0; a.out_fmt = out.scalar_type() == at::kBFloat16 ? 1 : 0;
+  int b = (int)bn;
+  if (b <= 0) {
+    // rows per group decide the token tile: decode batches spread thin over many experts
+    int per_group = lod.has_value() ? std::max(1, M / std::max(1, E / 4)) : M;
+    b = per_group <= 16 ? 16 : per_group <= 32 ? 32 : per_group <= 64 ? 64 : 128;
+  }
+  a.bn = b;
+  int64_t n_tiles = (N + 127) / 128;
+  int64_t max_tiles = n_tiles * ((M + b - 1) / b + (lod.has_value() ? E : 0));
+  a.grid = (int)std::min<int64_t>(max_tiles, (int64_t)gs.num_sms * (b <= 64 ? 2 : 1));
+  at::Tensor w2 = w.dim() == 3 ? w.view({(int64_t)E * N, K}) : w;
+  const int eb = x.element_size();
+  const Tmap& tw = get_tmap(gs, w2, 128, eb);
+  const Tmap& tx = get_tmap(gs, x, b, eb);
+  check(b200_grouped_gemm_launch(&a, tw.b, tx.b, stream()), "grouped gemm launch");
+}
+
+std::vector<at::Tensor> moe_route(const at::Tensor& logits, const c10::optional<at::Tensor>& bias, int64_t k,
+                                  int64_t mode, bool renorm, int64_t n_group, int64_t topk_group, double scale) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1);
+  auto w = at::empty({logits.size(0), k}, logits.options().dtype(at::kFloat));
+  auto ids = at::empty({logits.size(0), k}, logits.options().dtype(at::kInt));
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous());
+  check(b200_moe_route(w.data_ptr<float>(), ids.data_ptr<int>(), logits.data_ptr(),
+                       bias.has_value() ? bias->data_ptr<float>() : nullptr, logits.size(0), logits.size(1), k, mode,
+                       renorm, n_group, topk_group, (float)scale, logits.stride(0), dtype_code(logits), stream()),
+        "moe_route");
+  return {w, ids};
+}
+
+// Returns x_sorted [T*k, H], pos_of_pair [T*k], lod [E_local + 1].  `state` = int32 [2 * E_local] zero-initialised
+// scratch (counts | cursor) owned by the caller.
+std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& ids, const c10::optional<at::Tensor>& emap,
+                                    int64_t E_local, int64_t E_global, at::Tensor state) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && ids.is_contiguous() && ids.scalar_type() == at::kInt);
+  TORCH_CHECK(state.scalar_type() == at::kInt && state.numel() >= 2 * E_local);
+  const int64_t T = x.size(0), k = ids.size(1), H = x.size(1);
+  auto xs = at::empty({T * k, H}, x.options());
+  auto pos = at::empty({T * k}, ids.options());
+  auto lod = at::empty({E_local + 1}, ids.options());
+  check(b200_moe_permute(xs.data_ptr(), pos.data_ptr<int>(), lod.data_ptr<int>(), state.data_ptr<int>(),
+                         state.data_ptr<int>() + E_local, x.data_ptr(), ids.data_ptr<int>(),
+                         emap.has_value() ? emap->data_ptr<int>() : nullptr, T, k, H, E_local, E_global, x.stride(0),
+                         T * k, dtype_code(x), stream()),
+        "moe_permute", 3);
+  return {xs, pos, lod};
+}
+
+void moe_unpermute(at::Tensor out, const at::Tensor& y_sorted, const at::Tensor& pos, const at::Tensor& w) {
+  TORCH_CHECK(out.is_contiguous() && y_sorted.is_contiguous() && w.is_contiguous() && w.scalar_type() == at::kFloat);
+  check(b200_moe_unpermute(out.data_ptr(), y_sorted.data_ptr(), pos.data_ptr<int>(), w.data_ptr<float>(), out.size(0),
+                           w.size(1), out.size(1), dtype_code(out), stream()),
+        "moe_unpermute");
+}
+
+// (q uint8 [rows, K], scale_t float [K/128, stride]); rows beyond *rows_valid (device int) are skipped.
+std::vector<at::Tensor> quant_fp8_group(const at::Tensor& x, bool ue8m0, const c10::optional<at::Tensor>& rows_valid,
+                                        int64_t pad_rows_to) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1);
+  const int64_t rows = x.size(0), K = x.size(1);
+  int64_t stride = ((rows + pad_rows_to - 1) / pad_rows_to) * pad_rows_to;
+  stride = std::max<int64_t>(stride, 4);
+  auto q = at::empty({rows, K}, x.options().dtype(at::kByte));
+  auto s = at::zeros({K / 128, stride}, x.options().dtype(at::kFloat));
+  check(b200_quant_fp8_group(q.data_ptr(), s.data_ptr<float>(), x.data_ptr(), rows, K, x.stride(0), stride, ue8m0,
+                             rows_valid.has_value() ? rows_valid->data_ptr<int>() : nullptr, dtype_code(x), stream()),
+        "quant_fp8_group");
+  return {q, s};
+}
+
 // ---------------------------------------------------------------------------------------- elementwise
 void rmsnorm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, double eps, bool gemma) {
   int H = x.size(-1);
@@ -192,8 +295,18 @@ void embedding(at::Tensor out, const at::Tensor& ids, const at::Tensor& w, int64
 }
 void argmax(at::Tensor out, const at::Tensor& logits) {
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong);
+  // persistent scratch for the per-chunk partial maxima (grown on demand, never inside a capture)
+  static at::Tensor sval, sidx;
+  const int chunks = 32;
+  int64_t need = logits.size(0) * chunks;
+  if (!sval.defined() || sval.numel() < need || sval.device() != logits.device()) {
+    int64_t n = std::max<int64_t>(need, 4096 * chunks);
+    sval = at::empty({n}, logits.options().dtype(at::kFloat));
+    sidx = at::empty({n}, logits.options().dtype(at::kInt));
+  }
   check(b200_argmax(out.data_ptr<int64_t>(), logits.data_ptr(), logits.size(0), logits.size(1), logits.stride(0),
-                    dtype_code(logits), stream()), "argmax");
+                    dtype_code(logits), sval.data_ptr<float>(), sidx.data_ptr<int>(), chunks, stream()),
+        "argmax", 2);
 }
 
 // ---------------------------------------------------------------------------------------- rotary / cache
@@ -353,6 +466,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("moe_route", &moe_route);
+  m.def("moe_permute", &moe_permute);
+  m.def("moe_unpermute", &moe_unpermute);
+  m.def("quant_fp8_group", &quant_fp8_group);
   m.def("gemm_clear_tmap_cache", &gemm_clear_tmap_cache);
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);

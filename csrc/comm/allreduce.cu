@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "../common/utils.cuh"
 
 namespace b200 {
@@ -61,6 +62,8 @@ template <typename T, bool kNorm>
 __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams p) {
   constexpr int V = Vec16<T>::N;
   __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
   const int c = blockIdx.x, G = gridDim.x;
   const int tid = threadIdx.x;
   const uint32_t epoch = p.epochs[c] + 1;
@@ -174,16 +177,16 @@ extern "C" int b200_oneshot_allreduce(void* const* bufs, const void* in, void* o
   p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit;
   if (dtype == kBF16) {
     if (H % 8) return 2;
-    if (residual) oneshot_allreduce_kernel<__nv_bfloat16, true><<<grid, kArThreads, 0, st>>>(p);
-    else oneshot_allreduce_kernel<__nv_bfloat16, false><<<grid, kArThreads, 0, st>>>(p);
+    if (residual) launch_pdl(oneshot_allreduce_kernel<__nv_bfloat16, true>, dim3(grid), dim3(kArThreads), 0, st, p);
+    else launch_pdl(oneshot_allreduce_kernel<__nv_bfloat16, false>, dim3(grid), dim3(kArThreads), 0, st, p);
   } else if (dtype == kF16) {
     if (H % 8) return 2;
-    if (residual) oneshot_allreduce_kernel<__half, true><<<grid, kArThreads, 0, st>>>(p);
-    else oneshot_allreduce_kernel<__half, false><<<grid, kArThreads, 0, st>>>(p);
+    if (residual) launch_pdl(oneshot_allreduce_kernel<__half, true>, dim3(grid), dim3(kArThreads), 0, st, p);
+    else launch_pdl(oneshot_allreduce_kernel<__half, false>, dim3(grid), dim3(kArThreads), 0, st, p);
   } else if (dtype == kF32) {
     if (H % 4) return 2;
-    if (residual) oneshot_allreduce_kernel<float, true><<<grid, kArThreads, 0, st>>>(p);
-    else oneshot_allreduce_kernel<float, false><<<grid, kArThreads, 0, st>>>(p);
+    if (residual) launch_pdl(oneshot_allreduce_kernel<float, true>, dim3(grid), dim3(kArThreads), 0, st, p);
+    else launch_pdl(oneshot_allreduce_kernel<float, false>, dim3(grid), dim3(kArThreads), 0, st, p);
   } else {
     return 1;
   }

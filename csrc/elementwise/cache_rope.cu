@@ -10,6 +10,7 @@
 #include <math.h>
 
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "../common/utils.cuh"
 
 namespace b200 {
@@ -28,6 +29,8 @@ __global__ void qkv_split_norm_rope_cache_kernel(
     int Hkv, int D, int rot_dim, int neox, int gemma, T* __restrict__ kv_cache, const int64_t* __restrict__ slots,
     int block_size, int64_t num_blocks, int64_t max_pos, int64_t qkv_stride) {
   extern __shared__ float sm[];
+  griddep_launch();
+  griddep_wait();
   const int warps = blockDim.x >> 5;
   const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = blockIdx.x;
@@ -248,7 +251,7 @@ extern "C" int b200_qkv_split_norm_rope_cache(void* q_out, const void* qkv, cons
   const int warps = 4;
   dim3 grid((unsigned)T_, (Hq + 2 * Hkv + warps - 1) / warps);
   B200_DISPATCH_DTYPE(dtype, {
-    qkv_split_norm_rope_cache_kernel<T><<<grid, warps * 32, warps * D * sizeof(float), st>>>(
+    launch_pdl(qkv_split_norm_rope_cache_kernel<T>, grid, dim3(warps * 32), warps * D * sizeof(float), st,
         (T*)q_out, (const T*)qkv, positions, cos_sin, (const T*)q_w, (const T*)k_w, eps, Hq, Hkv, D, rot_dim, neox,
         gemma, (T*)kv_cache, slots, block_size, num_blocks, max_pos, qkv_stride);
   });

@@ -3,6 +3,7 @@
 #include <math.h>
 
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "../common/utils.cuh"
 
 namespace b200 {
@@ -18,6 +19,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(T* __restrict__ o
                                                                int64_t x_stride, int64_t out_stride) {
   constexpr int V = Vec16<T>::N;
   __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
   const int64_t row = blockIdx.x;
   const T* xr = x + row * x_stride;
   T* rr = kAdd ? residual + row * (int64_t)H : nullptr;
@@ -84,6 +87,8 @@ __global__ void warp_rownorm_kernel(T* __restrict__ out, const T* __restrict__ x
 template <typename T>
 __global__ void act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int d, int act) {
   constexpr int V = Vec16<T>::N;
+  griddep_launch();
+  griddep_wait();
   const int nvec = d / V;
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t total = rows * nvec;
@@ -127,6 +132,8 @@ template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const int64_t* __restrict__ ids, const T* __restrict__ w,
                                  int H, int64_t rows, int64_t vocab_start) {
   constexpr int V = Vec16<T>::N;
+  griddep_launch();
+  griddep_wait();
   int64_t t = blockIdx.x;
   int64_t id = ids[t] - vocab_start;
   bool ok = id >= 0 && id < rows;
@@ -142,40 +149,65 @@ __global__ void embedding_kernel(T* __restrict__ out, const int64_t* __restrict_
   }
 }
 
-// Arg-max over the vocabulary: one block per row; ties resolve to the lowest index (torch.argmax).
+// Arg-max over the vocabulary, two stages: grid (rows, chunks) partial maxima with 16-byte loads,
+// then one warp per row over the chunk results.  Ties resolve to the lowest index (torch.argmax).
+__device__ __forceinline__ void argmax_combine(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(1024) argmax_kernel(int64_t* __restrict__ out, const T* __restrict__ logits, int V_,
-                                                      int64_t stride) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+__global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__ pval, int* __restrict__ pidx,
+                                                             const T* __restrict__ logits, int V_, int64_t stride,
+                                                             int chunk) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  griddep_launch();
+  griddep_wait();
   const T* row = logits + blockIdx.x * stride;
+  const int lo = blockIdx.y * chunk, hi = min(V_, lo + chunk);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V_; i += blockDim.x) {
-    float f = to_f(row[i]);
-    if (f > best || (f == best && i < bi)) { best = f; bi = i; }
-  }
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15) == 0) && (lo % VN == 0);
+  int i0 = lo;
+  if (vec_ok) {
+    const int nvec = (hi - lo) / VN;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      Vec16<T> a = ld_vec(row + lo + v * VN);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffff, best, o);
-    int oi = __shfl_xor_sync(0xffffffff, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      for (int j = 0; j < VN; ++j) argmax_combine(best, bi, to_f(a.v[j]), lo + v * VN + j);
+    }
+    i0 = lo + nvec * VN;
   }
+  for (int i = i0 + threadIdx.x; i < hi; i += blockDim.x) argmax_combine(best, bi, to_f(row[i]), i);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_combine(best, bi, __shfl_xor_sync(0xffffffff, best, o), __shfl_xor_sync(0xffffffff, bi, o));
   int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   if (l == 0) { sv[w] = best; si[w] = bi; }
   __syncthreads();
   if (w == 0) {
-    int nw = blockDim.x >> 5;
-    best = l < nw ? sv[l] : -INFINITY;
-    bi = l < nw ? si[l] : 0x7fffffff;
+    best = l < 8 ? sv[l] : -INFINITY;
+    bi = l < 8 ? si[l] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffff, best, o);
-      int oi = __shfl_xor_sync(0xffffffff, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (l == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    for (int o = 4; o > 0; o >>= 1)
+      argmax_combine(best, bi, __shfl_xor_sync(0xffffffff, best, o), __shfl_xor_sync(0xffffffff, bi, o));
+    if (l == 0) { pval[blockIdx.x * gridDim.y + blockIdx.y] = best; pidx[blockIdx.x * gridDim.y + blockIdx.y] = bi; }
   }
+}
+
+__global__ void argmax_final_kernel(int64_t* __restrict__ out, const float* __restrict__ pval,
+                                    const int* __restrict__ pidx, int chunks) {
+  griddep_launch();
+  griddep_wait();
+  const int row = blockIdx.x, l = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = l; c < chunks; c += 32) argmax_combine(best, bi, pval[row * chunks + c], pidx[row * chunks + c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_combine(best, bi, __shfl_xor_sync(0xffffffff, best, o), __shfl_xor_sync(0xffffffff, bi, o));
+  if (l == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
 }  // namespace b200
@@ -188,11 +220,11 @@ extern "C" int b200_rmsnorm(void* out, const void* x, void* residual, const void
   B200_DISPATCH_DTYPE(dtype, {
     if (H % Vec16<T>::N) return 2;
     if (residual)
-      rmsnorm_kernel<T, true><<<rows, kNormThreads, 0, st>>>((T*)out, (const T*)x, (T*)residual, (const T*)w, H, eps,
-                                                             gemma, x_stride, out_stride);
+      launch_pdl(rmsnorm_kernel<T, true>, dim3(rows), dim3(kNormThreads), 0, st, (T*)out, (const T*)x, (T*)residual,
+                 (const T*)w, H, eps, gemma, x_stride, out_stride);
     else
-      rmsnorm_kernel<T, false><<<rows, kNormThreads, 0, st>>>((T*)out, (const T*)x, nullptr, (const T*)w, H, eps,
-                                                              gemma, x_stride, out_stride);
+      launch_pdl(rmsnorm_kernel<T, false>, dim3(rows), dim3(kNormThreads), 0, st, (T*)out, (const T*)x, (T*)nullptr,
+                 (const T*)w, H, eps, gemma, x_stride, out_stride);
   });
   return (int)cudaGetLastError();
 }
@@ -219,7 +251,7 @@ extern "C" int b200_act_and_mul(void* out, const void* x, int64_t rows, int d, i
     constexpr int V = Vec16<T>::N;
     if (d % V || (act == 2 && d % V)) return 2;
     int64_t total = rows * (d / V);
-    act_and_mul_kernel<T><<<(total + 255) / 256, 256, 0, st>>>((T*)out, (const T*)x, rows, d, act);
+    launch_pdl(act_and_mul_kernel<T>, dim3((total + 255) / 256), dim3(256), 0, st, (T*)out, (const T*)x, rows, d, act);
   });
   return (int)cudaGetLastError();
 }
@@ -235,14 +267,21 @@ extern "C" int b200_embedding(void* out, const int64_t* ids, const void* w, int6
   if (T_ == 0) return 0;
   B200_DISPATCH_DTYPE(dtype, {
     if (H % Vec16<T>::N) return 2;
-    embedding_kernel<T><<<T_, 128, 0, st>>>((T*)out, ids, (const T*)w, H, rows, vocab_start);
+    launch_pdl(embedding_kernel<T>, dim3(T_), dim3(128), 0, st, (T*)out, ids, (const T*)w, H, rows, vocab_start);
   });
   return (int)cudaGetLastError();
 }
 
 extern "C" int b200_argmax(int64_t* out, const void* logits, int64_t rows, int V_, int64_t stride, int dtype,
-                           cudaStream_t st) {
+                           float* scratch_val, int* scratch_idx, int chunks, cudaStream_t st) {
   if (rows == 0) return 0;
-  B200_DISPATCH_DTYPE(dtype, { argmax_kernel<T><<<rows, 1024, 0, st>>>(out, (const T*)logits, V_, stride); });
+  int chunk = ((V_ + chunks - 1) / chunks + 15) / 16 * 16;
+  chunks = (V_ + chunk - 1) / chunk;
+  B200_DISPATCH_DTYPE(dtype, {
+    launch_pdl(argmax_partial_kernel<T>, dim3(rows, chunks), dim3(256), 0, st, scratch_val, scratch_idx,
+               (const T*)logits, V_, stride, chunk);
+  });
+  launch_pdl(argmax_final_kernel, dim3(rows), dim3(32), 0, st, out, (const float*)scratch_val,
+             (const int*)scratch_idx, chunks);
   return (int)cudaGetLastError();
 }

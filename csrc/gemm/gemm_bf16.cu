@@ -19,7 +19,9 @@
 #include <cuda_fp16.h>
 
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "../common/ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace b200 {
 
@@ -37,40 +39,6 @@ struct GemmCfg {
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
 };
-
-struct Abort {
-  int* status;
-  volatile int* flag;  // shared-memory abort flag
-  __device__ __forceinline__ bool aborted() const { return *flag != 0; }
-  __device__ __forceinline__ void raise(int code) {
-    *flag = 1;
-    atomicCAS(status, 0, code);
-  }
-};
-
-// Bounded wait that also leaves early once another role of this CTA has given up.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Abort& ab, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < (1u << 20); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255) == 255 && ab.aborted()) return false;
-  }
-  ab.raise(code);
-  return false;
-}
-
-template <typename OutT>
-__device__ __forceinline__ OutT from_float(float v);
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
-template <>
-__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half(v); }
-template <typename T>
-__device__ __forceinline__ float to_float(T v);
-template <>
-__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <>
-__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
 
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads)
@@ -110,6 +78,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     mbar_fence_init();
     prefetch_tmap(&tmW);
     prefetch_tmap(&tmX);
+    griddep_launch();  // the next kernel may become resident and run its own prologue
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
@@ -175,18 +144,39 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
+      // Weights do not depend on the previous kernel: stream the first num_stages weight tiles
+      // before waiting for it, so HBM stays busy across the kernel boundary.  The activation tile
+      // of each of those stages is added after the wait (one barrier, two copies).
+      int pre = 0;
+      {
+        Work w2 = make_work();
+        int tile, kb0, kb1;
+        while (pre < num_stages && w2.next(tile, kb0, kb1)) {
+          int nt, tt;
+          tile_coords(tile, nt, tt);
+          for (int kb = kb0; kb < kb1 && pre < num_stages; ++kb, ++pre) {
+            mbar_expect_tx(&full_bar[pre], Cfg::kStageBytes);
+            tma_load_2d_hint(smem + pre * Cfg::kStageBytes, &tmW, &full_bar[pre], kb * BK, nt * BM, pol_w);
+          }
+        }
+      }
+      griddep_wait();
       Work work = make_work();
       int tile, kb0, kb1;
       while (ok && work.next(tile, kb0, kb1)) {
         int nt, tt;
         tile_coords(tile, nt, tt);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 101)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageBytesA;
-          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d_hint(sa, &tmW, &full_bar[stage], kb * BK, nt * BM, pol_w);
-          tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
+          if (issued < pre) {
+            tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
+          } else {
+            if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 101)) { ok = false; break; }
+            mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            tma_load_2d_hint(sa, &tmW, &full_bar[stage], kb * BK, nt * BM, pol_w);
+            tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
+          }
           ++issued;
           if (++stage == num_stages) { stage = 0; phase ^= 1; }
         }
@@ -241,6 +231,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int ep_tid = (warp - 2) * 32 + lane;
     int local = 0;
     bool ok = true;
+    griddep_wait();  // before the first global write / workspace access of this CTA
     Work work = make_work();
     int tile, kb0, kb1;
     for (; ok && work.next(tile, kb0, kb1); ++local) {
@@ -369,14 +360,16 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   int ctas_per_sm = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
   int budget = (kSmemBudget + 16 * 1024) / ctas_per_sm - 2048;
   int stages = a.stages > 0 ? a.stages : budget / Cfg::kStageBytes;
+  // decode-sized token tiles: keep a CTA near 110 KB so the next GEMM's CTA can become resident
+  // beside it (PDL) and start prefetching its weights while this one drains
+  if (a.stages <= 0 && BN <= 64 && a.t_tiles == 1 && stages > 6) stages = 6;
   if (stages > 12) stages = 12;
   if (stages > Cfg::kStagesRaw) stages = Cfg::kStagesRaw;
   if (stages < 2) stages = 2;
   int smem = stages * Cfg::kStageBytes + 1024 + 512;
-  kern<<<a.grid, kGemmThreads, smem, st>>>(tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.ws, a.counters, a.status,
-                                           a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta, a.max_contrib, a.fmt,
-                                           a.ldo, stages);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(a.grid), dim3(kGemmThreads), (size_t)smem, st, tmW, tmX, (OutT*)a.out,
+                    (const OutT*)a.bias, a.ws, a.counters, a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta,
+                    a.max_contrib, a.fmt, a.ldo, stages);
 }
 
 }  // namespace b200

@@ -1,0 +1,344 @@
+// MoE routing, permutation and fp8 activation quantisation kernels.
+//
+// route:     one warp per token over E <= 512 experts: softmax / sigmoid(+bias, group-limited) /
+//            top-k-then-softmax, k <= 16 rounds of warp arg-max (ties -> lowest expert id).
+// permute:   histogram of (token, slot) pairs per local expert -> exclusive scan (lod) -> scatter of
+//            token rows into expert-sorted order; pairs routed to non-local experts are dropped.
+// unpermute: out[t] = sum_j w[t, j] * y_sorted[pos(t, j)]   (fixed j order: deterministic)
+// quant:     dynamic 1x128 e4m3 quantisation, scales stored transposed [K/128, stride] for the GEMM.
+#include <cuda_fp8.h>
+#include <math.h>
+
+#include "../api.h"
+#include "../common/launch.cuh"
+#include "../common/utils.cuh"
+
+namespace b200 {
+
+constexpr int kMaxEPerLane = 16;  // E <= 512
+constexpr int kMaxTopK = 16;
+
+// mode: 0 softmax->topk, 1 sigmoid group-limited, 2 topk->softmax
+template <typename T>
+__global__ void moe_route_kernel(float* __restrict__ out_w, int* __restrict__ out_ids, const T* __restrict__ logits,
+                                 const float* __restrict__ bias, int64_t T_, int E, int k, int mode, int renorm,
+                                 int n_group, int topk_group, float scale, int64_t stride) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T_) return;
+  const int lane = threadIdx.x & 31;
+  const int per = (E + 31) / 32;
+  float score[kMaxEPerLane];  // unbiased weight source
+  float sel[kMaxEPerLane];    // selection score
+  const T* row = logits + t * stride;
+  // expert e lives on lane e % 32, slot e / 32
+  float mx = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < kMaxEPerLane; ++s) {
+    int e = s * 32 + lane;
+    float v = (s < per && e < E) ? to_f(row[e]) : -INFINITY;
+    score[s] = v;
+    mx = fmaxf(mx, v);
+  }
+  if (mode == 0) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxEPerLane; ++s) {
+      float p = (score[s] == -INFINITY) ? 0.f : __expf(score[s] - mx);
+      sum += p;
+      score[s] = p;
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int s = 0; s < kMaxEPerLane; ++s) {
+      int e = s * 32 + lane;
+      score[s] = (s < per && e < E) ? score[s] / sum : -INFINITY;
+      sel[s] = score[s];
+    }
+  } else if (mode == 1) {
+#pragma unroll
+    for (int s = 0; s < kMaxEPerLane; ++s) {
+      int e = s * 32 + lane;
+      bool ok = s < per && e < E;
+      float sg = ok ? 1.f / (1.f + __expf(-score[s])) : -INFINITY;
+      score[s] = sg;
+      sel[s] = ok ? sg + (bias ? bias[e] : 0.f) : -INFINITY;
+    }
+    if (n_group > 1) {
+      // group score = sum of the two best selection scores in the group; keep the best topk_group groups
+      const int gsz = E / n_group;
+      float gscore_mine = -INFINITY;  // lane g holds the score of group g (n_group <= 32)
+      for (int g = 0; g < n_group; ++g) {
+        float b1 = -INFINITY, b2 = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < kMaxEPerLane; ++s) {
+          int e = s * 32 + lane;
+          if (s < per && e < E && e / gsz == g) {
+            float v = sel[s];
+            if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v;
+          }
+        }
+        // merge (b1, b2) pairs across lanes
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          float o1 = __shfl_xor_sync(0xffffffff, b1, o), o2 = __shfl_xor_sync(0xffffffff, b2, o);
+          float n1 = fmaxf(b1, o1);
+          float n2 = fmaxf(fminf(b1, o1), fmaxf(b2, o2));
+          b1 = n1; b2 = n2;
+        }
+        float gs = (gsz >= 2) ? b1 + b2 : b1;
+        if (lane == g) gscore_mine = gs;
+      }
+      uint32_t keep = 0;
+      for (int r = 0; r < topk_group; ++r) {
+        float v = gscore_mine;
+        int idx = lane;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          float ov = __shfl_xor_sync(0xffffffff, v, o);
+          int oi = __shfl_xor_sync(0xffffffff, idx, o);
+          if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        keep |= 1u << idx;
+        if (lane == idx) gscore_mine = -INFINITY;
+      }
+#pragma unroll
+      for (int s = 0; s < kMaxEPerLane; ++s) {
+        int e = s * 32 + lane;
+        if (s < per && e < E && !((keep >> (e / gsz)) & 1u)) sel[s] = -INFINITY;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < kMaxEPerLane; ++s) sel[s] = score[s];
+  }
+  // k rounds of warp arg-max over sel
+  float wsel[kMaxTopK];
+  int isel[kMaxTopK];
+  float wsum = 0.f;
+  for (int r = 0; r < k; ++r) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    float sc = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxEPerLane; ++s) {
+      int e = s * 32 + lane;
+      if (s < per && e < E && (sel[s] > v || (sel[s] == v && e < idx))) { v = sel[s]; idx = e; sc = score[s]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffff, v, o);
+      int oi = __shfl_xor_sync(0xffffffff, idx, o);
+      float os = __shfl_xor_sync(0xffffffff, sc, o);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; sc = os; }
+    }
+    wsel[r] = sc;
+    isel[r] = idx;
+    wsum += sc;
+    if (idx != 0x7fffffff && (idx & 31) == lane) sel[idx >> 5] = -INFINITY;
+  }
+  if (mode == 2) {  // softmax over the selected logits
+    float m2 = -INFINITY;
+    for (int r = 0; r < k; ++r) m2 = fmaxf(m2, wsel[r]);
+    float s2 = 0.f;
+    for (int r = 0; r < k; ++r) { wsel[r] = __expf(wsel[r] - m2); s2 += wsel[r]; }
+    for (int r = 0; r < k; ++r) wsel[r] /= s2;
+  } else if (renorm) {
+    float inv = 1.f / (wsum + (mode == 1 ? 1e-20f : 0.f));
+    for (int r = 0; r < k; ++r) wsel[r] *= inv;
+  }
+  if (lane == 0) {
+    for (int r = 0; r < k; ++r) {
+      out_w[t * k + r] = wsel[r] * (mode == 2 ? 1.f : scale);
+      out_ids[t * k + r] = (isel[r] == 0x7fffffff) ? 0 : isel[r];
+    }
+  }
+}
+
+// counts[e] += number of pairs routed to local expert e  (counts zeroed by the caller kernel chain)
+__global__ void moe_count_kernel(int* __restrict__ counts, const int* __restrict__ ids, const int* __restrict__ emap,
+                                 int64_t pairs, int E_local, int E_global) {
+  extern __shared__ int sh_cnt[];
+  griddep_launch();
+  griddep_wait();
+  for (int i = threadIdx.x; i < E_local; i += blockDim.x) sh_cnt[i] = 0;
+  __syncthreads();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
+    int e = ids[i];
+    if (e < 0 || e >= E_global) continue;
+    if (emap) e = emap[e];
+    if (e >= 0 && e < E_local) atomicAdd(&sh_cnt[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E_local; i += blockDim.x)
+    if (sh_cnt[i]) atomicAdd(&counts[i], sh_cnt[i]);
+}
+
+// lod = exclusive scan of counts; cursor = lod[:-1]; counts re-zeroed for the next call
+__global__ void moe_scan_kernel(int* __restrict__ lod, int* __restrict__ cursor, int* __restrict__ counts, int E_local) {
+  griddep_launch();
+  griddep_wait();
+  const int lane = threadIdx.x;
+  int run = 0;
+  for (int e0 = 0; e0 < E_local; e0 += 32) {
+    int e = e0 + lane;
+    int c = e < E_local ? counts[e] : 0;
+    int inc = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int v = __shfl_up_sync(0xffffffff, inc, o);
+      if (lane >= o) inc += v;
+    }
+    if (e < E_local) { lod[e] = run + inc - c; cursor[e] = run + inc - c; counts[e] = 0; }
+    run += __shfl_sync(0xffffffff, inc, 31);
+  }
+  if (lane == 0) lod[E_local] = run;
+}
+
+// One warp per (token, slot) pair: claim a row of the expert's segment and copy the token row there.
+template <typename T>
+__global__ void moe_scatter_kernel(T* __restrict__ x_sorted, int* __restrict__ pos_of_pair, int* __restrict__ cursor,
+                                   const T* __restrict__ x, const int* __restrict__ ids, const int* __restrict__ emap,
+                                   int64_t pairs, int k, int H, int E_local, int E_global, int64_t x_stride,
+                                   int64_t max_rows) {
+  constexpr int V = Vec16<T>::N;
+  griddep_launch();
+  griddep_wait();
+  const int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  int e = ids[pair];
+  if (e >= 0 && e < E_global && emap) e = emap[e];
+  int pos = -1;
+  if (e >= 0 && e < E_local) {
+    if (lane == 0) pos = atomicAdd(&cursor[e], 1);
+    pos = __shfl_sync(0xffffffff, pos, 0);
+    if (pos >= max_rows) pos = -1;
+  }
+  if (lane == 0) pos_of_pair[pair] = pos;
+  if (pos < 0) return;
+  const T* src = x + (pair / k) * x_stride;
+  T* dst = x_sorted + (int64_t)pos * H;
+  for (int i = lane; i < H / V; i += 32) st_vec(dst + i * V, ld_vec(src + i * V));
+}
+
+template <typename T>
+__global__ void moe_unpermute_kernel(T* __restrict__ out, const T* __restrict__ y_sorted,
+                                     const int* __restrict__ pos_of_pair, const float* __restrict__ w, int64_t T_,
+                                     int k, int H) {
+  constexpr int V = Vec16<T>::N;
+  griddep_launch();
+  griddep_wait();
+  const int64_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < H / V; i += blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int s = 0; s < k; ++s) {
+      int pos = pos_of_pair[t * k + s];
+      if (pos < 0) continue;
+      float wt = w[t * k + s];
+      Vec16<T> a = ld_vec(y_sorted + (int64_t)pos * H + i * V);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += wt * to_f(a.v[j]);
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(acc[j]);
+    st_vec(out + t * H + i * V, o);
+  }
+}
+
+// One warp per (row, 128-group): absmax -> scale -> e4m3.  Rows >= *rows_valid_ptr (if given) are skipped.
+template <typename T>
+__global__ void quant_fp8_group_kernel(uint8_t* __restrict__ q, float* __restrict__ scale_t, const T* __restrict__ x,
+                                       int64_t rows, int K, int64_t x_stride, int64_t s_stride, int ue8m0,
+                                       const int* __restrict__ rows_valid_ptr) {
+  griddep_launch();
+  griddep_wait();
+  const int groups = K / 128;
+  const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * groups) return;
+  const int64_t row = w / groups;
+  const int g = (int)(w - row * groups);
+  if (rows_valid_ptr != nullptr && row >= *rows_valid_ptr) return;
+  const int lane = threadIdx.x & 31;
+  const T* src = x + row * x_stride + g * 128 + lane * 4;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = to_f(src[j]); amax = fmaxf(amax, fabsf(v[j])); }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  float scale = amax / 448.f;
+  if (ue8m0) scale = exp2f(ceilf(log2f(scale)));
+  const float inv = 1.f / scale;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    packed |= (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+  reinterpret_cast<uint32_t*>(q + row * (int64_t)K + g * 128)[lane] = packed;
+  if (lane == 0) scale_t[(int64_t)g * s_stride + row] = scale;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_moe_route(float* out_w, int* out_ids, const void* logits, const float* bias, int64_t T_, int E,
+                              int k, int mode, int renorm, int n_group, int topk_group, float scale, int64_t stride,
+                              int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  if (E > 32 * kMaxEPerLane || k > kMaxTopK || n_group > 32 || (n_group > 1 && E % n_group)) return 2;
+  const int wpb = 4;
+  B200_DISPATCH_DTYPE(dtype, {
+    launch_pdl(moe_route_kernel<T>, dim3((T_ + wpb - 1) / wpb), dim3(wpb * 32), 0, st, out_w, out_ids,
+               (const T*)logits, bias, T_, E, k, mode, renorm, n_group, topk_group, scale, stride);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_moe_permute(void* x_sorted, int* pos_of_pair, int* lod, int* counts, int* cursor, const void* x,
+                                const int* ids, const int* emap, int64_t T_, int k, int H, int E_local, int E_global,
+                                int64_t x_stride, int64_t max_rows, int dtype, cudaStream_t st) {
+  const int64_t pairs = T_ * k;
+  int blocks = (int)((pairs + 255) / 256);
+  if (blocks > 256) blocks = 256;
+  if (blocks < 1) blocks = 1;
+  launch_pdl(moe_count_kernel, dim3(blocks), dim3(256), (size_t)E_local * sizeof(int), st, counts, ids, emap, pairs,
+             E_local, E_global);
+  launch_pdl(moe_scan_kernel, dim3(1), dim3(32), 0, st, lod, cursor, counts, E_local);
+  if (pairs > 0) {
+    B200_DISPATCH_DTYPE(dtype, {
+      if (H % Vec16<T>::N) return 2;
+      launch_pdl(moe_scatter_kernel<T>, dim3((pairs + 7) / 8), dim3(256), 0, st, (T*)x_sorted, pos_of_pair, cursor,
+                 (const T*)x, ids, emap, pairs, k, H, E_local, E_global, x_stride, max_rows);
+    });
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_moe_unpermute(void* out, const void* y_sorted, const int* pos_of_pair, const float* w, int64_t T_,
+                                  int k, int H, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    if (H % Vec16<T>::N) return 2;
+    launch_pdl(moe_unpermute_kernel<T>, dim3(T_), dim3(256), 0, st, (T*)out, (const T*)y_sorted, pos_of_pair, w, T_,
+               k, H);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_quant_fp8_group(void* q, float* scale_t, const void* x, int64_t rows, int K, int64_t x_stride,
+                                    int64_t s_stride, int ue8m0, const int* rows_valid_ptr, int dtype,
+                                    cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (K % 128) return 2;
+  const int64_t warps = rows * (K / 128);
+  B200_DISPATCH_DTYPE(dtype, {
+    launch_pdl(quant_fp8_group_kernel<T>, dim3((warps + 7) / 8), dim3(256), 0, st, (uint8_t*)q, scale_t, (const T*)x,
+               rows, K, x_stride, s_stride, ue8m0, rows_valid_ptr);
+  });
+  return (int)cudaGetLastError();
+}

@@ -43,3 +43,15 @@ extern "C" int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, u
   memcpy(out, &tm, sizeof(tm));
   return 0;
 }
+
+// ---- PDL switch (see common/launch.cuh) ----
+#include <stdlib.h>
+namespace b200 {
+int pdl_enabled() {
+  static int v = [] {
+    const char* e = getenv("B200_PDL");
+    return (e != nullptr && e[0] == '0') ? 0 : 1;
+  }();
+  return v;
+}
+}  // namespace b200

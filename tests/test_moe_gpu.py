@@ -1,0 +1,135 @@
+"""MoE / fp8 CUDA kernels vs the fp32 oracles (B200)."""
+import pytest
+import torch
+
+from vllm_kunlun_b200 import LLM, SamplingParams, ops
+from vllm_kunlun_b200.config import qwen3_30b_a3b, tiny
+from vllm_kunlun_b200.ops.reference import basic as rb
+from vllm_kunlun_b200.ops.reference import moe as rm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol, name=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    bad = (err > atol + rtol * b.abs()).float().mean().item()
+    assert bad < 2e-3, f"{name}: {bad:.4%} elements off, max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 128, 8), (16, 128, 8), (77, 256, 8), (5, 32, 4), (300, 64, 6)])
+def test_route_softmax(T, E, k):
+    # bf16 logits tie often; ties may resolve to different experts with equal weight, so compare
+    # the sorted weights and check that every returned weight belongs to its returned expert
+    lg = torch.randn(T, E, device=DEV).bfloat16()
+    p = lg.float().softmax(-1).cpu()
+    for renorm in (True, False):
+        w, ids = ops.moe_route(lg, k, "softmax", renorm)
+        rw, rids = rm.route_softmax_topk(lg.cpu(), k, renorm)
+        _close(w.sort(-1).values, rw.sort(-1).values, 1e-4, 1e-3, "softmax weights")
+        own = p.gather(1, ids.cpu().long())
+        if renorm:
+            own = own / own.sum(-1, keepdim=True)
+        _close(w, own, 1e-4, 1e-3, "weight/expert pairing")
+        assert all(len(set(r)) == k for r in ids.cpu().tolist())
+    lg32 = torch.randn(T, E, device=DEV)
+    w, ids = ops.moe_route(lg32, k, "softmax", True)
+    rw, rids = rm.route_softmax_topk(lg32.cpu(), k, True)
+    assert torch.equal(ids.cpu().sort(-1).values, rids.sort(-1).values)
+    w, ids = ops.moe_route(lg32, k, "softmax_after_topk")
+    rw, rids = rm.route_topk_then_softmax(lg32.cpu(), k)
+    assert torch.equal(ids.cpu().sort(-1).values, rids.sort(-1).values)
+    _close(w.sort(-1).values, rw.sort(-1).values, 1e-4, 1e-3, "topk-softmax weights")
+
+
+@pytest.mark.parametrize("T", [1, 16, 130])
+def test_route_sigmoid_group(T):
+    E, k = 256, 8
+    lg = torch.randn(T, E, device=DEV)
+    bias = (torch.randn(E, device=DEV) * 0.1)
+    w, ids = ops.moe_route(lg, k, "sigmoid", True, bias, 8, 4, 2.5)
+    rw, rids = rm.route_sigmoid_group_topk(lg.cpu(), bias.cpu(), k, 8, 4, True, 2.5)
+    assert torch.equal(ids.cpu().sort(-1).values, rids.sort(-1).values)
+    _close(w.sort(-1).values, rw.sort(-1).values, 1e-4, 1e-3, "sigmoid weights")
+
+
+@pytest.mark.parametrize("T,N,K", [(16, 512, 1024), (1, 256, 128), (100, 1536, 2048), (300, 384, 7168)])
+def test_fp8_linear(T, N, K):
+    g = torch.Generator().manual_seed(T + N)
+    w = torch.randn(N, K, generator=g) * 0.02
+    q, s = rb.quant_fp8_block(w)
+    x = torch.randn(T, K, generator=g)
+    ref = ops.fp8_linear(x, q, s, out_dtype=torch.float32)
+    out = ops.fp8_linear(x.to(DEV).bfloat16(), q.to(DEV), s.to(DEV))
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    torch.cuda.synchronize()
+    check_status()
+    _close(out, ref, 0.03 * (K / 1024) ** 0.5, 0.05, f"fp8 linear {T}x{N}x{K}")
+
+
+def test_quant_fp8_group():
+    x = torch.randn(37, 512, device=DEV).bfloat16()
+    q, s = ops.quant_fp8_per_group(x)
+    rq, rs = rb.quant_fp8_per_group(x.cpu())
+    _close(s, rs, 1e-6, 1e-3, "scales")
+    deq = q.float().reshape(37, 4, 128) * s.unsqueeze(-1)
+    _close(deq.reshape(37, 512), x, 0.02, 0.07, "dequant")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("T,E,k,H,I", [(16, 128, 8, 2048, 768), (1, 16, 2, 256, 128), (200, 32, 4, 512, 256)])
+def test_fused_moe(fp8, T, E, k, H, I):
+    g = torch.Generator().manual_seed(E + T)
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.03)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.03)
+    tw, ids = rm.route_softmax_topk(torch.randn(T, E, generator=g), k)
+    if fp8:
+        q13, s13 = rb.quant_fp8_block(w13)
+        q2, s2 = rb.quant_fp8_block(w2)
+        ref = rm.fused_moe(x.float(), q13, q2, tw, ids, w13_scale=s13, w2_scale=s2)
+        out = ops.fused_moe(x.to(DEV), q13.to(DEV), q2.to(DEV), tw.to(DEV), ids.to(DEV), w13_scale=s13.to(DEV),
+                            w2_scale=s2.to(DEV))
+        tol = 0.06
+    else:
+        w13b, w2b = w13.bfloat16(), w2.bfloat16()
+        ref = rm.fused_moe(x.float(), w13b.float(), w2b.float(), tw, ids)
+        out = ops.fused_moe(x.to(DEV), w13b.to(DEV), w2b.to(DEV), tw.to(DEV), ids.to(DEV))
+        tol = 0.03
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    torch.cuda.synchronize()
+    check_status()
+    _close(out, ref, tol * ref.abs().max().item(), 0.05, f"fused_moe fp8={fp8}")
+
+
+def test_fused_moe_expert_map():
+    g = torch.Generator().manual_seed(3)
+    T, E, k, H, I = 40, 16, 4, 256, 128
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.03).bfloat16()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.03).bfloat16()
+    tw, ids = rm.route_softmax_topk(torch.randn(T, E, generator=g), k)
+    full = rm.fused_moe(x.float(), w13.float(), w2.float(), tw, ids)
+    acc = torch.zeros_like(full)
+    for r in range(2):
+        emap = torch.full((E,), -1, dtype=torch.int32)
+        emap[r * 8:(r + 1) * 8] = torch.arange(8, dtype=torch.int32)
+        acc += ops.fused_moe(x.to(DEV), w13[r * 8:(r + 1) * 8].to(DEV), w2[r * 8:(r + 1) * 8].to(DEV), tw.to(DEV),
+                             ids.to(DEV), expert_map=emap.to(DEV)).float().cpu()
+    _close(acc, full, 0.03 * full.abs().max().item(), 0.05, "expert-parallel halves")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_moe_engine_gpu(fp8):
+    cfg = tiny(qwen3_30b_a3b(fp8=fp8), num_layers=2, vocab_size=1024, hidden_size=512, num_heads=8, num_kv_heads=2,
+               head_dim=64, intermediate_size=1024, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256,
+               max_position=2048)
+    outs = []
+    for eager in (True, False):
+        llm = LLM(cfg, device="cuda", block_size=16, max_model_len=256, max_num_seqs=4, num_gpu_blocks=64,
+                  enforce_eager=eager, seed=11)
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (40, 7)]
+        outs.append([o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))])
+    assert outs[0] == outs[1]

@@ -1,0 +1,49 @@
+"""CUDA entries for quantised linears: dynamic 1x128 fp8 activation quantisation feeding the
+block-scaled tcgen05 GEMM (``csrc/gemm/gemm_grouped.cu``), and int8 W8A8."""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+
+
+def quant_fp8_group_cuda(x: torch.Tensor, group: int = 128, ue8m0: bool = False, transposed: bool = False):
+    """``(q, scale)``; ``scale`` is ``[rows, K/128]`` (or the kernel's transposed ``[K/128, stride]``)."""
+    assert group == 128
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    q, st = _ext.C().quant_fp8_group(x2, ue8m0, None, 4)
+    q = q.view(torch.float8_e4m3fn)
+    if transposed:
+        return q, st
+    return q.reshape(*lead, -1), st[:, : x2.shape[0]].T.reshape(*lead, -1)
+
+
+def fp8_linear_cuda(x, w_fp8, w_scale_inv, bias=None, block=(128, 128), out_dtype=torch.bfloat16):
+    assert tuple(block) == (128, 128), "the fp8 GEMM is specialised for 128x128 weight blocks"
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    C = _ext.C()
+    q, st = C.quant_fp8_group(x2, False, None, 4)
+    N = w_fp8.shape[0]
+    out = torch.empty(x2.shape[0], N, dtype=out_dtype, device=x.device)
+    ws = w_scale_inv if w_scale_inv.dim() == 3 else w_scale_inv.unsqueeze(0)
+    C.grouped_gemm(out, q, w_fp8.view(torch.uint8), None, bias, st, ws.contiguous(), 0)
+    return out.reshape(*lead, N)
+
+
+def int8_linear_cuda(x2, w_q, w_scale, bias, input_scale, out_dtype):
+    """W8A8 int8: weights are dequantised once into a cached bf16 copy in the GEMM layout and the
+    product runs on the 16-bit tcgen05 GEMM (per-channel weight scales fold into the cached copy;
+    activations stay in 16-bit, which is at least as accurate as the int8 path)."""
+    from .gemm_cuda import gemm_bf16
+    key = "_b200_dequant"
+    wd = getattr(w_q, key, None)
+    if wd is None:
+        wd = (w_q.float() * w_scale.float().reshape(-1, 1)).to(out_dtype)
+        setattr(w_q, key, wd)
+    return gemm_bf16(x2.to(out_dtype), wd, bias)
