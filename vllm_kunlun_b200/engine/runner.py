@@ -76,11 +76,15 @@ class ModelRunner:
             self.graphs = DecodeGraphs(self)
 
     # ------------------------------------------------------------------ memory
+    @staticmethod
+    def _layer_specs(spec):
+        """A layer's cache spec is ``(shape_per_block, dtype)`` or a list of such pairs."""
+        return spec if isinstance(spec, list) else [spec]
+
     def _bytes_per_block(self) -> int:
         total = 0
-        for _, (shape, dtype) in self.model.kv_cache_spec(self.block_size).items():
-            shapes = shape if isinstance(shape, list) else [(shape, dtype)]
-            for shp, dt in shapes:
+        for _, spec in self.model.kv_cache_spec(self.block_size).items():
+            for shp, dt in self._layer_specs(spec):
                 total += int(np.prod(shp)) * torch.empty((), dtype=dt).element_size()
         return total
 
@@ -106,12 +110,10 @@ class ModelRunner:
 
     def _alloc_kv(self):
         caches = {}
-        for i, (shape, dtype) in self.model.kv_cache_spec(self.block_size).items():
-            if isinstance(shape, list):  # several tensors per layer (e.g. MLA + indexer, GDN states)
-                caches[i] = tuple(torch.zeros((self.num_blocks if lead else n0, *shp), dtype=dt, device=self.device)
-                                  for (shp, dt), (lead, n0) in zip(shape, dtype))
-            else:
-                caches[i] = torch.zeros((self.num_blocks, *shape), dtype=dtype, device=self.device)
+        for i, spec in self.model.kv_cache_spec(self.block_size).items():
+            ts = [torch.zeros((self.num_blocks, *shp), dtype=dt, device=self.device)
+                  for shp, dt in self._layer_specs(spec)]
+            caches[i] = ts[0] if not isinstance(spec, list) else tuple(ts)
         return caches
 
     def _alloc_attn_workspace(self):

@@ -1,0 +1,212 @@
+"""DeepSeek-V2 / V3 / R1 / V3.2 (and GLM-MoE-DSA, Kimi-K2) : MLA attention + MoE with shared experts.
+
+Reference: ``vllm_kunlun/models/deepseek_v2.py`` - MLP ``:100-146``, MoE with shared experts and
+sigmoid group routing ``:149-308``, the sparse-attention indexer ``:475-788``, MLA wiring ``:791-960``,
+weight loading (``fused_qkv_a_proj``, expert mapping, MTP layers skipped) ``:1285-1413`` - and the MLA
+backends ``v1/attention/backends/mla/{common,flashmla,flashmla_sparse}.py``.
+
+Attention here always runs in the weight-absorbed form over the latent cache
+(``q_nope . W_UK`` -> 576-d MQA -> ``. W_UV``), for decode, speculative verify and prefill alike; the
+cache row is ``[kv_c (512) | k_pe (64)]``.  With ``index_topk > 0`` (V3.2) a lightning indexer
+selects the top-k context tokens per query and attention is restricted to them.
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..attention.metadata import get_forward_context
+from ..config import ModelConfig
+from ..ops.reference.basic import yarn_get_mscale
+from ..parallel.state import get_state
+from .dense import DenseDecoderLayer, GatedMLP
+from .layers import (ColumnParallelLinear, RMSNorm, ReplicatedLinear, RowParallelLinear, get_cos_sin_cache, param)
+from .moe import MoEForCausalLM, SparseMoEBlock
+
+
+class Indexer(nn.Module):
+    """Lightning indexer (``models/deepseek_v2.py:661-788``): 64 heads x 128 dims, LayerNorm on K, rotary
+    on the first 64 dims, fp8 keys with a per-token scale in their own paged cache."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.n_heads, self.head_dim, self.topk = cfg.index_n_heads, cfg.index_head_dim, cfg.index_topk
+        self.rope_dim = cfg.qk_rope_head_dim
+        self.wq_b = ReplicatedLinear(cfg.q_lora_rank, self.n_heads * self.head_dim, dtype=dtype, device=device)
+        self.wk = ReplicatedLinear(cfg.hidden_size, self.head_dim, dtype=dtype, device=device)
+        self.k_norm_weight = param(self.head_dim, dtype=dtype, device=device)
+        self.k_norm_bias = param(self.head_dim, dtype=dtype, device=device)
+        self.weights_proj = ReplicatedLinear(cfg.hidden_size, self.n_heads, dtype=dtype, device=device)
+        self.softmax_scale = self.head_dim ** -0.5
+
+    def forward(self, hidden, q_c, positions, cos_sin, k_cache, md):
+        T = hidden.shape[0]
+        q = self.wq_b(q_c).view(T, self.n_heads, self.head_dim)
+        k = self.wk(hidden)
+        k = torch.nn.functional.layer_norm(k.float(), (self.head_dim,), self.k_norm_weight.float(),
+                                           self.k_norm_bias.float(), 1e-6).to(hidden.dtype)
+        # rotary on the leading rope_dim dims of q and k (neox halves, as the reference indexer does)
+        q_pe, k_pe = ops.rope(q[..., : self.rope_dim].reshape(T, -1).contiguous(),
+                              k[:, : self.rope_dim].contiguous(), positions, cos_sin, self.rope_dim, True)
+        q = torch.cat([q_pe.view(T, self.n_heads, self.rope_dim), q[..., self.rope_dim:]], -1)
+        k = torch.cat([k_pe.view(T, self.rope_dim), k[:, self.rope_dim:]], -1)
+        ops.indexer_k_quant_and_cache(k.contiguous(), k_cache, md.slot_mapping, True)
+        q_fp8, q_scale = ops.quant_fp8_per_group(q.reshape(T * self.n_heads, self.head_dim).contiguous(), 128, True)
+        weights = self.weights_proj(hidden).float() * (self.n_heads ** -0.5) * self.softmax_scale
+        return ops.indexer_topk(q_fp8.view(T, self.n_heads, self.head_dim), q_scale.view(T, self.n_heads), weights,
+                                k_cache, md.block_tables, md.seq_lens, md.query_start_loc, self.topk,
+                                md.seq_lens_cpu, md.query_start_loc_cpu)
+
+
+class MLAAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        super().__init__()
+        st = get_state()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        self.num_heads = cfg.num_heads // st.tp_size
+        self.nope, self.rope, self.vdim, self.rank = (cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim,
+                                                      cfg.kv_lora_rank)
+        self.qk_dim = self.nope + self.rope
+        H = cfg.hidden_size
+        q = cfg.quantization
+        if cfg.q_lora_rank:
+            # checkpoint tensors q_a_proj + kv_a_proj_with_mqa are loaded into one replicated GEMM
+            self.fused_qkv_a_proj = ReplicatedLinear(H, cfg.q_lora_rank + self.rank + self.rope, dtype=dtype,
+                                                     device=device, quant=q)
+            self.q_a_layernorm = RMSNorm(cfg.q_lora_rank, cfg.rms_norm_eps, dtype, device)
+            self.q_b_proj = ColumnParallelLinear(cfg.q_lora_rank, [cfg.num_heads * self.qk_dim], dtype=dtype,
+                                                 device=device, quant=q)
+        else:
+            self.q_proj = ColumnParallelLinear(H, [cfg.num_heads * self.qk_dim], dtype=dtype, device=device, quant=q)
+            self.kv_a_proj_with_mqa = ReplicatedLinear(H, self.rank + self.rope, dtype=dtype, device=device, quant=q)
+        self.kv_a_layernorm = RMSNorm(self.rank, cfg.rms_norm_eps, dtype, device)
+        # kv_b_proj is kept in 16-bit and split into the absorbed factors after loading
+        self.kv_b_proj = ColumnParallelLinear(self.rank, [cfg.num_heads * (self.nope + self.vdim)], dtype=dtype,
+                                              device=device, quant=q)
+        self.o_proj = RowParallelLinear(cfg.num_heads * self.vdim, H, dtype=dtype, device=device, quant=q,
+                                        reduce_results=False)
+        self.w_uk = self.w_uv = None  # [N, nope, rank] / [N, rank, vdim], built in finish()
+        self.cos_sin = get_cos_sin_cache(self.rope, cfg.max_position, cfg.rope_theta, cfg.rope_scaling, device)
+        scale = self.qk_dim ** -0.5
+        rs = cfg.rope_scaling
+        if rs.type == "yarn" and rs.mscale_all_dim:
+            m = yarn_get_mscale(rs.factor, rs.mscale_all_dim)
+            scale = scale * m * m
+        self.scale = scale
+        self.indexer = Indexer(cfg, dtype, device) if cfg.index_topk else None
+        self._dtype = dtype
+
+    def finish(self):
+        """Absorb ``kv_b_proj`` (``mla/common.py:1423-1555``): ``W_UK [N, nope, rank]``, ``W_UV [N, rank, vdim]``."""
+        m = self.kv_b_proj
+        w = m.weight
+        if w.dtype == torch.float8_e4m3fn:
+            w = ops.reference_basic.dequant_fp8_block(w.cpu(), m.weight_scale_inv.cpu(), m.method.block).to(w.device)
+        w = w.to(self._dtype).view(self.num_heads, self.nope + self.vdim, self.rank)
+        self.w_uk = w[:, : self.nope].contiguous()                    # q_nope [T,N,nope] x [N,nope,rank]
+        self.w_uv = w[:, self.nope:].transpose(1, 2).contiguous()     # out [T,N,rank] x [N,rank,vdim]
+
+    def forward(self, hidden):
+        ctx = get_forward_context()
+        md = ctx.attn
+        cache = ctx.kv_caches[self.layer_idx]
+        kv_cache, idx_cache = (cache if isinstance(cache, tuple) else (cache, None))
+        T = hidden.shape[0]
+        cfg = self.cfg
+        if cfg.q_lora_rank:
+            qkv_a = self.fused_qkv_a_proj(hidden)
+            q_c = self.q_a_layernorm(qkv_a[:, : cfg.q_lora_rank].contiguous())
+            kv_c, k_pe = qkv_a[:, cfg.q_lora_rank: cfg.q_lora_rank + self.rank], qkv_a[:, cfg.q_lora_rank + self.rank:]
+            q = self.q_b_proj(q_c)
+        else:
+            q_c = None
+            q = self.q_proj(hidden)
+            kv = self.kv_a_proj_with_mqa(hidden)
+            kv_c, k_pe = kv[:, : self.rank], kv[:, self.rank:]
+        kv_c = self.kv_a_layernorm(kv_c.contiguous())
+        q = q.view(T, self.num_heads, self.qk_dim)
+        q_nope, q_pe = q[..., : self.nope], q[..., self.nope:]
+        q_pe, k_pe = ops.rope(q_pe.reshape(T, -1).contiguous(), k_pe.contiguous(), md.positions, self.cos_sin,
+                              self.rope, cfg.rope_neox)
+        ops.concat_and_cache_mla(kv_c, k_pe, kv_cache, md.slot_mapping)
+        # absorbed query: [T, N, rank] = q_nope . W_UK   (batched over heads)
+        ql = ops.bmm_heads(q_nope, self.w_uk)
+        qf = torch.cat([ql, q_pe.view(T, self.num_heads, self.rope)], -1)
+        if self.indexer is not None:
+            local_idx = self.indexer(hidden, q_c, md.positions, self.cos_sin, idx_cache, md)
+            slots = ops.convert_req_index_to_global_index(md.req_id_per_token, md.block_tables, local_idx,
+                                                          kv_cache.shape[1])
+            o = ops.sparse_mla_attention(qf.contiguous(), kv_cache, slots, self.scale, self.rank)
+        else:
+            o = ops.mla_attention(qf.contiguous(), kv_cache, md.block_tables, md.seq_lens, md.query_start_loc,
+                                  self.scale, self.rank, md.max_query_len, md.max_seq_len, md.seq_lens_cpu,
+                                  md.query_start_loc_cpu, md.workspace)
+        v = ops.bmm_heads(o, self.w_uv)  # [T, N, vdim]
+        return self.o_proj(v.reshape(T, self.num_heads * self.vdim))
+
+
+class DeepseekDecoderLayer(DenseDecoderLayer):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        nn.Module.__init__(self)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.self_attn = MLAAttention(cfg, layer_idx, dtype, device) if cfg.use_mla else None
+        if self.self_attn is None:
+            from .dense import GQAAttention
+            self.self_attn = GQAAttention(cfg, layer_idx, dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self.mlp = self.build_mlp(cfg, layer_idx, dtype, device)
+
+    def build_mlp(self, cfg, layer_idx, dtype, device):
+        if cfg.layer_is_moe(layer_idx):
+            return SparseMoEBlock(cfg, dtype, device)
+        return GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization, "silu",
+                        reduce_results=False)
+
+
+class DeepseekForCausalLM(MoEForCausalLM):
+    layer_cls = DeepseekDecoderLayer
+
+    def kv_cache_spec(self, block_size: int):
+        cfg = self.cfg
+        if not cfg.use_mla:
+            return super().kv_cache_spec(block_size)
+        spec = {}
+        for i in range(self.first_layer, self.last_layer):
+            main = ((block_size, cfg.mla_cache_dim), self.dtype)
+            spec[i] = [main, ((block_size, 132), torch.uint8)] if cfg.index_topk else main
+        return spec
+
+    def finish_loading(self):
+        super().finish_loading()
+        for m in self.modules():
+            if isinstance(m, MLAAttention):
+                m.finish()
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
+        """Checkpoint specifics (``models/deepseek_v2.py:1285-1413``): ``q_a_proj`` and
+        ``kv_a_proj_with_mqa`` stack into ``fused_qkv_a_proj``; layers past ``num_layers`` (MTP) are skipped;
+        ``mlp.gate.weight`` is the router."""
+        cfg = self.cfg
+        pending = {}
+        out = []
+        for name, w in weights:
+            parts = name.split(".")
+            if len(parts) > 2 and parts[1] == "layers" and parts[2].isdigit() and int(parts[2]) >= cfg.num_layers:
+                continue  # multi-token-prediction layers live in DeepSeekMTP
+            if cfg.q_lora_rank and (".q_a_proj." in name or ".kv_a_proj_with_mqa." in name):
+                key = name.replace(".q_a_proj.", ".fused_qkv_a_proj.").replace(".kv_a_proj_with_mqa.",
+                                                                               ".fused_qkv_a_proj.")
+                slot = 0 if ".q_a_proj." in name else 1
+                pending.setdefault(key, {})[slot] = w
+                if len(pending[key]) == 2:
+                    out.append((key, torch.cat([pending[key][0], pending[key][1]], 0)))
+                    del pending[key]
+                continue
+            name = name.replace(".indexer.k_norm.weight", ".indexer.k_norm_weight")
+            name = name.replace(".indexer.k_norm.bias", ".indexer.k_norm_bias")
+            out.append((name, w))
+        return super().load_weights(out)

@@ -326,3 +326,70 @@ def fused_moe(x, w13, w2, topk_weights, topk_ids, act: str = "silu", b13=None, b
         return fused_moe_cuda(x, w13, w2, topk_weights, topk_ids, act, b13, b2, w13_scale, w2_scale, block,
                               expert_map)
     return _rm.fused_moe(x, w13, w2, topk_weights, topk_ids, act, b13, b2, w13_scale, w2_scale, block, expert_map)
+
+
+# ----------------------------------------------------------------------------- MLA / sparse MLA / indexer
+
+def bmm_heads(x, w):
+    """Per-head batched product ``out[t, n, :] = x[t, n, :] @ w[n]`` - the MLA absorption BMMs
+    (``torch.bmm`` with ``W_UK_T`` / ``W_UV`` in ``mla/common.py:1140-1192,2009``)."""
+    if x.is_cuda:
+        from .mla_cuda import bmm_heads_cuda
+        return bmm_heads_cuda(x, w)
+    return torch.einsum("tnk,nkd->tnd", x.float(), w.float()).to(x.dtype)
+
+
+def mla_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float, kv_lora_rank: int,
+                  max_query_len: int, max_seq_len: int, seq_lens_cpu=None, query_start_loc_cpu=None, workspace=None):
+    """Weight-absorbed MLA attention over the latent cache (decode, spec-verify and causal prefill):
+    ``q [T, N, 576]`` -> ``out [T, N, 512]``."""
+    if q.is_cuda:
+        from .mla_cuda import mla_attention_cuda
+        return mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank,
+                                  max_query_len, max_seq_len, workspace)
+    sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
+    ql = query_start_loc if query_start_loc_cpu is None else query_start_loc_cpu
+    return _ra.mla_decode(q, kv_cache, block_tables, sl, ql, scale, kv_lora_rank)
+
+
+def sparse_mla_attention(q, kv_cache, indices, scale: float, d_v: int = 512):
+    """DeepSeek sparse attention: every query row attends its own ``indices [T, topk]`` (global slot ids,
+    -1 = none) of the flat latent cache.  Returns ``out [T, N, d_v]``."""
+    flat = kv_cache.reshape(-1, kv_cache.shape[-1])
+    if q.is_cuda:
+        from .mla_cuda import sparse_mla_cuda
+        return sparse_mla_cuda(q, flat, indices, scale, d_v)
+    return _ra.sparse_mla(q, flat, indices, scale, d_v)[0]
+
+
+def indexer_topk(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk: int,
+                 seq_lens_cpu=None, query_start_loc_cpu=None):
+    """Lightning-indexer scores over the paged fp8 key cache and per-row top-k.
+
+    ``q_fp8 [T, H, 128]`` (e4m3) with per-(token, head) ``q_scale [T, H]``; ``weights [T, H]``.  Row ``t`` of
+    request ``r`` sits at position ``p`` and scores keys ``0..p``.  Returns request-local token indices
+    ``[T, topk]`` (int32, -1 padded): ``_C::I8_(paged_)mqa_logits`` + ``topk_per_row`` of the reference
+    (``models/deepseek_v2.py:527-637``) in one call."""
+    if q_fp8.is_cuda:
+        from .mla_cuda import indexer_topk_cuda
+        return indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk)
+    sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
+    ql = query_start_loc if query_start_loc_cpu is None else query_start_loc_cpu
+    T = q_fp8.shape[0]
+    out = torch.full((T, topk), -1, dtype=torch.int32)
+    bs = k_cache.shape[1]
+    qf = q_fp8.float() * q_scale.float().unsqueeze(-1)
+    for r in range(block_tables.shape[0]):
+        qs, qe = int(ql[r]), int(ql[r + 1])
+        if qe == qs:
+            continue
+        L = int(sl[r])
+        pos = torch.arange(L)
+        rows = k_cache[block_tables[r, pos // bs].long(), pos % bs]
+        k = rows[:, :128].contiguous().view(torch.float8_e4m3fn).float()
+        ksc = rows[:, 128:132].contiguous().view(torch.float32).reshape(-1)
+        n = qe - qs
+        ke = torch.arange(L - n + 1, L + 1)
+        logits = _ra.indexer_logits(qf[qs:qe], k, ksc, weights[qs:qe], torch.zeros(n, dtype=torch.long), ke)
+        out[qs:qe] = _ra.topk_per_row(logits, torch.zeros(n, dtype=torch.long), ke, topk)
+    return out

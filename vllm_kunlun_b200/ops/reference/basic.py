@@ -110,6 +110,12 @@ def _yarn_find_dim(num_rot, dim, base, max_pos):
     return (dim * math.log(max_pos / (num_rot * 2 * math.pi))) / (2 * math.log(base))
 
 
+def yarn_get_mscale(scale: float = 1.0, mscale: float = 1.0) -> float:
+    if scale <= 1.0:
+        return 1.0
+    return 0.1 * mscale * math.log(scale) + 1.0
+
+
 def rope_inv_freq(rotary_dim: int, theta: float, scaling=None) -> tuple[torch.Tensor, float]:
     """Inverse frequencies and the cos/sin magnitude scale for plain / linear / llama3 / YaRN RoPE.
 
