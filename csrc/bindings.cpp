@@ -40,16 +40,17 @@ at::Tensor weak_ref_tensor(const at::Tensor& t) {
 
 // ---------------------------------------------------------------------------------------- GEMM
 struct TmapKey {
-  const void* p; int64_t rows, cols, stride; int box_rows;
+  const void* p; int64_t rows, cols, stride; int box_rows; int elem_bytes;
   bool operator==(const TmapKey& o) const {
-    return p == o.p && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows;
+    return p == o.p && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows &&
+           elem_bytes == o.elem_bytes;
   }
 };
 struct TmapHash {
   size_t operator()(const TmapKey& k) const {
     size_t h = std::hash<const void*>()(k.p);
     h ^= std::hash<int64_t>()(k.rows * 1315423911u + k.cols) + 0x9e3779b9 + (h << 6) + (h >> 2);
-    h ^= std::hash<int64_t>()(k.stride * 31 + k.box_rows) + 0x9e3779b9 + (h << 6) + (h >> 2);
+    h ^= std::hash<int64_t>()((k.stride * 31 + k.box_rows) * 4 + k.elem_bytes) + 0x9e3779b9 + (h << 6) + (h >> 2);
     return h;
   }
 };
@@ -65,7 +66,7 @@ struct GemmState {
 GemmState& gemm_state() { static GemmState s; return s; }
 
 const Tmap& get_tmap(GemmState& gs, const at::Tensor& t, int box_rows, int elem_bytes) {
-  TmapKey key{t.data_ptr(), t.size(0), t.size(1), t.stride(0), box_rows};
+  TmapKey key{t.data_ptr(), t.size(0), t.size(1), t.stride(0), box_rows, elem_bytes};
   auto it = gs.cache.find(key);
   if (it != gs.cache.end()) return it->second;
   if (gs.cache.size() > 4096) gs.cache.clear();
