@@ -89,6 +89,33 @@ def bench_gemm_sweep(iters):
         check_status()
 
 
+def profile_case(iters):
+    """A handful of launches of the two decode hot kernels on inputs larger than L2, sized for an
+    ``ncu --set full`` capture (weights 235 MB, KV cache 200 MB)."""
+    from vllm_kunlun_b200.ops.attention_cuda import AttnWorkspace, paged_attention_cuda
+    from vllm_kunlun_b200.ops.gemm_cuda import gemm_bf16
+    x = torch.randn(16, 4096, device="cuda").bfloat16()
+    w = (torch.randn(28672, 4096, device="cuda") * 0.02).bfloat16()
+    out = torch.empty(16, 28672, device="cuda", dtype=torch.bfloat16)
+    xl = torch.randn(4096, 4096, device="cuda").bfloat16()
+    wl = (torch.randn(6144, 4096, device="cuda") * 0.02).bfloat16()
+    outl = torch.empty(4096, 6144, device="cuda", dtype=torch.bfloat16)
+    B, L, Hq, Hkv, D, bs = 16, 3072, 32, 8, 128, 64
+    cache = (torch.randn(B * (L // bs) + 1, 2, Hkv, bs, D, device="cuda") * 0.5).bfloat16()
+    bt = torch.arange(B * (L // bs), device="cuda", dtype=torch.int32).reshape(B, -1)
+    sl = torch.full((B,), L, device="cuda", dtype=torch.int32)
+    qsl = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    o = torch.empty_like(q)
+    ws = AttnWorkspace(B, Hq, D, 16, "cuda")
+    for _ in range(max(1, iters)):
+        gemm_bf16(x, w, out=out)
+        gemm_bf16(xl, wl, out=outl)
+        paged_attention_cuda(o, q, cache, bt, sl, qsl, D ** -0.5, 1, L, workspace=ws)
+    torch.cuda.synchronize()
+    print("profile_case done")
+
+
 def bench_attn(iters):
     from vllm_kunlun_b200.ops.attention_cuda import AttnWorkspace, paged_attention_cuda
     hbm, tf, src = peaks()
@@ -149,4 +176,4 @@ if __name__ == "__main__":
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
     for w in a.what.split(","):
-        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "gemm_sweep": bench_gemm_sweep}[w](a.iters)
+        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "gemm_sweep": bench_gemm_sweep, "profile_case": profile_case}[w](a.iters)
