@@ -285,3 +285,39 @@ extern "C" int b200_argmax(int64_t* out, const void* logits, int64_t rows, int V
              (const int*)scratch_idx, chunks);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of b200_argmax (declaration and contract: no_alloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace {
+constexpr int kNoAllocChunks = 32;
+struct ArgmaxPartial { float val; int idx; };
+// File-scope scratch: MAX_ROWS x 32 partial maxima, split into a value plane and an index plane.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_argmax_scratch[B200_ARGMAX_NOALLOC_MAX_ROWS * kNoAllocChunks *
+                                                                 sizeof(ArgmaxPartial)];
+constexpr int kMaxDevices = 64;
+void* g_scratch_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int b200_argmax_noalloc(int64_t* out, const void* logits, int64_t rows, int V_, int64_t stride, int dtype,
+                                   cudaStream_t st) {
+  if (out == nullptr || logits == nullptr || rows < 0 || V_ <= 0 || rows > B200_ARGMAX_NOALLOC_MAX_ROWS) return 22;
+  if (rows == 0) return 0;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return 22;
+  if (g_scratch_ptr[dev] == nullptr) {
+    // once per device, with that device current: the device address of the file-scope array
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_argmax_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_scratch_ptr[dev] = p;
+  }
+  float* sval = reinterpret_cast<float*>(g_scratch_ptr[dev]);
+  int* sidx = reinterpret_cast<int*>(sval + (size_t)B200_ARGMAX_NOALLOC_MAX_ROWS * kNoAllocChunks);
+  return b200_argmax(out, logits, rows, V_, stride, dtype, sval, sidx, kNoAllocChunks, st);
+}
