@@ -29,6 +29,12 @@ typedef struct GemmArgs {
   int num_sms;
   int stages;         // 0 = choose from the shared-memory budget
   int ctas_per_sm;    // 0 = choose (2 for small token tiles)
+  // collective fusion over peer memory (all zero / null = plain GEMM)
+  void* rs_stage[8];  // reduce-scatter: staging area of every rank (peer mappings)
+  void* rs_flags[8];  // reduce-scatter: per-(source, token tile) arrival counters on every rank
+  const void* ag_flags;  // all-gather: local per-token-tile arrival counters
+  int rs_on, rs_tloc, rs_rank, ag_on, ag_expect;
+  unsigned spin_limit;
 } GemmArgs;
 int b200_gemm_pick_bn(int T);
 int b200_gemm_launch(const GemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
@@ -116,6 +122,18 @@ int b200_oneshot_allreduce(void* const* bufs, const void* in, void* out, void* r
                            uint32_t* epochs, int* status, int64_t parity_bytes, int64_t flags_offset, int rank,
                            int nranks, int rows, int H, float eps, int gemma, int grid, uint32_t spin_limit, int dtype,
                            cudaStream_t st);
+
+// Reduce-scatter consumer: sum R partial rows + residual, RMSNorm, push the row to every rank (see rs_norm_ag.cu)
+typedef struct RsNormArgs {
+  const void* stage; const void* rs_flags;
+  void* xfull[8]; void* ag_flags[8];
+  void* reset_a; void* reset_b; int reset_a_n, reset_b_n;
+  void* residual; const void* weight; int* status;
+  int rank, R, Tloc, H, rs_bn, n_tiles, ag_bn, rows_per_cta, max_tt, gemma, dtype;
+  float eps; unsigned spin_limit;
+} RsNormArgs;
+int b200_rs_norm_ag(const RsNormArgs* a, cudaStream_t st);
+int b200_sp_wait(const void* flags, int n_tt, unsigned expect, unsigned spin_limit, int* status, cudaStream_t st);
 
 #ifdef __cplusplus
 }

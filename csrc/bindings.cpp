@@ -77,6 +77,28 @@ const Tmap& get_tmap(GemmState& gs, const at::Tensor& t, int box_rows, int elem_
   return gs.cache.emplace(key, tm).first->second;
 }
 
+// Collective-fusion arguments for the NEXT gemm() call (consumed by it).
+struct GemmCommState {
+  bool active = false;
+  void* rs_stage[8] = {nullptr}; void* rs_flags[8] = {nullptr}; const void* ag_flags = nullptr;
+  int rs_on = 0, rs_tloc = 0, rs_rank = 0, ag_on = 0, ag_expect = 0;
+};
+GemmCommState g_comm;
+void set_gemm_comm(std::vector<int64_t> rs_stage, std::vector<int64_t> rs_flags, int64_t ag_flags, int64_t rs_tloc,
+                   int64_t rs_rank, int64_t ag_expect) {
+  g_comm = GemmCommState();
+  g_comm.active = true;
+  for (size_t i = 0; i < rs_stage.size() && i < 8; ++i) {
+    g_comm.rs_stage[i] = reinterpret_cast<void*>(rs_stage[i]);
+    g_comm.rs_flags[i] = reinterpret_cast<void*>(rs_flags[i]);
+  }
+  g_comm.rs_on = rs_stage.empty() ? 0 : 1;
+  g_comm.rs_tloc = rs_tloc; g_comm.rs_rank = rs_rank;
+  g_comm.ag_flags = reinterpret_cast<const void*>(ag_flags);
+  g_comm.ag_on = ag_flags != 0;
+  g_comm.ag_expect = ag_expect;
+}
+
 // out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  splits <= 0 lets the library choose.
 void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
           int64_t splits, int64_t bn_override, int64_t stages, int64_t ctas_per_sm) {
@@ -99,6 +121,14 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
     gs.status = at::zeros({1}, x.options().dtype(at::kInt));
   }
   GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.spin_limit = 1u << 22;
+  if (g_comm.active) {  // one-shot: collective fusion requested for this launch (set_gemm_comm)
+    for (int i = 0; i < 8; ++i) { a.rs_stage[i] = g_comm.rs_stage[i]; a.rs_flags[i] = g_comm.rs_flags[i]; }
+    a.ag_flags = g_comm.ag_flags; a.rs_on = g_comm.rs_on; a.rs_tloc = g_comm.rs_tloc; a.rs_rank = g_comm.rs_rank;
+    a.ag_on = g_comm.ag_on; a.ag_expect = g_comm.ag_expect;
+    g_comm.active = false;
+  }
   a.bn = bn_override > 0 ? (int)bn_override : b200_gemm_pick_bn(T);
   a.T = T; a.N = N; a.K = K;
   a.n_tiles = (N + 127) / 128;
@@ -460,6 +490,39 @@ void oneshot_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tens
         "oneshot_allreduce");
 }
 
+at::Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, at::ScalarType dtype, int64_t device) {
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, device);
+  return at::from_blob(reinterpret_cast<void*>(ptr), shape, opts);
+}
+
+void rs_norm_ag(int64_t stage, int64_t rs_flags, std::vector<int64_t> xfull, std::vector<int64_t> ag_flags,
+                int64_t reset_a, int64_t reset_a_n, int64_t reset_b, int64_t reset_b_n,
+                const c10::optional<at::Tensor>& residual, const at::Tensor& weight, at::Tensor status, int64_t rank,
+                int64_t Tloc, int64_t H, int64_t rs_bn, int64_t n_tiles, int64_t ag_bn, int64_t rows_per_cta,
+                int64_t max_tt, double eps, bool gemma, int64_t spin_limit) {
+  RsNormArgs a;
+  memset(&a, 0, sizeof(a));
+  a.stage = reinterpret_cast<const void*>(stage); a.rs_flags = reinterpret_cast<const void*>(rs_flags);
+  TORCH_CHECK(xfull.size() <= 8 && xfull.size() == ag_flags.size());
+  for (size_t i = 0; i < xfull.size(); ++i) {
+    a.xfull[i] = reinterpret_cast<void*>(xfull[i]);
+    a.ag_flags[i] = reinterpret_cast<void*>(ag_flags[i]);
+  }
+  a.reset_a = reinterpret_cast<void*>(reset_a); a.reset_a_n = reset_a_n;
+  a.reset_b = reinterpret_cast<void*>(reset_b); a.reset_b_n = reset_b_n;
+  if (residual.has_value()) { TORCH_CHECK(residual->is_contiguous()); a.residual = residual->data_ptr(); }
+  a.weight = weight.data_ptr(); a.status = status.data_ptr<int>();
+  a.rank = rank; a.R = xfull.size(); a.Tloc = Tloc; a.H = H; a.rs_bn = rs_bn; a.n_tiles = n_tiles; a.ag_bn = ag_bn;
+  a.rows_per_cta = rows_per_cta; a.max_tt = max_tt; a.gemma = gemma; a.dtype = dtype_code(weight); a.eps = (float)eps;
+  a.spin_limit = (unsigned)spin_limit;
+  check(b200_rs_norm_ag(&a, stream()), "rs_norm_ag");
+}
+
+void sp_wait(int64_t flags, int64_t n_tt, int64_t expect, int64_t spin_limit, at::Tensor status) {
+  check(b200_sp_wait(reinterpret_cast<const void*>(flags), n_tt, expect, spin_limit, status.data_ptr<int>(), stream()),
+        "sp_wait");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -498,4 +561,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("allreduce_max_ctas", &allreduce_max_ctas);
   m.def("allreduce_flag_bytes", &allreduce_flag_bytes);
   m.def("oneshot_allreduce", &oneshot_allreduce);
+  m.def("set_gemm_comm", &set_gemm_comm);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("rs_norm_ag", &rs_norm_ag);
+  m.def("sp_wait", &sp_wait);
 }

@@ -40,12 +40,41 @@ struct GemmCfg {
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
 };
 
+// Collective fusion over NVLink peer memory (all pointers are peer mappings in this process):
+//  * reduce-scatter epilogue: token t belongs to rank t / rs_tloc; the partial output tile is stored
+//    straight into that rank's staging area [src rank][local token][N] and a per-(src, token tile)
+//    counter on the owner is bumped once per finished tile, so the transfer overlaps the math;
+//  * all-gather prologue: the activation rows of a token tile were pushed into THIS rank's memory by
+//    their owners; the TMA producer waits (bounded) until the tile's arrival counter is complete
+//    and only then issues the (local) TMA loads of that tile.
+struct GemmComm {
+  void* rs_stage[8];
+  uint32_t* rs_flags[8];
+  const uint32_t* ag_flags;
+  int rs_on, rs_tloc, rs_rank;
+  int ag_on, ag_expect;
+  uint32_t spin_limit;
+};
+
+constexpr int kEpChunk = 64;             // token columns staged per pass of the coalescing epilogue
+constexpr int kEpStride = BM + 8;        // padded row of the staging tile (elements)
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
                int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
-               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages) {
+               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages,
+               const __grid_constant__ GemmComm cm) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -57,7 +86,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* ticket_slot = reinterpret_cast<int*>(tmem_base_slot + 2);
-  volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 3);
+  volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 3);  // [2]
+  OutT* smem_ep = reinterpret_cast<OutT*>((reinterpret_cast<uintptr_t>(tmem_base_slot + 6) + 15) & ~uintptr_t(15));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -166,6 +196,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       while (ok && work.next(tile, kb0, kb1)) {
         int nt, tt;
         tile_coords(tile, nt, tt);
+        if (cm.ag_on) {
+          // rows of this token tile are pushed by their owner ranks; wait until all have landed
+          bool arrived = false;
+          for (uint32_t i = 0; i < cm.spin_limit; ++i) {
+            if (ld_acquire_sys_u32(cm.ag_flags + tt) >= (uint32_t)cm.ag_expect) { arrived = true; break; }
+            if (i > 32) __nanosleep(40);
+            if ((i & 1023) == 1023 && ab.aborted()) break;
+          }
+          if (!arrived) { ab.raise(105); ok = false; break; }
+          fence_proxy_async_global();  // peer (generic-proxy) stores -> this CTA's TMA reads
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageBytesA;
@@ -253,22 +294,85 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const bool n_ok = n < N;
       if (kb0 == 0 && kb1 == total_kb) {
         float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
+        // destination row of token t: the local output, or the owner rank's staging area
+        auto row_ptr = [&](int t) -> OutT* {
+          if (cm.rs_on) {
+            int owner = t / cm.rs_tloc;
+            int tl = t - owner * cm.rs_tloc;
+            return reinterpret_cast<OutT*>(cm.rs_stage[owner]) + ((size_t)cm.rs_rank * cm.rs_tloc + tl) * N;
+          }
+          return out + (size_t)t * ldo;
+        };
+        if (BN >= kEpChunk) {
+          // TMEM -> registers -> shared [token][feature] -> 16-byte row segments (256 B per token row)
+          const int n_local = quarter * 32 + lane;
+          const int n0 = nt * BM;
+          const bool vec_ok = ((N & 7) == 0) && (cm.rs_on || (ldo & 7) == 0);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += kEpChunk) {
+            if (t0 + c0 < T) {
 #pragma unroll
-        for (int c = 0; c < BN; c += 16) {
-          uint32_t r[16];
-          tmem_ld_x16(taddr + c, r);
-          tmem_ld_wait();
-          if (n_ok) {
+              for (int c = 0; c < kEpChunk; c += 16) {
+                uint32_t r[16];
+                tmem_ld_x16(taddr + c0 + c, r);
+                tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              int t = t0 + c + j;
-              if (t < T) out[(size_t)t * ldo + n] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+                for (int j = 0; j < 16; ++j)
+                  smem_ep[(c + j) * kEpStride + n_local] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+              }
+            }
+            if (c0 + kEpChunk >= BN) {  // accumulator fully read: hand the TMEM buffer back
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (t0 + c0 < T) {
+              const int seg = ep_tid & 15;           // 16 segments of 8 features
+              const int nn = n0 + seg * 8;
+              for (int rr = ep_tid >> 4; rr < kEpChunk; rr += 8) {
+                const int t = t0 + c0 + rr;
+                if (t >= T) break;
+                OutT* dst = row_ptr(t) + nn;
+                const OutT* src = smem_ep + rr * kEpStride + seg * 8;
+                if (vec_ok && nn + 8 <= N) {
+                  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+                } else {
+                  for (int e = 0; e < 8; ++e)
+                    if (nn + e < N) dst[e] = src[e];
+                }
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN; c += 16) {
+            uint32_t r[16];
+            tmem_ld_x16(taddr + c, r);
+            tmem_ld_wait();
+            if (n_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                int t = t0 + c + j;
+                if (t < T) row_ptr(t)[n] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+              }
             }
           }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        if (cm.rs_on) {
+          // tile delivered: publish it on the owner (one arrival per tile)
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (ep_tid == 0) {
+            int owner = t0 / cm.rs_tloc;
+            int tl0 = t0 - owner * cm.rs_tloc;
+            red_release_sys_add(cm.rs_flags[owner] + tl0 / BN, 1u);
+          }
+        }
       } else {
         // partial tile -> workspace [tile][slot][BN][128]; slot = rank of this CTA among the CTAs
         // whose unit ranges intersect the tile (ascending K order)
@@ -348,17 +452,23 @@ template <int BN, typename OutT>
 static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CUtensorMap& tmX, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tn_kernel<BN, OutT>;
+  constexpr int kEpBytes = (BN >= kEpChunk) ? kEpChunk * kEpStride * 2 + 64 : 64;
+  GemmComm cm;
+  for (int i = 0; i < 8; ++i) { cm.rs_stage[i] = a.rs_stage[i]; cm.rs_flags[i] = (uint32_t*)a.rs_flags[i]; }
+  cm.ag_flags = (const uint32_t*)a.ag_flags;
+  cm.rs_on = a.rs_on; cm.rs_tloc = a.rs_tloc; cm.rs_rank = a.rs_rank; cm.ag_on = a.ag_on; cm.ag_expect = a.ag_expect;
+  cm.spin_limit = a.spin_limit;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kStagesRaw * Cfg::kStageBytes + 1024 + 512);
+                                         Cfg::kStagesRaw * Cfg::kStageBytes + 1024 + 512 + kEpBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
   // Shared memory per CTA decides how many CTAs share an SM: small token tiles run two CTAs per SM
   // so one CTA's prologue / split-K epilogue overlaps the other's main loop.
   int ctas_per_sm = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
-  int budget = (kSmemBudget + 16 * 1024) / ctas_per_sm - 2048;
+  int budget = (kSmemBudget + 24 * 1024) / ctas_per_sm - 2048 - kEpBytes;
   int stages = a.stages > 0 ? a.stages : budget / Cfg::kStageBytes;
   // decode-sized token tiles: keep a CTA near 110 KB so the next GEMM's CTA can become resident
   // beside it (PDL) and start prefetching its weights while this one drains
@@ -366,10 +476,10 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   if (stages > 12) stages = 12;
   if (stages > Cfg::kStagesRaw) stages = Cfg::kStagesRaw;
   if (stages < 2) stages = 2;
-  int smem = stages * Cfg::kStageBytes + 1024 + 512;
+  int smem = stages * Cfg::kStageBytes + 1024 + 512 + kEpBytes;
   return launch_pdl(kern, dim3(a.grid), dim3(kGemmThreads), (size_t)smem, st, tmW, tmX, (OutT*)a.out,
                     (const OutT*)a.bias, a.ws, a.counters, a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta,
-                    a.max_contrib, a.fmt, a.ldo, stages);
+                    a.max_contrib, a.fmt, a.ldo, stages, cm);
 }
 
 }  // namespace b200

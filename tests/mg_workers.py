@@ -50,7 +50,9 @@ def engine(rank, world, fused):
                head_dim=128, intermediate_size=2048, max_position=4096)
     llm = LLM(cfg, device="cuda", tensor_parallel_size=world, block_size=64, max_model_len=512, max_num_seqs=4,
               num_gpu_blocks=64, fused_collectives=bool(int(fused)), seed=5)
-    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (70, 9)]
+    # 192 + 64 = 256 prompt tokens in the first step: a multiple of world * 64, so the fused
+    # GEMM+reduce-scatter / all-gather+GEMM path serves the prefill
+    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (192, 64)]
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     torch.cuda.synchronize()
     peer = llm.engine.pstate.tp_comm.peer
@@ -59,6 +61,7 @@ def engine(rank, world, fused):
         assert peer is not None and peer.launches > 0
         peer.check_status()
         launches = peer.launches
+        assert getattr(peer, "sp_calls", 0) > 0, "fused GEMM+collective path was not taken"
     return {"tokens": [o.token_ids for o in outs], "peer_launches": launches}
 
 

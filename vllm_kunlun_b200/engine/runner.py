@@ -67,6 +67,7 @@ class ModelRunner:
         self.kv_caches = self._alloc_kv()
         self._alloc_staging()
         self.graphs = None
+        self.sp_peer = self._init_sequence_parallel()
         self.attn_workspace = self._alloc_attn_workspace()
         self.last_tokens: Optional[torch.Tensor] = None  # previous step's sampled tokens (device)
         self.last_rows: dict = {}  # request_id -> row in last_tokens of its newest token
@@ -115,6 +116,19 @@ class ModelRunner:
                   for shp, dt in self._layer_specs(spec)]
             caches[i] = ts[0] if not isinstance(spec, list) else tuple(ts)
         return caches
+
+    def _init_sequence_parallel(self):
+        """Fused GEMM+reduce-scatter / all-gather+GEMM path for large (prefill) steps under TP."""
+        st = self.pstate
+        m = self.cfg.model
+        if (not self.is_cuda or st.tp_size == 1 or st.pp_size > 1 or st.tp_comm is None
+                or st.tp_comm.peer is None or m.quantization is not None or self.model.dtype != torch.bfloat16):
+            return None
+        peer = st.tp_comm.peer
+        peer.sp_init(self.max_tokens, m.hidden_size, self.model.dtype)
+        from ..ops import gemm_cuda
+        gemm_cuda.PEER = peer
+        return peer
 
     def _alloc_attn_workspace(self):
         if not self.is_cuda or self.cfg.model.use_mla:
@@ -278,10 +292,16 @@ class ModelRunner:
         pad = self.graphs.padded_batch(len(srs)) if use_graph else 0
         md, input_ids, (sample_reqs, rows_per_req, n_logits) = self.prepare(sched, pad)
         sp = self.sampler.make_params([r.sampling for r in sample_reqs], rows_per_req, n_logits)
+        from ..models.layers import set_sp_mode
         if use_graph:
+            set_sp_mode(False)
             tokens, hidden = self.graphs.run(md, input_ids, sp)
         else:
-            tokens, hidden = self.forward_and_sample(md, input_ids, sp)
+            set_sp_mode(self.sp_peer is not None and md.num_tokens >= 128 * self.pstate.tp_size)
+            try:
+                tokens, hidden = self.forward_and_sample(md, input_ids, sp)
+            finally:
+                set_sp_mode(False)
         n_real = sum(rows_per_req)
         tokens = tokens[:n_real]
         # bookkeeping at launch time: the KV of these tokens is (being) written

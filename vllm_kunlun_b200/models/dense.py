@@ -18,7 +18,7 @@ from ..attention.metadata import get_forward_context
 from ..config import ModelConfig
 from ..parallel.state import get_state
 from .layers import (DTYPES, ColumnParallelLinear, ParallelLMHead, RMSNorm, RowParallelLinear,
-                     VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm)
+                     VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm, sp_sync)
 
 
 class GQAAttention(nn.Module):
@@ -165,9 +165,12 @@ class DenseForCausalLM(nn.Module):
         if self.norm is None:
             st = get_state()
             if st.tp_size > 1:  # hand a fully reduced activation to the next pipeline stage
+                from .layers import SPPartial
+                assert not isinstance(hidden, SPPartial), "sequence-parallel mode is not combined with PP"
                 hidden = st.tp_comm.all_reduce(hidden)
             return hidden, residual
         hidden, _ = reduce_add_rmsnorm(hidden, residual, self.norm, partial)
+        sp_sync()
         return hidden, None
 
     def compute_logits(self, hidden):

@@ -156,6 +156,12 @@ class RowParallelLinear(LinearBase):
             self.bias = param(out_features, dtype=dtype, device=device)
 
     def forward(self, x):
+        if (self.tp_size > 1 and not self.reduce_results and self.bias is None and x.is_cuda
+                and type(self.method) is UnquantizedLinearMethod):
+            peer = getattr(get_state().tp_comm, "peer", None)
+            if peer is not None and sp_mode_active() and peer.sp_ok(x.shape[0], self.out_features, x.dtype):
+                # GEMM -> reduce-scatter fused over peer memory; finished by reduce_add_rmsnorm
+                return SPPartial(peer, peer.gemm_rs(x.reshape(-1, x.shape[-1]), self.weight))
         bias = self.bias
         if self.tp_rank != 0:
             self.bias = None  # add the bias once
@@ -231,6 +237,34 @@ class RMSNorm(nn.Module):
         self.weight.data.copy_(w)
 
 
+class SPPartial:
+    """Result of a row-parallel GEMM whose tiles were scattered to their owner ranks."""
+
+    def __init__(self, peer, handle):
+        self.peer, self.handle = peer, handle
+
+
+_SP_MODE = False
+
+
+def sp_mode_active() -> bool:
+    return _SP_MODE
+
+
+def set_sp_mode(on: bool) -> None:
+    """Enabled by the runner for eager steps (never while capturing a CUDA graph)."""
+    global _SP_MODE
+    _SP_MODE = on
+
+
+def sp_sync():
+    """Wait for gathered activations before a consumer that is not the fused GEMM."""
+    st = get_state()
+    peer = getattr(st.tp_comm, "peer", None) if st.tp_comm is not None else None
+    if peer is not None and getattr(peer, "sp_pending", None) is not None:
+        peer.sp_sync()
+
+
 def reduce_add_rmsnorm(x, residual, norm: "RMSNorm", partial: bool):
     """``residual += all_reduce(x); out = norm(residual)`` for a row-parallel partial ``x``.
 
@@ -238,6 +272,9 @@ def reduce_add_rmsnorm(x, residual, norm: "RMSNorm", partial: bool):
     replacing all-reduce call sites C1 / C2 of the reference plus the ``add_rmsnorm`` that follows
     them); otherwise a collective followed by the fused add+norm kernel."""
     st = get_state()
+    if isinstance(x, SPPartial):
+        out = x.peer.rs_norm_ag(x.handle, residual, norm.weight, norm.eps, norm.gemma)
+        return out, residual
     if partial and st.tp_size > 1:
         comm = st.tp_comm
         if (residual is not None and comm.peer is not None and not comm.disabled

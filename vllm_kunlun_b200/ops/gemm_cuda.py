@@ -10,6 +10,7 @@ import torch
 from . import _ext
 
 LAUNCHES = 0
+PEER = None  # PeerBuffers of the tensor-parallel group once its sequence-parallel buffers exist
 
 
 def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits: int = 0, bn: int = 0,
@@ -23,6 +24,10 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits
     if out is None:
         out = torch.empty(x2.shape[0], N, dtype=x.dtype, device=x.device)
     out2 = out.reshape(-1, N)
+    if PEER is not None and PEER.sp_pending is not None:
+        ag_bn = PEER.sp_consume(x2)
+        if ag_bn:  # gathered activations: the producer waits per token tile, tiles must match the counters
+            bn, splits = ag_bn, 1
     _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm)
     LAUNCHES += 1
     return out.reshape(*lead, N)

@@ -83,10 +83,119 @@ class PeerBuffers:
         self.launches += 1
         return x, residual
 
+    # ------------------------------------------------------------------ fused GEMM + collectives
+    # Sequence-parallel chain for large token counts (prefill), all over peer memory:
+    #   row-parallel GEMM  --(epilogue stores tiles into the owner rank's staging area)-->  reduce-scatter
+    #   rs_norm_ag kernel  --(sum + residual + RMSNorm, rows pushed to every rank)-------->  all-gather
+    #   column-parallel GEMM (TMA producer waits per token tile for the pushed rows)
+    # Two call parities alternate.  Counters of parity p are zeroed by the rs_norm_ag kernel of the next
+    # call (parity 1-p): by then this rank's consumers of parity p have finished (stream order), and no
+    # peer can produce for parity p again before it has consumed this rank's pushes of that next call.
+    SP_MAX_TT = 512
+
+    def sp_init(self, max_tokens: int, hidden: int, dtype=torch.bfloat16) -> None:
+        if getattr(self, "sp_ready", False):
+            return
+        C = self.C
+        es = torch.empty((), dtype=dtype).element_size()
+        self.sp_H, self.sp_T, self.sp_dtype = hidden, max_tokens, dtype
+        self.sp_stage_off = 0
+        self.sp_xfull_off = max_tokens * hidden * es
+        self.sp_rsflag_off = 2 * max_tokens * hidden * es
+        self.sp_agflag_off = self.sp_rsflag_off + 2 * self.world * self.SP_MAX_TT * 4
+        total = self.sp_agflag_off + 2 * self.SP_MAX_TT * 4
+        self.sp_local = C.peer_alloc(total)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, C.peer_export(self.sp_local),
+                               group=self.comm.cpu_group if self._use_cpu_group() else self.comm.group)
+        self.sp_ptrs = [self.sp_local if r == self.rank else C.peer_open(h) for r, h in enumerate(handles)]
+        self.sp_calls = 0
+        self.sp_pending = None
+        self.sp_ready = True
+        torch.cuda.synchronize()
+        dist.barrier(group=self.comm.group, device_ids=[self.device.index or 0])
+
+    def sp_ok(self, T: int, hidden: int, dtype) -> bool:
+        if not getattr(self, "sp_ready", False):
+            return False
+        R = self.world
+        return (dtype == self.sp_dtype and hidden == self.sp_H and T <= self.sp_T and T % (R * 64) == 0
+                and T // 64 <= self.SP_MAX_TT and hidden % 128 == 0)
+
+    @staticmethod
+    def _pick_bn(n: int) -> int:
+        for bn in (256, 128, 64):
+            if n % bn == 0:
+                return bn
+        raise ValueError(n)
+
+    def _rs_flags(self, r: int, parity: int) -> int:
+        return self.sp_ptrs[r] + self.sp_rsflag_off + parity * self.world * self.SP_MAX_TT * 4
+
+    def _ag_flags(self, r: int, parity: int) -> int:
+        return self.sp_ptrs[r] + self.sp_agflag_off + parity * self.SP_MAX_TT * 4
+
+    def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor):
+        """Row-parallel partial GEMM whose epilogue scatters the tiles to the token owners.
+        Returns a handle for :meth:`rs_norm_ag`."""
+        from ..ops import gemm_cuda
+        T, R = x.shape[0], self.world
+        tloc = T // R
+        bn = self._pick_bn(tloc)
+        parity = self.sp_calls & 1
+        self.sp_calls += 1
+        stage = [p + self.sp_stage_off for p in self.sp_ptrs]
+        flags = [self._rs_flags(r, parity) + self.rank * self.SP_MAX_TT * 4 for r in range(R)]
+        self.C.set_gemm_comm(stage, flags, 0, tloc, self.rank, 0)
+        gemm_cuda.gemm_bf16(x, weight, None, out=self._fake_out(T, weight.shape[0], x), splits=1, bn=bn)
+        self.launches += 1
+        return {"T": T, "tloc": tloc, "bn": bn, "parity": parity, "N": weight.shape[0]}
+
+    def _fake_out(self, T, N, x):
+        # the GEMM API wants an output tensor of the right shape; in reduce-scatter mode nothing is
+        # written to it, so a view of the (large enough) local staging area serves
+        return self.C.tensor_from_ptr(self.sp_local + self.sp_stage_off, [T, N], x.dtype, self.device.index or 0)
+
+    def rs_norm_ag(self, handle, residual, weight, eps: float, gemma: bool = False):
+        """Reduce the scattered partials, add the residual (own rows), RMSNorm, gather to all ranks.
+        Returns the gathered activations ``[T, H]`` (a view of this rank's symmetric buffer); the next
+        GEMM on that tensor waits per token tile for the rows to arrive."""
+        T, tloc, bn, parity = handle["T"], handle["tloc"], handle["bn"], handle["parity"]
+        R, H = self.world, self.sp_H
+        ag_bn = self._pick_bn(T) if T % 64 == 0 else 64
+        prev = 1 - parity
+        self.C.rs_norm_ag(self.sp_local + self.sp_stage_off, self._rs_flags(self.rank, parity),
+                          [p + self.sp_xfull_off for p in self.sp_ptrs], [self._ag_flags(r, parity) for r in range(R)],
+                          self._rs_flags(self.rank, prev), R * self.SP_MAX_TT, self._ag_flags(self.rank, prev),
+                          self.SP_MAX_TT, residual, weight, self.status, self.rank, tloc, H, bn, H // 128, ag_bn, 4,
+                          self.SP_MAX_TT, eps, gemma, self.spin_limit)
+        self.launches += 1
+        x = self.C.tensor_from_ptr(self.sp_local + self.sp_xfull_off, [T, H], self.sp_dtype, self.device.index or 0)
+        self.sp_pending = {"ptr": x.data_ptr(), "flags": self._ag_flags(self.rank, parity), "expect": ag_bn,
+                           "bn": ag_bn, "n_tt": T // ag_bn}
+        return x
+
+    def sp_consume(self, x: torch.Tensor):
+        """Called by the GEMM entry: if ``x`` is the pending gathered buffer, arm the all-gather wait
+        for the next GEMM launch and return its token tile size."""
+        pd = getattr(self, "sp_pending", None)
+        if pd is None or x.data_ptr() != pd["ptr"]:
+            return 0
+        self.C.set_gemm_comm([], [], pd["flags"], 0, self.rank, pd["expect"])
+        self.sp_pending = None
+        return pd["bn"]
+
+    def sp_sync(self) -> None:
+        """Make the stream wait for all gathered rows (for consumers other than the fused GEMM)."""
+        pd = getattr(self, "sp_pending", None)
+        if pd is not None:
+            self.C.sp_wait(pd["flags"], pd["n_tt"], pd["expect"], self.spin_limit, self.status)
+            self.sp_pending = None
+
     def check_status(self) -> None:
         code = int(self.status.item())
         if code:
-            raise RuntimeError(f"peer all-reduce: bounded wait on rank {code - 200} timed out")
+            raise RuntimeError(f"peer-memory collective: a bounded wait timed out (code {code})")
 
     def close(self) -> None:
         if self.local_ptr is None:
@@ -101,3 +210,9 @@ class PeerBuffers:
             pass
         self.C.peer_free(self.local_ptr)
         self.local_ptr = None
+        if getattr(self, "sp_ready", False):
+            for r, p in enumerate(self.sp_ptrs):
+                if r != self.rank:
+                    self.C.peer_close(p)
+            self.C.peer_free(self.sp_local)
+            self.sp_ready = False
