@@ -104,6 +104,14 @@ int b200_paged_attention(void* out, const void* q, const void* kv_cache, const i
                          int Hkv, int D, int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
                          int num_splits, int window, float scale, int decode_layout, int dtype, cudaStream_t st);
 
+int b200_merge_splits(void* out, const float* ws_o, const float* ws_lse, int64_t rows, int Hq, int D, int splits,
+                      int64_t T, int dtype, cudaStream_t st);
+// Absorbed MLA attention over the latent cache: dense paged (indices == null) or sparse by index list.
+int b200_mla_attention(void* out, const void* q, const void* kv, const int* block_tables, const int* seq_lens,
+                       const int* qsl, const int* req_of_token, const int* indices, float* ws_o, float* ws_lse,
+                       int64_t T, int B, int N, int block_size, int max_blocks, int64_t total_slots, int topk,
+                       int num_splits, float scale, int dtype, cudaStream_t st);
+
 // ---- MoE / fp8 activation quantisation --------------------------------------------------------
 int b200_moe_route(float* out_w, int* out_ids, const void* logits, const float* bias, int64_t T, int E, int k, int mode,
                    int renorm, int n_group, int topk_group, float scale, int64_t stride, int dtype, cudaStream_t st);

@@ -420,3 +420,18 @@ extern "C" int b200_paged_attention(void* out, const void* q, const void* kv_cac
   }
   return 0;
 }
+
+// Split-KV merge as a stand-alone entry (also used by the MLA kernels): rows = T * heads.
+extern "C" int b200_merge_splits(void* out, const float* ws_o, const float* ws_lse, int64_t rows, int Hq, int D,
+                                 int splits, int64_t T_, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (dtype == kBF16)
+    return (int)launch_pdl(merge_splits_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, st,
+                           (__nv_bfloat16*)out, (float*)nullptr, ws_o, ws_lse, (const float*)nullptr, rows, Hq, D,
+                           splits, T_, (const int*)nullptr, 0);
+  if (dtype == kF16)
+    return (int)launch_pdl(merge_splits_kernel<__half>, dim3((rows + 7) / 8), dim3(256), 0, st, (__half*)out,
+                           (float*)nullptr, ws_o, ws_lse, (const float*)nullptr, rows, Hq, D, splits, T_,
+                           (const int*)nullptr, 0);
+  return 1;
+}

@@ -443,6 +443,34 @@ void paged_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_c
         "paged_attention", num_splits > 1 ? 2 : 1);
 }
 
+// q [T, N, 576], kv [blocks, bs, 576] -> out [T, N, 512]; dense (block tables) or sparse (indices [T, topk])
+void mla_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, const c10::optional<at::Tensor>& block_tables,
+                   const c10::optional<at::Tensor>& seq_lens, const c10::optional<at::Tensor>& qsl,
+                   const c10::optional<at::Tensor>& req_of_token, const c10::optional<at::Tensor>& indices,
+                   const c10::optional<at::Tensor>& ws_o, const c10::optional<at::Tensor>& ws_lse, int64_t num_splits,
+                   double scale) {
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && kv.is_contiguous() && q.dim() == 3 && q.size(2) == 576);
+  TORCH_CHECK(kv.size(-1) == 576 && out.size(2) == 512);
+  const bool sparse = indices.has_value();
+  if (sparse) {
+    TORCH_CHECK(indices->is_contiguous() && indices->scalar_type() == at::kInt);
+  } else {
+    TORCH_CHECK(block_tables.has_value() && seq_lens.has_value() && qsl.has_value() && req_of_token.has_value());
+  }
+  if (num_splits > 1) TORCH_CHECK(ws_o.has_value() && ws_lse.has_value());
+  int64_t total_slots = kv.numel() / 576;
+  check(b200_mla_attention(out.data_ptr(), q.data_ptr(), kv.data_ptr(),
+                           sparse ? nullptr : block_tables->data_ptr<int>(), sparse ? nullptr : seq_lens->data_ptr<int>(),
+                           sparse ? nullptr : qsl->data_ptr<int>(), sparse ? nullptr : req_of_token->data_ptr<int>(),
+                           sparse ? indices->data_ptr<int>() : nullptr,
+                           ws_o.has_value() ? ws_o->data_ptr<float>() : nullptr,
+                           ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, q.size(0),
+                           sparse ? 0 : seq_lens->size(0), q.size(1), kv.dim() == 3 ? kv.size(1) : 64,
+                           sparse ? 0 : block_tables->stride(0), total_slots, sparse ? indices->size(1) : 0, num_splits,
+                           (float)scale, dtype_code(q), stream()),
+        "mla_attention", num_splits > 1 ? 2 : 1);
+}
+
 // ---------------------------------------------------------------------------------------- peer memory
 // Symmetric buffers are plain cudaMalloc allocations shared between the ranks of one node with CUDA
 // IPC handles (exchanged by the Python side over the process group).
@@ -553,6 +581,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("copy_blocks", &copy_blocks);
   m.def("merge_attn_states", &merge_attn_states);
   m.def("paged_attention", &paged_attention);
+  m.def("mla_attention", &mla_attention);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);
   m.def("peer_export", &peer_export);

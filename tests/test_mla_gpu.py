@@ -1,0 +1,107 @@
+"""MLA CUDA kernels (absorbed attention, dense and sparse; per-head products) vs the fp32 oracles."""
+import pytest
+import torch
+
+from vllm_kunlun_b200 import LLM, SamplingParams, ops
+from vllm_kunlun_b200.config import RopeScaling, deepseek_v3, tiny
+from vllm_kunlun_b200.ops.reference import attention as ra
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol, name=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    bad = (err > atol + rtol * b.abs()).float().mean().item()
+    assert bad < 2e-3, f"{name}: {bad:.4%} elements off, max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("N", [16, 128, 5])
+@pytest.mark.parametrize("q_len", [1, 2])
+def test_mla_dense(N, q_len):
+    bs = 64
+    seq_lens = [q_len + 1, 33, 64, 65, 700, 2100]
+    B = len(seq_lens)
+    g = torch.Generator().manual_seed(N + q_len)
+    nblk = sum(-(-s // bs) for s in seq_lens) + 2
+    perm = torch.randperm(nblk, generator=g)
+    bt = torch.zeros(B, max(-(-s // bs) for s in seq_lens) + 1, dtype=torch.int32)
+    k = 0
+    for b, s in enumerate(seq_lens):
+        n = -(-s // bs)
+        bt[b, :n] = perm[k:k + n]
+        k += n
+    cache = (torch.randn(nblk, bs, 576, generator=g) * 0.3).bfloat16()
+    q = (torch.randn(B * q_len, N, 576, generator=g) * 0.3).bfloat16()
+    qsl = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32)
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    scale = 0.1
+    ref = ra.mla_decode(q, cache, bt, sl, qsl, scale)
+    out = ops.mla_attention(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), scale, 512, q_len,
+                            max(seq_lens))
+    _close(out, ref, 2e-2, 3e-2, f"mla dense N={N} q_len={q_len}")
+
+
+def test_mla_prefill_rows():
+    bs, N = 64, 16
+    spec = [(40, 40), (100, 300), (1, 77)]
+    g = torch.Generator().manual_seed(9)
+    seq_lens = [s for _, s in spec]
+    nblk = sum(-(-s // bs) for s in seq_lens) + 1
+    bt = torch.zeros(len(spec), 6, dtype=torch.int32)
+    k = 0
+    for b, s in enumerate(seq_lens):
+        n = -(-s // bs)
+        bt[b, :n] = torch.arange(k, k + n)
+        k += n
+    cache = (torch.randn(nblk, bs, 576, generator=g) * 0.3).bfloat16()
+    qsl = torch.tensor([0, 40, 140, 141], dtype=torch.int32)
+    q = (torch.randn(141, N, 576, generator=g) * 0.3).bfloat16()
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    ref = ra.mla_decode(q, cache, bt, sl, qsl, 0.1)
+    out = ops.mla_attention(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), 0.1, 512, 100, 300)
+    _close(out, ref, 2e-2, 3e-2, "mla prefill rows")
+
+
+@pytest.mark.parametrize("topk", [64, 2048])
+def test_sparse_mla(topk):
+    g = torch.Generator().manual_seed(topk)
+    T, N, slots = 9, 16, 5000
+    cache = (torch.randn(slots // 64 + 1, 64, 576, generator=g) * 0.3).bfloat16()
+    q = (torch.randn(T, N, 576, generator=g) * 0.3).bfloat16()
+    idx = torch.full((T, topk), -1, dtype=torch.int32)
+    for t in range(T):
+        n = int(torch.randint(1, min(topk, slots) + 1, (1,), generator=g))
+        idx[t, :n] = torch.randperm(slots, generator=g)[:n].to(torch.int32)
+    idx[3, 5] = -1  # a hole in the middle of the list
+    ref, _, _ = ra.sparse_mla(q, cache.reshape(-1, 576), idx, 0.1)
+    out = ops.sparse_mla_attention(q.to(DEV), cache.to(DEV), idx.to(DEV), 0.1)
+    _close(out, ref, 2e-2, 3e-2, f"sparse mla topk={topk}")
+
+
+def test_bmm_heads():
+    g = torch.Generator().manual_seed(1)
+    for T, N, K, D in [(16, 16, 128, 512), (7, 128, 512, 128), (300, 4, 128, 512)]:
+        x = (torch.randn(T, N, K, generator=g) * 0.5).bfloat16()
+        w = (torch.randn(N, K, D, generator=g) * 0.05).bfloat16()
+        ref = torch.einsum("tnk,nkd->tnd", x.float(), w.float())
+        out = ops.bmm_heads(x.to(DEV), w.to(DEV))
+        _close(out, ref, 0.03, 0.03, f"bmm_heads {T},{N},{K},{D}")
+
+
+def test_deepseek_engine_gpu():
+    cfg = tiny(deepseek_v3(fp8=False), num_layers=3, first_dense_layers=1, vocab_size=1024, hidden_size=512,
+               num_heads=16, num_kv_heads=16, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+               qk_rope_head_dim=64, v_head_dim=128, head_dim=192, rotary_dim=64, intermediate_size=1024,
+               num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, n_group=4, topk_group=2,
+               max_position=2048, rope_scaling=RopeScaling(type="yarn", factor=4.0, original_max_position=512,
+                                                           mscale=1.0, mscale_all_dim=1.0), num_mtp_layers=0)
+    outs = []
+    for eager in (True, False):
+        llm = LLM(cfg, device="cuda", block_size=64, max_model_len=512, max_num_seqs=4, num_gpu_blocks=32,
+                  enforce_eager=eager, seed=2)
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (90, 11)]
+        outs.append([o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))])
+    assert outs[0] == outs[1]

@@ -1,0 +1,76 @@
+"""CUDA entries of the MLA family: absorbed attention over the latent cache (dense paged and sparse),
+the per-head absorption products and the lightning-indexer scoring.
+
+Kernels: ``csrc/attention/mla_attention.cu`` (one kernel for dense and sparse key sources, split-KV)
+and the grouped tcgen05 GEMM (``csrc/gemm/gemm_grouped.cu``) with heads as groups for
+``q_nope . W_UK`` / ``o . W_UV``."""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+from .attention_cuda import sm_count
+
+_LOD: dict = {}
+_WT: dict = {}
+
+
+def _splits(ctas: int, tiles: int, device, cap: int = 16) -> int:
+    want = -(-2 * sm_count(device) // max(1, ctas))
+    return int(max(1, min(want, cap, max(1, tiles // 2))))
+
+
+def _ws(T, N, splits, device):
+    return (torch.empty(splits * T * N * 512, dtype=torch.float32, device=device),
+            torch.empty(splits * T * N, dtype=torch.float32, device=device))
+
+
+def mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank, max_query_len,
+                       max_seq_len, workspace=None, req_of_token=None):
+    assert kv_lora_rank == 512 and q.shape[-1] == 576 and kv_cache.dtype == q.dtype
+    T, N, _ = q.shape
+    if req_of_token is None:
+        lens = (query_start_loc[1:] - query_start_loc[:-1]).long()
+        req_of_token = torch.repeat_interleave(torch.arange(lens.shape[0], device=q.device, dtype=torch.int32), lens,
+                                               output_size=T)
+    out = torch.empty(T, N, 512, dtype=q.dtype, device=q.device)
+    splits = _splits(-(-N // 16) * T, -(-max_seq_len // 32), q.device)
+    ws_o, ws_lse = _ws(T, N, splits, q.device) if splits > 1 else (None, None)
+    _ext.C().mla_attention(out, q, kv_cache, block_tables, seq_lens, query_start_loc, req_of_token, None, ws_o, ws_lse,
+                           splits, scale)
+    return out
+
+
+def sparse_mla_cuda(q, kv_flat, indices, scale, d_v=512):
+    assert d_v == 512 and kv_flat.dtype == q.dtype, "sparse MLA kernel reads the 16-bit latent cache"
+    T, N, _ = q.shape
+    out = torch.empty(T, N, 512, dtype=q.dtype, device=q.device)
+    topk = indices.shape[1]
+    splits = _splits(-(-N // 16) * T, -(-topk // 32), q.device)
+    ws_o, ws_lse = _ws(T, N, splits, q.device) if splits > 1 else (None, None)
+    _ext.C().mla_attention(out, q, kv_flat, None, None, None, None, indices.contiguous(), ws_o, ws_lse, splits, scale)
+    return out
+
+
+def bmm_heads_cuda(x, w):
+    """``out[t, n, :] = x[t, n, :] @ w[n]`` with ``w [N, K, D]``: heads are the groups of a grouped GEMM."""
+    T, N, K = x.shape
+    D = w.shape[2]
+    key = (w.data_ptr(), tuple(w.shape))
+    wt = _WT.get(key)
+    if wt is None:  # K-major copy [N, D, K], made once per weight
+        wt = w.transpose(1, 2).contiguous()
+        _WT[key] = wt
+    lk = (N, T, str(x.device))
+    lod = _LOD.get(lk)
+    if lod is None:
+        lod = (torch.arange(N + 1, dtype=torch.int32, device=x.device) * T).contiguous()
+        _LOD[lk] = lod
+    xs = x.transpose(0, 1).contiguous().view(N * T, K)
+    out = torch.empty(N * T, D, dtype=x.dtype, device=x.device)
+    _ext.C().grouped_gemm(out, xs, wt, lod, None, None, None, 0)
+    return out.view(N, T, D).transpose(0, 1)
+
+
+def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk):
+    raise NotImplementedError("lightning-indexer scoring kernel: see DESIGN.md (oracle path on CPU only)")
