@@ -112,6 +112,13 @@ int b200_mla_attention(void* out, const void* q, const void* kv, const int* bloc
                        int64_t T, int B, int N, int block_size, int max_blocks, int64_t total_slots, int topk,
                        int num_splits, float scale, int dtype, cudaStream_t st);
 
+// Lightning indexer: fp8 scores over the paged 132-byte key cache, then per-row top-k (unordered, -1 padded)
+int b200_indexer_logits(float* logits, const void* q_fp8, const float* w, const void* k_cache, const int* block_tables,
+                        const int* seq_lens, const int* qsl, const int* req_of_token, int64_t T, int B, int block_size,
+                        int max_blocks, int64_t total_slots, int64_t ld_logits, cudaStream_t st);
+int b200_topk_rows(int* out, const float* logits, const int* row_len, int64_t rows, int64_t ld, int k, int64_t max_len,
+                   cudaStream_t st);
+
 // ---- MoE / fp8 activation quantisation --------------------------------------------------------
 int b200_moe_route(float* out_w, int* out_ids, const void* logits, const float* bias, int64_t T, int E, int k, int mode,
                    int renorm, int n_group, int topk_group, float scale, int64_t stride, int dtype, cudaStream_t st);

@@ -471,6 +471,27 @@ void mla_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, co
         "mla_attention", num_splits > 1 ? 2 : 1);
 }
 
+// logits [T, max_len] fp32 of the lightning indexer; w already carries the per-(token, head) query scale
+void indexer_logits(at::Tensor logits, const at::Tensor& q_fp8, const at::Tensor& w, const at::Tensor& k_cache,
+                    const at::Tensor& block_tables, const at::Tensor& seq_lens, const at::Tensor& qsl,
+                    const at::Tensor& req_of_token) {
+  TORCH_CHECK(q_fp8.is_contiguous() && q_fp8.element_size() == 1 && q_fp8.size(1) == 64 && q_fp8.size(2) == 128);
+  TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kFloat && k_cache.is_contiguous() && k_cache.size(-1) == 132);
+  TORCH_CHECK(logits.is_contiguous() && logits.scalar_type() == at::kFloat && block_tables.stride(1) == 1);
+  check(b200_indexer_logits(logits.data_ptr<float>(), q_fp8.data_ptr(), w.data_ptr<float>(), k_cache.data_ptr(),
+                            block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), qsl.data_ptr<int>(),
+                            req_of_token.data_ptr<int>(), q_fp8.size(0), seq_lens.size(0), k_cache.size(1),
+                            block_tables.stride(0), k_cache.size(0) * k_cache.size(1), logits.size(1), stream()),
+        "indexer_logits");
+}
+void topk_rows(at::Tensor out, const at::Tensor& logits, const c10::optional<at::Tensor>& row_len) {
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kInt && logits.scalar_type() == at::kFloat && logits.stride(1) == 1);
+  check(b200_topk_rows(out.data_ptr<int>(), logits.data_ptr<float>(),
+                       row_len.has_value() ? row_len->data_ptr<int>() : nullptr, logits.size(0), logits.stride(0),
+                       out.size(1), logits.size(1), stream()),
+        "topk_rows");
+}
+
 // ---------------------------------------------------------------------------------------- peer memory
 // Symmetric buffers are plain cudaMalloc allocations shared between the ranks of one node with CUDA
 // IPC handles (exchanged by the Python side over the process group).
@@ -582,6 +603,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("merge_attn_states", &merge_attn_states);
   m.def("paged_attention", &paged_attention);
   m.def("mla_attention", &mla_attention);
+  m.def("indexer_logits", &indexer_logits);
+  m.def("topk_rows", &topk_rows);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);
   m.def("peer_export", &peer_export);

@@ -105,3 +105,56 @@ def test_deepseek_engine_gpu():
         prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (90, 11)]
         outs.append([o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))])
     assert outs[0] == outs[1]
+
+
+def test_indexer_logits_and_topk():
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.reference import basic as rb
+    g = torch.Generator().manual_seed(4)
+    bs, H = 64, 64
+    spec = [(1, 700), (2, 131), (1, 3000), (40, 40)]  # (q_len, seq_len): decode rows, spec rows, a prefill
+    B = len(spec)
+    seq_lens = [s for _, s in spec]
+    nblk = sum(-(-s // bs) for s in seq_lens) + 2
+    bt = torch.zeros(B, max(-(-s // bs) for s in seq_lens) + 1, dtype=torch.int32)
+    k = 1
+    for b, s in enumerate(seq_lens):
+        n = -(-s // bs)
+        bt[b, :n] = torch.arange(k, k + n)
+        k += n
+    cache = torch.zeros(nblk + 1, bs, 132, dtype=torch.uint8)
+    keys = torch.randn(sum(seq_lens), 128, generator=g)
+    slots, off = [], 0
+    for b, s in enumerate(seq_lens):
+        pos = torch.arange(s)
+        slots.append(bt[b, pos // bs].long() * bs + pos % bs)
+    ra.indexer_k_quant_and_cache(keys, cache, torch.cat(slots))
+    qsl = torch.tensor([0] + list(torch.tensor([q for q, _ in spec]).cumsum(0)), dtype=torch.int32)
+    T = int(qsl[-1])
+    q = torch.randn(T, H, 128, generator=g)
+    qq, qs_ = rb.quant_fp8_per_group(q.reshape(T * H, 128), 128, True)
+    qq, qs_ = qq.view(T, H, 128), qs_.view(T, H)
+    w = torch.randn(T, H, generator=g) * 0.1
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    topk = 256
+    want = ops.indexer_topk(qq, qs_, w, cache, bt, sl, qsl, topk)
+    got = ops.indexer_topk(qq.to(DEV), qs_.to(DEV), w.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), topk)
+    got = got.cpu()
+    # same number of selected keys per row, and (up to ties / rounding at the cut) the same sets
+    for t in range(T):
+        a, b = set(want[t][want[t] >= 0].tolist()), set(got[t][got[t] >= 0].tolist())
+        assert len(a) == len(b), (t, len(a), len(b))
+        assert len(a & b) >= 0.97 * len(a), (t, len(a & b), len(a))
+    # top-k kernel alone against torch.topk
+    x = torch.randn(5, 5000, device=DEV)
+    x[2, 100:200] = 1.5  # ties at the cut
+    out = torch.empty(5, 512, dtype=torch.int32, device=DEV)
+    lens = torch.tensor([5000, 300, 5000, 4097, 512], dtype=torch.int32, device=DEV)
+    _ext.C().topk_rows(out, x, lens)
+    for r in range(5):
+        n = int(lens[r])
+        sel = out[r][out[r] >= 0].long()
+        kk = min(512, n)
+        assert sel.numel() == kk and len(set(sel.tolist())) == kk and int(sel.max()) < n
+        ref_vals = x[r, :n].topk(kk).values.sort().values
+        assert torch.equal(x[r, sel].sort().values, ref_vals)

@@ -72,5 +72,27 @@ def bmm_heads_cuda(x, w):
     return out.view(N, T, D).transpose(0, 1)
 
 
-def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk):
-    raise NotImplementedError("lightning-indexer scoring kernel: see DESIGN.md (oracle path on CPU only)")
+def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk,
+                      req_of_token=None, max_len=None):
+    """fp8 scoring (``csrc/attention/indexer.cu``) + radix-select top-k; request-local indices ``[T, topk]``."""
+    T, H, D = q_fp8.shape
+    assert H == 64 and D == 128, "indexer kernel is specialised for 64 heads x 128 dims"
+    if req_of_token is None:
+        lens = (query_start_loc[1:] - query_start_loc[:-1]).long()
+        req_of_token = torch.repeat_interleave(torch.arange(lens.shape[0], device=q_fp8.device, dtype=torch.int32),
+                                               lens, output_size=T)
+    if max_len is None:
+        max_len = block_tables.shape[1] * k_cache.shape[1]
+    ld = -(-max_len // 512) * 512
+    logits = torch.empty(T, ld, dtype=torch.float32, device=q_fp8.device)
+    w = (weights.float() * q_scale.float()).contiguous()
+    C = _ext.C()
+    C.indexer_logits(logits, q_fp8.view(torch.uint8).contiguous(), w, k_cache, block_tables, seq_lens,
+                     query_start_loc, req_of_token)
+    # keys visible to row t: pos(t) + 1
+    qs = query_start_loc.long()[req_of_token.long()]
+    q_len = (query_start_loc[1:] - query_start_loc[:-1]).long()[req_of_token.long()]
+    row_len = (seq_lens.long()[req_of_token.long()] - q_len + (torch.arange(T, device=q_fp8.device) - qs) + 1)
+    out = torch.empty(T, topk, dtype=torch.int32, device=q_fp8.device)
+    C.topk_rows(out, logits, row_len.to(torch.int32).contiguous())
+    return out
