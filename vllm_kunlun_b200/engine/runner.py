@@ -34,8 +34,11 @@ class StepHandle:
     tokens: torch.Tensor
     tokens_cpu: torch.Tensor
     event: Optional[object]
-    hidden: Optional[torch.Tensor] = None  # last hidden states of sampled rows (MTP input)
+    hidden: Optional[torch.Tensor] = None  # last hidden states of sampled rows
     launch_time: float = 0.0
+    md: Optional[object] = None            # kept for the draft model (speculative decoding)
+    input_ids: Optional[torch.Tensor] = None
+    full_hidden: Optional[torch.Tensor] = None
 
     def wait(self) -> torch.Tensor:
         if self.event is not None:
@@ -72,6 +75,8 @@ class ModelRunner:
         self.last_tokens: Optional[torch.Tensor] = None  # previous step's sampled tokens (device)
         self.last_rows: dict = {}  # request_id -> row in last_tokens of its newest token
         self.kernel_launches = 0
+        self.keep_full_hidden = False  # set by a proposer that needs every row's hidden state
+        self._full_hidden = None
         if self.is_cuda and cfg.compilation.mode != "none":
             from ..compilation.cuda_graph import DecodeGraphs
             self.graphs = DecodeGraphs(self)
@@ -322,7 +327,10 @@ class ModelRunner:
             ev.record()
         else:
             tokens_cpu = tokens
-        return StepHandle(sched, sample_reqs, rows_per_req, tokens, tokens_cpu, ev, hidden, t0)
+        full = None
+        if self.keep_full_hidden:
+            full = hidden if use_graph else self._full_hidden
+        return StepHandle(sched, sample_reqs, rows_per_req, tokens, tokens_cpu, ev, hidden, t0, md, input_ids, full)
 
     def forward_and_sample(self, md: AttentionMetadata, input_ids, sp, capturing: bool = False):
         ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing)
@@ -333,6 +341,7 @@ class ModelRunner:
                 tokens = torch.zeros(md.logits_indices.shape[0], dtype=torch.int64, device=self.device)
                 sel = None
             else:
+                self._full_hidden = hidden if self.keep_full_hidden else None
                 sel = hidden.index_select(0, md.logits_indices.long()) if md.logits_indices is not None else hidden
                 logits = self.model.compute_logits(sel)
                 tokens = self.sampler(logits, sp)
