@@ -1,0 +1,177 @@
+"""Reasoning parser, tool parser, plugin entry points, platform, env registry, loader, utils."""
+import json
+import os
+
+import torch
+
+import vllm_kunlun_b200 as pkg
+from vllm_kunlun_b200.entrypoints.tool_parsers import Glm47ToolParser
+from vllm_kunlun_b200.reasoning import Qwen3ReasoningParser
+
+
+def test_qwen3_reasoning_whole_and_streaming():
+    p = Qwen3ReasoningParser()
+    assert p.extract_reasoning("<think>abc</think>xyz") == ("abc", "xyz")
+    assert p.extract_reasoning("abc</think>xyz") == ("abc", "xyz")
+    assert p.extract_reasoning("still thinking") == ("still thinking", None)
+    assert Qwen3ReasoningParser(chat_template_kwargs={"enable_thinking": False}).extract_reasoning("hi") == (None, "hi")
+    s = Qwen3ReasoningParser()
+    r, c = "", ""
+    for piece in ["<thi", "nk>rea", "son</th", "ink>ans", "wer"]:
+        d = s.extract_reasoning_streaming(piece)
+        if d:
+            r += d.reasoning or ""
+            c += d.content or ""
+    assert (r, c) == ("reason", "answer")
+
+
+def test_glm47_tool_parser():
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"},
+                                         "opts": {"type": "object"}}}}}]
+    out = ("I will call.<tool_call>get_weather\n<arg_key>city</arg_key><arg_value>Paris</arg_value>"
+           "<arg_key>days</arg_key><arg_value>3</arg_value><arg_key>opts</arg_key>"
+           "<arg_value>{\"units\": \"C\"}</arg_value></tool_call>")
+    p = Glm47ToolParser()
+    ex = p.extract_tool_calls(out, tools)
+    assert ex.tools_called and ex.content == "I will call."
+    assert ex.tool_calls[0].name == "get_weather"
+    assert json.loads(ex.tool_calls[0].arguments) == {"city": "Paris", "days": 3, "opts": {"units": "C"}}
+    assert not p.extract_tool_calls("no tools here").tools_called
+    # streaming: name first, then argument text that concatenates to the final JSON
+    sp = Glm47ToolParser()
+    name, args = None, ""
+    for i in range(1, len(out) + 1, 7):
+        for d in sp.extract_tool_calls_streaming(out[:i], tools):
+            name = d.get("name", name)
+            args += d.get("arguments", "")
+    for d in sp.extract_tool_calls_streaming(out, tools):
+        args += d.get("arguments", "")
+    assert name == "get_weather" and json.loads(args) == {"city": "Paris", "days": 3, "opts": {"units": "C"}}
+
+
+def test_plugin_entry_points_and_platform():
+    assert pkg.register() == "vllm_kunlun_b200.platforms.b200.B200Platform"
+    pkg.register_reasoning_parser()
+    pkg.register_quant_method()
+    from vllm_kunlun_b200.platforms.b200 import B200Platform
+    assert B200Platform.dist_backend == "nccl" and B200Platform.device_type == "cuda"
+    assert B200Platform.get_device_communicator_cls().endswith("DeviceCommunicator")
+    assert "MLA" in B200Platform.get_attn_backend_cls(use_mla=True)
+    assert B200Platform.get_device_total_memory() > (1 << 30)
+
+    class _C:  # minimal stand-in for a vLLM config
+        class cache_config:
+            block_size = None
+        class model_config:
+            use_mla = True
+        compilation_config = None
+        parallel_config = None
+    B200Platform.check_and_update_config(_C)
+    assert _C.cache_config.block_size == 64
+    from vllm_kunlun_b200.models import supported_architectures
+    archs = supported_architectures()
+    for a in ("LlamaForCausalLM", "Qwen3MoeForCausalLM", "DeepseekV32ForCausalLM", "DeepSeekMTPModel", "GptOssForCausalLM"):
+        assert a in archs
+
+
+def test_env_registry_is_lazy(monkeypatch):
+    from vllm_kunlun_b200 import envs
+    monkeypatch.setenv("B200_PDL", "0")
+    assert envs.B200_PDL is False
+    monkeypatch.setenv("B200_PDL", "1")
+    assert envs.B200_PDL is True
+    assert "B200_SPIN_LIMIT" in envs.describe()
+
+
+def test_safetensors_roundtrip_with_fp8_scales(tmp_path):
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    from vllm_kunlun_b200.config import qwen3_30b_a3b, tiny
+    from vllm_kunlun_b200.models.loader import load_safetensors, save_safetensors
+    cfg = tiny(qwen3_30b_a3b(fp8=True), num_layers=1, vocab_size=128, hidden_size=128, num_heads=2, num_kv_heads=2,
+               head_dim=64, intermediate_size=256, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+               max_position=256, dtype="float32")
+    a = LLM(cfg, device="cpu", block_size=16, max_model_len=64, max_num_seqs=2, num_gpu_blocks=8)
+    # export in checkpoint naming: split fused tensors back into q/k/v, gate/up and per-expert tensors
+    m = a.engine.runner.model
+    sd = {}
+    L = m.layers["0"]
+    q, kv = cfg.q_size, cfg.kv_size
+    for suffix in ("weight", "weight_scale_inv"):
+        t = getattr(L.self_attn.qkv_proj, suffix).data
+        div = 128 if suffix == "weight_scale_inv" else 1
+        sd[f"model.layers.0.self_attn.q_proj.{suffix}"] = t[: q // div]
+        sd[f"model.layers.0.self_attn.k_proj.{suffix}"] = t[q // div:(q + kv) // div]
+        sd[f"model.layers.0.self_attn.v_proj.{suffix}"] = t[(q + kv) // div:]
+        sd[f"model.layers.0.self_attn.o_proj.{suffix}"] = getattr(L.self_attn.o_proj, suffix).data
+    sd["model.layers.0.self_attn.q_norm.weight"] = L.self_attn.q_norm.weight.data
+    sd["model.layers.0.self_attn.k_norm.weight"] = L.self_attn.k_norm.weight.data
+    sd["model.layers.0.input_layernorm.weight"] = L.input_layernorm.weight.data
+    sd["model.layers.0.post_attention_layernorm.weight"] = L.post_attention_layernorm.weight.data
+    sd["model.layers.0.mlp.gate.weight"] = L.mlp.gate.weight.data
+    ex = L.mlp.experts
+    I = ex.i_local
+    for e in range(4):
+        sd[f"model.layers.0.mlp.experts.{e}.gate_proj.weight"] = ex.w13.data[e, :I]
+        sd[f"model.layers.0.mlp.experts.{e}.up_proj.weight"] = ex.w13.data[e, I:]
+        sd[f"model.layers.0.mlp.experts.{e}.down_proj.weight"] = ex.w2.data[e]
+        sd[f"model.layers.0.mlp.experts.{e}.gate_proj.weight_scale_inv"] = ex.w13_scale.data[e, : I // 128]
+        sd[f"model.layers.0.mlp.experts.{e}.up_proj.weight_scale_inv"] = ex.w13_scale.data[e, I // 128:]
+        sd[f"model.layers.0.mlp.experts.{e}.down_proj.weight_scale_inv"] = ex.w2_scale.data[e]
+    sd["model.embed_tokens.weight"] = m.embed_tokens.weight.data[: cfg.vocab_size]
+    sd["model.norm.weight"] = m.norm.weight.data
+    sd["lm_head.weight"] = m.lm_head.weight.data[: cfg.vocab_size]
+    save_safetensors({k: v.clone() for k, v in sd.items()}, str(tmp_path))
+    names = {n for n, _ in load_safetensors(str(tmp_path))}
+    assert "model.layers.0.mlp.experts.3.down_proj.weight_scale_inv" in names
+    b = LLM(cfg, device="cpu", block_size=16, max_model_len=64, max_num_seqs=2, num_gpu_blocks=8, seed=99)
+    with torch.inference_mode():
+        b.engine.runner.model.load_weights(load_safetensors(str(tmp_path)))
+    prompt = [list(range(3, 20))]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    assert a.generate(prompt, sp)[0].token_ids == b.generate(prompt, sp)[0].token_ids
+
+
+def test_module_tracer_and_stage_timer():
+    from vllm_kunlun_b200.utils import ModuleTracer, StageTimer
+    lines = []
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.ReLU())
+    with ModuleTracer(net, lines.append):
+        net(torch.zeros(2, 4))
+    assert any("Linear" in l for l in lines) and any("<-" in l for l in lines)
+    st = StageTimer(sink=None)
+    with st.stage("first token"):
+        pass
+    assert st.records[0][0] == "first token"
+
+
+def test_openai_server_completions_and_chat_stream():
+    from fastapi.testclient import TestClient
+
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    cfg = tiny(qwen2_0_5b(), num_layers=1, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    app = build_app(llm, "tiny", reasoning_parser="qwen3")
+    with TestClient(app) as c:
+        assert c.get("/health").text == "ok"
+        assert c.get("/v1/models").json()["data"][0]["id"] == "tiny"
+        r = c.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 4, "temperature": 0, "ignore_eos": True})
+        body = r.json()
+        assert body["usage"]["completion_tokens"] == 4 and body["choices"][0]["finish_reason"] == "length"
+        ref = llm_tokens = body["choices"][0]["text"]
+        # same request, streamed: the concatenated chunks equal the non-streamed text
+        with c.stream("POST", "/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 4, "temperature": 0,
+                                                       "ignore_eos": True, "stream": True}) as s:
+            pieces = []
+            for line in s.iter_lines():
+                if line.startswith("data: ") and line != "data: [DONE]":
+                    pieces.append(json.loads(line[6:])["choices"][0]["text"])
+        assert " ".join(p for p in pieces if p) == ref
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "1 2 3"}], "max_tokens": 3,
+                                                 "temperature": 0, "ignore_eos": True})
+        msg = r.json()["choices"][0]["message"]
+        assert msg["role"] == "assistant" and "reasoning_content" in msg
+        assert "b200_requests_total 3" in c.get("/metrics").text

@@ -1,0 +1,42 @@
+"""Typed environment registry, read lazily (no import-time side effects).
+
+Mirrors the reference's lazy ``__getattr__`` registry (``vllm_kunlun/platforms/envs.py:34-92``) with this
+framework's names.  ``envs.NAME`` evaluates the variable at access time."""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable
+
+_ENV: dict[str, Callable[[], Any]] = {
+    # per-rank stdout/stderr redirection to $B200_MULTI_LOGPATH/pp={p}_rank={r}.log (utils.logging)
+    "B200_MULTI_LOGPATH": lambda: os.environ.get("B200_MULTI_LOGPATH", "./logs"),
+    "B200_ENABLE_MULTI_LOG": lambda: os.environ.get("B200_ENABLE_MULTI_LOG", "0") == "1",
+    # forward pre/post hook tracer on every nn.Module (utils.hooks)
+    "B200_ENABLE_MODULE_HOOK": lambda: os.environ.get("B200_ENABLE_MODULE_HOOK", "0") == "1",
+    # print every ops.* call with shapes (utils.hooks.LoggingOps)
+    "B200_ENABLE_OPS_HOOK": lambda: os.environ.get("B200_ENABLE_OPS_HOOK", "0") == "1",
+    # NVTX ranges around layers / ops
+    "B200_NVTX": lambda: os.environ.get("B200_NVTX", "0") == "1",
+    # programmatic dependent launch on decode-path kernels (read by the C++ side too)
+    "B200_PDL": lambda: os.environ.get("B200_PDL", "1") != "0",
+    # peer-memory collectives (one-shot all-reduce, fused GEMM+collectives)
+    "B200_PEER_COLLECTIVES": lambda: os.environ.get("B200_PEER_COLLECTIVES", "1") != "0",
+    # exponential-race sampling with a cached noise tensor (the reference's FAST_RANDOM_SAMPLE)
+    "B200_FAST_RANDOM_SAMPLE": lambda: os.environ.get("B200_FAST_RANDOM_SAMPLE", "0") == "1",
+    # bounded-wait budget of cross-GPU spins (iterations)
+    "B200_SPIN_LIMIT": lambda: int(os.environ.get("B200_SPIN_LIMIT", str(1 << 22))),
+}
+
+
+def __getattr__(name: str):
+    if name in _ENV:
+        return _ENV[name]()
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def __dir__():
+    return list(_ENV)
+
+
+def describe() -> dict:
+    return {k: v() for k, v in _ENV.items()}
