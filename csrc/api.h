@@ -150,6 +150,42 @@ typedef struct RsNormArgs {
 int b200_rs_norm_ag(const RsNormArgs* a, cudaStream_t st);
 int b200_sp_wait(const void* flags, int n_tt, unsigned expect, unsigned spin_limit, int* status, cudaStream_t st);
 
+// ---- sampling ---------------------------------------------------------------------------------
+int b200_topk_topp_sample(int64_t* out, const void* logits, int64_t rows, int V, int64_t stride,
+                          const float* temperature, const int* top_k, const float* top_p, const float* noise,
+                          int64_t noise_stride, uint64_t seed, uint64_t step, int dtype, cudaStream_t st);
+int b200_repetition_penalty(void* logits, int64_t rows, int V, int64_t stride, const int64_t* tokens,
+                            int64_t tok_stride, int max_tokens, const int* n_tokens, const float* penalty,
+                            uint32_t* seen, int dtype, cudaStream_t st);
+int b200_rejection_sample(int64_t* out, int64_t B, int S, const int64_t* draft_ids, const int* cu_draft,
+                          const float* target_probs, const float* draft_probs, int V, const int64_t* bonus,
+                          const uint8_t* is_greedy, const float* uniform, const float* recover_q, uint64_t seed,
+                          uint64_t step, cudaStream_t st);
+
+// ---- gated delta net / conv / MTP glue --------------------------------------------------------
+int b200_causal_conv1d_fwd(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* w,
+                           const void* bias, const int* cu, int R, void* states, const int* slots,
+                           const uint8_t* has_init, int C, int W, int act, int64_t T_, int dtype, cudaStream_t st);
+int b200_causal_conv1d_update(void* out, int64_t out_stride, const void* x, int64_t x_stride, void* states,
+                              const void* w, const void* bias, const int* slots, int64_t B, int C, int W, int act,
+                              int dtype, cudaStream_t st);
+int b200_gdn_gating(float* g, float* beta, const void* a, int64_t a_stride, const void* b, int64_t b_stride,
+                    const float* A_log, const float* dt_bias, int H, int64_t T_, int dtype, cudaStream_t st);
+int b200_gdn_recurrent(void* out, int64_t o_stride, const void* q, const void* k, int64_t qk_stride, const void* v,
+                       int64_t v_stride, const float* g, const float* beta, float* states, const int* cu,
+                       const int* slots, const uint8_t* has_init, int R, int Hk, int Hv, int Dk, int Dv, float scale,
+                       int l2norm, int dtype, cudaStream_t st);
+int b200_sigmoid_gate_mul(void* out, const void* o, const void* gate, int64_t gate_stride, int D, int64_t T_,
+                          int dtype, cudaStream_t st);
+int b200_mtp_concat_norm(void* out, const void* embed, const void* hidden, const void* we, const void* wh,
+                         const int64_t* pos, int64_t T_, int H, float eps, int dtype, cudaStream_t st);
+
+// ---- LoRA ---------------------------------------------------------------------------------------
+int b200_lora_shrink(float* out, const void* x, int64_t x_stride, const void* A, const int* ids, int64_t T_, int r,
+                     int K, float scale, int dtype, cudaStream_t st);
+int b200_lora_expand(void* out, int64_t out_stride, int offset, const float* h, const void* B, const int* ids,
+                     int64_t T_, int N, int r, int add, int dtype, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

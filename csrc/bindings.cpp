@@ -572,6 +572,114 @@ void sp_wait(int64_t flags, int64_t n_tt, int64_t expect, int64_t spin_limit, at
         "sp_wait");
 }
 
+// ------------------------------------------------------------------- sampling / GDN / LoRA
+template <typename T> const T* optp(const c10::optional<at::Tensor>& t) {
+  return t.has_value() ? t->data_ptr<T>() : nullptr;
+}
+
+void topk_topp_sample(at::Tensor out, const at::Tensor& logits, const c10::optional<at::Tensor>& temperature,
+                      const c10::optional<at::Tensor>& top_k, const c10::optional<at::Tensor>& top_p,
+                      const c10::optional<at::Tensor>& noise, int64_t seed, int64_t step) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong);
+  check(b200_topk_topp_sample(out.data_ptr<int64_t>(), logits.data_ptr(), logits.size(0), (int)logits.size(1),
+                              logits.stride(0), optp<float>(temperature), optp<int>(top_k), optp<float>(top_p),
+                              optp<float>(noise), noise.has_value() ? noise->stride(0) : 0, (uint64_t)seed, (uint64_t)step,
+                              dtype_code(logits), stream()), "topk_topp_sample");
+}
+
+void repetition_penalty(at::Tensor logits, const at::Tensor& tokens, const at::Tensor& n_tokens, const at::Tensor& penalty,
+                        at::Tensor seen) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && tokens.scalar_type() == at::kLong && tokens.stride(1) == 1);
+  int V = (int)logits.size(1);
+  TORCH_CHECK(seen.numel() * seen.element_size() >= logits.size(0) * ((V + 31) / 32) * 4, "seen bitmap too small");
+  check(b200_repetition_penalty(logits.data_ptr(), logits.size(0), V, logits.stride(0), tokens.data_ptr<int64_t>(),
+                                tokens.stride(0), (int)tokens.size(1), n_tokens.data_ptr<int>(), penalty.data_ptr<float>(),
+                                (uint32_t*)seen.data_ptr(), dtype_code(logits), stream()), "repetition_penalty");
+}
+
+void rejection_sample(at::Tensor out, const at::Tensor& draft_ids, const at::Tensor& cu_draft, const at::Tensor& target_probs,
+                      const c10::optional<at::Tensor>& draft_probs, const at::Tensor& bonus, const at::Tensor& is_greedy,
+                      const c10::optional<at::Tensor>& uniform, const c10::optional<at::Tensor>& recover_q, int64_t seed,
+                      int64_t step) {
+  TORCH_CHECK(target_probs.scalar_type() == at::kFloat && target_probs.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(!draft_probs.has_value() || (draft_probs->scalar_type() == at::kFloat && draft_probs->is_contiguous()));
+  TORCH_CHECK(!recover_q.has_value() || recover_q->is_contiguous());
+  check(b200_rejection_sample(out.data_ptr<int64_t>(), out.size(0), (int)out.size(1) - 1, draft_ids.data_ptr<int64_t>(),
+                              cu_draft.data_ptr<int>(), target_probs.data_ptr<float>(), optp<float>(draft_probs),
+                              (int)target_probs.size(1), bonus.data_ptr<int64_t>(), (const uint8_t*)is_greedy.data_ptr(),
+                              optp<float>(uniform), optp<float>(recover_q), (uint64_t)seed, (uint64_t)step, stream()),
+        "rejection_sample");
+}
+
+void causal_conv1d_fwd(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+                       const at::Tensor& cu, at::Tensor states, const at::Tensor& slots, const at::Tensor& has_init,
+                       bool act) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1 && w.is_contiguous() && states.is_contiguous());
+  check(b200_causal_conv1d_fwd(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), opt_ptr(bias),
+                               cu.data_ptr<int>(), (int)slots.size(0), states.data_ptr(), slots.data_ptr<int>(),
+                               (const uint8_t*)has_init.data_ptr(), (int)x.size(1), (int)w.size(1), act, x.size(0),
+                               dtype_code(x), stream()), "causal_conv1d_fwd", 2);
+}
+
+void causal_conv1d_update(at::Tensor out, const at::Tensor& x, at::Tensor states, const at::Tensor& w,
+                          const c10::optional<at::Tensor>& bias, const at::Tensor& slots, bool act) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.stride(1) == 1 && w.is_contiguous() && states.is_contiguous());
+  check(b200_causal_conv1d_update(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), states.data_ptr(), w.data_ptr(),
+                                  opt_ptr(bias), slots.data_ptr<int>(), x.size(0), (int)x.size(1), (int)w.size(1), act,
+                                  dtype_code(x), stream()), "causal_conv1d_update");
+}
+
+void gdn_gating(at::Tensor g, at::Tensor beta, const at::Tensor& a, const at::Tensor& b, const at::Tensor& A_log,
+                const at::Tensor& dt_bias) {
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && g.is_contiguous() && beta.is_contiguous());
+  check(b200_gdn_gating(g.data_ptr<float>(), beta.data_ptr<float>(), a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                        A_log.data_ptr<float>(), dt_bias.data_ptr<float>(), (int)a.size(1), a.size(0), dtype_code(a), stream()),
+        "gdn_gating");
+}
+
+void gdn_recurrent(at::Tensor out, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g,
+                   const at::Tensor& beta, at::Tensor states, const at::Tensor& cu, const at::Tensor& slots,
+                   const at::Tensor& has_init, double scale, bool l2norm) {
+  // q, k [T, Hk, Dk] (same row stride), v [T, Hv, Dv], out [T, Hv, Dv], states [slots, Hv, Dv, Dk] fp32
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2) && k.stride(0) == q.stride(0) &&
+              k.stride(1) == k.size(2) && v.stride(2) == 1 && v.stride(1) == v.size(2) && out.stride(1) == out.size(2));
+  TORCH_CHECK(states.scalar_type() == at::kFloat && states.is_contiguous() && g.is_contiguous() && beta.is_contiguous());
+  check(b200_gdn_recurrent(out.data_ptr(), out.stride(0), q.data_ptr(), k.data_ptr(), q.stride(0), v.data_ptr(), v.stride(0),
+                           g.data_ptr<float>(), beta.data_ptr<float>(), states.data_ptr<float>(), cu.data_ptr<int>(),
+                           slots.data_ptr<int>(), (const uint8_t*)has_init.data_ptr(), (int)slots.size(0), (int)q.size(1),
+                           (int)v.size(1), (int)q.size(2), (int)v.size(2), (float)scale, l2norm, dtype_code(q), stream()),
+        "gdn_recurrent");
+}
+
+void mtp_concat_norm(at::Tensor out, const at::Tensor& embed, const at::Tensor& hidden, const at::Tensor& we,
+                     const at::Tensor& wh, const c10::optional<at::Tensor>& pos, double eps) {
+  TORCH_CHECK(embed.is_contiguous() && hidden.is_contiguous() && out.is_contiguous());
+  check(b200_mtp_concat_norm(out.data_ptr(), embed.data_ptr(), hidden.data_ptr(), we.data_ptr(), wh.data_ptr(),
+                             optp<int64_t>(pos), embed.size(0), (int)embed.size(1), (float)eps, dtype_code(embed), stream()),
+        "mtp_concat_norm");
+}
+
+void sigmoid_gate_mul(at::Tensor out, const at::Tensor& o, const at::Tensor& gate) {
+  TORCH_CHECK(o.is_contiguous() && out.is_contiguous() && gate.stride(1) == 1 && o.dim() == 2);
+  check(b200_sigmoid_gate_mul(out.data_ptr(), o.data_ptr(), gate.data_ptr(), gate.stride(0), (int)o.size(1), o.size(0),
+                              dtype_code(o), stream()), "sigmoid_gate_mul");
+}
+
+void lora_shrink(at::Tensor out, const at::Tensor& x, const at::Tensor& A, const at::Tensor& ids, double scale) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && A.dim() == 3 && A.is_contiguous() && out.scalar_type() == at::kFloat &&
+              out.is_contiguous() && A.scalar_type() == x.scalar_type());
+  check(b200_lora_shrink(out.data_ptr<float>(), x.data_ptr(), x.stride(0), A.data_ptr(), ids.data_ptr<int>(), x.size(0),
+                         (int)A.size(1), (int)A.size(2), (float)scale, dtype_code(x), stream()), "lora_shrink");
+}
+
+void lora_expand(at::Tensor out, const at::Tensor& h, const at::Tensor& B, const at::Tensor& ids, int64_t offset, bool add) {
+  TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && B.dim() == 3 && B.is_contiguous() && h.scalar_type() == at::kFloat &&
+              h.is_contiguous() && B.scalar_type() == out.scalar_type());
+  TORCH_CHECK(offset + B.size(1) <= out.size(1));
+  check(b200_lora_expand(out.data_ptr(), out.stride(0), (int)offset, h.data_ptr<float>(), B.data_ptr(), ids.data_ptr<int>(),
+                         out.size(0), (int)B.size(1), (int)B.size(2), add, dtype_code(out), stream()), "lora_expand");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -587,6 +695,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_clear_tmap_cache", &gemm_clear_tmap_cache);
   m.def("rmsnorm", &rmsnorm);
   m.def("add_rmsnorm", &add_rmsnorm);
+  m.def("topk_topp_sample", &topk_topp_sample);
+  m.def("repetition_penalty", &repetition_penalty);
+  m.def("rejection_sample", &rejection_sample);
+  m.def("causal_conv1d_fwd", &causal_conv1d_fwd);
+  m.def("causal_conv1d_update", &causal_conv1d_update);
+  m.def("gdn_gating", &gdn_gating);
+  m.def("gdn_recurrent", &gdn_recurrent);
+  m.def("mtp_concat_norm", &mtp_concat_norm);
+  m.def("sigmoid_gate_mul", &sigmoid_gate_mul);
+  m.def("lora_shrink", &lora_shrink);
+  m.def("lora_expand", &lora_expand);
   m.def("rownorm", &rownorm);
   m.def("act_and_mul", &act_and_mul);
   m.def("quick_gelu", &quick_gelu);

@@ -1,0 +1,299 @@
+// Gated DeltaNet (Qwen3-Next linear-attention layers) device ops: varlen causal conv1d with a state
+// cache, single-token conv update, gating, and the gated delta rule as a sequential scan that keeps the
+// [Dv, Dk] state of one head in registers.
+//
+// Reference entry points: kunlun_ops.causal_conv1d_fn / causal_conv1d_update
+// (vllm_kunlun/ops/mamba/causal_conv1d.py:15-74,118-225), fused_gdn_gating (models/qwen3_next.py:262-781),
+// fused_recurrent_gated_delta_rule (ops/fla/fused_recurrent.py:52-155) and the chunked form
+// (ops/fla/chunk.py:23-140), which is numerically the same recurrence.
+#include "../api.h"
+#include "../common/utils.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxW = 8;
+
+__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+
+__device__ __forceinline__ int find_seq(const int* __restrict__ cu, int R, int t) {
+  int lo = 0, hi = R;  // largest r with cu[r] <= t
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (cu[mid] <= t) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// y[t, c] = act(bias[c] + sum_j w[c, j] * in[t - (W-1) + j, c]); positions before the sequence start read
+// the cached state (rows W-1+p.. of the previous inputs) or zero.
+template <typename T>
+__global__ void conv1d_fwd_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
+                                  const T* __restrict__ w, const T* __restrict__ bias, const int* __restrict__ cu, int R,
+                                  const T* __restrict__ states, const int* __restrict__ slots,
+                                  const uint8_t* __restrict__ has_init, int C, int W, int act, int64_t Ttot) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t t = blockIdx.y;
+  if (c >= C || t >= Ttot) return;
+  const int r = find_seq(cu, R, (int)t);
+  const int p = (int)t - cu[r];
+  const int slot = slots[r];
+  const bool init = has_init[r] != 0 && slot >= 0;
+  float acc = bias ? to_f(bias[c]) : 0.f;
+#pragma unroll 4
+  for (int j = 0; j < W; ++j) {
+    const int q = p - (W - 1) + j;  // position within the sequence
+    float v;
+    if (q >= 0) v = to_f(x[(t - (W - 1) + j) * x_stride + c]);
+    else v = init ? to_f(states[((int64_t)slot * (W - 1) + (W - 1 + q)) * C + c]) : 0.f;
+    acc += to_f(w[(int64_t)c * W + j]) * v;
+  }
+  out[t * out_stride + c] = from_f<T>(act ? silu(acc) : acc);
+}
+
+// states[slot] <- last W-1 rows of (old state ++ x[seq]); one thread owns a channel column.
+template <typename T>
+__global__ void conv1d_state_kernel(T* __restrict__ states, const T* __restrict__ x, int64_t x_stride,
+                                    const int* __restrict__ cu, const int* __restrict__ slots,
+                                    const uint8_t* __restrict__ has_init, int C, int W) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = blockIdx.y;
+  if (c >= C) return;
+  const int s = cu[r], L = cu[r + 1] - s, slot = slots[r];
+  if (L == 0 || slot < 0) return;
+  const bool init = has_init[r] != 0;
+  float keep[kMaxW];
+  for (int j = 0; j < W - 1; ++j) {
+    const int q = L - (W - 1) + j;
+    if (q >= 0) keep[j] = to_f(x[(int64_t)(s + q) * x_stride + c]);
+    else keep[j] = init ? to_f(states[((int64_t)slot * (W - 1) + (W - 1 + q)) * C + c]) : 0.f;
+  }
+  for (int j = 0; j < W - 1; ++j) states[((int64_t)slot * (W - 1) + j) * C + c] = from_f<T>(keep[j]);
+}
+
+template <typename T>
+__global__ void conv1d_update_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
+                                     T* __restrict__ states, const T* __restrict__ w, const T* __restrict__ bias,
+                                     const int* __restrict__ slots, int C, int W, int act) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (c >= C) return;
+  const int slot = slots[b];
+  if (slot < 0) { out[(int64_t)b * out_stride + c] = from_f<T>(0.f); return; }
+  T* st = states + (int64_t)slot * (W - 1) * C + c;
+  float acc = bias ? to_f(bias[c]) : 0.f;
+  float cur = to_f(x[(int64_t)b * x_stride + c]);
+  for (int j = 0; j < W - 1; ++j) {
+    float v = to_f(st[(int64_t)j * C]);
+    acc += to_f(w[(int64_t)c * W + j]) * v;
+    if (j > 0) st[(int64_t)(j - 1) * C] = from_f<T>(v);
+  }
+  acc += to_f(w[(int64_t)c * W + W - 1]) * cur;
+  st[(int64_t)(W - 2) * C] = from_f<T>(cur);
+  out[(int64_t)b * out_stride + c] = from_f<T>(act ? silu(acc) : acc);
+}
+
+// g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b)
+template <typename T>
+__global__ void gdn_gating_kernel(float* __restrict__ g, float* __restrict__ beta, const T* __restrict__ a, int64_t a_stride,
+                                  const T* __restrict__ b, int64_t b_stride, const float* __restrict__ A_log,
+                                  const float* __restrict__ dt_bias, int H, int64_t T_) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= T_ * H) return;
+  int64_t t = i / H;
+  int h = (int)(i % H);
+  float xa = to_f(a[t * a_stride + h]) + dt_bias[h];
+  float sp = xa > 20.f ? xa : log1pf(__expf(xa));
+  g[i] = -__expf(A_log[h]) * sp;
+  beta[i] = 1.f / (1.f + __expf(-to_f(b[t * b_stride + h])));
+}
+
+// Sequential gated delta rule.  Block = 128 threads = 32 state rows (of Dv) x 4 quarters of Dk; grid
+// (Dv/32, Hv, sequences).  Per token: S *= exp(g); pred = S k; S += beta (v - pred) k^T; o = S q.
+template <typename T, int DK>
+__global__ void __launch_bounds__(128) gdn_recurrent_kernel(
+    T* __restrict__ out, int64_t o_stride, const T* __restrict__ q, const T* __restrict__ k, int64_t qk_stride,
+    const T* __restrict__ v, int64_t v_stride, const float* __restrict__ g, const float* __restrict__ beta,
+    float* __restrict__ states /*[slots, Hv, Dv, DK]*/, const int* __restrict__ cu, const int* __restrict__ slots,
+    const uint8_t* __restrict__ has_init, int Hk, int Hv, int Dv, float scale, int l2norm) {
+  static_assert(DK % 16 == 0, "DK");
+  constexpr int QW = DK / 4;  // state columns per thread
+  __shared__ __align__(16) float sk[2][DK];
+  __shared__ __align__(16) float sq[2][DK];
+  __shared__ float ssum[2][2][4];
+  const int tid = threadIdx.x, rl = tid >> 2, qd = tid & 3;
+  const int hv = blockIdx.y, r = blockIdx.z, hk = hv / (Hv / Hk);
+  const int row = blockIdx.x * 32 + rl;
+  const int s = cu[r], L = cu[r + 1] - s, slot = slots[r];
+  if (L == 0 || slot < 0) return;
+  float* sp = states + (((int64_t)slot * Hv + hv) * Dv + row) * DK + qd * QW;
+  float S[QW];
+  if (has_init[r]) {
+#pragma unroll
+    for (int j = 0; j < QW; j += 4) *reinterpret_cast<float4*>(&S[j]) = *reinterpret_cast<const float4*>(sp + j);
+  } else {
+#pragma unroll
+    for (int j = 0; j < QW; ++j) S[j] = 0.f;
+  }
+  const bool ldr = tid < DK;  // DK <= 128: one loader thread per column
+  float kn = 0.f, qn = 0.f;
+  if (ldr) {
+    kn = to_f(k[(int64_t)s * qk_stride + hk * DK + tid]);
+    qn = to_f(q[(int64_t)s * qk_stride + hk * DK + tid]);
+  }
+  for (int t = 0; t < L; ++t) {
+    const int buf = t & 1;
+    if (ldr) { sk[buf][tid] = kn; sq[buf][tid] = qn; }
+    float k2 = warp_sum(kn * kn), q2 = warp_sum(qn * qn);
+    if ((tid & 31) == 0) { ssum[buf][0][tid >> 5] = k2; ssum[buf][1][tid >> 5] = q2; }
+    __syncthreads();
+    const int64_t tok = s + t;
+    if (ldr && t + 1 < L) {
+      kn = to_f(k[(tok + 1) * qk_stride + hk * DK + tid]);
+      qn = to_f(q[(tok + 1) * qk_stride + hk * DK + tid]);
+    }
+    const float gt = __expf(g[tok * Hv + hv]), bt = beta[tok * Hv + hv];
+    const float vt = to_f(v[tok * v_stride + hv * Dv + row]);
+    float rk = 1.f, rq = scale;
+    if (l2norm) {
+      rk = rsqrtf(ssum[buf][0][0] + ssum[buf][0][1] + ssum[buf][0][2] + ssum[buf][0][3] + 1e-6f);
+      rq = scale * rsqrtf(ssum[buf][1][0] + ssum[buf][1][1] + ssum[buf][1][2] + ssum[buf][1][3] + 1e-6f);
+    }
+    const float* kk = &sk[buf][qd * QW];
+    const float* qq = &sq[buf][qd * QW];
+    float pred = 0.f;
+#pragma unroll
+    for (int j = 0; j < QW; j += 4) {
+      float4 k4 = *reinterpret_cast<const float4*>(kk + j);
+      S[j] *= gt; S[j + 1] *= gt; S[j + 2] *= gt; S[j + 3] *= gt;
+      pred += S[j] * k4.x + S[j + 1] * k4.y + S[j + 2] * k4.z + S[j + 3] * k4.w;
+    }
+    pred += __shfl_xor_sync(0xffffffff, pred, 1);
+    pred += __shfl_xor_sync(0xffffffff, pred, 2);
+    const float delta = (vt - pred * rk) * bt * rk;
+    float o = 0.f;
+#pragma unroll
+    for (int j = 0; j < QW; j += 4) {
+      float4 k4 = *reinterpret_cast<const float4*>(kk + j);
+      float4 q4 = *reinterpret_cast<const float4*>(qq + j);
+      S[j] += delta * k4.x; S[j + 1] += delta * k4.y; S[j + 2] += delta * k4.z; S[j + 3] += delta * k4.w;
+      o += S[j] * q4.x + S[j + 1] * q4.y + S[j + 2] * q4.z + S[j + 3] * q4.w;
+    }
+    o += __shfl_xor_sync(0xffffffff, o, 1);
+    o += __shfl_xor_sync(0xffffffff, o, 2);
+    if (qd == 0) out[tok * o_stride + hv * Dv + row] = from_f<T>(o * rq);
+  }
+#pragma unroll
+  for (int j = 0; j < QW; j += 4) *reinterpret_cast<float4*>(sp + j) = *reinterpret_cast<const float4*>(&S[j]);
+}
+
+// MTP input glue: out[t] = [rmsnorm(embed[t]) * (pos != 0), rmsnorm(hidden[t])]  (deepseek_mtp.py:79-87)
+template <typename T>
+__global__ void mtp_concat_norm_kernel(T* __restrict__ out, const T* __restrict__ embed, const T* __restrict__ hidden,
+                                       const T* __restrict__ we, const T* __restrict__ wh, const int64_t* __restrict__ pos,
+                                       int H, float eps) {
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const bool zero = pos && pos[t] == 0;
+  float se = 0.f, sh = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float e = zero ? 0.f : to_f(embed[t * H + i]), h = to_f(hidden[t * H + i]);
+    se += e * e;
+    sh += h * h;
+  }
+  se = block_sum(se, red);
+  sh = block_sum(sh, red);
+  const float re = rsqrtf(se / H + eps), rh = rsqrtf(sh / H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float e = zero ? 0.f : to_f(embed[t * H + i]), h = to_f(hidden[t * H + i]);
+    out[t * 2 * H + i] = from_f<T>(e * re * to_f(we[i]));
+    out[t * 2 * H + H + i] = from_f<T>(h * rh * to_f(wh[i]));
+  }
+}
+
+// out[t, i] = o[t, i] * sigmoid(gate[t, i]) with a strided gate (column slice of a fused projection)
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ out, const T* __restrict__ o, const T* __restrict__ gate,
+                                        int64_t gate_stride, int D, int64_t n) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int64_t t = i / D;
+  int c = (int)(i % D);
+  float gv = to_f(gate[t * gate_stride + c]);
+  out[i] = from_f<T>(to_f(o[i]) / (1.f + __expf(-gv)));
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_causal_conv1d_fwd(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* w,
+                                      const void* bias, const int* cu, int R, void* states, const int* slots,
+                                      const uint8_t* has_init, int C, int W, int act, int64_t T_, int dtype, cudaStream_t st) {
+  if (W > b200::kMaxW || W < 2) return 3;
+  if (T_ == 0) return 0;
+  dim3 g1((C + 255) / 256, (unsigned)T_), g2((C + 255) / 256, R);
+  B200_DISPATCH_DTYPE(dtype, {
+    b200::conv1d_fwd_kernel<T><<<g1, 256, 0, st>>>((T*)out, out_stride, (const T*)x, x_stride, (const T*)w, (const T*)bias, cu,
+                                                   R, (const T*)states, slots, has_init, C, W, act, T_);
+    b200::conv1d_state_kernel<T><<<g2, 256, 0, st>>>((T*)states, (const T*)x, x_stride, cu, slots, has_init, C, W);
+  });
+  return cudaGetLastError() != cudaSuccess;
+}
+
+extern "C" int b200_causal_conv1d_update(void* out, int64_t out_stride, const void* x, int64_t x_stride, void* states,
+                                         const void* w, const void* bias, const int* slots, int64_t B, int C, int W, int act,
+                                         int dtype, cudaStream_t st) {
+  if (W > b200::kMaxW || W < 2) return 3;
+  if (B == 0) return 0;
+  dim3 g((C + 255) / 256, (unsigned)B);
+  B200_DISPATCH_DTYPE(dtype, (b200::conv1d_update_kernel<T><<<g, 256, 0, st>>>((T*)out, out_stride, (const T*)x, x_stride,
+                                                                              (T*)states, (const T*)w, (const T*)bias, slots,
+                                                                              C, W, act)));
+  return cudaGetLastError() != cudaSuccess;
+}
+
+extern "C" int b200_gdn_gating(float* g, float* beta, const void* a, int64_t a_stride, const void* b, int64_t b_stride,
+                               const float* A_log, const float* dt_bias, int H, int64_t T_, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  unsigned blocks = (unsigned)((T_ * H + 255) / 256);
+  B200_DISPATCH_DTYPE(dtype, (b200::gdn_gating_kernel<T><<<blocks, 256, 0, st>>>(g, beta, (const T*)a, a_stride, (const T*)b,
+                                                                                 b_stride, A_log, dt_bias, H, T_)));
+  return cudaGetLastError() != cudaSuccess;
+}
+
+extern "C" int b200_gdn_recurrent(void* out, int64_t o_stride, const void* q, const void* k, int64_t qk_stride, const void* v,
+                                  int64_t v_stride, const float* g, const float* beta, float* states, const int* cu,
+                                  const int* slots, const uint8_t* has_init, int R, int Hk, int Hv, int Dk, int Dv, float scale,
+                                  int l2norm, int dtype, cudaStream_t st) {
+  if (R == 0) return 0;
+  if (Dv % 32 != 0 || Hv % Hk != 0) return 3;
+  dim3 grid(Dv / 32, Hv, R);
+#define B200_GDN_LAUNCH(DK)                                                                                          \
+  B200_DISPATCH_DTYPE(dtype, (b200::gdn_recurrent_kernel<T, DK><<<grid, 128, 0, st>>>(                                  \
+                                 (T*)out, o_stride, (const T*)q, (const T*)k, qk_stride, (const T*)v, v_stride, g, beta, \
+                                 states, cu, slots, has_init, Hk, Hv, Dv, scale, l2norm)))
+  if (Dk == 128) { B200_GDN_LAUNCH(128); }
+  else if (Dk == 64) { B200_GDN_LAUNCH(64); }
+  else if (Dk == 32) { B200_GDN_LAUNCH(32); }
+  else if (Dk == 16) { B200_GDN_LAUNCH(16); }
+  else return 3;
+#undef B200_GDN_LAUNCH
+  return cudaGetLastError() != cudaSuccess;
+}
+
+extern "C" int b200_mtp_concat_norm(void* out, const void* embed, const void* hidden, const void* we, const void* wh,
+                                    const int64_t* pos, int64_t T_, int H, float eps, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, (b200::mtp_concat_norm_kernel<T><<<(unsigned)T_, 512, 0, st>>>(
+                                 (T*)out, (const T*)embed, (const T*)hidden, (const T*)we, (const T*)wh, pos, H, eps)));
+  return cudaGetLastError() != cudaSuccess;
+}
+
+extern "C" int b200_sigmoid_gate_mul(void* out, const void* o, const void* gate, int64_t gate_stride, int D, int64_t T_,
+                                     int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  int64_t n = T_ * D;
+  B200_DISPATCH_DTYPE(dtype, (b200::sigmoid_gate_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+                                 (T*)out, (const T*)o, (const T*)gate, gate_stride, D, n)));
+  return cudaGetLastError() != cudaSuccess;
+}

@@ -97,6 +97,7 @@ class ModelConfig:
     gdn_head_k_dim: int = 0
     gdn_head_v_dim: int = 0
     gdn_conv_kernel: int = 4
+    attn_output_gate: bool = False  # q_proj carries a sigmoid output gate (Qwen3-Next full-attention layers)
     # quantization of the checkpoint
     quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq"
     weight_block_size: tuple = (128, 128)
@@ -244,6 +245,22 @@ class ModelConfig:
             kw.update(attention_sinks=True, sliding_window_pattern=2, hidden_act="swigluoai",
                       moe_bias=True, qkv_bias=True, o_bias=True,
                       sliding_window=cfg.get("sliding_window", 128))
+        if arch.startswith("Qwen3Next") or arch.startswith("Qwen3_5"):
+            tc = cfg.get("text_config") or cfg
+            kw.update(
+                linear_attn_pattern=tc.get("full_attention_interval", 4), gdn_num_k_heads=tc.get("linear_num_key_heads", 16),
+                gdn_num_v_heads=tc.get("linear_num_value_heads", 32), gdn_head_k_dim=tc.get("linear_key_head_dim", 128),
+                gdn_head_v_dim=tc.get("linear_value_head_dim", 128), gdn_conv_kernel=tc.get("linear_conv_kernel_dim", 4),
+                attn_output_gate=True, gemma_norm=True, qk_norm=True,
+                rotary_dim=int(kw["head_dim"] * float(tc.get("partial_rotary_factor", 0.25))),
+                num_shared_experts=1 if tc.get("shared_expert_intermediate_size") else 0, shared_expert_gate=True)
+        if arch.startswith("Gemma"):
+            kw.update(gemma_norm=True, hidden_act="gelu_tanh", qk_norm=True,
+                      sliding_window=cfg.get("sliding_window"), sliding_window_pattern=cfg.get("sliding_window_pattern", 6),
+                      tie_word_embeddings=True)
+        if arch == "MiMoV2FlashForCausalLM":
+            kw.update(v_head_dim=cfg.get("v_head_dim", kw["head_dim"]), attention_sinks=bool(cfg.get("add_swa_attention_sink_bias", True)),
+                      sliding_window=cfg.get("sliding_window", 128), sliding_window_pattern=cfg.get("hybrid_block_size", 0) or 0)
         return cls(**kw)
 
     @classmethod
@@ -302,6 +319,13 @@ class CompilationConfig:
 
 
 @dataclass
+class LoRAConfig:
+    enable: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 16
+
+
+@dataclass
 class EngineConfig:
     model: ModelConfig
     cache: CacheConfig = field(default_factory=CacheConfig)
@@ -309,6 +333,7 @@ class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
     compilation: CompilationConfig = field(default_factory=CompilationConfig)
+    lora: LoRAConfig = field(default_factory=LoRAConfig)
     device: str = "cpu"
     seed: int = 0
     weights_path: Optional[str] = None
@@ -324,6 +349,11 @@ class EngineConfig:
             self.cache.cache_dtype = "bfloat16"
         if self.device == "cpu":
             self.compilation.mode = "none"
+        if m.linear_attn_pattern:
+            # the recurrent state of a cached prefix is not kept, and a rejected draft cannot be rolled back
+            self.cache.enable_prefix_caching = False
+            if self.speculative.num_speculative_tokens:
+                raise ValueError("speculative decoding is not supported with linear-attention layers")
         if self.speculative.method == "mtp" and not m.num_mtp_layers:
             raise ValueError("MTP speculative decoding needs a model with MTP layers")
         self.scheduler.max_num_batched_tokens = max(
@@ -355,6 +385,16 @@ def qwen3_8b() -> ModelConfig:
         architecture="Qwen3ForCausalLM", name="qwen3-8b", vocab_size=151936, hidden_size=4096,
         num_layers=36, num_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=12288,
         rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, max_position=40960)
+
+
+def qwen3_next_80b_a3b() -> ModelConfig:
+    return ModelConfig(
+        architecture="Qwen3NextForCausalLM", name="qwen3-next-80b-a3b", vocab_size=151936, hidden_size=2048,
+        num_layers=48, num_heads=16, num_kv_heads=2, head_dim=256, intermediate_size=5120, rms_norm_eps=1e-6,
+        rope_theta=1e7, rotary_dim=64, qk_norm=True, gemma_norm=True, attn_output_gate=True, max_position=262144,
+        num_experts=512, num_experts_per_tok=10, moe_intermediate_size=512, num_shared_experts=1,
+        shared_expert_gate=True, norm_topk_prob=True, linear_attn_pattern=4, gdn_num_k_heads=16, gdn_num_v_heads=32,
+        gdn_head_k_dim=128, gdn_head_v_dim=128, gdn_conv_kernel=4)
 
 
 def qwen3_30b_a3b(fp8: bool = True) -> ModelConfig:
@@ -397,6 +437,7 @@ PRESETS = {
     "llama-3.1-8b": llama_3_1_8b,
     "qwen3-8b": qwen3_8b,
     "qwen3-30b-a3b": qwen3_30b_a3b,
+    "qwen3-next-80b-a3b": qwen3_next_80b_a3b,
     "deepseek-v3": deepseek_v3,
     "deepseek-v3.2": lambda: deepseek_v3(sparse=True),
     "gpt-oss-20b": gpt_oss_20b,

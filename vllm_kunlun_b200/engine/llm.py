@@ -13,7 +13,7 @@ from typing import Iterable, Optional, Sequence, Union
 
 import torch
 
-from ..config import (CacheConfig, CompilationConfig, EngineConfig, ModelConfig, ParallelConfig, PRESETS,
+from ..config import (CacheConfig, CompilationConfig, EngineConfig, LoRAConfig, ModelConfig, ParallelConfig, PRESETS,
                       SchedulerConfig, SpeculativeConfig)
 from ..parallel import state as pstate_mod
 from .request import Request, RequestOutput, SamplingParams
@@ -149,7 +149,8 @@ class LLM:
                  num_gpu_blocks: Optional[int] = None, enable_prefix_caching: bool = False,
                  enforce_eager: bool = False, speculative_config: Optional[dict] = None, seed: int = 0,
                  enable_chunked_prefill: bool = True, kv_cache_dtype: str = "auto",
-                 fused_collectives: bool = True, tokenizer=None):
+                 fused_collectives: bool = True, tokenizer=None, enable_lora: bool = False, max_loras: int = 4,
+                 max_lora_rank: int = 16):
         import os
         weights = None
         if isinstance(model, ModelConfig):
@@ -180,22 +181,36 @@ class LLM:
             scheduler=SchedulerConfig(max_num_seqs, max_num_batched_tokens, max_model_len, enable_chunked_prefill),
             speculative=spec,
             compilation=CompilationConfig(mode="none" if enforce_eager else "full_decode"),
+            lora=LoRAConfig(enable_lora, max_loras, max_lora_rank),
             device=device, seed=seed, weights_path=weights)
         self.engine = LLMEngine(cfg)
         self.tokenizer = tokenizer
         self.eos_token_id = getattr(tokenizer, "eos_token_id", None)
 
+    def add_lora(self, lora_request) -> int:
+        """Load an adapter (:class:`vllm_kunlun_b200.lora.LoRARequest`) into a slot; returns the slot."""
+        assert self.engine.runner.lora is not None, "construct the LLM with enable_lora=True"
+        with torch.inference_mode():
+            return self.engine.runner.lora.add_adapter(lora_request)
+
     def generate(self, prompt_token_ids: Iterable[Sequence[int]],
-                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 lora_request=None) -> list:
         prompts = list(prompt_token_ids)
+        if lora_request is None or not isinstance(lora_request, (list, tuple)):
+            lora_request = [lora_request] * len(prompts)
+        for lr in lora_request:
+            if lr is not None:
+                self.add_lora(lr)
         if isinstance(prompts[0], str):
             assert self.tokenizer is not None, "string prompts need a tokenizer"
             prompts = [self.tokenizer.encode(p) for p in prompts]
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             sampling_params = [sampling_params or SamplingParams()] * len(prompts)
         import copy
-        reqs = [self.engine.add_request(p, copy.copy(sp), eos_token_id=self.eos_token_id)
-                for p, sp in zip(prompts, sampling_params)]
+        reqs = [self.engine.add_request(p, copy.copy(sp), eos_token_id=self.eos_token_id,
+                                        lora_id=-1 if lr is None else lr.lora_int_id)
+                for p, sp, lr in zip(prompts, sampling_params, lora_request)]
         self.engine.run_until_done()
         outs = [RequestOutput.from_request(r) for r in reqs]
         if self.tokenizer is not None:

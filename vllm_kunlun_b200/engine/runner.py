@@ -68,9 +68,21 @@ class ModelRunner:
         self.sampler = Sampler(m.vocab_size, self.device, seed=cfg.seed)
         self.num_blocks = self._plan_num_blocks()
         self.kv_caches = self._alloc_kv()
+        self.num_state_slots = 0
+        if getattr(self.model, "uses_state_cache", False):
+            # one slot per running request for the linear-attention (conv + recurrent) state
+            self.num_state_slots = self.max_bs
+            for i, specs in self.model.state_cache_spec().items():
+                self.kv_caches[i] = tuple(torch.zeros((self.num_state_slots, *shp), dtype=dt, device=self.device)
+                                          for shp, dt in specs)
         self._alloc_staging()
         self.graphs = None
-        self.sp_peer = self._init_sequence_parallel()
+        self.lora = None
+        if cfg.lora.enable:
+            from ..lora import LoRAManager
+            self.lora = LoRAManager(self.model, cfg.lora.max_loras, cfg.lora.max_lora_rank, self.max_tokens, self.max_bs,
+                                    self.device, self.model.dtype)
+        self.sp_peer = None if self.lora is not None else self._init_sequence_parallel()
         self.attn_workspace = self._alloc_attn_workspace()
         self.last_tokens: Optional[torch.Tensor] = None  # previous step's sampled tokens (device)
         self.last_rows: dict = {}  # request_id -> row in last_tokens of its newest token
@@ -147,7 +159,7 @@ class ModelRunner:
         T, B, MB = self.max_tokens, self.max_bs, self.max_blocks_per_seq
         pin = self.is_cuda
         self.n64 = 3 * T
-        self.n32 = 2 * B + 2 + B * MB + T + T
+        self.n32 = 2 * B + 2 + B * MB + T + T + 2 * B + 2 * T
         # Two staging sets used alternately: the host may fill step i+1 while the copies of step i
         # are still queued (the engine runs at most one step ahead of the device).
         self._h64s = [torch.zeros(self.n64, dtype=torch.int64, pin_memory=pin) for _ in range(2)]
@@ -194,6 +206,13 @@ class ModelRunner:
         logits_idx = self.h32_np[o_li:o_li + self.max_tokens]
         o_rq = o_li + self.max_tokens
         req_of_tok = self.h32_np[o_rq:o_rq + Tp]
+        o_ss = o_rq + self.max_tokens
+        state_idx = self.h32_np[o_ss:o_ss + Bp]
+        has_init = self.h32_np[o_ss + self.max_bs:o_ss + self.max_bs + Bp]
+        o_lo = o_ss + 2 * self.max_bs
+        lora_tok = self.h32_np[o_lo:o_lo + Tp]
+        lora_row = self.h32_np[o_lo + self.max_tokens:o_lo + 2 * self.max_tokens]
+        any_lora = False
         t = 0
         n_logits = 0
         sample_reqs, rows_per_req = [], []
@@ -223,6 +242,11 @@ class ModelRunner:
             bt[b, len(r.block_ids):] = 0
             seq_lens[b] = c + n
             qsl[b + 1] = t + n
+            state_idx[b] = r.state_slot
+            has_init[b] = 1 if c > 0 else 0
+            lslot = self.lora.slot_for(r.lora_id) if self.lora is not None else -1
+            any_lora |= lslot >= 0
+            lora_tok[t:t + n] = lslot
             req_of_tok[t:t + n] = b
             max_seq = max(max_seq, c + n)
             max_q = max(max_q, n)
@@ -232,6 +256,7 @@ class ModelRunner:
             if sr.samples:
                 rows = n if (sr.is_decode and n_spec) else 1
                 logits_idx[n_logits:n_logits + rows] = np.arange(t + n - rows, t + n)
+                lora_row[n_logits:n_logits + rows] = lslot
                 n_logits += rows
                 sample_reqs.append(r)
                 rows_per_req.append(rows)
@@ -243,6 +268,10 @@ class ModelRunner:
             bt[b, :] = 0
             seq_lens[b] = 0
             qsl[b + 1] = t + 1
+            state_idx[b] = -1
+            has_init[b] = 0
+            lora_tok[t] = -1
+            lora_row[n_logits] = -1
             req_of_tok[t] = b
             logits_idx[n_logits] = t
             n_logits += 1
@@ -259,6 +288,14 @@ class ModelRunner:
                 self.d64.copy_(self.h64, non_blocking=True)
             n32_used = o_rq + Tp
             self.d32[:n32_used].copy_(self.h32[:n32_used], non_blocking=True)
+            if self.lora is not None:
+                self.d32[o_lo:o_lo + Tp].copy_(self.h32[o_lo:o_lo + Tp], non_blocking=True)
+                o_lr = o_lo + self.max_tokens
+                self.d32[o_lr:o_lr + n_logits].copy_(self.h32[o_lr:o_lr + n_logits], non_blocking=True)
+                self.h2d_bytes += 4 * (Tp + n_logits)
+            if self.num_state_slots:
+                self.d32[o_ss:o_ss + 2 * self.max_bs].copy_(self.h32[o_ss:o_ss + 2 * self.max_bs], non_blocking=True)
+                self.h2d_bytes += 8 * self.max_bs
             self.h2d_bytes += Tp * 8 * 3 + (Bp * 2 + 1 + Bp * nblk + n_logits + Tp) * 4
             src64, src32 = self.d64, self.d32
         else:
@@ -272,6 +309,14 @@ class ModelRunner:
             max_seq_len=max(max_seq, 1), num_decodes=num_decodes, num_decode_tokens=num_decode_tokens,
             num_prefills=Bp - num_decodes, workspace=self.attn_workspace, req_id_per_token=src32[o_rq:o_rq + Tp],
             logits_indices=src32[o_li:o_li + n_logits], num_spec_tokens=self.num_spec)
+        if self.lora is not None:
+            # a captured graph always runs the adapter kernels (ids of -1 make them no-ops)
+            self.lora.punica.update_metadata(src32[o_lo:o_lo + Tp],
+                                             src32[o_lo + self.max_tokens:o_lo + self.max_tokens + n_logits],
+                                             no_lora=not any_lora and not pad_reqs)
+        if self.num_state_slots:
+            md.state_indices = src32[o_ss:o_ss + Bp]
+            md.has_initial_state = src32[o_ss + self.max_bs:o_ss + self.max_bs + Bp]
         if not self.is_cuda:
             md.seq_lens_cpu, md.query_start_loc_cpu = md.seq_lens, md.query_start_loc
         else:
@@ -333,7 +378,8 @@ class ModelRunner:
         return StepHandle(sched, sample_reqs, rows_per_req, tokens, tokens_cpu, ev, hidden, t0, md, input_ids, full)
 
     def forward_and_sample(self, md: AttentionMetadata, input_ids, sp, capturing: bool = False):
-        ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing)
+        ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing,
+                             lora=None if self.lora is None else self.lora.punica)
         with set_forward_context(ctx):
             hidden = self.run_model(input_ids, md)
             st = self.pstate

@@ -33,8 +33,8 @@ class MTPLayer(nn.Module):
         self.shared_head_norm = RMSNorm(H, cfg.rms_norm_eps, dtype, device)
 
     def forward(self, embeds, prev_hidden, positions):
-        embeds = embeds * (positions > 0).unsqueeze(-1).to(embeds.dtype)
-        x = torch.cat([self.enorm(embeds), self.hnorm(prev_hidden)], -1)
+        # one kernel: position-0 mask, both RMSNorms and the concatenation
+        x = ops.mtp_concat_norm(embeds, prev_hidden, self.enorm.weight, self.hnorm.weight, self.enorm.eps, positions)
         h = self.eh_proj(x)
         h, res = self.mtp_block(h, None, False)
         st = get_state()

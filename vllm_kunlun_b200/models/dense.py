@@ -238,6 +238,8 @@ class DenseForCausalLM(nn.Module):
             if r is None:
                 continue
             mod, pname, shard = r
+            if shard is not None:
+                shard += getattr(mod, "shard_offset", 0)
             if not hasattr(mod, pname) or getattr(mod, pname) is None:
                 continue
             kw = {}

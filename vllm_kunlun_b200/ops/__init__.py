@@ -393,3 +393,157 @@ def indexer_topk(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query
         logits = _ra.indexer_logits(qf[qs:qe], k, ksc, weights[qs:qe], torch.zeros(n, dtype=torch.long), ke)
         out[qs:qe] = _ra.topk_per_row(logits, torch.zeros(n, dtype=torch.long), ke, topk)
     return out
+
+
+# ----------------------------------------------------------------------------- sampling kernels
+
+_sample_step = [0]
+_seen_bitmaps: dict = {}
+
+
+def topk_topp_sample(logits, temperature=None, top_k=None, top_p=None, noise=None, seed: int = 0):
+    """Temperature / top-k / top-p / exponential-race draw, one launch for the whole batch.
+    ``temperature == 0`` rows are greedy.  ``noise [B, V]`` (Exp(1) variates) overrides the in-kernel
+    counter-based generator."""
+    if logits.is_cuda:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+        _sample_step[0] += 1
+        _c().topk_topp_sample(out, logits, temperature, None if top_k is None else top_k.int(), top_p, noise, seed,
+                              _sample_step[0])
+        return out
+    B = logits.shape[0]
+    t = temperature if temperature is not None else torch.ones(B)
+    return _rx.sample(logits, t, top_k, top_p, q=noise)
+
+
+def apply_repetition_penalty(logits, token_ids, num_tokens, penalties):
+    """In place: for every distinct token of ``token_ids[b, :num_tokens[b]]``, positive logits are divided by
+    the row's penalty and negative ones multiplied (``apply_repetition_penalties_`` of the reference)."""
+    if logits.is_cuda:
+        B, V = logits.shape
+        key = (logits.device, B, V)
+        seen = _seen_bitmaps.get(key)
+        if seen is None:
+            seen = _seen_bitmaps[key] = torch.empty(B * ((V + 31) // 32), dtype=torch.int32, device=logits.device)
+        _c().repetition_penalty(logits, token_ids, num_tokens.int(), penalties.float(), seen)
+        return logits
+    for b in range(logits.shape[0]):
+        ids = token_ids[b, : int(num_tokens[b])].unique()
+        ids = ids[(ids >= 0) & (ids < logits.shape[1])]
+        row = logits[b, ids].float()
+        pen = float(penalties[b])
+        logits[b, ids] = torch.where(row > 0, row / pen, row * pen).to(logits.dtype)
+    return logits
+
+
+def rejection_sample(draft_token_ids, num_draft, target_probs, bonus_token_ids, is_greedy, draft_probs=None,
+                     uniform=None, recover_q=None, max_spec_len: int = 1, seed: int = 0):
+    """Speculative-decoding verifier, one block per request; output ``[B, max_spec_len + 1]`` padded with -1."""
+    B = num_draft.shape[0]
+    if target_probs.is_cuda:
+        out = torch.empty(B, max_spec_len + 1, dtype=torch.int64, device=target_probs.device)
+        cu = torch.zeros(B + 1, dtype=torch.int32, device=target_probs.device)
+        cu[1:] = num_draft.cumsum(0)
+        _sample_step[0] += 1
+        _c().rejection_sample(out, draft_token_ids.long(), cu, target_probs.float().contiguous(),
+                              None if draft_probs is None else draft_probs.float().contiguous(), bonus_token_ids.long(),
+                              is_greedy.to(torch.uint8), uniform, recover_q, seed, _sample_step[0])
+        return out
+    from ..sample.rejection_sampler import RejectionSampler
+    return RejectionSampler().forward(draft_token_ids, num_draft, target_probs, bonus_token_ids, is_greedy, draft_probs,
+                                      uniform, recover_q, max_spec_len)
+
+
+# ----------------------------------------------------------------------------- conv / gated delta net
+
+def causal_conv1d_fn(x, weight, bias, cu_seqlens, conv_states, state_indices, has_initial_state, activation=True):
+    if x.is_cuda:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        _c().causal_conv1d_fwd(out, x, weight, bias, cu_seqlens.int(), conv_states, state_indices.int(),
+                               has_initial_state.to(torch.uint8), activation)
+        return out
+    return _rx.causal_conv1d_fn(x, weight, bias, cu_seqlens, conv_states, state_indices, has_initial_state, activation)
+
+
+def causal_conv1d_update(x, conv_states, weight, bias, state_indices, activation=True):
+    if x.is_cuda:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        _c().causal_conv1d_update(out, x, conv_states, weight, bias, state_indices.int(), activation)
+        return out
+    return _rx.causal_conv1d_update(x, conv_states, weight, bias, state_indices, activation)
+
+
+def fused_gdn_gating(A_log, a, b, dt_bias):
+    """``g = -exp(A_log) * softplus(a + dt_bias)``, ``beta = sigmoid(b)``; fp32 ``[T, Hv]`` each."""
+    if a.is_cuda:
+        g = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+        beta = torch.empty_like(g)
+        _c().gdn_gating(g, beta, a, b, A_log.float(), dt_bias.float())
+        return g, beta
+    g = -torch.exp(A_log.float()) * torch.nn.functional.softplus(a.float() + dt_bias.float())
+    return g, torch.sigmoid(b.float())
+
+
+def gated_delta_rule(q, k, v, g, beta, states, cu_seqlens, state_indices, has_initial_state, scale=None,
+                     use_qk_l2norm=True):
+    """Varlen gated delta rule over a state cache ``[slots, Hv, Dv, Dk]`` (fp32, updated in place).
+    ``q, k [T, Hk, Dk]``, ``v [T, Hv, Dv]``, ``g, beta [T, Hv]`` fp32.  Serves prefill (chunked form in the
+    reference) and decode (recurrent form) alike."""
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    if q.is_cuda:
+        out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        _c().gdn_recurrent(out, q, k, v, g, beta, states, cu_seqlens.int(), state_indices.int(),
+                           has_initial_state.to(torch.uint8), scale, use_qk_l2norm)
+        return out
+    out = torch.empty_like(v)
+    for r in range(len(cu_seqlens) - 1):
+        s, e = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        slot = int(state_indices[r])
+        if e == s or slot < 0:
+            continue
+        S0 = states[slot] if bool(has_initial_state[r]) else torch.zeros_like(states[slot])
+        o, S = _rx.recurrent_gated_delta_rule(q[s:e], k[s:e], v[s:e], g[s:e], beta[s:e], S0, scale, use_qk_l2norm)
+        out[s:e] = o
+        states[slot] = S
+    return out
+
+
+def sigmoid_gate_mul(o, gate):
+    """``o * sigmoid(gate)``; ``gate`` may be a column slice of a wider tensor."""
+    if o.is_cuda:
+        out = torch.empty(o.shape, dtype=o.dtype, device=o.device)
+        _c().sigmoid_gate_mul(out, o.contiguous(), gate)
+        return out
+    return (o.float() * torch.sigmoid(gate.float())).to(o.dtype)
+
+
+def mtp_concat_norm(embed, hidden, enorm_w, hnorm_w, eps, positions=None):
+    """MTP layer input: ``[rmsnorm(embed) (zeroed at position 0), rmsnorm(hidden)]`` (``deepseek_mtp.py:79-87``)."""
+    if embed.is_cuda:
+        out = torch.empty(embed.shape[0], 2 * embed.shape[1], dtype=embed.dtype, device=embed.device)
+        _c().mtp_concat_norm(out, embed.contiguous(), hidden.contiguous(), enorm_w, hnorm_w, positions, eps)
+        return out
+    e = embed if positions is None else torch.where((positions == 0).unsqueeze(-1), torch.zeros_like(embed), embed)
+    return torch.cat([_rb.rmsnorm(e, enorm_w, eps), _rb.rmsnorm(hidden, hnorm_w, eps)], -1)
+
+
+# ----------------------------------------------------------------------------- LoRA
+
+def lora_shrink(x, lora_a, token_lora_ids, scale: float = 1.0):
+    """``out[t] = x[t] @ A[id[t]].T * scale`` (fp32 ``[T, r]``); ``id < 0`` rows are zero."""
+    if x.is_cuda:
+        out = torch.empty(x.shape[0], lora_a.shape[1], dtype=torch.float32, device=x.device)
+        _c().lora_shrink(out, x, lora_a, token_lora_ids.int(), scale)
+        return out
+    return _rx.bgmv_shrink(x, lora_a, token_lora_ids, scale)
+
+
+def lora_expand(h, lora_b, token_lora_ids, out, offset: int = 0, add: bool = True):
+    """``out[t, offset:offset+N] (+)= h[t] @ B[id[t]].T``."""
+    if out.is_cuda:
+        _c().lora_expand(out, h, lora_b, token_lora_ids.int(), offset, add)
+        return out
+    return _rx.bgmv_expand(h, lora_b, token_lora_ids, out, offset, add)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]

@@ -31,6 +31,7 @@ class Sampler:
         self.device = torch.device(device)
         self.gen = torch.Generator(device=self.device)
         self.gen.manual_seed(seed)
+        self.seed = seed
 
     def make_params(self, params: list, rows_per_req: list, n_rows: int) -> SamplingTensors:
         if all(p.greedy for p in params):
@@ -58,6 +59,9 @@ class Sampler:
         return self.sample(logits, sp.temperature, sp.top_k, sp.top_p)
 
     def sample(self, logits, temperature, top_k=None, top_p=None, q=None):
+        if logits.is_cuda:
+            # one launch: temperature, radix-select top-k / top-p thresholds, exponential race
+            return ops.topk_topp_sample(logits, temperature, top_k, top_p, noise=q, seed=self.seed)
         greedy = ops.argmax(logits)
         t = temperature
         lg = logits.float() / torch.where(t == 0, torch.ones_like(t), t).unsqueeze(1)
