@@ -49,7 +49,8 @@ class DecodeGraphs:
     def _forward(self, md: AttentionMetadata, input_ids):
         from ..attention.metadata import ForwardContext, set_forward_context
         r = self.runner
-        ctx = ForwardContext(attn=md, kv_caches=r.kv_caches, pstate=r.pstate, capturing=True)
+        ctx = ForwardContext(attn=md, kv_caches=r.kv_caches, pstate=r.pstate, capturing=True,
+                             lora=None if r.lora is None else r.lora.punica)
         with set_forward_context(ctx):
             hidden = r.run_model(input_ids, md)
             sel = hidden.index_select(0, md.logits_indices.long())
