@@ -51,7 +51,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(AttnParam
   const int tok_lo = row0 / g;
   const int tok_hi = min(q_len - 1, (row0 + BM - 1) / g);
   // keys visible to any row of this tile
-  int kv_end = min(seq_len, ctx + tok_hi + 1);
+  // window < 0 selects bidirectional attention (vision towers): every row sees the whole sequence
+  const bool bidir = p.window < 0;
+  int kv_end = bidir ? seq_len : min(seq_len, ctx + tok_hi + 1);
   int kv_begin = 0;
   if (p.window > 0) kv_begin = max(0, ctx + tok_lo - p.window + 1) / kTileN * kTileN;
   // this split's share (whole tiles)
@@ -117,8 +119,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attention_kernel(AttnParam
   // rows owned by this thread: r_a = wm*16 + lane/4, r_b = r_a + 8
   const int r_a = wm * 16 + (lane >> 2), r_b = r_a + 8;
   const int pa = row0 + r_a, pb = row0 + r_b;
-  const int pos_a = (pa < rows_total) ? ctx + pa / g : -1;  // -1: padding row (sees nothing)
-  const int pos_b = (pb < rows_total) ? ctx + pb / g : -1;
+  const int pos_a = (pa < rows_total) ? (bidir ? seq_len - 1 : ctx + pa / g) : -1;  // -1: padding row (sees nothing)
+  const int pos_b = (pb < rows_total) ? (bidir ? seq_len - 1 : ctx + pb / g) : -1;
   const int lo_a = (p.window > 0) ? pos_a - p.window + 1 : 0;
   const int lo_b = (p.window > 0) ? pos_b - p.window + 1 : 0;
 

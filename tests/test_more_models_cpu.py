@@ -1,0 +1,77 @@
+"""Gemma-family (sandwich norms, KV sharing) and MiMo-V2-Flash (narrow value heads) on the CPU oracle path."""
+import torch
+
+from vllm_kunlun_b200 import LLM, SamplingParams
+from vllm_kunlun_b200.config import ModelConfig, llama_3_1_8b, qwen3_30b_a3b, tiny
+from vllm_kunlun_b200.models.gemma4 import kv_source_layer
+
+KW = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=48)
+
+
+def _gemma():
+    cfg = tiny(llama_3_1_8b(), num_layers=6, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    cfg.architecture = "Gemma4ForCausalLM"
+    cfg.gemma_norm, cfg.qk_norm, cfg.hidden_act, cfg.tie_word_embeddings = True, True, "gelu_tanh", True
+    cfg.sliding_window, cfg.sliding_window_pattern = 8, 3
+    cfg.num_kv_shared_layers, cfg.final_logit_softcapping, cfg.attn_scale = 2, 30.0, 1.0
+    return cfg
+
+
+def test_gemma_kv_sharing_layout_and_generation():
+    cfg = _gemma()
+    # layers 0,1 sliding, 2 full, 3,4 sliding, 5 full; the last two share: 4 -> 3 (sliding), 5 -> 2 (full)
+    assert [kv_source_layer(cfg, i) for i in range(6)] == [0, 1, 2, 3, 3, 2]
+    llm = LLM(cfg, max_num_batched_tokens=64, **KW)
+    assert sorted(llm.engine.runner.kv_caches) == [0, 1, 2, 3]
+    prompts = [list(range(3, 40)), list(range(50, 57))]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    a = [o.token_ids for o in llm.generate(prompts, sp)]
+    b = [o.token_ids for o in LLM(cfg, max_num_batched_tokens=16, **KW).generate(prompts, sp)]
+    assert a == b
+    lg = llm.engine.runner.model.compute_logits(torch.randn(2, 64) * 100)
+    assert lg.abs().max() <= 30.0
+
+
+def test_mimo_narrow_value_heads_are_padded_in_the_weights():
+    cfg = tiny(qwen3_30b_a3b(fp8=False), num_layers=1, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=2,
+               head_dim=32, v_head_dim=16, intermediate_size=128, num_experts=4, num_experts_per_tok=2,
+               moe_intermediate_size=64, max_position=256, dtype="float32")
+    cfg.architecture = "MiMoV2FlashForCausalLM"
+    cfg.attention_sinks, cfg.sliding_window = True, 16
+    llm = LLM(cfg, **KW)
+    m = llm.engine.runner.model
+    g = torch.Generator().manual_seed(0)
+    H, D, Dv, hid = 2, 32, 16, 64
+    ck = {"model.layers.0.self_attn.q_proj.weight": torch.randn(H * D, hid, generator=g),
+          "model.layers.0.self_attn.k_proj.weight": torch.randn(H * D, hid, generator=g),
+          "model.layers.0.self_attn.v_proj.weight": torch.randn(H * Dv, hid, generator=g),
+          "model.layers.0.self_attn.o_proj.weight": torch.randn(hid, H * Dv, generator=g),
+          "model.layers.0.self_attn.attention_sink_bias": torch.randn(H, generator=g)}
+    with torch.inference_mode():
+        m.load_weights(ck.items())
+    qkv = m.layers["0"].self_attn.qkv_proj.weight.data
+    v = qkv[2 * H * D:].reshape(H, D, hid)
+    assert torch.equal(v[:, :Dv].reshape(H * Dv, hid), ck["model.layers.0.self_attn.v_proj.weight"])
+    assert v[:, Dv:].abs().sum() == 0
+    o = m.layers["0"].self_attn.o_proj.weight.data.reshape(hid, H, D)
+    assert torch.equal(o[:, :, :Dv].reshape(hid, H * Dv), ck["model.layers.0.self_attn.o_proj.weight"])
+    assert o[:, :, Dv:].abs().sum() == 0
+    assert torch.equal(m.layers["0"].self_attn.sinks.data, ck["model.layers.0.self_attn.attention_sink_bias"])
+    # padded-weight attention equals attention with narrow V followed by the narrow o_proj
+    x = torch.randn(5, hid, generator=g)
+    attn = m.layers["0"].self_attn
+    vv = (x @ qkv[2 * H * D:].T).reshape(5, H, D)
+    narrow = (vv[:, :, :Dv].reshape(5, H * Dv) @ ck["model.layers.0.self_attn.o_proj.weight"].T)
+    padded = vv.reshape(5, H * D) @ attn.o_proj.weight.data.T
+    torch.testing.assert_close(narrow, padded)
+    out = llm.generate([list(range(3, 30))], SamplingParams(max_tokens=4, ignore_eos=True))
+    assert len(out[0].token_ids) == 4
+
+
+def test_mimo_fp8_attention_weights_are_dequantised_on_load():
+    from vllm_kunlun_b200.models.mimo_v2_flash import _dequant_block
+    from vllm_kunlun_b200.models.moe import _quant_block_device
+    w = torch.randn(256, 256)
+    q, s = _quant_block_device(w)
+    torch.testing.assert_close(_dequant_block(q, s), w, atol=0.15, rtol=0.1)

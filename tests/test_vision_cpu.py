@@ -1,0 +1,81 @@
+"""Vision-language wrappers on the CPU oracle path: tower shapes, image-row injection, M-RoPE, chunked prefill."""
+import torch
+
+from vllm_kunlun_b200 import LLM, SamplingParams
+from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+from vllm_kunlun_b200.models.vision import get_mrope_positions
+
+IMG = 127
+
+
+def _qwen_vl():
+    cfg = tiny(qwen2_0_5b(), num_layers=2, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=512, dtype="float32")
+    cfg.architecture = "Qwen2_5_VLForConditionalGeneration"
+    cfg.vision = dict(depth=2, hidden=32, heads=2, patch=2, temporal_patch=1, merge=2, intermediate=64, in_channels=3,
+                      norm="rmsnorm", gated_mlp=True, image_token_id=IMG, text_architecture="Qwen2ForCausalLM")
+    cfg.mrope_section = (4, 6, 6)
+    return cfg
+
+
+def _intern():
+    cfg = tiny(qwen2_0_5b(), num_layers=2, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=512, dtype="float32")
+    cfg.architecture = "InternVLChatModel"
+    cfg.vision = dict(depth=2, hidden=32, heads=2, patch=2, intermediate=64, in_channels=3, norm="layernorm", act="gelu",
+                      layer_scale=True, image_size=8, downsample=0.5, image_token_id=IMG,
+                      text_architecture="Qwen2ForCausalLM")
+    return cfg
+
+
+def test_mrope_positions():
+    ids = [1, 2, IMG, IMG, IMG, IMG, 3, 4]
+    pos, delta = get_mrope_positions(ids, [(1, 4, 4)], IMG, 2)
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:6].tolist() == [2, 2, 2, 2]          # temporal axis constant inside one image
+    assert pos[1, 2:6].tolist() == [2, 2, 3, 3] and pos[2, 2:6].tolist() == [2, 3, 2, 3]
+    assert pos[:, 6].tolist() == [4, 4, 4] and delta == 6 - 8
+
+
+def test_qwen_vl_generation_uses_the_image_and_survives_chunking():
+    cfg = _qwen_vl()
+    grid = [(1, 8, 4)]  # 32 patches -> 8 merged tokens
+    px = torch.randn(32, 3 * 1 * 2 * 2, generator=torch.Generator().manual_seed(0))
+    prompt = [5, 6, 7] + [IMG] * 8 + [9, 10, 11, 12]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    mm = {"pixel_values": px, "image_grid_thw": grid}
+    whole = LLM(cfg, max_num_batched_tokens=64, **kw)
+    a = whole.generate([prompt, [3, 4, 5, 6]], sp, multi_modal_data=[mm, None])
+    chunked = LLM(cfg, max_num_batched_tokens=16, **kw)  # the image straddles two prefill chunks
+    b = chunked.generate([prompt, [3, 4, 5, 6]], sp, multi_modal_data=[mm, None])
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+
+    def logits(mm_data):
+        from vllm_kunlun_b200.attention.metadata import ForwardContext, set_forward_context
+        eng = whole.engine
+        eng.add_request(prompt, SamplingParams(max_tokens=1), multi_modal_data=mm_data)
+        sched = eng.scheduler.schedule()
+        md, ids, _ = eng.runner.prepare(sched)
+        ctx = ForwardContext(md, eng.runner.kv_caches, eng.pstate, extras=eng.runner._step_extras)
+        with torch.inference_mode(), set_forward_context(ctx):
+            h, _ = eng.runner.model(ids)
+            out = eng.runner.model.compute_logits(h[-1:]).float()
+        eng.run_until_done()
+        return out
+
+    l1, l2 = logits(mm), logits({"pixel_values": px * -3.0, "image_grid_thw": grid})
+    assert (l1 - l2).abs().max() > 1e-4  # the image content reaches the logits
+    emb = whole.engine.runner.model.embed_multimodal(px, grid)
+    assert emb.shape == (8, cfg.hidden_size)
+
+
+def test_internvl_tower_and_generation():
+    cfg = _intern()
+    px = torch.randn(2, 16, 3 * 2 * 2, generator=torch.Generator().manual_seed(1))  # 2 tiles, 4x4 patches each
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    emb = llm.engine.runner.model.embed_multimodal(px)
+    assert emb.shape == (2 * 4, cfg.hidden_size)  # pixel shuffle: 16 -> 4 tokens per tile
+    prompt = [5] + [IMG] * 8 + [9, 10]
+    out = llm.generate([prompt], SamplingParams(max_tokens=4, ignore_eos=True), multi_modal_data={"pixel_values": px})
+    assert len(out[0].token_ids) == 4

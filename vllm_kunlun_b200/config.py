@@ -97,9 +97,17 @@ class ModelConfig:
     gdn_head_k_dim: int = 0
     gdn_head_v_dim: int = 0
     gdn_conv_kernel: int = 4
+    # vision-language: tower description (depth, hidden, heads, patch, ...) and M-RoPE sections of the decoder
+    vision: Optional[dict] = None
+    mrope_section: tuple = ()
+    mrope_interleaved: bool = False
+    num_kv_shared_layers: int = 0  # Gemma: trailing layers that reuse an earlier layer's KV cache
+    attn_scale: Optional[float] = None  # softmax scale override (Gemma query_pre_attn_scalar)
+    final_logit_softcapping: float = 0.0
     attn_output_gate: bool = False  # q_proj carries a sigmoid output gate (Qwen3-Next full-attention layers)
     # quantization of the checkpoint
     quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq"
+    attn_quantization: Optional[str] = "same"  # "same" = follow ``quantization``; None = keep attention projections unquantised
     weight_block_size: tuple = (128, 128)
     dtype: str = "bfloat16"
 
@@ -254,7 +262,28 @@ class ModelConfig:
                 attn_output_gate=True, gemma_norm=True, qk_norm=True,
                 rotary_dim=int(kw["head_dim"] * float(tc.get("partial_rotary_factor", 0.25))),
                 num_shared_experts=1 if tc.get("shared_expert_intermediate_size") else 0, shared_expert_gate=True)
+        vcfg = cfg.get("vision_config")
+        if vcfg and ("VL" in arch or arch.startswith("Intern")):
+            tc = cfg.get("text_config") or cfg.get("llm_config") or cfg
+            intern = arch.startswith("Intern")
+            kw["vision"] = dict(
+                depth=vcfg.get("depth", vcfg.get("num_hidden_layers", 32)),
+                hidden=vcfg.get("embed_dim", vcfg.get("hidden_size", 1280)),
+                heads=vcfg.get("num_heads", vcfg.get("num_attention_heads", 16)), patch=vcfg.get("patch_size", 14),
+                temporal_patch=vcfg.get("temporal_patch_size", 2), merge=vcfg.get("spatial_merge_size", 2),
+                intermediate=vcfg.get("intermediate_size", int(vcfg.get("embed_dim", 1280) * vcfg.get("mlp_ratio", 4))),
+                in_channels=vcfg.get("in_channels", vcfg.get("in_chans", 3)),
+                norm="rmsnorm" if "2_5" in arch else "layernorm", gated_mlp="2_5" in arch,
+                act="gelu" if intern else "quick_gelu", layer_scale=intern, image_size=vcfg.get("image_size", 448),
+                downsample=cfg.get("downsample_ratio", 0.5), image_token_id=cfg.get("image_token_id", 151655),
+                text_architecture=(tc.get("architectures") or ["Qwen2ForCausalLM"])[0] if intern else
+                ("Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"))
+            rsc = tc.get("rope_scaling") or {}
+            kw["mrope_section"] = tuple(rsc.get("mrope_section", ()))
         if arch.startswith("Gemma"):
+            kw.update(num_kv_shared_layers=cfg.get("num_kv_shared_layers", 0) or 0,
+                      final_logit_softcapping=float(cfg.get("final_logit_softcapping") or 0.0),
+                      attn_scale=(float(cfg["query_pre_attn_scalar"]) ** -0.5 if cfg.get("query_pre_attn_scalar") else None))
             kw.update(gemma_norm=True, hidden_act="gelu_tanh", qk_norm=True,
                       sliding_window=cfg.get("sliding_window"), sliding_window_pattern=cfg.get("sliding_window_pattern", 6),
                       tie_word_embeddings=True)

@@ -52,9 +52,14 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], sampling: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None, eos_token_id: Optional[int] = None, lora_id: int = -1):
+                    request_id: Optional[str] = None, eos_token_id: Optional[int] = None, lora_id: int = -1,
+                    multi_modal_data: Optional[dict] = None):
+        """``multi_modal_data``: ``{"pixel_values": tensor, "image_grid_thw": [[t, h, w], ...]}`` for
+        vision-language models; the vision tower runs here, once per request."""
         rid = request_id or f"req-{next(self._ids)}"
         req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), eos_token_id, lora_id=lora_id)
+        if multi_modal_data is not None:
+            req.mm = self.runner.encode_multimodal(req.prompt_token_ids, multi_modal_data)
         self.scheduler.add(req)
         return req
 
@@ -195,8 +200,10 @@ class LLM:
 
     def generate(self, prompt_token_ids: Iterable[Sequence[int]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 lora_request=None) -> list:
+                 lora_request=None, multi_modal_data=None) -> list:
         prompts = list(prompt_token_ids)
+        if multi_modal_data is None or isinstance(multi_modal_data, dict):
+            multi_modal_data = [multi_modal_data] * len(prompts)
         if lora_request is None or not isinstance(lora_request, (list, tuple)):
             lora_request = [lora_request] * len(prompts)
         for lr in lora_request:
@@ -209,8 +216,8 @@ class LLM:
             sampling_params = [sampling_params or SamplingParams()] * len(prompts)
         import copy
         reqs = [self.engine.add_request(p, copy.copy(sp), eos_token_id=self.eos_token_id,
-                                        lora_id=-1 if lr is None else lr.lora_int_id)
-                for p, sp, lr in zip(prompts, sampling_params, lora_request)]
+                                        lora_id=-1 if lr is None else lr.lora_int_id, multi_modal_data=mm)
+                for p, sp, lr, mm in zip(prompts, sampling_params, lora_request, multi_modal_data)]
         self.engine.run_until_done()
         outs = [RequestOutput.from_request(r) for r in reqs]
         if self.tokenizer is not None:

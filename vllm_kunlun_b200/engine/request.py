@@ -49,6 +49,7 @@ class Request:
     eos_token_id: Optional[int] = None
     arrival_time: float = field(default_factory=time.perf_counter)
     lora_id: int = -1
+    mm: Optional[dict] = None  # multimodal: projected image embeddings, prompt rows they replace, M-RoPE positions
     # mutable state
     status: RequestStatus = RequestStatus.WAITING
     output_token_ids: list = field(default_factory=list)

@@ -77,6 +77,8 @@ class ModelRunner:
                                           for shp, dt in specs)
         self._alloc_staging()
         self.graphs = None
+        self.is_vl = hasattr(self.model, "embed_multimodal")
+        self._step_extras: dict = {}
         self.lora = None
         if cfg.lora.enable:
             from ..lora import LoRAManager
@@ -178,6 +180,58 @@ class ModelRunner:
         self.h64, self.h32, self.tokens_host = self._h64s[k], self._h32s[k], self._tok_hosts[k]
         self.h64_np, self.h32_np = self.h64.numpy(), self.h32.numpy()
 
+    # ------------------------------------------------------------------ multimodal
+    def encode_multimodal(self, prompt_token_ids, data: dict) -> dict:
+        """Run the vision tower for one request and work out which prompt rows its embeddings replace."""
+        assert self.is_vl, "the loaded model has no vision tower"
+        grid = data.get("image_grid_thw")
+        grid = [tuple(int(x) for x in g) for g in (grid.tolist() if hasattr(grid, "tolist") else grid)] if grid is not None else None
+        embeds = self.model.embed_multimodal(data["pixel_values"], grid)
+        rows, pos3, delta = self.model.mm_metadata(prompt_token_ids, grid)
+        assert len(rows) == embeds.shape[0], f"{len(rows)} image placeholder tokens but {embeds.shape[0]} image embeddings"
+        return {"embeds": embeds, "rows": np.asarray(rows, dtype=np.int64), "pos3": None if pos3 is None else pos3.numpy(),
+                "delta": int(delta)}
+
+    def _prepare_multimodal(self, srs, pos, Tp):
+        """Image-row overrides and 3-axis rotary positions for this step (prefill chunks that touch images)."""
+        self._step_extras = {}
+        dst, src = [], []
+        pos3 = None
+        t = 0
+        for sr in srs:
+            r, n, c = sr.req, sr.num_new_tokens, sr.req.num_computed_tokens
+            if r.mm is not None:
+                L = r.num_prompt_tokens
+                if r.mm["delta"]:
+                    hi = np.arange(c, c + n)
+                    pos[t:t + n] = np.where(hi >= L, hi + r.mm["delta"], hi)
+                rows = r.mm["rows"]
+                sel = np.nonzero((rows >= c) & (rows < c + n))[0]
+                if len(sel):
+                    dst.append(torch.from_numpy(t + rows[sel] - c))
+                    src.append(r.mm["embeds"].index_select(0, torch.from_numpy(sel).to(self.device)))
+                if r.mm["pos3"] is not None and c < L:
+                    if pos3 is None:
+                        pos3 = np.repeat(pos[None, :Tp], 3, 0)
+                    k = min(n, L - c)
+                    pos3[:, t:t + k] = r.mm["pos3"][:, c:c + k]
+            t += n
+        if pos3 is not None:
+            # rows filled after this request's turn still hold the 1-D positions written by the main loop
+            t = 0
+            for sr in srs:
+                r, n, c = sr.req, sr.num_new_tokens, sr.req.num_computed_tokens
+                if r.mm is None or r.mm["pos3"] is None or c >= r.num_prompt_tokens:
+                    pos3[:, t:t + n] = pos[t:t + n]
+                else:
+                    k = min(n, r.num_prompt_tokens - c)
+                    pos3[:, t + k:t + n] = pos[t + k:t + n]
+                t += n
+            self._step_extras["mrope_positions"] = torch.from_numpy(pos3.copy()).to(self.device, non_blocking=True)
+        if dst:
+            self._step_extras["mm_dst"] = torch.cat(dst).to(self.device, non_blocking=True)
+            self._step_extras["mm_src"] = torch.cat(src)
+
     # ------------------------------------------------------------------ input preparation
     def prepare(self, sched: SchedulerOutput, pad_reqs: int = 0):
         """Fill the staging buffers for this step; returns ``(AttentionMetadata, input_ids, info)``."""
@@ -276,6 +330,8 @@ class ModelRunner:
             logits_idx[n_logits] = t
             n_logits += 1
             t += 1
+        if self.is_vl:
+            self._prepare_multimodal(srs, pos, Tp)
         if pad_reqs:  # a padded (graph) batch is decode-shaped throughout
             num_decodes, num_decode_tokens = Bp, Tp
         # ---- host -> device
@@ -379,7 +435,7 @@ class ModelRunner:
 
     def forward_and_sample(self, md: AttentionMetadata, input_ids, sp, capturing: bool = False):
         ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing,
-                             lora=None if self.lora is None else self.lora.punica)
+                             lora=None if self.lora is None else self.lora.punica, extras=self._step_extras)
         with set_forward_context(ctx):
             hidden = self.run_model(input_ids, md)
             st = self.pstate

@@ -42,11 +42,12 @@ class GQAAttention(nn.Module):
             repl = [False, True, True]
         else:
             sizes, repl = [cfg.q_size, kv_total, v_total], [False, False, False]
+        quant = cfg.quantization if cfg.attn_quantization == "same" else cfg.attn_quantization
         self.qkv_proj = ColumnParallelLinear(cfg.hidden_size, sizes, bias=cfg.qkv_bias, dtype=dtype,
-                                             device=device, quant=cfg.quantization, replicate=repl)
+                                             device=device, quant=quant, replicate=repl)
         # the all-reduce of o_proj is fused into the add+RMSNorm that follows (reduce_add_rmsnorm)
         self.o_proj = RowParallelLinear(cfg.num_heads * cfg.v_head_dim, cfg.hidden_size, bias=cfg.o_bias,
-                                        dtype=dtype, device=device, quant=cfg.quantization, reduce_results=False)
+                                        dtype=dtype, device=device, quant=quant, reduce_results=False)
         self.q_norm = self.k_norm = None
         if cfg.qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)

@@ -1,0 +1,121 @@
+"""Gemma-family decoder: sandwich norms, (1 + w) RMSNorm, GELU-tanh gated MLP, per-layer sliding window,
+scaled embeddings, q/k norm, final-logit soft-capping, cross-layer KV sharing, optional MoE blocks.
+
+Reference: ``vllm_kunlun/models/gemma4.py`` (per-layer sliding window and cross-layer KV sharing :327-412, per-layer
+inputs, MoE router) and ``ops/rotary_embedding/gemma4_rope.py:56-76`` (proportional RoPE: only a fraction of each
+head is rotated, the rest passes through).  KV sharing: the last ``num_kv_shared_layers`` layers own no K/V
+projection output in the cache; they attend over the cache written by the latest earlier layer of the same kind
+(sliding / full).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..attention.metadata import get_forward_context
+from ..config import ModelConfig
+from ..parallel.state import get_state
+from .dense import GatedMLP, GQAAttention
+from .layers import RMSNorm, reduce_add_rmsnorm
+from .moe import MoEForCausalLM, SparseMoEBlock
+
+
+def kv_source_layer(cfg: ModelConfig, i: int) -> int:
+    """Layer whose KV cache layer ``i`` reads (itself unless it is a KV-shared layer)."""
+    first_shared = cfg.num_layers - cfg.num_kv_shared_layers
+    if cfg.num_kv_shared_layers <= 0 or i < first_shared:
+        return i
+    kind = cfg.layer_is_sliding(i)
+    for j in range(first_shared - 1, -1, -1):
+        if cfg.layer_is_sliding(j) == kind:
+            return j
+    return i
+
+
+class Gemma4Attention(GQAAttention):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        super().__init__(cfg, layer_idx, dtype, device)
+        self.kv_layer = kv_source_layer(cfg, layer_idx)
+        if cfg.attn_scale is not None:
+            self.scale = cfg.attn_scale
+
+    def forward(self, hidden):
+        if self.kv_layer == self.layer_idx:
+            return super().forward(hidden)
+        # KV-shared layer: only the query is used; keys / values come from the source layer's cache
+        ctx = get_forward_context()
+        md, cfg = ctx.attn, self.cfg
+        qkv = self.qkv_proj(hidden)
+        T = qkv.shape[0]
+        q = ops.qkv_split_norm_rope_cache(
+            qkv, md.positions, self.cos_sin, None if self.q_norm is None else self.q_norm.weight,
+            None if self.k_norm is None else self.k_norm.weight, cfg.rms_norm_eps, self.num_heads, self.num_kv_heads,
+            self.head_dim, cfg.rope_neox, None, md.slot_mapping, cfg.gemma_norm)
+        o = ops.paged_attention(
+            q.view(T, self.num_heads, self.head_dim), ctx.kv_caches[self.kv_layer], md.block_tables, md.seq_lens,
+            md.query_start_loc, self.scale, md.max_query_len, md.max_seq_len, self.window, self.sinks, md.seq_lens_cpu,
+            md.query_start_loc_cpu, workspace=md.workspace, num_decodes=md.num_decodes,
+            decode_query_len=1 + md.num_spec_tokens, num_decode_tokens=md.num_decode_tokens)
+        return self.o_proj(o.reshape(T, self.num_heads * self.head_dim))
+
+
+class Gemma4DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        super().__init__()
+        def norm():
+            return RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
+        self.input_layernorm, self.post_attention_layernorm = norm(), norm()
+        self.pre_feedforward_layernorm, self.post_feedforward_layernorm = norm(), norm()
+        self.self_attn = Gemma4Attention(cfg, layer_idx, dtype, device)
+        if cfg.layer_is_moe(layer_idx):
+            self.mlp = SparseMoEBlock(cfg, dtype, device)
+        else:
+            self.mlp = GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization, cfg.hidden_act,
+                                cfg.mlp_bias, reduce_results=False)
+
+    def forward(self, hidden, residual, partial: bool = False):
+        """``hidden`` is the complete (already reduced and post-normed) output of the previous layer."""
+        if residual is None:
+            residual = hidden
+            h = self.input_layernorm(hidden)
+        else:
+            h, residual = self.input_layernorm(hidden, residual)
+        a = self.self_attn(h)
+        a, _ = reduce_add_rmsnorm(a, None, self.post_attention_layernorm, True)
+        h, residual = self.pre_feedforward_layernorm(a, residual)
+        m = self.mlp(h)
+        m, _ = reduce_add_rmsnorm(m, None, self.post_feedforward_layernorm, True)
+        return m, residual
+
+
+class Gemma4ForCausalLM(MoEForCausalLM):
+    layer_cls = Gemma4DecoderLayer
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype=None):
+        super().__init__(cfg, device, dtype)
+        self.embed_scale = cfg.hidden_size ** 0.5
+
+    def forward(self, input_ids, hidden=None, residual=None):
+        if hidden is None:
+            hidden = self.embed_tokens(input_ids)
+            hidden = hidden * torch.tensor(self.embed_scale, dtype=hidden.dtype, device=hidden.device)
+        for i in range(self.first_layer, self.last_layer):
+            hidden, residual = self.layers[str(i)](hidden, residual)
+        if self.norm is None:
+            return hidden, residual
+        hidden, _ = self.norm(hidden, residual)  # layer outputs are complete: no reduction here
+        return hidden, None
+
+    def compute_logits(self, hidden):
+        lg = super().compute_logits(hidden)
+        cap = self.cfg.final_logit_softcapping
+        if cap:
+            lg = (torch.tanh(lg.float() / cap) * cap).to(lg.dtype)
+        return lg
+
+    def kv_cache_spec(self, block_size: int):
+        st = get_state()
+        kvh = max(1, self.cfg.num_kv_heads // st.tp_size)
+        return {i: ((2, kvh, block_size, self.cfg.head_dim), self.dtype)
+                for i in range(self.first_layer, self.last_layer) if kv_source_layer(self.cfg, i) == i}

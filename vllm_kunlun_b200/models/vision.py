@@ -1,0 +1,329 @@
+"""Vision-language wrappers: a vision tower + projector in front of a registered text decoder.
+
+Reference: ``models/qwen2_vl.py`` / ``qwen2_5_vl.py`` / ``qwen3_vl.py`` (ViT attention through
+``flash_attn_varlen_func`` / SDPA ``qwen2_5_vl.py:356-393``, 2-D rotary ``xspeedgate_ops.rope_vit``
+``qwen2_vl.py:255``, M-RoPE text positions ``ops/rotary_embedding/kunlun_mrope.py:47-71``) and
+``models/internvl.py`` / ``intern_vit.py`` / ``interns1*.py`` (InternViT with SDPA ``intern_vit.py:299``,
+pixel-shuffle + MLP projector).
+
+Flow: the engine runs the tower once per request when the request is added, keeps the projected image
+embeddings on the device, and during prefill the rows of the step that hold image placeholder tokens are
+overwritten with them right after the embedding lookup.  The tower is replicated on every TP rank (it is small
+next to the decoder); its GEMMs and attention run on the same kernels as the decoder.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..attention.metadata import get_forward_context
+from ..config import ModelConfig
+from .dense import DenseForCausalLM, GQAAttention
+from .layers import RMSNorm, ReplicatedLinear, param
+
+
+class _Norm(nn.Module):
+    def __init__(self, size, eps, kind, dtype, device):
+        super().__init__()
+        self.kind, self.eps = kind, eps
+        self.weight = param(size, dtype=dtype, device=device)
+        self.bias = param(size, dtype=dtype, device=device) if kind == "layernorm" else None
+
+    def forward(self, x):
+        if self.kind == "layernorm":
+            return ops.layernorm(x, self.weight, self.bias, self.eps)
+        return ops.rmsnorm(x, self.weight, self.eps)
+
+
+class VisionBlock(nn.Module):
+    def __init__(self, vc: dict, dtype, device):
+        super().__init__()
+        h, self.heads = vc["hidden"], vc["heads"]
+        self.head_dim = h // self.heads
+        kind = vc.get("norm", "layernorm")
+        self.norm1 = _Norm(h, vc.get("eps", 1e-6), kind, dtype, device)
+        self.norm2 = _Norm(h, vc.get("eps", 1e-6), kind, dtype, device)
+        self.qkv = ReplicatedLinear(h, 3 * h, bias=True, dtype=dtype, device=device)
+        self.proj = ReplicatedLinear(h, h, bias=True, dtype=dtype, device=device)
+        self.gated = vc.get("gated_mlp", False)
+        inter = vc["intermediate"]
+        self.fc1 = ReplicatedLinear(h, inter * (2 if self.gated else 1), bias=True, dtype=dtype, device=device)
+        self.fc2 = ReplicatedLinear(inter, h, bias=True, dtype=dtype, device=device)
+        self.act = vc.get("act", "quick_gelu")
+        self.ls1 = param(h, dtype=dtype, device=device) if vc.get("layer_scale") else None
+        self.ls2 = param(h, dtype=dtype, device=device) if vc.get("layer_scale") else None
+
+    def forward(self, x, cu_seqlens, cos=None, sin=None):
+        T = x.shape[0]
+        qkv = self.qkv(self.norm1(x)).view(T, 3, self.heads, self.head_dim)
+        q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+        if cos is not None:
+            q, k = ops.rope_vit(q, k, cos, sin)
+        a = ops.varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, self.head_dim ** -0.5)
+        a = self.proj(a.reshape(T, -1))
+        x = x + (a if self.ls1 is None else a * self.ls1)
+        m = self.fc1(self.norm2(x))
+        if self.gated:
+            m = ops.act_and_mul(m, "silu")
+        elif self.act == "quick_gelu":
+            m = ops.quick_gelu(m)
+        else:
+            m = torch.nn.functional.gelu(m.float()).to(m.dtype)
+        m = self.fc2(m)
+        return x + (m if self.ls2 is None else m * self.ls2)
+
+
+class QwenVisionTransformer(nn.Module):
+    """Patch embedding (the 3-D conv is a GEMM over flattened patches), 2-D rotary blocks, 2x2 patch merger."""
+
+    def __init__(self, vc: dict, out_hidden: int, dtype, device):
+        super().__init__()
+        self.vc = vc
+        h = vc["hidden"]
+        self.patch_dim = vc.get("in_channels", 3) * vc.get("temporal_patch", 2) * vc["patch"] ** 2
+        self.patch_embed = ReplicatedLinear(self.patch_dim, h, bias=False, dtype=dtype, device=device)
+        self.blocks = nn.ModuleList([VisionBlock(vc, dtype, device) for _ in range(vc["depth"])])
+        self.merge = vc.get("merge", 2)
+        self.ln_q = _Norm(h, vc.get("eps", 1e-6), vc.get("norm", "layernorm"), dtype, device)
+        mh = h * self.merge ** 2
+        self.merger_fc1 = ReplicatedLinear(mh, mh, bias=True, dtype=dtype, device=device)
+        self.merger_fc2 = ReplicatedLinear(mh, out_hidden, bias=True, dtype=dtype, device=device)
+        self.head_dim = h // vc["heads"]
+
+    def rot_pos_emb(self, grid_thw, device):
+        """Per-token (h, w) rotary angles; tokens are ordered so that each ``merge x merge`` window is contiguous."""
+        m = self.merge
+        dim = self.head_dim // 2
+        inv = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+        chunks = []
+        for t, h, w in grid_thw:
+            hp = torch.arange(h).unsqueeze(1).expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).reshape(-1)
+            wp = torch.arange(w).unsqueeze(0).expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).reshape(-1)
+            ang = torch.cat([hp.unsqueeze(1).float() * inv, wp.unsqueeze(1).float() * inv], -1)  # [h*w, dim]
+            chunks.append(ang.repeat(t, 1))
+        ang = torch.cat(chunks, 0).to(device)
+        return ang.cos(), ang.sin()
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+        """``pixel_values [n_patches, patch_dim]`` -> ``[n_patches / merge^2, out_hidden]``."""
+        x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        cos, sin = self.rot_pos_emb(grid_thw, x.device)
+        lens = torch.tensor([h * w for t, h, w in grid_thw for _ in range(t)], dtype=torch.int32)
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+        cu[1:] = lens.cumsum(0)
+        cu = cu.to(x.device)
+        for blk in self.blocks:
+            x = blk(x, cu, cos, sin)
+        x = self.ln_q(x).reshape(-1, x.shape[-1] * self.merge ** 2)
+        x = torch.nn.functional.gelu(self.merger_fc1(x).float()).to(x.dtype)
+        return self.merger_fc2(x)
+
+
+class InternVisionModel(nn.Module):
+    """InternViT: class token + learned position embedding, LayerNorm blocks with layer scale, then pixel-shuffle
+    down-sampling and the two-layer projector of InternVL."""
+
+    def __init__(self, vc: dict, out_hidden: int, dtype, device):
+        super().__init__()
+        self.vc = vc
+        h = vc["hidden"]
+        self.patch_dim = vc.get("in_channels", 3) * vc["patch"] ** 2
+        self.patch_embed = ReplicatedLinear(self.patch_dim, h, bias=True, dtype=dtype, device=device)
+        self.tokens_per_image = (vc["image_size"] // vc["patch"]) ** 2
+        self.cls = param(1, h, dtype=dtype, device=device)
+        self.pos = param(self.tokens_per_image + 1, h, dtype=dtype, device=device)
+        self.blocks = nn.ModuleList([VisionBlock(vc, dtype, device) for _ in range(vc["depth"])])
+        self.ratio = vc.get("downsample", 0.5)
+        mh = int(h / self.ratio ** 2)
+        self.proj_norm = _Norm(mh, 1e-5, "layernorm", dtype, device)
+        self.proj_fc1 = ReplicatedLinear(mh, out_hidden, bias=True, dtype=dtype, device=device)
+        self.proj_fc2 = ReplicatedLinear(out_hidden, out_hidden, bias=True, dtype=dtype, device=device)
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw=None) -> torch.Tensor:
+        """``pixel_values [n_images, tokens_per_image, patch_dim]`` -> ``[n_images * tokens * ratio^2, out_hidden]``."""
+        n, L, _ = pixel_values.shape
+        x = self.patch_embed(pixel_values.reshape(n * L, -1).to(self.cls.dtype)).view(n, L, -1)
+        x = torch.cat([self.cls.unsqueeze(0).expand(n, 1, -1), x], 1) + self.pos.unsqueeze(0)
+        x = x.reshape(n * (L + 1), -1)
+        cu = (torch.arange(n + 1, dtype=torch.int32) * (L + 1)).to(x.device)
+        for blk in self.blocks:
+            x = blk(x, cu)
+        x = x.view(n, L + 1, -1)[:, 1:]
+        s = int(math.isqrt(L))
+        r = int(1 / self.ratio)
+        x = x.view(n, s // r, r, s // r, r, -1).permute(0, 1, 3, 2, 4, 5).reshape(n * (s // r) ** 2, -1)  # pixel shuffle
+        x = self.proj_fc1(self.proj_norm(x))
+        return self.proj_fc2(torch.nn.functional.gelu(x.float()).to(x.dtype))
+
+
+class MRopeAttention(GQAAttention):
+    """Decoder attention with 3-section rotary positions for steps that contain image tokens; text-only steps
+    (all decode steps) use the fused 1-D path with positions shifted by the request's M-RoPE delta."""
+
+    def forward(self, hidden):
+        ctx = get_forward_context()
+        pos3 = ctx.extras.get("mrope_positions")
+        if pos3 is None:
+            return super().forward(hidden)
+        md, cfg = ctx.attn, self.cfg
+        qkv = self.qkv_proj(hidden)
+        T = qkv.shape[0]
+        qs, ks = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        q, k, v = qkv[:, :qs].contiguous(), qkv[:, qs:qs + ks].contiguous(), qkv[:, qs + ks:].contiguous()
+        if self.q_norm is not None:
+            q = self.q_norm(q.view(-1, self.head_dim)).view(T, qs)
+            k = self.k_norm(k.view(-1, self.head_dim)).view(T, ks)
+        q, k = ops.mrope(q, k, pos3, self.cos_sin, self.head_dim, list(cfg.mrope_section), cfg.mrope_interleaved)
+        kv_cache = ctx.kv_caches[self.layer_idx]
+        ops.reshape_and_cache(k.view(T, self.num_kv_heads, self.head_dim), v.view(T, self.num_kv_heads, self.head_dim),
+                              kv_cache, md.slot_mapping)
+        o = ops.paged_attention(
+            q.view(T, self.num_heads, self.head_dim), kv_cache, md.block_tables, md.seq_lens, md.query_start_loc,
+            self.scale, md.max_query_len, md.max_seq_len, self.window, self.sinks, md.seq_lens_cpu,
+            md.query_start_loc_cpu, workspace=md.workspace, num_decodes=md.num_decodes,
+            decode_query_len=1 + md.num_spec_tokens, num_decode_tokens=md.num_decode_tokens)
+        return self.o_proj(o.reshape(T, qs))
+
+
+def get_mrope_positions(token_ids, grid_thw, image_token_id: int, merge: int):
+    """``[3, L]`` (t, h, w) positions and the delta ``next_position - L`` for a prompt whose image placeholders
+    (runs of ``image_token_id``) correspond to ``grid_thw`` in order."""
+    L = len(token_ids)
+    pos = torch.zeros(3, L, dtype=torch.long)
+    i, nxt, img = 0, 0, 0
+    while i < L:
+        if token_ids[i] == image_token_id and img < len(grid_thw):
+            t, h, w = grid_thw[img]
+            gh, gw = h // merge, w // merge
+            n = t * gh * gw
+            tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).reshape(-1)
+            hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).reshape(-1)
+            ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).reshape(-1)
+            n = min(n, L - i)
+            pos[:, i:i + n] = torch.stack([tt, hh, ww])[:, :n] + nxt
+            nxt += max(t, gh, gw)
+            i += n
+            img += 1
+        else:
+            pos[:, i] = nxt
+            nxt += 1
+            i += 1
+    return pos, nxt - L
+
+
+class _VLBase(nn.Module):
+    tower_cls = QwenVisionTransformer
+    uses_mrope = True
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        super().__init__()
+        from . import resolve_model_cls
+        self.cfg = cfg
+        text_arch = cfg.vision.get("text_architecture", "Qwen2ForCausalLM")
+        self.language_model = resolve_model_cls(text_arch)(cfg, device=device, dtype=dtype)
+        self.dtype, self.device = self.language_model.dtype, self.language_model.device
+        if self.uses_mrope:
+            for layer in self.language_model.layers.values():
+                layer.self_attn.__class__ = MRopeAttention
+        self.visual = self.tower_cls(cfg.vision, cfg.hidden_size, self.dtype, device)
+        self.image_token_id = cfg.vision.get("image_token_id", cfg.vocab_size - 1)
+        self.layers = self.language_model.layers
+        self.first_layer, self.last_layer = self.language_model.first_layer, self.language_model.last_layer
+
+    # ---- multimodal
+    @torch.inference_mode()
+    def embed_multimodal(self, pixel_values, grid_thw=None):
+        return self.visual(pixel_values.to(self.device), grid_thw)
+
+    def mm_metadata(self, token_ids, grid_thw):
+        """Rows of the prompt to overwrite, and M-RoPE positions when the decoder uses them."""
+        rows = [i for i, t in enumerate(token_ids) if t == self.image_token_id]
+        if not self.uses_mrope:
+            return rows, None, 0
+        pos, delta = get_mrope_positions(token_ids, grid_thw, self.image_token_id, self.visual.merge)
+        return rows, pos, delta
+
+    def forward(self, input_ids, hidden=None, residual=None):
+        lm = self.language_model
+        if hidden is None and lm.embed_tokens is not None:
+            hidden = lm.embed_tokens(input_ids)
+            ex = get_forward_context().extras
+            if ex.get("mm_dst") is not None:
+                hidden.index_copy_(0, ex["mm_dst"], ex["mm_src"].to(hidden.dtype))
+        return lm(input_ids, hidden, residual)
+
+    def compute_logits(self, hidden):
+        return self.language_model.compute_logits(hidden)
+
+    def kv_cache_spec(self, block_size: int):
+        return self.language_model.kv_cache_spec(block_size)
+
+    def init_random(self, seed: int = 0, std: float = 0.02):
+        self.language_model.init_random(seed, std)
+        g = torch.Generator(device=self.device).manual_seed(seed + 77)
+        for name, p in self.visual.named_parameters():
+            if name.endswith("weight") and p.dim() == 1 and "ls" not in name:
+                p.data.fill_(1.0)
+            elif name.endswith("bias"):
+                p.data.zero_()
+            else:
+                p.data.copy_((torch.randn(p.shape, generator=g, device=self.device, dtype=torch.float32) * std).to(p.dtype))
+
+    def finish_loading(self):
+        self.language_model.finish_loading()
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
+        text, loaded = [], set()
+        vis = dict(self.visual.named_parameters())
+        for name, w in weights:
+            v = self._vision_name(name)
+            if v is not None:
+                if v in vis:
+                    vis[v].data.copy_(w.reshape(vis[v].shape))
+                    loaded.add(name)
+                continue
+            text.append((name.replace("language_model.model.", "model.").replace("language_model.", ""), w))
+        return loaded | self.language_model.load_weights(text)
+
+    def _vision_name(self, name: str) -> Optional[str]:
+        raise NotImplementedError
+
+
+class QwenVLForConditionalGeneration(_VLBase):
+    """Qwen2-VL / Qwen2.5-VL / Qwen3-VL."""
+
+    _MAP = {"patch_embed.proj.weight": "patch_embed.weight", "attn.qkv.": "qkv.", "attn.proj.": "proj.",
+            "mlp.fc1.": "fc1.", "mlp.fc2.": "fc2.", "merger.ln_q.": "ln_q.", "merger.mlp.0.": "merger_fc1.",
+            "merger.mlp.2.": "merger_fc2."}
+
+    def _vision_name(self, name):
+        if not name.startswith("visual."):
+            return None
+        n = name[len("visual."):]
+        for a, b in self._MAP.items():
+            n = n.replace(a, b)
+        return n
+
+
+class InternVLChatModel(_VLBase):
+    """InternVL / Intern-S1: InternViT tower, pixel-shuffle projector, 1-D rotary decoder."""
+
+    tower_cls = InternVisionModel
+    uses_mrope = False
+
+    _MAP = {"vision_model.embeddings.patch_embedding.": "patch_embed.", "vision_model.embeddings.class_embedding": "cls",
+            "vision_model.embeddings.position_embedding": "pos", "vision_model.encoder.layers.": "blocks.",
+            ".attn.qkv.": ".qkv.", ".attn.proj.": ".proj.", ".mlp.fc1.": ".fc1.", ".mlp.fc2.": ".fc2.",
+            "mlp1.0.": "proj_norm.", "mlp1.1.": "proj_fc1.", "mlp1.3.": "proj_fc2."}
+
+    def _vision_name(self, name):
+        if not (name.startswith("vision_model.") or name.startswith("mlp1.")):
+            return None
+        n = name
+        for a, b in self._MAP.items():
+            n = n.replace(a, b)
+        return n

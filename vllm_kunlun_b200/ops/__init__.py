@@ -547,3 +547,67 @@ def lora_expand(h, lora_b, token_lora_ids, out, offset: int = 0, add: bool = Tru
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]
+
+
+# ----------------------------------------------------------------------------- vision-tower ops
+
+_SUPPORTED_HEAD_DIMS = (64, 128, 256)
+
+
+def varlen_attention(q, k, v, cu_seqlens, scale: Optional[float] = None, max_seqlen: Optional[int] = None):
+    """Bidirectional attention over packed sequences (ViT blocks; the reference calls
+    ``flash_attn_varlen_func`` / SDPA, ``models/qwen2_5_vl.py:356-393``, ``ops/attention/layer.py:121-180``).
+    ``q, k, v [T, H, D]``.  CUDA: K/V are laid out as pages of a scratch cache and the prefill kernel runs in
+    its bidirectional mode; head sizes are zero-padded to the next supported size (exact)."""
+    T, H, D = q.shape
+    scale = D ** -0.5 if scale is None else scale
+    if not q.is_cuda:
+        out = torch.empty_like(q)
+        for i in range(len(cu_seqlens) - 1):
+            s, e = int(cu_seqlens[i]), int(cu_seqlens[i + 1])
+            if e > s:
+                out[s:e] = _ra._attend(q[s:e], k[s:e], v[s:e], scale, None, None, None).to(q.dtype)
+        return out
+    Dp = next(d for d in _SUPPORTED_HEAD_DIMS if d >= D)
+    if Dp != D:
+        pad = (0, Dp - D)
+        q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+    bs = 64
+    cu = cu_seqlens.to(torch.int64)
+    lens = cu[1:] - cu[:-1]
+    nblk = (lens + bs - 1) // bs
+    first = torch.zeros_like(nblk)
+    first[1:] = nblk.cumsum(0)[:-1]
+    total_blocks = int(nblk.sum().item())
+    max_blocks = int(nblk.max().item())
+    tok = torch.arange(T, device=q.device)
+    seq_of = torch.searchsorted(cu[1:], tok, right=True)
+    slots = first[seq_of] * bs + (tok - cu[seq_of])
+    cache = torch.empty(total_blocks, 2, H, bs, Dp, dtype=q.dtype, device=q.device)
+    _c().reshape_and_cache(k.contiguous(), v.contiguous(), cache, slots)
+    bt = (first.unsqueeze(1) + torch.arange(max_blocks, device=q.device).unsqueeze(0)).clamp(max=total_blocks - 1).int()
+    out = torch.empty(T, H, Dp, dtype=q.dtype, device=q.device)
+    mq = int(lens.max().item()) if max_seqlen is None else max_seqlen
+    _c().paged_attention(out, q.contiguous(), cache, bt.contiguous(), lens.int(), cu.int(), None, None, None, max(mq, 17), 1,
+                         -1, scale, False)
+    return out[..., :D] if Dp != D else out
+
+
+def rope_vit(q, k, cos, sin):
+    """2-D rotary embedding of vision tokens (``xspeedgate_ops.rope_vit``, ``models/qwen2_vl.py:255``):
+    rotate-half with per-token ``cos / sin [T, D/2]`` shared by all heads."""
+    def rot(x):
+        xf = x.float()
+        d = xf.shape[-1] // 2
+        c, s = cos.float().unsqueeze(1), sin.float().unsqueeze(1)
+        x1, x2 = xf[..., :d], xf[..., d:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
+    return rot(q), rot(k)
+
+
+def layernorm(x, weight, bias, eps: float):
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), weight.float(), None if bias is None else bias.float(),
+                                          eps).to(x.dtype)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]
