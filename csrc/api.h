@@ -186,6 +186,32 @@ int b200_lora_shrink(float* out, const void* x, int64_t x_stride, const void* A,
 int b200_lora_expand(void* out, int64_t out_stride, int offset, const float* h, const void* B, const int* ids,
                      int64_t T_, int N, int r, int add, int dtype, cudaStream_t st);
 
+// ---- expert-parallel dispatch / combine over peer memory (see comm/ep_a2a.cu) --------------------
+typedef struct EpArgs {
+  void* peer[8];             // every rank's symmetric buffer (index = rank)
+  int64_t off_x, off_scale, off_ids, off_w, off_recv_flag, off_comb, off_comb_flag;
+  const void* x;             // local payload rows [T][x_row_bytes] (bf16, or fp8 already quantised)
+  const float* x_scale_t;    // fp8 payload: transposed scales [H/128][scale_stride], else null
+  int64_t x_row_bytes, scale_stride;
+  const int* topk_ids;       // [T][k] global expert ids
+  const float* topk_w;       // [T][k]
+  int* send_count;           // [R] zero between calls
+  int* sent_slot;            // [T][R]
+  int* recv_count;           // [R]
+  int* prev_count;           // [R]
+  int* ticket;               // [3] zero between calls
+  uint32_t* epoch;           // [1]
+  int* status;
+  int64_t T;
+  int rank, R, cap, H, k, E, row_bytes;
+  unsigned spin_limit;
+} EpArgs;
+int b200_ep_dispatch(const EpArgs* a, cudaStream_t st);
+int b200_ep_permute_scales(float* scale_t, int64_t s_stride, const float* recv_scale, const int* pos_of_pair,
+                           int64_t pairs, int k, int ngroups, cudaStream_t st);
+int b200_ep_combine(const EpArgs* a, const void* y_sorted, const int* pos_of_pair, void* out, const void* addend,
+                    int dtype, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

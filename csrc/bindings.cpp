@@ -248,17 +248,18 @@ std::vector<at::Tensor> moe_route(const at::Tensor& logits, const c10::optional<
 // Returns x_sorted [T*k, H], pos_of_pair [T*k], lod [E_local + 1].  `state` = int32 [2 * E_local] zero-initialised
 // scratch (counts | cursor) owned by the caller.
 std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& ids, const c10::optional<at::Tensor>& emap,
-                                    int64_t E_local, int64_t E_global, at::Tensor state) {
+                                    int64_t E_local, int64_t E_global, at::Tensor state, int64_t max_rows) {
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && ids.is_contiguous() && ids.scalar_type() == at::kInt);
   TORCH_CHECK(state.scalar_type() == at::kInt && state.numel() >= 2 * E_local);
   const int64_t T = x.size(0), k = ids.size(1), H = x.size(1);
-  auto xs = at::empty({T * k, H}, x.options());
+  if (max_rows <= 0 || max_rows > T * k) max_rows = T * k;  // rows beyond the bound are dropped (pos = -1)
+  auto xs = at::empty({max_rows, H}, x.options());
   auto pos = at::empty({T * k}, ids.options());
   auto lod = at::empty({E_local + 1}, ids.options());
   check(b200_moe_permute(xs.data_ptr(), pos.data_ptr<int>(), lod.data_ptr<int>(), state.data_ptr<int>(),
                          state.data_ptr<int>() + E_local, x.data_ptr(), ids.data_ptr<int>(),
                          emap.has_value() ? emap->data_ptr<int>() : nullptr, T, k, H, E_local, E_global, x.stride(0),
-                         T * k, dtype_code(x), stream()),
+                         max_rows, dtype_code(x), stream()),
         "moe_permute", 3);
   return {xs, pos, lod};
 }
@@ -665,6 +666,60 @@ void sigmoid_gate_mul(at::Tensor out, const at::Tensor& o, const at::Tensor& gat
                               dtype_code(o), stream()), "sigmoid_gate_mul");
 }
 
+// ------------------------------------------------------------------- expert-parallel dispatch / combine
+struct EpHandle {
+  EpArgs a;
+  at::Tensor state;  // int32: send_count[R] | recv_count[R] | prev_count[R] | ticket[3] | epoch[1] | status[1]
+  at::Tensor sent_slot;
+  EpHandle(std::vector<int64_t> peers, std::vector<int64_t> offs, int64_t rank, int64_t cap, int64_t H, int64_t k, int64_t E,
+           int64_t row_bytes, int64_t max_tokens, int64_t spin_limit, int64_t device) {
+    memset(&a, 0, sizeof(a));
+    const int R = (int)peers.size();
+    TORCH_CHECK(R <= 8 && offs.size() == 7);
+    for (int i = 0; i < R; ++i) a.peer[i] = reinterpret_cast<void*>(peers[i]);
+    a.off_x = offs[0]; a.off_scale = offs[1]; a.off_ids = offs[2]; a.off_w = offs[3]; a.off_recv_flag = offs[4];
+    a.off_comb = offs[5]; a.off_comb_flag = offs[6];
+    auto opts = at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device);
+    state = at::zeros({3 * R + 8}, opts);
+    sent_slot = at::full({std::max<int64_t>(max_tokens, 1), R}, -1, opts);
+    int* sp = state.data_ptr<int>();
+    a.send_count = sp; a.recv_count = sp + R; a.prev_count = sp + 2 * R; a.ticket = sp + 3 * R;
+    a.epoch = reinterpret_cast<uint32_t*>(sp + 3 * R + 3); a.status = sp + 3 * R + 4;
+    a.sent_slot = sent_slot.data_ptr<int>();
+    a.rank = rank; a.R = R; a.cap = cap; a.H = H; a.k = k; a.E = E; a.row_bytes = row_bytes; a.spin_limit = (unsigned)spin_limit;
+  }
+  // `cap` = per-call capacity of one source region (identical on all ranks, >= every rank's token count, <= allocated)
+  void dispatch(const at::Tensor& x, const c10::optional<at::Tensor>& scale_t, const at::Tensor& ids, const at::Tensor& w,
+                int64_t cap) {
+    TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && ids.is_contiguous() && ids.scalar_type() == at::kInt &&
+                w.is_contiguous() && w.scalar_type() == at::kFloat && ids.size(1) == a.k);
+    TORCH_CHECK(x.size(0) <= cap && cap <= a.cap && x.size(1) * (int64_t)x.element_size() == a.row_bytes);
+    TORCH_CHECK((x.stride(0) * x.element_size()) % 16 == 0);
+    EpArgs b = a;
+    b.x = x.data_ptr(); b.x_row_bytes = x.stride(0) * x.element_size();
+    b.x_scale_t = scale_t.has_value() ? scale_t->data_ptr<float>() : nullptr;
+    b.scale_stride = scale_t.has_value() ? scale_t->stride(0) : 0;
+    b.topk_ids = ids.data_ptr<int>(); b.topk_w = w.data_ptr<float>(); b.T = x.size(0); b.cap = (int)cap;
+    check(b200_ep_dispatch(&b, stream()), "ep_dispatch", 2);
+  }
+  void permute_scales(at::Tensor scale_t, const at::Tensor& recv_scale, const at::Tensor& pos) {
+    check(b200_ep_permute_scales(scale_t.data_ptr<float>(), scale_t.stride(0), recv_scale.data_ptr<float>(), pos.data_ptr<int>(),
+                                 pos.numel(), a.k, a.H / 128, stream()), "ep_permute_scales");
+  }
+  void combine(const at::Tensor& y_sorted, const at::Tensor& pos, at::Tensor out, const c10::optional<at::Tensor>& addend,
+               int64_t cap) {
+    TORCH_CHECK(y_sorted.is_contiguous() && pos.is_contiguous() && out.is_contiguous() && out.size(1) == a.H);
+    TORCH_CHECK(pos.numel() == (int64_t)a.R * cap * a.k && cap <= a.cap);
+    TORCH_CHECK(!addend.has_value() || (addend->is_contiguous() && addend->scalar_type() == out.scalar_type()));
+    EpArgs b = a;
+    b.T = out.size(0); b.cap = (int)cap;
+    check(b200_ep_combine(&b, y_sorted.data_ptr(), pos.data_ptr<int>(), out.data_ptr(), opt_ptr(addend), dtype_code(out),
+                          stream()), "ep_combine", 2);
+  }
+  int64_t status() { return state[3 * a.R + 4].item<int>(); }
+  at::Tensor recv_count() { return state.slice(0, a.R, 2 * a.R); }
+};
+
 void lora_shrink(at::Tensor out, const at::Tensor& x, const at::Tensor& A, const at::Tensor& ids, double scale) {
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && A.dim() == 3 && A.is_contiguous() && out.scalar_type() == at::kFloat &&
               out.is_contiguous() && A.scalar_type() == x.scalar_type());
@@ -689,7 +744,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_status", &gemm_status);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("moe_route", &moe_route);
-  m.def("moe_permute", &moe_permute);
+  m.def("moe_permute", &moe_permute, py::arg("x"), py::arg("ids"), py::arg("emap"), py::arg("E_local"),
+        py::arg("E_global"), py::arg("state"), py::arg("max_rows") = 0);
   m.def("moe_unpermute", &moe_unpermute);
   m.def("quant_fp8_group", &quant_fp8_group);
   m.def("gemm_clear_tmap_cache", &gemm_clear_tmap_cache);
@@ -736,4 +792,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("rs_norm_ag", &rs_norm_ag);
   m.def("sp_wait", &sp_wait);
+  py::class_<EpHandle>(m, "EpHandle")
+      .def(py::init<std::vector<int64_t>, std::vector<int64_t>, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                    int64_t, int64_t>())
+      .def("dispatch", &EpHandle::dispatch)
+      .def("permute_scales", &EpHandle::permute_scales)
+      .def("combine", &EpHandle::combine)
+      .def("status", &EpHandle::status)
+      .def("recv_count", &EpHandle::recv_count);
 }

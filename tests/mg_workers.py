@@ -65,13 +65,152 @@ def engine(rank, world, fused):
     return {"tokens": [o.token_ids for o in outs], "peer_launches": launches}
 
 
+def ep_a2a(rank, world, fp8):
+    """Dispatch / combine over peer memory against the library baseline and the dense oracle."""
+    import time
+
+    from vllm_kunlun_b200 import ops
+    from vllm_kunlun_b200.models.moe import _quant_block_device
+    from vllm_kunlun_b200.parallel import state as ps
+    from vllm_kunlun_b200.parallel.ep_a2a import EPAll2All, EPLibraryBaseline
+    fp8 = bool(int(fp8))
+    ps.init_distributed("nccl")
+    st = ps.initialize_model_parallel(tp=world, device=f"cuda:{rank}")
+    dev = f"cuda:{rank}"
+    H, I, E, k, cap = 2048, 768, 128, 8, 2048
+    el = E // world
+    g = torch.Generator(device=dev).manual_seed(1234)  # same weights on every rank, each keeps its slice
+    w13 = (torch.randn(E, 2 * I, H, device=dev, generator=g) * 0.05)
+    w2 = (torch.randn(E, H, I, device=dev, generator=g) * 0.05)
+    s13 = s2 = None
+    if fp8:
+        q13, q2, s13l, s2l = [], [], [], []
+        for e in range(rank * el, (rank + 1) * el):
+            a, b = _quant_block_device(w13[e])
+            c, d = _quant_block_device(w2[e])
+            q13.append(a), s13l.append(b), q2.append(c), s2l.append(d)
+        lw13, lw2, s13, s2 = torch.stack(q13), torch.stack(q2), torch.stack(s13l), torch.stack(s2l)
+    else:
+        lw13 = w13[rank * el:(rank + 1) * el].to(torch.bfloat16).contiguous()
+        lw2 = w2[rank * el:(rank + 1) * el].to(torch.bfloat16).contiguous()
+    ep = EPAll2All(st.tp_comm, cap, H, k, E, fp8_payload=fp8)
+    base = EPLibraryBaseline(st.tp_comm.group, rank, world, E)
+    worst = 0.0
+    for it, T in enumerate([64, 1, 300, 2048, 16, 16]):
+        gr = torch.Generator(device=dev).manual_seed(77 * it + rank)
+        x = torch.randn(T, H, device=dev, generator=gr).to(torch.bfloat16)
+        logits = torch.randn(T, E, device=dev, generator=gr)
+        wts, ids = ops.moe_route(logits, k, "softmax", True)
+        add = torch.randn(T, H, device=dev, generator=gr).to(torch.bfloat16) if it % 2 else None
+        got = ep.moe(x, ids, wts, lw13, lw2, "silu", None, None, s13, s2, addend=add, bound=T if it % 3 else None)
+        want = base.moe(x, ids, wts, lw13, lw2, "silu", None, None, s13, s2, addend=add)
+        torch.cuda.synchronize()
+        ep.check_status()
+        err = (got.float() - want.float()).abs().max().item() / (want.float().abs().max().item() + 1e-6)
+        worst = max(worst, err)
+    # uneven token counts, including a rank with none
+    T = 0 if rank == 0 else 40 + rank
+    gr = torch.Generator(device=dev).manual_seed(999 + rank)
+    x = torch.randn(T, H, device=dev, generator=gr).to(torch.bfloat16)
+    wts, ids = ops.moe_route(torch.randn(T, E, device=dev, generator=gr), k, "softmax", True) if T else (
+        torch.zeros(0, k, device=dev), torch.zeros(0, k, dtype=torch.int32, device=dev))
+    got = ep.moe(x, ids, wts, lw13, lw2, "silu", None, None, s13, s2, bound=40 + world)
+    torch.cuda.synchronize()
+    ep.check_status()
+    if T and not fp8:
+        dense = ops.fused_moe(x, w13.to(torch.bfloat16), w2.to(torch.bfloat16), wts, ids)
+        worst = max(worst, (got.float() - dense.float()).abs().max().item() / (dense.float().abs().max().item() + 1e-6))
+    # timing, device clock, max over ranks
+    res = {"worst_rel_err": worst}
+    for T in (16, 1024):
+        gr = torch.Generator(device=dev).manual_seed(5 + rank)
+        x = torch.randn(T, H, device=dev, generator=gr).to(torch.bfloat16)
+        wts, ids = ops.moe_route(torch.randn(T, E, device=dev, generator=gr), k, "softmax", True)
+        for name, impl in (("a2a", ep), ("lib", base)):
+            kw = {"bound": T} if name == "a2a" else {}
+            for _ in range(5):
+                impl.moe(x, ids, wts, lw13, lw2, "silu", None, None, s13, s2, **kw)
+            torch.cuda.synchronize()
+            dist.barrier(device_ids=[rank])
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                impl.moe(x, ids, wts, lw13, lw2, "silu", None, None, s13, s2, **kw)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 20], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[f"{name}_ms_T{T}"] = round(t.item(), 4)
+    ep.check_status()
+    return res
+
+
+def ep_block(rank, world):
+    """One sparse-MoE block on replicated tokens: dispatch / combine path against the replicated-token path."""
+    os.environ["B200_EP_A2A"] = "1"
+    os.environ["B200_EP_A2A_MAX_TOKENS"] = "1024"
+    from vllm_kunlun_b200.config import qwen3_30b_a3b, tiny
+    from vllm_kunlun_b200.models.moe import SparseMoEBlock
+    from vllm_kunlun_b200.parallel import state as ps
+    ps.init_distributed("nccl")
+    st = ps.initialize_model_parallel(tp=world, ep=True, device=f"cuda:{rank}")
+    dev = f"cuda:{rank}"
+    cfg = tiny(qwen3_30b_a3b(fp8=False), num_layers=1, vocab_size=2048, hidden_size=1024, num_heads=8, num_kv_heads=2,
+               head_dim=128, intermediate_size=1024, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256)
+    worst = 0.0
+    with torch.inference_mode():
+        blk = SparseMoEBlock(cfg, torch.bfloat16, dev)
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        for p in blk.parameters():
+            p.data.copy_((torch.randn(p.shape, device=dev, generator=g) * 0.05).to(p.dtype))
+        dist.broadcast(blk.gate.weight.data, 0)
+        for T in (253, 4, 3, 2, 700):
+            x = torch.randn(T, 1024, device=dev, generator=torch.Generator(device=dev).manual_seed(T)).to(torch.bfloat16)
+            a2a = blk._a2a(x)
+            assert a2a is not None
+            ya = blk._forward_a2a(x, a2a).float()
+            os.environ["B200_EP_A2A"] = "0"
+            yb = blk(x).float()
+            os.environ["B200_EP_A2A"] = "1"
+            dist.all_reduce(ya)
+            dist.all_reduce(yb)
+            torch.cuda.synchronize()
+            a2a.check_status()
+            worst = max(worst, (ya - yb).abs().max().item() / (yb.abs().max().item() + 1e-6))
+    return {"worst_rel_err": worst}
+
+
+def ep_engine(rank, world, a2a):
+    """Expert-parallel MoE engine: replicated-token path vs the dispatch / combine path, eager and captured."""
+    os.environ["B200_EP_A2A_MAX_TOKENS"] = "1024"
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    from vllm_kunlun_b200.config import qwen3_30b_a3b, tiny
+    cfg = tiny(qwen3_30b_a3b(fp8=False), num_layers=2, vocab_size=2048, hidden_size=1024, num_heads=8, num_kv_heads=2,
+               head_dim=128, intermediate_size=1024, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256,
+               max_position=2048)
+    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (150, 33, 70)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    res = {}
+    for name, env, eager in (("a2a_eager", "1", True), ("rep_eager", "0", True), ("a2a_graph", "1", False)):
+        os.environ["B200_EP_A2A"] = env
+        llm = LLM(cfg, device="cuda", tensor_parallel_size=world, enable_expert_parallel=True, block_size=64,
+                  max_model_len=512, max_num_seqs=4, num_gpu_blocks=64, seed=11, enforce_eager=eager)
+        res[name] = [o.token_ids for o in llm.generate(prompts, sp)]
+        torch.cuda.synchronize()
+        a2a = getattr(llm.engine.pstate, "ep_a2a", None)
+        if env == "1":
+            assert a2a is not None, "dispatch / combine path was not taken"
+            a2a.check_status()
+    return res
+
+
 if __name__ == "__main__":
     name, out = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     code = 0
     try:
-        res = {"allreduce": allreduce, "engine": engine}[name](rank, world, *sys.argv[3:])
+        res = {"allreduce": allreduce, "engine": engine, "ep_a2a": ep_a2a, "ep_engine": ep_engine, "ep_block": ep_block}[name](rank, world, *sys.argv[3:])
     except Exception:  # noqa: BLE001
         import traceback
         res = {"error": traceback.format_exc()}

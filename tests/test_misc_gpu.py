@@ -265,3 +265,55 @@ def test_lora_engine_on_gpu():
     assert outs[0] == outs[1]
     base = LLM(cfg, device="cuda", enforce_eager=True, seed=2, **{k: v for k, v in kw.items() if "lora" not in k})
     assert [o.token_ids for o in base.generate(prompts[2:], sp)] == outs[0][2:]
+
+
+@pytest.mark.parametrize("D", [64, 80, 128])
+def test_varlen_bidirectional_attention(D):
+    torch.manual_seed(8)
+    H = 4
+    cu = torch.tensor([0, 100, 100, 357, 400], dtype=torch.int32)
+    T = int(cu[-1])
+    q, k, v = (torch.randn(T, H, D).to(torch.bfloat16) for _ in range(3))
+    want = ops.varlen_attention(q, k, v, cu)
+    got = ops.varlen_attention(q.to(DEV), k.to(DEV), v.to(DEV), cu.to(DEV))
+    torch.testing.assert_close(got.cpu().float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_qwen_vl_engine_on_gpu():
+    import dataclasses
+
+    from test_vision_cpu import IMG, _qwen_vl
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    cfg = _qwen_vl()
+    cfg = dataclasses.replace(cfg, hidden_size=512, num_heads=8, num_kv_heads=2, head_dim=64, rotary_dim=64,
+                              intermediate_size=1024, vocab_size=2048, dtype="bfloat16", mrope_section=(8, 12, 12))
+    cfg.vision = dict(cfg.vision, hidden=128, heads=2, intermediate=256, patch=4, image_token_id=2047)
+    grid = [(1, 16, 8)]
+    px = torch.randn(128, 3 * 1 * 4 * 4, generator=torch.Generator().manual_seed(0))
+    prompt = [5, 6, 7] + [2047] * 32 + [9, 10, 11, 12]
+    kw = dict(block_size=16, max_model_len=256, max_num_seqs=4, num_gpu_blocks=64)
+    gpu = LLM(cfg, device="cuda", enforce_eager=True, **kw)
+    cpu = LLM(dataclasses.replace(cfg, dtype="float32"), device="cpu", **kw)
+    sd = {k: v.float().cpu() for k, v in gpu.engine.runner.model.state_dict().items()}
+    with torch.inference_mode():
+        cpu.engine.runner.model.load_state_dict(sd)
+    mm = {"pixel_values": px, "image_grid_thw": grid}
+    ea = gpu.engine.runner.model.embed_multimodal(px, grid).float().cpu()
+    eb = cpu.engine.runner.model.embed_multimodal(px, grid).float()
+    assert torch.nn.functional.cosine_similarity(ea.flatten(), eb.flatten(), dim=0) > 0.99
+
+    def logits(llm):
+        from vllm_kunlun_b200.attention.metadata import ForwardContext, set_forward_context
+        eng = llm.engine
+        eng.add_request(prompt, SamplingParams(max_tokens=1), multi_modal_data=mm)
+        sched = eng.scheduler.schedule()
+        md, ids, _ = eng.runner.prepare(sched)
+        ctx = ForwardContext(md, eng.runner.kv_caches, eng.pstate, extras=eng.runner._step_extras)
+        with torch.inference_mode(), set_forward_context(ctx):
+            h, _ = eng.runner.model(ids)
+            return eng.runner.model.compute_logits(h[-1:]).float().cpu()
+
+    cos = torch.nn.functional.cosine_similarity(logits(gpu), logits(cpu)).item()
+    assert cos > 0.99, cos
+    out = LLM(cfg, device="cuda", **kw).generate([prompt], SamplingParams(max_tokens=5, ignore_eos=True), multi_modal_data=mm)
+    assert len(out[0].token_ids) == 5

@@ -23,6 +23,10 @@ _ENV: dict[str, Callable[[], Any]] = {
     "B200_PEER_COLLECTIVES": lambda: os.environ.get("B200_PEER_COLLECTIVES", "1") != "0",
     # exponential-race sampling with a cached noise tensor (the reference's FAST_RANDOM_SAMPLE)
     "B200_FAST_RANDOM_SAMPLE": lambda: os.environ.get("B200_FAST_RANDOM_SAMPLE", "0") == "1",
+    # expert parallelism: route each rank's slice of the tokens through the dispatch / combine kernels instead of
+    # computing local experts over replicated tokens; capacity = tokens per step the exchange buffers are sized for
+    "B200_EP_A2A": lambda: os.environ.get("B200_EP_A2A", "0") == "1",
+    "B200_EP_A2A_MAX_TOKENS": lambda: int(os.environ.get("B200_EP_A2A_MAX_TOKENS", "8192")),
     # bounded-wait budget of cross-GPU spins (iterations)
     "B200_SPIN_LIMIT": lambda: int(os.environ.get("B200_SPIN_LIMIT", str(1 << 22))),
 }

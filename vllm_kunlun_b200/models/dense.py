@@ -189,15 +189,26 @@ class DenseForCausalLM(nn.Module):
     def init_random(self, seed: int = 0, std: float = 0.02):
         """Seeded ``N(0, std)`` weights, norm weights = 1, biases/sinks ~ N(0, std)."""
         g = torch.Generator(device=self.device).manual_seed(seed + 1000 * get_state().tp_rank)
+        g_rep = torch.Generator(device=self.device).manual_seed(seed + 7)  # replicated parameters: same on all ranks
+        replicated = self.replicated_param_names()
         for name, p in self.named_parameters():
             if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
                 continue
             if name.endswith("norm.weight") or "layernorm.weight" in name:
                 p.data.fill_(0.0 if self.cfg.gemma_norm else 1.0)
             else:
-                p.data.copy_((torch.randn(p.shape, generator=g, device=self.device, dtype=torch.float32) * std)
+                gen = g_rep if name in replicated else g
+                p.data.copy_((torch.randn(p.shape, generator=gen, device=self.device, dtype=torch.float32) * std)
                              .to(p.dtype))
         self.finish_loading()
+
+    def replicated_param_names(self) -> set:
+        from .layers import ReplicatedLinear
+        out = set()
+        for mname, m in self.named_modules():
+            if isinstance(m, ReplicatedLinear):
+                out.update(f"{mname}.{n}" for n, _ in m.named_parameters(recurse=False))
+        return out
 
     def finish_loading(self):
         for m in self.modules():

@@ -110,8 +110,53 @@ class SparseMoEBlock(nn.Module):
         self.shared_expert_gate = (ReplicatedLinear(cfg.hidden_size, 1, dtype=dtype, device=device)
                                    if cfg.shared_expert_gate else None)
 
+    def _a2a(self, x):
+        """The dispatch / combine exchange, created on first use when enabled (expert-parallel CUDA runs only)."""
+        from .. import envs
+        st = get_state()
+        if not (self.experts.use_ep and x.is_cuda and envs.B200_EP_A2A and x.dtype == torch.bfloat16):
+            return None
+        if getattr(st, "ep_a2a", None) is None:
+            if st.tp_comm is None or st.ep_size != st.tp_size:
+                return None
+            from ..parallel.ep_a2a import EPAll2All
+            cap = -(-envs.B200_EP_A2A_MAX_TOKENS // st.ep_size)
+            st.ep_a2a = EPAll2All(st.tp_comm, cap, self.cfg.hidden_size, self.cfg.num_experts_per_tok, self.cfg.num_experts,
+                                  fp8_payload=self.experts.fp8, spin_limit=envs.B200_SPIN_LIMIT)
+        a2a = st.ep_a2a
+        chunk = -(-x.shape[0] // st.ep_size)
+        return a2a if (x.shape[0] >= st.ep_size and chunk <= a2a.cap) else None
+
+    def _forward_a2a(self, x, a2a):
+        """Sequence-parallel MoE: this rank routes and dispatches only its slice of the (replicated) tokens; the
+        routed result goes into its rows of the partial output, and the reduction fused into the next norm - which
+        the shared-expert partial needs anyway - completes the other ranks' rows."""
+        cfg, st, ex = self.cfg, get_state(), self.experts
+        T = x.shape[0]
+        chunk = -(-T // st.ep_size)
+        lo, hi = min(T, st.ep_rank * chunk), min(T, (st.ep_rank + 1) * chunk)
+        xl = x[lo:hi]
+        if hi > lo:
+            w, ids = ops.moe_route(self.gate(xl), cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
+                                   self.e_score_correction_bias, cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor)
+        else:
+            w = torch.zeros(0, cfg.num_experts_per_tok, dtype=torch.float32, device=x.device)
+            ids = torch.zeros(0, cfg.num_experts_per_tok, dtype=torch.int32, device=x.device)
+        routed = a2a.moe(xl, ids, w, ex.w13, ex.w2, ex.act, ex.b13, ex.b2, ex.w13_scale, ex.w2_scale, bound=chunk)
+        if self.shared_experts is not None:
+            out = self.shared_experts(x)
+            if self.shared_expert_gate is not None:
+                out = out * torch.sigmoid(self.shared_expert_gate(x).float()).to(out.dtype)
+        else:
+            out = torch.zeros_like(x)
+        out[lo:hi] += routed
+        return out
+
     def forward(self, x):
         cfg = self.cfg
+        a2a = self._a2a(x)
+        if a2a is not None:
+            return self._forward_a2a(x, a2a)
         logits = self.gate(x)
         w, ids = ops.moe_route(logits, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
                                self.e_score_correction_bias, cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor)
@@ -145,8 +190,11 @@ class MoEForCausalLM(DenseForCausalLM):
         from ..quantization.fp8 import Fp8BlockLinearMethod
         g = torch.Generator(device=self.device).manual_seed(seed + 1000 * get_state().tp_rank)
 
-        def draw(shape):
-            return torch.randn(shape, generator=g, device=self.device, dtype=torch.float32) * std
+        g_rep = torch.Generator(device=self.device).manual_seed(seed + 7)  # replicated parameters (router, ...)
+        replicated = self.replicated_param_names()
+
+        def draw(shape, gen=None):
+            return torch.randn(shape, generator=gen or g, device=self.device, dtype=torch.float32) * std
 
         done = set()
         for mname, m in self.named_modules():
@@ -171,7 +219,7 @@ class MoEForCausalLM(DenseForCausalLM):
             elif name.endswith("e_score_correction_bias"):
                 p.data.zero_()
             else:
-                p.data.copy_(draw(p.shape).to(p.dtype))
+                p.data.copy_(draw(p.shape, g_rep if name in replicated else None).to(p.dtype))
         self.finish_loading()
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
