@@ -203,7 +203,7 @@ def test_hybrid_engine_on_gpu():
     from vllm_kunlun_b200 import LLM, SamplingParams
     from vllm_kunlun_b200.config import qwen3_next_80b_a3b, tiny
     cfg = tiny(qwen3_next_80b_a3b(), num_layers=4, vocab_size=2048, hidden_size=512, num_heads=8, num_kv_heads=2,
-               head_dim=64, rotary_dim=16, intermediate_size=512, num_experts=8, num_experts_per_tok=2,
+               head_dim=64, rotary_dim=16, intermediate_size=512, num_experts=4, num_experts_per_tok=4,  # no routing ties
                moe_intermediate_size=256, gdn_num_k_heads=2, gdn_num_v_heads=4, gdn_head_k_dim=64, gdn_head_v_dim=64,
                max_position=1024)
     kw = dict(block_size=16, max_model_len=512, max_num_seqs=4, num_gpu_blocks=128, max_num_batched_tokens=256)
@@ -285,7 +285,7 @@ def test_qwen_vl_engine_on_gpu():
     from test_vision_cpu import IMG, _qwen_vl
     from vllm_kunlun_b200 import LLM, SamplingParams
     cfg = _qwen_vl()
-    cfg = dataclasses.replace(cfg, hidden_size=512, num_heads=8, num_kv_heads=2, head_dim=64, rotary_dim=64,
+    cfg = dataclasses.replace(cfg, hidden_size=512, num_heads=8, num_kv_heads=2, head_dim=64, v_head_dim=64, rotary_dim=64,
                               intermediate_size=1024, vocab_size=2048, dtype="bfloat16", mrope_section=(8, 12, 12))
     cfg.vision = dict(cfg.vision, hidden=128, heads=2, intermediate=256, patch=4, image_token_id=2047)
     grid = [(1, 16, 8)]
