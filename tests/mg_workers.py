@@ -145,6 +145,27 @@ def ep_a2a(rank, world, fp8):
     return res
 
 
+def dcp_engine(rank, world):
+    """MLA engine with the latent cache interleaved over the ranks (decode context parallel) vs plain TP."""
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    from vllm_kunlun_b200.config import RopeScaling, deepseek_v3, tiny
+    cfg = tiny(deepseek_v3(fp8=False), num_layers=3, first_dense_layers=1, vocab_size=1024, hidden_size=512,
+               num_heads=16, num_kv_heads=16, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+               qk_rope_head_dim=64, v_head_dim=128, head_dim=192, rotary_dim=64, intermediate_size=1024,
+               num_experts=16, num_experts_per_tok=16, moe_intermediate_size=256, n_group=1, topk_group=1,
+               max_position=2048, rope_scaling=RopeScaling(type="yarn", factor=4.0, original_max_position=512,
+                                                           mscale=1.0, mscale_all_dim=1.0), num_mtp_layers=0)
+    prompts = [torch.randint(0, 1024, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (150, 33, 70)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    res = {}
+    for name, dcp, eager in (("tp", 1, True), ("dcp_eager", world, True), ("dcp_graph", world, False)):
+        llm = LLM(cfg, device="cuda", tensor_parallel_size=world, decode_context_parallel_size=dcp, block_size=64,
+                  max_model_len=512, max_num_seqs=4, num_gpu_blocks=32, seed=3, enforce_eager=eager)
+        res[name] = [o.token_ids for o in llm.generate(prompts, sp)]
+        torch.cuda.synchronize()
+    return res
+
+
 def ep_block(rank, world):
     """One sparse-MoE block on replicated tokens: dispatch / combine path against the replicated-token path."""
     os.environ["B200_EP_A2A"] = "1"
@@ -210,7 +231,7 @@ if __name__ == "__main__":
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     code = 0
     try:
-        res = {"allreduce": allreduce, "engine": engine, "ep_a2a": ep_a2a, "ep_engine": ep_engine, "ep_block": ep_block}[name](rank, world, *sys.argv[3:])
+        res = {"allreduce": allreduce, "engine": engine, "ep_a2a": ep_a2a, "ep_engine": ep_engine, "ep_block": ep_block, "dcp_engine": dcp_engine}[name](rank, world, *sys.argv[3:])
     except Exception:  # noqa: BLE001
         import traceback
         res = {"error": traceback.format_exc()}

@@ -79,3 +79,12 @@ def test_ep_engine_a2a_vs_replicated_2gpu():
     # the two paths add the expert outputs in different orders (bf16): most greedy tokens agree
     assert sum(x == y for x, y in zip(flat["a2a_eager"], flat["rep_eager"])) >= 0.7 * n, flat
     assert sum(x == y for x, y in zip(flat["a2a_graph"], flat["a2a_eager"])) >= 0.9 * n, flat
+
+
+def test_dcp_engine_2gpu():
+    a = _run(2, "dcp_engine", timeout=600)
+    assert a[0] == a[1], "ranks disagree"
+    flat = {k: sum(v, []) for k, v in a[0].items()}
+    n = len(flat["tp"])
+    assert sum(x == y for x, y in zip(flat["dcp_eager"], flat["tp"])) >= 0.7 * n, flat
+    assert sum(x == y for x, y in zip(flat["dcp_graph"], flat["dcp_eager"])) >= 0.9 * n, flat

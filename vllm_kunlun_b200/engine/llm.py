@@ -33,7 +33,8 @@ class LLMEngine:
             fused_collectives=cfg.parallel.fused_collectives) \
             if torch.distributed.is_initialized() else pstate_mod.get_state()
         self.runner = ModelRunner(self.cfg, self.pstate)
-        self.pool = BlockPool(self.runner.num_blocks, self.cfg.cache.block_size, self.cfg.cache.enable_prefix_caching)
+        # with decode context parallelism a block spans block_size tokens on EACH rank of the DCP group
+        self.pool = BlockPool(self.runner.num_blocks, self.runner.tokens_per_block, self.cfg.cache.enable_prefix_caching)
         self.scheduler = Scheduler(
             self.pool, self.cfg.scheduler.max_num_seqs, self.cfg.scheduler.max_num_batched_tokens,
             self.cfg.scheduler.max_model_len, self.cfg.scheduler.enable_chunked_prefill,
@@ -155,7 +156,7 @@ class LLM:
                  enforce_eager: bool = False, speculative_config: Optional[dict] = None, seed: int = 0,
                  enable_chunked_prefill: bool = True, kv_cache_dtype: str = "auto",
                  fused_collectives: bool = True, tokenizer=None, enable_lora: bool = False, max_loras: int = 4,
-                 max_lora_rank: int = 16):
+                 max_lora_rank: int = 16, decode_context_parallel_size: int = 1):
         import os
         weights = None
         if isinstance(model, ModelConfig):
@@ -182,6 +183,7 @@ class LLM:
                               enable_prefix_caching=enable_prefix_caching),
             parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size,
                                     enable_expert_parallel=enable_expert_parallel,
+                                    decode_context_parallel_size=decode_context_parallel_size,
                                     fused_collectives=fused_collectives),
             scheduler=SchedulerConfig(max_num_seqs, max_num_batched_tokens, max_model_len, enable_chunked_prefill),
             speculative=spec,

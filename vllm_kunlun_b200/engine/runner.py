@@ -61,9 +61,13 @@ class ModelRunner:
             else:
                 self.model.init_random(cfg.seed, cfg.init_std)
         self.block_size = cfg.cache.block_size
+        self.dcp, self.dcp_rank = self.pstate.dcp_size, self.pstate.dcp_rank
+        if self.dcp > 1:
+            assert m.use_mla and not m.index_topk, "decode context parallelism serves dense MLA models"
+        self.tokens_per_block = self.block_size * self.dcp
         self.max_bs = cfg.scheduler.max_num_seqs
         self.max_tokens = cfg.scheduler.max_num_batched_tokens
-        self.max_blocks_per_seq = cdiv(cfg.scheduler.max_model_len, self.block_size)
+        self.max_blocks_per_seq = cdiv(cfg.scheduler.max_model_len, self.tokens_per_block)
         self.num_spec = cfg.speculative.num_speculative_tokens
         self.sampler = Sampler(m.vocab_size, self.device, seed=cfg.seed)
         self.num_blocks = self._plan_num_blocks()
@@ -291,7 +295,11 @@ class ModelRunner:
             p = np.arange(c, c + n)
             pos[t:t + n] = p
             blocks = np.asarray(r.block_ids, dtype=np.int64)
-            slots[t:t + n] = blocks[p // bs] * bs + p % bs
+            if self.dcp > 1:  # token p lives on rank p % dcp at local position p // dcp
+                vb = bs * self.dcp
+                slots[t:t + n] = np.where(p % self.dcp == self.dcp_rank, blocks[p // vb] * bs + (p % vb) // self.dcp, -1)
+            else:
+                slots[t:t + n] = blocks[p // bs] * bs + p % bs
             bt[b, :len(r.block_ids)] = r.block_ids
             bt[b, len(r.block_ids):] = 0
             seq_lens[b] = c + n

@@ -141,6 +141,9 @@ class MLAAttention(nn.Module):
             slots = ops.convert_req_index_to_global_index(md.req_id_per_token, md.block_tables, local_idx,
                                                           kv_cache.shape[1])
             o = ops.sparse_mla_attention(qf.contiguous(), kv_cache, slots, self.scale, self.rank)
+        elif ctx.pstate.dcp_size > 1:
+            from ..attention.dcp import dcp_mla_attention
+            o = dcp_mla_attention(qf.contiguous(), kv_cache, md, self.scale, self.rank, ctx.pstate)
         else:
             o = ops.mla_attention(qf.contiguous(), kv_cache, md.block_tables, md.seq_lens, md.query_start_loc,
                                   self.scale, self.rank, md.max_query_len, md.max_seq_len, md.seq_lens_cpu,

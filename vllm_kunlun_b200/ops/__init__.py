@@ -340,16 +340,18 @@ def bmm_heads(x, w):
 
 
 def mla_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float, kv_lora_rank: int,
-                  max_query_len: int, max_seq_len: int, seq_lens_cpu=None, query_start_loc_cpu=None, workspace=None):
+                  max_query_len: int, max_seq_len: int, seq_lens_cpu=None, query_start_loc_cpu=None, workspace=None,
+                  return_lse: bool = False):
     """Weight-absorbed MLA attention over the latent cache (decode, spec-verify and causal prefill):
-    ``q [T, N, 576]`` -> ``out [T, N, 512]``."""
+    ``q [T, N, 576]`` -> ``out [T, N, 512]`` (and the natural-log LSE ``[T, N]`` when asked; rows without any
+    visible key give zeros and ``-inf``)."""
     if q.is_cuda:
         from .mla_cuda import mla_attention_cuda
         return mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank,
-                                  max_query_len, max_seq_len, workspace)
+                                  max_query_len, max_seq_len, workspace, return_lse=return_lse)
     sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
     ql = query_start_loc if query_start_loc_cpu is None else query_start_loc_cpu
-    return _ra.mla_decode(q, kv_cache, block_tables, sl, ql, scale, kv_lora_rank)
+    return _ra.mla_decode(q, kv_cache, block_tables, sl, ql, scale, kv_lora_rank, return_lse=return_lse)
 
 
 def sparse_mla_attention(q, kv_cache, indices, scale: float, d_v: int = 512):

@@ -26,7 +26,7 @@ def _ws(T, N, splits, device):
 
 
 def mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank, max_query_len,
-                       max_seq_len, workspace=None, req_of_token=None):
+                       max_seq_len, workspace=None, req_of_token=None, return_lse: bool = False):
     assert kv_lora_rank == 512 and q.shape[-1] == 576 and kv_cache.dtype == q.dtype
     T, N, _ = q.shape
     if req_of_token is None:
@@ -35,10 +35,16 @@ def mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, sca
                                                output_size=T)
     out = torch.empty(T, N, 512, dtype=q.dtype, device=q.device)
     splits = _splits(-(-N // 16) * T, -(-max_seq_len // 32), q.device)
+    if return_lse:
+        splits = max(splits, 2)  # the split-KV path keeps per-split log-sum-exps (base 2) in the workspace
     ws_o, ws_lse = _ws(T, N, splits, q.device) if splits > 1 else (None, None)
     _ext.C().mla_attention(out, q, kv_cache, block_tables, seq_lens, query_start_loc, req_of_token, None, ws_o, ws_lse,
                            splits, scale)
-    return out
+    if not return_lse:
+        return out
+    lse = torch.logsumexp(ws_lse.view(splits, T, N) * 0.6931471805599453, 0)
+    empty = torch.isinf(lse) & (lse < 0)
+    return torch.where(empty.unsqueeze(-1), torch.zeros_like(out), out), lse
 
 
 def sparse_mla_cuda(q, kv_flat, indices, scale, d_v=512):

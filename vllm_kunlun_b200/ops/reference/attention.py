@@ -257,6 +257,8 @@ def mla_decode(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_l
         if qe == qs:
             continue
         L = int(seq_lens[r])
+        if L == 0:  # nothing cached for this row (possible on a context-parallel rank): zeros and -inf
+            continue
         pos = torch.arange(L)
         rows = kv_cache[block_tables[r, pos // bs].long(), pos % bs]
         rows = dequant_mla_fp8_rows(rows) if kv_cache.dtype == torch.uint8 else rows.float()

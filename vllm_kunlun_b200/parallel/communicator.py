@@ -71,7 +71,12 @@ class DeviceCommunicator:
         assert xm.shape[0] % self.world_size == 0
         out = torch.empty((xm.shape[0] // self.world_size,) + tuple(xm.shape[1:]), dtype=x.dtype,
                           device=x.device)
-        dist.reduce_scatter_tensor(out, xm, group=self.group)
+        if xm.is_cuda:
+            dist.reduce_scatter_tensor(out, xm, group=self.group)
+        else:  # gloo has no reduce-scatter
+            dist.all_reduce(xm, group=self.group)
+            n = out.shape[0]
+            out.copy_(xm[self.rank_in_group * n:(self.rank_in_group + 1) * n])
         return out.movedim(0, dim)
 
     def gather(self, x: torch.Tensor, dst: int = 0, dim: int = -1) -> Optional[torch.Tensor]:
