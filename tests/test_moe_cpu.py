@@ -76,3 +76,44 @@ def test_moe_engine_cpu(fp8):
         llm2.engine.runner.model.load_state_dict(llm.engine.runner.model.state_dict())
     b = llm2.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))
     assert [o.token_ids for o in a] == [o.token_ids for o in b]
+
+
+def test_int8_and_awq_expert_checkpoints_dequantise_on_load():
+    """compressed-tensors W8A8 and AWQ-packed experts end up as the dense weights they encode."""
+    import dataclasses
+
+    from vllm_kunlun_b200.config import qwen3_30b_a3b, tiny
+    from vllm_kunlun_b200.models.moe import FusedExperts
+    from vllm_kunlun_b200.ops.reference import basic as rb
+    base = tiny(qwen3_30b_a3b(fp8=False), num_layers=1, vocab_size=64, hidden_size=64, num_heads=2, num_kv_heads=1,
+                head_dim=32, intermediate_size=64, num_experts=2, num_experts_per_tok=1, moe_intermediate_size=32,
+                dtype="float32")
+    g = torch.Generator().manual_seed(0)
+    H, I = 64, 32
+    # int8 per-channel
+    ex = FusedExperts(dataclasses.replace(base, quantization="int8"), torch.float32, "cpu")
+    want = {}
+    for e in range(2):
+        for which, shape in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+            w = torch.randn(*shape, generator=g)
+            s = w.abs().amax(-1, keepdim=True) / 127
+            q = torch.round(w / s).to(torch.int8)
+            ex.load_expert(e, which, "weight", q)
+            ex.load_expert(e, which, "weight_scale", s)
+            want[(e, which)] = q.float() * s
+    for e in range(2):
+        torch.testing.assert_close(ex.w13.data[e, :I], want[(e, "gate_proj")])
+        torch.testing.assert_close(ex.w13.data[e, I:], want[(e, "up_proj")])
+        torch.testing.assert_close(ex.w2.data[e], want[(e, "down_proj")])
+    # AWQ int4, group 32
+    ex = FusedExperts(dataclasses.replace(base, quantization="awq"), torch.float32, "cpu")
+    for which, (N, K) in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+        wi = torch.randint(0, 16, (K, N), generator=g)
+        zi = torch.randint(0, 16, (K // 32, N), generator=g)
+        sc = torch.rand(K // 32, N, generator=g) * 0.1
+        qw, qz = rb.awq_pack(wi), rb.awq_pack(zi)
+        for pname, t in (("qweight", qw), ("qzeros", qz), ("scales", sc)):
+            ex.load_expert(1, which, pname, t)
+        dense = rb.awq_dequantize(qw, sc, qz, 32).T
+        got = ex.w2.data[1] if which == "down_proj" else ex.w13.data[1, (0 if which == "gate_proj" else I):][:I]
+        torch.testing.assert_close(got, dense)

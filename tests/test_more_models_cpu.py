@@ -75,3 +75,40 @@ def test_mimo_fp8_attention_weights_are_dequantised_on_load():
     w = torch.randn(256, 256)
     q, s = _quant_block_device(w)
     torch.testing.assert_close(_dequant_block(q, s), w, atol=0.15, rtol=0.1)
+
+
+def test_gpt_oss_checkpoint_layout():
+    from vllm_kunlun_b200.config import gpt_oss_20b
+    cfg = tiny(gpt_oss_20b(), num_layers=2, vocab_size=128, hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16,
+               intermediate_size=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, max_position=256,
+               dtype="float32")
+    llm = LLM(cfg, **KW)
+    m = llm.engine.runner.model
+    g = torch.Generator().manual_seed(0)
+    E, H, I = 4, 64, 32
+    gu = torch.randn(E, H, 2 * I, generator=g)
+    gub = torch.randn(E, 2 * I, generator=g)
+    dn = torch.randn(E, I, H, generator=g)
+    dnb = torch.randn(E, H, generator=g)
+    sinks = torch.randn(4, generator=g)
+    router = torch.randn(E, H, generator=g)
+    ck = {"model.layers.1.mlp.experts.gate_up_proj": gu, "model.layers.1.mlp.experts.gate_up_proj_bias": gub,
+          "model.layers.1.mlp.experts.down_proj": dn, "model.layers.1.mlp.experts.down_proj_bias": dnb,
+          "model.layers.1.self_attn.sinks": sinks, "model.layers.1.mlp.router.weight": router,
+          "model.layers.1.mlp.router.bias": torch.zeros(E)}
+    with torch.inference_mode():
+        loaded = m.load_weights(ck.items())
+    assert {n.replace('.mlp.gate.', '.mlp.router.') for n in loaded} == set(ck)
+    ex = m.layers["1"].mlp.experts
+    x = torch.randn(3, H, generator=g)
+    e = 2
+    h = x @ gu[e] + gub[e]                                   # checkpoint semantics: interleaved gate / up
+    gate, up = h[:, 0::2], h[:, 1::2]
+    mine = x @ ex.w13.data[e].T + ex.b13.data[e]
+    torch.testing.assert_close(mine[:, :I], gate, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(mine[:, I:], up, atol=1e-5, rtol=1e-5)
+    a = torch.randn(3, I, generator=g)
+    torch.testing.assert_close(a @ ex.w2.data[e].T + ex.b2.data[e], a @ dn[e] + dnb[e], atol=1e-5, rtol=1e-5)
+    assert torch.equal(m.layers["1"].self_attn.sinks.data, sinks)
+    assert torch.equal(m.layers["1"].mlp.gate.weight.data, router)
+    assert len(llm.generate([list(range(3, 40))], SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids) == 4

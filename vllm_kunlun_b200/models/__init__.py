@@ -21,7 +21,7 @@ _REGISTRY = {
     # MoE
     "Qwen3MoeForCausalLM": "moe:MoEForCausalLM",
     "Qwen2MoeForCausalLM": "moe:MoEForCausalLM",
-    "GptOssForCausalLM": "moe:MoEForCausalLM",
+    "GptOssForCausalLM": "gpt_oss:GptOssForCausalLM",
     "MixtralForCausalLM": "moe:MoEForCausalLM",
     # MLA family
     "DeepseekV2ForCausalLM": "deepseek:DeepseekForCausalLM",

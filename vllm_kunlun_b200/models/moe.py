@@ -73,10 +73,47 @@ class FusedExperts(nn.Module):
         return ops.fused_moe(x, self.w13, self.w2, topk_w, topk_ids, self.act, self.b13, self.b2, self.w13_scale,
                              self.w2_scale, self.block, self.expert_map)
 
+    # ---- int8 / int4 expert checkpoints (compressed-tensors W8A8 and W4A16 MoE, ``moe_wna16``, AWQ / GPTQ experts;
+    # ``quantization/compressed_tensors/compressed_tensors_moe.py:111-360``, ``quantization/moe_wna16.py:242-289``):
+    # the pieces of one projection are collected and de-quantised ONCE into the 16-bit grouped-GEMM layout (the
+    # reference de-quantises int4 experts to dense weights on every call).
+    _QUANT_PIECES = {"weight_scale": ("weight", "weight_scale"), "weight_packed": ("weight_packed", "weight_scale"),
+                     "qweight": ("qweight", "scales", "qzeros"), "scales": ("qweight", "scales", "qzeros"),
+                     "qzeros": ("qweight", "scales", "qzeros")}
+
+    def _load_quantised(self, e: int, which: str, pname: str, w: torch.Tensor) -> bool:
+        """Returns True when ``pname`` belongs to an int8 / int4 format (and was consumed)."""
+        q = self.cfg.quantization
+        if q not in ("int8", "awq", "gptq", "wna16"):
+            return False
+        if pname in ("bias", "g_idx", "weight_shape", "input_scale"):
+            return True  # not needed by the de-quantised layout
+        pend = self.__dict__.setdefault("_pending", {})
+        slot = pend.setdefault((e, which), {})
+        slot[pname] = w
+        from ..ops.reference import basic as rb
+        dense = None
+        if q == "int8" and "weight" in slot and "weight_scale" in slot:
+            dense = slot["weight"].float() * slot["weight_scale"].float().reshape(-1, 1)
+        elif q in ("awq", "gptq", "wna16") and all(k in slot for k in ("qweight", "scales", "qzeros")):
+            g = slot["qweight"].shape[0] * (1 if q == "awq" else 8) // slot["scales"].shape[0]
+            if q == "awq":
+                dense = rb.awq_dequantize(slot["qweight"], slot["scales"], slot["qzeros"], g).T
+            else:
+                K = slot["qweight"].shape[0] * 8
+                gidx = torch.arange(K, dtype=torch.int32) // g
+                dense = rb.gptq_dequantize(slot["qweight"], slot["scales"], slot["qzeros"], gidx, 4).T
+        if dense is not None:
+            del pend[(e, which)]
+            self.load_expert(e, which, "weight", dense.to(self.w13.dtype), _raw=True)
+        return True
+
     # ---- checkpoint loading: ``experts.{e}.{gate,up,down}_proj.{weight,weight_scale_inv}`` ----
-    def load_expert(self, e: int, which: str, pname: str, w: torch.Tensor):
+    def load_expert(self, e: int, which: str, pname: str, w: torch.Tensor, _raw: bool = False):
         le = e - self.first
         if not (0 <= le < self.num_local):
+            return
+        if not _raw and self._load_quantised(e, which, pname, w):
             return
         scale = pname == "weight_scale_inv"
         I = self.i_local
