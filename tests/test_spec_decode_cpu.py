@@ -68,3 +68,21 @@ def test_mtp_spec_decode_equals_plain():
     b = [o.token_ids for o in spec.generate(prompts, sp)]
     assert a == b  # verification makes the output independent of draft quality
     assert spec.engine.stats["spec_proposed"] > 0
+
+
+@pytest.mark.parametrize("method", ["eagle", "eagle3"])
+def test_eagle_drafts_do_not_change_greedy_output(method):
+    """Whatever the (random-init) draft proposes, verification keeps the target's greedy tokens."""
+    from vllm_kunlun_b200.config import llama_3_1_8b, tiny
+    cfg = tiny(llama_3_1_8b(), num_layers=6, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=48)
+    prompts = [list(range(3, 30)), list(range(40, 49))]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    want = [o.token_ids for o in LLM(cfg, **kw).generate(prompts, sp)]
+    llm = LLM(cfg, speculative_config={"method": method, "num_speculative_tokens": 1}, **kw)
+    got = [o.token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    assert llm.engine.stats["spec_proposed"] > 0
+    if method == "eagle3":
+        assert llm.engine.runner.model.aux_hidden_state_layers == (2, 3, 3)

@@ -335,6 +335,7 @@ class SpeculativeConfig:
     method: Optional[str] = None  # None | "mtp" | "eagle" | "eagle3" | "ngram"
     num_speculative_tokens: int = 0
     ngram_n: int = 3
+    draft_weights_path: Optional[str] = None  # safetensors directory of the draft model (random init when absent)
 
 
 @dataclass
@@ -383,6 +384,8 @@ class EngineConfig:
             self.cache.enable_prefix_caching = False
             if self.speculative.num_speculative_tokens:
                 raise ValueError("speculative decoding is not supported with linear-attention layers")
+        if self.speculative.method == "eagle3":
+            self.compilation.mode = "none"  # the auxiliary hidden states are not carried through captured graphs
         if self.speculative.method == "mtp" and not m.num_mtp_layers:
             raise ValueError("MTP speculative decoding needs a model with MTP layers")
         self.scheduler.max_num_batched_tokens = max(

@@ -452,6 +452,8 @@ class ModelRunner:
                 sel = None
             else:
                 self._full_hidden = hidden if self.keep_full_hidden else None
+                if self.keep_full_hidden and getattr(self.model, "aux_hidden", None) is not None:
+                    self._full_hidden = self.model.aux_hidden  # EAGLE-3 drafts read three layers' states
                 sel = hidden.index_select(0, md.logits_indices.long()) if md.logits_indices is not None else hidden
                 logits = self.model.compute_logits(sel)
                 tokens = self.sampler(logits, sp)

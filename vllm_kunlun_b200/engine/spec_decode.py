@@ -59,17 +59,26 @@ def _accept(req, vals, stats):
 
 
 class MTPProposer:
-    """One MTP layer, one draft token per step (the configuration the benchmark names)."""
+    """A draft model that reads the target's hidden states: one draft token per step.  MTP (the configuration
+    the benchmark names) by default; :class:`EagleProposer` swaps the draft network."""
+
+    def build_model(self, engine):
+        from ..models.deepseek_mtp import DeepSeekMTP
+        cfg = engine.cfg
+        return DeepSeekMTP(cfg.model, device=cfg.device, target=engine.runner.model)
 
     def __init__(self, engine):
-        from ..models.deepseek_mtp import DeepSeekMTP
         self.engine = engine
         r = engine.runner
         cfg = engine.cfg
-        assert cfg.speculative.num_speculative_tokens == 1, "MTP proposer drafts one token per step"
+        assert cfg.speculative.num_speculative_tokens == 1, "the draft-model proposers draft one token per step"
         with torch.inference_mode():
-            self.model = DeepSeekMTP(cfg.model, device=cfg.device, target=r.model)
-            self.model.init_random(cfg.seed)
+            self.model = self.build_model(engine)
+            if cfg.speculative.draft_weights_path:
+                from ..models.loader import load_safetensors
+                self.model.load_weights(load_safetensors(cfg.speculative.draft_weights_path))
+            else:
+                self.model.init_random(cfg.seed)
         # the draft layer's KV cache uses the target's block ids
         for i, spec in self.model.kv_cache_spec(r.block_size).items():
             specs = spec if isinstance(spec, list) else [spec]
@@ -124,10 +133,27 @@ class MTPProposer:
             req.spec_token_ids = [int(d)]
 
 
+class EagleProposer(MTPProposer):
+    """EAGLE / EAGLE-3 drafts (``v1/sample/spec_decode/eagle.py:22-252``).  For EAGLE-3 the target collects the
+    hidden states of three layers and the runner hands their concatenation to the draft."""
+
+    def build_model(self, engine):
+        from ..models.eagle import EagleDraftModel
+        cfg = engine.cfg
+        eagle3 = cfg.speculative.method == "eagle3"
+        target = engine.runner.model
+        if eagle3:
+            assert hasattr(target, "set_aux_hidden_state_layers"), "the target model does not expose auxiliary hidden states"
+            target.set_aux_hidden_state_layers(target.get_eagle3_aux_hidden_state_layers())
+        return EagleDraftModel(cfg.model, device=cfg.device, target=target, eagle3=eagle3)
+
+
 def build_proposer(engine):
     sc = engine.cfg.speculative
     if sc.method == "mtp":
         return MTPProposer(engine)
+    if sc.method in ("eagle", "eagle3"):
+        return EagleProposer(engine)
     if sc.method == "ngram":
         return NgramProposer(engine, sc.num_speculative_tokens, sc.ngram_n)
-    raise ValueError(f"unsupported speculative method {sc.method!r} (mtp, ngram)")
+    raise ValueError(f"unsupported speculative method {sc.method!r} (mtp, eagle, eagle3, ngram)")

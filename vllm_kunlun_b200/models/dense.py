@@ -134,6 +134,15 @@ class DenseForCausalLM(nn.Module):
     passes ``(hidden, residual)`` on, ``models/deepseek_v2.py:1102-1158``)."""
 
     layer_cls = DenseDecoderLayer
+    aux_hidden_state_layers: tuple = ()  # EAGLE-3 target interface (``models/interfaces.py`` of the reference)
+    aux_hidden = None
+
+    def set_aux_hidden_state_layers(self, layers) -> None:
+        self.aux_hidden_state_layers = tuple(layers)
+
+    def get_eagle3_aux_hidden_state_layers(self) -> tuple:
+        n = self.cfg.num_layers
+        return (2, n // 2, n - 3) if n >= 6 else tuple(range(min(3, n)))
 
     def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
         super().__init__()
@@ -160,9 +169,13 @@ class DenseForCausalLM(nn.Module):
         if hidden is None:
             hidden = self.embed_tokens(input_ids)
         partial = False
+        aux = []
         for i in range(self.first_layer, self.last_layer):
+            if i in self.aux_hidden_state_layers:  # EAGLE-3: the stream entering layer i (needs a complete sum)
+                aux += [self._complete(hidden, residual, partial)] * self.aux_hidden_state_layers.count(i)
             hidden, residual = self.layers[str(i)](hidden, residual, partial)
             partial = True
+        self.aux_hidden = torch.cat(aux, -1) if aux else None
         if self.norm is None:
             st = get_state()
             if st.tp_size > 1:  # hand a fully reduced activation to the next pipeline stage
@@ -173,6 +186,12 @@ class DenseForCausalLM(nn.Module):
         hidden, _ = reduce_add_rmsnorm(hidden, residual, self.norm, partial)
         sp_sync()
         return hidden, None
+
+    def _complete(self, hidden, residual, partial: bool):
+        st = get_state()
+        if partial and st.tp_size > 1:
+            hidden = st.tp_comm.all_reduce(hidden.clone())
+        return hidden if residual is None else hidden + residual
 
     def compute_logits(self, hidden):
         return self.lm_head.logits(hidden)
