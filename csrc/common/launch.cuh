@@ -18,6 +18,7 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 
 // Process-wide switch (default on; B200_PDL=0 in the environment turns it off).
 int pdl_enabled();
+int gemm_l2_prefetch();
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(kGemmThreads)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
                int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
-               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages,
+               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages, int l2_prefetch,
                const __grid_constant__ GemmComm cm) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -177,16 +177,28 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       // Weights do not depend on the previous kernel: stream the first num_stages weight tiles
       // before waiting for it, so HBM stays busy across the kernel boundary.  The activation tile
       // of each of those stages is added after the wait (one barrier, two copies).
+      // For decode-shaped calls (weights are read once, the kernel is bandwidth bound) the weight tiles that
+      // follow the ring are pulled into L2 as well: the kernel in front of a GEMM is usually a short
+      // normalisation / activation / merge kernel that leaves HBM idle, and this CTA is already resident beside it.
       int pre = 0;
       {
+        int l2_ahead = (t_tiles <= 2) ? l2_prefetch : 0;
         Work w2 = make_work();
         int tile, kb0, kb1;
-        while (pre < num_stages && w2.next(tile, kb0, kb1)) {
+        while ((pre < num_stages || l2_ahead > 0) && w2.next(tile, kb0, kb1)) {
           int nt, tt;
           tile_coords(tile, nt, tt);
-          for (int kb = kb0; kb < kb1 && pre < num_stages; ++kb, ++pre) {
-            mbar_expect_tx(&full_bar[pre], Cfg::kStageBytes);
-            tma_load_2d_hint(smem + pre * Cfg::kStageBytes, &tmW, &full_bar[pre], kb * BK, nt * BM, pol_w);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (pre < num_stages) {
+              mbar_expect_tx(&full_bar[pre], Cfg::kStageBytes);
+              tma_load_2d_hint(smem + pre * Cfg::kStageBytes, &tmW, &full_bar[pre], kb * BK, nt * BM, pol_w);
+              ++pre;
+            } else if (l2_ahead > 0) {
+              tma_prefetch_l2_2d(&tmW, kb * BK, nt * BM);
+              --l2_ahead;
+            } else {
+              break;
+            }
           }
         }
       }
@@ -479,7 +491,7 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   int smem = stages * Cfg::kStageBytes + 1024 + 512 + kEpBytes;
   return launch_pdl(kern, dim3(a.grid), dim3(kGemmThreads), (size_t)smem, st, tmW, tmX, (OutT*)a.out,
                     (const OutT*)a.bias, a.ws, a.counters, a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta,
-                    a.max_contrib, a.fmt, a.ldo, stages, cm);
+                    a.max_contrib, a.fmt, a.ldo, stages, b200::gemm_l2_prefetch(), cm);
 }
 
 }  // namespace b200

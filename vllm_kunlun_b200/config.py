@@ -174,6 +174,10 @@ class ModelConfig:
     def from_hf_config(cls, cfg: dict) -> "ModelConfig":
         """Build from a Hugging Face ``config.json`` dict (same checkpoints the reference serves)."""
         arch = (cfg.get("architectures") or ["LlamaForCausalLM"])[0]
+        if "hidden_size" not in cfg and isinstance(cfg.get("text_config"), dict):
+            # nested layouts (Qwen3.5, vision-language wrappers): the decoder's fields live under text_config
+            cfg = {**cfg["text_config"], **{k: v for k, v in cfg.items() if k != "text_config"},
+                   "text_config": cfg["text_config"]}
         h = cfg["hidden_size"]
         nh = cfg["num_attention_heads"]
         rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}

@@ -19,6 +19,8 @@ _ENV: dict[str, Callable[[], Any]] = {
     "B200_NVTX": lambda: os.environ.get("B200_NVTX", "0") == "1",
     # programmatic dependent launch on decode-path kernels (read by the C++ side too)
     "B200_PDL": lambda: os.environ.get("B200_PDL", "1") != "0",
+    # 16 KB weight tiles per CTA that a decode-shaped GEMM pulls into L2 ahead of its smem ring (read by the C++ side; measured slower than off)
+    "B200_GEMM_L2_PREFETCH": lambda: int(os.environ.get("B200_GEMM_L2_PREFETCH", "0")),
     # peer-memory collectives (one-shot all-reduce, fused GEMM+collectives)
     "B200_PEER_COLLECTIVES": lambda: os.environ.get("B200_PEER_COLLECTIVES", "1") != "0",
     # exponential-race sampling with a cached noise tensor (the reference's FAST_RANDOM_SAMPLE)
