@@ -27,28 +27,76 @@ __device__ __forceinline__ int find_seq(const int* __restrict__ cu, int R, int t
 
 // y[t, c] = act(bias[c] + sum_j w[c, j] * in[t - (W-1) + j, c]); positions before the sequence start read
 // the cached state (rows W-1+p.. of the previous inputs) or zero.
-template <typename T>
-__global__ void conv1d_fwd_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
-                                  const T* __restrict__ w, const T* __restrict__ bias, const int* __restrict__ cu, int R,
-                                  const T* __restrict__ states, const int* __restrict__ slots,
-                                  const uint8_t* __restrict__ has_init, int C, int W, int act, int64_t Ttot) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t t = blockIdx.y;
-  if (c >= C || t >= Ttot) return;
-  const int r = find_seq(cu, R, (int)t);
-  const int p = (int)t - cu[r];
-  const int slot = slots[r];
-  const bool init = has_init[r] != 0 && slot >= 0;
-  float acc = bias ? to_f(bias[c]) : 0.f;
-#pragma unroll 4
-  for (int j = 0; j < W; ++j) {
-    const int q = p - (W - 1) + j;  // position within the sequence
-    float v;
-    if (q >= 0) v = to_f(x[(t - (W - 1) + j) * x_stride + c]);
-    else v = init ? to_f(states[((int64_t)slot * (W - 1) + (W - 1 + q)) * C + c]) : 0.f;
-    acc += to_f(w[(int64_t)c * W + j]) * v;
+// One thread = one 16-byte channel vector x kConvTok consecutive tokens, with a sliding window of the last W-1
+// input rows in registers, so every input row is loaded once per thread.
+constexpr int kConvTok = 8;
+
+template <typename T, int W>
+__global__ void __launch_bounds__(128) conv1d_fwd_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x,
+                                                         int64_t x_stride, const T* __restrict__ w, const T* __restrict__ bias,
+                                                         const int* __restrict__ cu, int R, const T* __restrict__ states,
+                                                         const int* __restrict__ slots, const uint8_t* __restrict__ has_init,
+                                                         int C, int act, int64_t Ttot) {
+  constexpr int V = Vec16<T>::N;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+  const int64_t t0 = (int64_t)blockIdx.y * kConvTok;
+  if (c0 >= C || t0 >= Ttot) return;
+  float wv[W][V], bv[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    bv[e] = bias ? to_f(bias[c0 + e]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) wv[j][e] = to_f(w[(int64_t)(c0 + e) * W + j]);
   }
-  out[t * out_stride + c] = from_f<T>(act ? silu(acc) : acc);
+  float win[W][V];  // win[j] = input row at (current token) - (W-1) + j
+  int r = find_seq(cu, R, (int)t0);
+  int seq_start = cu[r], seq_end = cu[r + 1];
+  auto load_hist = [&](int64_t t) {  // fill win[0 .. W-2] with the W-1 rows in front of token t
+    const int p = (int)t - seq_start;
+    const int slot = slots[r];
+    const bool init = has_init[r] != 0 && slot >= 0;
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {
+      const int q = p - (W - 1) + j;
+      if (q >= 0) {
+        Vec16<T> v = ld_vec(x + (t - (W - 1) + j) * x_stride + c0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) win[j][e] = to_f(v.v[e]);
+      } else if (init) {
+        Vec16<T> v = ld_vec(states + ((int64_t)slot * (W - 1) + (W - 1 + q)) * C + c0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) win[j][e] = to_f(v.v[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) win[j][e] = 0.f;
+      }
+    }
+  };
+  load_hist(t0);
+  for (int i = 0; i < kConvTok; ++i) {
+    const int64_t t = t0 + i;
+    if (t >= Ttot) break;
+    if (t >= seq_end) {  // crossed into the next (non-empty) sequence: its history comes from its own state
+      while (t >= seq_end) { ++r; seq_start = cu[r]; seq_end = cu[r + 1]; }
+      load_hist(t);
+    }
+    Vec16<T> cur = ld_vec(x + t * x_stride + c0);
+    Vec16<T> o;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      win[W - 1][e] = to_f(cur.v[e]);
+      float acc = bv[e];
+#pragma unroll
+      for (int j = 0; j < W; ++j) acc += wv[j][e] * win[j][e];
+      o.v[e] = from_f<T>(act ? silu(acc) : acc);
+    }
+    st_vec(out + t * out_stride + c0, o);
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) win[j][e] = win[j + 1][e];
+    }
+  }
 }
 
 // states[slot] <- last W-1 rows of (old state ++ x[seq]); one thread owns a channel column.
@@ -141,6 +189,9 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
     kn = to_f(k[(int64_t)s * qk_stride + hk * DK + tid]);
     qn = to_f(q[(int64_t)s * qk_stride + hk * DK + tid]);
   }
+  // per-token scalars of this thread, fetched one token ahead so that no global load sits on the recurrence
+  float g_n = g[(int64_t)s * Hv + hv], b_n = beta[(int64_t)s * Hv + hv];
+  float v_n = to_f(v[(int64_t)s * v_stride + hv * Dv + row]);
   for (int t = 0; t < L; ++t) {
     const int buf = t & 1;
     if (ldr) { sk[buf][tid] = kn; sq[buf][tid] = qn; }
@@ -148,12 +199,16 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
     if ((tid & 31) == 0) { ssum[buf][0][tid >> 5] = k2; ssum[buf][1][tid >> 5] = q2; }
     __syncthreads();
     const int64_t tok = s + t;
-    if (ldr && t + 1 < L) {
-      kn = to_f(k[(tok + 1) * qk_stride + hk * DK + tid]);
-      qn = to_f(q[(tok + 1) * qk_stride + hk * DK + tid]);
+    const float gt = __expf(g_n), bt = b_n, vt = v_n;
+    if (t + 1 < L) {
+      if (ldr) {
+        kn = to_f(k[(tok + 1) * qk_stride + hk * DK + tid]);
+        qn = to_f(q[(tok + 1) * qk_stride + hk * DK + tid]);
+      }
+      g_n = g[(tok + 1) * Hv + hv];
+      b_n = beta[(tok + 1) * Hv + hv];
+      v_n = to_f(v[(tok + 1) * v_stride + hv * Dv + row]);
     }
-    const float gt = __expf(g[tok * Hv + hv]), bt = beta[tok * Hv + hv];
-    const float vt = to_f(v[tok * v_stride + hv * Dv + row]);
     float rk = 1.f, rq = scale;
     if (l2norm) {
       rk = rsqrtf(ssum[buf][0][0] + ssum[buf][0][1] + ssum[buf][0][2] + ssum[buf][0][3] + 1e-6f);
@@ -226,18 +281,42 @@ __global__ void sigmoid_gate_mul_kernel(T* __restrict__ out, const T* __restrict
 }  // namespace
 }  // namespace b200
 
+namespace b200 {
+namespace {
+template <typename T>
+int launch_conv_fwd(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* w, const void* bias,
+                    const int* cu, int R, void* states, const int* slots, const uint8_t* has_init, int C, int W, int act,
+                    int64_t T_, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  if (C % V != 0 || (x_stride % V) != 0 || (out_stride % V) != 0) return 3;
+  dim3 g1((C / V + 127) / 128, (unsigned)((T_ + kConvTok - 1) / kConvTok)), g2((C + 255) / 256, R);
+#define B200_CONV_W(WW)                                                                                                   \
+  conv1d_fwd_kernel<T, WW><<<g1, 128, 0, st>>>((T*)out, out_stride, (const T*)x, x_stride, (const T*)w, (const T*)bias, cu, \
+                                               R, (const T*)states, slots, has_init, C, act, T_)
+  switch (W) {
+    case 2: B200_CONV_W(2); break;
+    case 3: B200_CONV_W(3); break;
+    case 4: B200_CONV_W(4); break;
+    case 5: B200_CONV_W(5); break;
+    case 6: B200_CONV_W(6); break;
+    case 7: B200_CONV_W(7); break;
+    default: B200_CONV_W(8); break;
+  }
+#undef B200_CONV_W
+  conv1d_state_kernel<T><<<g2, 256, 0, st>>>((T*)states, (const T*)x, x_stride, cu, slots, has_init, C, W);
+  return cudaGetLastError() != cudaSuccess;
+}
+}  // namespace
+}  // namespace b200
+
 extern "C" int b200_causal_conv1d_fwd(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* w,
                                       const void* bias, const int* cu, int R, void* states, const int* slots,
                                       const uint8_t* has_init, int C, int W, int act, int64_t T_, int dtype, cudaStream_t st) {
   if (W > b200::kMaxW || W < 2) return 3;
   if (T_ == 0) return 0;
-  dim3 g1((C + 255) / 256, (unsigned)T_), g2((C + 255) / 256, R);
-  B200_DISPATCH_DTYPE(dtype, {
-    b200::conv1d_fwd_kernel<T><<<g1, 256, 0, st>>>((T*)out, out_stride, (const T*)x, x_stride, (const T*)w, (const T*)bias, cu,
-                                                   R, (const T*)states, slots, has_init, C, W, act, T_);
-    b200::conv1d_state_kernel<T><<<g2, 256, 0, st>>>((T*)states, (const T*)x, x_stride, cu, slots, has_init, C, W);
-  });
-  return cudaGetLastError() != cudaSuccess;
+  B200_DISPATCH_DTYPE(dtype, return (b200::launch_conv_fwd<T>(out, out_stride, x, x_stride, w, bias, cu, R, states, slots,
+                                                              has_init, C, W, act, T_, st)));
+  return 1;
 }
 
 extern "C" int b200_causal_conv1d_update(void* out, int64_t out_stride, const void* x, int64_t x_stride, void* states,

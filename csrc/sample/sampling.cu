@@ -6,8 +6,12 @@
 // low-probability tail whose cumulative mass is <= 1 - p, then draw argmax(prob / Exp(1)) (:141-174).
 // Instead of sorting the row, both thresholds come from an MSB-first radix select over the float bit
 // patterns (count histogram for top-k, probability-mass histogram for top-p): 4 passes of 8 bits each.
+#include <cooperative_groups.h>
+
 #include "../api.h"
 #include "../common/utils.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace b200 {
 namespace {
@@ -188,6 +192,203 @@ __global__ void __launch_bounds__(kThreads) topk_topp_sample_kernel(
   if (tid == 0) out[row] = b.i;
 }
 
+// ---- cluster version: 8 CTAs share a row, every thread keeps its elements in registers ------------------------
+// All passes after the load run out of registers.  Thresholds are found by refining a value interval: each pass
+// splits the current interval of scaled logits into 256 equal bins (spread-out bins keep shared-memory atomics
+// from piling onto one address, unlike digit histograms of float bit patterns, whose leading digits are almost
+// constant), the 8 CTAs' histograms are summed through distributed shared memory, and the bin that contains the
+// k-th largest element (top-k, by count) or the point where the low-probability tail reaches 1 - p (top-p, by
+// mass) becomes the next interval.  Four passes narrow the interval to range * 2^-32, i.e. to ties.
+// Used whenever the row fits (V <= 8 * 1024 * kMaxPerThread).
+constexpr int kCluster = 8;
+constexpr int kMaxPerThread = 24;
+constexpr int kRefine = 4;
+
+struct ClusterScratch {
+  float hist[2][256];
+  float val[4];
+  ArgBest best;
+};
+
+__device__ __forceinline__ float cluster_reduce(cg::cluster_group& cl, ClusterScratch* s, float v, float* red, int slot,
+                                                int op /*0 sum, 1 max, 2 min*/) {
+  v = op == 0 ? block_sum(v, red) : (op == 1 ? block_max(v, red) : -block_max(-v, red));
+  if (threadIdx.x == 0) s->val[slot] = v;
+  cl.sync();
+  float acc = op == 0 ? 0.f : (op == 1 ? -INFINITY : INFINITY);
+  for (int r = 0; r < kCluster; ++r) {
+    float o = cl.map_shared_rank(s, r)->val[slot];
+    acc = op == 0 ? acc + o : (op == 1 ? fmaxf(acc, o) : fminf(acc, o));
+  }
+  return acc;
+}
+
+template <typename T, int NPT>
+__global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads) topk_topp_sample_cluster_kernel(
+    int64_t* __restrict__ out, const T* __restrict__ logits, int64_t stride, int V, const float* __restrict__ temperature,
+    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ noise, int64_t noise_stride,
+    uint64_t seed, uint64_t step) {
+  __shared__ ClusterScratch sc;
+  __shared__ float red[32];
+  __shared__ float s_tot[256];  // cluster-wide histogram totals (identical in every CTA)
+  __shared__ ArgBest ared[32];
+  __shared__ int s_bin;
+  __shared__ float s_acc;
+  cg::cluster_group cl = cg::this_cluster();
+  const int crank = (int)cl.block_rank();
+  const int row = blockIdx.x / kCluster, tid = threadIdx.x;
+  const T* x = logits + row * stride;
+  const float temp = temperature ? temperature[row] : 1.f;
+  const bool greedy = temp == 0.f;
+  const float inv_t = greedy ? 1.f : 1.f / temp;
+  // element j of this thread: interleaved over the cluster so that every load instruction is coalesced
+  float l[NPT];
+#pragma unroll
+  for (int j = 0; j < NPT; ++j) {
+    const int i = (j * kCluster + crank) * kThreads + tid;
+    l[j] = i < V ? to_f(x[i]) * inv_t : -INFINITY;
+  }
+  auto index_of = [&](int j) { return (j * kCluster + crank) * kThreads + tid; };
+  auto cluster_argbest = [&](ArgBest bb) {
+    bb = block_argbest(bb, ared);
+    if (tid == 0) sc.best = bb;
+    cl.sync();
+    ArgBest r{-INFINITY, 0x7fffffff};
+    for (int c = 0; c < kCluster; ++c) r = better(r, cl.map_shared_rank(&sc, c)->best);
+    return r;
+  };
+
+  if (greedy) {
+    ArgBest bb{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int j = 0; j < NPT; ++j) bb = better(bb, ArgBest{l[j], index_of(j)});
+    bb = cluster_argbest(bb);
+    if (crank == 0 && tid == 0) out[row] = bb.i;
+    cl.sync();  // nobody leaves while its shared memory may still be read
+    return;
+  }
+  int k = top_k ? top_k[row] : 0;
+  if (k <= 0 || k > V) k = V;
+  const float p = top_p ? top_p[row] : 1.f;
+
+  float m = -INFINITY, lowest = INFINITY;
+#pragma unroll
+  for (int j = 0; j < NPT; ++j) {
+    m = fmaxf(m, l[j]);
+    if (l[j] != -INFINITY) lowest = fminf(lowest, l[j]);
+  }
+  m = cluster_reduce(cl, &sc, m, red, 0, 1);
+  lowest = cluster_reduce(cl, &sc, lowest, red, 1, 2);
+
+  // element state: bit j of `keep` = survives, bit j of `alive` = inside the interval still being refined
+  uint32_t keep = 0, alive = 0;
+#pragma unroll
+  for (int j = 0; j < NPT; ++j)
+    if (l[j] != -INFINITY) alive |= 1u << j;
+  int pass_no = 0;  // selects the histogram buffer: a buffer is rewritten two cluster syncs after its last read
+
+  // One refinement pass.  `by_mass`: histogram of exp(l - m) walked from the bottom until `target` is exceeded
+  // (elements under the chosen bin are dropped); otherwise a count histogram walked from the top until `target`
+  // elements are covered (elements above the chosen bin are kept).  Returns the chosen bin's interval in lo / hi
+  // and the amount accumulated outside it in `acc`.
+  auto refine = [&](bool by_mass, float& lo, float& hi, float target, float& acc_out) {
+    float* h = sc.hist[pass_no & 1];
+    for (int i = tid; i < 256; i += kThreads) h[i] = 0.f;
+    __syncthreads();
+    const float scale = 256.f / fmaxf(hi - lo, 1e-30f);
+    int bins[NPT];
+#pragma unroll
+    for (int j = 0; j < NPT; ++j) {
+      bins[j] = -1;
+      if (!(alive >> j & 1)) continue;
+      int bi = (int)((l[j] - lo) * scale);
+      bi = bi < 0 ? 0 : (bi > 255 ? 255 : bi);
+      bins[j] = bi;
+      atomicAdd(&h[bi], by_mass ? __expf(l[j] - m) : 1.f);
+    }
+    cl.sync();
+    if (tid < 256) {
+      float c = 0.f;
+      for (int r = 0; r < kCluster; ++r) c += cl.map_shared_rank(&sc, r)->hist[pass_no & 1][tid];  // fixed order
+      s_tot[tid] = c;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float acc = acc_out;
+      int d;
+      if (by_mass) {
+        int last = -1;
+        float acc_last = acc;
+        for (d = 0; d < 256; ++d) {
+          if (s_tot[d] > 0.f) { last = d; acc_last = acc; }
+          if (acc + s_tot[d] > target) break;
+          acc += s_tot[d];
+        }
+        if (d == 256) { d = last < 0 ? 0 : last; acc = acc_last; }  // rounding: stay on the highest occupied bin
+      } else {
+        for (d = 255; d > 0; --d) {
+          if (acc + s_tot[d] >= target) break;
+          acc += s_tot[d];
+        }
+      }
+      s_bin = d;
+      s_acc = acc;
+    }
+    __syncthreads();
+    const int d = s_bin;
+    acc_out = s_acc;
+#pragma unroll
+    for (int j = 0; j < NPT; ++j) {
+      if (bins[j] < 0 || bins[j] == d) continue;
+      alive &= ~(1u << j);
+      if (bins[j] > d) keep |= 1u << j;  // above the boundary bin: kept by both criteria
+    }
+    const float width = (hi - lo) * (1.f / 256.f);
+    lo = lo + width * d;
+    hi = lo + width;
+    ++pass_no;
+  };
+
+  // ---- top-k: count from the top
+  if (k < V) {
+    float lo = lowest, hi = m + fmaxf(fabsf(m), 1.f) * 1e-6f, covered = 0.f;
+    for (int r = 0; r < kRefine; ++r) refine(false, lo, hi, (float)k, covered);
+  }
+  keep |= alive;  // whatever is still inside the last interval ties with the k-th element
+  alive = keep;
+  keep = 0;
+
+  // ---- soft-max denominator over the survivors
+  float z = 0.f;
+  float low2 = INFINITY;
+#pragma unroll
+  for (int j = 0; j < NPT; ++j)
+    if (alive >> j & 1) { z += __expf(l[j] - m); low2 = fminf(low2, l[j]); }
+  z = cluster_reduce(cl, &sc, z, red, 2, 0);
+
+  // ---- top-p: mass from the bottom
+  if (p < 1.f) {
+    low2 = cluster_reduce(cl, &sc, low2, red, 3, 2);
+    float lo = low2, hi = m + fmaxf(fabsf(m), 1.f) * 1e-6f, below = 0.f;
+    const float budget = (1.f - p) * z;
+    for (int r = 0; r < kRefine; ++r) refine(true, lo, hi, budget, below);
+  }
+  keep |= alive;
+
+  // ---- exponential race
+  ArgBest bb{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int j = 0; j < NPT; ++j) {
+    if (!(keep >> j & 1)) continue;
+    const int i = index_of(j);
+    float q = noise ? noise[row * noise_stride + i] : exp_variate(seed, step * 65536ull + row, i);
+    bb = better(bb, ArgBest{__expf(l[j] - m) / q, i});
+  }
+  bb = cluster_argbest(bb);
+  if (crank == 0 && tid == 0) out[row] = bb.i;
+  cl.sync();
+}
+
 // logits[b, tok] /= or *= penalty once per distinct token of the row's history
 template <typename T>
 __global__ void repetition_penalty_kernel(T* __restrict__ logits, int64_t stride, int V, const int64_t* __restrict__ tokens,
@@ -265,6 +466,19 @@ extern "C" int b200_topk_topp_sample(int64_t* out, const void* logits, int64_t r
                                      const float* temperature, const int* top_k, const float* top_p, const float* noise,
                                      int64_t noise_stride, uint64_t seed, uint64_t step, int dtype, cudaStream_t st) {
   if (rows == 0) return 0;
+  const int per = (V + b200::kCluster * b200::kThreads - 1) / (b200::kCluster * b200::kThreads);
+  if (per <= b200::kMaxPerThread) {
+    const unsigned grid = (unsigned)rows * b200::kCluster;
+#define B200_SAMPLE_CASE(NPT)                                                                                            \
+  B200_DISPATCH_DTYPE(dtype, (b200::topk_topp_sample_cluster_kernel<T, NPT><<<grid, b200::kThreads, 0, st>>>(             \
+                                 out, (const T*)logits, stride, V, temperature, top_k, top_p, noise, noise_stride, seed, step)))
+    if (per <= 4) { B200_SAMPLE_CASE(4); }
+    else if (per <= 8) { B200_SAMPLE_CASE(8); }
+    else if (per <= 16) { B200_SAMPLE_CASE(16); }
+    else { B200_SAMPLE_CASE(24); }
+#undef B200_SAMPLE_CASE
+    return cudaGetLastError() != cudaSuccess;
+  }
   B200_DISPATCH_DTYPE(dtype, (b200::topk_topp_sample_kernel<T><<<(unsigned)rows, b200::kThreads, 0, st>>>(
                                  out, (const T*)logits, stride, V, temperature, top_k, top_p, noise, noise_stride, seed, step)));
   return cudaGetLastError() != cudaSuccess;
