@@ -158,88 +158,128 @@ __global__ void gdn_gating_kernel(float* __restrict__ g, float* __restrict__ bet
 
 // Sequential gated delta rule.  Block = 128 threads = 32 state rows (of Dv) x 4 quarters of Dk; grid
 // (Dv/32, Hv, sequences).  Per token: S *= exp(g); pred = S k; S += beta (v - pred) k^T; o = S q.
+// Tokens are staged through shared memory in chunks of kGdnChunk: while the block works through one chunk
+// (no block-wide barrier inside: a row's four quarter-threads are adjacent lanes), every thread already holds its
+// share of the next chunk's q / k / v / g / beta in registers, so global-memory latency never sits on the
+// recurrence and the block synchronises twice per chunk instead of once per token.
+constexpr int kGdnChunk = 16;
+
 template <typename T, int DK>
 __global__ void __launch_bounds__(128) gdn_recurrent_kernel(
     T* __restrict__ out, int64_t o_stride, const T* __restrict__ q, const T* __restrict__ k, int64_t qk_stride,
     const T* __restrict__ v, int64_t v_stride, const float* __restrict__ g, const float* __restrict__ beta,
     float* __restrict__ states /*[slots, Hv, Dv, DK]*/, const int* __restrict__ cu, const int* __restrict__ slots,
     const uint8_t* __restrict__ has_init, int Hk, int Hv, int Dv, float scale, int l2norm) {
-  static_assert(DK % 16 == 0, "DK");
-  constexpr int QW = DK / 4;  // state columns per thread
-  __shared__ __align__(16) float sk[2][DK];
-  __shared__ __align__(16) float sq[2][DK];
-  __shared__ float ssum[2][2][4];
-  const int tid = threadIdx.x, rl = tid >> 2, qd = tid & 3;
+  static_assert(DK % 16 == 0 && DK <= 128, "DK");
+  constexpr int QW = DK / 4;                      // state columns per thread
+  constexpr int CH = kGdnChunk;
+  constexpr int QK_PER = CH * DK / 128;           // q (and k) elements of a chunk per thread
+  constexpr int V_PER = CH * 32 / 128;            // v elements of a chunk per thread
+  __shared__ __align__(16) float sk[CH][DK];
+  __shared__ __align__(16) float sq[CH][DK];
+  __shared__ float sv[CH][32];
+  __shared__ float sg[CH], sb[CH], srk[CH], srq[CH];
+  const int tid = threadIdx.x, rl = tid >> 2, qd = tid & 3, warp = tid >> 5, lane = tid & 31;
   const int hv = blockIdx.y, r = blockIdx.z, hk = hv / (Hv / Hk);
-  const int row = blockIdx.x * 32 + rl;
+  const int row0 = blockIdx.x * 32, row = row0 + rl;
   const int s = cu[r], L = cu[r + 1] - s, slot = slots[r];
   if (L == 0 || slot < 0) return;
-  float* sp = states + (((int64_t)slot * Hv + hv) * Dv + row) * DK + qd * QW;
+  // Column ownership is interleaved in 16-byte pieces: registers S[4i .. 4i+3] of quarter qd hold columns
+  // 16 i + 4 qd .. + 3, so that the four quarter-lanes of a row read four consecutive float4 of the shared k / q row
+  // (distinct banks) instead of four addresses 128 bytes apart (one bank, a 4-way conflict on every load).
+  float* sp = states + (((int64_t)slot * Hv + hv) * Dv + row) * DK + qd * 4;
   float S[QW];
   if (has_init[r]) {
 #pragma unroll
-    for (int j = 0; j < QW; j += 4) *reinterpret_cast<float4*>(&S[j]) = *reinterpret_cast<const float4*>(sp + j);
+    for (int j = 0; j < QW; j += 4) *reinterpret_cast<float4*>(&S[j]) = *reinterpret_cast<const float4*>(sp + j * 4);
   } else {
 #pragma unroll
     for (int j = 0; j < QW; ++j) S[j] = 0.f;
   }
-  const bool ldr = tid < DK;  // DK <= 128: one loader thread per column
-  float kn = 0.f, qn = 0.f;
-  if (ldr) {
-    kn = to_f(k[(int64_t)s * qk_stride + hk * DK + tid]);
-    qn = to_f(q[(int64_t)s * qk_stride + hk * DK + tid]);
-  }
-  // per-token scalars of this thread, fetched one token ahead so that no global load sits on the recurrence
-  float g_n = g[(int64_t)s * Hv + hv], b_n = beta[(int64_t)s * Hv + hv];
-  float v_n = to_f(v[(int64_t)s * v_stride + hv * Dv + row]);
-  for (int t = 0; t < L; ++t) {
-    const int buf = t & 1;
-    if (ldr) { sk[buf][tid] = kn; sq[buf][tid] = qn; }
-    float k2 = warp_sum(kn * kn), q2 = warp_sum(qn * qn);
-    if ((tid & 31) == 0) { ssum[buf][0][tid >> 5] = k2; ssum[buf][1][tid >> 5] = q2; }
+  // register staging of one chunk: element e of the flattened [CH, DK] (resp. [CH, 32]) tile, e = i * 128 + tid
+  float rk_[QK_PER], rq_[QK_PER], rv_[V_PER], rg = 0.f, rb = 0.f;
+  auto fetch = [&](int c0) {
+#pragma unroll
+    for (int i = 0; i < QK_PER; ++i) {
+      const int e = i * 128 + tid, t = e / DK, d = e % DK;
+      const bool ok = c0 + t < L;
+      const int64_t tok = s + c0 + t;
+      rk_[i] = ok ? to_f(k[tok * qk_stride + hk * DK + d]) : 0.f;
+      rq_[i] = ok ? to_f(q[tok * qk_stride + hk * DK + d]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < V_PER; ++i) {
+      const int e = i * 128 + tid, t = e / 32, d = e % 32;
+      rv_[i] = (c0 + t < L) ? to_f(v[(int64_t)(s + c0 + t) * v_stride + hv * Dv + row0 + d]) : 0.f;
+    }
+    if (tid < CH && c0 + tid < L) {
+      rg = g[(int64_t)(s + c0 + tid) * Hv + hv];
+      rb = beta[(int64_t)(s + c0 + tid) * Hv + hv];
+    }
+  };
+  fetch(0);
+  for (int c0 = 0; c0 < L; c0 += CH) {
+    __syncthreads();  // the previous chunk has been consumed
+#pragma unroll
+    for (int i = 0; i < QK_PER; ++i) {
+      const int e = i * 128 + tid;
+      sk[e / DK][e % DK] = rk_[i];
+      sq[e / DK][e % DK] = rq_[i];
+    }
+#pragma unroll
+    for (int i = 0; i < V_PER; ++i) {
+      const int e = i * 128 + tid;
+      sv[e / 32][e % 32] = rv_[i];
+    }
+    if (tid < CH) { sg[tid] = __expf(rg); sb[tid] = rb; }
     __syncthreads();
-    const int64_t tok = s + t;
-    const float gt = __expf(g_n), bt = b_n, vt = v_n;
-    if (t + 1 < L) {
-      if (ldr) {
-        kn = to_f(k[(tok + 1) * qk_stride + hk * DK + tid]);
-        qn = to_f(q[(tok + 1) * qk_stride + hk * DK + tid]);
+    // squared norms: warp w handles tokens w, w + 4, ...
+    for (int t = warp; t < CH; t += 4) {
+      float k2 = 0.f, q2 = 0.f;
+      for (int d = lane; d < DK; d += 32) { k2 += sk[t][d] * sk[t][d]; q2 += sq[t][d] * sq[t][d]; }
+      k2 = warp_sum(k2);
+      q2 = warp_sum(q2);
+      if (lane == 0) {
+        srk[t] = l2norm ? rsqrtf(k2 + 1e-6f) : 1.f;
+        srq[t] = l2norm ? scale * rsqrtf(q2 + 1e-6f) : scale;
       }
-      g_n = g[(tok + 1) * Hv + hv];
-      b_n = beta[(tok + 1) * Hv + hv];
-      v_n = to_f(v[(tok + 1) * v_stride + hv * Dv + row]);
     }
-    float rk = 1.f, rq = scale;
-    if (l2norm) {
-      rk = rsqrtf(ssum[buf][0][0] + ssum[buf][0][1] + ssum[buf][0][2] + ssum[buf][0][3] + 1e-6f);
-      rq = scale * rsqrtf(ssum[buf][1][0] + ssum[buf][1][1] + ssum[buf][1][2] + ssum[buf][1][3] + 1e-6f);
-    }
-    const float* kk = &sk[buf][qd * QW];
-    const float* qq = &sq[buf][qd * QW];
-    float pred = 0.f;
+    if (c0 + CH < L) fetch(c0 + CH);  // next chunk's global loads fly while this one is processed
+    __syncthreads();
+    const int n = min(CH, L - c0);
+    for (int t = 0; t < n; ++t) {
+      const float gt = sg[t], bt = sb[t], vt = sv[t][rl], rk = srk[t], rq = srq[t];
+      const float* kk = &sk[t][qd * 4];
+      const float* qq = &sq[t][qd * 4];
+      float pred = 0.f, pred2 = 0.f;
 #pragma unroll
-    for (int j = 0; j < QW; j += 4) {
-      float4 k4 = *reinterpret_cast<const float4*>(kk + j);
-      S[j] *= gt; S[j + 1] *= gt; S[j + 2] *= gt; S[j + 3] *= gt;
-      pred += S[j] * k4.x + S[j + 1] * k4.y + S[j + 2] * k4.z + S[j + 3] * k4.w;
-    }
-    pred += __shfl_xor_sync(0xffffffff, pred, 1);
-    pred += __shfl_xor_sync(0xffffffff, pred, 2);
-    const float delta = (vt - pred * rk) * bt * rk;
-    float o = 0.f;
+      for (int j = 0; j < QW; j += 4) {
+        float4 k4 = *reinterpret_cast<const float4*>(kk + j * 4);
+        S[j] *= gt; S[j + 1] *= gt; S[j + 2] *= gt; S[j + 3] *= gt;
+        pred += S[j] * k4.x + S[j + 1] * k4.y;
+        pred2 += S[j + 2] * k4.z + S[j + 3] * k4.w;
+      }
+      pred += pred2;
+      pred += __shfl_xor_sync(0xffffffff, pred, 1);
+      pred += __shfl_xor_sync(0xffffffff, pred, 2);
+      const float delta = (vt - pred * rk) * bt * rk;
+      float o = 0.f, o2 = 0.f;
 #pragma unroll
-    for (int j = 0; j < QW; j += 4) {
-      float4 k4 = *reinterpret_cast<const float4*>(kk + j);
-      float4 q4 = *reinterpret_cast<const float4*>(qq + j);
-      S[j] += delta * k4.x; S[j + 1] += delta * k4.y; S[j + 2] += delta * k4.z; S[j + 3] += delta * k4.w;
-      o += S[j] * q4.x + S[j + 1] * q4.y + S[j + 2] * q4.z + S[j + 3] * q4.w;
+      for (int j = 0; j < QW; j += 4) {
+        float4 k4 = *reinterpret_cast<const float4*>(kk + j * 4);
+        float4 q4 = *reinterpret_cast<const float4*>(qq + j * 4);
+        S[j] += delta * k4.x; S[j + 1] += delta * k4.y; S[j + 2] += delta * k4.z; S[j + 3] += delta * k4.w;
+        o += S[j] * q4.x + S[j + 1] * q4.y;
+        o2 += S[j + 2] * q4.z + S[j + 3] * q4.w;
+      }
+      o += o2;
+      o += __shfl_xor_sync(0xffffffff, o, 1);
+      o += __shfl_xor_sync(0xffffffff, o, 2);
+      if (qd == 0) out[(int64_t)(s + c0 + t) * o_stride + hv * Dv + row] = from_f<T>(o * rq);
     }
-    o += __shfl_xor_sync(0xffffffff, o, 1);
-    o += __shfl_xor_sync(0xffffffff, o, 2);
-    if (qd == 0) out[tok * o_stride + hv * Dv + row] = from_f<T>(o * rq);
   }
 #pragma unroll
-  for (int j = 0; j < QW; j += 4) *reinterpret_cast<float4*>(sp + j) = *reinterpret_cast<const float4*>(&S[j]);
+  for (int j = 0; j < QW; j += 4) *reinterpret_cast<float4*>(sp + j * 4) = *reinterpret_cast<const float4*>(&S[j]);
 }
 
 // MTP input glue: out[t] = [rmsnorm(embed[t]) * (pos != 0), rmsnorm(hidden[t])]  (deepseek_mtp.py:79-87)
