@@ -73,12 +73,14 @@ struct AttnParams {
   const int* qsl;           // [B+1]
   const float* sinks;       // [Hq] or null
   int Hq, Hkv, block_size, max_blocks, num_splits, window;
+  int fuse_merge;         // decode kernel: the last split CTA of a tile merges the partials itself
   int64_t num_blocks, T;
   float scale_log2;
 };
 
 
 // decode-shaped batches (<= 16 packed query rows per KV head): csrc/attention/paged_decode.cu
-int paged_decode_dispatch(const AttnParams& p, int B, int max_q_rows, int D, int dtype, cudaStream_t st);
+// *merged is set when the kernel combined its split-KV partials itself (no merge kernel needed)
+int paged_decode_dispatch(const AttnParams& p, int B, int max_q_rows, int D, int dtype, cudaStream_t st, bool* merged);
 
 }  // namespace b200

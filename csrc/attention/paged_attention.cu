@@ -394,8 +394,10 @@ extern "C" int b200_paged_attention(void* out, const void* q, const void* kv_cac
   p.scale_log2 = scale * 1.4426950408889634f;
   int max_q_rows = max_query_len * (Hq / Hkv);
   int rc = 3;
+  bool merged = false;
+  p.fuse_merge = 0;
   if (decode_layout && max_q_rows <= 16 && block_size % 16 == 0) {
-    rc = paged_decode_dispatch(p, B, max_q_rows, D, dtype, st);
+    rc = paged_decode_dispatch(p, B, max_q_rows, D, dtype, st, &merged);
   } else {
 #define B200_ATTN_CASE(TT, DD) rc = launch_attn<TT, DD, 4, 1, 2>(p, B, max_q_rows, st)
     if (dtype == kBF16) {
@@ -410,7 +412,7 @@ extern "C" int b200_paged_attention(void* out, const void* q, const void* kv_cac
 #undef B200_ATTN_CASE
   }
   if (rc != 0) return rc;
-  if (num_splits > 1) {
+  if (num_splits > 1 && !merged) {
     int64_t rows = T_ * Hq;
     if (dtype == kBF16)
       launch_pdl(merge_splits_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, st, (__nv_bfloat16*)out,

@@ -9,11 +9,19 @@
 // fp32 workspace consumed by merge_splits_kernel.
 #include "../api.h"
 #include "../common/launch.cuh"
+#include <stdlib.h>
+
 #include "attn_common.cuh"
 
 namespace b200 {
 
 constexpr int kDecTile = 16;
+
+// Arrival counters of the split CTAs of one (request, kv head, row tile); zero between launches (the merging CTA
+// resets its counter).  One launch at a time per device uses them: concurrent decode-attention launches on
+// different streams must not share a device.
+constexpr int kMaxTickets = 1 << 18;
+static __device__ int g_decode_tickets[kMaxTickets];
 
 template <typename T, int D, int kWarps, int kStages>
 __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(AttnParams p) {
@@ -273,10 +281,45 @@ __global__ void __launch_bounds__(kWarps * 32) paged_decode_kernel(AttnParams p)
       if (c == 0) p.ws_lse[(int64_t)split * p.T * p.Hq + orow] = (L > 0.f) ? Ms + log2f(L) : -INFINITY;
     }
   }
+  if (p.num_splits == 1 || !p.fuse_merge) return;
+  // ---------------------------------------------------------------- split-KV merge by the last CTA to arrive
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  const int ticket_idx = (req * p.Hkv + kvh) * gridDim.x + blockIdx.x;
+  if (tid == 0) s_last = (atomicAdd(&g_decode_tickets[ticket_idx], 1) == p.num_splits - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = tid; idx < 16 * kPairs; idx += kWarps * 32) {
+    const int r = idx / kPairs, c = (idx % kPairs) * 2;
+    const int prow = row0 + r;
+    if (prow >= rows_total) continue;
+    const int tok = prow / g, hh = kvh * g + prow % g;
+    const int64_t orow = (int64_t)(qs + tok) * p.Hq + hh;
+    const int64_t sstride = p.T * p.Hq;
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, __ldcg(p.ws_lse + s2 * sstride + orow));
+    const float Ms = (M == -INFINITY) ? 0.f : M;
+    float den = 0.f, ax = 0.f, ay = 0.f;
+    for (int s2 = 0; s2 < p.num_splits; ++s2) {
+      const float wg = exp2f(__ldcg(p.ws_lse + s2 * sstride + orow) - Ms);
+      den += wg;
+      if (wg > 0.f) {
+        float2 v = __ldcg(reinterpret_cast<const float2*>(p.ws_o + (s2 * sstride + orow) * D + c));
+        ax += v.x * wg;
+        ay += v.y * wg;
+      }
+    }
+    if (p.sinks != nullptr) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    *reinterpret_cast<uint32_t*>(reinterpret_cast<T*>(p.out) + orow * D + c) = MT::pack(ax * inv, ay * inv);
+  }
+  if (tid == 0) g_decode_tickets[ticket_idx] = 0;
 }
 
 template <typename T, int D, int kWarps, int kStages>
-static int launch_decode(const AttnParams& p, int B, int max_q_rows, cudaStream_t st) {
+static int launch_decode(AttnParams p, int B, int max_q_rows, cudaStream_t st, bool* merged) {
   size_t kv_bytes = (size_t)kWarps * kStages * 2 * kDecTile * D * sizeof(T);
   size_t merge_bytes = (size_t)(kWarps * 16 * D + 2 * kWarps * 16) * sizeof(float);
   size_t smem = (size_t)16 * D * sizeof(T) + (kv_bytes > merge_bytes ? kv_bytes : merge_bytes);
@@ -288,19 +331,23 @@ static int launch_decode(const AttnParams& p, int B, int max_q_rows, cudaStream_
     attr_set = true;
   }
   dim3 grid((max_q_rows + 15) / 16, p.Hkv, B * p.num_splits);
+  static const bool fuse_on = [] { const char* e = getenv("B200_ATTN_FUSE_MERGE"); return !(e != nullptr && e[0] == '0'); }();
+  p.fuse_merge = fuse_on && p.num_splits > 1 && (int64_t)B * p.Hkv * grid.x <= kMaxTickets;
+  *merged = p.fuse_merge != 0;
   return (int)launch_pdl(kern, grid, dim3(kWarps * 32), smem, st, p);
 }
 
-int paged_decode_dispatch(const AttnParams& p, int B, int max_q_rows, int D, int dtype, cudaStream_t st) {
+int paged_decode_dispatch(const AttnParams& p, int B, int max_q_rows, int D, int dtype, cudaStream_t st, bool* merged) {
+  *merged = false;
   if (p.block_size % kDecTile) return 4;
   if (dtype == kBF16) {
-    if (D == 128) return launch_decode<__nv_bfloat16, 128, 4, 3>(p, B, max_q_rows, st);
-    if (D == 64) return launch_decode<__nv_bfloat16, 64, 4, 4>(p, B, max_q_rows, st);
-    if (D == 256) return launch_decode<__nv_bfloat16, 256, 4, 2>(p, B, max_q_rows, st);
+    if (D == 128) return launch_decode<__nv_bfloat16, 128, 4, 3>(p, B, max_q_rows, st, merged);
+    if (D == 64) return launch_decode<__nv_bfloat16, 64, 4, 4>(p, B, max_q_rows, st, merged);
+    if (D == 256) return launch_decode<__nv_bfloat16, 256, 4, 2>(p, B, max_q_rows, st, merged);
   } else if (dtype == kF16) {
-    if (D == 128) return launch_decode<__half, 128, 4, 3>(p, B, max_q_rows, st);
-    if (D == 64) return launch_decode<__half, 64, 4, 4>(p, B, max_q_rows, st);
-    if (D == 256) return launch_decode<__half, 256, 4, 2>(p, B, max_q_rows, st);
+    if (D == 128) return launch_decode<__half, 128, 4, 3>(p, B, max_q_rows, st, merged);
+    if (D == 64) return launch_decode<__half, 64, 4, 4>(p, B, max_q_rows, st, merged);
+    if (D == 256) return launch_decode<__half, 256, 4, 2>(p, B, max_q_rows, st, merged);
   }
   return 3;
 }
