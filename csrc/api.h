@@ -29,6 +29,7 @@ typedef struct GemmArgs {
   int num_sms;
   int stages;         // 0 = choose from the shared-memory budget
   int ctas_per_sm;    // 0 = choose (2 for small token tiles)
+  int act;            // 0 = plain; 1 silu, 2 gelu-tanh, 3 swigluoai on [64 gate | 64 up] interleaved weight tiles
   // collective fusion over peer memory (all zero / null = plain GEMM)
   void* rs_stage[8];  // reduce-scatter: staging area of every rank (peer mappings)
   void* rs_flags[8];  // reduce-scatter: per-(source, token tile) arrival counters on every rank

@@ -101,14 +101,18 @@ void set_gemm_comm(std::vector<int64_t> rs_stage, std::vector<int64_t> rs_flags,
 
 // out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  splits <= 0 lets the library choose.
 void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
-          int64_t splits, int64_t bn_override, int64_t stages, int64_t ctas_per_sm) {
+          int64_t splits, int64_t bn_override, int64_t stages, int64_t ctas_per_sm, int64_t act) {
   TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda());
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2);
   TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == out.scalar_type());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "gemm: bf16/fp16 only");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1);
   const int T = x.size(0), K = x.size(1), N = w.size(0);
-  TORCH_CHECK(w.size(1) == K && out.size(0) == T && out.size(1) == N);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == T && out.size(1) == (act ? N / 2 : N));
+  if (act) {
+    TORCH_CHECK(N % 128 == 0 && out.stride(0) % 8 == 0, "fused gate/up activation needs whole [64 | 64] weight tiles");
+    splits = 1;  // whole tiles only: both halves of a feature pair must meet in one epilogue
+  }
   TORCH_CHECK(K % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0, "gemm: K and row strides must be multiples of 8");
   if (T == 0 || N == 0) return;
   c10::cuda::CUDAGuard guard(x.device());
@@ -169,6 +173,7 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
   a.num_sms = gs.num_sms;
   a.stages = (int)stages;
   a.ctas_per_sm = (int)ctas_per_sm;
+  a.act = (int)act;
   const Tmap& tw = get_tmap(gs, w, 128, 2);
   const Tmap& tx = get_tmap(gs, x, a.bn, 2);
   check(b200_gemm_launch(&a, tw.b, tx.b, stream()), "gemm launch");

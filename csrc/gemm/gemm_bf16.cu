@@ -68,12 +68,25 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Gated activations fused into the epilogue of a gate/up projection whose weight rows are interleaved per tile as
+// [64 gate rows | 64 up rows]: act = 1 SiLU, 2 GELU (tanh), 3 clamped SwiGLU of GPT-OSS.
+__device__ __forceinline__ float gated_act(float g, float u, int act) {
+  if (act == 1) return g / (1.f + __expf(-g)) * u;
+  if (act == 2) {
+    const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    return 0.5f * g * (1.f + t) * u;
+  }
+  g = fminf(g, 7.f);
+  u = fminf(fmaxf(u, -7.f), 7.f);
+  return g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+}
+
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
                int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
-               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages, int l2_prefetch,
+               int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages, int l2_prefetch, int act,
                const __grid_constant__ GemmComm cm) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -315,7 +328,49 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
           return out + (size_t)t * ldo;
         };
-        if (BN >= kEpChunk) {
+        if (act != 0) {
+          // gate / up tile: stage [token][128] in shared memory (rounded to OutT, as an unfused projection would hand
+          // it to the activation kernel), then every thread combines 8 gate features with their 8 up features and
+          // writes 16 bytes of the half-width output row
+          constexpr int kChunk = BN < kEpChunk ? BN : kEpChunk;
+          const int n_local = quarter * 32 + lane;
+          const int n0 = nt * (BM / 2);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += kChunk) {
+            if (t0 + c0 < T) {
+#pragma unroll
+              for (int c = 0; c < kChunk; c += 16) {
+                uint32_t r[16];
+                tmem_ld_x16(taddr + c0 + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  smem_ep[(c + j) * kEpStride + n_local] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+              }
+            }
+            if (c0 + kChunk >= BN) {
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (t0 + c0 < T) {
+              const int seg = ep_tid & 7;            // 8 segments of 8 output features
+              for (int rr = ep_tid >> 3; rr < kChunk; rr += 16) {
+                const int t = t0 + c0 + rr;
+                if (t >= T) break;
+                const OutT* gsrc = smem_ep + rr * kEpStride + seg * 8;
+                const OutT* usrc = gsrc + BM / 2;
+                alignas(16) OutT res[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  res[e] = from_float<OutT>(gated_act(to_float<OutT>(gsrc[e]), to_float<OutT>(usrc[e]), act));
+                *reinterpret_cast<uint4*>(out + (size_t)t * ldo + n0 + seg * 8) = *reinterpret_cast<const uint4*>(res);
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+        } else if (BN >= kEpChunk) {
           // TMEM -> registers -> shared [token][feature] -> 16-byte row segments (256 B per token row)
           const int n_local = quarter * 32 + lane;
           const int n0 = nt * BM;
@@ -464,7 +519,7 @@ template <int BN, typename OutT>
 static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CUtensorMap& tmX, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tn_kernel<BN, OutT>;
-  constexpr int kEpBytes = (BN >= kEpChunk) ? kEpChunk * kEpStride * 2 + 64 : 64;
+  constexpr int kEpBytes = (BN >= kEpChunk ? kEpChunk : BN) * kEpStride * 2 + 64;  // staging tile of the epilogue
   GemmComm cm;
   for (int i = 0; i < 8; ++i) { cm.rs_stage[i] = a.rs_stage[i]; cm.rs_flags[i] = (uint32_t*)a.rs_flags[i]; }
   cm.ag_flags = (const uint32_t*)a.ag_flags;
@@ -491,7 +546,7 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   int smem = stages * Cfg::kStageBytes + 1024 + 512 + kEpBytes;
   return launch_pdl(kern, dim3(a.grid), dim3(kGemmThreads), (size_t)smem, st, tmW, tmX, (OutT*)a.out,
                     (const OutT*)a.bias, a.ws, a.counters, a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta,
-                    a.max_contrib, a.fmt, a.ldo, stages, b200::gemm_l2_prefetch(), cm);
+                    a.max_contrib, a.fmt, a.ldo, stages, b200::gemm_l2_prefetch(), a.act, cm);
 }
 
 }  // namespace b200

@@ -75,3 +75,13 @@ def test_preemption_recompute():
     assert llm.engine.stats["preemptions"] > 0
     for p, o in zip(prompts, outs):
         assert o.token_ids == greedy_plain(model, cfg, p, 20)
+
+
+def test_profile_run_leaves_engine_usable():
+    from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+    cfg = tiny(qwen2_0_5b(), num_layers=1, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    want = llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids
+    assert llm.engine.runner.profile_run(64) == 0
+    assert llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids == want

@@ -53,3 +53,17 @@ def test_graph_decode_equals_eager():
         if not eager:
             assert llm.engine.runner.graphs.hits > 0
     assert outs[0] == outs[1]
+
+
+def test_capture_all_then_generate_matches_lazy_capture():
+    cfg = _tiny()
+    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (40, 12)]
+    sp = SamplingParams(max_tokens=16, ignore_eos=True)
+    kw = dict(device="cuda", block_size=16, max_model_len=512, max_num_seqs=8, num_gpu_blocks=256, seed=3)
+    lazy = LLM(cfg, **kw)
+    a = [o.token_ids for o in lazy.generate(prompts, sp)]
+    warm = LLM(cfg, **kw)
+    sizes = warm.engine.runner.graphs.capture_all()
+    assert sizes and warm.engine.runner.profile_run(256) > 0
+    b = [o.token_ids for o in warm.generate(prompts, sp)]
+    assert a == b

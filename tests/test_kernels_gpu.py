@@ -225,3 +225,22 @@ def test_cache_ops():
     ro, rl = ra.merge_attn_states(o1.cpu(), l1.cpu(), o2.cpu(), l2.cpu())
     _close(mo, ro, 2e-2, 2e-2, "merge o")
     _close(ml, rl, 1e-3, 1e-3, "merge lse")
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh", "swigluoai"])
+@pytest.mark.parametrize("T", [1, 16, 200, 1000])
+def test_gemm_fused_gated_activation(T, act):
+    """Gate/up projection with the activation in the GEMM epilogue == projection followed by act_and_mul (bitwise:
+    the epilogue rounds gate and up to bf16 before the activation, exactly like the two-kernel path)."""
+    from vllm_kunlun_b200.ops.gemm_cuda import gemm_bf16, interleave_gate_up
+    torch.manual_seed(T)
+    K, I = 512, 1536
+    x = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device="cuda") * 0.05).to(torch.bfloat16)
+    b = (torch.randn(2 * I, device="cuda") * 0.1).to(torch.bfloat16)
+    want = ops.act_and_mul(gemm_bf16(x, w, b), act)
+    got = ops.linear_gated_act(x, interleave_gate_up(w), interleave_gate_up(b), act)
+    assert got.shape == (T, I)
+    assert torch.equal(got, want)
+    ref = ops.act_and_mul((x.float().cpu() @ w.float().cpu().T + b.float().cpu()).to(torch.bfloat16), act)
+    torch.testing.assert_close(got.float().cpu(), ref.float(), atol=3e-2, rtol=3e-2)

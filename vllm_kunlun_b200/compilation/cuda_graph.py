@@ -6,8 +6,7 @@ captured, and attention runs eagerly between pieces, one host launch sequence pe
 ``platforms/kunlun.py:100-106,366-378``).  The attention kernels here read all per-step state from
 device tensors at fixed addresses (block tables, lengths, slot mapping live in the runner's
 persistent staging buffers), so a whole decode step - embedding to logits - is captured as ONE graph
-per padded batch size and replayed with no per-layer host work.  ``mode="piecewise"`` keeps the
-reference's behaviour (attention outside the graphs) for backends that cannot be captured.
+per padded batch size and replayed with no per-layer host work.
 """
 from __future__ import annotations
 
@@ -90,5 +89,30 @@ class DecodeGraphs:
         return tokens, self.hidden[key]
 
     def capture_all(self):
-        """Eagerly capture every configured size with a synthetic batch (server warm-up)."""
-        raise NotImplementedError
+        """Eagerly capture every configured size with a synthetic decode batch (server warm-up), so that the first
+        real request of each size does not pay for the capture."""
+        from ..engine.request import Request, SamplingParams
+        from ..engine.scheduler import ScheduledRequest, SchedulerOutput
+        r = self.runner
+        done = []
+        with torch.inference_mode():
+            for size in self.sizes:
+                if size in self.graphs:
+                    continue
+                reqs = []
+                for i in range(size):
+                    q = Request(f"warmup-{size}-{i}", [1] * self.tokens_per_req, SamplingParams(max_tokens=1))
+                    q.block_ids = [0]
+                    q.num_computed_tokens = 0
+                    reqs.append(ScheduledRequest(q, self.tokens_per_req, True, True))
+                    if self.tokens_per_req > 1:
+                        q.prompt_token_ids, q.spec_token_ids = [1], [1] * (self.tokens_per_req - 1)
+                sched = SchedulerOutput(scheduled=reqs, num_tokens=size * self.tokens_per_req)
+                r.step_idx += 1
+                r._bind_staging()
+                md, ids, _ = r.prepare(sched, size)
+                md.slot_mapping.fill_(-1)  # synthetic tokens must not touch the cache
+                self._capture(md, ids)
+                done.append(size)
+            torch.cuda.synchronize()
+        return done

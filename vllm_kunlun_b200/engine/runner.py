@@ -479,4 +479,26 @@ class ModelRunner:
     def profile_run(self, num_tokens: int):
         """Dummy forward to size activations (``attn_metadata is None`` path of the reference,
         ``kunlun_attn.py:770-772``)."""
-        raise NotImplementedError
+        from .request import Request, SamplingParams
+        from .scheduler import ScheduledRequest
+        n = max(1, min(num_tokens, self.max_tokens))
+        req = Request("profile-run", [1] * n, SamplingParams(max_tokens=1))
+        req.block_ids = [0] * cdiv(n, self.tokens_per_block)
+        if self.num_state_slots:
+            req.state_slot = 0
+        sched = SchedulerOutput(scheduled=[ScheduledRequest(req, n, False, True)], num_tokens=n)
+        self.step_idx += 1
+        self._bind_staging()
+        with torch.inference_mode():
+            md, ids, (sample_reqs, rows, n_logits) = self.prepare(sched)
+            md.slot_mapping.fill_(-1)  # nothing is written to the cache
+            md.is_dummy = True
+            sp = self.sampler.make_params([req.sampling], rows, n_logits)
+            if self.is_cuda:
+                torch.cuda.synchronize()
+                torch.cuda.reset_peak_memory_stats(self.device)
+            self.forward_and_sample(md, ids, sp)
+            if self.is_cuda:
+                torch.cuda.synchronize()
+                return int(torch.cuda.max_memory_allocated(self.device))
+        return 0

@@ -247,6 +247,9 @@ def main(argv=None):
     llm = LLM(a.model, tensor_parallel_size=a.tensor_parallel_size, max_model_len=a.max_model_len,
               max_num_seqs=a.max_num_seqs, block_size=a.block_size, gpu_memory_utilization=a.gpu_memory_utilization,
               enforce_eager=a.enforce_eager, tokenizer=tokenizer)
+    graphs = llm.engine.runner.graphs
+    if graphs is not None:  # capture every decode batch size before the first request arrives
+        graphs.capture_all()
     app = build_app(llm, a.served_model_name or a.model, a.reasoning_parser, a.tool_call_parser)
     uvicorn.run(app, host=a.host, port=a.port, log_level="info")
 

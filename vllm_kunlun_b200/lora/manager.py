@@ -77,6 +77,11 @@ class LoRAManager:
         self.states: dict = {}
         self.slot_of: dict = {}  # lora_int_id -> slot
         self.lru: list = []
+        from ..models import dense as _dense
+        _dense.ACT_FUSION[0] = False  # adapters add to the separate gate / up outputs
+        for mod in model.modules():
+            if isinstance(mod, _dense.GatedMLP):
+                mod.set_act_fused(False)
         for name, mod in model.named_modules():
             if isinstance(mod, (ColumnParallelLinear, RowParallelLinear)) and getattr(mod, "weight", None) is not None \
                     and mod.weight.dim() == 2 and name.split(".")[-1] != "in_proj_ba":

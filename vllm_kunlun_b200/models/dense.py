@@ -21,6 +21,9 @@ from .layers import (DTYPES, ColumnParallelLinear, ParallelLMHead, RMSNorm, RowP
                      VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm, sp_sync)
 
 
+ACT_FUSION = [True]  # switched off while LoRA adapters wrap the gate / up projection
+
+
 class GQAAttention(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
         super().__init__()
@@ -95,9 +98,42 @@ class GatedMLP(nn.Module):
         self.down_proj = RowParallelLinear(inter, hidden, bias=bias, dtype=dtype, device=device, quant=quant,
                                            reduce_results=reduce_results, tp_size=tp_size, tp_rank=tp_rank)
         self.act = act
+        self.act_fused = False  # gate_up weight rows interleaved for the fused activation epilogue
 
     def forward(self, x):
+        if self.act_fused:
+            gu = self.gate_up_proj
+            return self.down_proj(ops.linear_gated_act(x, gu.weight, gu.bias, self.act))
         return self.down_proj(ops.act_and_mul(self.gate_up_proj(x), self.act))
+
+    # The fused layout is an in-place row permutation of the loaded weight: checkpoints are loaded and saved in
+    # the plain [gate | up] order.
+    def set_act_fused(self, on: bool) -> None:
+        from ..ops.gemm_cuda import interleave_gate_up
+        gu = self.gate_up_proj
+        w = getattr(gu, "weight", None)
+        eligible = (type(gu.method).__name__ == "UnquantizedLinearMethod" and w is not None and w.is_cuda
+                    and w.dtype in (torch.bfloat16, torch.float16) and (w.shape[0] // 2) % 64 == 0
+                    and self.act in ("silu", "gelu_tanh", "swigluoai") and ACT_FUSION[0])
+        if on == self.act_fused or (on and not eligible):
+            return
+        w.data.copy_(interleave_gate_up(w.data, inverse=not on))
+        if gu.bias is not None:
+            gu.bias.data.copy_(interleave_gate_up(gu.bias.data, inverse=not on))
+        self.act_fused = on
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+
+    def state_dict(self, *args, destination=None, prefix="", keep_vars=False):
+        from ..ops.gemm_cuda import interleave_gate_up
+        sd = super().state_dict(*args, destination=destination, prefix=prefix, keep_vars=keep_vars)
+        if self.act_fused:
+            for name in ("weight", "bias"):
+                key = f"{prefix}gate_up_proj.{name}"
+                if key in sd and sd[key] is not None:
+                    sd[key] = interleave_gate_up(sd[key], inverse=True)
+        return sd
 
 
 class DenseDecoderLayer(nn.Module):
@@ -234,6 +270,8 @@ class DenseForCausalLM(nn.Module):
             meth = getattr(m, "method", None)
             if meth is not None:
                 meth.process_weights_after_loading(m)
+            if isinstance(m, GatedMLP):
+                m.set_act_fused(True)
 
     def _resolve(self, name: str):
         """Checkpoint tensor name -> (module, param name, shard id) or None when not on this stage."""
@@ -260,6 +298,9 @@ class DenseForCausalLM(nn.Module):
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
         loaded = set()
+        for m in self.modules():
+            if isinstance(m, GatedMLP):
+                m.set_act_fused(False)  # checkpoints carry the plain [gate | up] order
         for name, w in weights:
             if "rotary_emb.inv_freq" in name:
                 continue

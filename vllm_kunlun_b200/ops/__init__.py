@@ -234,6 +234,17 @@ def linear(x, weight, bias=None, out=None):
     return _rb.linear(x, weight, bias)
 
 
+def linear_gated_act(x, weight_interleaved, bias_interleaved=None, act: str = "silu"):
+    """``act(x W_gate^T) * (x W_up^T)`` in one GEMM: the activation runs in the epilogue over weight tiles that
+    hold 64 gate rows and the 64 matching up rows (CUDA only; see ``gemm_cuda.interleave_gate_up``)."""
+    from .gemm_cuda import gemm_bf16, interleave_gate_up
+    if x.is_cuda:
+        return gemm_bf16(x, weight_interleaved, bias_interleaved, act=act)
+    w = interleave_gate_up(weight_interleaved, inverse=True)
+    b = None if bias_interleaved is None else interleave_gate_up(bias_interleaved, inverse=True)
+    return act_and_mul(_rb.linear(x, w, b), act)
+
+
 def embedding(ids, weight, vocab_start: int = 0):
     """Vocab-parallel gather: rows outside ``[vocab_start, vocab_start + rows)`` yield zeros
     (``ops/vocab_parallel_embedding.py:94-118``)."""

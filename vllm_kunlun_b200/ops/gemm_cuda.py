@@ -13,14 +13,32 @@ LAUNCHES = 0
 PEER = None  # PeerBuffers of the tensor-parallel group once its sequence-parallel buffers exist
 
 
+ACT_CODES = {None: 0, "silu": 1, "gelu_tanh": 2, "swigluoai": 3}
+
+
+def interleave_gate_up(w: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """Row order of a ``[gate | up]`` projection for the fused activation epilogue: per 128-row weight tile,
+    64 gate rows followed by the 64 up rows of the same features (``inverse`` undoes it)."""
+    n2 = w.shape[0]
+    n = n2 // 2
+    assert n % 64 == 0
+    if inverse:
+        v = w.reshape(n // 64, 2, 64, *w.shape[1:])
+        return torch.cat([v[:, 0].reshape(n, *w.shape[1:]), v[:, 1].reshape(n, *w.shape[1:])], 0)
+    g, u = w[:n].reshape(n // 64, 1, 64, *w.shape[1:]), w[n:].reshape(n // 64, 1, 64, *w.shape[1:])
+    return torch.cat([g, u], 1).reshape(n2, *w.shape[1:]).contiguous()
+
+
 def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits: int = 0, bn: int = 0,
-              stages: int = 0, ctas_per_sm: int = 0):
+              stages: int = 0, ctas_per_sm: int = 0, act=None):
+    """``act``: gated activation fused into the epilogue; ``weight`` (and ``bias``) rows are then interleaved per
+    tile (:func:`interleave_gate_up`) and the output has ``N / 2`` features."""
     global LAUNCHES
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
         x2 = x2.contiguous()
-    N = weight.shape[0]
+    N = weight.shape[0] // 2 if act else weight.shape[0]
     if out is None:
         out = torch.empty(x2.shape[0], N, dtype=x.dtype, device=x.device)
     out2 = out.reshape(-1, N)
@@ -28,7 +46,7 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits
         ag_bn = PEER.sp_consume(x2)
         if ag_bn:  # gathered activations: the producer waits per token tile, tiles must match the counters
             bn, splits = ag_bn, 1
-    _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm)
+    _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm, ACT_CODES[act])
     LAUNCHES += 1
     return out.reshape(*lead, N)
 
