@@ -21,6 +21,10 @@ _ENV: dict[str, Callable[[], Any]] = {
     "B200_PDL": lambda: os.environ.get("B200_PDL", "1") != "0",
     # 16 KB weight tiles per CTA that a decode-shaped GEMM pulls into L2 ahead of its smem ring (read by the C++ side; measured slower than off)
     "B200_GEMM_L2_PREFETCH": lambda: int(os.environ.get("B200_GEMM_L2_PREFETCH", "0")),
+    # gated activation inside the gate/up GEMM epilogue (interleaved weight tiles); decode attention merging its own
+    # split-KV partials (read by the C++ side)
+    "B200_FUSE_ACT": lambda: os.environ.get("B200_FUSE_ACT", "1") != "0",
+    "B200_ATTN_FUSE_MERGE": lambda: os.environ.get("B200_ATTN_FUSE_MERGE", "1") != "0",
     # peer-memory collectives (one-shot all-reduce, fused GEMM+collectives)
     "B200_PEER_COLLECTIVES": lambda: os.environ.get("B200_PEER_COLLECTIVES", "1") != "0",
     # exponential-race sampling with a cached noise tensor (the reference's FAST_RANDOM_SAMPLE)

@@ -8,6 +8,7 @@ RoPE -> cache write -> attention -> o_proj (all-reduce) -> add+RMSNorm -> gate_u
 """
 from __future__ import annotations
 
+import os
 from typing import Iterable, Optional
 
 import torch
@@ -21,7 +22,7 @@ from .layers import (DTYPES, ColumnParallelLinear, ParallelLMHead, RMSNorm, RowP
                      VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm, sp_sync)
 
 
-ACT_FUSION = [True]  # switched off while LoRA adapters wrap the gate / up projection
+ACT_FUSION = [os.environ.get("B200_FUSE_ACT", "1") != "0"]  # also switched off while LoRA adapters wrap gate / up
 
 
 class GQAAttention(nn.Module):
@@ -114,7 +115,7 @@ class GatedMLP(nn.Module):
         w = getattr(gu, "weight", None)
         eligible = (type(gu.method).__name__ == "UnquantizedLinearMethod" and w is not None and w.is_cuda
                     and w.dtype in (torch.bfloat16, torch.float16) and (w.shape[0] // 2) % 64 == 0
-                    and self.act in ("silu", "gelu_tanh", "swigluoai") and ACT_FUSION[0])
+                    and self.act in ("silu", "gelu_tanh") and ACT_FUSION[0])
         if on == self.act_fused or (on and not eligible):
             return
         w.data.copy_(interleave_gate_up(w.data, inverse=not on))
