@@ -139,6 +139,10 @@ int b200_oneshot_allreduce(void* const* bufs, const void* in, void* out, void* r
                            int nranks, int rows, int H, float eps, int gemma, int grid, uint32_t spin_limit, int dtype,
                            cudaStream_t st);
 
+int b200_ll_allreduce(void* const* bufs, const void* in, void* out, void* residual, const void* weight,
+                      uint32_t* epochs, int* status, int64_t slot_bytes, int rank, int nranks, int rows, int H,
+                      float eps, int gemma, int grid, uint32_t spin_limit, int dtype, cudaStream_t st);
+
 // Reduce-scatter consumer: sum R partial rows + residual, RMSNorm, push the row to every rank (see rs_norm_ag.cu)
 typedef struct RsNormArgs {
   const void* stage; const void* rs_flags;

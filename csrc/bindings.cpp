@@ -545,6 +545,21 @@ void oneshot_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tens
         "oneshot_allreduce");
 }
 
+void ll_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tensor out,
+                  const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& weight, at::Tensor epochs,
+                  at::Tensor status, int64_t slot_bytes, int64_t rank, double eps, bool gemma, int64_t grid,
+                  int64_t spin_limit) {
+  TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.dim() == 2 && in.element_size() == 2);
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && weight.has_value());
+  void* ptrs[8] = {nullptr};
+  TORCH_CHECK(bufs.size() <= 8);
+  for (size_t i = 0; i < bufs.size(); ++i) ptrs[i] = reinterpret_cast<void*>(bufs[i]);
+  check(b200_ll_allreduce(ptrs, in.data_ptr(), out.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
+                          opt_ptr(weight), reinterpret_cast<uint32_t*>(epochs.data_ptr<int>()), status.data_ptr<int>(),
+                          slot_bytes, rank, bufs.size(), in.size(0), in.size(1), (float)eps, gemma, grid,
+                          (uint32_t)spin_limit, dtype_code(in), stream()), "ll_allreduce");
+}
+
 at::Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, at::ScalarType dtype, int64_t device) {
   auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, device);
   return at::from_blob(reinterpret_cast<void*>(ptr), shape, opts);
@@ -793,6 +808,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("allreduce_max_ctas", &allreduce_max_ctas);
   m.def("allreduce_flag_bytes", &allreduce_flag_bytes);
   m.def("oneshot_allreduce", &oneshot_allreduce);
+  m.def("ll_allreduce", &ll_allreduce);
   m.def("set_gemm_comm", &set_gemm_comm);
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("rs_norm_ag", &rs_norm_ag);

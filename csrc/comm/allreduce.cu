@@ -56,6 +56,7 @@ struct ArParams {
   float eps;
   int gemma;
   uint32_t spin_limit;
+  int64_t ll_slot_bytes;     // low-latency variant: bytes of one (parity, source) slot of a symmetric buffer
 };
 
 template <typename T, bool kNorm>
@@ -157,6 +158,126 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams 
   }
 }
 
+
+// ---- low-latency variant for decode-sized payloads -------------------------------------------------------------
+// Every 4 bytes of payload travel in an 8-byte unit {data, epoch}, written straight into the DESTINATION rank's
+// buffer (slot [parity][source]) with 16-byte stores whose 8-byte halves are each written atomically.  A receiver
+// polls its own memory until all units of a vector carry the current epoch: arrival of the flag is arrival of the
+// data, so no fence, no separate flag store and no remote load is on the critical path - one NVLink traversal
+// instead of three.  Sums are taken in rank order (own contribution from the input tensor), so all ranks end up
+// with the same bits.  Two parities for the same reason as above; epochs live in device memory.
+__device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T, bool kNorm>
+__global__ void __launch_bounds__(kArThreads) ll_allreduce_kernel(ArParams p) {
+  static_assert(sizeof(T) == 2, "16-bit payloads");
+  constexpr int V = 8;
+  __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
+  const int c = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
+  const uint32_t epoch = p.epochs[c] + 1;
+  const int parity = epoch & 1;
+  const int nvec = p.H / V;
+  const int64_t row_bytes = (int64_t)p.H * 4;  // 2 H bytes of payload, doubled by the flags
+  auto slot = [&](int dest, int src) {
+    return reinterpret_cast<uint8_t*>(p.bufs[dest]) + ((int64_t)parity * p.nranks + src) * p.ll_slot_bytes;
+  };
+  // 1. push my rows to every peer
+  for (int row = c; row < p.rows; row += G) {
+    for (int i = tid; i < nvec; i += kArThreads) {
+      const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.in) + (int64_t)row * p.H + i * V);
+      for (int d = 0; d < p.nranks; ++d) {
+        if (d == p.rank) continue;
+        uint8_t* dst = slot(d, p.rank) + row * row_bytes + (int64_t)i * 32;
+        st_volatile_v4(dst, v.x, epoch, v.y, epoch);
+        st_volatile_v4(dst + 16, v.z, epoch, v.w, epoch);
+      }
+    }
+  }
+  // 2. collect and reduce
+  for (int row = c; row < p.rows; row += G) {
+    float ss = 0.f;
+    constexpr int kMaxKeep = 4;
+    float keep[kMaxKeep][V];
+    int k = 0;
+    for (int i = tid; i < nvec; i += kArThreads, ++k) {
+      float acc[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+      for (int r = 0; r < p.nranks; ++r) {
+        uint4 raw;
+        if (r == p.rank) {
+          raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.in) + (int64_t)row * p.H + i * V);
+        } else {
+          const uint8_t* src = slot(p.rank, r) + row * row_bytes + (int64_t)i * 32;
+          bool ok = false;
+          for (uint32_t it = 0; it < p.spin_limit; ++it) {
+            uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(src + 16);
+            if (a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch) {
+              raw = make_uint4(a.x, a.z, b.x, b.z);
+              ok = true;
+              break;
+            }
+            if (it > 4096) __nanosleep(32);
+          }
+          if (!ok) { atomicCAS(p.status, 0, 210 + r); raw = make_uint4(0, 0, 0, 0); }
+        }
+        const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] += to_f(v[j]);
+      }
+      if (kNorm) {
+        T* rr = reinterpret_cast<T*>(p.residual) + (int64_t)row * p.H + i * V;
+        Vec16<T> res = ld_vec(rr);
+        Vec16<T> sum;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float s = to_f(from_f<T>(acc[j])) + to_f(res.v[j]);
+          sum.v[j] = from_f<T>(s);
+          float f = to_f(sum.v[j]);
+          ss += f * f;
+          if (k < kMaxKeep) keep[k][j] = f;
+        }
+        st_vec(rr, sum);
+      } else {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(acc[j]);
+        st_vec(reinterpret_cast<T*>(p.out) + (int64_t)row * p.H + i * V, o);
+      }
+    }
+    if (kNorm) {
+      ss = block_sum(ss, red);
+      const float inv = rsqrtf(ss / p.H + p.eps);
+      k = 0;
+      for (int i = tid; i < nvec; i += kArThreads, ++k) {
+        Vec16<T> w = ld_vec(reinterpret_cast<const T*>(p.weight) + i * V);
+        Vec16<T> o;
+        if (k < kMaxKeep) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(keep[k][j] * inv * (to_f(w.v[j]) + (p.gemma ? 1.f : 0.f)));
+        } else {
+          Vec16<T> s2 = ld_vec(reinterpret_cast<const T*>(p.residual) + (int64_t)row * p.H + i * V);
+#pragma unroll
+          for (int j = 0; j < V; ++j) o.v[j] = from_f<T>(to_f(s2.v[j]) * inv * (to_f(w.v[j]) + (p.gemma ? 1.f : 0.f)));
+        }
+        st_vec(reinterpret_cast<T*>(p.out) + (int64_t)row * p.H + i * V, o);
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  if (tid == 0) p.epochs[c] = epoch;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -174,7 +295,7 @@ extern "C" int b200_oneshot_allreduce(void* const* bufs, const void* in, void* o
   for (int i = 0; i < kArMaxRanks; ++i) p.bufs[i] = i < nranks ? bufs[i] : nullptr;
   p.in = in; p.out = out; p.residual = residual; p.weight = weight; p.epochs = epochs; p.status = status;
   p.parity_bytes = parity_bytes; p.flags_offset = flags_offset; p.rank = rank; p.nranks = nranks; p.rows = rows;
-  p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit;
+  p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit; p.ll_slot_bytes = 0;
   if (dtype == kBF16) {
     if (H % 8) return 2;
     if (residual) launch_pdl(oneshot_allreduce_kernel<__nv_bfloat16, true>, dim3(grid), dim3(kArThreads), 0, st, p);
@@ -187,6 +308,29 @@ extern "C" int b200_oneshot_allreduce(void* const* bufs, const void* in, void* o
     if (H % 4) return 2;
     if (residual) launch_pdl(oneshot_allreduce_kernel<float, true>, dim3(grid), dim3(kArThreads), 0, st, p);
     else launch_pdl(oneshot_allreduce_kernel<float, false>, dim3(grid), dim3(kArThreads), 0, st, p);
+  } else {
+    return 1;
+  }
+  return (int)cudaGetLastError();
+}
+
+// Low-latency all-reduce (see ll_allreduce_kernel): `bufs` are the ranks' LL buffers of 2 * nranks slots each.
+extern "C" int b200_ll_allreduce(void* const* bufs, const void* in, void* out, void* residual, const void* weight,
+                                 uint32_t* epochs, int* status, int64_t slot_bytes, int rank, int nranks, int rows, int H,
+                                 float eps, int gemma, int grid, uint32_t spin_limit, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (nranks > kArMaxRanks || grid > kArMaxCtas || grid < 1 || H % 8 || (int64_t)rows * H * 4 > slot_bytes) return 2;
+  ArParams p;
+  for (int i = 0; i < kArMaxRanks; ++i) p.bufs[i] = i < nranks ? bufs[i] : nullptr;
+  p.in = in; p.out = out; p.residual = residual; p.weight = weight; p.epochs = epochs; p.status = status;
+  p.parity_bytes = 0; p.flags_offset = 0; p.rank = rank; p.nranks = nranks; p.rows = rows;
+  p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit; p.ll_slot_bytes = slot_bytes;
+  if (dtype == kBF16) {
+    if (residual) launch_pdl(ll_allreduce_kernel<__nv_bfloat16, true>, dim3(grid), dim3(kArThreads), 0, st, p);
+    else launch_pdl(ll_allreduce_kernel<__nv_bfloat16, false>, dim3(grid), dim3(kArThreads), 0, st, p);
+  } else if (dtype == kF16) {
+    if (residual) launch_pdl(ll_allreduce_kernel<__half, true>, dim3(grid), dim3(kArThreads), 0, st, p);
+    else launch_pdl(ll_allreduce_kernel<__half, false>, dim3(grid), dim3(kArThreads), 0, st, p);
   } else {
     return 1;
   }

@@ -37,6 +37,18 @@ class PeerBuffers:
         self.ptrs = []
         for r, h in enumerate(handles):
             self.ptrs.append(self.local_ptr if r == self.rank else C.peer_open(h))
+        # low-latency buffers for decode-sized payloads: 2 parities x world slots, payload + flags interleaved
+        import os
+        self.ll_max_bytes = 256 << 10 if os.environ.get("B200_AR_LL", "1") != "0" else 0
+        self.ll_slot_bytes = 2 * self.ll_max_bytes
+        self.ll_ptrs = None
+        if self.ll_max_bytes:
+            self.ll_local = C.peer_alloc(2 * self.world * self.ll_slot_bytes)
+            ll_handles = [None] * self.world
+            dist.all_gather_object(ll_handles, C.peer_export(self.ll_local),
+                                   group=comm.cpu_group if self._use_cpu_group() else comm.group)
+            self.ll_ptrs = [self.ll_local if r == self.rank else C.peer_open(h) for r, h in enumerate(ll_handles)]
+            self.ll_epochs = torch.zeros(C.allreduce_max_ctas(), dtype=torch.int32, device=self.device)
         self.epochs = torch.zeros(C.allreduce_max_ctas(), dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.max_ctas = C.allreduce_max_ctas()
@@ -65,9 +77,18 @@ class PeerBuffers:
     def _grid(self, rows: int) -> int:
         return max(1, min(rows, self.max_ctas))
 
+    def _can_ll(self, x2: torch.Tensor) -> bool:
+        return (self.ll_ptrs is not None and x2.element_size() == 2 and x2.shape[-1] % 8 == 0
+                and x2.numel() * 2 <= self.ll_max_bytes)
+
     def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         x2 = x.reshape(-1, x.shape[-1])
         out = torch.empty_like(x2) if out is None else out.reshape(-1, x.shape[-1])
+        if self._can_ll(x2):
+            self.C.ll_allreduce(self.ll_ptrs, x2, out, None, None, self.ll_epochs, self.status, self.ll_slot_bytes,
+                                self.rank, 0.0, False, self._grid(x2.shape[0]), self.spin_limit)
+            self.launches += 1
+            return out.reshape(x.shape)
         self.C.oneshot_allreduce(self.ptrs, x2, out, None, None, self.epochs, self.status, self.parity_bytes,
                                  self.flags_offset, self.rank, 0.0, False, self._grid(x2.shape[0]), self.spin_limit)
         self.launches += 1
@@ -77,6 +98,12 @@ class PeerBuffers:
                                gemma: bool = False):
         """``residual += all_reduce(x); x = rmsnorm(residual) * w`` in one kernel; returns ``(x, residual)``."""
         x2 = x.reshape(-1, x.shape[-1])
+        if self._can_ll(x2):
+            self.C.ll_allreduce(self.ll_ptrs, x2, x2, residual.reshape(-1, x.shape[-1]), weight, self.ll_epochs,
+                                self.status, self.ll_slot_bytes, self.rank, eps, gemma, self._grid(x2.shape[0]),
+                                self.spin_limit)
+            self.launches += 1
+            return x, residual
         self.C.oneshot_allreduce(self.ptrs, x2, x2, residual.reshape(-1, x.shape[-1]), weight, self.epochs,
                                  self.status, self.parity_bytes, self.flags_offset, self.rank, eps, gemma,
                                  self._grid(x2.shape[0]), self.spin_limit)
