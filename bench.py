@@ -101,7 +101,7 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The reference is a Kunlun-XPU plugin: `pip install --no-index ... /root/reference` fails offline
+    # The reference is a Kunlun-XPU plugin: its offline `pip install --no-index ...` fails
     # (build backend `hatchling` is not in the wheelhouse) and, installed or not, it imports closed
     # vendor wheels (kunlun_ops, xspeedgate_ops, cocopod) at module top level.
     print(json.dumps({"impl": "reference", "unavailable":
