@@ -36,6 +36,13 @@ BASELINE_TOK_S = {  # published by the reference (Kunlun3 P800), 16-way, 2048/20
 }
 
 
+BASELINE_REF = {
+    "llama-3.1-8b": "Qwen3-8B TP=1 on Kunlun3 P800 (closest published analogue)",
+    "qwen3-8b": "Qwen3-8B TP=1 on Kunlun3 P800",
+    "qwen3-30b-a3b": "Qwen3-30B-A3B TP=2 on 2x Kunlun3 P800",
+}
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -47,6 +54,8 @@ def parse():
     ap.add_argument("--in-len", type=int, default=2048)
     ap.add_argument("--out-len", type=int, default=2048)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ep", action="store_true", help="expert parallelism for MoE models (whole experts per rank)")
+    ap.add_argument("--spec", default=None, help="speculative method (mtp | ngram | eagle), one draft token")
     return ap.parse_args()
 
 
@@ -127,8 +136,10 @@ def main():
         raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local)
     C, IN, OUT = args.concurrency, args.in_len, args.out_len
+    spec = {"method": args.spec, "num_speculative_tokens": 1} if args.spec else None
     llm = LLM(args.model, tensor_parallel_size=world, device="cuda", block_size=64, max_model_len=IN + OUT + 64,
-              max_num_seqs=C, max_num_batched_tokens=8192, gpu_memory_utilization=0.9, seed=0)
+              max_num_seqs=C, max_num_batched_tokens=8192, gpu_memory_utilization=0.9, seed=0,
+              enable_expert_parallel=args.ep and world > 1, speculative_config=spec)
     eng = llm.engine
     vocab = eng.cfg.model.vocab_size
     g = torch.Generator().manual_seed(1234)
@@ -196,13 +207,15 @@ def main():
             "metric": "output tok/s at 16 concurrency, 2048 in/2048 out", "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 2),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": round(value / base, 3) if base else None,
-            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+            "dtype": "fp8 weights (128x128 block scales), bf16 activations" if eng.cfg.model.quantization == "fp8" else "bf16",
+            "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": C, "seq_len": IN + OUT, "in_len": IN, "out_len": OUT,
-                       "parallelism": f"tp{world}", "step": "one full serving round of 16 requests",
-                       "l2": "inputs larger than L2: every decode step streams the whole weight set (16 GB bf16) "
-                             "and the KV cache",
-                       "baseline_ref": "Qwen3-8B TP=1 on Kunlun3 P800 (closest published analogue)"},
+                       "parallelism": f"tp{world}" + ("+ep" if args.ep and world > 1 else "") + (f"+{args.spec}" if args.spec else ""),
+                       "step": "one full serving round of 16 requests",
+                       "l2": "inputs larger than L2: every decode step streams the active weight set and the KV cache "
+                             "(16 GB of bf16 weights for the 8B dense model)",
+                       "baseline_ref": BASELINE_REF.get(args.model, "none published")},
             "p50_ttft_ms": round(statistics.median(ttfts) * 1e3, 1) if ttfts else None,
             "p50_tpot_ms": round(statistics.median(tpots) * 1e3, 3) if tpots else None,
             "clocks": clocks, "gpu_launches": int(launches),
