@@ -269,6 +269,38 @@ std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& ids, 
   return {xs, pos, lod};
 }
 
+// Small-batch permute in one launch; with `quant` the rows are written as fp8 with transposed 1x128 scales.
+// Returns (x_sorted | q_sorted, pos_of_pair, lod, scale_t or empty).
+std::vector<at::Tensor> moe_prepare_small(const at::Tensor& x, const at::Tensor& ids, const c10::optional<at::Tensor>& emap,
+                                          int64_t E_local, int64_t E_global, bool quant) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && ids.is_contiguous() && ids.scalar_type() == at::kInt);
+  const int64_t T = x.size(0), k = ids.size(1), H = x.size(1), M = T * k;
+  TORCH_CHECK(M <= b200_moe_small_pairs() && M >= 1);
+  auto xs = at::empty({M, H}, quant ? x.options().dtype(at::kByte) : x.options());
+  auto pos = at::empty({M}, ids.options());
+  auto lod = at::empty({E_local + 1}, ids.options());
+  int64_t stride = std::max<int64_t>(4, (M + 3) / 4 * 4);
+  auto st = quant ? at::zeros({H / 128, stride}, x.options().dtype(at::kFloat)) : at::empty({0}, x.options().dtype(at::kFloat));
+  check(b200_moe_prepare_small(xs.data_ptr(), quant ? st.data_ptr<float>() : nullptr, stride, pos.data_ptr<int>(),
+                               lod.data_ptr<int>(), x.data_ptr(), ids.data_ptr<int>(),
+                               emap.has_value() ? emap->data_ptr<int>() : nullptr, T, k, H, E_local, E_global, x.stride(0),
+                               quant, dtype_code(x), stream()), "moe_prepare_small");
+  return {xs, pos, lod, st};
+}
+
+// (q uint8 [rows, I], scale_t [I/128, stride]) = fp8(act(h[:, :I]) * h[:, I:])
+std::vector<at::Tensor> act_mul_quant_fp8(const at::Tensor& h, int64_t act, const c10::optional<at::Tensor>& rows_valid) {
+  TORCH_CHECK(h.dim() == 2 && h.is_contiguous() && h.size(1) % 256 == 0);
+  const int64_t rows = h.size(0), I = h.size(1) / 2;
+  int64_t stride = std::max<int64_t>(4, (rows + 3) / 4 * 4);
+  auto q = at::empty({rows, I}, h.options().dtype(at::kByte));
+  auto s = at::zeros({I / 128, stride}, h.options().dtype(at::kFloat));
+  check(b200_act_mul_quant_fp8(q.data_ptr(), s.data_ptr<float>(), h.data_ptr(), rows, I, stride, act,
+                               rows_valid.has_value() ? rows_valid->data_ptr<int>() : nullptr, dtype_code(h), stream()),
+        "act_mul_quant_fp8");
+  return {q, s};
+}
+
 void moe_unpermute(at::Tensor out, const at::Tensor& y_sorted, const at::Tensor& pos, const at::Tensor& w) {
   TORCH_CHECK(out.is_contiguous() && y_sorted.is_contiguous() && w.is_contiguous() && w.scalar_type() == at::kFloat);
   check(b200_moe_unpermute(out.data_ptr(), y_sorted.data_ptr(), pos.data_ptr<int>(), w.data_ptr<float>(), out.size(0),
@@ -767,6 +799,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_permute", &moe_permute, py::arg("x"), py::arg("ids"), py::arg("emap"), py::arg("E_local"),
         py::arg("E_global"), py::arg("state"), py::arg("max_rows") = 0);
   m.def("moe_unpermute", &moe_unpermute);
+  m.def("moe_prepare_small", &moe_prepare_small);
+  m.def("act_mul_quant_fp8", &act_mul_quant_fp8);
+  m.def("moe_small_pairs", []() { return (int64_t)b200_moe_small_pairs(); });
   m.def("quant_fp8_group", &quant_fp8_group);
   m.def("gemm_clear_tmap_cache", &gemm_clear_tmap_cache);
   m.def("rmsnorm", &rmsnorm);

@@ -282,6 +282,133 @@ __global__ void quant_fp8_group_kernel(uint8_t* __restrict__ q, float* __restric
   if (lane == 0) scale_t[(int64_t)g * s_stride + row] = scale;
 }
 
+
+// ---- small batches (decode): permute (+ fp8 quantisation) in ONE launch ----------------------------------------
+// With at most kSmallPairs (token, slot) pairs every CTA recomputes the whole schedule in shared memory - expert
+// counts, their exclusive scan and, for each pair, its rank among the earlier pairs of the same expert - so that
+// positions are deterministic and no global counters or second / third launch are needed.  CTA b then moves the
+// pairs b, b + G, ...: a plain row copy, or the 1x128 fp8 quantisation of the row straight into its permuted
+// place (scales in the transposed layout the grouped GEMM reads).  Replaces count + scan + scatter (+ quant).
+constexpr int kSmallPairs = 1024;
+
+template <typename T, bool kQuant>
+__global__ void __launch_bounds__(256) moe_prepare_small_kernel(
+    void* __restrict__ x_sorted, float* __restrict__ scale_t, int64_t s_stride, int* __restrict__ pos_of_pair,
+    int* __restrict__ lod, const T* __restrict__ x, const int* __restrict__ ids, const int* __restrict__ emap, int pairs,
+    int k, int H, int E_local, int E_global, int64_t x_stride) {
+  extern __shared__ int sh[];          // [E_local + 1] lod | [pairs] expert of pair | [pairs] position
+  int* s_lod = sh;
+  int* s_e = sh + E_local + 1;
+  int* s_pos = s_e + pairs;
+  griddep_launch();
+  griddep_wait();
+  const int tid = threadIdx.x;
+  for (int i = tid; i <= E_local; i += blockDim.x) s_lod[i] = 0;
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    int e = ids[p];
+    if (e >= 0 && e < E_global && emap) e = emap[e];
+    if (e < 0 || e >= E_local) e = -1;
+    s_e[p] = e;
+    if (e >= 0) atomicAdd(&s_lod[e + 1], 1);
+  }
+  __syncthreads();
+  if (tid < 32) {  // inclusive scan of the counts, 32 experts per round
+    int run = 0;
+    for (int e0 = 0; e0 < E_local; e0 += 32) {
+      int e = e0 + tid;
+      int c = e < E_local ? s_lod[e + 1] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffff, inc, o);
+        if (tid >= o) inc += v;
+      }
+      if (e < E_local) s_lod[e + 1] = run + inc;
+      run += __shfl_sync(0xffffffff, inc, 31);
+    }
+  }
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    const int e = s_e[p];
+    int pos = -1;
+    if (e >= 0) {
+      int rank = 0;
+      for (int q = 0; q < p; ++q) rank += (s_e[q] == e);
+      pos = s_lod[e] + rank;
+    }
+    s_pos[p] = pos;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int i = tid; i <= E_local; i += blockDim.x) lod[i] = s_lod[i];
+    for (int p = tid; p < pairs; p += blockDim.x) pos_of_pair[p] = s_pos[p];
+  }
+  const int warp = tid >> 5, lane = tid & 31, wpb = blockDim.x >> 5;
+  for (int p = blockIdx.x * wpb + warp; p < pairs; p += gridDim.x * wpb) {
+    const int pos = s_pos[p];
+    if (pos < 0) continue;
+    const T* src = x + (int64_t)(p / k) * x_stride;
+    if (kQuant) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(x_sorted) + (int64_t)pos * H;
+      for (int g = 0; g < H / 128; ++g) {
+        float v[4];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { v[j] = to_f(src[g * 128 + lane * 4 + j]); amax = fmaxf(amax, fabsf(v[j])); }
+        amax = fmaxf(warp_max(amax), 1e-10f);
+        const float scale = amax / 448.f, inv = 1.f / scale;
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          packed |= (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+        reinterpret_cast<uint32_t*>(dst + g * 128)[lane] = packed;
+        if (lane == 0) scale_t[(int64_t)g * s_stride + pos] = scale;
+      }
+    } else {
+      constexpr int V = Vec16<T>::N;
+      T* dst = reinterpret_cast<T*>(x_sorted) + (int64_t)pos * H;
+      for (int i = lane; i < H / V; i += 32) st_vec(dst + i * V, ld_vec(src + i * V));
+    }
+  }
+}
+
+// a = act(h[:, :I]) * h[:, I:] quantised to fp8 with 1x128 scales in one pass (rows >= *rows_valid are skipped)
+template <typename T>
+__global__ void act_mul_quant_fp8_kernel(uint8_t* __restrict__ q, float* __restrict__ scale_t, const T* __restrict__ h,
+                                         int64_t rows, int I, int64_t s_stride, int act, const int* __restrict__ rows_valid_ptr) {
+  griddep_launch();
+  griddep_wait();
+  const int groups = I / 128;
+  const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * groups) return;
+  const int64_t row = w / groups;
+  const int g = (int)(w - row * groups);
+  if (rows_valid_ptr != nullptr && row >= *rows_valid_ptr) return;
+  const int lane = threadIdx.x & 31;
+  const T* gp = h + row * 2 * (int64_t)I + g * 128 + lane * 4;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float gf = to_f(gp[j]), uf = to_f(gp[I + j]);
+    float a;
+    if (act == 0) a = gf / (1.f + __expf(-gf));
+    else { float t = 0.7978845608f * (gf + 0.044715f * gf * gf * gf); a = 0.5f * gf * (1.f + tanhf(t)); }
+    // round through T exactly like the two-kernel path (activation kernel output, then quantiser input)
+    v[j] = to_f(from_f<T>(a * uf));
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  const float scale = amax / 448.f, inv = 1.f / scale;
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    packed |= (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+  reinterpret_cast<uint32_t*>(q + row * (int64_t)I + g * 128)[lane] = packed;
+  if (lane == 0) scale_t[(int64_t)g * s_stride + row] = scale;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -339,6 +466,40 @@ extern "C" int b200_quant_fp8_group(void* q, float* scale_t, const void* x, int6
   B200_DISPATCH_DTYPE(dtype, {
     launch_pdl(quant_fp8_group_kernel<T>, dim3((warps + 7) / 8), dim3(256), 0, st, (uint8_t*)q, scale_t, (const T*)x,
                rows, K, x_stride, s_stride, ue8m0, rows_valid_ptr);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_moe_small_pairs() { return kSmallPairs; }
+
+extern "C" int b200_moe_prepare_small(void* x_sorted, float* scale_t, int64_t s_stride, int* pos_of_pair, int* lod,
+                                      const void* x, const int* ids, const int* emap, int64_t T_, int k, int H, int E_local,
+                                      int E_global, int64_t x_stride, int quant, int dtype, cudaStream_t st) {
+  const int pairs = (int)(T_ * k);
+  if (pairs > kSmallPairs || pairs < 1 || (quant && H % 128)) return 2;
+  const size_t smem = (size_t)(E_local + 1 + 2 * pairs) * sizeof(int);
+  int grid = (pairs + 7) / 8;
+  if (grid > 64) grid = 64;
+  B200_DISPATCH_DTYPE(dtype, {
+    if (H % Vec16<T>::N) return 2;
+    if (quant)
+      launch_pdl(moe_prepare_small_kernel<T, true>, dim3(grid), dim3(256), smem, st, x_sorted, scale_t, s_stride, pos_of_pair,
+                 lod, (const T*)x, ids, emap, pairs, k, H, E_local, E_global, x_stride);
+    else
+      launch_pdl(moe_prepare_small_kernel<T, false>, dim3(grid), dim3(256), smem, st, x_sorted, scale_t, s_stride,
+                 pos_of_pair, lod, (const T*)x, ids, emap, pairs, k, H, E_local, E_global, x_stride);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_act_mul_quant_fp8(void* q, float* scale_t, const void* h, int64_t rows, int I, int64_t s_stride, int act,
+                                      const int* rows_valid_ptr, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (I % 128 || act > 1) return 2;
+  const int64_t warps = rows * (I / 128);
+  B200_DISPATCH_DTYPE(dtype, {
+    launch_pdl(act_mul_quant_fp8_kernel<T>, dim3((warps + 7) / 8), dim3(256), 0, st, (uint8_t*)q, scale_t, (const T*)h, rows,
+               I, s_stride, act, rows_valid_ptr);
   });
   return (int)cudaGetLastError();
 }

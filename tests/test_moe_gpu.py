@@ -133,3 +133,35 @@ def test_moe_engine_gpu(fp8):
         prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (40, 7)]
         outs.append([o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))])
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("T,k,E", [(1, 8, 128), (16, 8, 128), (128, 8, 64), (100, 4, 32)])
+def test_small_batch_fusion_is_bitwise_equal(fp8, T, k, E):
+    """One-launch permute (+ fp8 quantisation) and the fused activation + quantiser give the same bits as the
+    separate kernels: rows are processed independently of where they sit in the permuted buffer."""
+    from vllm_kunlun_b200.models.moe import _quant_block_device
+    from vllm_kunlun_b200.ops import moe_cuda
+    torch.manual_seed(T + k)
+    H, I = 512, 256
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    w13 = torch.randn(E, 2 * I, H, device=DEV) * 0.05
+    w2 = torch.randn(E, H, I, device=DEV) * 0.05
+    s13 = s2 = None
+    if fp8:
+        q13, q2 = [_quant_block_device(w13[e]) for e in range(E)], [_quant_block_device(w2[e]) for e in range(E)]
+        w13, s13 = torch.stack([a for a, _ in q13]), torch.stack([b for _, b in q13])
+        w2, s2 = torch.stack([a for a, _ in q2]), torch.stack([b for _, b in q2])
+    else:
+        w13, w2 = w13.bfloat16(), w2.bfloat16()
+    wts, ids = ops.moe_route(torch.randn(T, E, device=DEV), k, "softmax", True)
+    emap = torch.arange(E, dtype=torch.int32, device=DEV)
+    emap[E // 2:] = -1  # half of the experts live elsewhere
+    outs = []
+    for on in (True, False):
+        moe_cuda.SMALL_BATCH_FUSION[0] = on
+        outs.append(ops.fused_moe(x, w13[: E // 2].contiguous(), w2[: E // 2].contiguous(), wts, ids, "silu", None, None,
+                                  None if s13 is None else s13[: E // 2].contiguous(),
+                                  None if s2 is None else s2[: E // 2].contiguous(), (128, 128), emap))
+    moe_cuda.SMALL_BATCH_FUSION[0] = True
+    assert torch.equal(outs[0], outs[1])

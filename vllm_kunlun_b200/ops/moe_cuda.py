@@ -19,6 +19,16 @@ def moe_route_cuda(logits, k, scoring, renormalize, bias, n_group, topk_group, s
     return w, ids
 
 
+SMALL_BATCH_FUSION = [__import__("os").environ.get("B200_MOE_SMALL_FUSION", "1") != "0"]
+_SMALL = []
+
+
+def _small_pairs() -> int:
+    if not _SMALL:
+        _SMALL.append(int(_ext.C().moe_small_pairs()))
+    return _SMALL[0]
+
+
 def _state(device, e_local: int):
     key = (str(device), e_local)
     if key not in _STATE:
@@ -34,22 +44,31 @@ def fused_moe_cuda(x, w13, w2, topk_weights, topk_ids, act="silu", b13=None, b2=
     k = topk_ids.shape[1]
     E_local = w13.shape[0]
     E_global = expert_map.shape[0] if expert_map is not None else E_local
-    xs, pos, lod = C.moe_permute(x, topk_ids.contiguous(), expert_map, E_local, E_global, _state(x.device, E_local))
-    M = xs.shape[0]
     fp8 = w13_scale is not None
+    small = 0 < T * k <= _small_pairs() and SMALL_BATCH_FUSION[0]
+    if small:
+        # decode-sized batch: count + scan + scatter (+ fp8 quantisation of the rows) in one launch
+        xs, pos, lod, st = C.moe_prepare_small(x, topk_ids.contiguous(), expert_map, E_local, E_global, fp8)
+        q = xs
+    else:
+        xs, pos, lod = C.moe_permute(x, topk_ids.contiguous(), expert_map, E_local, E_global, _state(x.device, E_local))
+        if fp8:
+            q, st = C.quant_fp8_group(xs, False, lod[E_local:], 4)
+    M = xs.shape[0]
     h = torch.empty(M, w13.shape[1], dtype=x.dtype, device=x.device)
     if fp8:
-        q, st = C.quant_fp8_group(xs, False, lod[E_local:], 4)
         C.grouped_gemm(h, q, w13.view(torch.uint8), lod, b13, st, w13_scale, 0)
     else:
         C.grouped_gemm(h, xs, w13, lod, b13, None, None, 0)
-    a = act_and_mul(h, act)
     y = torch.empty(M, H, dtype=x.dtype, device=x.device)
     if fp8:
-        q2, st2 = C.quant_fp8_group(a, False, lod[E_local:], 4)
+        if act in ("silu", "gelu_tanh") and SMALL_BATCH_FUSION[0]:
+            q2, st2 = C.act_mul_quant_fp8(h, 0 if act == "silu" else 1, lod[E_local:])  # activation + quantiser fused
+        else:
+            q2, st2 = C.quant_fp8_group(act_and_mul(h, act), False, lod[E_local:], 4)
         C.grouped_gemm(y, q2, w2.view(torch.uint8), lod, b2, st2, w2_scale, 0)
     else:
-        C.grouped_gemm(y, a, w2, lod, b2, None, None, 0)
+        C.grouped_gemm(y, act_and_mul(h, act), w2, lod, b2, None, None, 0)
     out = torch.empty(T, H, dtype=x.dtype, device=x.device)
     C.moe_unpermute(out, y, pos, topk_weights.contiguous())
     return out
