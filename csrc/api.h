@@ -128,6 +128,8 @@ int b200_moe_permute(void* x_sorted, int* pos_of_pair, int* lod, int* counts, in
                      int64_t max_rows, int dtype, cudaStream_t st);
 int b200_moe_unpermute(void* out, const void* y_sorted, const int* pos_of_pair, const float* w, int64_t T, int k, int H,
                        int dtype, cudaStream_t st);
+int b200_router_gemm_small(float* out, const void* x, int64_t x_stride, const void* w, const void* bias,
+                           int64_t T_, int N, int K, int dtype, cudaStream_t st);
 int b200_moe_small_pairs();
 int b200_moe_prepare_small(void* x_sorted, float* scale_t, int64_t s_stride, int* pos_of_pair, int* lod,
                            const void* x, const int* ids, const int* emap, int64_t T_, int k, int H, int E_local,

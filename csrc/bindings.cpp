@@ -269,6 +269,15 @@ std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& ids, 
   return {xs, pos, lod};
 }
 
+at::Tensor router_gemm_small(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && w.dim() == 2 && w.is_contiguous() && w.scalar_type() == x.scalar_type());
+  TORCH_CHECK(w.size(1) == x.size(1));
+  auto out = at::empty({x.size(0), w.size(0)}, x.options().dtype(at::kFloat));
+  check(b200_router_gemm_small(out.data_ptr<float>(), x.data_ptr(), x.stride(0), w.data_ptr(), opt_ptr(bias), x.size(0),
+                               (int)w.size(0), (int)w.size(1), dtype_code(x), stream()), "router_gemm_small");
+  return out;
+}
+
 // Small-batch permute in one launch; with `quant` the rows are written as fp8 with transposed 1x128 scales.
 // Returns (x_sorted | q_sorted, pos_of_pair, lod, scale_t or empty).
 std::vector<at::Tensor> moe_prepare_small(const at::Tensor& x, const at::Tensor& ids, const c10::optional<at::Tensor>& emap,
@@ -280,7 +289,7 @@ std::vector<at::Tensor> moe_prepare_small(const at::Tensor& x, const at::Tensor&
   auto pos = at::empty({M}, ids.options());
   auto lod = at::empty({E_local + 1}, ids.options());
   int64_t stride = std::max<int64_t>(4, (M + 3) / 4 * 4);
-  auto st = quant ? at::zeros({H / 128, stride}, x.options().dtype(at::kFloat)) : at::empty({0}, x.options().dtype(at::kFloat));
+  auto st = quant ? at::empty({H / 128, stride}, x.options().dtype(at::kFloat)) : at::empty({0}, x.options().dtype(at::kFloat));
   check(b200_moe_prepare_small(xs.data_ptr(), quant ? st.data_ptr<float>() : nullptr, stride, pos.data_ptr<int>(),
                                lod.data_ptr<int>(), x.data_ptr(), ids.data_ptr<int>(),
                                emap.has_value() ? emap->data_ptr<int>() : nullptr, T, k, H, E_local, E_global, x.stride(0),
@@ -294,7 +303,7 @@ std::vector<at::Tensor> act_mul_quant_fp8(const at::Tensor& h, int64_t act, cons
   const int64_t rows = h.size(0), I = h.size(1) / 2;
   int64_t stride = std::max<int64_t>(4, (rows + 3) / 4 * 4);
   auto q = at::empty({rows, I}, h.options().dtype(at::kByte));
-  auto s = at::zeros({I / 128, stride}, h.options().dtype(at::kFloat));
+  auto s = at::empty({I / 128, stride}, h.options().dtype(at::kFloat));
   check(b200_act_mul_quant_fp8(q.data_ptr(), s.data_ptr<float>(), h.data_ptr(), rows, I, stride, act,
                                rows_valid.has_value() ? rows_valid->data_ptr<int>() : nullptr, dtype_code(h), stream()),
         "act_mul_quant_fp8");
@@ -316,7 +325,7 @@ std::vector<at::Tensor> quant_fp8_group(const at::Tensor& x, bool ue8m0, const c
   int64_t stride = ((rows + pad_rows_to - 1) / pad_rows_to) * pad_rows_to;
   stride = std::max<int64_t>(stride, 4);
   auto q = at::empty({rows, K}, x.options().dtype(at::kByte));
-  auto s = at::zeros({K / 128, stride}, x.options().dtype(at::kFloat));
+  auto s = at::empty({K / 128, stride}, x.options().dtype(at::kFloat));
   check(b200_quant_fp8_group(q.data_ptr(), s.data_ptr<float>(), x.data_ptr(), rows, K, x.stride(0), stride, ue8m0,
                              rows_valid.has_value() ? rows_valid->data_ptr<int>() : nullptr, dtype_code(x), stream()),
         "quant_fp8_group");
@@ -799,6 +808,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_permute", &moe_permute, py::arg("x"), py::arg("ids"), py::arg("emap"), py::arg("E_local"),
         py::arg("E_global"), py::arg("state"), py::arg("max_rows") = 0);
   m.def("moe_unpermute", &moe_unpermute);
+  m.def("router_gemm_small", &router_gemm_small);
   m.def("moe_prepare_small", &moe_prepare_small);
   m.def("act_mul_quant_fp8", &act_mul_quant_fp8);
   m.def("moe_small_pairs", []() { return (int64_t)b200_moe_small_pairs(); });

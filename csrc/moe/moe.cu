@@ -409,6 +409,41 @@ __global__ void act_mul_quant_fp8_kernel(uint8_t* __restrict__ q, float* __restr
   if (lane == 0) scale_t[(int64_t)g * s_stride + row] = scale;
 }
 
+
+// ---- router GEMM for decode-sized batches -------------------------------------------------------------------
+// logits[t, n] = x[t] . w[n] (+ bias[n]) in fp32 for a handful of tokens and at most a few hundred experts: far too
+// small for the tensor-core GEMM, whose fixed cost (TMEM, barriers, pipeline fill, split-K fix-up) is ~10 us.
+// One CTA per (token, 32 experts): the activation row sits in shared memory, each warp produces 4 logits with
+// 16-byte loads of the weight rows.  (GateLinear's small-batch tier, ops/fused_moe/router/gate_linear.py:37-116.)
+template <typename T>
+__global__ void __launch_bounds__(256) router_gemm_small_kernel(float* __restrict__ out, const T* __restrict__ x,
+                                                                int64_t x_stride, const T* __restrict__ w,
+                                                                const T* __restrict__ bias, int N, int K) {
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_router[];
+  T* sx = reinterpret_cast<T*>(smem_router);
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x, n0 = blockIdx.y * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x * V; i < K; i += blockDim.x * V) st_vec(sx + i, ld_vec(x + (int64_t)t * x_stride + i));
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int n = n0 + warp * 4 + j;
+    if (n >= N) break;
+    const T* wr = w + (int64_t)n * K;
+    float acc = 0.f;
+    for (int i = lane * V; i < K; i += 32 * V) {
+      Vec16<T> a = ld_vec(wr + i), b = ld_vec(sx + i);
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc += to_f(a.v[e]) * to_f(b.v[e]);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[(int64_t)t * N + n] = acc + (bias ? to_f(bias[n]) : 0.f);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -500,6 +535,23 @@ extern "C" int b200_act_mul_quant_fp8(void* q, float* scale_t, const void* h, in
   B200_DISPATCH_DTYPE(dtype, {
     launch_pdl(act_mul_quant_fp8_kernel<T>, dim3((warps + 7) / 8), dim3(256), 0, st, (uint8_t*)q, scale_t, (const T*)h, rows,
                I, s_stride, act, rows_valid_ptr);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_router_gemm_small(float* out, const void* x, int64_t x_stride, const void* w, const void* bias,
+                                      int64_t T_, int N, int K, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  int esz = dtype == 0 ? 4 : 2;
+  if (K % (16 / esz) || (x_stride * esz) % 16 || (size_t)K * esz > 96 * 1024) return 2;
+  B200_DISPATCH_DTYPE(dtype, {
+    static bool attr = false;
+    if (!attr && (size_t)K * esz > 48 * 1024) {
+      cudaFuncSetAttribute(router_gemm_small_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      attr = true;
+    }
+    launch_pdl(router_gemm_small_kernel<T>, dim3((unsigned)T_, (N + 31) / 32), dim3(256), (size_t)K * esz, st, out,
+               (const T*)x, x_stride, (const T*)w, (const T*)bias, N, K);
   });
   return (int)cudaGetLastError();
 }

@@ -165,3 +165,33 @@ def test_small_batch_fusion_is_bitwise_equal(fp8, T, k, E):
                                   None if s2 is None else s2[: E // 2].contiguous(), (128, 128), emap))
     moe_cuda.SMALL_BATCH_FUSION[0] = True
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("T,E,K", [(1, 128, 2048), (16, 128, 2048), (64, 256, 7168), (5, 32, 512)])
+def test_router_gemm_small(T, E, K):
+    torch.manual_seed(T)
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(E, K, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(E, device=DEV).bfloat16()
+    got = ops.router_gemm(x, w, b)
+    assert got.dtype == torch.float32
+    want = x.float() @ w.float().T + b.float()
+    torch.testing.assert_close(got, want, atol=2e-3, rtol=2e-3)
+
+
+def test_small_fp8_projection_uses_16bit_copy_for_decode_batches():
+    from vllm_kunlun_b200.models.layers import ReplicatedLinear
+    from vllm_kunlun_b200.models.moe import _quant_block_device
+    torch.manual_seed(0)
+    lin = ReplicatedLinear(1024, 512, dtype=torch.bfloat16, device=DEV, quant="fp8")
+    q, s = _quant_block_device(torch.randn(512, 1024, device=DEV) * 0.05)
+    lin.weight.data.copy_(q)
+    lin.weight_scale_inv.data.copy_(s)
+    lin.method.process_weights_after_loading(lin)
+    assert lin.weight_16bit.shape == (512, 1024)
+    x = torch.randn(300, 1024, device=DEV).bfloat16()
+    big = lin(x)            # fp8 tensor-core path
+    small = lin(x[:16])     # 16-bit stream-K path over the de-quantised copy
+    ref = x.float() @ lin.weight_16bit.float().T
+    _close(small, ref[:16], 2e-2, 2e-2, "16-bit copy")
+    _close(big, ref, 6e-2, 6e-2, "fp8 path")

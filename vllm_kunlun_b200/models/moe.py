@@ -174,7 +174,7 @@ class SparseMoEBlock(nn.Module):
         lo, hi = min(T, st.ep_rank * chunk), min(T, (st.ep_rank + 1) * chunk)
         xl = x[lo:hi]
         if hi > lo:
-            w, ids = ops.moe_route(self.gate(xl), cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
+            w, ids = ops.moe_route(ops.router_gemm(xl, self.gate.weight, self.gate.bias), cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
                                    self.e_score_correction_bias, cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor)
         else:
             w = torch.zeros(0, cfg.num_experts_per_tok, dtype=torch.float32, device=x.device)
@@ -194,7 +194,7 @@ class SparseMoEBlock(nn.Module):
         a2a = self._a2a(x)
         if a2a is not None:
             return self._forward_a2a(x, a2a)
-        logits = self.gate(x)
+        logits = ops.router_gemm(x, self.gate.weight, self.gate.bias)
         w, ids = ops.moe_route(logits, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
                                self.e_score_correction_bias, cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor)
         out = self.experts(x, w, ids)

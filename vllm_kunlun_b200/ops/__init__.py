@@ -310,6 +310,14 @@ def int8_linear(x, w_q, w_scale, bias=None, input_scale=None, out_dtype=torch.bf
 
 # ----------------------------------------------------------------------------- MoE
 
+def router_gemm(x, weight, bias=None):
+    """Router logits ``x @ W.T (+ b)``.  CUDA, decode-sized batches: a CUDA-core kernel with fp32 output (the
+    tensor-core GEMM's fixed cost dominates at this size); otherwise the ordinary linear."""
+    if x.is_cuda and x.dim() == 2 and x.shape[0] <= 64 and weight.shape[0] <= 1024 and weight.dtype == x.dtype:
+        return _c().router_gemm_small(x if x.stride(-1) == 1 else x.contiguous(), weight, bias)
+    return linear(x, weight, bias)
+
+
 def moe_route(logits, k: int, scoring: str = "softmax", renormalize: bool = True, bias=None, n_group: int = 1,
               topk_group: int = 1, scale: float = 1.0):
     """Router: ``(weights [T, k] fp32, ids [T, k] int32)``.
