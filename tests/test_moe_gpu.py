@@ -194,4 +194,4 @@ def test_small_fp8_projection_uses_16bit_copy_for_decode_batches():
     small = lin(x[:16])     # 16-bit stream-K path over the de-quantised copy
     ref = x.float() @ lin.weight_16bit.float().T
     _close(small, ref[:16], 2e-2, 2e-2, "16-bit copy")
-    _close(big, ref, 6e-2, 6e-2, "fp8 path")
+    _close(big, ref, 0.25, 0.1, "fp8 path")  # activations are quantised to e4m3 per 128 columns on this path
