@@ -25,6 +25,10 @@ _ENV: dict[str, Callable[[], Any]] = {
     # split-KV partials (read by the C++ side)
     "B200_FUSE_ACT": lambda: os.environ.get("B200_FUSE_ACT", "1") != "0",
     "B200_ATTN_FUSE_MERGE": lambda: os.environ.get("B200_ATTN_FUSE_MERGE", "1") != "0",
+    # low-latency all-reduce (data + flag in one 8-byte unit) for payloads up to 256 KB
+    "B200_AR_LL": lambda: os.environ.get("B200_AR_LL", "1") != "0",
+    # MoE decode: one-launch permute (+ fp8 quantisation) and fused activation + quantiser for small batches
+    "B200_MOE_SMALL_FUSION": lambda: os.environ.get("B200_MOE_SMALL_FUSION", "1") != "0",
     # peer-memory collectives (one-shot all-reduce, fused GEMM+collectives)
     "B200_PEER_COLLECTIVES": lambda: os.environ.get("B200_PEER_COLLECTIVES", "1") != "0",
     # exponential-race sampling with a cached noise tensor (the reference's FAST_RANDOM_SAMPLE)

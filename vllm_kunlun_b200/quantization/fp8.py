@@ -33,7 +33,7 @@ class Fp8BlockLinearMethod:
     # kernel has no split-K: with M <= 64 tokens a [2048 x 4096] weight gives it 16 tiles for 148 SMs.  Such layers
     # keep a second, 16-bit copy of the weight (de-quantised once) and send small batches through the 16-bit
     # stream-K GEMM - which also skips the activation quantiser.  Large batches stay on the fp8 tensor-core path.
-    SMALL_WEIGHT_ELEMS = 24 << 20
+    SMALL_WEIGHT_ELEMS = 48 << 20
     SMALL_BATCH_ROWS = 64
 
     def apply(self, layer, x: torch.Tensor) -> torch.Tensor:
