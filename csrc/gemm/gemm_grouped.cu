@@ -40,7 +40,10 @@ struct GCfg {
   static constexpr int kStageBytesA = GBM * 128;
   static constexpr int kStageBytesB = BN * 128;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  // accumulator buffers in TMEM: the fp8 path hands one over per k-block, so a deeper ring hides the hand-off
+  // latency (commit -> barrier -> tcgen05.ld -> arrive); 4 x BN columns fit for BN <= 128
+  static constexpr int kAccBufs = (kFp8 && BN <= 128) ? 4 : 2;
+  static constexpr int kTmemCols = (kAccBufs * BN < 32) ? 32 : kAccBufs * BN;
 };
 
 struct GParams {
@@ -64,9 +67,10 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + num_stages * Cfg::kStageBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + num_stages;
-  uint64_t* tmem_full = bars + 2 * num_stages;  // [2]
-  uint64_t* tmem_empty = tmem_full + 2;         // [2]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  constexpr int NB = Cfg::kAccBufs;
+  uint64_t* tmem_full = bars + 2 * num_stages;  // [NB]
+  uint64_t* tmem_empty = tmem_full + NB;        // [NB]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + NB);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 2);  // [2]
   int* tile_start = reinterpret_cast<int*>(tmem_base_slot + 4);                     // [E + 1]
@@ -83,7 +87,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < num_stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    for (int b = 0; b < NB; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
     mbar_fence_init();
     prefetch_tmap(&tmW);
     prefetch_tmap(&tmX);
@@ -173,9 +177,9 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < total_kb; ++kb) {
           const bool new_acc = kFp8 || kb == 0;
-          const int buf = acc_it & 1;
+          const int buf = acc_it % NB;
           if (new_acc) {
-            if (!wait_or_abort(&tmem_empty[buf], ((acc_it >> 1) & 1) ^ 1, ab, 112)) { ok = false; break; }
+            if (!wait_or_abort(&tmem_empty[buf], ((acc_it / NB) & 1) ^ 1, ab, 112)) { ok = false; break; }
             tc_fence_after_sync();
           }
           if (!wait_or_abort(&full_bar[stage], phase, ab, 113)) { ok = false; break; }
@@ -219,19 +223,34 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         for (int j = 0; j < BN; ++j) acc[j] = 0.f;
       }
       const int kb_rounds = kFp8 ? total_kb : 1;
+      // The scales of a k-block are fetched one k-block ahead into registers: a dependent global load in front of
+      // every TMEM hand-off would otherwise bound the kernel at one L2 round trip per 16 KB of weights.
+      constexpr int kScPerLane = (BN + 31) / 32;
+      const int nkb = (p.K + 127) / 128;
+      float a_next[kScPerLane];
+      float w_next = 0.f;
+      auto fetch_scales = [&](int kb) {
+        w_next = p.w_scale[((size_t)e * n_tiles + nt) * nkb + kb];
+#pragma unroll
+        for (int i = 0; i < kScPerLane; ++i) {
+          const int j = lane + 32 * i, r = row0 + j;
+          a_next[i] = (j < BN && r < row_end) ? p.a_scale[(size_t)kb * p.a_stride + r] : 0.f;
+        }
+      };
+      if (kFp8) fetch_scales(0);
       for (int kb = 0; kb < kb_rounds && ok; ++kb, ++acc_it) {
-        const int buf = acc_it & 1;
-        const uint32_t ph = (acc_it >> 1) & 1;
+        const int buf = acc_it % NB;
+        const uint32_t ph = (acc_it / NB) & 1;
         if (kFp8) {
           // stage this k-block's column scales (activation scale x weight block scale) per warp
-          const int nkb = (p.K + 127) / 128;
-          const float wsc = p.w_scale[((size_t)e * n_tiles + nt) * nkb + kb];
           float* dst = my_sc + (kb & 1) * BN;
-          for (int j = lane; j < BN; j += 32) {
-            int r = row0 + j;
-            dst[j] = (r < row_end) ? p.a_scale[(size_t)kb * p.a_stride + r] * wsc : 0.f;
+#pragma unroll
+          for (int i = 0; i < kScPerLane; ++i) {
+            const int j = lane + 32 * i;
+            if (j < BN) dst[j] = a_next[i] * w_next;
           }
           __syncwarp();
+          if (kb + 1 < kb_rounds) fetch_scales(kb + 1);
         }
         if (ep_tid == 0) ep_ok_slot[acc_it & 1] = wait_or_abort(&tmem_full[buf], ph, ab, 114) ? 1 : 0;
         asm volatile("bar.sync 1, 128;" ::: "memory");
