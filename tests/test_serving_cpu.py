@@ -175,3 +175,43 @@ def test_openai_server_completions_and_chat_stream():
         msg = r.json()["choices"][0]["message"]
         assert msg["role"] == "assistant" and "reasoning_content" in msg
         assert "b200_requests_total 3" in c.get("/metrics").text
+
+
+def test_bench_serving_client_against_live_server():
+    """The serving benchmark client drives a real HTTP server (uvicorn on a free port) over the tiny CPU engine."""
+    import importlib.util
+    import socket
+    import threading
+    import time
+
+    import uvicorn
+
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    cfg = tiny(qwen2_0_5b(), num_layers=1, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    server = uvicorn.Server(uvicorn.Config(build_app(llm, "tiny"), host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    for _ in range(100):
+        if server.started:
+            break
+        time.sleep(0.1)
+    assert server.started
+    spec = importlib.util.spec_from_file_location(
+        "bench_serving", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "bench_serving.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    try:
+        out = mod.main(["--port", str(port), "--num-prompts", "4", "--max-concurrency", "2", "--random-input-len", "12",
+                        "--random-output-len", "6", "--vocab-size", "100"])
+    finally:
+        server.should_exit = True
+        th.join(timeout=10)
+    assert out["completed"] == 4 and out["failed"] == 0 and out["output_tok_per_s"] > 0
