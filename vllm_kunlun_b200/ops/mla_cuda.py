@@ -12,7 +12,6 @@ from . import _ext
 from .attention_cuda import sm_count
 
 _LOD: dict = {}
-_WT: dict = {}
 
 
 def _splits(ctas: int, tiles: int, device, cap: int = 16) -> int:
@@ -62,11 +61,12 @@ def bmm_heads_cuda(x, w):
     """``out[t, n, :] = x[t, n, :] @ w[n]`` with ``w [N, K, D]``: heads are the groups of a grouped GEMM."""
     T, N, K = x.shape
     D = w.shape[2]
-    key = (w.data_ptr(), tuple(w.shape))
-    wt = _WT.get(key)
-    if wt is None:  # K-major copy [N, D, K], made once per weight
+    # K-major copy [N, D, K], made once per weight and kept ON the weight tensor: a cache keyed by address would hand
+    # a later model the copy of an earlier one whose (freed) weight lived at the same address
+    wt = getattr(w, "_b200_kmajor", None)
+    if wt is None or wt.shape != (N, D, K):
         wt = w.transpose(1, 2).contiguous()
-        _WT[key] = wt
+        w._b200_kmajor = wt
     lk = (N, T, str(x.device))
     lod = _LOD.get(lk)
     if lod is None:
