@@ -130,6 +130,9 @@ int b200_moe_unpermute(void* out, const void* y_sorted, const int* pos_of_pair, 
                        int dtype, cudaStream_t st);
 int b200_router_gemm_small(float* out, const void* x, int64_t x_stride, const void* w, const void* bias,
                            int64_t T_, int N, int K, int dtype, cudaStream_t st);
+int b200_router_route_small(float* out_w, int* out_ids, const void* x, int64_t x_stride, const void* w,
+                            const void* wbias, const float* bias, int64_t T_, int E, int K, int k, int mode,
+                            int renorm, int n_group, int topk_group, float scale, int dtype, cudaStream_t st);
 int b200_moe_small_pairs();
 int b200_moe_prepare_small(void* x_sorted, float* scale_t, int64_t s_stride, int* pos_of_pair, int* lod,
                            const void* x, const int* ids, const int* emap, int64_t T_, int k, int H, int E_local,

@@ -269,6 +269,22 @@ std::vector<at::Tensor> moe_permute(const at::Tensor& x, const at::Tensor& ids, 
   return {xs, pos, lod};
 }
 
+// (weights [T, k] fp32, ids [T, k] int32) straight from the hidden states: router GEMM + routing in one launch
+std::vector<at::Tensor> router_route_small(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& wbias,
+                                           const c10::optional<at::Tensor>& bias, int64_t k, int64_t mode, bool renorm,
+                                           int64_t n_group, int64_t topk_group, double scale) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && w.dim() == 2 && w.is_contiguous() && w.scalar_type() == x.scalar_type());
+  TORCH_CHECK(w.size(1) == x.size(1));
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous());
+  auto ow = at::empty({x.size(0), k}, x.options().dtype(at::kFloat));
+  auto oi = at::empty({x.size(0), k}, x.options().dtype(at::kInt));
+  check(b200_router_route_small(ow.data_ptr<float>(), oi.data_ptr<int>(), x.data_ptr(), x.stride(0), w.data_ptr(),
+                                opt_ptr(wbias), bias.has_value() ? bias->data_ptr<float>() : nullptr, x.size(0),
+                                (int)w.size(0), (int)w.size(1), (int)k, (int)mode, renorm, (int)n_group, (int)topk_group,
+                                (float)scale, dtype_code(x), stream()), "router_route_small");
+  return {ow, oi};
+}
+
 at::Tensor router_gemm_small(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias) {
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && w.dim() == 2 && w.is_contiguous() && w.scalar_type() == x.scalar_type());
   TORCH_CHECK(w.size(1) == x.size(1));
@@ -809,6 +825,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("E_global"), py::arg("state"), py::arg("max_rows") = 0);
   m.def("moe_unpermute", &moe_unpermute);
   m.def("router_gemm_small", &router_gemm_small);
+  m.def("router_route_small", &router_route_small);
   m.def("moe_prepare_small", &moe_prepare_small);
   m.def("act_mul_quant_fp8", &act_mul_quant_fp8);
   m.def("moe_small_pairs", []() { return (int64_t)b200_moe_small_pairs(); });

@@ -19,19 +19,14 @@ constexpr int kMaxEPerLane = 16;  // E <= 512
 constexpr int kMaxTopK = 16;
 
 // mode: 0 softmax->topk, 1 sigmoid group-limited, 2 topk->softmax
+// One warp routes one token; `row` holds the token's E router logits (global or shared memory).
 template <typename T>
-__global__ void moe_route_kernel(float* __restrict__ out_w, int* __restrict__ out_ids, const T* __restrict__ logits,
-                                 const float* __restrict__ bias, int64_t T_, int E, int k, int mode, int renorm,
-                                 int n_group, int topk_group, float scale, int64_t stride) {
-  griddep_launch();
-  griddep_wait();
-  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T_) return;
-  const int lane = threadIdx.x & 31;
+__device__ __forceinline__ void route_row(float* __restrict__ out_w, int* __restrict__ out_ids, const T* row,
+                                          const float* __restrict__ bias, int64_t t, int lane, int E, int k, int mode,
+                                          int renorm, int n_group, int topk_group, float scale) {
   const int per = (E + 31) / 32;
   float score[kMaxEPerLane];  // unbiased weight source
   float sel[kMaxEPerLane];    // selection score
-  const T* row = logits + t * stride;
   // expert e lives on lane e % 32, slot e / 32
   float mx = -INFINITY;
 #pragma unroll
@@ -155,6 +150,51 @@ __global__ void moe_route_kernel(float* __restrict__ out_w, int* __restrict__ ou
       out_ids[t * k + r] = (isel[r] == 0x7fffffff) ? 0 : isel[r];
     }
   }
+}
+
+
+template <typename T>
+__global__ void moe_route_kernel(float* __restrict__ out_w, int* __restrict__ out_ids, const T* __restrict__ logits,
+                                 const float* __restrict__ bias, int64_t T_, int E, int k, int mode, int renorm,
+                                 int n_group, int topk_group, float scale, int64_t stride) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T_) return;
+  route_row<T>(out_w, out_ids, logits + t * stride, bias, t, threadIdx.x & 31, E, k, mode, renorm, n_group, topk_group,
+               scale);
+}
+
+// Router GEMM and routing in one launch for decode-sized batches: one CTA per token computes its E logits into
+// shared memory (each warp a slice of the experts, 16-byte loads of the router rows), then warp 0 routes the token.
+template <typename T>
+__global__ void __launch_bounds__(256) router_route_small_kernel(
+    float* __restrict__ out_w, int* __restrict__ out_ids, const T* __restrict__ x, int64_t x_stride,
+    const T* __restrict__ w, const T* __restrict__ wbias, const float* __restrict__ bias, int E, int K, int k, int mode,
+    int renorm, int n_group, int topk_group, float scale) {
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_rr[];
+  T* sx = reinterpret_cast<T*>(smem_rr);
+  float* slog = reinterpret_cast<float*>(smem_rr + (((size_t)K * sizeof(T) + 15) & ~(size_t)15));
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x * V; i < K; i += blockDim.x * V) st_vec(sx + i, ld_vec(x + (int64_t)t * x_stride + i));
+  __syncthreads();
+  for (int n = warp; n < E; n += nw) {
+    const T* wr = w + (int64_t)n * K;
+    float acc = 0.f;
+    for (int i = lane * V; i < K; i += 32 * V) {
+      Vec16<T> a = ld_vec(wr + i), b = ld_vec(sx + i);
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc += to_f(a.v[e]) * to_f(b.v[e]);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) slog[n] = acc + (wbias ? to_f(wbias[n]) : 0.f);
+  }
+  __syncthreads();
+  if (warp == 0) route_row<float>(out_w, out_ids, slog, bias, t, lane, E, k, mode, renorm, n_group, topk_group, scale);
 }
 
 // counts[e] += number of pairs routed to local expert e  (counts zeroed by the caller kernel chain)
@@ -552,6 +592,27 @@ extern "C" int b200_router_gemm_small(float* out, const void* x, int64_t x_strid
     }
     launch_pdl(router_gemm_small_kernel<T>, dim3((unsigned)T_, (N + 31) / 32), dim3(256), (size_t)K * esz, st, out,
                (const T*)x, x_stride, (const T*)w, (const T*)bias, N, K);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_router_route_small(float* out_w, int* out_ids, const void* x, int64_t x_stride, const void* w,
+                                       const void* wbias, const float* bias, int64_t T_, int E, int K, int k, int mode,
+                                       int renorm, int n_group, int topk_group, float scale, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  if (E > 32 * kMaxEPerLane || k > kMaxTopK || n_group > 32 || (n_group > 1 && E % n_group)) return 2;
+  const int esz = dtype == 0 ? 4 : 2;
+  if (K % (16 / esz) || (x_stride * esz) % 16) return 2;
+  const size_t smem = (((size_t)K * esz + 15) & ~(size_t)15) + (size_t)E * 4;
+  if (smem > 96 * 1024) return 2;
+  B200_DISPATCH_DTYPE(dtype, {
+    static bool attr = false;
+    if (!attr && smem > 48 * 1024) {
+      cudaFuncSetAttribute(router_route_small_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      attr = true;
+    }
+    launch_pdl(router_route_small_kernel<T>, dim3((unsigned)T_), dim3(256), smem, st, out_w, out_ids, (const T*)x,
+               x_stride, (const T*)w, (const T*)wbias, bias, E, K, k, mode, renorm, n_group, topk_group, scale);
   });
   return (int)cudaGetLastError();
 }

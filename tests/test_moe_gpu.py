@@ -195,3 +195,17 @@ def test_small_fp8_projection_uses_16bit_copy_for_decode_batches():
     ref = x.float() @ lin.weight_16bit.float().T
     _close(small, ref[:16], 2e-2, 2e-2, "16-bit copy")
     _close(big, ref, 0.25, 0.1, "fp8 path")  # activations are quantised to e4m3 per 128 columns on this path
+
+
+@pytest.mark.parametrize("scoring,E,k,ng,tg", [("softmax", 128, 8, 1, 1), ("sigmoid", 256, 8, 8, 4), ("softmax_after_topk", 32, 4, 1, 1)])
+def test_router_and_route_fused_equals_two_kernels(scoring, E, k, ng, tg):
+    torch.manual_seed(E)
+    T, K = 16, 2048
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(E, K, device=DEV) * 0.05).bfloat16()
+    bias = torch.randn(E, device=DEV) * 0.1 if scoring == "sigmoid" else None
+    w1, i1 = ops.router_and_route(x, w, None, k, scoring, True, bias, ng, tg, 2.5)
+    w2, i2 = ops.moe_route(ops.router_gemm(x, w, None), k, scoring, True, bias, ng, tg, 2.5)
+    # both read fp32 logits produced by the same dot-product order
+    assert torch.equal(i1.sort(-1).values, i2.sort(-1).values)
+    torch.testing.assert_close(w1.sort(-1).values, w2.sort(-1).values, atol=1e-5, rtol=1e-5)

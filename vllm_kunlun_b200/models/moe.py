@@ -194,9 +194,9 @@ class SparseMoEBlock(nn.Module):
         a2a = self._a2a(x)
         if a2a is not None:
             return self._forward_a2a(x, a2a)
-        logits = ops.router_gemm(x, self.gate.weight, self.gate.bias)
-        w, ids = ops.moe_route(logits, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
-                               self.e_score_correction_bias, cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor)
+        w, ids = ops.router_and_route(x, self.gate.weight, self.gate.bias, cfg.num_experts_per_tok, cfg.scoring_func,
+                                      cfg.norm_topk_prob, self.e_score_correction_bias, cfg.n_group, cfg.topk_group,
+                                      cfg.routed_scaling_factor)
         out = self.experts(x, w, ids)
         if self.shared_experts is not None:
             sh = self.shared_experts(x)

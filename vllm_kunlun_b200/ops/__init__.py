@@ -318,6 +318,20 @@ def router_gemm(x, weight, bias=None):
     return linear(x, weight, bias)
 
 
+def router_and_route(x, weight, wbias, k: int, scoring: str = "softmax", renormalize: bool = True, bias=None,
+                     n_group: int = 1, topk_group: int = 1, scale: float = 1.0):
+    """Router logits and top-k routing from the hidden states.  CUDA, decode-sized batches: ONE launch (logits stay
+    in shared memory); otherwise the router GEMM followed by :func:`moe_route`."""
+    if (x.is_cuda and x.dim() == 2 and 0 < x.shape[0] <= 64 and weight.shape[0] <= 512 and weight.dtype == x.dtype
+            and x.shape[1] * x.element_size() + weight.shape[0] * 4 <= 90 * 1024):
+        from .moe_cuda import _MODES
+        w, ids = _c().router_route_small(x if x.stride(-1) == 1 else x.contiguous(), weight, wbias,
+                                         None if bias is None else bias.float(), k, _MODES[scoring], renormalize,
+                                         n_group, topk_group, scale)
+        return w, ids
+    return moe_route(router_gemm(x, weight, wbias), k, scoring, renormalize, bias, n_group, topk_group, scale)
+
+
 def moe_route(logits, k: int, scoring: str = "softmax", renormalize: bool = True, bias=None, n_group: int = 1,
               topk_group: int = 1, scale: float = 1.0):
     """Router: ``(weights [T, k] fp32, ids [T, k] int32)``.
