@@ -204,7 +204,11 @@ def test_router_and_route_fused_equals_two_kernels(scoring, E, k, ng, tg):
     x = torch.randn(T, K, device=DEV).bfloat16()
     w = (torch.randn(E, K, device=DEV) * 0.05).bfloat16()
     bias = torch.randn(E, device=DEV) * 0.1 if scoring == "sigmoid" else None
-    w1, i1 = ops.router_and_route(x, w, None, k, scoring, True, bias, ng, tg, 2.5)
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.moe_cuda import _MODES
+    w1, i1 = _ext.C().router_route_small(x, w, None, bias, k, _MODES[scoring], True, ng, tg, 2.5)  # the fused kernel itself
+    w3, i3 = ops.router_and_route(x, w, None, k, scoring, True, bias, ng, tg, 2.5)               # dispatcher
+    assert torch.equal(i3.sort(-1).values, i1.sort(-1).values)
     w2, i2 = ops.moe_route(ops.router_gemm(x, w, None), k, scoring, True, bias, ng, tg, 2.5)
     # both read fp32 logits produced by the same dot-product order
     assert torch.equal(i1.sort(-1).values, i2.sort(-1).values)
