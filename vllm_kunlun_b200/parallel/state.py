@@ -97,6 +97,8 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, ep: bool = 
                               device: str = "cpu", with_cpu_group: bool = True,
                               fused_collectives: bool = True) -> ParallelState:
     """Create TP / PP / DP / EP / DCP groups and their communicators."""
+    from .. import envs
+    fused_collectives = fused_collectives and envs.B200_PEER_COLLECTIVES
     from .communicator import DeviceCommunicator
 
     if not dist.is_initialized():
