@@ -215,3 +215,19 @@ def test_bench_serving_client_against_live_server():
         server.should_exit = True
         th.join(timeout=10)
     assert out["completed"] == 4 and out["failed"] == 0 and out["output_tok_per_s"] > 0
+
+
+def test_platform_class_paths_resolve():
+    """Every "module.Class" string the platform hands to an engine imports and names an existing attribute."""
+    import importlib
+
+    from vllm_kunlun_b200.platforms.b200 import B200Platform
+    paths = [B200Platform.get_device_communicator_cls(), B200Platform.get_punica_wrapper(),
+             B200Platform.get_attn_backend_cls(), B200Platform.get_attn_backend_cls(use_mla=True),
+             B200Platform.get_attn_backend_cls(use_mla=True, use_sparse=True), B200Platform.get_static_graph_wrapper_cls(),
+             pkg.register()]
+    for p in paths:
+        mod, _, name = p.rpartition(".")
+        assert hasattr(importlib.import_module(mod), name), p
+    for dt in (torch.bfloat16, torch.float8_e4m3fn, torch.int8):
+        B200Platform.check_if_supports_dtype(dt)
