@@ -85,3 +85,55 @@ def test_profile_run_leaves_engine_usable():
     want = llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids
     assert llm.engine.runner.profile_run(64) == 0
     assert llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids == want
+
+
+def _tiny_llm(**kw):
+    from vllm_kunlun_b200.config import tiny
+    cfg = tiny(qwen2_0_5b(), num_layers=2, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=512, dtype="float32")
+    base = dict(device="cpu", block_size=16, max_model_len=256, max_num_seqs=4, num_gpu_blocks=64)
+    base.update(kw)
+    return LLM(cfg, **base)
+
+
+def test_prefix_caching_reuses_blocks_and_keeps_outputs():
+    shared = list(range(5, 5 + 70))  # four full blocks and a bit
+    prompts = [shared + [100, 101], shared + [102], shared + [100, 101]]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    plain = [o.token_ids for o in _tiny_llm().generate(prompts, sp)]
+    llm = _tiny_llm(enable_prefix_caching=True)
+    first = llm.generate(prompts[:1], sp)[0].token_ids
+    before = llm.engine.stats["prefill_tokens"]
+    rest = [o.token_ids for o in llm.generate(prompts[1:], sp)]
+    assert [first] + rest == plain
+    # the two later prompts recompute only what lies beyond the cached 64-token prefix
+    assert llm.engine.stats["prefill_tokens"] - before <= 2 * (len(shared) + 2 - 64)
+
+
+def test_abort_frees_blocks_and_other_requests_finish():
+    llm = _tiny_llm()
+    eng = llm.engine
+    free0 = eng.pool.num_free
+    a = eng.add_request(list(range(3, 40)), SamplingParams(max_tokens=50, ignore_eos=True))
+    b = eng.add_request(list(range(50, 70)), SamplingParams(max_tokens=6, ignore_eos=True))
+    for _ in range(3):
+        eng.step()
+    assert eng.abort(a.request_id)
+    eng.run_until_done()
+    assert b.status.finished and len(b.output_token_ids) == 6
+    assert a.status.name == "FINISHED_ABORTED" and len(a.output_token_ids) < 50
+    assert eng.pool.num_free == free0
+
+
+def test_stop_tokens_eos_and_sampling_parameters():
+    llm = _tiny_llm()
+    greedy = llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=8, ignore_eos=True))[0].token_ids
+    stop_at = greedy[2]
+    cut = llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=8, stop_token_ids=(stop_at,)))[0]
+    assert cut.token_ids[-1] == stop_at and len(cut.token_ids) <= 3 and cut.finish_reason == "stop"
+    # top_k = 1 is greedy whatever the temperature; different seeds at high temperature give different text
+    k1 = llm.generate([[5, 6, 7, 8]], SamplingParams(max_tokens=8, temperature=1.5, top_k=1, ignore_eos=True))[0].token_ids
+    assert k1 == greedy
+    hot = [_tiny_llm(seed=s).generate([[5, 6, 7, 8]], SamplingParams(max_tokens=12, temperature=5.0, ignore_eos=True))[0].token_ids
+           for s in (0, 0, 1)]
+    assert hot[0] == hot[1]
