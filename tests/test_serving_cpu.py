@@ -231,3 +231,19 @@ def test_platform_class_paths_resolve():
         assert hasattr(importlib.import_module(mod), name), p
     for dt in (torch.bfloat16, torch.float8_e4m3fn, torch.int8):
         B200Platform.check_if_supports_dtype(dt)
+
+
+def test_graph_input_watcher_detects_moved_tensors():
+    import pytest
+
+    from vllm_kunlun_b200.utils import GraphInputWatcher
+    w = GraphInputWatcher()
+    buf = torch.zeros(8)
+    w.capture("g", {"ids": buf[:4], "n": 3})
+    w.check("g", {"ids": buf[:4]})
+    buf[:4].fill_(7)                      # new contents at the same address are what a replay expects
+    w.check("g", {"ids": buf[:4]})
+    with pytest.raises(RuntimeError):
+        w.check("g", {"ids": buf[4:]})    # another address
+    with pytest.raises(KeyError):
+        w.check("other", {})

@@ -100,3 +100,33 @@ class StageTimer:
             self.records.append((name, dt))
             if self.sink:
                 self.sink(f"[stage] {name} end {dt * 1e3:.3f} ms")
+
+
+class GraphInputWatcher:
+    """Guards the tensors a captured CUDA graph reads: their addresses (and shapes) must not change between capture
+    and replay, or the graph silently reads stale memory.  Counterpart of the reference's ``CUDAGraphInnerWatcher``
+    (``vllm_kunlun/utils.py:235-288``), which logs tensor addresses inside compiled graphs for the same purpose.
+
+        watcher = GraphInputWatcher()
+        watcher.capture("decode_b16", {"ids": ids, "block_tables": bt})
+        ...
+        watcher.check("decode_b16", {"ids": ids, "block_tables": bt})   # raises on a moved / reshaped tensor
+    """
+
+    def __init__(self):
+        self._seen: dict = {}
+
+    @staticmethod
+    def _sig(t: torch.Tensor):
+        return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype)
+
+    def capture(self, key: str, tensors: dict) -> None:
+        self._seen[key] = {n: self._sig(t) for n, t in tensors.items() if isinstance(t, torch.Tensor)}
+
+    def check(self, key: str, tensors: dict) -> None:
+        ref = self._seen.get(key)
+        if ref is None:
+            raise KeyError(f"graph {key!r} was never captured")
+        for n, t in tensors.items():
+            if isinstance(t, torch.Tensor) and n in ref and self._sig(t) != ref[n]:
+                raise RuntimeError(f"input {n!r} of captured graph {key!r} changed: {ref[n]} -> {self._sig(t)}")
