@@ -34,6 +34,11 @@ class DecodeGraphs:
         self.kernels_per_graph: dict = {}
         self.replayed_kernels = 0
         self.misses = 0
+        from .. import envs
+        self.watcher = None
+        if envs.B200_GRAPH_WATCH:
+            from ..utils.hooks import GraphInputWatcher
+            self.watcher = GraphInputWatcher()
 
     def supports(self, num_reqs: int, num_tokens: int) -> bool:
         ok = (num_reqs > 0 and num_tokens == num_reqs * self.tokens_per_req and self.sizes
@@ -76,6 +81,8 @@ class DecodeGraphs:
         if self.pool is None:
             self.pool = g.pool()
         self.graphs[key], self.logits[key], self.hidden[key] = g, logits, sel
+        if self.watcher is not None:
+            self.watcher.capture(str(key), self._watched(md, input_ids))
 
     @torch.inference_mode()
     def run(self, md: AttentionMetadata, input_ids, sp):
@@ -83,10 +90,18 @@ class DecodeGraphs:
         if key not in self.graphs:
             self._capture(md, input_ids)
         self.hits += 1
+        if self.watcher is not None:  # debug aid: a replay must see its inputs at the captured addresses
+            self.watcher.check(str(key), self._watched(md, input_ids))
         self.graphs[key].replay()
         self.replayed_kernels += self.kernels_per_graph[key]
         tokens = self.runner.sampler(self.logits[key], sp)
         return tokens, self.hidden[key]
+
+    @staticmethod
+    def _watched(md, input_ids) -> dict:
+        return {"input_ids": input_ids, "positions": md.positions, "slot_mapping": md.slot_mapping,
+                "block_tables": md.block_tables, "seq_lens": md.seq_lens, "query_start_loc": md.query_start_loc,
+                "logits_indices": md.logits_indices}
 
     def capture_all(self):
         """Eagerly capture every configured size with a synthetic decode batch (server warm-up), so that the first

@@ -15,6 +15,8 @@ _ENV: dict[str, Callable[[], Any]] = {
     "B200_ENABLE_MODULE_HOOK": lambda: os.environ.get("B200_ENABLE_MODULE_HOOK", "0") == "1",
     # print every ops.* call with shapes (utils.hooks.LoggingOps)
     "B200_ENABLE_OPS_HOOK": lambda: os.environ.get("B200_ENABLE_OPS_HOOK", "0") == "1",
+    # check on every decode-graph replay that the graph's input tensors still sit at the captured addresses
+    "B200_GRAPH_WATCH": lambda: os.environ.get("B200_GRAPH_WATCH", "0") == "1",
     # NVTX ranges around layers / ops
     "B200_NVTX": lambda: os.environ.get("B200_NVTX", "0") == "1",
     # programmatic dependent launch on decode-path kernels (read by the C++ side too)
