@@ -123,9 +123,6 @@ class GatedMLP(nn.Module):
             gu.bias.data.copy_(interleave_gate_up(gu.bias.data, inverse=not on))
         self.act_fused = on
 
-    def _save_to_state_dict(self, destination, prefix, keep_vars):
-        super()._save_to_state_dict(destination, prefix, keep_vars)
-
     def state_dict(self, *args, destination=None, prefix="", keep_vars=False):
         from ..ops.gemm_cuda import interleave_gate_up
         sd = super().state_dict(*args, destination=destination, prefix=prefix, keep_vars=keep_vars)
