@@ -26,7 +26,7 @@ def test_sources_avoid_closed_batch_copy_calls():
     banned = ["Memcpy" + "BatchAsync", "Memcpy3D" + "BatchAsync"]
     hits = []
     for base, _, files in os.walk(ROOT):
-        if any(part in base for part in (".git", "gpurun_out", "_work", "baseline", "build")):
+        if any(part in base for part in (".git", "_out", "_work", "baseline", "build")):
             continue
         for f in files:
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h", ".sh")):
