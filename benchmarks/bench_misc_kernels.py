@@ -119,13 +119,34 @@ def case_lora(small):
     report("lora_expand_kernel", sec, 2 * T * N * 2 + T * r * 4, f"T={T} N={N} r={r}")
 
 
+def case_gemm_splits(small):
+    """Decode-sized bf16 GEMMs of an 8B dense model at TP 1-8: default K split against forced 1-8 equal parts."""
+    from vllm_kunlun_b200.ops.gemm_cuda import gemm_bf16
+    shapes = [("qkv tp8", 768, 4096), ("qkv tp4", 1536, 4096), ("qkv tp2", 3072, 4096), ("qkv tp1", 6144, 4096),
+              ("o tp1", 4096, 4096), ("o tp2", 4096, 2048), ("o tp4", 4096, 1024), ("down tp1", 4096, 14336),
+              ("down tp2", 4096, 7168), ("down tp4", 4096, 3584), ("down tp8", 4096, 1792),
+              ("gate_up tp8", 3584, 4096)]
+    for name, N, K in shapes[:3] if small else shapes:
+        x = torch.randn(16, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+        out = torch.empty(16, N, device="cuda", dtype=torch.bfloat16)
+        res = {"default": timeit(lambda: gemm_bf16(x, w, None, out), iters=15, warm=4)}
+        for sp in (1, 2, 3, 4, 6, 8):
+            res[str(sp)] = timeit(lambda: gemm_bf16(x, w, None, out, splits=sp), iters=15, warm=4)
+        print(json.dumps({"kernel": "gemm_bf16", "shape": f"16x{N}x{K}", "name": name, "tiles": (N + 127) // 128,
+                          "us_by_splits": {k: round(v * 1e6, 1) for k, v in res.items()}}))
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all")
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     cases = {"sample": case_sample, "gdn": case_gdn, "conv": case_conv, "lora": case_lora}
+    explicit = {"gemm_splits": case_gemm_splits}  # not part of "all"
     with torch.inference_mode():
         for n, fn in cases.items():
             if a.case in ("all", n):
                 fn(a.small)
+        if a.case in explicit:
+            explicit[a.case](a.small)
