@@ -33,3 +33,27 @@ def test_sources_avoid_closed_batch_copy_calls():
                 text = open(os.path.join(base, f), errors="ignore").read()
                 hits += [(f, b) for b in banned if b in text]
     assert not hits, hits
+
+
+def test_community_stats_tool(tmp_path):
+    """The contribution-statistics tool parses `git log --numstat` of a scratch repository."""
+    import importlib.util
+    import subprocess
+
+    spec = importlib.util.spec_from_file_location("collect_repo_stats", os.path.join(ROOT, "community",
+                                                                                      "collect_repo_stats.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    repo = str(tmp_path)
+    env = dict(os.environ, GIT_AUTHOR_NAME="a", GIT_AUTHOR_EMAIL="a@x", GIT_COMMITTER_NAME="a",
+               GIT_COMMITTER_EMAIL="a@x")
+    subprocess.run(["git", "init", "-q", repo], check=True)
+    for i in range(2):
+        with open(os.path.join(repo, f"f{i}.txt"), "w") as f:
+            f.write("x\n" * (i + 1))
+        subprocess.run(["git", "-C", repo, "add", "-A"], check=True)
+        subprocess.run(["git", "-C", repo, "commit", "-qm", f"area: change {i}"], check=True, env=env)
+    s = mod.summarise(mod.git_log(repo, None))
+    assert s["commits"] == 2 and s["contributors"] == 1 and s["lines_added"] == 3
+    assert s["per_subject_prefix"] == {"area": 2}
+    assert "| a | 2 | 3 | 0 |" in mod.to_markdown(s)
