@@ -27,6 +27,7 @@ setup(
         "vllm.general_plugins": [
             "b200_model = vllm_kunlun_b200:register_model",
             "b200_quant = vllm_kunlun_b200:register_quant_method",
+            "b200_ops = vllm_kunlun_b200:register_custom_ops",
             "b200_reasoning_parser = vllm_kunlun_b200:register_reasoning_parser",
         ],
         "console_scripts": ["vllm-kunlun-b200 = vllm_kunlun_b200.entrypoints.cli:main"],

@@ -52,6 +52,12 @@ def register_quant_method() -> None:
     from . import quantization  # noqa: F401
 
 
+def register_custom_ops() -> None:
+    """``vllm.general_plugins`` entry point: define the ``torch.ops.b200.*`` dispatcher ops for tracing hosts."""
+    from .ops.custom_ops import register_custom_ops as _reg
+    _reg()
+
+
 def __getattr__(name):
     if name in ("LLM", "LLMEngine", "SamplingParams", "RequestOutput"):
         from . import engine
