@@ -247,3 +247,55 @@ def test_graph_input_watcher_detects_moved_tensors():
         w.check("g", {"ids": buf[4:]})    # another address
     with pytest.raises(KeyError):
         w.check("other", {})
+
+
+def test_serve_flags_map_to_llm_arguments():
+    import inspect
+
+    import pytest
+
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.entrypoints.openai_server import llm_kwargs, make_parser, parse_lora_modules
+    a = make_parser().parse_args([
+        "--model", "qwen3-30b-a3b", "-tp", "2", "--enable-expert-parallel", "--no-enable-chunked-prefill",
+        "--enable-prefix-caching", "--speculative-config", '{"method": "ngram", "num_speculative_tokens": 2}',
+        "--lora-modules", "sql=/adapters/sql", '{"name": "chat", "path": "/adapters/chat"}', "--max-loras", "1",
+        "--num-gpu-blocks-override", "77", "--kv-cache-dtype", "fp8", "--trust-remote-code"])
+    kw = llm_kwargs(a)
+    assert set(kw) <= set(inspect.signature(LLM.__init__).parameters)  # every key is a constructor argument
+    assert kw["tensor_parallel_size"] == 2 and kw["enable_expert_parallel"] and not kw["enable_chunked_prefill"]
+    assert kw["enable_prefix_caching"] and kw["speculative_config"]["method"] == "ngram"
+    assert kw["enable_lora"] and kw["max_loras"] == 2 and kw["num_gpu_blocks"] == 77 and kw["kv_cache_dtype"] == "fp8"
+    assert parse_lora_modules(a.lora_modules) == [("sql", "/adapters/sql"), ("chat", "/adapters/chat")]
+    for bad in (["x"], ["=p"], ["a=1", "a=2"]):
+        with pytest.raises(ValueError):
+            parse_lora_modules(bad)
+    d = llm_kwargs(make_parser().parse_args(["--model", "m"]))
+    assert not d["enable_lora"] and d["enable_chunked_prefill"] and d["speculative_config"] is None
+
+
+def test_openai_server_routes_adapters_by_model_name():
+    from fastapi.testclient import TestClient
+
+    from test_lora_cpu import _adapter, _cfg
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    cfg = _cfg()
+    kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    llm = LLM(cfg, enable_lora=True, max_loras=2, max_lora_rank=8, **kw)
+    ad = _adapter(cfg, 1)
+    llm.add_lora(ad)
+    prompt = list(range(3, 20))
+    sp = SamplingParams(max_tokens=6, ignore_eos=True, temperature=0.0)
+    want_base = llm.generate([prompt], sp)[0].token_ids
+    want_lora = llm.generate([prompt], sp, lora_request=ad)[0].token_ids
+    assert want_base != want_lora
+    app = build_app(llm, "base", lora_modules={"sql": ad.lora_int_id})
+    with TestClient(app) as c:
+        assert [m["id"] for m in c.get("/v1/models").json()["data"]] == ["base", "sql"]
+        body = {"prompt": prompt, "max_tokens": 6, "temperature": 0.0, "ignore_eos": True}
+        got_base = c.post("/v1/completions", json=dict(body, model="base")).json()["choices"][0]["text"]
+        got_lora = c.post("/v1/completions", json=dict(body, model="sql")).json()["choices"][0]["text"]
+        assert got_base == " ".join(map(str, want_base)) and got_lora == " ".join(map(str, want_lora))
+        r = c.post("/v1/completions", json=dict(body, model="nope"))
+        assert r.status_code == 404 and "does not exist" in r.json()["error"]["message"]

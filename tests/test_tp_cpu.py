@@ -101,3 +101,51 @@ def _launch(tp, pp):
 def test_parallel_matches_single(tp, pp):
     ref = _launch(1, 1)
     assert _launch(tp, pp) == ref
+
+
+def _serve_rank(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.entrypoints.openai_server import EngineLoop, build_app
+    cfg = _cfg()
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=world, block_size=16, max_model_len=128, max_num_seqs=4,
+              num_gpu_blocks=64)
+    with torch.inference_mode():
+        llm.engine.runner.model.load_weights(_full_state(cfg).items())
+    if rank > 0:
+        EngineLoop(llm).run_follower()  # returns when rank 0 stops
+    else:
+        from fastapi.testclient import TestClient
+        app = build_app(llm, "tiny")
+        with TestClient(app) as c:
+            texts = [c.post("/v1/completions", json={"prompt": p, "max_tokens": 8, "temperature": 0.0,
+                                                     "ignore_eos": True}).json()["choices"][0]["text"]
+                     for p in _prompts()]
+        app.state.engine_loop.stop()
+        q.put([[int(t) for t in s.split()] for s in texts])
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+def test_http_server_over_two_tp_ranks():
+    """Rank 0 serves HTTP and broadcasts each batch of new requests; rank 1 mirrors the steps.  The tokens equal
+    the single-process engine's."""
+    want = _launch(1, 1)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_serve_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        got = q.get(timeout=180)
+    except Exception:
+        for p in procs:
+            p.kill()
+        raise
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == want

@@ -54,57 +54,104 @@ class ChatPostProcessor:
 
 
 class EngineLoop:
-    """Owns the engine on a worker thread."""
+    """Owns the engine on a worker thread.
 
-    def __init__(self, llm):
+    With several ranks (one process per GPU, SPMD engine) rank 0 takes the HTTP requests and, once per loop
+    iteration, broadcasts the batch of new requests over a gloo control group; every rank then adds the same
+    requests and takes the same engine step, so the ranks' schedulers stay identical.  The other ranks call
+    :meth:`run_follower` instead of serving HTTP.  The control group is separate from the NCCL groups so that a
+    control message never waits on, or syncs with, the GPU streams."""
+
+    def __init__(self, llm, start: bool = True):
+        import torch.distributed as dist
         self.llm = llm
         self.inbox: "queue.Queue" = queue.Queue()
         self.streams: dict = {}
         self.stats = {"requests": 0, "tokens": 0}
         self._stop = False
-        self.thread = threading.Thread(target=self._run, daemon=True)
-        self.thread.start()
+        self.multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        self.rank = dist.get_rank() if self.multi else 0
+        self.ctrl = dist.new_group(backend="gloo") if self.multi else None  # collective: every rank creates it
+        self.thread = None
+        if start and self.rank == 0:
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
 
-    def submit(self, prompt_ids, sp: SamplingParams, loop, out_q):
+    def submit(self, prompt_ids, sp: SamplingParams, loop, out_q, lora_id: int = -1):
         rid = f"cmpl-{uuid.uuid4().hex}"
-        self.inbox.put((rid, prompt_ids, sp, loop, out_q))
+        self.inbox.put((rid, prompt_ids, sp, loop, out_q, lora_id))
         return rid
+
+    def stop(self):
+        """Ends the loop (and, through the last control message, the followers)."""
+        self._stop = True
+        if self.thread is not None:
+            self.thread.join(timeout=30)
+
+    def _broadcast(self, msg):
+        import torch.distributed as dist
+        box = [msg]
+        dist.broadcast_object_list(box, src=0, group=self.ctrl)
+        return box[0]
+
+    def run_follower(self):
+        """Ranks > 0: mirror rank 0's requests and steps until it says stop."""
+        eng = self.llm.engine
+        while True:
+            kind, new = self._broadcast(None)
+            if kind == "stop":
+                return
+            for rid, ids, sp, lora_id in new:
+                eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+            if eng.has_unfinished():
+                eng.step()
 
     def _run(self):
         eng = self.llm.engine
         sent: dict = {}
         while not self._stop:
+            new = []
             try:
                 while True:
-                    rid, ids, sp, loop, out_q = self.inbox.get_nowait() if eng.has_unfinished() else self.inbox.get(timeout=0.05)
-                    req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id)
-                    self.streams[rid] = (req, loop, out_q)
-                    sent[rid] = 0
-                    self.stats["requests"] += 1
+                    new.append(self.inbox.get_nowait() if (eng.has_unfinished() or new)
+                               else self.inbox.get(timeout=0.05))
             except queue.Empty:
                 pass
+            if self.multi:
+                self._broadcast(("step", [(rid, ids, sp, lora_id) for rid, ids, sp, _, _, lora_id in new]))
+            for rid, ids, sp, loop, out_q, lora_id in new:
+                req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                self.streams[rid] = (req, loop, out_q)
+                sent[rid] = 0
+                self.stats["requests"] += 1
             if not eng.has_unfinished():
                 continue
             eng.step()
             for rid, (req, loop, out_q) in list(self.streams.items()):
                 n = len(req.output_token_ids)
                 if n > sent[rid]:
-                    new = req.output_token_ids[sent[rid]:n]
-                    self.stats["tokens"] += len(new)
+                    new_toks = req.output_token_ids[sent[rid]:n]
+                    self.stats["tokens"] += len(new_toks)
                     sent[rid] = n
-                    loop.call_soon_threadsafe(out_q.put_nowait, ("tokens", new))
+                    loop.call_soon_threadsafe(out_q.put_nowait, ("tokens", new_toks))
                 if req.status.finished:
                     reason = "length" if req.status.name.endswith("LENGTH") else "stop"
                     loop.call_soon_threadsafe(out_q.put_nowait, ("done", reason))
                     del self.streams[rid], sent[rid]
+        if self.multi:
+            self._broadcast(("stop", []))
 
 
-def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None):
+def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lora_modules: Optional[dict] = None):
+    """``lora_modules``: adapter name -> adapter id of adapters already loaded with ``llm.add_lora``; a request
+    whose ``model`` field names one runs with that adapter (upstream's ``--lora-modules`` convention)."""
     from fastapi import FastAPI, Request
+    lora_modules = dict(lora_modules or {})
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
     app = FastAPI()
     loop_obj = EngineLoop(llm)
+    app.state.engine_loop = loop_obj
     tok = llm.tokenizer
 
     def encode(text):
@@ -128,7 +175,10 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None):
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "vllm_kunlun_b200"}]}
+        data = [{"id": model_name, "object": "model", "owned_by": "vllm_kunlun_b200"}]
+        data += [{"id": n, "object": "model", "owned_by": "vllm_kunlun_b200", "parent": model_name}
+                 for n in lora_modules]
+        return {"object": "list", "data": data}
 
     @app.get("/metrics")
     async def metrics():
@@ -138,10 +188,14 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None):
                  f"b200_spec_accepted_total {e['spec_accepted']}", f"b200_spec_proposed_total {e['spec_proposed']}"]
         return PlainTextResponse("\n".join(lines) + "\n")
 
-    async def run(prompt_ids, sp, stream, make_chunk, make_final):
+    async def run(prompt_ids, sp, stream, make_chunk, make_final, requested_model=None):
+        # the name selects an adapter; with no adapters loaded every name is served by the base model
+        if lora_modules and requested_model not in (None, "", model_name) and requested_model not in lora_modules:
+            return JSONResponse({"error": {"message": f"The model `{requested_model}` does not exist.",
+                                           "type": "NotFoundError", "code": 404}}, status_code=404)
         loop = asyncio.get_running_loop()
         out_q: asyncio.Queue = asyncio.Queue()
-        rid = loop_obj.submit(prompt_ids, sp, loop, out_q)
+        rid = loop_obj.submit(prompt_ids, sp, loop, out_q, lora_modules.get(requested_model, -1))
         created = int(time.time())
         if stream:
             async def gen():
@@ -179,7 +233,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None):
             d = chunk(rid, created, text, fin)
             d["usage"] = {"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out}
             return d
-        return await run(ids, sampling(body), bool(body.get("stream")), chunk, final)
+        return await run(ids, sampling(body), bool(body.get("stream")), chunk, final, body.get("model"))
 
     @app.post("/v1/chat/completions")
     async def chat(req: Request):
@@ -213,45 +267,112 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None):
                     "choices": [{"index": 0, "message": msg,
                                  "finish_reason": "tool_calls" if msg.get("tool_calls") else fin}],
                     "usage": {"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out}}
-        return await run(list(ids), sampling(body), bool(body.get("stream")), chunk, final)
+        return await run(list(ids), sampling(body), bool(body.get("stream")), chunk, final, body.get("model"))
 
     return app
 
 
-def main(argv=None):
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--model", required=True)
+def make_parser() -> argparse.ArgumentParser:
+    """The flags of upstream's ``vllm serve`` that this engine implements, under the same names."""
+    ap = argparse.ArgumentParser(prog="vllm-kunlun-b200 serve")
+    ap.add_argument("--model", required=True, help="HF directory or a preset name")
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--dtype", default=None, choices=[None, "bfloat16", "float16", "float32"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--tensor-parallel-size", "-tp", type=int, default=1)
+    ap.add_argument("--pipeline-parallel-size", "-pp", type=int, default=1)
+    ap.add_argument("--decode-context-parallel-size", "-dcp", type=int, default=1)
+    ap.add_argument("--enable-expert-parallel", action="store_true")
     ap.add_argument("--max-model-len", type=int, default=8192)
     ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--block-size", type=int, default=64)
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    ap.add_argument("--num-gpu-blocks-override", type=int, default=None)
+    ap.add_argument("--kv-cache-dtype", default="auto")
+    ap.add_argument("--enable-prefix-caching", action=argparse.BooleanOptionalAction, default=False)
+    ap.add_argument("--enable-chunked-prefill", action=argparse.BooleanOptionalAction, default=True)
     ap.add_argument("--enforce-eager", action="store_true")
+    ap.add_argument("--speculative-config", type=json.loads, default=None,
+                    help='JSON, e.g. \'{"method": "mtp", "num_speculative_tokens": 1}\'')
+    ap.add_argument("--enable-lora", action="store_true")
+    ap.add_argument("--max-loras", type=int, default=4)
+    ap.add_argument("--max-lora-rank", type=int, default=16)
+    ap.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH",
+                    help="adapters to load at start; also JSON objects with name / path keys")
     ap.add_argument("--reasoning-parser", default=None)
     ap.add_argument("--tool-call-parser", default=None)
-    ap.add_argument("--served-model-name", default=None)
-    a = ap.parse_args(argv)
+    ap.add_argument("--enable-auto-tool-choice", action="store_true", help="accepted for compatibility")
+    ap.add_argument("--trust-remote-code", action="store_true", help="accepted for compatibility; never executed")
+    return ap
+
+
+def llm_kwargs(a: argparse.Namespace) -> dict:
+    """Parsed flags -> keyword arguments of :class:`vllm_kunlun_b200.engine.llm.LLM`."""
+    return dict(tensor_parallel_size=a.tensor_parallel_size, pipeline_parallel_size=a.pipeline_parallel_size,
+                decode_context_parallel_size=a.decode_context_parallel_size,
+                enable_expert_parallel=a.enable_expert_parallel, dtype=a.dtype, seed=a.seed,
+                max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
+                max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size,
+                gpu_memory_utilization=a.gpu_memory_utilization, num_gpu_blocks=a.num_gpu_blocks_override,
+                kv_cache_dtype=a.kv_cache_dtype, enable_prefix_caching=a.enable_prefix_caching,
+                enable_chunked_prefill=a.enable_chunked_prefill, enforce_eager=a.enforce_eager,
+                speculative_config=a.speculative_config, enable_lora=a.enable_lora or bool(a.lora_modules),
+                max_loras=max(a.max_loras, len(a.lora_modules)), max_lora_rank=a.max_lora_rank)
+
+
+def parse_lora_modules(items) -> list:
+    """``NAME=PATH`` or ``{"name": ..., "path": ...}`` -> ``[(name, path)]`` in order, names unique."""
+    out, seen = [], set()
+    for it in items or []:
+        if it.lstrip().startswith("{"):
+            d = json.loads(it)
+            name, path = d["name"], d["path"]
+        else:
+            name, sep, path = it.partition("=")
+            if not sep or not name or not path:
+                raise ValueError(f"--lora-modules wants NAME=PATH, got {it!r}")
+        if name in seen:
+            raise ValueError(f"adapter name {name!r} given twice")
+        seen.add(name)
+        out.append((name, path))
+    return out
+
+
+def main(argv=None):
+    a = make_parser().parse_args(argv)
+    import os
+
     import uvicorn
 
     from ..engine.llm import LLM
     tokenizer = None
-    import os
     if os.path.isdir(a.model):
         try:
             from transformers import AutoTokenizer
             tokenizer = AutoTokenizer.from_pretrained(a.model)
         except Exception:
             tokenizer = None
-    llm = LLM(a.model, tensor_parallel_size=a.tensor_parallel_size, max_model_len=a.max_model_len,
-              max_num_seqs=a.max_num_seqs, block_size=a.block_size, gpu_memory_utilization=a.gpu_memory_utilization,
-              enforce_eager=a.enforce_eager, tokenizer=tokenizer)
+    llm = LLM(a.model, tokenizer=tokenizer, **llm_kwargs(a))
+    lora_ids = {}
+    if a.lora_modules:
+        from ..lora import LoRARequest
+        for i, (name, path) in enumerate(parse_lora_modules(a.lora_modules), start=1):
+            llm.add_lora(LoRARequest(name, i, lora_path=path))
+            lora_ids[name] = i
     graphs = llm.engine.runner.graphs
     if graphs is not None:  # capture every decode batch size before the first request arrives
         graphs.capture_all()
-    app = build_app(llm, a.served_model_name or a.model, a.reasoning_parser, a.tool_call_parser)
-    uvicorn.run(app, host=a.host, port=a.port, log_level="info")
+    if int(os.environ.get("RANK", "0")) > 0:  # SPMD follower: no HTTP, mirror rank 0
+        EngineLoop(llm).run_follower()
+        return
+    app = build_app(llm, a.served_model_name or a.model, a.reasoning_parser, a.tool_call_parser, lora_ids)
+    try:
+        uvicorn.run(app, host=a.host, port=a.port, log_level="info")
+    finally:
+        app.state.engine_loop.stop()
 
 
 if __name__ == "__main__":
