@@ -299,3 +299,57 @@ def test_openai_server_routes_adapters_by_model_name():
         assert got_base == " ".join(map(str, want_base)) and got_lora == " ".join(map(str, want_lora))
         r = c.post("/v1/completions", json=dict(body, model="nope"))
         assert r.status_code == 404 and "does not exist" in r.json()["error"]["message"]
+
+
+def test_stop_strings_incremental():
+    from vllm_kunlun_b200.entrypoints.openai_server import StopStrings, stop_list
+    s = StopStrings(["</end>", "\n\n"])
+    out, hit = "", False
+    for piece in ["hel", "lo <", "/en", "x <", "/end", ">tail"]:
+        p, hit = s.feed(piece)
+        out += p
+        if hit:
+            break
+    assert hit and out == "hello </enx "  # a look-alike prefix is released once it cannot match any more
+    s = StopStrings(["STOP"])
+    assert s.feed("abcST") == ("ab", False) and s.flush() == "cST"  # held-back tail comes out at the end
+    assert StopStrings(()).feed("abc") == ("abc", False)
+    assert stop_list({}) == () and stop_list({"stop": "a"}) == ("a",) and stop_list({"stop": ["a", "b"]}) == ("a", "b")
+
+
+def test_openai_server_stop_string_and_stop_token_abort_the_request():
+    import json
+
+    from fastapi.testclient import TestClient
+
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    cfg = tiny(qwen2_0_5b(), num_layers=1, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    app = build_app(llm, "tiny")
+    body = {"prompt": list(range(5, 17)), "max_tokens": 12, "temperature": 0.0, "ignore_eos": True}
+    with TestClient(app) as c:
+        toks = [int(t) for t in c.post("/v1/completions", json=body).json()["choices"][0]["text"].split()]
+        assert len(toks) == 12
+        # a stop token id ends the request inside the engine, at its first occurrence
+        r = c.post("/v1/completions", json=dict(body, stop_token_ids=[toks[4]])).json()
+        got = [int(t) for t in r["choices"][0]["text"].split()]
+        assert got == toks[:toks.index(toks[4]) + 1] and r["choices"][0]["finish_reason"] == "stop"
+        # a stop string is matched on the decoded text (without a tokenizer: the ids' digits, one piece per token)
+        full = "".join(map(str, toks))
+        stop = str(toks[6])
+        r = c.post("/v1/completions", json=dict(body, stop=stop)).json()
+        assert r["choices"][0]["text"] == full[:full.find(stop)] and r["choices"][0]["finish_reason"] == "stop"
+        assert r["usage"]["completion_tokens"] < 12
+        # streaming: the same text arrives in pieces and the stream closes with finish_reason stop
+        with c.stream("POST", "/v1/completions", json=dict(body, stop=stop, stream=True)) as resp:
+            events = [json.loads(l[6:]) for l in resp.iter_lines() if l.startswith("data: {")]
+        assert "".join(e["choices"][0]["text"] for e in events) == full[:full.find(stop)]
+        assert events[-1]["choices"][0]["finish_reason"] == "stop"
+        # the aborted requests released their blocks: a fresh request still runs to its full length
+        again = c.post("/v1/completions", json=body).json()["choices"][0]["text"].split()
+        assert [int(t) for t in again] == toks
+        assert app.state.engine_loop.stats["aborted"] >= 1
+    assert not llm.engine.has_unfinished()

@@ -53,6 +53,38 @@ class ChatPostProcessor:
         return msg
 
 
+class StopStrings:
+    """Incremental stop-string matching on decoded text: ``feed`` returns the text that is safe to emit (nothing
+    that could still turn out to be the beginning of a stop string) and whether a stop string was reached; the
+    stop string itself is never emitted (OpenAI ``stop`` semantics)."""
+
+    def __init__(self, stops=()):
+        self.stops = [s for s in stops if s]
+        self.hold = max((len(s) for s in self.stops), default=1) - 1
+        self.buf = ""
+
+    def feed(self, text: str):
+        if not self.stops:
+            return text, False
+        self.buf += text
+        at = min((i for i in (self.buf.find(s) for s in self.stops) if i >= 0), default=-1)
+        if at >= 0:
+            out, self.buf = self.buf[:at], ""
+            return out, True
+        keep = min(self.hold, len(self.buf))
+        out, self.buf = self.buf[:len(self.buf) - keep], self.buf[len(self.buf) - keep:]
+        return out, False
+
+    def flush(self) -> str:
+        out, self.buf = self.buf, ""
+        return out
+
+
+def stop_list(body) -> tuple:
+    st = body.get("stop")
+    return () if not st else ((st,) if isinstance(st, str) else tuple(st))
+
+
 class EngineLoop:
     """Owns the engine on a worker thread.
 
@@ -67,8 +99,9 @@ class EngineLoop:
         self.llm = llm
         self.inbox: "queue.Queue" = queue.Queue()
         self.streams: dict = {}
-        self.stats = {"requests": 0, "tokens": 0}
+        self.stats = {"requests": 0, "tokens": 0, "aborted": 0}
         self._stop = False
+        self.aborts: "queue.Queue" = queue.Queue()
         self.multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
         self.rank = dist.get_rank() if self.multi else 0
         self.ctrl = dist.new_group(backend="gloo") if self.multi else None  # collective: every rank creates it
@@ -81,6 +114,10 @@ class EngineLoop:
         rid = f"cmpl-{uuid.uuid4().hex}"
         self.inbox.put((rid, prompt_ids, sp, loop, out_q, lora_id))
         return rid
+
+    def abort(self, rid: str):
+        """Ask the loop to drop a request (stop string matched, client gone); takes effect before the next step."""
+        self.aborts.put(rid)
 
     def stop(self):
         """Ends the loop (and, through the last control message, the followers)."""
@@ -98,9 +135,11 @@ class EngineLoop:
         """Ranks > 0: mirror rank 0's requests and steps until it says stop."""
         eng = self.llm.engine
         while True:
-            kind, new = self._broadcast(None)
+            kind, new, aborts = self._broadcast(None)
             if kind == "stop":
                 return
+            for rid in aborts:
+                eng.abort(rid)
             for rid, ids, sp, lora_id in new:
                 eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
             if eng.has_unfinished():
@@ -117,16 +156,22 @@ class EngineLoop:
                                else self.inbox.get(timeout=0.05))
             except queue.Empty:
                 pass
+            aborts = []
+            while not self.aborts.empty():
+                aborts.append(self.aborts.get_nowait())
             if self.multi:
-                self._broadcast(("step", [(rid, ids, sp, lora_id) for rid, ids, sp, _, _, lora_id in new]))
+                self._broadcast(("step", [(rid, ids, sp, lora_id) for rid, ids, sp, _, _, lora_id in new], aborts))
+            for rid in aborts:
+                self.stats["aborted"] += int(eng.abort(rid))
             for rid, ids, sp, loop, out_q, lora_id in new:
                 req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
                 self.streams[rid] = (req, loop, out_q)
                 sent[rid] = 0
                 self.stats["requests"] += 1
-            if not eng.has_unfinished():
+            if eng.has_unfinished():
+                eng.step()
+            elif not aborts:
                 continue
-            eng.step()
             for rid, (req, loop, out_q) in list(self.streams.items()):
                 n = len(req.output_token_ids)
                 if n > sent[rid]:
@@ -139,7 +184,7 @@ class EngineLoop:
                     loop.call_soon_threadsafe(out_q.put_nowait, ("done", reason))
                     del self.streams[rid], sent[rid]
         if self.multi:
-            self._broadcast(("stop", []))
+            self._broadcast(("stop", [], []))
 
 
 def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lora_modules: Optional[dict] = None):
@@ -167,6 +212,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                               temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
                               top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
                               ignore_eos=bool(body.get("ignore_eos", False)),
+                              stop_token_ids=tuple(int(t) for t in (body.get("stop_token_ids") or ())),
                               repetition_penalty=float(body.get("repetition_penalty", 1.0)))
 
     @app.get("/health")
@@ -188,7 +234,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                  f"b200_spec_accepted_total {e['spec_accepted']}", f"b200_spec_proposed_total {e['spec_proposed']}"]
         return PlainTextResponse("\n".join(lines) + "\n")
 
-    async def run(prompt_ids, sp, stream, make_chunk, make_final, requested_model=None):
+    async def run(prompt_ids, sp, stream, make_chunk, make_final, requested_model=None, stops=()):
         # the name selects an adapter; with no adapters loaded every name is served by the base model
         if lora_modules and requested_model not in (None, "", model_name) and requested_model not in lora_modules:
             return JSONResponse({"error": {"message": f"The model `{requested_model}` does not exist.",
@@ -197,27 +243,50 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
         out_q: asyncio.Queue = asyncio.Queue()
         rid = loop_obj.submit(prompt_ids, sp, loop, out_q, lora_modules.get(requested_model, -1))
         created = int(time.time())
+        cut = StopStrings(stops)
         if stream:
             async def gen():
                 ids = []
-                while True:
-                    kind, val = await out_q.get()
-                    if kind == "tokens":
-                        ids += val
-                        yield f"data: {json.dumps(make_chunk(rid, created, decode(val), None))}\n\n"
-                    else:
-                        yield f"data: {json.dumps(make_chunk(rid, created, '', val))}\n\n"
-                        yield "data: [DONE]\n\n"
-                        return
+                try:
+                    while True:
+                        kind, val = await out_q.get()
+                        if kind == "tokens":
+                            ids += val
+                            piece, hit = cut.feed(decode(val))
+                            if piece:
+                                yield f"data: {json.dumps(make_chunk(rid, created, piece, None))}\n\n"
+                            if hit:
+                                loop_obj.abort(rid)
+                                yield f"data: {json.dumps(make_chunk(rid, created, '', 'stop'))}\n\n"
+                                yield "data: [DONE]\n\n"
+                                return
+                        else:
+                            rest = cut.flush()
+                            if rest:
+                                yield f"data: {json.dumps(make_chunk(rid, created, rest, None))}\n\n"
+                            yield f"data: {json.dumps(make_chunk(rid, created, '', val))}\n\n"
+                            yield "data: [DONE]\n\n"
+                            return
+                except asyncio.CancelledError:  # the client went away: free the request's blocks
+                    loop_obj.abort(rid)
+                    raise
             return StreamingResponse(gen(), media_type="text/event-stream")
-        ids, reason = [], None
+        ids, reason, text = [], None, ""
         while reason is None:
             kind, val = await out_q.get()
             if kind == "tokens":
                 ids += val
+                if stops:
+                    piece, hit = cut.feed(decode(val))
+                    text += piece
+                    if hit:
+                        loop_obj.abort(rid)
+                        reason = "stop"
             else:
                 reason = val
-        return JSONResponse(make_final(rid, created, decode(ids), reason, len(prompt_ids), len(ids)))
+                text += cut.flush()
+        return JSONResponse(make_final(rid, created, text if stops else decode(ids), reason, len(prompt_ids),
+                                       len(ids)))
 
     @app.post("/v1/completions")
     async def completions(req: Request):
@@ -233,7 +302,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
             d = chunk(rid, created, text, fin)
             d["usage"] = {"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out}
             return d
-        return await run(ids, sampling(body), bool(body.get("stream")), chunk, final, body.get("model"))
+        return await run(ids, sampling(body), bool(body.get("stream")), chunk, final, body.get("model"), stop_list(body))
 
     @app.post("/v1/chat/completions")
     async def chat(req: Request):
@@ -267,7 +336,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                     "choices": [{"index": 0, "message": msg,
                                  "finish_reason": "tool_calls" if msg.get("tool_calls") else fin}],
                     "usage": {"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out}}
-        return await run(list(ids), sampling(body), bool(body.get("stream")), chunk, final, body.get("model"))
+        return await run(list(ids), sampling(body), bool(body.get("stream")), chunk, final, body.get("model"), stop_list(body))
 
     return app
 
