@@ -230,6 +230,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
     async def metrics():
         s, e = loop_obj.stats, llm.engine.stats
         lines = [f"b200_requests_total {s['requests']}", f"b200_generation_tokens_total {s['tokens']}",
+                 f"b200_requests_aborted_total {s['aborted']}",
                  f"b200_engine_steps_total {e['steps']}", f"b200_preemptions_total {e['preemptions']}",
                  f"b200_spec_accepted_total {e['spec_accepted']}", f"b200_spec_proposed_total {e['spec_proposed']}"]
         return PlainTextResponse("\n".join(lines) + "\n")
