@@ -40,6 +40,28 @@ typedef struct GemmArgs {
 int b200_gemm_pick_bn(int T);
 int b200_gemm_launch(const GemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
 
+// Decode-sized GEMM (one token tile of at most 32 rows): cluster split-K with the reduction in the leader CTA's
+// shared memory; optional gated activation or tensor-parallel push epilogue (gemm/gemm_decode.cu).
+typedef struct GemmDecodeArgs {
+  void* out;            // [T, ldo]
+  const void* bias;     // [N] or null
+  int* status;
+  int T, N, K;
+  int n_tiles;          // ceil(N / 128)
+  int S;                // CTAs per cluster = K splits per weight tile, 1..8 (at most 4 when bn = 32)
+  int kb_per_cta;       // ceil(ceil(K / 64) / S); (S - 1) * kb_per_cta must be < ceil(K / 64)
+  int fmt, ldo, bn;     // bn: 16 or 32
+  int stages;           // 0 = choose
+  int ctas_per_sm;      // 1 or 2: shared-memory budget per CTA
+  int act;              // as in GemmArgs
+  // row-parallel epilogue under tensor parallelism: store locally and push {data, epoch} units to every peer
+  int ar_on, rank, nranks;
+  void* ll_bufs[8];     // low-latency all-reduce buffers of all ranks (peer mappings)
+  const void* epoch_word;  // device word holding the number of completed all-reduce calls
+  int64_t ll_slot_bytes;
+} GemmDecodeArgs;
+int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
+
 // Grouped (rows sorted by expert) and/or fp8 block-scaled GEMM; lod == null -> one group of M rows.
 typedef struct GroupedGemmArgs {
   void* out;             // [M, ldo] bf16/fp16
@@ -152,7 +174,7 @@ int b200_oneshot_allreduce(void* const* bufs, const void* in, void* out, void* r
 
 int b200_ll_allreduce(void* const* bufs, const void* in, void* out, void* residual, const void* weight,
                       uint32_t* epochs, int* status, int64_t slot_bytes, int rank, int nranks, int rows, int H,
-                      float eps, int gemma, int grid, uint32_t spin_limit, int dtype, cudaStream_t st);
+                      float eps, int gemma, int grid, uint32_t spin_limit, int skip_push, int dtype, cudaStream_t st);
 
 // Reduce-scatter consumer: sum R partial rows + residual, RMSNorm, push the row to every rank (see rs_norm_ag.cu)
 typedef struct RsNormArgs {

@@ -190,10 +190,100 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
   gs.launches++;
 }
 
+// Row-parallel push epilogue for the NEXT gemm_decode() call: the output is also written, as {data, epoch} units,
+// into the low-latency all-reduce slots of every peer (consumed by ll_allreduce(..., skip_push = true)).
+struct DecCommState {
+  bool active = false;
+  void* ll_bufs[8] = {nullptr};
+  const void* epoch_word = nullptr;
+  int64_t slot_bytes = 0;
+  int rank = 0, nranks = 0;
+};
+DecCommState g_dec_comm;
+void set_gemm_decode_comm(std::vector<int64_t> ll_bufs, at::Tensor epochs, int64_t slot_bytes, int64_t rank) {
+  g_dec_comm = DecCommState();
+  TORCH_CHECK(ll_bufs.size() <= 8 && ll_bufs.size() >= 2);
+  g_dec_comm.active = true;
+  for (size_t i = 0; i < ll_bufs.size(); ++i) g_dec_comm.ll_bufs[i] = reinterpret_cast<void*>(ll_bufs[i]);
+  g_dec_comm.epoch_word = epochs.data_ptr<int>();
+  g_dec_comm.slot_bytes = slot_bytes;
+  g_dec_comm.rank = rank;
+  g_dec_comm.nranks = ll_bufs.size();
+}
+
+// Decode-sized GEMM (T <= 32): cluster split-K with the reduction in distributed shared memory.
+// splits <= 0 lets the library choose the cluster size.
+void gemm_decode(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+                 int64_t splits, int64_t stages, int64_t ctas_per_sm, int64_t act) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda());
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2);
+  TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == out.scalar_type());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "gemm_decode: bf16/fp16 only");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1);
+  const int T = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(T <= 32, "gemm_decode: at most 32 rows");
+  TORCH_CHECK(w.size(1) == K && out.size(0) == T && out.size(1) == (act ? N / 2 : N));
+  if (act) TORCH_CHECK(N % 128 == 0 && out.stride(0) % 8 == 0, "fused gate/up activation needs whole [64 | 64] weight tiles");
+  TORCH_CHECK(K % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0, "gemm_decode: K and row strides must be multiples of 8");
+  if (T == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(x.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, x.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, x.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, x.options().dtype(at::kInt));
+  }
+  GemmDecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.out = out.data_ptr(); a.bias = opt_ptr(bias); a.status = gs.status.data_ptr<int>();
+  a.T = T; a.N = N; a.K = K;
+  a.n_tiles = (N + 127) / 128;
+  a.bn = T <= 16 ? 16 : 32;
+  a.fmt = x.scalar_type() == at::kBFloat16 ? 1 : 0;
+  a.ldo = out.stride(0);
+  a.act = (int)act;
+  const int total_kb = (K + 63) / 64;
+  const int max_s = a.bn == 16 ? 8 : 4;
+  int S = (int)splits;
+  if (S <= 0) {
+    // Measured in graph chains over the decode shapes of an 8B model at TP 1-8 (benchmarks/bench_gemm_decode_sweep.py):
+    // the largest power-of-two cluster that keeps all CTAs on distinct SMs and leaves every CTA at least 8 k-blocks
+    // (128 KB of weights) wins or ties; odd cluster sizes schedule badly; a cluster costs about 1 us over S = 1.
+    S = 1;
+    while (S * 2 <= max_s && a.n_tiles * S * 2 <= gs.num_sms && total_kb / (S * 2) >= 8) S *= 2;
+  }
+  S = std::max(1, std::min(S, std::min(max_s, total_kb)));
+  while (S > 1 && (S - 1) * ((total_kb + S - 1) / S) >= total_kb) --S;  // no CTA without work
+  a.S = S;
+  a.kb_per_cta = (total_kb + S - 1) / S;
+  a.stages = (int)stages;
+  a.ctas_per_sm = ctas_per_sm > 0 ? (int)ctas_per_sm : (a.n_tiles * S > gs.num_sms ? 2 : 1);
+  if (g_dec_comm.active) {
+    TORCH_CHECK(!act && N % 8 == 0 && out.stride(0) == N, "push epilogue needs a contiguous [T, N] output");
+    TORCH_CHECK((int64_t)T * N * 4 <= g_dec_comm.slot_bytes, "push epilogue: payload exceeds the all-reduce slot");
+    a.ar_on = 1; a.rank = g_dec_comm.rank; a.nranks = g_dec_comm.nranks;
+    for (int i = 0; i < 8; ++i) a.ll_bufs[i] = g_dec_comm.ll_bufs[i];
+    a.epoch_word = g_dec_comm.epoch_word; a.ll_slot_bytes = g_dec_comm.slot_bytes;
+    g_dec_comm.active = false;
+  }
+  const Tmap& tw = get_tmap(gs, w, 128, 2);
+  const Tmap& tx = get_tmap(gs, x, a.bn, 2);
+  check(b200_gemm_decode_launch(&a, tw.b, tx.b, stream()), "gemm_decode launch");
+  gs.launches++;
+}
+
 int64_t gemm_status() {
   GemmState& gs = gemm_state();
   if (!gs.status.defined()) return 0;
   return gs.status.item<int>();
+}
+// The GEMM status word itself (one int32 on the device), for callers that copy it to the host with other results.
+c10::optional<at::Tensor> gemm_status_tensor() {
+  GemmState& gs = gemm_state();
+  if (!gs.status.defined()) return c10::nullopt;
+  return gs.status;
 }
 void gemm_clear_tmap_cache() { gemm_state().cache.clear(); }
 
@@ -615,7 +705,7 @@ void oneshot_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tens
 void ll_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tensor out,
                   const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& weight, at::Tensor epochs,
                   at::Tensor status, int64_t slot_bytes, int64_t rank, double eps, bool gemma, int64_t grid,
-                  int64_t spin_limit) {
+                  int64_t spin_limit, bool skip_push) {
   TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.dim() == 2 && in.element_size() == 2);
   if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && weight.has_value());
   void* ptrs[8] = {nullptr};
@@ -624,7 +714,7 @@ void ll_allreduce(std::vector<int64_t> bufs, const at::Tensor& in, at::Tensor ou
   check(b200_ll_allreduce(ptrs, in.data_ptr(), out.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
                           opt_ptr(weight), reinterpret_cast<uint32_t*>(epochs.data_ptr<int>()), status.data_ptr<int>(),
                           slot_bytes, rank, bufs.size(), in.size(0), in.size(1), (float)eps, gemma, grid,
-                          (uint32_t)spin_limit, dtype_code(in), stream()), "ll_allreduce");
+                          (uint32_t)spin_limit, skip_push ? 1 : 0, dtype_code(in), stream()), "ll_allreduce");
 }
 
 at::Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, at::ScalarType dtype, int64_t device) {
@@ -804,6 +894,7 @@ struct EpHandle {
                           stream()), "ep_combine", 2);
   }
   int64_t status() { return state[3 * a.R + 4].item<int>(); }
+  at::Tensor status_tensor() { return state.slice(0, 3 * a.R + 4, 3 * a.R + 5); }
   at::Tensor recv_count() { return state.slice(0, a.R, 2 * a.R); }
 };
 
@@ -829,6 +920,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("gemm_status", &gemm_status);
+  m.def("gemm_status_tensor", &gemm_status_tensor);
+  m.def("gemm_decode", &gemm_decode);
+  m.def("set_gemm_decode_comm", &set_gemm_decode_comm);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("moe_route", &moe_route);
   m.def("moe_permute", &moe_permute, py::arg("x"), py::arg("ids"), py::arg("emap"), py::arg("E_local"),
@@ -892,5 +986,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("permute_scales", &EpHandle::permute_scales)
       .def("combine", &EpHandle::combine)
       .def("status", &EpHandle::status)
+      .def("status_tensor", &EpHandle::status_tensor)
       .def("recv_count", &EpHandle::recv_count);
 }

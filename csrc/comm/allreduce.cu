@@ -11,9 +11,12 @@
 //      then either store, or add the residual, store it back and RMS-normalise the row.
 // Two data parities make one barrier per call enough: a rank can only reach call k+2 (which
 // reuses parity k) after every peer has entered call k+1, i.e. finished reading call k.
-// Epochs live in device memory and are advanced by the kernel itself, so CUDA-graph replays
-// need no host-side reset.  The wait is bounded; on time-out the status word is set and the
-// kernel completes (with wrong data) instead of hanging the GPU.
+// The epoch is ONE call counter per communicator, kept in device memory (epochs[0]) and advanced by
+// the kernel itself (the last CTA to finish, found through the ticket in epochs[1]), so CUDA-graph
+// replays need no host-side reset and every CTA of a call - whatever the grid or the row width of
+// this and earlier calls - works with the same epoch and the same parity.  The wait is bounded; on
+// time-out the status word is set and the kernel completes (with wrong data) instead of hanging
+// the GPU; the host reads the word with every step's result.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -48,7 +51,7 @@ struct ArParams {
   void* out;                 // [rows, H]
   void* residual;            // [rows, H] (fused norm) or null
   const void* weight;        // [H] (fused norm) or null
-  uint32_t* epochs;          // [kArMaxCtas] local per-CTA call counters
+  uint32_t* epochs;          // [0] completed calls of this communicator, [1] finished-CTA ticket of the running call
   int* status;
   int64_t parity_bytes;      // size of one data parity
   int64_t flags_offset;      // byte offset of the flag block inside a symmetric buffer
@@ -57,7 +60,22 @@ struct ArParams {
   int gemma;
   uint32_t spin_limit;
   int64_t ll_slot_bytes;     // low-latency variant: bytes of one (parity, source) slot of a symmetric buffer
+  int skip_push;             // low-latency variant: the producer of `in` (a GEMM epilogue) has already pushed it
 };
+
+// Called by every CTA after its last use of the epoch: the last one publishes the finished call.
+__device__ __forceinline__ void finish_call(uint32_t* epochs, uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(&epochs[1], 1u);
+    if (t == gridDim.x - 1) {
+      epochs[1] = 0;
+      __threadfence();
+      epochs[0] = epoch;
+    }
+  }
+}
 
 template <typename T, bool kNorm>
 __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams p) {
@@ -67,7 +85,7 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams 
   griddep_wait();
   const int c = blockIdx.x, G = gridDim.x;
   const int tid = threadIdx.x;
-  const uint32_t epoch = p.epochs[c] + 1;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.epochs) + 1;
   const int parity = epoch & 1;
   const int nvec = p.H / V;
   T* my_data = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(p.bufs[p.rank]) + parity * p.parity_bytes);
@@ -94,7 +112,6 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams 
     if (!ok) atomicCAS(p.status, 0, 200 + tid);
   }
   __syncthreads();
-  if (tid == 0) p.epochs[c] = epoch;
 
   // 4. reduce (and normalise)
   for (int row = c; row < p.rows; row += G) {
@@ -156,6 +173,7 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(ArParams 
       __syncthreads();
     }
   }
+  finish_call(p.epochs, epoch);
 }
 
 
@@ -183,15 +201,15 @@ __global__ void __launch_bounds__(kArThreads) ll_allreduce_kernel(ArParams p) {
   griddep_launch();
   griddep_wait();
   const int c = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
-  const uint32_t epoch = p.epochs[c] + 1;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.epochs) + 1;
   const int parity = epoch & 1;
   const int nvec = p.H / V;
   const int64_t row_bytes = (int64_t)p.H * 4;  // 2 H bytes of payload, doubled by the flags
   auto slot = [&](int dest, int src) {
     return reinterpret_cast<uint8_t*>(p.bufs[dest]) + ((int64_t)parity * p.nranks + src) * p.ll_slot_bytes;
   };
-  // 1. push my rows to every peer
-  for (int row = c; row < p.rows; row += G) {
+  // 1. push my rows to every peer (unless the kernel that produced them already has)
+  for (int row = c; row < p.rows && !p.skip_push; row += G) {
     for (int i = tid; i < nvec; i += kArThreads) {
       const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.in) + (int64_t)row * p.H + i * V);
       for (int d = 0; d < p.nranks; ++d) {
@@ -274,8 +292,7 @@ __global__ void __launch_bounds__(kArThreads) ll_allreduce_kernel(ArParams p) {
       __syncthreads();
     }
   }
-  __syncthreads();
-  if (tid == 0) p.epochs[c] = epoch;
+  finish_call(p.epochs, epoch);
 }
 
 }  // namespace b200
@@ -295,7 +312,7 @@ extern "C" int b200_oneshot_allreduce(void* const* bufs, const void* in, void* o
   for (int i = 0; i < kArMaxRanks; ++i) p.bufs[i] = i < nranks ? bufs[i] : nullptr;
   p.in = in; p.out = out; p.residual = residual; p.weight = weight; p.epochs = epochs; p.status = status;
   p.parity_bytes = parity_bytes; p.flags_offset = flags_offset; p.rank = rank; p.nranks = nranks; p.rows = rows;
-  p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit; p.ll_slot_bytes = 0;
+  p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit; p.ll_slot_bytes = 0; p.skip_push = 0;
   if (dtype == kBF16) {
     if (H % 8) return 2;
     if (residual) launch_pdl(oneshot_allreduce_kernel<__nv_bfloat16, true>, dim3(grid), dim3(kArThreads), 0, st, p);
@@ -317,7 +334,8 @@ extern "C" int b200_oneshot_allreduce(void* const* bufs, const void* in, void* o
 // Low-latency all-reduce (see ll_allreduce_kernel): `bufs` are the ranks' LL buffers of 2 * nranks slots each.
 extern "C" int b200_ll_allreduce(void* const* bufs, const void* in, void* out, void* residual, const void* weight,
                                  uint32_t* epochs, int* status, int64_t slot_bytes, int rank, int nranks, int rows, int H,
-                                 float eps, int gemma, int grid, uint32_t spin_limit, int dtype, cudaStream_t st) {
+                                 float eps, int gemma, int grid, uint32_t spin_limit, int skip_push, int dtype,
+                                 cudaStream_t st) {
   if (rows == 0) return 0;
   if (nranks > kArMaxRanks || grid > kArMaxCtas || grid < 1 || H % 8 || (int64_t)rows * H * 4 > slot_bytes) return 2;
   ArParams p;
@@ -325,6 +343,7 @@ extern "C" int b200_ll_allreduce(void* const* bufs, const void* in, void* out, v
   p.in = in; p.out = out; p.residual = residual; p.weight = weight; p.epochs = epochs; p.status = status;
   p.parity_bytes = 0; p.flags_offset = 0; p.rank = rank; p.nranks = nranks; p.rows = rows;
   p.H = H; p.eps = eps; p.gemma = gemma; p.spin_limit = spin_limit; p.ll_slot_bytes = slot_bytes;
+  p.skip_push = skip_push;
   if (dtype == kBF16) {
     if (residual) launch_pdl(ll_allreduce_kernel<__nv_bfloat16, true>, dim3(grid), dim3(kArThreads), 0, st, p);
     else launch_pdl(ll_allreduce_kernel<__nv_bfloat16, false>, dim3(grid), dim3(kArThreads), 0, st, p);

@@ -1,0 +1,417 @@
+// Decode-sized bf16/fp16 GEMM for sm_100a:  out[T <= 32, N] = x[T, K] . W[N, K]^T (+ bias), one token tile.
+//
+// A decode step is a chain of small dependent kernels, so what counts is how short the dependent
+// latency chain inside each kernel is and how many SMs pull weight bytes at the same time.  This
+// kernel therefore
+//   * gives every 128-row weight tile to a thread-block CLUSTER of S CTAs (1 <= S <= 8) that split the
+//     K range; the partial accumulators meet in the leader CTA's shared memory (st.shared::cluster +
+//     a remote mbarrier arrive), not in a global workspace with a fence, an atomic ticket and a re-read;
+//     the leader sums the partials in rank order, so the result is deterministic;
+//   * runs one tile per CTA (no persistent loop): with two CTAs resident per SM all CTAs of a
+//     weight matrix stream concurrently and share HBM bandwidth evenly, whatever the tile count;
+//   * streams its first weight tiles before waiting for the previous kernel (programmatic dependent
+//     launch), like the general kernel in gemm_bf16.cu;
+//   * finishes with one of several epilogues on the leader: plain (+ bias), gated activation over
+//     [64 gate | 64 up] interleaved weight tiles, or the row-parallel form under tensor parallelism:
+//     store the local partial AND push it, as {2 x 16-bit, epoch} 8-byte units, straight into every
+//     peer's low-latency all-reduce slot over NVLink (plain peer stores), so that the kernel after it
+//     only collects, adds the residual and normalises (all-reduce call sites C1 / C2 of the reference,
+//     vllm_kunlun/models/deepseek_v2.py:126-134,399-405).
+// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 TMEM owner + tcgen05.mma issuer, warps 2-5 epilogue.
+// TMA loads carry no cluster multicast.  Every wait is bounded; on time-out the status word is set and the
+// CTA unwinds (drains its copies, meets the cluster barrier, frees TMEM).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "../api.h"
+#include "../common/launch.cuh"
+#include "../common/ptx.cuh"
+#include "gemm_common.cuh"
+
+namespace b200 {
+
+namespace dec {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kStageBytesA = BM * BK * 2;
+constexpr int kTileStride = BM + 8;  // staging row (elements of OutT)
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ float gated(float g, float u, int act) {
+  if (act == 1) return g / (1.f + __expf(-g)) * u;
+  if (act == 2) {
+    const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    return 0.5f * g * (1.f + t) * u;
+  }
+  g = fminf(g, 7.f);
+  u = fminf(fmaxf(u, -7.f), 7.f);
+  return g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+}
+
+// Low-latency all-reduce slots of every rank (peer mappings); see comm/allreduce.cu for the layout.
+struct Comm {
+  void* ll_bufs[8];
+  const uint32_t* epoch_word;
+  int64_t slot_bytes;
+  int on, rank, nranks;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageBytes = kStageBytesA + BN * BK * 2;
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kSlotBytes = BN * BM * 4;                    // one partial tile: [BN / 4][128 features] float4
+  static constexpr int kTileBytes = BN * kTileStride * 2;
+};
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                   OutT* __restrict__ out, const OutT* __restrict__ bias, int* __restrict__ status, int T, int N, int K,
+                   int kb_per_cta, int fmt, int ldo, int num_stages, int S, int act, int l2_prefetch,
+                   const __grid_constant__ Comm cm) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + num_stages * C::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + num_stages;
+  uint64_t* tmem_full = bars + 2 * num_stages;
+  uint64_t* red_bar = tmem_full + 1;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(red_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 2);  // [2]
+  uint8_t* after = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tmem_base_slot + 4) + 15) & ~uintptr_t(15));
+  float4* slots = reinterpret_cast<float4*>(after);                                 // [(S-1)][BN / 4][128]
+  OutT* tile = reinterpret_cast<OutT*>(after + (size_t)(S - 1) * C::kSlotBytes);    // [BN][128 + 8]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
+  const int nt = blockIdx.x / S;
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb0 = (int)crank * kb_per_cta;
+  const int kb1 = min(total_kb, kb0 + kb_per_cta);
+  const int nkb = kb1 - kb0;  // >= 1 by construction on the host
+  Abort ab{status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < num_stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    mbar_init(red_bar, (uint32_t)(S > 1 ? (S - 1) * 4 : 1));
+    mbar_fence_init();
+    prefetch_tmap(&tmW);
+    prefetch_tmap(&tmX);
+    griddep_launch();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (S > 1) {  // the leader's reduction barrier must exist before any peer CTA can arrive on it
+    cluster_arrive();
+    cluster_wait();
+  }
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      const uint64_t pol_w = policy_evict_first();
+      int pre = 0;
+      // weights do not depend on the previous kernel: fill the ring (and pull what follows into L2) first
+      for (; pre < num_stages && pre < nkb; ++pre) {
+        mbar_expect_tx(&full_bar[pre], C::kStageBytes);
+        tma_load_2d_hint(smem + pre * C::kStageBytes, &tmW, &full_bar[pre], (kb0 + pre) * BK, nt * BM, pol_w);
+      }
+      for (int i = 0; i < l2_prefetch && pre + i < nkb; ++i) tma_prefetch_l2_2d(&tmW, (kb0 + pre + i) * BK, nt * BM);
+      griddep_wait();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        uint8_t* sa = smem + stage * C::kStageBytes;
+        uint8_t* sb = sa + kStageBytesA;
+        if (i < pre) {
+          tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BK, 0);
+        } else {
+          if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 121)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d_hint(sa, &tmW, &full_bar[stage], (kb0 + i) * BK, nt * BM, pol_w);
+          tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BK, 0);
+        }
+        ++issued;
+        if (++stage == num_stages) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        int pending = issued < num_stages ? issued : num_stages;
+        for (int i = 0; i < pending; ++i) {
+          int s = (stage - 1 - i + 2 * num_stages) % num_stages;
+          uint32_t ph = (s < stage) ? phase : (phase ^ 1);
+          for (uint32_t p = 0; p < (1u << 16); ++p)
+            if (mbar_try_wait(&full_bar[s], ph)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc(BM, BN, fmt, fmt);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        if (!wait_or_abort(&full_bar[stage], phase, ab, 123)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+        uint32_t sb = sa + kStageBytesA;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          uint64_t da = umma_desc_k_sw128(sa + k * UMMA_K * 2);
+          uint64_t db = umma_desc_k_sw128(sb + k * UMMA_K * 2);
+          umma_f16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[stage]);
+        if (++stage == num_stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(tmem_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    const int ep_tid = (warp - 2) * 32 + lane;
+    const int n_local = quarter * 32 + lane;
+    griddep_wait();
+    if (ep_tid == 0) ep_ok_slot[0] = wait_or_abort(tmem_full, 0, ab, 124) ? 1 : 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool acc_ok = ep_ok_slot[0] != 0;
+    float acc[BN];
+    if (acc_ok) {
+      while (!mbar_try_wait(tmem_full, 0)) {}
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t r[16];
+        tmem_ld_x16(taddr + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[c + j] = __uint_as_float(r[j]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+    }
+    if (S > 1 && crank != 0) {
+      // partial tile -> the leader's slot [crank - 1][token / 4][feature] (16 bytes per lane, lane-contiguous),
+      // then one arrival per warp
+      const uint32_t local = smem_u32(slots + (size_t)(crank - 1) * (BN / 4) * BM + n_local);
+      const uint32_t remote = mapa(local, 0);
+#pragma unroll
+      for (int c = 0; c < BN; c += 4)
+        st_cluster_v4(remote + (c / 4) * BM * 16, acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+      fence_acq_rel_cluster();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(mapa(smem_u32(red_bar), 0));
+    } else {
+      bool ok = acc_ok;
+      if (S > 1) {
+        if (ep_tid == 0) {
+          bool got = false;
+          for (uint32_t i = 0; i < (1u << 22); ++i) {
+            if (mbar_try_wait_cluster(red_bar, 0)) { got = true; break; }
+            if ((i & 255) == 255 && ab.aborted()) break;
+          }
+          if (!got) ab.raise(125);
+          ep_ok_slot[1] = got ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        ok = ok && ep_ok_slot[1] != 0;
+        if (ok) {
+          while (!mbar_try_wait_cluster(red_bar, 0)) {}
+          for (int s = 0; s < S - 1; ++s) {  // rank order: deterministic
+            const float4* src = slots + (size_t)s * (BN / 4) * BM + n_local;
+#pragma unroll
+            for (int c = 0; c < BN; c += 4) {
+              float4 v = src[(c / 4) * BM];
+              acc[c] += v.x; acc[c + 1] += v.y; acc[c + 2] += v.z; acc[c + 3] += v.w;
+            }
+          }
+        }
+      }
+      if (ok) {
+        // ---- final epilogue: stage [token][feature] as OutT, then 16-byte row segments
+        const int n = nt * BM + n_local;
+        const float bv = (bias != nullptr && n < N) ? to_float<OutT>(bias[n]) : 0.f;
+#pragma unroll
+        for (int c = 0; c < BN; ++c) tile[c * kTileStride + n_local] = from_float<OutT>(acc[c] + bv);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (act != 0) {
+          const int n0 = nt * (BM / 2);
+          const int seg = ep_tid & 7;  // 8 segments of 8 output features
+          for (int rr = ep_tid >> 3; rr < BN; rr += 16) {
+            if (rr >= T) break;
+            const OutT* gsrc = tile + rr * kTileStride + seg * 8;
+            const OutT* usrc = gsrc + BM / 2;
+            alignas(16) OutT res[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              res[e] = from_float<OutT>(gated(to_float<OutT>(gsrc[e]), to_float<OutT>(usrc[e]), act));
+            *reinterpret_cast<uint4*>(out + (size_t)rr * ldo + n0 + seg * 8) = *reinterpret_cast<const uint4*>(res);
+          }
+        } else {
+          const int seg = ep_tid & 15;  // 16 segments of 8 features
+          const int nn = nt * BM + seg * 8;
+          const bool vec_ok = ((N & 7) == 0) && ((ldo & 7) == 0);
+          uint32_t epoch = 0;
+          if (cm.on) epoch = *cm.epoch_word + 1u;
+          for (int rr = ep_tid >> 4; rr < BN; rr += 8) {
+            if (rr >= T) break;
+            const OutT* src = tile + rr * kTileStride + seg * 8;
+            OutT* dst = out + (size_t)rr * ldo + nn;
+            if (vec_ok && nn + 8 <= N) {
+              const uint4 v = *reinterpret_cast<const uint4*>(src);
+              *reinterpret_cast<uint4*>(dst) = v;
+              if (cm.on) {
+                // {2 x 16-bit, epoch} units into slot [parity][my rank] of every peer
+                const int parity = epoch & 1;
+                const int64_t off = ((int64_t)parity * cm.nranks + cm.rank) * cm.slot_bytes + (int64_t)rr * N * 4 +
+                                    (int64_t)nn * 4;
+                for (int d = 0; d < cm.nranks; ++d) {
+                  if (d == cm.rank) continue;
+                  uint8_t* p = reinterpret_cast<uint8_t*>(cm.ll_bufs[d]) + off;
+                  st_volatile_v4(p, v.x, epoch, v.y, epoch);
+                  st_volatile_v4(p + 16, v.z, epoch, v.w, epoch);
+                }
+              }
+            } else {
+              for (int e = 0; e < 8; ++e)
+                if (nn + e < N) dst[e] = src[e];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (S > 1) {  // no CTA leaves while a peer may still write into (or read) cluster shared memory
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int BN, typename OutT>
+static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const CUtensorMap& tmX, cudaStream_t st) {
+  using C = Cfg<BN>;
+  auto kern = gemm_decode_kernel<BN, OutT>;
+  const int fixed = 1024 /*align*/ + 512 /*barriers*/ + (a.S - 1) * C::kSlotBytes + C::kTileBytes + 64;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const int total_kb = (a.K + BK - 1) / BK;
+  const int nkb = a.kb_per_cta;
+  // shared memory per CTA: about half an SM when two CTAs should be resident together
+  int budget = (a.ctas_per_sm >= 2 ? 112 * 1024 : 216 * 1024) - fixed;
+  int stages = a.stages > 0 ? a.stages : budget / C::kStageBytes;
+  if (stages > nkb) stages = nkb;
+  if (stages > 12) stages = 12;
+  if (stages < 2) stages = 2;
+  const size_t smem = (size_t)stages * C::kStageBytes + fixed;
+  (void)total_kb;
+  Comm cm;
+  for (int i = 0; i < 8; ++i) cm.ll_bufs[i] = a.ll_bufs[i];
+  cm.epoch_word = (const uint32_t*)a.epoch_word;
+  cm.slot_bytes = a.ll_slot_bytes; cm.on = a.ar_on; cm.rank = a.rank; cm.nranks = a.nranks;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.n_tiles * a.S);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = a.S;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.status, a.T, a.N, a.K,
+                            a.kb_per_cta, a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), cm);
+}
+
+}  // namespace dec
+}  // namespace b200
+
+extern "C" int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmW, const void* tmX, cudaStream_t st) {
+  using namespace b200;
+  const CUtensorMap& w = *reinterpret_cast<const CUtensorMap*>(tmW);
+  const CUtensorMap& x = *reinterpret_cast<const CUtensorMap*>(tmX);
+  if (a->S < 1 || a->S > 8 || a->T > a->bn || a->kb_per_cta < 1) return (int)cudaErrorInvalidValue;
+  if ((a->S - 1) * a->kb_per_cta >= (a->K + 63) / 64 && a->S > 1) return (int)cudaErrorInvalidValue;  // an empty CTA
+  if (a->bn == 32 && a->S > 4) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaErrorInvalidValue;
+  if (a->bn == 16) e = (a->fmt == 1) ? dec::launch<16, __nv_bfloat16>(*a, w, x, st) : dec::launch<16, __half>(*a, w, x, st);
+  else if (a->bn == 32) e = (a->fmt == 1) ? dec::launch<32, __nv_bfloat16>(*a, w, x, st) : dec::launch<32, __half>(*a, w, x, st);
+  return (int)e;
+}

@@ -38,8 +38,49 @@ def allreduce(rank, world):
             eo, er = rb.add_rmsnorm(ref.to(dt).cpu(), res.cpu(), w.cpu(), 1e-5)
             assert (ro.float().cpu() - er.float()).abs().max() < 0.05 * (er.float().abs().max() + 1)
             assert (xo.float().cpu() - eo.float()).abs().max() < 0.05 * (eo.float().abs().max() + 1)
+    # Low-latency path with the row width and the row count changing from call to call and no other
+    # synchronisation between the calls: one call-wide epoch keeps every CTA of every rank on the same parity.
+    shapes = [(16, 4096), (3, 1024), (32, 2048), (1, 4096), (16, 512), (8, 7168), (16, 4096), (2, 128)]
+    xs, refs = [], []
+    for it in range(48):
+        rows, H = shapes[it % len(shapes)]
+        g = torch.Generator(device=dev).manual_seed(7000 + 10 * it + rank)
+        x = torch.randn(rows, H, device=dev, generator=g).to(torch.bfloat16)
+        ref = x.clone().float()
+        dist.all_reduce(ref)
+        xs.append(x); refs.append(ref)
+    torch.cuda.synchronize()
+    dist.barrier()
+    outs = [peer.all_reduce(x) for x in xs]  # 48 back-to-back launches
+    torch.cuda.synchronize()
+    for out, ref in zip(outs, refs):
+        assert (out.float() - ref).abs().max() <= 0.01 * ref.abs().max() + 0.02, "mixed-shape low-latency all-reduce"
+    # Row-parallel decode GEMM that pushes its partials from the epilogue, then collect + residual + norm.
+    from vllm_kunlun_b200.ops.gemm_cuda import gemm_decode_push
+    for it, (rows, N, K) in enumerate([(16, 4096, 512), (16, 4096, 1792), (5, 1024, 2048), (32, 2048, 256)] * 2):
+        g = torch.Generator(device=dev).manual_seed(9000 + 10 * it + rank)
+        x = torch.randn(rows, K, device=dev, generator=g).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        res = torch.randn(rows, N, device=dev, generator=torch.Generator(device=dev).manual_seed(it)).to(torch.bfloat16)
+        nw = torch.randn(N, device=dev, generator=torch.Generator(device=dev).manual_seed(it + 1)).to(torch.bfloat16)
+        part = (x.float() @ w.float().T).to(torch.bfloat16)
+        ref = part.float()
+        dist.all_reduce(ref)
+        assert peer.can_push(rows, N, x.dtype)
+        y = gemm_decode_push(x, w, peer)
+        assert (y.float() - part.float()).abs().max() <= 0.01 * part.float().abs().max() + 0.02, "local partial"
+        r2 = res.clone()
+        xo, ro = peer.all_reduce_add_rmsnorm(y, r2, nw, 1e-5, pushed=True)
+        eo, er = rb.add_rmsnorm(ref.to(torch.bfloat16).cpu(), res.cpu(), nw.cpu(), 1e-5)
+        assert (ro.float().cpu() - er.float()).abs().max() < 0.02 * (er.float().abs().max() + 1), "pushed residual"
+        assert (xo.float().cpu() - eo.float()).abs().max() < 0.03 * (eo.float().abs().max() + 1), "pushed norm"
+        gathered = [torch.empty_like(xo) for _ in range(world)]
+        dist.all_gather(gathered, xo.contiguous())
+        assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree bitwise after the pushed GEMM"
     torch.cuda.synchronize()
     peer.check_status()
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    check_status()
     return {"worst_rel_err": worst}
 
 
@@ -48,11 +89,13 @@ def engine(rank, world, fused):
     from vllm_kunlun_b200.config import llama_3_1_8b, tiny
     cfg = tiny(llama_3_1_8b(), num_layers=2, vocab_size=2048, hidden_size=1024, num_heads=8, num_kv_heads=2,
                head_dim=128, intermediate_size=2048, max_position=4096)
-    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, block_size=64, max_model_len=512, max_num_seqs=4,
+    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, block_size=64, max_model_len=1024, max_num_seqs=4,
               num_gpu_blocks=64, fused_collectives=bool(int(fused)), seed=5)
-    # 192 + 64 = 256 prompt tokens in the first step: a multiple of world * 64, so the fused
+    # the prompt tokens of the first step add up to a multiple of world * 64, so the fused
     # GEMM+reduce-scatter / all-gather+GEMM path serves the prefill
-    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (192, 64)]
+    total = max(256, world * 64)
+    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist()
+               for n in (total - 64, 64)]
     outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     torch.cuda.synchronize()
     peer = llm.engine.pstate.tp_comm.peer

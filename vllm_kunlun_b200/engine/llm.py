@@ -21,6 +21,26 @@ from .runner import ModelRunner, StepHandle
 from .scheduler import BlockPool, Scheduler
 
 
+def _mm_digest(data: dict) -> bytes:
+    """Digest of the pixel data and grid of a request: image placeholder tokens are identical for different images,
+    so the prefix-cache hash must see the images themselves."""
+    import hashlib
+    h = hashlib.blake2b(digest_size=16)
+    for key in sorted(data):
+        v = data[key]
+        h.update(key.encode())
+        if isinstance(v, torch.Tensor):
+            h.update(str(tuple(v.shape)).encode())
+            h.update(v.detach().to("cpu").contiguous().view(torch.uint8).numpy().tobytes())
+        else:
+            h.update(repr(v.tolist() if hasattr(v, "tolist") else v).encode())
+    return h.digest()
+
+
+class InvalidRequest(ValueError):
+    """A request the engine can never serve (the server answers it with HTTP 400)."""
+
+
 class LLMEngine:
     def __init__(self, cfg: EngineConfig):
         self.cfg = cfg.finalize()
@@ -58,14 +78,57 @@ class LLMEngine:
         """``multi_modal_data``: ``{"pixel_values": tensor, "image_grid_thw": [[t, h, w], ...]}`` for
         vision-language models; the vision tower runs here, once per request."""
         rid = request_id or f"req-{next(self._ids)}"
-        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), eos_token_id, lora_id=lora_id)
+        sampling = sampling or SamplingParams()
+        self.validate_request(prompt_token_ids, sampling)
+        req = Request(rid, list(prompt_token_ids), sampling, eos_token_id, lora_id=lora_id)
+        salt = b"" if lora_id < 0 else f"lora{lora_id}".encode()
         if multi_modal_data is not None:
             req.mm = self.runner.encode_multimodal(req.prompt_token_ids, multi_modal_data)
+            if self.cfg.cache.enable_prefix_caching:
+                salt += b"|mm" + _mm_digest(multi_modal_data)
+        req.cache_salt = salt
         self.scheduler.add(req)
         return req
 
+    def validate_request(self, prompt_token_ids: Sequence[int], sampling: SamplingParams) -> None:
+        """Raise :class:`InvalidRequest` for a request that could never be scheduled or sampled: an empty prompt, a
+        prompt that leaves no room for one generated token, a prompt larger than the whole block pool, token ids
+        outside the vocabulary, sampling parameters outside their domains (upstream answers these with HTTP 400)."""
+        n = len(prompt_token_ids)
+        mml = self.cfg.scheduler.max_model_len
+        if n == 0:
+            raise InvalidRequest("the prompt is empty")
+        if n >= mml:
+            raise InvalidRequest(f"the prompt has {n} tokens; with max_model_len={mml} there is no room to generate")
+        need = -(-(n + 1) // self.pool.block_size)
+        if need > self.pool.num_blocks:
+            raise InvalidRequest(f"the prompt needs {need} KV blocks but the pool has {self.pool.num_blocks}")
+        V = self.cfg.model.vocab_size
+        lo, hi = min(prompt_token_ids), max(prompt_token_ids)
+        if lo < 0 or hi >= V:
+            raise InvalidRequest(f"token id {lo if lo < 0 else hi} is outside the vocabulary [0, {V})")
+        sp = sampling
+        if sp.max_tokens < 1:
+            raise InvalidRequest("max_tokens must be at least 1")
+        if sp.temperature < 0 or sp.temperature != sp.temperature:
+            raise InvalidRequest("temperature must be non-negative")
+        if not (0.0 < sp.top_p <= 1.0):
+            raise InvalidRequest("top_p must be in (0, 1]")
+        if sp.top_k < 0:
+            raise InvalidRequest("top_k must be non-negative (0 disables it)")
+        if not sp.repetition_penalty > 0:
+            raise InvalidRequest("repetition_penalty must be positive")
+
     def abort(self, request_id: str) -> bool:
         return self.scheduler.abort(request_id)
+
+    def abort_all(self) -> list:
+        """Drop every request (after a failed step): frees their blocks; returns the dropped requests."""
+        self._inflight = None
+        dropped = list(self.scheduler.running) + list(self.scheduler.waiting)
+        for r in dropped:
+            self.scheduler.abort(r.request_id)
+        return dropped
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work() or self._inflight is not None
@@ -74,19 +137,21 @@ class LLMEngine:
     def _process(self, h: StepHandle) -> list:
         """Append sampled tokens, run stop checks, free finished requests."""
         toks = h.wait().tolist()
+        lps = None if h.logprobs_cpu is None else h.logprobs_cpu.tolist()
         now = time.perf_counter()
         finished = []
         row = 0
         for req, rows in zip(h.sample_reqs, h.rows_per_req):
             vals = toks[row:row + rows]
+            lp = None if lps is None or not req.sampling.logprobs else lps[row:row + rows]
             row += rows
             req.num_pending = max(0, req.num_pending - 1)
             if req.status.finished:
                 continue  # finished while this step was in flight: drop the extra token
             if self.spec is not None and rows > 1:
                 vals = self.spec.accept(req, vals, self.stats)
-            for v in vals:
-                req.append_token(v, now)
+            for j, v in enumerate(vals):
+                req.append_token(v, now, None if lp is None or j >= len(lp) else lp[j])
                 if req.check_stop():
                     self.scheduler.finish(req)
                     finished.append(req)
@@ -95,6 +160,12 @@ class LLMEngine:
 
     def step(self) -> list:
         """Run one engine iteration; returns requests that finished."""
+        if self._inflight is not None and self._needs_host_tokens():
+            # repetition penalties and per-request seeds read the full token history on the host: finish the step in
+            # flight before the next one is prepared
+            done = self._process(self._inflight)
+            self._inflight = None
+            return done + self.step() if self.scheduler.has_work() else done
         sched = self.scheduler.schedule()
         self.stats["preemptions"] += len(sched.preempted)
         finished = []
@@ -127,6 +198,10 @@ class LLMEngine:
         return finished
 
     _finished_since: list = []
+
+    def _needs_host_tokens(self) -> bool:
+        return any(r.sampling.repetition_penalty != 1.0 or (r.sampling.seed is not None and not r.sampling.greedy)
+                   for r in self.scheduler.running)
 
     def _drain(self):
         self._finished_since = []

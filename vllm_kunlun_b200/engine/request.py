@@ -62,6 +62,8 @@ class Request:
     token_times: list = field(default_factory=list)
     num_pending: int = 0  # tokens launched on the device whose values the host has not seen yet
     num_preemptions: int = 0
+    output_logprobs: list = field(default_factory=list)  # log-probability of every sampled token (sampling.logprobs)
+    cache_salt: bytes = b""  # prefix-cache hash seed: LoRA adapter id + digest of the multimodal inputs
 
     @property
     def num_prompt_tokens(self) -> int:
@@ -79,12 +81,14 @@ class Request:
     def in_prefill(self) -> bool:
         return self.num_computed_tokens < self.num_prompt_tokens
 
-    def append_token(self, tok: int, now: Optional[float] = None) -> None:
+    def append_token(self, tok: int, now: Optional[float] = None, logprob: Optional[float] = None) -> None:
         now = time.perf_counter() if now is None else now
         if self.first_token_time is None:
             self.first_token_time = now
         self.token_times.append(now)
         self.output_token_ids.append(int(tok))
+        if logprob is not None:
+            self.output_logprobs.append(float(logprob))
 
     def check_stop(self) -> bool:
         sp = self.sampling
@@ -112,6 +116,7 @@ class RequestOutput:
     ttft: Optional[float] = None  # seconds
     tpot: Optional[float] = None  # mean seconds per output token after the first
     text: Optional[str] = None
+    logprobs: Optional[list] = None  # per output token, when SamplingParams.logprobs was set
 
     @classmethod
     def from_request(cls, r: Request) -> "RequestOutput":
@@ -121,4 +126,5 @@ class RequestOutput:
             tpot = (r.token_times[-1] - r.token_times[0]) / (len(r.token_times) - 1)
         reason = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
                   RequestStatus.FINISHED_ABORTED: "abort"}.get(r.status)
-        return cls(r.request_id, r.prompt_token_ids, list(r.output_token_ids), r.status.finished, reason, ttft, tpot)
+        return cls(r.request_id, r.prompt_token_ids, list(r.output_token_ids), r.status.finished, reason, ttft, tpot,
+                   logprobs=list(r.output_logprobs) if r.sampling.logprobs else None)

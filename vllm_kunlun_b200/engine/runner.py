@@ -39,11 +39,24 @@ class StepHandle:
     md: Optional[object] = None            # kept for the draft model (speculative decoding)
     input_ids: Optional[torch.Tensor] = None
     full_hidden: Optional[torch.Tensor] = None
+    logprobs_cpu: Optional[torch.Tensor] = None  # log p of every sampled row (when a request asked for it)
+    status_cpu: Optional[torch.Tensor] = None    # device status words copied with the tokens (0 = all waits were met)
+    status_names: tuple = ()
 
     def wait(self) -> torch.Tensor:
         if self.event is not None:
             self.event.synchronize()
+        if self.status_cpu is not None:
+            codes = self.status_cpu.tolist()
+            if any(codes):
+                bad = ", ".join(f"{n}={c}" for n, c in zip(self.status_names, codes) if c)
+                raise DeviceWaitTimeout(f"a bounded device-side wait timed out during this step ({bad}); "
+                                        "the tokens of the step are not trustworthy")
         return self.tokens_cpu
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A kernel gave up on a bounded wait (peer flag, mbarrier) and finished with wrong data."""
 
 
 class ModelRunner:
@@ -67,8 +80,9 @@ class ModelRunner:
         self.tokens_per_block = self.block_size * self.dcp
         self.max_bs = cfg.scheduler.max_num_seqs
         self.max_tokens = cfg.scheduler.max_num_batched_tokens
-        self.max_blocks_per_seq = cdiv(cfg.scheduler.max_model_len, self.tokens_per_block)
         self.num_spec = cfg.speculative.num_speculative_tokens
+        # a verify step may run num_spec draft positions past the last allowed token
+        self.max_blocks_per_seq = cdiv(cfg.scheduler.max_model_len + self.num_spec, self.tokens_per_block)
         self.sampler = Sampler(m.vocab_size, self.device, seed=cfg.seed)
         self.num_blocks = self._plan_num_blocks()
         self.kv_caches = self._alloc_kv()
@@ -174,6 +188,10 @@ class ModelRunner:
         self.d32 = torch.zeros(self.n32, dtype=torch.int32, device=self.device)
         self._tok_hosts = [torch.zeros(max(T, B * (1 + self.num_spec)), dtype=torch.int64, pin_memory=pin)
                            for _ in range(2)]
+        self._lp_hosts = [torch.zeros(max(T, B * (1 + self.num_spec)), dtype=torch.float32, pin_memory=pin)
+                          for _ in range(2)]
+        self._status_hosts = [torch.zeros(8, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._status_cache = None
         self.step_idx = 0
         self._bind_staging()
         self.h2d_bytes = 0
@@ -405,7 +423,7 @@ class ModelRunner:
                      and self.graphs.supports(len(srs), sched.num_tokens))
         pad = self.graphs.padded_batch(len(srs)) if use_graph else 0
         md, input_ids, (sample_reqs, rows_per_req, n_logits) = self.prepare(sched, pad)
-        sp = self.sampler.make_params([r.sampling for r in sample_reqs], rows_per_req, n_logits)
+        sp = self.sampler.make_params([r.sampling for r in sample_reqs], rows_per_req, n_logits, reqs=sample_reqs)
         from ..models.layers import set_sp_mode
         if use_graph:
             set_sp_mode(False)
@@ -428,18 +446,58 @@ class ModelRunner:
             sr.req.num_computed_tokens += sr.num_new_tokens
         self.last_tokens = tokens
         ev = None
+        lp_cpu = status_cpu = None
+        names = ()
+        lp = self.sampler.last_logprobs
         if self.is_cuda:
             tokens_cpu = self.tokens_host[:n_real]
             tokens_cpu.copy_(tokens, non_blocking=True)
             self.d2h_bytes += n_real * 8
+            if lp is not None:
+                lp_cpu = self._lp_hosts[self.step_idx & 1][:n_real]
+                lp_cpu.copy_(lp[:n_real], non_blocking=True)
+                self.d2h_bytes += n_real * 4
+            words = self._status_words()
+            if words:
+                # the status words of every kernel family that waits on a peer or a barrier ride along with the
+                # tokens, so a timed-out wait surfaces as an error of THIS step instead of as silently wrong tokens
+                names = tuple(n for n, _ in words)
+                status_cpu = self._status_hosts[self.step_idx & 1][:len(words)]
+                for i, (_, w) in enumerate(words):
+                    status_cpu[i:i + 1].copy_(w.view(-1)[:1], non_blocking=True)
+                self.d2h_bytes += 4 * len(words)
             ev = torch.cuda.Event()
             ev.record()
         else:
             tokens_cpu = tokens
+            lp_cpu = None if lp is None else lp[:n_real]
         full = None
         if self.keep_full_hidden:
             full = hidden if use_graph else self._full_hidden
-        return StepHandle(sched, sample_reqs, rows_per_req, tokens, tokens_cpu, ev, hidden, t0, md, input_ids, full)
+        return StepHandle(sched, sample_reqs, rows_per_req, tokens, tokens_cpu, ev, hidden, t0, md, input_ids, full,
+                          lp_cpu, status_cpu, names)
+
+    def _status_words(self) -> list:
+        """``(name, int32 device tensor)`` of every status word a kernel of this process may have set."""
+        st = self.pstate
+        a2a = getattr(st, "ep_a2a", None)
+        if getattr(self, "_status_cache", None) is None or self._status_has_a2a != (a2a is not None):
+            self._status_has_a2a = a2a is not None
+            words = []
+            for name, comm in (("tp", st.tp_comm), ("ep", getattr(st, "ep_comm", None)),
+                               ("dcp", getattr(st, "dcp_comm", None))):
+                peer = getattr(comm, "peer", None) if comm is not None else None
+                if peer is not None and all(peer.status is not w for _, w in words):
+                    words.append((f"{name}_peer", peer.status))
+            if a2a is not None:  # expert dispatch / combine (created on first use)
+                words.append(("ep_a2a", a2a.h.status_tensor()))
+            from ..ops import _ext
+            if _ext.available():
+                gs = _ext.C().gemm_status_tensor()
+                if gs is not None:
+                    words.append(("gemm", gs))
+            self._status_cache = words
+        return self._status_cache
 
     def forward_and_sample(self, md: AttentionMetadata, input_ids, sp, capturing: bool = False):
         ctx = ForwardContext(attn=md, kv_caches=self.kv_caches, pstate=self.pstate, capturing=capturing,

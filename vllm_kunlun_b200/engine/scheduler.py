@@ -65,11 +65,13 @@ class BlockPool:
     def chain_hash(prev: bytes, tokens) -> bytes:
         return hashlib.blake2b(prev + b"|" + ",".join(map(str, tokens)).encode(), digest_size=16).digest()
 
-    def match_prefix(self, token_ids) -> list:
-        """Longest run of full cached blocks for this prompt (never the whole prompt)."""
+    def match_prefix(self, token_ids, salt: bytes = b"") -> list:
+        """Longest run of full cached blocks for this prompt (never the whole prompt).  ``salt`` seeds the hash
+        chain with everything besides token ids that decides the KV contents: the LoRA adapter and a digest of the
+        multimodal inputs (upstream mixes the lora id and the mm hashes into its block hash the same way)."""
         if not self.enable_prefix_caching:
             return []
-        out, h = [], b""
+        out, h = [], salt
         bs = self.block_size
         for i in range((len(token_ids) - 1) // bs):
             h = self.chain_hash(h, token_ids[i * bs:(i + 1) * bs])
@@ -88,7 +90,7 @@ class BlockPool:
             return
         bs = self.block_size
         toks = req.all_token_ids
-        h = b""
+        h = req.cache_salt
         for i in range(min(req.num_computed_tokens // bs, len(req.block_ids))):
             h = self.chain_hash(h, toks[i * bs:(i + 1) * bs])
             b = req.block_ids[i]
@@ -177,6 +179,10 @@ class Scheduler:
                     continue
                 is_decode = False
             else:
+                # drafts must not run past the last position the model may see
+                room = self.max_model_len - req.num_computed_tokens - 1
+                if len(req.spec_token_ids) > max(0, room):
+                    req.spec_token_ids = req.spec_token_ids[:max(0, room)]
                 n = 1 + len(req.spec_token_ids)
                 if n > budget:
                     i += 1
@@ -201,7 +207,7 @@ class Scheduler:
             if self.uses_state and not self.free_state_slots:
                 break
             if req.num_computed_tokens == 0 and not req.block_ids:
-                cached = self.pool.match_prefix(req.all_token_ids)
+                cached = self.pool.match_prefix(req.all_token_ids, req.cache_salt)
                 if cached:
                     req.block_ids = list(cached)
                     req.num_computed_tokens = len(cached) * self.pool.block_size

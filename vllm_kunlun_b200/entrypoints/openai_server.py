@@ -13,6 +13,7 @@ tokens stream back through per-request asyncio queues."""
 import argparse
 import asyncio
 import json
+import logging
 import queue
 import threading
 import time
@@ -85,6 +86,14 @@ def stop_list(body) -> tuple:
     return () if not st else ((st,) if isinstance(st, str) else tuple(st))
 
 
+log = logging.getLogger("vllm_kunlun_b200.server")
+try:
+    from ..engine.runner import DeviceWaitTimeout
+    DEVICE_ERRORS: tuple = (DeviceWaitTimeout,)
+except Exception:  # pragma: no cover
+    DEVICE_ERRORS = ()
+
+
 class EngineLoop:
     """Owns the engine on a worker thread.
 
@@ -99,7 +108,8 @@ class EngineLoop:
         self.llm = llm
         self.inbox: "queue.Queue" = queue.Queue()
         self.streams: dict = {}
-        self.stats = {"requests": 0, "tokens": 0, "aborted": 0}
+        self.stats = {"requests": 0, "tokens": 0, "aborted": 0, "failed": 0}
+        self.healthy = True  # cleared when a step failed with a device error (wrong data may be in the caches)
         self._stop = False
         self.aborts: "queue.Queue" = queue.Queue()
         self.multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
@@ -141,9 +151,16 @@ class EngineLoop:
             for rid in aborts:
                 eng.abort(rid)
             for rid, ids, sp, lora_id in new:
-                eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                try:
+                    eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                except Exception:  # rank 0 validated the request; a failure here is reported there as well
+                    log.exception("follower: add_request failed for %s", rid)
             if eng.has_unfinished():
-                eng.step()
+                try:
+                    eng.step()
+                except Exception:  # rank 0 hits the same failure in its own step and fails the streams
+                    log.exception("follower: engine step failed; dropping all requests")
+                    eng.abort_all()
 
     def _run(self):
         eng = self.llm.engine
@@ -164,12 +181,30 @@ class EngineLoop:
             for rid in aborts:
                 self.stats["aborted"] += int(eng.abort(rid))
             for rid, ids, sp, loop, out_q, lora_id in new:
-                req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                try:
+                    req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                except Exception as e:  # an unservable request fails alone; the loop and the other streams go on
+                    loop.call_soon_threadsafe(out_q.put_nowait, ("error", f"{type(e).__name__}: {e}"))
+                    self.stats["failed"] = self.stats.get("failed", 0) + 1
+                    continue
                 self.streams[rid] = (req, loop, out_q)
                 sent[rid] = 0
                 self.stats["requests"] += 1
             if eng.has_unfinished():
-                eng.step()
+                try:
+                    eng.step()
+                except Exception as e:
+                    # A failed step (device-side wait time-out, an internal error) must not kill this thread: /health
+                    # would keep answering while every request hangs.  Fail the requests that were in the engine, free
+                    # their blocks and keep serving.
+                    log.exception("engine step failed; failing %d active request(s)", len(self.streams))
+                    self.healthy = not isinstance(e, DEVICE_ERRORS)
+                    eng.abort_all()
+                    for rid, (req, loop, out_q) in list(self.streams.items()):
+                        loop.call_soon_threadsafe(out_q.put_nowait, ("error", f"engine step failed: {type(e).__name__}: {e}"))
+                        del self.streams[rid], sent[rid]
+                    self.stats["failed"] = self.stats.get("failed", 0) + 1
+                    continue
             elif not aborts:
                 continue
             for rid, (req, loop, out_q) in list(self.streams.items()):
@@ -207,16 +242,28 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
     def decode(ids):
         return " ".join(map(str, ids)) if tok is None else tok.decode(ids)
 
-    def sampling(body) -> SamplingParams:
-        return SamplingParams(max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
-                              temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
-                              top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
-                              ignore_eos=bool(body.get("ignore_eos", False)),
-                              stop_token_ids=tuple(int(t) for t in (body.get("stop_token_ids") or ())),
-                              repetition_penalty=float(body.get("repetition_penalty", 1.0)))
+    def sampling(body):
+        """Request body -> SamplingParams, or an error string (answered with HTTP 400)."""
+        try:
+            mt = body.get("max_tokens") if body.get("max_tokens") is not None else body.get("max_completion_tokens")
+            seed = body.get("seed")
+            lp = body.get("logprobs")
+            return SamplingParams(max_tokens=16 if mt is None else int(mt),
+                                  temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
+                                  top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
+                                  ignore_eos=bool(body.get("ignore_eos", False)),
+                                  stop_token_ids=tuple(int(t) for t in (body.get("stop_token_ids") or ())),
+                                  repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+                                  seed=None if seed is None else int(seed), logprobs=bool(lp))
+        except (TypeError, ValueError) as e:
+            return f"invalid sampling parameter: {e}"
 
     @app.get("/health")
     async def health():
+        alive = loop_obj.thread is None or loop_obj.thread.is_alive()
+        if not alive or not loop_obj.healthy:
+            return PlainTextResponse("engine loop stopped" if not alive else "device error in an earlier step",
+                                     status_code=503)
         return PlainTextResponse("ok")
 
     @app.get("/v1/models")
@@ -235,11 +282,21 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                  f"b200_spec_accepted_total {e['spec_accepted']}", f"b200_spec_proposed_total {e['spec_proposed']}"]
         return PlainTextResponse("\n".join(lines) + "\n")
 
+    def bad_request(msg: str, code: int = 400):
+        kind = "BadRequestError" if code == 400 else "InternalServerError"
+        return JSONResponse({"error": {"message": msg, "type": kind, "code": code}}, status_code=code)
+
     async def run(prompt_ids, sp, stream, make_chunk, make_final, requested_model=None, stops=()):
+        if isinstance(sp, str):  # the sampling parameters did not parse
+            return bad_request(sp)
         # the name selects an adapter; with no adapters loaded every name is served by the base model
         if lora_modules and requested_model not in (None, "", model_name) and requested_model not in lora_modules:
             return JSONResponse({"error": {"message": f"The model `{requested_model}` does not exist.",
                                            "type": "NotFoundError", "code": 404}}, status_code=404)
+        try:
+            llm.engine.validate_request(prompt_ids, sp)
+        except ValueError as e:
+            return bad_request(str(e))
         loop = asyncio.get_running_loop()
         out_q: asyncio.Queue = asyncio.Queue()
         rid = loop_obj.submit(prompt_ids, sp, loop, out_q, lora_modules.get(requested_model, -1))
@@ -261,6 +318,10 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                                 yield f"data: {json.dumps(make_chunk(rid, created, '', 'stop'))}\n\n"
                                 yield "data: [DONE]\n\n"
                                 return
+                        elif kind == "error":
+                            yield f"data: {json.dumps({'error': {'message': val, 'type': 'InternalServerError', 'code': 500}})}\n\n"
+                            yield "data: [DONE]\n\n"
+                            return
                         else:
                             rest = cut.flush()
                             if rest:
@@ -283,6 +344,8 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                     if hit:
                         loop_obj.abort(rid)
                         reason = "stop"
+            elif kind == "error":
+                return bad_request(val, 500)
             else:
                 reason = val
                 text += cut.flush()

@@ -86,6 +86,8 @@ class LoRAManager:
             if isinstance(mod, (ColumnParallelLinear, RowParallelLinear)) and getattr(mod, "weight", None) is not None \
                     and mod.weight.dim() == 2 and name.split(".")[-1] != "in_proj_ba":
                 st = _LoRAState(mod, max_loras, max_rank, dtype, device)
+                if isinstance(mod, RowParallelLinear):
+                    mod.push_ok = False  # the adapter's delta is added after the GEMM, before the reduction
                 self.states[name] = st
                 self._wrap(mod, st)
 

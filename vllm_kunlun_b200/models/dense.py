@@ -141,6 +141,10 @@ class DenseDecoderLayer(nn.Module):
         self.self_attn = GQAAttention(cfg, layer_idx, dtype, device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.gemma_norm)
         self.mlp = self.build_mlp(cfg, layer_idx, dtype, device)
+        # both row-parallel outputs of a plain dense layer feed reduce_add_rmsnorm directly
+        self.self_attn.o_proj.push_ok = True
+        if type(self.mlp) is GatedMLP:
+            self.mlp.down_proj.push_ok = True
 
     def build_mlp(self, cfg, layer_idx, dtype, device):
         return GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization,

@@ -151,6 +151,9 @@ class RowParallelLinear(LinearBase):
         super().__init__(in_features, out_features, bias, dtype, device, quant, quant_kw)
         self.in_local = in_features // self.tp_size
         self.reduce_results = reduce_results
+        # set by the owner when the output goes straight into reduce_add_rmsnorm: decode-sized calls then push
+        # their partial sums to the peers from the GEMM epilogue
+        self.push_ok = False
         self.method.create_weights(self, out_features, self.in_local, dtype, device)
         if bias:
             self.bias = param(out_features, dtype=dtype, device=device)
@@ -162,6 +165,12 @@ class RowParallelLinear(LinearBase):
             if peer is not None and sp_mode_active() and peer.sp_ok(x.shape[0], self.out_features, x.dtype):
                 # GEMM -> reduce-scatter fused over peer memory; finished by reduce_add_rmsnorm
                 return SPPartial(peer, peer.gemm_rs(x.reshape(-1, x.shape[-1]), self.weight))
+            if (peer is not None and self.push_ok and PUSH_EPILOGUE[0] and x.dim() == 2 and not get_state().tp_comm.disabled
+                    and peer.can_push(x.shape[0], self.out_features, x.dtype)):
+                from ..ops.gemm_cuda import gemm_decode_push
+                y = gemm_decode_push(x, self.weight, peer)
+                y._b200_pushed = peer  # the consumer (reduce_add_rmsnorm) only collects
+                return y
         bias = self.bias
         if self.tp_rank != 0:
             self.bias = None  # add the bias once
@@ -245,6 +254,8 @@ class SPPartial:
 
 
 _SP_MODE = False
+import os as _os
+PUSH_EPILOGUE = [_os.environ.get("B200_GEMM_PUSH", "1") != "0"]
 
 
 def sp_mode_active() -> bool:
@@ -279,7 +290,8 @@ def reduce_add_rmsnorm(x, residual, norm: "RMSNorm", partial: bool):
         comm = st.tp_comm
         if (residual is not None and comm.peer is not None and not comm.disabled
                 and comm.peer.can_one_shot(x)):
-            return comm.peer.all_reduce_add_rmsnorm(x, residual, norm.weight, norm.eps, norm.gemma)
+            pushed = getattr(x, "_b200_pushed", None) is comm.peer
+            return comm.peer.all_reduce_add_rmsnorm(x, residual, norm.weight, norm.eps, norm.gemma, pushed=pushed)
         x = comm.all_reduce(x)
     if residual is None:
         return norm(x), x

@@ -5,11 +5,16 @@ The reference runs dense linears through ``F.linear`` on the vendor BLAS
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _ext
 
 LAUNCHES = 0
+# Calls of at most 32 rows go to the cluster split-K kernel (csrc/gemm/gemm_decode.cu); B200_DECODE_GEMM=0 keeps
+# them on the general kernel.
+DECODE_GEMM = [os.environ.get("B200_DECODE_GEMM", "1") != "0"]
 PEER = None  # PeerBuffers of the tensor-parallel group once its sequence-parallel buffers exist
 
 
@@ -46,9 +51,32 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias=None, out=None, splits
         ag_bn = PEER.sp_consume(x2)
         if ag_bn:  # gathered activations: the producer waits per token tile, tiles must match the counters
             bn, splits = ag_bn, 1
-    _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm, ACT_CODES[act])
+            _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm, ACT_CODES[act])
+            LAUNCHES += 1
+            return out.reshape(*lead, N)
+    if DECODE_GEMM[0] and x2.shape[0] <= 32 and bn == 0:
+        _ext.C().gemm_decode(out2, x2, weight, bias, splits, stages, ctas_per_sm, ACT_CODES[act])
+    else:
+        _ext.C().gemm(out2, x2, weight, bias, splits, bn, stages, ctas_per_sm, ACT_CODES[act])
     LAUNCHES += 1
     return out.reshape(*lead, N)
+
+
+def gemm_decode_push(x: torch.Tensor, weight: torch.Tensor, peer, bias=None, out=None):
+    """Row-parallel decode GEMM whose epilogue also pushes the partial result into every peer's low-latency
+    all-reduce slot; finish with ``peer.collect_add_rmsnorm`` / ``peer.collect`` on the returned tensor."""
+    global LAUNCHES
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    N = weight.shape[0]
+    if out is None:
+        out = torch.empty(x2.shape[0], N, dtype=x.dtype, device=x.device)
+    C = _ext.C()
+    C.set_gemm_decode_comm(peer.ll_ptrs, peer.ll_epochs, peer.ll_slot_bytes, peer.rank)
+    C.gemm_decode(out, x2, weight, bias, 0, 0, 0, 0)
+    LAUNCHES += 1
+    return out
 
 
 def check_status() -> None:

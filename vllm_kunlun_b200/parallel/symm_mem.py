@@ -86,7 +86,7 @@ class PeerBuffers:
         out = torch.empty_like(x2) if out is None else out.reshape(-1, x.shape[-1])
         if self._can_ll(x2):
             self.C.ll_allreduce(self.ll_ptrs, x2, out, None, None, self.ll_epochs, self.status, self.ll_slot_bytes,
-                                self.rank, 0.0, False, self._grid(x2.shape[0]), self.spin_limit)
+                                self.rank, 0.0, False, self._grid(x2.shape[0]), self.spin_limit, False)
             self.launches += 1
             return out.reshape(x.shape)
         self.C.oneshot_allreduce(self.ptrs, x2, out, None, None, self.epochs, self.status, self.parity_bytes,
@@ -94,16 +94,23 @@ class PeerBuffers:
         self.launches += 1
         return out.reshape(x.shape)
 
+    def can_push(self, rows: int, width: int, dtype) -> bool:
+        """Whether a row-parallel decode GEMM of this output shape may push its partials from the epilogue."""
+        return (self.ll_ptrs is not None and rows <= 32 and width % 128 == 0 and dtype in (torch.bfloat16, torch.float16)
+                and rows * width * 2 <= self.ll_max_bytes)
+
     def all_reduce_add_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
-                               gemma: bool = False):
-        """``residual += all_reduce(x); x = rmsnorm(residual) * w`` in one kernel; returns ``(x, residual)``."""
+                               gemma: bool = False, pushed: bool = False):
+        """``residual += all_reduce(x); x = rmsnorm(residual) * w`` in one kernel; returns ``(x, residual)``.
+        ``pushed``: the GEMM that produced ``x`` has already written it into the peers' slots."""
         x2 = x.reshape(-1, x.shape[-1])
         if self._can_ll(x2):
             self.C.ll_allreduce(self.ll_ptrs, x2, x2, residual.reshape(-1, x.shape[-1]), weight, self.ll_epochs,
                                 self.status, self.ll_slot_bytes, self.rank, eps, gemma, self._grid(x2.shape[0]),
-                                self.spin_limit)
+                                self.spin_limit, pushed)
             self.launches += 1
             return x, residual
+        assert not pushed
         self.C.oneshot_allreduce(self.ptrs, x2, x2, residual.reshape(-1, x.shape[-1]), weight, self.epochs,
                                  self.status, self.parity_bytes, self.flags_offset, self.rank, eps, gemma,
                                  self._grid(x2.shape[0]), self.spin_limit)
