@@ -127,6 +127,15 @@ int b200_paged_attention(void* out, const void* q, const void* kv_cache, const i
                          int Hkv, int D, int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
                          int num_splits, int window, float scale, int decode_layout, int dtype, cudaStream_t st);
 
+// Decode-shaped paged GQA attention on tcgen05 with TMA-fed KV tiles (attention/decode_umma.cu): head dim 128,
+// at most 16 packed query rows per KV head, cache blocks of a multiple of 64 tokens.  `tmap`: the cache as a 2-D
+// [blocks * 2 * Hkv * block_size, 128] tensor, 64 x 64 boxes, 128-byte swizzle.  Returns 3 for shapes it does not serve.
+int b200_decode_attention_umma(void* out, const void* q, const void* tmap, const int* block_tables,
+                               const int* seq_lens, const int* qsl, const float* sinks, float* ws_o, float* ws_lse,
+                               int* status, int64_t T, int B, int Hq, int Hkv, int D, int block_size, int max_blocks,
+                               int64_t num_blocks, int max_query_len, int num_splits, int window, float scale,
+                               int dtype, cudaStream_t st);
+
 int b200_merge_splits(void* out, const float* ws_o, const float* ws_lse, int64_t rows, int Hq, int D, int splits,
                       int64_t T, int dtype, cudaStream_t st);
 // Absorbed MLA attention over the latent cache: dense paged (indices == null) or sparse by index list.

@@ -1,0 +1,479 @@
+// Paged GQA decode attention on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA straight from the
+// paged KV cache.
+//
+// Orientation ("swap A/B"): a decode step has only a handful of query rows per KV head (group size x query
+// tokens <= 16) but thousands of keys, so the KEYS are the UMMA M side and the query rows the N side:
+//     S^T[128 keys, 16 rows] = K_tile[128 keys, D] . Q^T            (A = K tile, K-major, as cached)
+//     O^T[D dims,   16 rows] += V_tile^T[D dims, 128 keys] . P      (A = V tile, MN-major, as cached)
+// Both accumulators live in TMEM with one lane per key (S^T) / per output dim (O^T) and 16 fp32 columns, so the
+// tensor-core rows are always full, the online-softmax rescale of O is a 16-column TMEM round trip, and the final
+// store is one coalesced 256-byte row of `out` per query row.
+//
+// One CTA serves one (request, kv head, kv split).  192 threads:
+//   warp 0     TMA producer: per 128-key tile two cache pages x (K, V) x two 64-dim halves as 64x64 boxes
+//              (128-byte swizzle) into a 3-stage ring; pages are looked up in the block table
+//   warp 1     allocates TMEM, issues tcgen05.mma (one thread): S^T of tile i+1 is issued before P.V of tile i
+//   warps 2-5  softmax: thread t owns key t of the tile (TMEM lane t): mask, tile max per row (redux + a
+//              shared-memory exchange between the four warps), exp2, P^T to shared memory (bf16, K-major, swizzled)
+//              for the second MMA; the same threads own output dim t in the epilogue
+// Split-KV partials go through the fp32 workspace and are merged by the last CTA of a (request, head) to arrive.
+// Every wait is bounded: on time-out the status word is set, the CTA drains its copies, frees TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+#include <stdlib.h>
+
+#include "../api.h"
+#include "../common/launch.cuh"
+#include "../common/ptx.cuh"
+#include "../gemm/gemm_common.cuh"
+
+namespace b200 {
+namespace dattn {
+
+constexpr int kThreads = 192;
+constexpr int kTileKeys = 128;   // UMMA M
+constexpr int kRows = 16;        // UMMA N: packed query rows (group x query tokens), zero padded
+constexpr int kPage = 64;        // keys per TMA box = cache block granularity handled by one box
+constexpr int kMaxTickets = 1 << 16;
+static __device__ int g_tickets[kMaxTickets];
+
+struct Params {
+  const void* q;            // [T, Hq, D]
+  void* out;                // [T, Hq, D]
+  float* ws_o;              // [splits, T, Hq, D]
+  float* ws_lse;            // [splits, T, Hq]
+  const int* block_tables;  // [B, max_blocks]
+  const int* seq_lens;
+  const int* qsl;
+  const float* sinks;
+  int* status;
+  int Hq, Hkv, block_size, max_blocks, num_splits, window, num_stages, mn_swap;
+  int64_t num_blocks, T;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// warp-wide float max through the integer reduction unit (order-preserving float <-> int map)
+__device__ __forceinline__ float warp_max_redux(float v) {
+  int i = __float_as_int(v);
+  i = i >= 0 ? i : i ^ 0x7fffffff;
+  i = __reduce_max_sync(0xffffffffu, i);
+  i = i >= 0 ? i : i ^ 0x7fffffff;
+  return __int_as_float(i);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+
+template <typename T> struct FmtOf;
+template <> struct FmtOf<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+template <> struct FmtOf<__half> { static constexpr uint32_t v = 0; };
+template <typename T> __device__ __forceinline__ uint16_t to_bits16(float v);
+template <> __device__ __forceinline__ uint16_t to_bits16<__nv_bfloat16>(float v) {
+  return __bfloat16_as_ushort(__float2bfloat16(v));
+}
+template <> __device__ __forceinline__ uint16_t to_bits16<__half>(float v) { return __half_as_ushort(__float2half(v)); }
+
+// D = head dim (128): K-blocks of 64 dims.  Shared memory per stage: K [D/64][128 keys][128 B] then V the same.
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ Params p) {
+  constexpr int KB = D / 64;                       // 64-dim blocks
+  constexpr int kHalfBytes = kTileKeys * 128;      // one 64-dim block of a 128-key tile
+  constexpr int kOpBytes = KB * kHalfBytes;        // K (or V) of one tile
+  constexpr int kStageBytes = 2 * kOpBytes;
+  constexpr int kQBytes = KB * kRows * 128;        // Q^T operand: [D/64][16 rows][128 B]
+  constexpr int kPBytes = (kTileKeys / 64) * kRows * 128;
+  constexpr int kTmemCols = 64;                    // S^T x 2 buffers (16 cols each) + O^T (D/128 x 16 cols)
+  static_assert(D == 128, "one 128-lane O^T tile");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int num_stages = p.num_stages;
+  uint8_t* sQ = smem + num_stages * kStageBytes;
+  uint8_t* sP = sQ + kQBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+  uint64_t* kv_full = bars;                        // [stages]
+  uint64_t* kv_empty = bars + num_stages;          // [stages]
+  uint64_t* s_full = bars + 2 * num_stages;        // [2]
+  uint64_t* s_empty = s_full + 2;                  // [2]
+  uint64_t* p_ready = s_empty + 2;                 // [1]
+  uint64_t* o_done = p_ready + 1;                  // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
+  int* s_last = reinterpret_cast<int*>(tmem_slot + 4);
+  float* sMax = reinterpret_cast<float*>(tmem_slot + 8);  // [2][4 warps][16 rows]
+  float* sSum = sMax + 2 * 4 * kRows;                     // [4][16]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  Abort ab{p.status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < num_stages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4); }
+    mbar_init(p_ready, 4);
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmKV);
+    griddep_launch();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();
+
+  const int g = p.Hq / p.Hkv;
+  const int kvh = blockIdx.x;
+  const int req = blockIdx.y / p.num_splits;
+  const int split = blockIdx.y % p.num_splits;
+  const int qs = p.qsl[req], q_len = p.qsl[req + 1] - qs;
+  const int seq_len = p.seq_lens[req];
+  const int rows_total = q_len * g;
+  const int ctx = seq_len - q_len;
+  const int kv_end = seq_len;
+  int kv_begin = 0;
+  if (p.window > 0) kv_begin = max(0, ctx - p.window + 1) / kTileKeys * kTileKeys;
+  const int n_tiles_all = (q_len > 0 && rows_total <= kRows) ? (kv_end - kv_begin + kTileKeys - 1) / kTileKeys : 0;
+  const int per_split = (n_tiles_all + p.num_splits - 1) / p.num_splits;
+  const int tile_lo = split * per_split;
+  const int tile_hi = min(n_tiles_all, tile_lo + per_split);
+  const int n_tiles = max(0, tile_hi - tile_lo);
+
+  // ---- Q^T operand (all threads): [D/64][16 rows][128 B], 16-byte chunk c of row r at chunk c ^ (r & 7)
+  for (int c = threadIdx.x; c < kRows * (D / 8); c += kThreads) {
+    const int r = c / (D / 8), ch = c % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows_total && q_len > 0) {
+      const int tok = r / g, hh = r % g;
+      v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
+                                          ((int64_t)(qs + tok) * p.Hq + kvh * g + hh) * D + ch * 8);
+    }
+    const int kb = ch / 8, cc = ch % 8;
+    *reinterpret_cast<uint4*>(sQ + kb * (kRows * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && n_tiles > 0) {
+      const int* bt = p.block_tables + (int64_t)req * p.max_blocks;
+      const int pages_per_block = p.block_size / kPage;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; i < n_tiles; ++i) {
+        if (i >= num_stages && !wait_or_abort(&kv_empty[stage], phase ^ 1, ab, 501)) { ok = false; break; }
+        mbar_expect_tx(&kv_full[stage], kStageBytes);
+        uint8_t* sK = smem + stage * kStageBytes;
+        uint8_t* sV = sK + kOpBytes;
+        const int key0 = kv_begin + (tile_lo + i) * kTileKeys;
+#pragma unroll
+        for (int pg = 0; pg < kTileKeys / kPage; ++pg) {
+          const int key = key0 + pg * kPage;
+          const int bi = key / p.block_size;
+          int64_t blk = (key < kv_end && bi < p.max_blocks) ? bt[bi] : 0;
+          if (blk < 0 || blk >= p.num_blocks) blk = 0;  // masked keys: any initialised page will do
+          const int64_t rowK = ((blk * 2) * p.Hkv + kvh) * p.block_size + (key % p.block_size);
+          const int64_t rowV = rowK + (int64_t)p.Hkv * p.block_size;
+          (void)pages_per_block;
+#pragma unroll
+          for (int h = 0; h < KB; ++h) {
+            tma_load_2d(sK + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowK);
+            tma_load_2d(sV + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowV);
+          }
+        }
+        ++issued;
+        if (++stage == num_stages) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        int pending = issued < num_stages ? issued : num_stages;
+        for (int i = 0; i < pending; ++i) {
+          int s = (stage - 1 - i + 2 * num_stages) % num_stages;
+          uint32_t ph = (s < stage) ? phase : (phase ^ 1);
+          for (uint32_t q2 = 0; q2 < (1u << 16); ++q2)
+            if (mbar_try_wait(&kv_full[s], ph)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && n_tiles > 0) {
+      const uint32_t fmt = FmtOf<T>::v;
+      const uint32_t idesc_s = umma_idesc(kTileKeys, kRows, fmt, fmt, 0, 0);   // A = K (K-major), B = Q^T (K-major)
+      const uint32_t idesc_o = umma_idesc(D, kRows, fmt, fmt, 1, 0);           // A = V (MN-major), B = P (K-major)
+      const uint32_t tS = tmem_base, tO = tmem_base + 2 * kRows;
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = true;
+      auto issue_s = [&](int i) {
+        const int stage = i % num_stages;
+        const uint32_t ph = (i / num_stages) & 1;
+        const int buf = i & 1;
+        if (!wait_or_abort(&kv_full[stage], ph, ab, 502)) return false;
+        if (i >= 2 && !wait_or_abort(&s_empty[buf], ((i >> 1) - 1) & 1, ab, 503)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(smem + stage * kStageBytes);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const int kb = k / 4, kk = k % 4;
+          uint64_t da = umma_desc_k_sw128(k_addr + kb * kHalfBytes + kk * 32);
+          uint64_t db = umma_desc_k_sw128(q_addr + kb * (kRows * 128) + kk * 32);
+          umma_f16(tS + buf * kRows, da, db, idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[buf]);
+        return true;
+      };
+      ok = issue_s(0);
+      for (int i = 0; ok && i < n_tiles; ++i) {
+        if (i + 1 < n_tiles) ok = issue_s(i + 1);
+        if (!ok) break;
+        // P.V of tile i once the softmax warps have written P (and rescaled O^T)
+        if (!wait_or_abort(p_ready, i & 1, ab, 504)) { ok = false; break; }
+        tc_fence_after_sync();
+        const int stage = i % num_stages;
+        const uint32_t v_addr = smem_u32(smem + stage * kStageBytes + kOpBytes);
+#pragma unroll
+        for (int k = 0; k < kTileKeys / 16; ++k) {
+          // A: 16 keys (two 8-row groups of 1024 B) x D dims (64-dim blocks kHalfBytes apart)
+          uint64_t da = p.mn_swap ? umma_desc_mn_sw128(v_addr + k * 2048, 1024, kHalfBytes)
+                                  : umma_desc_mn_sw128(v_addr + k * 2048, kHalfBytes, 1024);
+          uint64_t db = umma_desc_k_sw128(p_addr + (k / 4) * (kRows * 128) + (k % 4) * 32);
+          umma_f16(tO, da, db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[stage]);
+        umma_commit(o_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    const int tid = (warp - 2) * 32 + lane;          // 0..127 (named-barrier group)
+    const int lane_id = quarter * 32 + lane;         // TMEM lane: key of the tile / output dim
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off, tO = tmem_base + 2 * kRows + lane_off;
+    float m_run[kRows], l_part[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) { m_run[r] = -INFINITY; l_part[r] = 0.f; }
+    bool ok = true;
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int buf = i & 1;
+      if (tid == 0) ok_slot[buf] = wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 505) ? 1 : 0;
+      named_bar_sync(1, 128);
+      if (ok_slot[buf] == 0) { ok = false; break; }
+      while (!mbar_try_wait(&s_full[buf], (i >> 1) & 1)) {}
+      tc_fence_after_sync();
+      uint32_t sr[kRows];
+      tmem_ld_x16(tS + buf * kRows, sr);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);
+      // ---- mask + tile max per row
+      const int key = kv_begin + (tile_lo + i) * kTileKeys + lane_id;
+      float sc[kRows];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const int pos = ctx + r / g;  // position of this row's query token
+        const bool in = r < rows_total && key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
+        sc[r] = in ? __uint_as_float(sr[r]) * p.scale_log2 : -INFINITY;
+        const float wm = warp_max_redux(sc[r]);
+        if (lane == r) sMax[(buf * 4 + quarter) * kRows + r] = wm;
+      }
+      named_bar_sync(1, 128);
+      float alpha[kRows];
+      bool any_scale = false;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const float* mm = sMax + buf * 4 * kRows + r;
+        const float tm = fmaxf(fmaxf(mm[0], mm[kRows]), fmaxf(mm[2 * kRows], mm[3 * kRows]));
+        const float mn = fmaxf(m_run[r], tm);
+        const float ms = (mn == -INFINITY) ? 0.f : mn;
+        alpha[r] = (r < rows_total) ? exp2f(m_run[r] - ms) : 1.f;  // 0 when nothing has been accumulated yet
+        any_scale |= (alpha[r] != 1.f);
+        m_run[r] = mn;
+        sc[r] = exp2f(sc[r] - ms);
+        l_part[r] = l_part[r] * alpha[r] + sc[r];
+      }
+      // ---- the previous P.V must have finished before P is overwritten and O^T rescaled
+      if (i > 0) {
+        if (tid == 0) ok_slot[buf] = wait_or_abort(o_done, (i - 1) & 1, ab, 506) ? 1 : 0;
+        named_bar_sync(1, 128);
+        if (ok_slot[buf] == 0) { ok = false; break; }
+        while (!mbar_try_wait(o_done, (i - 1) & 1)) {}
+        tc_fence_after_sync();
+        if (any_scale) {  // uniform over the CTA: alpha is the same in every thread
+          uint32_t orr[kRows];
+          tmem_ld_x16(tO, orr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int r = 0; r < kRows; ++r) orr[r] = __float_as_uint(__uint_as_float(orr[r]) * alpha[r]);
+          tmem_st_x16(tO, orr);
+          tmem_st_wait();
+        }
+      }
+      // ---- P^T (B operand, K-major): element (row r, key k) of 64-key block kb
+      {
+        const int kb = lane_id >> 6, kk = lane_id & 63;
+        uint8_t* base = sP + kb * (kRows * 128) + (kk & 7) * 2;
+        const int ch = kk >> 3;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+          *reinterpret_cast<uint16_t*>(base + r * 128 + ((ch ^ (r & 7)) << 4)) = to_bits16<T>(sc[r]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    // ---- epilogue: O^T lane = output dim, 16 columns = query rows
+    if (ok && n_tiles > 0) {
+      const int last = n_tiles - 1;
+      if (tid == 0) ok_slot[0] = wait_or_abort(o_done, last & 1, ab, 507) ? 1 : 0;
+      named_bar_sync(1, 128);
+      ok = ok_slot[0] != 0;
+      if (ok) {
+        while (!mbar_try_wait(o_done, last & 1)) {}
+        tc_fence_after_sync();
+      }
+    }
+    // row sums: every thread holds the part of its own keys
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      float v = l_part[r];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == r) sSum[quarter * kRows + r] = v;
+    }
+    named_bar_sync(1, 128);
+    if (ok && q_len > 0 && rows_total <= kRows) {
+      uint32_t orr[kRows];
+      if (n_tiles > 0) {
+        tmem_ld_x16(tO, orr);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) orr[r] = 0;
+      }
+      const int d = lane_id;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        if (r >= rows_total) break;
+        const float L = sSum[r] + sSum[kRows + r] + sSum[2 * kRows + r] + sSum[3 * kRows + r];
+        const float Ms = (m_run[r] == -INFINITY) ? 0.f : m_run[r];
+        const int tok = r / g, hh = kvh * g + r % g;
+        const int64_t orow = (int64_t)(qs + tok) * p.Hq + hh;
+        const float o = __uint_as_float(orr[r]);
+        if (p.num_splits == 1) {
+          float den = L;
+          if (p.sinks != nullptr) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
+          const float inv = den > 0.f ? 1.f / den : 0.f;
+          reinterpret_cast<T*>(p.out)[orow * D + d] = from_float<T>(o * inv);
+        } else {
+          const float inv = L > 0.f ? 1.f / L : 0.f;
+          p.ws_o[((int64_t)split * p.T * p.Hq + orow) * D + d] = o * inv;
+          if (d == 0) p.ws_lse[(int64_t)split * p.T * p.Hq + orow] = (L > 0.f) ? Ms + log2f(L) : -INFINITY;
+        }
+      }
+    }
+    if (p.num_splits > 1 && q_len > 0 && rows_total <= kRows) {
+      // ---- split-KV merge by the last CTA of this (request, kv head) to arrive
+      __threadfence();
+      named_bar_sync(1, 128);
+      const int ticket_idx = req * p.Hkv + kvh;
+      if (tid == 0) *s_last = (atomicAdd(&g_tickets[ticket_idx], 1) == p.num_splits - 1);
+      named_bar_sync(1, 128);
+      if (*s_last) {
+        __threadfence();
+        const int d = lane_id;
+        const int64_t sstride = p.T * p.Hq;
+        for (int r = 0; r < rows_total; ++r) {
+          const int tok = r / g, hh = kvh * g + r % g;
+          const int64_t orow = (int64_t)(qs + tok) * p.Hq + hh;
+          float M = -INFINITY;
+          for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, __ldcg(p.ws_lse + s2 * sstride + orow));
+          const float Ms = (M == -INFINITY) ? 0.f : M;
+          float den = 0.f, acc = 0.f;
+          for (int s2 = 0; s2 < p.num_splits; ++s2) {
+            const float wg = exp2f(__ldcg(p.ws_lse + s2 * sstride + orow) - Ms);
+            den += wg;
+            if (wg > 0.f) acc += __ldcg(p.ws_o + (s2 * sstride + orow) * D + d) * wg;
+          }
+          if (p.sinks != nullptr) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
+          const float inv = den > 0.f ? 1.f / den : 0.f;
+          reinterpret_cast<T*>(p.out)[orow * D + d] = from_float<T>(acc * inv);
+        }
+        if (tid == 0) g_tickets[ticket_idx] = 0;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T>
+static int launch(const Params& p0, const CUtensorMap& tm, int B, cudaStream_t st) {
+  constexpr int D = 128;
+  auto kern = decode_umma_kernel<T, D>;
+  Params p = p0;
+  constexpr int kStageBytes = 2 * (D / 64) * kTileKeys * 128;
+  p.num_stages = 3;
+  const size_t smem = 1024 + (size_t)p.num_stages * kStageBytes + (D / 64) * kRows * 128 + 2 * kRows * 128 + 1024;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
+  }
+  return (int)launch_pdl(kern, dim3(p.Hkv, B * p.num_splits), dim3(kThreads), smem, st, tm, p);
+}
+
+}  // namespace dattn
+}  // namespace b200
+
+// Decode-shaped paged attention (at most 16 packed query rows per KV head, head dim 128, cache blocks that are a
+// multiple of 64 tokens) on tcgen05.  `tmap` describes the cache as a 2-D [blocks * 2 * Hkv * block_size, 128]
+// 16-bit tensor with 64 x 64 boxes and 128-byte swizzle.  Returns 3 when the shape is not served.
+extern "C" int b200_decode_attention_umma(void* out, const void* q, const void* tmap, const int* block_tables,
+                                          const int* seq_lens, const int* qsl, const float* sinks, float* ws_o,
+                                          float* ws_lse, int* status, int64_t T_, int B, int Hq, int Hkv, int D,
+                                          int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
+                                          int num_splits, int window, float scale, int dtype, cudaStream_t st) {
+  using namespace b200;
+  if (B == 0 || T_ == 0) return 0;
+  if (D != 128 || Hq % Hkv || max_query_len * (Hq / Hkv) > dattn::kRows || block_size % dattn::kPage) return 3;
+  if (num_splits < 1 || (num_splits > 1 && (ws_o == nullptr || (int64_t)B * Hkv > dattn::kMaxTickets))) return 2;
+  dattn::Params p;
+  p.q = q; p.out = out; p.ws_o = ws_o; p.ws_lse = ws_lse; p.block_tables = block_tables; p.seq_lens = seq_lens;
+  p.qsl = qsl; p.sinks = sinks; p.status = status; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size;
+  p.max_blocks = max_blocks; p.num_splits = num_splits; p.window = window; p.num_blocks = num_blocks; p.T = T_;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_stages = 3;
+  {
+    const char* e = getenv("B200_UMMA_MN_SWAP");
+    p.mn_swap = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  const CUtensorMap& tm = *reinterpret_cast<const CUtensorMap*>(tmap);
+  if (dtype == 1) return dattn::launch<__nv_bfloat16>(p, tm, B, st);
+  if (dtype == 2) return dattn::launch<__half>(p, tm, B, st);
+  return 3;
+}

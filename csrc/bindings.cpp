@@ -38,6 +38,17 @@ at::Tensor weak_ref_tensor(const at::Tensor& t) {
   return torch::from_blob(t.data_ptr(), t.sizes(), t.strides(), t.options());
 }
 
+}  // namespace
+
+// Dispatcher registration (the reference registers the same function as ``torch.ops._C.weak_ref_tensor``,
+// vllm_kunlun/csrc/utils.cpp:26-28).  The op lives in this library's own namespace because an installed vLLM
+// defines ``_C::weak_ref_tensor`` itself and a second definition would abort the load; the Python loader aliases it
+// into ``_C`` when that name is still free.
+TORCH_LIBRARY(_C_b200, m) { m.def("weak_ref_tensor(Tensor input) -> Tensor"); }
+TORCH_LIBRARY_IMPL(_C_b200, CUDA, m) { m.impl("weak_ref_tensor", &weak_ref_tensor); }
+
+namespace {
+
 // ---------------------------------------------------------------------------------------- GEMM
 struct TmapKey {
   const void* p; int64_t rows, cols, stride; int box_rows; int elem_bytes;
@@ -606,6 +617,38 @@ void paged_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_c
         "paged_attention", num_splits > 1 ? 2 : 1);
 }
 
+// Decode attention on tcgen05 (see api.h); shares the GEMM module's tensor-map cache and status word.
+void decode_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_cache, const at::Tensor& block_tables,
+                           const at::Tensor& seq_lens, const at::Tensor& qsl, const c10::optional<at::Tensor>& sinks,
+                           const c10::optional<at::Tensor>& ws_o, const c10::optional<at::Tensor>& ws_lse,
+                           int64_t max_query_len, int64_t num_splits, int64_t window, double scale) {
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && kv_cache.is_contiguous() && q.dim() == 3 && kv_cache.dim() == 5);
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
+  TORCH_CHECK(block_tables.stride(1) == 1 && q.scalar_type() == kv_cache.scalar_type());
+  if (num_splits > 1) TORCH_CHECK(ws_o.has_value() && ws_lse.has_value());
+  c10::cuda::CUDAGuard guard(q.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, q.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, q.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, q.options().dtype(at::kInt));
+  }
+  const int D = q.size(2);
+  at::Tensor flat = kv_cache.view({-1, D});
+  const Tmap& tm = get_tmap(gs, flat, 64, 2);
+  int B = seq_lens.size(0);
+  check(b200_decode_attention_umma(out.data_ptr(), q.data_ptr(), tm.b, block_tables.data_ptr<int>(),
+                                   seq_lens.data_ptr<int>(), qsl.data_ptr<int>(),
+                                   sinks.has_value() ? sinks->data_ptr<float>() : nullptr,
+                                   ws_o.has_value() ? ws_o->data_ptr<float>() : nullptr,
+                                   ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, gs.status.data_ptr<int>(),
+                                   q.size(0), B, q.size(1), kv_cache.size(2), D, kv_cache.size(3), block_tables.stride(0),
+                                   kv_cache.size(0), max_query_len, num_splits, window, (float)scale, dtype_code(q),
+                                   stream()), "decode_attention_umma");
+}
+
 // q [T, N, 576], kv [blocks, bs, 576] -> out [T, N, 512]; dense (block tables) or sparse (indices [T, topk])
 void mla_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, const c10::optional<at::Tensor>& block_tables,
                    const c10::optional<at::Tensor>& seq_lens, const c10::optional<at::Tensor>& qsl,
@@ -963,6 +1006,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("copy_blocks", &copy_blocks);
   m.def("merge_attn_states", &merge_attn_states);
   m.def("paged_attention", &paged_attention);
+  m.def("decode_attention_umma", &decode_attention_umma);
   m.def("mla_attention", &mla_attention);
   m.def("indexer_logits", &indexer_logits);
   m.def("topk_rows", &topk_rows);

@@ -3,6 +3,15 @@
 from setuptools import find_packages, setup
 from setuptools.command.build_py import build_py
 
+import importlib.util
+import os
+
+_spec = importlib.util.spec_from_file_location(
+    "_b200_entry_points", os.path.join(os.path.dirname(os.path.abspath(__file__)), "vllm_kunlun_b200", "_entry_points.py"))
+_mod = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_mod)
+ENTRY_POINTS = _mod.ENTRY_POINTS
+
 
 class BuildWithKernels(build_py):
     def run(self):
@@ -22,14 +31,5 @@ setup(
     package_data={"vllm_kunlun_b200": ["_C*.so"]},
     python_requires=">=3.10",
     cmdclass={"build_py": BuildWithKernels},
-    entry_points={
-        "vllm.platform_plugins": ["b200 = vllm_kunlun_b200:register"],
-        "vllm.general_plugins": [
-            "b200_model = vllm_kunlun_b200:register_model",
-            "b200_quant = vllm_kunlun_b200:register_quant_method",
-            "b200_ops = vllm_kunlun_b200:register_custom_ops",
-            "b200_reasoning_parser = vllm_kunlun_b200:register_reasoning_parser",
-        ],
-        "console_scripts": ["vllm-kunlun-b200 = vllm_kunlun_b200.entrypoints.cli:main"],
-    },
+    entry_points=ENTRY_POINTS,
 )

@@ -6,6 +6,15 @@ import pytest
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def pytest_sessionstart(session):
+    # entry-point metadata beside the sources: lets the installed vLLM discover the plugin from this checkout
+    try:
+        from vllm_kunlun_b200._entry_points import write_egg_info
+        write_egg_info()
+    except Exception:
+        pass
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
     config.addinivalue_line("markers", "multigpu: needs >= 2 CUDA devices")

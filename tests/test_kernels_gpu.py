@@ -276,6 +276,69 @@ def test_cache_ops():
     _close(ml, rl, 1e-3, 1e-3, "merge lse")
 
 
+@pytest.mark.parametrize("Hq,Hkv,q_len", [(32, 8, 1), (4, 1, 1), (8, 2, 2), (16, 1, 1), (4, 4, 3)])
+@pytest.mark.parametrize("splits", [None, 1, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_attention_umma(Hq, Hkv, q_len, splits, dtype):
+    """tcgen05 decode attention (keys on the UMMA M side) vs the fp32 oracle: ragged lengths that end inside a tile,
+    inside a page and on a page edge, an empty request, several query tokens per request, split-KV merge."""
+    from vllm_kunlun_b200.ops.attention_cuda import UMMA_DECODE, paged_attention_cuda
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    assert UMMA_DECODE[0]
+    D, bs = 128, 64
+    lens = [1, 63, 64, 65, 128, 129, 700, 1337, 5, 2048]
+    lens = [max(n, q_len) for n in lens]
+    B = len(lens)
+    g = torch.Generator(device=DEV).manual_seed(Hq * 100 + q_len)
+    nblk_per = [-(-n // bs) for n in lens]
+    nblk = sum(nblk_per) + 3
+    kv = (torch.randn(nblk, 2, Hkv, bs, D, device=DEV, generator=g) * 1.0).to(dtype)
+    perm = torch.randperm(nblk - 1, device=DEV, generator=g) + 1  # block 0 stays unused
+    bt = torch.zeros(B, max(nblk_per), dtype=torch.int32, device=DEV)
+    o = 0
+    for b, n in enumerate(nblk_per):
+        bt[b, :n] = perm[o:o + n].int()
+        o += n
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    qsl = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device=DEV)
+    T = B * q_len
+    q = torch.randn(T, Hq, D, device=DEV, generator=g).to(dtype)
+    out = torch.full((T, Hq, D), float("nan"), device=DEV, dtype=dtype)
+    scale = D ** -0.5
+    paged_attention_cuda(out, q, kv, bt, seq_lens, qsl, scale, q_len, max(lens), None, None, None, splits)
+    torch.cuda.synchronize()
+    check_status()
+    ref = ra.paged_attention(q.cpu(), kv.cpu(), bt.cpu(), seq_lens.cpu(), qsl.cpu(), scale, None, None)
+    # P and V are 16-bit, sums are fp32: outputs are convex combinations of V rows of magnitude ~1
+    _close(out, ref, atol=0.02, rtol=0.02, name=f"decode umma {Hq}/{Hkv}/{q_len}/{splits}")
+
+
+def test_decode_attention_umma_window_and_sinks():
+    from vllm_kunlun_b200.ops.attention_cuda import paged_attention_cuda
+    D, bs, Hq, Hkv = 128, 64, 8, 2
+    lens = [900, 131, 64, 300]
+    B = len(lens)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    nblk_per = [-(-n // bs) for n in lens]
+    nblk = sum(nblk_per) + 1
+    kv = torch.randn(nblk, 2, Hkv, bs, D, device=DEV, generator=g).to(torch.bfloat16)
+    bt = torch.zeros(B, max(nblk_per), dtype=torch.int32, device=DEV)
+    o = 1
+    for b, n in enumerate(nblk_per):
+        bt[b, :n] = torch.arange(o, o + n, dtype=torch.int32, device=DEV)
+        o += n
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    qsl = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    q = torch.randn(B, Hq, D, device=DEV, generator=g).to(torch.bfloat16)
+    sinks = torch.randn(Hq, device=DEV, generator=g)
+    for window, sk, splits in [(200, None, 1), (200, sinks, 2), (None, sinks, 3)]:
+        out = torch.empty(B, Hq, D, device=DEV, dtype=torch.bfloat16)
+        paged_attention_cuda(out, q, kv, bt, seq_lens, qsl, D ** -0.5, 1, max(lens), window, sk, None, splits)
+        ref = ra.paged_attention(q.cpu(), kv.cpu(), bt.cpu(), seq_lens.cpu(), qsl.cpu(), D ** -0.5, window,
+                                 None if sk is None else sk.cpu())
+        _close(out, ref, atol=0.02, rtol=0.02, name=f"decode umma window={window} sinks={sk is not None}")
+
+
 @pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
 @pytest.mark.parametrize("T", [1, 16, 200, 1000])
 def test_gemm_fused_gated_activation(T, act):

@@ -56,8 +56,9 @@ def test_plugin_entry_points_and_platform():
     pkg.register_quant_method()
     from vllm_kunlun_b200.platforms.b200 import B200Platform
     assert B200Platform.dist_backend == "nccl" and B200Platform.device_type == "cuda"
-    assert B200Platform.get_device_communicator_cls().endswith("DeviceCommunicator")
-    assert "MLA" in B200Platform.get_attn_backend_cls(use_mla=True)
+    assert B200Platform.get_device_communicator_cls().endswith("B200Communicator")
+    from types import SimpleNamespace
+    assert "MLA" in B200Platform.get_attn_backend_cls(None, SimpleNamespace(use_mla=True, use_sparse=False))
     assert B200Platform.get_device_total_memory() > (1 << 30)
 
     class _C:  # minimal stand-in for a vLLM config
@@ -217,14 +218,19 @@ def test_bench_serving_client_against_live_server():
     assert out["completed"] == 4 and out["failed"] == 0 and out["output_tok_per_s"] > 0
 
 
+class _Sel:
+    def __init__(self, use_mla, use_sparse):
+        self.use_mla, self.use_sparse = use_mla, use_sparse
+
+
 def test_platform_class_paths_resolve():
     """Every "module.Class" string the platform hands to an engine imports and names an existing attribute."""
     import importlib
 
     from vllm_kunlun_b200.platforms.b200 import B200Platform
     paths = [B200Platform.get_device_communicator_cls(), B200Platform.get_punica_wrapper(),
-             B200Platform.get_attn_backend_cls(), B200Platform.get_attn_backend_cls(use_mla=True),
-             B200Platform.get_attn_backend_cls(use_mla=True, use_sparse=True), B200Platform.get_static_graph_wrapper_cls(),
+             B200Platform.get_attn_backend_cls(None, None), B200Platform.get_attn_backend_cls(None, _Sel(True, False)),
+             B200Platform.get_attn_backend_cls(None, _Sel(True, True)), B200Platform.get_static_graph_wrapper_cls(),
              pkg.register()]
     for p in paths:
         mod, _, name = p.rpartition(".")

@@ -50,12 +50,16 @@ def register_quant_method() -> None:
         return
     _completed_steps.add("quant")
     from . import quantization  # noqa: F401
+    from .quantization.vllm_registry import register_quant_configs
+    register_quant_configs()
 
 
 def register_custom_ops() -> None:
     """``vllm.general_plugins`` entry point: define the ``torch.ops.b200.*`` dispatcher ops for tracing hosts."""
     from .ops.custom_ops import register_custom_ops as _reg
     _reg()
+    from .ops.oot_layers import register_oot_layers
+    register_oot_layers()
 
 
 def __getattr__(name):

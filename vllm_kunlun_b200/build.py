@@ -131,6 +131,13 @@ def build(verbose: bool = False, force: bool = False) -> str:
     return OUT
 
 
+def write_egg_info() -> str:
+    """Entry-point metadata beside the sources, so that the installed vLLM finds the plugin from a checkout."""
+    from ._entry_points import write_egg_info as _w
+    return _w(ROOT)
+
+
 if __name__ == "__main__":
+    write_egg_info()
     path = build(verbose="-v" in sys.argv, force="-f" in sys.argv)
     print(path)

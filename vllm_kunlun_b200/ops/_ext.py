@@ -40,6 +40,7 @@ def load(required: bool = False):
                     mod = importlib.util.module_from_spec(spec)
                     spec.loader.exec_module(mod)
                     _MOD = mod
+                    _alias_weak_ref_tensor()
                 except Exception as e:  # pragma: no cover - depends on the build
                     _ERR = e
             else:
@@ -47,6 +48,27 @@ def load(required: bool = False):
     if _MOD is None and required:
         raise RuntimeError(f"vllm_kunlun_b200 CUDA extension is not available: {_ERR!r}")
     return _MOD
+
+
+_LIB = []
+
+
+def _alias_weak_ref_tensor() -> None:
+    """``torch.ops._C.weak_ref_tensor`` is the name upstream's graph capture looks up; define it on top of
+    ``_C_b200::weak_ref_tensor`` unless an installed vLLM has already defined it."""
+    import torch
+    try:
+        if hasattr(torch.ops._C, "weak_ref_tensor"):
+            return
+    except Exception:
+        pass
+    try:
+        lib = torch.library.Library("_C", "FRAGMENT")
+        lib.define("weak_ref_tensor(Tensor input) -> Tensor")
+        lib.impl("weak_ref_tensor", lambda t: torch.ops._C_b200.weak_ref_tensor(t), "CUDA")
+        _LIB.append(lib)
+    except Exception:  # defined concurrently by another library: theirs serves
+        pass
 
 
 def C():

@@ -10,9 +10,14 @@ from typing import Optional
 
 import torch
 
+import os
+
 from . import _ext
 
 _SM_COUNT: dict = {}
+# decode-shaped calls with head dim 128 and cache blocks of a multiple of 64 tokens run on the tcgen05 kernel
+# (csrc/attention/decode_umma.cu); B200_ATTN_UMMA=0 keeps them on the mma.sync kernel
+UMMA_DECODE = [os.environ.get("B200_ATTN_UMMA", "1") != "0"]
 
 
 def sm_count(device) -> int:
@@ -50,6 +55,15 @@ def plan_splits(num_reqs: int, num_kv_heads: int, q_tiles: int, max_seq_len: int
     return best
 
 
+def plan_splits_umma(num_reqs: int, num_kv_heads: int, max_seq_len: int, device, max_splits: int = 16) -> int:
+    """One CTA per SM streams 128-key tiles through a deep TMA ring, so a (request, kv head) pair is split only as
+    far as it takes to occupy the SMs, and never below two tiles per CTA."""
+    base = max(1, num_reqs * num_kv_heads)
+    tiles = max(1, -(-max_seq_len // 128))
+    s = max(1, sm_count(device) // base)
+    return int(max(1, min(s, max_splits, max(1, tiles // 2))))
+
+
 def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
                          max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
                          workspace: Optional[AttnWorkspace] = None, num_splits: Optional[int] = None):
@@ -58,6 +72,20 @@ def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_l
     g = Hq // Hkv
     B = seq_lens.shape[0]
     decode_layout = max_query_len * g <= 16
+    if (decode_layout and UMMA_DECODE[0] and D == 128 and kv_cache.shape[3] % 64 == 0
+            and q.dtype in (torch.bfloat16, torch.float16)):
+        if num_splits is None:
+            num_splits = plan_splits_umma(B, Hkv, max_seq_len, q.device,
+                                          workspace.max_splits if workspace is not None else 16)
+        ws_o = ws_lse = None
+        if num_splits > 1:
+            if workspace is None:
+                workspace = AttnWorkspace(T, Hq, D, num_splits, q.device)
+            assert T <= workspace.max_tokens and num_splits <= workspace.max_splits
+            ws_o, ws_lse = workspace.o, workspace.lse
+        _ext.C().decode_attention_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, ws_o, ws_lse,
+                                       max_query_len, num_splits, window or 0, scale)
+        return out
     if num_splits is None:
         if decode_layout:
             num_splits = plan_splits(B, Hkv, 1, max_seq_len, q.device,

@@ -84,21 +84,41 @@ class B200Platform(_VllmPlatform):
     # ---- class paths (the extension points upstream resolves by string) ----
     @classmethod
     def get_device_communicator_cls(cls) -> str:
-        return "vllm_kunlun_b200.parallel.communicator.DeviceCommunicator"
+        # a ``DeviceCommunicatorBase`` subclass with upstream's constructor; the standalone engine uses
+        # ``vllm_kunlun_b200.parallel.communicator.DeviceCommunicator`` on the same peer-memory kernels
+        return "vllm_kunlun_b200.distributed.b200_communicator.B200Communicator"
 
     @classmethod
     def get_punica_wrapper(cls) -> str:
-        return "vllm_kunlun_b200.lora.punica.PunicaWrapperB200"
+        return "vllm_kunlun_b200.lora.punica_vllm.PunicaWrapperB200"
 
     @classmethod
-    def get_attn_backend_cls(cls, selected_backend=None, *args, **kwargs) -> str:
-        use_mla = bool(kwargs.get("use_mla", False))
-        use_sparse = bool(kwargs.get("use_sparse", False))
+    def get_attn_backend_cls(cls, selected_backend, attn_selector_config, num_heads=None) -> str:
+        """Upstream's selector calls ``(selected_backend, attn_selector_config, num_heads)``; the choice follows
+        ``attn_selector_config.use_mla`` / ``use_sparse`` (``platforms/kunlun.py:247-283``)."""
+        use_mla = bool(getattr(attn_selector_config, "use_mla", False))
+        use_sparse = bool(getattr(attn_selector_config, "use_sparse", False))
         if use_mla and use_sparse:
             return "vllm_kunlun_b200.attention.backends.SparseMLABackend"
         if use_mla:
             return "vllm_kunlun_b200.attention.backends.MLABackend"
         return "vllm_kunlun_b200.attention.backends.GQABackend"
+
+    @classmethod
+    def is_cuda_alike(cls) -> bool:
+        return True
+
+    @classmethod
+    def use_custom_allreduce(cls) -> bool:
+        return False  # the peer-memory kernels live in the device communicator, not in upstream's custom all-reduce
+
+    @classmethod
+    def import_kernels(cls) -> None:
+        """Load the in-tree extension instead of upstream's ``vllm._C`` and register the out-of-tree layers."""
+        from ..ops import _ext
+        _ext.load(required=False)
+        from ..ops.oot_layers import register_oot_layers
+        register_oot_layers()
 
     @classmethod
     def get_static_graph_wrapper_cls(cls) -> str:
@@ -144,6 +164,8 @@ class B200Platform(_VllmPlatform):
     @classmethod
     def pre_register_and_update(cls, parser=None) -> None:
         from .. import quantization  # noqa: F401  (registers fp8 / int8 / awq / gptq methods)
+        from ..ops.oot_layers import register_oot_layers
+        register_oot_layers()
 
 
 def register_models_with_vllm() -> int:
