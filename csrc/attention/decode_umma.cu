@@ -436,13 +436,9 @@ static int launch(const Params& p0, const CUtensorMap& tm, int B, cudaStream_t s
   constexpr int kStageBytes = 2 * (D / 64) * kTileKeys * 128;
   p.num_stages = 3;
   const size_t smem = 1024 + (size_t)p.num_stages * kStageBytes + (D / 64) * kRows * 128 + 2 * kRows * 128 + 1024;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev] = true;
   }
   return (int)launch_pdl(kern, dim3(p.Hkv, B * p.num_splits), dim3(kThreads), smem, st, tm, p);
 }

@@ -267,11 +267,9 @@ static int launch_mla(const MlaParams& p, cudaStream_t st) {
   size_t smem = (size_t)(16 * kMlaD + kMlaStages * kMlaTile * kMlaD + 2 * 16 * kMlaTile) * sizeof(T) +
                 (2 * 4 * 16 + 4 * 16) * sizeof(float) + kMlaStages * kMlaTile * sizeof(int);
   auto kern = mla_attention_kernel<T, kSparse>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   dim3 grid((p.N + 15) / 16, (unsigned)p.T, p.num_splits);
   return (int)launch_pdl(kern, grid, dim3(kMlaThreads), smem, st, p);

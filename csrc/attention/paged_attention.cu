@@ -364,11 +364,9 @@ static int launch_attn(const AttnParams& p, int B, int max_q_rows, cudaStream_t 
   size_t tail = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
   size_t smem = (size_t)BM * D * sizeof(T) + tail;
   auto kern = paged_attention_kernel<T, D, WM, WN, kStages>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   dim3 grid((max_q_rows + BM - 1) / BM, p.Hkv, B * p.num_splits);
   kern<<<grid, kAttnThreads, smem, st>>>(p);

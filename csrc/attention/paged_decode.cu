@@ -324,11 +324,9 @@ static int launch_decode(AttnParams p, int B, int max_q_rows, cudaStream_t st, b
   size_t merge_bytes = (size_t)(kWarps * 16 * D + 2 * kWarps * 16) * sizeof(float);
   size_t smem = (size_t)16 * D * sizeof(T) + (kv_bytes > merge_bytes ? kv_bytes : merge_bytes);
   auto kern = paged_decode_kernel<T, D, kWarps, kStages>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   dim3 grid((max_q_rows + 15) / 16, p.Hkv, B * p.num_splits);
   static const bool fuse_on = [] { const char* e = getenv("B200_ATTN_FUSE_MERGE"); return !(e != nullptr && e[0] == '0'); }();

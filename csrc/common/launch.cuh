@@ -19,6 +19,10 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 // Process-wide switch (default on; B200_PDL=0 in the environment turns it off).
 int pdl_enabled();
 int gemm_l2_prefetch();
+// Raises a kernel's dynamic shared-memory limit to at least `bytes` on the CURRENT device, once per
+// (kernel, device) pair: the attribute belongs to the device context, so a process that drives several GPUs must
+// set it on each of them (defined in runtime/tma.cpp).
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,

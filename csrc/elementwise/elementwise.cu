@@ -305,6 +305,7 @@ void* g_scratch_ptr[kMaxDevices] = {nullptr};
 extern "C" int b200_argmax_noalloc(int64_t* out, const void* logits, int64_t rows, int V_, int64_t stride, int dtype,
                                    cudaStream_t st) {
   if (out == nullptr || logits == nullptr || rows < 0 || V_ <= 0 || rows > B200_ARGMAX_NOALLOC_MAX_ROWS) return 22;
+  if (stride < V_ || dtype < 0 || dtype > 2) return 22;  // rows would overlap / unknown element type
   if (rows == 0) return 0;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);

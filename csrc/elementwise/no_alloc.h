@@ -23,14 +23,16 @@ extern "C" {
 // out[r] = index of the largest element of logits[r, 0..V)  (ties -> lowest index), r < rows.
 //   logits  device pointer, row stride `stride` elements, dtype 0 = f32, 1 = bf16, 2 = f16
 //   out     device pointer to `rows` int64
-// Returns 0 on success, 22 (EINVAL) when rows > B200_ARGMAX_NOALLOC_MAX_ROWS or an argument is
-// null / non-positive (nothing is launched), otherwise the cudaError_t of the failing call.
+// Returns 0 on success (rows == 0 is a successful no-op); 22 (EINVAL), with nothing launched, when
+// rows > B200_ARGMAX_NOALLOC_MAX_ROWS, rows < 0, V <= 0, stride < V, dtype is not 0 / 1 / 2, or a pointer is
+// null; otherwise the cudaError_t of the failing call.
 //
 // * Calls no cudaMalloc / cudaFree and no allocating library routine; the caller passes only its
 //   inputs and outputs.
 // * The first call on each device resolves the device address of the scratch array
-//   (cudaGetSymbolAddress, with that device current).  Make that first call outside any stream
-//   capture.
+//   (cudaGetSymbolAddress, with that device current) and caches it in a host-side table without a
+//   lock.  Make that first call outside any stream capture, and do not let two host threads make
+//   the first call on the same device at the same time (later calls only read the table).
 // * All calls on one device share the one scratch array.  Each call overwrites every scratch
 //   entry it later reads, so nothing needs clearing between calls - but two calls whose kernels
 //   overlap on the GPU (different streams, no dependency) race on it.  Serialise them.

@@ -525,12 +525,9 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   cm.ag_flags = (const uint32_t*)a.ag_flags;
   cm.rs_on = a.rs_on; cm.rs_tloc = a.rs_tloc; cm.rs_rank = a.rs_rank; cm.ag_on = a.ag_on; cm.ag_expect = a.ag_expect;
   cm.spin_limit = a.spin_limit;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kStagesRaw * Cfg::kStageBytes + 1024 + 512 + kEpBytes);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, Cfg::kStagesRaw * Cfg::kStageBytes + 1024 + 512 + kEpBytes);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   // Shared memory per CTA decides how many CTAs share an SM: small token tiles run two CTAs per SM
   // so one CTA's prologue / split-K epilogue overlaps the other's main loop.

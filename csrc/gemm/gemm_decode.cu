@@ -360,13 +360,9 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   using C = Cfg<BN>;
   auto kern = gemm_decode_kernel<BN, OutT>;
   const int fixed = 1024 /*align*/ + 512 /*barriers*/ + (a.S - 1) * C::kSlotBytes + C::kTileBytes + 64;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, 220 * 1024);
     if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
   }
   const int total_kb = (a.K + BK - 1) / BK;
   const int nkb = a.kb_per_cta;

@@ -329,11 +329,9 @@ static cudaError_t launch_grouped(const GroupedGemmArgs& a, const CUtensorMap& t
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
   int smem = stages * Cfg::kStageBytes + extra;
-  static int attr_smem = 0;
-  if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, smem);
     if (e != cudaSuccess) return e;
-    attr_smem = smem;
   }
   GParams p;
   p.out = a.out; p.bias = a.bias; p.lod = a.lod; p.a_scale = a.a_scale; p.w_scale = a.w_scale; p.status = a.status;

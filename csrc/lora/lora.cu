@@ -7,6 +7,7 @@
 // bgmv_expand(_slice)_lora (vllm_kunlun/ops/_custom_ops.py:2435-2836), driven by PunicaWrapperKunlun
 // (vllm_kunlun/lora/punica_wrapper/punica_kunlun.py:273-545).
 #include "../api.h"
+#include "../common/launch.cuh"
 #include "../common/utils.cuh"
 
 namespace b200 {
@@ -83,8 +84,7 @@ extern "C" int b200_lora_shrink(float* out, const void* x, int64_t x_stride, con
   size_t smem = (size_t)K * esz;
   if (smem > 200 * 1024) return 3;
   B200_DISPATCH_DTYPE(dtype, {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(b200::lora_shrink_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024) b200::ensure_dynamic_smem((const void*)b200::lora_shrink_kernel<T>, (int)smem);
     b200::lora_shrink_kernel<T><<<(unsigned)T_, 256, smem, st>>>(out, (const T*)x, x_stride, (const T*)A, ids, r, K, scale);
   });
   return cudaGetLastError() != cudaSuccess;

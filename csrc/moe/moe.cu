@@ -585,11 +585,7 @@ extern "C" int b200_router_gemm_small(float* out, const void* x, int64_t x_strid
   int esz = dtype == 0 ? 4 : 2;
   if (K % (16 / esz) || (x_stride * esz) % 16 || (size_t)K * esz > 96 * 1024) return 2;
   B200_DISPATCH_DTYPE(dtype, {
-    static bool attr = false;
-    if (!attr && (size_t)K * esz > 48 * 1024) {
-      cudaFuncSetAttribute(router_gemm_small_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      attr = true;
-    }
+    if ((size_t)K * esz > 48 * 1024) ensure_dynamic_smem((const void*)router_gemm_small_kernel<T>, 96 * 1024);
     launch_pdl(router_gemm_small_kernel<T>, dim3((unsigned)T_, (N + 31) / 32), dim3(256), (size_t)K * esz, st, out,
                (const T*)x, x_stride, (const T*)w, (const T*)bias, N, K);
   });
@@ -606,11 +602,7 @@ extern "C" int b200_router_route_small(float* out_w, int* out_ids, const void* x
   const size_t smem = (((size_t)K * esz + 15) & ~(size_t)15) + (size_t)E * 4;
   if (smem > 96 * 1024) return 2;
   B200_DISPATCH_DTYPE(dtype, {
-    static bool attr = false;
-    if (!attr && smem > 48 * 1024) {
-      cudaFuncSetAttribute(router_route_small_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      attr = true;
-    }
+    if (smem > 48 * 1024) ensure_dynamic_smem((const void*)router_route_small_kernel<T>, 96 * 1024);
     launch_pdl(router_route_small_kernel<T>, dim3((unsigned)T_), dim3(256), smem, st, out_w, out_ids, (const T*)x,
                x_stride, (const T*)w, (const T*)wbias, bias, E, K, k, mode, renorm, n_group, topk_group, scale);
   });

@@ -46,7 +46,25 @@ extern "C" int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, u
 
 // ---- PDL switch (see common/launch.cuh) ----
 #include <stdlib.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
 namespace b200 {
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> done;  // (kernel, device) -> limit already set
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_pair(kernel, dev);
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[key] = bytes;
+  return e;
+}
 int pdl_enabled() {
   static int v = [] {
     const char* e = getenv("B200_PDL");

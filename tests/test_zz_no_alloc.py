@@ -36,10 +36,19 @@ def test_argmax_noalloc_matches_regular_entry_point():
         for (logits, out), (r, v, dt) in zip(tensors, cases):
             out.fill_(-7)
             before = torch.cuda.memory_allocated(dev)
+            if round_ == 1:  # after the first call per device (which resolves the symbol) the driver must not
+                torch.cuda.synchronize()  # hand out a single byte either: compare the device-wide free memory
+                free_before = torch.cuda.mem_get_info(dev)[0]
             rc = fn(out.data_ptr(), logits.data_ptr(), r, v, logits.stride(0), codes[dt], stream)
             assert rc == 0, rc
             assert torch.cuda.memory_allocated(dev) == before
             torch.cuda.synchronize()
+            if round_ == 1 and torch.cuda.mem_get_info(dev)[0] < free_before:
+                # free memory is a device-wide figure: make sure it was this call and not a neighbour process
+                free_before = torch.cuda.mem_get_info(dev)[0]
+                assert fn(out.data_ptr(), logits.data_ptr(), r, v, logits.stride(0), codes[dt], stream) == 0
+                torch.cuda.synchronize()
+                assert torch.cuda.mem_get_info(dev)[0] >= free_before, "the call took memory from the driver"
             want = ops.argmax(logits)
             assert torch.equal(out, want), (round_, r, v, dt)
             assert torch.equal(out.cpu(), logits.float().argmax(-1).cpu())
@@ -49,3 +58,11 @@ def test_argmax_noalloc_matches_regular_entry_point():
     assert fn(out.data_ptr(), big.data_ptr(), 4096, 64, 64, 0, stream) == 22
     torch.cuda.synchronize()
     assert int(out.min()) == -7 and int(out.max()) == -7
+    # malformed arguments: rows that would overlap, an unknown element type, nothing to do
+    small = torch.zeros(4, 64, device=dev)
+    out4 = torch.full((4,), -7, dtype=torch.int64, device=dev)
+    assert fn(out4.data_ptr(), small.data_ptr(), 4, 64, 32, 0, stream) == 22
+    assert fn(out4.data_ptr(), small.data_ptr(), 4, 64, 64, 9, stream) == 22
+    assert fn(out4.data_ptr(), small.data_ptr(), 0, 64, 64, 0, stream) == 0
+    torch.cuda.synchronize()
+    assert int(out4.min()) == -7

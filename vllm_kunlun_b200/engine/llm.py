@@ -68,6 +68,14 @@ class LLMEngine:
         self.async_scheduling = self.runner.is_cuda and self.spec is None
         self._inflight: Optional[StepHandle] = None
         self._ids = itertools.count()
+        # host-side failure detection between steps (parallel/health.py): every N-th step the ranks shake hands
+        # through the job's key-value store before launching; off unless B200_HEALTH_CHECK_INTERVAL > 0
+        self.monitor = None
+        from .. import envs
+        self._health_every = int(envs.B200_HEALTH_CHECK_INTERVAL)
+        if self._health_every > 0:
+            from ..parallel.health import RankMonitor
+            self.monitor = RankMonitor.from_default_group(timeout=float(envs.B200_HEALTH_TIMEOUT_S))
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
                       "spec_proposed": 0, "spec_accepted": 0}
 
@@ -174,6 +182,10 @@ class LLMEngine:
                 finished = self._process(self._inflight)
                 self._inflight = None
             return finished
+        if self.monitor is not None and self.stats["steps"] % self._health_every == 0:
+            # no kernel of the coming step has been launched yet: a peer that left or stopped beating surfaces
+            # here as RankLeft / RankTimeout instead of as a collective that never completes
+            self.monitor.check(wait_for_step=self.monitor.beat())
         h = self.runner.execute(sched)
         self.stats["steps"] += 1
         for sr in sched.scheduled:

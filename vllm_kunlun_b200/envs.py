@@ -23,6 +23,13 @@ _ENV: dict[str, Callable[[], Any]] = {
     "B200_PDL": lambda: os.environ.get("B200_PDL", "1") != "0",
     # 16 KB weight tiles per CTA that a decode-shaped GEMM pulls into L2 ahead of its smem ring (read by the C++ side; measured slower than off)
     "B200_GEMM_L2_PREFETCH": lambda: int(os.environ.get("B200_GEMM_L2_PREFETCH", "0")),
+    # decode-sized GEMMs on the cluster split-K kernel / its peer-push epilogue under TP / tcgen05 decode attention
+    "B200_DECODE_GEMM": lambda: os.environ.get("B200_DECODE_GEMM", "1") != "0",
+    "B200_GEMM_PUSH": lambda: os.environ.get("B200_GEMM_PUSH", "1") != "0",
+    "B200_ATTN_UMMA": lambda: os.environ.get("B200_ATTN_UMMA", "1") != "0",
+    # host-side rank handshake every N engine steps (0 = off) and how long to wait for a silent peer
+    "B200_HEALTH_CHECK_INTERVAL": lambda: int(os.environ.get("B200_HEALTH_CHECK_INTERVAL", "0")),
+    "B200_HEALTH_TIMEOUT_S": lambda: float(os.environ.get("B200_HEALTH_TIMEOUT_S", "30")),
     # gated activation inside the gate/up GEMM epilogue (interleaved weight tiles); decode attention merging its own
     # split-KV partials (read by the C++ side)
     "B200_FUSE_ACT": lambda: os.environ.get("B200_FUSE_ACT", "1") != "0",
