@@ -33,6 +33,8 @@ BASELINE_TOK_S = {  # published by the reference (Kunlun3 P800), 16-way, 2048/20
     "llama-3.1-8b": 1779.8,   # closest published analogue: Qwen3-8B, TP=1
     "qwen3-8b": 1779.8,
     "qwen3-30b-a3b": 1927.4,  # Qwen3-30B-A3B, TP=2
+    # nothing is published for DeepSeek-V3 / V3.2; the nearest chart entry by size is Qwen3-235B-A22B at TP=8
+    "deepseek-v3": 927.5,
 }
 
 
@@ -40,6 +42,16 @@ BASELINE_REF = {
     "llama-3.1-8b": "Qwen3-8B TP=1 on Kunlun3 P800 (closest published analogue)",
     "qwen3-8b": "Qwen3-8B TP=1 on Kunlun3 P800",
     "qwen3-30b-a3b": "Qwen3-30B-A3B TP=2 on 2x Kunlun3 P800",
+    "deepseek-v3": "none published for DeepSeek-V3; Qwen3-235B-A22B TP=8 on 8x Kunlun3 P800 is the nearest chart entry",
+    "deepseek-v3.2": "none published",
+}
+
+# The benchmark configurations by number: 2 is the default (the driver's command line does not change).
+CONFIGS = {
+    2: dict(model="llama-3.1-8b", in_len=2048, out_len=2048, ep=False, spec=None, kv_cache_dtype="auto"),
+    3: dict(model="qwen3-30b-a3b", in_len=2048, out_len=2048, ep=True, spec=None, kv_cache_dtype="auto"),
+    4: dict(model="deepseek-v3", in_len=2048, out_len=2048, ep=True, spec="mtp", kv_cache_dtype="auto"),
+    5: dict(model="deepseek-v3.2", in_len=32768, out_len=1024, ep=True, spec=None, kv_cache_dtype="auto"),
 }
 
 
@@ -49,14 +61,28 @@ def parse():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="llama-3.1-8b")
+    ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS),
+                    help="benchmark configuration: 2 Llama-3.1-8B bf16 (default), 3 Qwen3-30B-A3B fp8 TP+EP, "
+                         "4 DeepSeek-V3 fp8 TP+EP+MTP, 5 DeepSeek-V3.2 sparse attention at 32k context")
+    ap.add_argument("--model", default=None, help="override the model of the configuration")
     ap.add_argument("--concurrency", type=int, default=16)
-    ap.add_argument("--in-len", type=int, default=2048)
-    ap.add_argument("--out-len", type=int, default=2048)
+    ap.add_argument("--in-len", type=int, default=None)
+    ap.add_argument("--out-len", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ep", action="store_true", help="expert parallelism for MoE models (whole experts per rank)")
     ap.add_argument("--spec", default=None, help="speculative method (mtp | ngram | eagle), one draft token")
-    return ap.parse_args()
+    ap.add_argument("--kv-cache-dtype", default=None)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="debugging only: run with this many layers (the JSON line then says so and is not a result)")
+    a = ap.parse_args()
+    c = CONFIGS[a.config]
+    a.model = a.model or c["model"]
+    a.in_len = a.in_len or c["in_len"]
+    a.out_len = a.out_len or c["out_len"]
+    a.ep = a.ep or c["ep"]
+    a.spec = a.spec or c["spec"]
+    a.kv_cache_dtype = a.kv_cache_dtype or c["kv_cache_dtype"]
+    return a
 
 
 class ClockSampler:
@@ -110,12 +136,22 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The reference is a Kunlun-XPU plugin: its offline `pip install --no-index ...` fails
-    # (build backend `hatchling` is not in the wheelhouse) and, installed or not, it imports closed
-    # vendor wheels (kunlun_ops, xspeedgate_ops, cocopod) at module top level.
+    """The reference arm: the unmodified reference through its own public API, or one ``unavailable`` line.
+
+    Two independent facts keep it from running here (``baseline/probe_reference.py`` reproduces the second):
+    * its offline install (``pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target
+      baseline/_ref``) fails because the build backend ``hatchling`` is not in the wheelhouse;
+    * a plain copy of the package with empty stand-ins for the closed Kunlun wheels registers its platform, but the
+      modules behind it do not import on the installed vLLM 0.22 (the reference pins 0.15.1): the first failures are
+      ``from vllm.v1.attention.backends.tree_attn import TreeAttentionMetadata`` (``v1/sample/spec_decode/eagle.py:10``,
+      reached from ``vllm_kunlun.ops`` and from the attention backend) and ``from vllm.attention.backends.abstract
+      import AttentionBackend`` (``v1/worker/utils.py:8``); both modules are gone from vLLM 0.22.
+    """
     print(json.dumps({"impl": "reference", "unavailable":
-                      "reference needs closed Kunlun wheels (kunlun_ops/xspeedgate_ops/cocopod) and its hatchling "
-                      "build backend is absent offline; baseline/_ref could not be installed"}))
+                      "reference pins vLLM 0.15.1 and does not import on the installed vLLM 0.22 "
+                      "(ModuleNotFoundError: vllm.v1.attention.backends.tree_attn, vllm.attention); its kernels are "
+                      "closed Kunlun wheels (kunlun_ops/xspeedgate_ops/cocopod) and its hatchling build backend is "
+                      "absent offline, so baseline/_ref could not be installed"}))
     return 0
 
 
@@ -137,9 +173,18 @@ def main():
     torch.cuda.set_device(local)
     C, IN, OUT = args.concurrency, args.in_len, args.out_len
     spec = {"method": args.spec, "num_speculative_tokens": 1} if args.spec else None
-    llm = LLM(args.model, tensor_parallel_size=world, device="cuda", block_size=64, max_model_len=IN + OUT + 64,
+    model = args.model
+    if args.layers:
+        import dataclasses
+
+        from vllm_kunlun_b200.config import PRESETS
+        mc = PRESETS[args.model]()
+        model = dataclasses.replace(mc, num_layers=args.layers,
+                                    first_dense_layers=min(mc.first_dense_layers, max(1, args.layers // 2)))
+    llm = LLM(model, tensor_parallel_size=world, device="cuda", block_size=64, max_model_len=IN + OUT + 64,
               max_num_seqs=C, max_num_batched_tokens=8192, gpu_memory_utilization=0.9, seed=0,
-              enable_expert_parallel=args.ep and world > 1, speculative_config=spec)
+              enable_expert_parallel=args.ep and world > 1, speculative_config=spec,
+              kv_cache_dtype=args.kv_cache_dtype)
     eng = llm.engine
     vocab = eng.cfg.model.vocab_size
     g = torch.Generator().manual_seed(1234)
@@ -199,20 +244,33 @@ def main():
     dev_ms, e2e_max = t.tolist()
     from vllm_kunlun_b200.ops.gemm_cuda import check_status
     check_status()
+    # every status word of the peer-memory collectives and the expert exchange must be clean as well: a number
+    # from a run in which a bounded wait gave up would come from wrong data
+    for comm in (eng.pstate.tp_comm, eng.pstate.ep_comm, eng.pstate.dcp_comm):
+        peer = getattr(comm, "peer", None) if comm is not None else None
+        if peer is not None:
+            peer.check_status()
+    a2a = getattr(eng.pstate, "ep_a2a", None)
+    if a2a is not None:
+        a2a.check_status()
     if rank == 0:
         tokens = C * OUT * args.steps
         value = tokens / (dev_ms / 1e3)
         base = BASELINE_TOK_S.get(args.model)
         out = {
-            "metric": "output tok/s at 16 concurrency, 2048 in/2048 out", "value": round(value, 1), "unit": "tok/s",
+            "metric": f"output tok/s at {C} concurrency, {IN} in/{OUT} out", "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 2),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": round(value / base, 3) if base else None,
             "dtype": "fp8 weights (128x128 block scales), bf16 activations" if eng.cfg.model.quantization == "fp8" else "bf16",
             "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "impl": "ours",
-            "config": {"model": args.model, "global_batch": C, "seq_len": IN + OUT, "in_len": IN, "out_len": OUT,
+            "config": {"model": args.model, "bench_config": args.config, "global_batch": C, "seq_len": IN + OUT,
+                       "in_len": IN, "out_len": OUT,
                        "parallelism": f"tp{world}" + ("+ep" if args.ep and world > 1 else "") + (f"+{args.spec}" if args.spec else ""),
-                       "step": "one full serving round of 16 requests",
+                       "step": f"one full serving round of {C} requests",
+                       **({"reduced_layers": args.layers, "valid": False} if args.layers else {}),
+                       **({"spec_acceptance": round(eng.stats["spec_accepted"] / max(1, eng.stats["spec_proposed"]), 3)}
+                          if args.spec else {}),
                        "l2": "inputs larger than L2: every decode step streams the active weight set and the KV cache "
                              "(16 GB of bf16 weights for the 8B dense model)",
                        "baseline_ref": BASELINE_REF.get(args.model, "none published")},
@@ -226,12 +284,23 @@ def main():
                           "ms_per_step": round(e2e_max / args.steps, 2)}
         print(json.dumps(out), flush=True)
     if world > 1:
-        # leave together; captured graphs still reference the NCCL communicator, so the process
-        # exits without an explicit communicator teardown
+        # orderly teardown: drop the captured graphs first (they hold references into the communicators'
+        # buffers), then the peer mappings, then the process group
         torch.cuda.synchronize()
         dist.barrier(device_ids=[local])
         sys.stdout.flush()
-        os._exit(0)
+        try:
+            if eng.runner.graphs is not None:
+                eng.runner.graphs.graphs.clear()
+                eng.runner.graphs = None
+            torch.cuda.synchronize()
+            from vllm_kunlun_b200.parallel.state import destroy_model_parallel
+            destroy_model_parallel()
+            dist.barrier(device_ids=[local])
+            dist.destroy_process_group()
+        except Exception as e:  # a failed teardown must not turn a measured run into a failed one
+            print(f"[bench] teardown: {e!r}", file=sys.stderr, flush=True)
+            os._exit(0)
     return 0
 
 

@@ -14,8 +14,8 @@
 //              (128-byte swizzle) into a 3-stage ring; pages are looked up in the block table
 //   warp 1     allocates TMEM, issues tcgen05.mma (one thread): S^T of tile i+1 is issued before P.V of tile i
 //   warps 2-5  softmax: thread t owns key t of the tile (TMEM lane t): mask, tile max per row (redux + a
-//              shared-memory exchange between the four warps), exp2, P^T to shared memory (bf16, K-major, swizzled)
-//              for the second MMA; the same threads own output dim t in the epilogue
+//              shared-memory exchange between the four warps), exp2, P^T to one of two shared-memory buffers
+//              (16-bit, K-major, swizzled) for the second MMA; the same threads own output dim t in the epilogue
 // Split-KV partials go through the fp32 workspace and are merged by the last CTA of a (request, head) to arrive.
 // Every wait is bounded: on time-out the status word is set, the CTA drains its copies, frees TMEM and returns.
 #include <cuda.h>
@@ -49,7 +49,7 @@ struct Params {
   const int* qsl;
   const float* sinks;
   int* status;
-  int Hq, Hkv, block_size, max_blocks, num_splits, window, num_stages, mn_swap;
+  int Hq, Hkv, block_size, max_blocks, num_splits, window, num_stages;
   int64_t num_blocks, T;
   float scale_log2;
 };
@@ -81,7 +81,14 @@ template <> __device__ __forceinline__ uint16_t to_bits16<__nv_bfloat16>(float v
 template <> __device__ __forceinline__ uint16_t to_bits16<__half>(float v) { return __half_as_ushort(__float2half(v)); }
 
 // D = head dim (128): K-blocks of 64 dims.  Shared memory per stage: K [D/64][128 keys][128 B] then V the same.
-template <typename T, int D>
+// NR = number of query rows that are computed (4, 8 or 16 >= group x query tokens); the UMMA N stays 16 with the
+// rows beyond the real ones zero.
+//
+// Online softmax with a LAZY running maximum: the reference maximum m_used of a row only moves when a tile's
+// maximum exceeds it by more than kMaxSlack (in log2 units), so p = exp2(s - m_used) stays below 2^kMaxSlack and the
+// result O / l is unchanged; in the common case O^T needs no rescale and the softmax warps never wait for the
+// previous P.V to finish - they run ahead into a second P buffer while the tensor core works.
+template <typename T, int D, int NR>
 __global__ void __launch_bounds__(kThreads)
 decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ Params p) {
   constexpr int KB = D / 64;                       // 64-dim blocks
@@ -89,27 +96,30 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   constexpr int kOpBytes = KB * kHalfBytes;        // K (or V) of one tile
   constexpr int kStageBytes = 2 * kOpBytes;
   constexpr int kQBytes = KB * kRows * 128;        // Q^T operand: [D/64][16 rows][128 B]
-  constexpr int kPBytes = (kTileKeys / 64) * kRows * 128;
-  constexpr int kTmemCols = 64;                    // S^T x 2 buffers (16 cols each) + O^T (D/128 x 16 cols)
+  constexpr int kPBytes = (kTileKeys / 64) * kRows * 128;  // one P buffer: [2 key blocks][16 rows][128 B]
+  constexpr int kTmemCols = 64;                    // S^T x 2 buffers (16 cols each) + O^T (16 cols)
+  constexpr float kMaxSlack = 8.f;
   static_assert(D == 128, "one 128-lane O^T tile");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int num_stages = p.num_stages;
   uint8_t* sQ = smem + num_stages * kStageBytes;
-  uint8_t* sP = sQ + kQBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);
+  uint8_t* sP = sQ + kQBytes;                      // [2][kPBytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
   uint64_t* kv_full = bars;                        // [stages]
   uint64_t* kv_empty = bars + num_stages;          // [stages]
   uint64_t* s_full = bars + 2 * num_stages;        // [2]
   uint64_t* s_empty = s_full + 2;                  // [2]
-  uint64_t* p_ready = s_empty + 2;                 // [1]
-  uint64_t* o_done = p_ready + 1;                  // [1]
+  uint64_t* p_ready = s_empty + 2;                 // [2]
+  uint64_t* p_free = p_ready + 2;                  // [2]
+  uint64_t* o_done = p_free + 2;                   // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
   int* s_last = reinterpret_cast<int*>(tmem_slot + 4);
   float* sMax = reinterpret_cast<float*>(tmem_slot + 8);  // [2][4 warps][16 rows]
   float* sSum = sMax + 2 * 4 * kRows;                     // [4][16]
+  float* sLse = sSum + 4 * kRows;                         // [16 splits][16 rows] (merge)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Abort ab{p.status, abort_flag};
@@ -117,8 +127,10 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < num_stages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4); }
-    mbar_init(p_ready, 4);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
+      mbar_init(&p_ready[b], 4); mbar_init(&p_free[b], 1);
+    }
     mbar_init(o_done, 1);
     mbar_fence_init();
     prefetch_tmap(&tmKV);
@@ -132,8 +144,11 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  griddep_wait();
 
+  // Request geometry comes from host-prepared buffers (lengths, block table): it does not depend on the kernel in
+  // front of this one, so it is read - and the tiles that lie wholly in the old context are fetched - BEFORE the
+  // programmatic-dependency wait.  Only q and the cache rows of this step's own tokens (positions >= ctx) are
+  // produced by the preceding kernels.
   const int g = p.Hq / p.Hkv;
   const int kvh = blockIdx.x;
   const int req = blockIdx.y / p.num_splits;
@@ -145,37 +160,28 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   const int kv_end = seq_len;
   int kv_begin = 0;
   if (p.window > 0) kv_begin = max(0, ctx - p.window + 1) / kTileKeys * kTileKeys;
-  const int n_tiles_all = (q_len > 0 && rows_total <= kRows) ? (kv_end - kv_begin + kTileKeys - 1) / kTileKeys : 0;
+  const bool served = q_len > 0 && rows_total <= NR;
+  const int n_tiles_all = served ? (kv_end - kv_begin + kTileKeys - 1) / kTileKeys : 0;
   const int per_split = (n_tiles_all + p.num_splits - 1) / p.num_splits;
   const int tile_lo = split * per_split;
   const int tile_hi = min(n_tiles_all, tile_lo + per_split);
   const int n_tiles = max(0, tile_hi - tile_lo);
 
-  // ---- Q^T operand (all threads): [D/64][16 rows][128 B], 16-byte chunk c of row r at chunk c ^ (r & 7)
-  for (int c = threadIdx.x; c < kRows * (D / 8); c += kThreads) {
-    const int r = c / (D / 8), ch = c % (D / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rows_total && q_len > 0) {
-      const int tok = r / g, hh = r % g;
-      v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
-                                          ((int64_t)(qs + tok) * p.Hq + kvh * g + hh) * D + ch * 8);
-    }
-    const int kb = ch / 8, cc = ch % 8;
-    *reinterpret_cast<uint4*>(sQ + kb * (kRows * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
-  }
-  fence_proxy_async_smem();
-  __syncthreads();
-
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (does not need Q)
     if (elect_one() && n_tiles > 0) {
       const int* bt = p.block_tables + (int64_t)req * p.max_blocks;
-      const int pages_per_block = p.block_size / kPage;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int issued = 0;
+      bool waited = false;
       for (int i = 0; i < n_tiles; ++i) {
+        const bool old_ctx = kv_begin + (tile_lo + i + 1) * kTileKeys <= ctx;  // no key of this step in the tile
+        if (!waited && (i >= num_stages || !old_ctx)) {
+          griddep_wait();
+          waited = true;
+        }
         if (i >= num_stages && !wait_or_abort(&kv_empty[stage], phase ^ 1, ab, 501)) { ok = false; break; }
         mbar_expect_tx(&kv_full[stage], kStageBytes);
         uint8_t* sK = smem + stage * kStageBytes;
@@ -189,7 +195,6 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
           if (blk < 0 || blk >= p.num_blocks) blk = 0;  // masked keys: any initialised page will do
           const int64_t rowK = ((blk * 2) * p.Hkv + kvh) * p.block_size + (key % p.block_size);
           const int64_t rowV = rowK + (int64_t)p.Hkv * p.block_size;
-          (void)pages_per_block;
 #pragma unroll
           for (int h = 0; h < KB; ++h) {
             tma_load_2d(sK + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowK);
@@ -209,7 +214,28 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
+  } else {
+    griddep_wait();  // q (and everything these warps write) depends on the preceding kernels
+    // ---- Q^T operand (warps 1-5): [D/64][16 rows][128 B], 16-byte chunk c of row r at chunk c ^ (r & 7)
+    for (int c = threadIdx.x - 32; c < kRows * (D / 8); c += kThreads - 32) {
+      const int r = c / (D / 8), ch = c % (D / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows_total && served) {
+        const int tok = r / g, hh = r % g;
+        v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
+                                            ((int64_t)(qs + tok) * p.Hq + kvh * g + hh) * D + ch * 8);
+      }
+      const int kb = ch / 8, cc = ch % 8;
+      *reinterpret_cast<uint4*>(sQ + kb * (kRows * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+    }
+    // padded rows of both P buffers stay zero for the whole kernel
+    for (int c = threadIdx.x - 32; c < 2 * kPBytes / 16; c += kThreads - 32)
+      reinterpret_cast<uint4*>(sP)[c] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async_smem();
+    named_bar_sync(2, kThreads - 32);
+  }
+
+  if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one() && n_tiles > 0) {
       const uint32_t fmt = FmtOf<T>::v;
@@ -240,33 +266,43 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       for (int i = 0; ok && i < n_tiles; ++i) {
         if (i + 1 < n_tiles) ok = issue_s(i + 1);
         if (!ok) break;
-        // P.V of tile i once the softmax warps have written P (and rescaled O^T)
-        if (!wait_or_abort(p_ready, i & 1, ab, 504)) { ok = false; break; }
+        // P.V of tile i once the softmax warps have written P[i & 1] (and rescaled O^T if they had to)
+        const int pb = i & 1;
+        if (!wait_or_abort(&p_ready[pb], (i >> 1) & 1, ab, 504)) { ok = false; break; }
         tc_fence_after_sync();
         const int stage = i % num_stages;
         const uint32_t v_addr = smem_u32(smem + stage * kStageBytes + kOpBytes);
 #pragma unroll
         for (int k = 0; k < kTileKeys / 16; ++k) {
           // A: 16 keys (two 8-row groups of 1024 B) x D dims (64-dim blocks kHalfBytes apart)
-          uint64_t da = p.mn_swap ? umma_desc_mn_sw128(v_addr + k * 2048, 1024, kHalfBytes)
-                                  : umma_desc_mn_sw128(v_addr + k * 2048, kHalfBytes, 1024);
-          uint64_t db = umma_desc_k_sw128(p_addr + (k / 4) * (kRows * 128) + (k % 4) * 32);
+          uint64_t da = umma_desc_mn_sw128(v_addr + k * 2048, kHalfBytes, 1024);
+          uint64_t db = umma_desc_k_sw128(p_addr + pb * kPBytes + (k / 4) * (kRows * 128) + (k % 4) * 32);
           umma_f16(tO, da, db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&kv_empty[stage]);
+        umma_commit(&p_free[pb]);
         umma_commit(o_done);
       }
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
     const int quarter = warp & 3;
     const int tid = (warp - 2) * 32 + lane;          // 0..127 (named-barrier group)
     const int lane_id = quarter * 32 + lane;         // TMEM lane: key of the tile / output dim
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem_base + lane_off, tO = tmem_base + 2 * kRows + lane_off;
-    float m_run[kRows], l_part[kRows];
+    float m_used[NR], l_part[NR];
+    int pos[NR];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) { m_run[r] = -INFINITY; l_part[r] = 0.f; }
+    for (int r = 0; r < NR; ++r) {
+      m_used[r] = -INFINITY;
+      l_part[r] = 0.f;
+      pos[r] = (r < rows_total) ? ctx + r / g : -1;  // position of the row's query token (-1: padded row)
+    }
+    const int pos_min = ctx, pos_max = ctx + max(q_len, 1) - 1;
+    // byte offset of this key's column in a P buffer row
+    const int p_off = (lane_id >> 6) * (kRows * 128) + (lane_id & 7) * 2;
+    const int p_ch = (lane_id & 63) >> 3;
     bool ok = true;
     for (int i = 0; i < n_tiles && ok; ++i) {
       const int buf = i & 1;
@@ -281,62 +317,74 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[buf]);
-      // ---- mask + tile max per row
-      const int key = kv_begin + (tile_lo + i) * kTileKeys + lane_id;
-      float sc[kRows];
+      // ---- mask (only on tiles that touch the causal / length / window edge) + tile max per row
+      const int key0 = kv_begin + (tile_lo + i) * kTileKeys;
+      const int key = key0 + lane_id;
+      const bool full = key0 + kTileKeys - 1 <= pos_min && key0 + kTileKeys <= kv_end &&
+                        (p.window <= 0 || key0 > pos_max - p.window);
+      float sc[NR];
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        const int pos = ctx + r / g;  // position of this row's query token
-        const bool in = r < rows_total && key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
-        sc[r] = in ? __uint_as_float(sr[r]) * p.scale_log2 : -INFINITY;
-        const float wm = warp_max_redux(sc[r]);
+      for (int r = 0; r < NR; ++r) {
+        float v = __uint_as_float(sr[r]) * p.scale_log2;
+        if (!full) {
+          const bool in = key < kv_end && key <= pos[r] && (p.window <= 0 || key > pos[r] - p.window);
+          v = in ? v : -INFINITY;
+        } else if (NR > 4 && pos[r] < 0) {
+          v = -INFINITY;
+        }
+        sc[r] = v;
+        const float wm = warp_max_redux(v);
         if (lane == r) sMax[(buf * 4 + quarter) * kRows + r] = wm;
       }
       named_bar_sync(1, 128);
-      float alpha[kRows];
-      bool any_scale = false;
+      float alpha[NR];
+      bool rescale = false;
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
+      for (int r = 0; r < NR; ++r) {
         const float* mm = sMax + buf * 4 * kRows + r;
         const float tm = fmaxf(fmaxf(mm[0], mm[kRows]), fmaxf(mm[2 * kRows], mm[3 * kRows]));
-        const float mn = fmaxf(m_run[r], tm);
-        const float ms = (mn == -INFINITY) ? 0.f : mn;
-        alpha[r] = (r < rows_total) ? exp2f(m_run[r] - ms) : 1.f;  // 0 when nothing has been accumulated yet
-        any_scale |= (alpha[r] != 1.f);
-        m_run[r] = mn;
+        alpha[r] = 1.f;
+        if (tm > m_used[r] + kMaxSlack) {            // also the first finite maximum (m_used = -inf)
+          alpha[r] = exp2f(m_used[r] - tm);          // exp2(-inf) = 0: nothing accumulated yet
+          m_used[r] = tm;
+          rescale = true;
+        }
+        const float ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
         sc[r] = exp2f(sc[r] - ms);
         l_part[r] = l_part[r] * alpha[r] + sc[r];
       }
-      // ---- the previous P.V must have finished before P is overwritten and O^T rescaled
-      if (i > 0) {
-        if (tid == 0) ok_slot[buf] = wait_or_abort(o_done, (i - 1) & 1, ab, 506) ? 1 : 0;
+      // ---- P buffer i & 1 must have been consumed (P.V of tile i - 2); a rescale needs ALL earlier P.V done
+      if (i >= 2) {
+        if (tid == 0) ok_slot[buf] = wait_or_abort(&p_free[buf], ((i >> 1) - 1) & 1, ab, 506) ? 1 : 0;
+        named_bar_sync(1, 128);
+        if (ok_slot[buf] == 0) { ok = false; break; }
+        while (!mbar_try_wait(&p_free[buf], ((i >> 1) - 1) & 1)) {}
+      }
+      if (rescale && i > 0) {  // uniform over the CTA: every thread sees the same maxima
+        if (tid == 0) ok_slot[buf] = wait_or_abort(o_done, (i - 1) & 1, ab, 508) ? 1 : 0;
         named_bar_sync(1, 128);
         if (ok_slot[buf] == 0) { ok = false; break; }
         while (!mbar_try_wait(o_done, (i - 1) & 1)) {}
         tc_fence_after_sync();
-        if (any_scale) {  // uniform over the CTA: alpha is the same in every thread
-          uint32_t orr[kRows];
-          tmem_ld_x16(tO, orr);
-          tmem_ld_wait();
+        uint32_t orr[kRows];
+        tmem_ld_x16(tO, orr);
+        tmem_ld_wait();
 #pragma unroll
-          for (int r = 0; r < kRows; ++r) orr[r] = __float_as_uint(__uint_as_float(orr[r]) * alpha[r]);
-          tmem_st_x16(tO, orr);
-          tmem_st_wait();
-        }
+        for (int r = 0; r < NR; ++r) orr[r] = __float_as_uint(__uint_as_float(orr[r]) * alpha[r]);
+        tmem_st_x16(tO, orr);
+        tmem_st_wait();
       }
-      // ---- P^T (B operand, K-major): element (row r, key k) of 64-key block kb
+      // ---- P^T (B operand, K-major): element (row r, this thread's key)
       {
-        const int kb = lane_id >> 6, kk = lane_id & 63;
-        uint8_t* base = sP + kb * (kRows * 128) + (kk & 7) * 2;
-        const int ch = kk >> 3;
+        uint8_t* base = sP + buf * kPBytes + p_off;
 #pragma unroll
-        for (int r = 0; r < kRows; ++r)
-          *reinterpret_cast<uint16_t*>(base + r * 128 + ((ch ^ (r & 7)) << 4)) = to_bits16<T>(sc[r]);
+        for (int r = 0; r < NR; ++r)
+          *reinterpret_cast<uint16_t*>(base + r * 128 + ((p_ch ^ (r & 7)) << 4)) = to_bits16<T>(sc[r]);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[buf]);
     }
     // ---- epilogue: O^T lane = output dim, 16 columns = query rows
     if (ok && n_tiles > 0) {
@@ -351,14 +399,14 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
     }
     // row sums: every thread holds the part of its own keys
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
+    for (int r = 0; r < NR; ++r) {
       float v = l_part[r];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
       if (lane == r) sSum[quarter * kRows + r] = v;
     }
     named_bar_sync(1, 128);
-    if (ok && q_len > 0 && rows_total <= kRows) {
+    if (ok && served) {
       uint32_t orr[kRows];
       if (n_tiles > 0) {
         tmem_ld_x16(tO, orr);
@@ -369,10 +417,10 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       }
       const int d = lane_id;
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
+      for (int r = 0; r < NR; ++r) {
         if (r >= rows_total) break;
         const float L = sSum[r] + sSum[kRows + r] + sSum[2 * kRows + r] + sSum[3 * kRows + r];
-        const float Ms = (m_run[r] == -INFINITY) ? 0.f : m_run[r];
+        const float Ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
         const int tok = r / g, hh = kvh * g + r % g;
         const int64_t orow = (int64_t)(qs + tok) * p.Hq + hh;
         const float o = __uint_as_float(orr[r]);
@@ -388,7 +436,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
         }
       }
     }
-    if (p.num_splits > 1 && q_len > 0 && rows_total <= kRows) {
+    if (p.num_splits > 1 && served) {
       // ---- split-KV merge by the last CTA of this (request, kv head) to arrive
       __threadfence();
       named_bar_sync(1, 128);
@@ -399,17 +447,41 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
         __threadfence();
         const int d = lane_id;
         const int64_t sstride = p.T * p.Hq;
-        for (int r = 0; r < rows_total; ++r) {
-          const int tok = r / g, hh = kvh * g + r % g;
-          const int64_t orow = (int64_t)(qs + tok) * p.Hq + hh;
+        // all log-sum-exps of this (request, head) in one round of loads: thread t -> (split t / 16, row t % 16)
+        for (int idx = tid; idx < p.num_splits * kRows; idx += 128) {
+          const int s2 = idx / kRows, r = idx % kRows;
+          float v = -INFINITY;
+          if (r < rows_total) {
+            const int64_t orow = (int64_t)(qs + r / g) * p.Hq + kvh * g + r % g;
+            v = __ldcg(p.ws_lse + s2 * sstride + orow);
+          }
+          sLse[idx] = v;
+        }
+        named_bar_sync(1, 128);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          if (r >= rows_total) break;
+          const int hh = kvh * g + r % g;
+          const int64_t orow = (int64_t)(qs + r / g) * p.Hq + hh;
           float M = -INFINITY;
-          for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, __ldcg(p.ws_lse + s2 * sstride + orow));
+          for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, sLse[s2 * kRows + r]);
           const float Ms = (M == -INFINITY) ? 0.f : M;
           float den = 0.f, acc = 0.f;
-          for (int s2 = 0; s2 < p.num_splits; ++s2) {
-            const float wg = exp2f(__ldcg(p.ws_lse + s2 * sstride + orow) - Ms);
-            den += wg;
-            if (wg > 0.f) acc += __ldcg(p.ws_o + (s2 * sstride + orow) * D + d) * wg;
+          int s2 = 0;
+          for (; s2 + 4 <= p.num_splits; s2 += 4) {  // four independent loads in flight
+            float v[4], w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              v[u] = __ldcg(p.ws_o + ((s2 + u) * sstride + orow) * D + d);
+              w[u] = exp2f(sLse[(s2 + u) * kRows + r] - Ms);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { den += w[u]; acc += w[u] > 0.f ? v[u] * w[u] : 0.f; }
+          }
+          for (; s2 < p.num_splits; ++s2) {
+            const float w = exp2f(sLse[s2 * kRows + r] - Ms);
+            den += w;
+            if (w > 0.f) acc += __ldcg(p.ws_o + (s2 * sstride + orow) * D + d) * w;
           }
           if (p.sinks != nullptr) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
           const float inv = den > 0.f ? 1.f / den : 0.f;
@@ -428,19 +500,26 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   }
 }
 
-template <typename T>
-static int launch(const Params& p0, const CUtensorMap& tm, int B, cudaStream_t st) {
+template <typename T, int NR>
+static int launch_nr(const Params& p0, const CUtensorMap& tm, int B, cudaStream_t st) {
   constexpr int D = 128;
-  auto kern = decode_umma_kernel<T, D>;
+  auto kern = decode_umma_kernel<T, D, NR>;
   Params p = p0;
   constexpr int kStageBytes = 2 * (D / 64) * kTileKeys * 128;
   p.num_stages = 3;
-  const size_t smem = 1024 + (size_t)p.num_stages * kStageBytes + (D / 64) * kRows * 128 + 2 * kRows * 128 + 1024;
+  const size_t smem = 1024 + (size_t)p.num_stages * kStageBytes + (D / 64) * kRows * 128 + 2 * 2 * kRows * 128 + 4096;
   {
     cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   return (int)launch_pdl(kern, dim3(p.Hkv, B * p.num_splits), dim3(kThreads), smem, st, tm, p);
+}
+
+template <typename T>
+static int launch(const Params& p, const CUtensorMap& tm, int B, int max_rows, cudaStream_t st) {
+  if (max_rows <= 4) return launch_nr<T, 4>(p, tm, B, st);
+  if (max_rows <= 8) return launch_nr<T, 8>(p, tm, B, st);
+  return launch_nr<T, 16>(p, tm, B, st);
 }
 
 }  // namespace dattn
@@ -457,19 +536,18 @@ extern "C" int b200_decode_attention_umma(void* out, const void* q, const void* 
   using namespace b200;
   if (B == 0 || T_ == 0) return 0;
   if (D != 128 || Hq % Hkv || max_query_len * (Hq / Hkv) > dattn::kRows || block_size % dattn::kPage) return 3;
-  if (num_splits < 1 || (num_splits > 1 && (ws_o == nullptr || (int64_t)B * Hkv > dattn::kMaxTickets))) return 2;
+  if (num_splits < 1 || num_splits > 16 ||
+      (num_splits > 1 && (ws_o == nullptr || (int64_t)B * Hkv > dattn::kMaxTickets)))
+    return 2;
   dattn::Params p;
   p.q = q; p.out = out; p.ws_o = ws_o; p.ws_lse = ws_lse; p.block_tables = block_tables; p.seq_lens = seq_lens;
   p.qsl = qsl; p.sinks = sinks; p.status = status; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size;
   p.max_blocks = max_blocks; p.num_splits = num_splits; p.window = window; p.num_blocks = num_blocks; p.T = T_;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.num_stages = 3;
-  {
-    const char* e = getenv("B200_UMMA_MN_SWAP");
-    p.mn_swap = (e != nullptr && e[0] == '1') ? 1 : 0;
-  }
   const CUtensorMap& tm = *reinterpret_cast<const CUtensorMap*>(tmap);
-  if (dtype == 1) return dattn::launch<__nv_bfloat16>(p, tm, B, st);
-  if (dtype == 2) return dattn::launch<__half>(p, tm, B, st);
+  const int max_rows = max_query_len * (Hq / Hkv);
+  if (dtype == 1) return dattn::launch<__nv_bfloat16>(p, tm, B, max_rows, st);
+  if (dtype == 2) return dattn::launch<__half>(p, tm, B, max_rows, st);
   return 3;
 }

@@ -169,19 +169,10 @@ class B200Platform(_VllmPlatform):
 
 
 def register_models_with_vllm() -> int:
-    """Expose this package's architectures to upstream's ``ModelRegistry`` (general plugin)."""
-    try:
-        from vllm import ModelRegistry
-    except Exception:
-        return 0
-    from ..models import _REGISTRY
-    n = 0
-    for arch, target in _REGISTRY.items():
-        mod, cls = target.split(":")
-        path = f"vllm_kunlun_b200.models.{mod}:{cls}" if "." not in mod else f"{mod}:{cls}"
-        try:
-            ModelRegistry.register_model(arch, path)
-            n += 1
-        except Exception:
-            pass
-    return n
+    """Nothing is registered with upstream's ``ModelRegistry``: under upstream vLLM the UPSTREAM model files run,
+    on this plugin's out-of-tree layers, attention backends and communicator (dense Llama / Qwen models run that way
+    in the reference too, ``vllm_kunlun/models/__init__.py:24-31``).  The model classes of this package belong to
+    its standalone engine - they are not ``vllm`` model classes (no ``VllmConfig`` constructor, no
+    ``IntermediateTensors``), so registering them would replace working upstream entries with classes upstream
+    cannot construct.  Returns the number of registered architectures (0)."""
+    return 0
