@@ -97,7 +97,7 @@ def k_rope(l):
 def k_attn(l):
     from vllm_kunlun_b200.ops.attention_cuda import paged_attention_cuda
     return paged_attention_cuda(o_buf.view(B, hq, D), q_buf, kv[l], block_tables, seq_lens, qsl, scale, 1, a.ctx + 64,
-                                None, None, ws, a.attn_splits or None)
+                                None, None, ws, a.attn_splits or None, stable_metadata=True)
 
 
 def k_o(l):
@@ -116,6 +116,8 @@ def k_down(l):
 CHAINS = {
     "full": [k_norm, k_qkv, k_rope, k_attn, k_o, k_norm, k_gate_up, k_down],
     "gemm4": [k_qkv, k_o, k_gate_up, k_down],
+    "noattn": [k_norm, k_qkv, k_rope, k_o, k_norm, k_gate_up, k_down],
+    "rope_attn": [k_rope, k_attn],
     "qkv": [k_qkv], "o": [k_o], "gate_up": [k_gate_up], "down": [k_down],
     "norm": [k_norm], "rope": [k_rope], "attn": [k_attn],
 }
@@ -125,6 +127,8 @@ BYTES = {
 }
 BYTES["gemm4"] = BYTES["qkv"] + BYTES["o"] + BYTES["gate_up"] + BYTES["down"]
 BYTES["full"] = BYTES["gemm4"] + BYTES["attn"]
+BYTES["noattn"] = BYTES["gemm4"]
+BYTES["rope_attn"] = BYTES["attn"]
 
 
 def time_chain(fns):

@@ -134,7 +134,15 @@ int b200_decode_attention_umma(void* out, const void* q, const void* tmap, const
                                const int* seq_lens, const int* qsl, const float* sinks, float* ws_o, float* ws_lse,
                                int* status, int64_t T, int B, int Hq, int Hkv, int D, int block_size, int max_blocks,
                                int64_t num_blocks, int max_query_len, int num_splits, int window, float scale,
-                               int dtype, cudaStream_t st);
+                               int early_meta, int dtype, cudaStream_t st);
+
+// Dense paged MLA decode on tcgen05 (attention/mla_decode_umma.cu): cache blocks of 64 tokens, at most 32 query
+// tokens per request.  `tmap`: the cache as a 2-D [blocks * 64, 576] 16-bit tensor, 64 x 64 boxes, 128-byte swizzle.
+// early_meta as for b200_decode_attention_umma.  Returns 3 for shapes it does not serve.
+int b200_mla_decode_umma(void* out, const void* q, const void* tmap, const int* block_tables, const int* seq_lens,
+                         const int* qsl, float* ws_o, float* ws_lse, int* status, int64_t T, int B, int N,
+                         int block_size, int max_blocks, int64_t num_blocks, int max_query_len, int num_splits,
+                         float scale, int early_meta, int dtype, cudaStream_t st);
 
 int b200_merge_splits(void* out, const float* ws_o, const float* ws_lse, int64_t rows, int Hq, int D, int splits,
                       int64_t T, int dtype, cudaStream_t st);

@@ -50,6 +50,8 @@ struct Params {
   const float* sinks;
   int* status;
   int Hq, Hkv, block_size, max_blocks, num_splits, window, num_stages;
+  int early_meta;           // lengths / block table were written long before this launch: read them, and fetch
+                            // old-context tiles, before the programmatic-dependency wait
   int64_t num_blocks, T;
   float scale_log2;
 };
@@ -145,10 +147,12 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Request geometry comes from host-prepared buffers (lengths, block table): it does not depend on the kernel in
-  // front of this one, so it is read - and the tiles that lie wholly in the old context are fetched - BEFORE the
-  // programmatic-dependency wait.  Only q and the cache rows of this step's own tokens (positions >= ctx) are
-  // produced by the preceding kernels.
+  // With early_meta the request geometry comes from buffers the host filled before the step started (lengths, block
+  // table): it does not depend on the kernels in front of this one, so it is read - and the tiles that lie wholly in
+  // the old context are fetched - BEFORE the programmatic-dependency wait; only q and the cache rows of this step's
+  // own tokens (positions >= ctx) are produced by the preceding kernels.  Without it (metadata written by a kernel
+  // that may still be draining) everything waits first.
+  if (!p.early_meta) griddep_wait();
   const int g = p.Hq / p.Hkv;
   const int kvh = blockIdx.x;
   const int req = blockIdx.y / p.num_splits;
@@ -532,7 +536,8 @@ extern "C" int b200_decode_attention_umma(void* out, const void* q, const void* 
                                           const int* seq_lens, const int* qsl, const float* sinks, float* ws_o,
                                           float* ws_lse, int* status, int64_t T_, int B, int Hq, int Hkv, int D,
                                           int block_size, int max_blocks, int64_t num_blocks, int max_query_len,
-                                          int num_splits, int window, float scale, int dtype, cudaStream_t st) {
+                                          int num_splits, int window, float scale, int early_meta, int dtype,
+                                          cudaStream_t st) {
   using namespace b200;
   if (B == 0 || T_ == 0) return 0;
   if (D != 128 || Hq % Hkv || max_query_len * (Hq / Hkv) > dattn::kRows || block_size % dattn::kPage) return 3;
@@ -545,6 +550,7 @@ extern "C" int b200_decode_attention_umma(void* out, const void* q, const void* 
   p.max_blocks = max_blocks; p.num_splits = num_splits; p.window = window; p.num_blocks = num_blocks; p.T = T_;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.num_stages = 3;
+  p.early_meta = early_meta;
   const CUtensorMap& tm = *reinterpret_cast<const CUtensorMap*>(tmap);
   const int max_rows = max_query_len * (Hq / Hkv);
   if (dtype == 1) return dattn::launch<__nv_bfloat16>(p, tm, B, max_rows, st);

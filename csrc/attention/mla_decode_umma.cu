@@ -1,0 +1,509 @@
+// Weight-absorbed MLA decode attention over the paged latent cache on tcgen05 + TMEM, fed by TMA.
+//
+//   q   [T, N, 576]        = [q_nope . W_UK (512) | q_pe (64)], a few query tokens per request (decode / MTP verify)
+//   kv  [blocks, 64, 576]  = [kv_c (512) | k_pe (64)] per cached token, 16-bit
+//   out [T, N, 512]        = softmax(q . kv^T * scale) . kv[:, :512]
+//
+// All heads of a token share ONE latent row, so a request's (heads x query tokens) rows are the small side of both
+// products and the cached tokens the large one.  As in decode_umma.cu the operands are swapped so that the tensor
+// core rows are full:
+//     S^T[64 keys, R rows]   = K_page[64 keys, 576] . Q^T                         (36 k-steps, UMMA M = 64)
+//     O^T[512 dims, R rows] += V_page^T[512 dims, 64 keys] . P[64 keys, R rows]    (4 M-tiles of 128 dims x 4 k-steps)
+// with V = the first 512 dims of the SAME shared-memory page (MN-major operand), so a latent row crosses HBM once
+// per CTA, whatever the number of heads or query tokens: a q_len = 2 verify step reads the cache once.
+// TMEM: two S^T buffers (R columns each, lanes (i / 16) * 32 + i % 16 hold key i of an M = 64 accumulator) and four
+// O^T tiles (R columns each): 6 R <= 192 columns.
+//
+// One CTA = (request, group of up to R / q_len heads, kv split).  192 threads: warp 0 TMA producer (one cache page =
+// nine 64 x 64 boxes, 128-byte swizzle, 2-stage ring; pages of the old context are fetched before the
+// programmatic-dependency wait when the caller vouches for the metadata), warp 1 MMA issuer, warps 2-5 softmax
+// (thread = key) and epilogue (thread = output dim).  Lazy running maximum as in decode_umma.cu.  Split partials go
+// through the fp32 workspace; the last CTA of a (request, head group) to arrive merges them.
+// Every wait is bounded; on time-out the status word is set and the CTA unwinds.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "../api.h"
+#include "../common/launch.cuh"
+#include "../common/ptx.cuh"
+#include "../gemm/gemm_common.cuh"
+
+namespace b200 {
+namespace mlad {
+
+constexpr int kThreads = 192;
+constexpr int kKeys = 64;          // keys per tile = one cache page = UMMA M of S^T
+constexpr int kD = 576, kDV = 512;
+constexpr int kBlocks = kD / 64;   // 9 dim blocks of 64
+constexpr int kBlockBytes = kKeys * 128;
+constexpr int kStageBytes = kBlocks * kBlockBytes;  // 72 KB
+constexpr int kStages = 2;
+constexpr int kMaxTickets = 1 << 16;
+static __device__ int g_tickets[kMaxTickets];
+
+struct Params {
+  const void* q;
+  void* out;
+  float* ws_o;              // [splits, T, N, 512]
+  float* ws_lse;            // [splits, T, N]
+  const int* block_tables;
+  const int* seq_lens;
+  const int* qsl;
+  int* status;
+  int N, heads_per_cta, max_blocks, num_splits, early_meta;
+  int64_t num_blocks, T;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ float warp_max_redux(float v) {
+  int i = __float_as_int(v);
+  i = i >= 0 ? i : i ^ 0x7fffffff;
+  i = __reduce_max_sync(0xffffffffu, i);
+  i = i >= 0 ? i : i ^ 0x7fffffff;
+  return __int_as_float(i);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+
+template <typename T> struct FmtOf;
+template <> struct FmtOf<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+template <> struct FmtOf<__half> { static constexpr uint32_t v = 0; };
+template <typename T> __device__ __forceinline__ uint16_t to_bits16(float v);
+template <> __device__ __forceinline__ uint16_t to_bits16<__nv_bfloat16>(float v) {
+  return __bfloat16_as_ushort(__float2bfloat16(v));
+}
+template <> __device__ __forceinline__ uint16_t to_bits16<__half>(float v) { return __half_as_ushort(__float2half(v)); }
+
+// R = UMMA N = rows of the Q^T operand (16 or 32): heads_per_cta * q_len <= R.
+template <typename T, int R>
+__global__ void __launch_bounds__(kThreads)
+mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ Params p) {
+  constexpr int kQBytes = kBlocks * R * 128;   // Q^T operand: [9 dim blocks][R rows][128 B]
+  constexpr int kPBytes = R * 128;             // one P buffer: [R rows][64 keys] 16-bit
+  constexpr int kTmemCols = 256;               // 2 x R (S^T) + 4 x R (O^T) <= 192
+  constexpr float kMaxSlack = 8.f;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + kStages * kStageBytes;
+  uint8_t* sP = sQ + kQBytes;                  // [2][kPBytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
+  uint64_t* kv_full = bars;                    // [2]
+  uint64_t* kv_empty = bars + 2;               // [2]
+  uint64_t* s_full = bars + 4;                 // [2]
+  uint64_t* s_empty = bars + 6;                // [2]
+  uint64_t* p_ready = bars + 8;                // [2]
+  uint64_t* p_free = bars + 10;                // [2]
+  uint64_t* o_done = bars + 12;                // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
+  int* s_last = reinterpret_cast<int*>(tmem_slot + 4);
+  float* sMax = reinterpret_cast<float*>(tmem_slot + 8);   // [2][4 warps][R]
+  float* sSum = sMax + 2 * 4 * R;                          // [4][R]
+  float* sAlpha = sSum + 4 * R;                            // [R]
+  float* sLse = sAlpha + R;                                // [16 splits][R]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  Abort ab{p.status, abort_flag};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&kv_full[b], 1); mbar_init(&kv_empty[b], 1);
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
+      mbar_init(&p_ready[b], 4); mbar_init(&p_free[b], 1);
+    }
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmKV);
+    griddep_launch();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  if (!p.early_meta) griddep_wait();
+
+  const int H = p.heads_per_cta;
+  const int head0 = blockIdx.x * H;
+  const int nh = min(H, p.N - head0);          // heads served by this CTA
+  const int req = blockIdx.y / p.num_splits;
+  const int split = blockIdx.y % p.num_splits;
+  const int qs = p.qsl[req], q_len = p.qsl[req + 1] - qs;
+  const int seq_len = p.seq_lens[req];
+  const int rows_total = q_len * nh;           // row r = token r / nh, head r % nh
+  const int ctx = seq_len - q_len;
+  const int kv_end = seq_len;
+  const bool served = q_len > 0 && rows_total <= R && nh > 0;
+  const int n_tiles_all = served ? (kv_end + kKeys - 1) / kKeys : 0;
+  const int per_split = (n_tiles_all + p.num_splits - 1) / p.num_splits;
+  const int tile_lo = split * per_split;
+  const int tile_hi = min(n_tiles_all, tile_lo + per_split);
+  const int n_tiles = max(0, tile_hi - tile_lo);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && n_tiles > 0) {
+      const int* bt = p.block_tables + (int64_t)req * p.max_blocks;
+      bool ok = true, waited = p.early_meta == 0;
+      int issued = 0;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int stage = i & 1;
+        const int page = tile_lo + i;
+        const bool old_ctx = (page + 1) * kKeys <= ctx;
+        if (!waited && (i >= kStages || !old_ctx)) { griddep_wait(); waited = true; }
+        if (i >= kStages && !wait_or_abort(&kv_empty[stage], ((i >> 1) - 1) & 1, ab, 601)) { ok = false; break; }
+        mbar_expect_tx(&kv_full[stage], kStageBytes);
+        int64_t blk = page < p.max_blocks ? bt[page] : 0;
+        if (blk < 0 || blk >= p.num_blocks) blk = 0;
+        uint8_t* dst = smem + stage * kStageBytes;
+#pragma unroll
+        for (int b = 0; b < kBlocks; ++b)
+          tma_load_2d(dst + b * kBlockBytes, &tmKV, &kv_full[stage], b * 64, (int)(blk * kKeys));
+        ++issued;
+      }
+      if (!ok) {
+        for (int i = max(0, issued - kStages); i < issued; ++i)
+          for (uint32_t q2 = 0; q2 < (1u << 16); ++q2)
+            if (mbar_try_wait(&kv_full[i & 1], (i >> 1) & 1)) break;
+      }
+    }
+  } else {
+    griddep_wait();
+    // ---- Q^T operand (warps 1-5): [9 blocks][R rows][128 B]; 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+    for (int c = threadIdx.x - 32; c < R * (kD / 8); c += kThreads - 32) {
+      const int r = c / (kD / 8), ch = c % (kD / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows_total && served) {
+        const int tok = r / nh, hh = r % nh;
+        v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
+                                            ((int64_t)(qs + tok) * p.N + head0 + hh) * kD + ch * 8);
+      }
+      const int kb = ch / 8, cc = ch % 8;
+      *reinterpret_cast<uint4*>(sQ + kb * (R * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+    }
+    for (int c = threadIdx.x - 32; c < 2 * kPBytes / 16; c += kThreads - 32)
+      reinterpret_cast<uint4*>(sP)[c] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async_smem();
+    named_bar_sync(2, kThreads - 32);
+  }
+
+  if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && n_tiles > 0) {
+      const uint32_t fmt = FmtOf<T>::v;
+      const uint32_t idesc_s = umma_idesc(kKeys, R, fmt, fmt, 0, 0);   // A = K page (K-major), B = Q^T (K-major)
+      const uint32_t idesc_o = umma_idesc(128, R, fmt, fmt, 1, 0);     // A = V page (MN-major), B = P (K-major)
+      const uint32_t tS = tmem_base, tO = tmem_base + 2 * R;
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = true;
+      auto issue_s = [&](int i) {
+        const int stage = i & 1, buf = i & 1;
+        if (!wait_or_abort(&kv_full[stage], (i >> 1) & 1, ab, 602)) return false;
+        if (i >= 2 && !wait_or_abort(&s_empty[buf], ((i >> 1) - 1) & 1, ab, 603)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(smem + stage * kStageBytes);
+#pragma unroll
+        for (int k = 0; k < kD / 16; ++k) {
+          const int kb = k / 4, kk = k % 4;
+          uint64_t da = umma_desc_k_sw128(k_addr + kb * kBlockBytes + kk * 32);
+          uint64_t db = umma_desc_k_sw128(q_addr + kb * (R * 128) + kk * 32);
+          umma_f16(tS + buf * R, da, db, idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[buf]);
+        return true;
+      };
+      ok = issue_s(0);
+      for (int i = 0; ok && i < n_tiles; ++i) {
+        // the next page shares its stage with page i - 1: its S^T can only be issued once that P.V has finished,
+        // which the producer's kv_empty wait already guarantees before it refills the stage
+        if (i + 1 < n_tiles) ok = issue_s(i + 1);
+        if (!ok) break;
+        const int pb = i & 1, stage = i & 1;
+        if (!wait_or_abort(&p_ready[pb], (i >> 1) & 1, ab, 604)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(smem + stage * kStageBytes);
+#pragma unroll
+        for (int j = 0; j < kDV / 128; ++j) {       // O^T tile j: dims [128 j, 128 j + 128) = blocks 2j, 2j + 1
+#pragma unroll
+          for (int k = 0; k < kKeys / 16; ++k) {
+            uint64_t da = umma_desc_mn_sw128(v_addr + (2 * j) * kBlockBytes + k * 2048, kBlockBytes, 1024);
+            uint64_t db = umma_desc_k_sw128(p_addr + pb * kPBytes + k * 32);
+            umma_f16(tO + j * R, da, db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&kv_empty[stage]);
+        umma_commit(&p_free[pb]);
+        umma_commit(o_done);
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    const int tid = (warp - 2) * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off, tO = tmem_base + 2 * R + lane_off;
+    const bool key_thread = lane < 16;               // an M = 64 accumulator uses lanes 0..15 of every quadrant
+    const int key_in_tile = quarter * 16 + lane;     // valid when key_thread
+    float m_used[R], l_part[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) { m_used[r] = -INFINITY; l_part[r] = 0.f; }
+    const int p_off = (key_in_tile & 7) * 2, p_ch = (key_in_tile & 63) >> 3;
+    bool ok = true;
+    for (int i = 0; i < n_tiles && ok; ++i) {
+      const int buf = i & 1;
+      if (tid == 0) ok_slot[buf] = wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 605) ? 1 : 0;
+      named_bar_sync(1, 128);
+      if (ok_slot[buf] == 0) { ok = false; break; }
+      while (!mbar_try_wait(&s_full[buf], (i >> 1) & 1)) {}
+      tc_fence_after_sync();
+      float sc[R];
+#pragma unroll
+      for (int c = 0; c < R; c += 16) {
+        uint32_t sr[16];
+        tmem_ld_x16(tS + buf * R + c, sr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sc[c + j] = __uint_as_float(sr[j]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);
+      const int key0 = (tile_lo + i) * kKeys;
+      const int key = key0 + key_in_tile;
+      const bool full = key0 + kKeys - 1 <= ctx && key0 + kKeys <= kv_end;
+      if (full) {  // every key of the page is visible to every query token: no per-row positions needed
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float v = (key_thread && r < rows_total) ? sc[r] * p.scale_log2 : -INFINITY;
+          sc[r] = v;
+          const float wm = warp_max_redux(v);
+          if (lane == (r & 31)) sMax[(buf * 4 + quarter) * R + r] = wm;
+        }
+      } else {
+        int tok = 0, hh = 0;  // row r = token tok, head hh (walked without divisions)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const bool in = key_thread && r < rows_total && key < kv_end && key <= ctx + tok;
+          const float v = in ? sc[r] * p.scale_log2 : -INFINITY;
+          sc[r] = v;
+          const float wm = warp_max_redux(v);
+          if (lane == (r & 31)) sMax[(buf * 4 + quarter) * R + r] = wm;
+          if (++hh == nh) { hh = 0; ++tok; }
+        }
+      }
+      named_bar_sync(1, 128);
+      bool rescale = false;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float* mm = sMax + buf * 4 * R + r;
+        const float tm = fmaxf(fmaxf(mm[0], mm[R]), fmaxf(mm[2 * R], mm[3 * R]));
+        float alpha = 1.f;
+        if (tm > m_used[r] + kMaxSlack) {
+          alpha = exp2f(m_used[r] - tm);
+          m_used[r] = tm;
+          rescale = true;
+        }
+        if (tid == 0) sAlpha[r] = alpha;
+        const float ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
+        sc[r] = exp2f(sc[r] - ms);
+        l_part[r] = l_part[r] * alpha + sc[r];
+      }
+      if (i >= 2) {
+        if (tid == 0) ok_slot[buf] = wait_or_abort(&p_free[buf], ((i >> 1) - 1) & 1, ab, 606) ? 1 : 0;
+        named_bar_sync(1, 128);
+        if (ok_slot[buf] == 0) { ok = false; break; }
+        while (!mbar_try_wait(&p_free[buf], ((i >> 1) - 1) & 1)) {}
+      }
+      if (rescale && i > 0) {
+        if (tid == 0) ok_slot[buf] = wait_or_abort(o_done, (i - 1) & 1, ab, 608) ? 1 : 0;
+        named_bar_sync(1, 128);   // also publishes sAlpha
+        if (ok_slot[buf] == 0) { ok = false; break; }
+        while (!mbar_try_wait(o_done, (i - 1) & 1)) {}
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int j = 0; j < kDV / 128; ++j) {
+#pragma unroll
+          for (int c = 0; c < R; c += 16) {
+            uint32_t orr[16];
+            tmem_ld_x16(tO + j * R + c, orr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * sAlpha[c + e]);
+            tmem_st_x16(tO + j * R + c, orr);
+          }
+        }
+        tmem_st_wait();
+      }
+      if (key_thread) {
+        uint8_t* base = sP + buf * kPBytes + p_off;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          *reinterpret_cast<uint16_t*>(base + r * 128 + ((p_ch ^ (r & 7)) << 4)) = to_bits16<T>(sc[r]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[buf]);
+    }
+    if (ok && n_tiles > 0) {
+      const int last = n_tiles - 1;
+      if (tid == 0) ok_slot[0] = wait_or_abort(o_done, last & 1, ab, 607) ? 1 : 0;
+      named_bar_sync(1, 128);
+      ok = ok_slot[0] != 0;
+      if (ok) {
+        while (!mbar_try_wait(o_done, last & 1)) {}
+        tc_fence_after_sync();
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float v = l_part[r];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == (r & 31)) sSum[quarter * R + r] = v;
+    }
+    named_bar_sync(1, 128);
+    const int d = quarter * 32 + lane;               // output dim within an O^T tile (M = 128: lane = row)
+    if (ok && served) {
+#pragma unroll 1
+      for (int j = 0; j < kDV / 128; ++j) {
+#pragma unroll
+        for (int c = 0; c < R; c += 16) {
+          uint32_t orr[16];
+          if (n_tiles > 0) {
+            tmem_ld_x16(tO + j * R + c, orr);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) orr[e] = 0;
+          }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int r = c + e;
+            if (r < rows_total) {
+              const float L = sSum[r] + sSum[R + r] + sSum[2 * R + r] + sSum[3 * R + r];
+              const int tok = r / nh, hh = head0 + r % nh;
+              const int64_t orow = (int64_t)(qs + tok) * p.N + hh;
+              const float inv = L > 0.f ? 1.f / L : 0.f;
+              const float o = __uint_as_float(orr[e]) * inv;
+              if (p.num_splits == 1) {
+                reinterpret_cast<T*>(p.out)[orow * kDV + j * 128 + d] = from_float<T>(o);
+              } else {
+                p.ws_o[((int64_t)split * p.T * p.N + orow) * kDV + j * 128 + d] = o;
+                if (j == 0 && d == 0) {
+                  const float Ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
+                  p.ws_lse[(int64_t)split * p.T * p.N + orow] = (L > 0.f) ? Ms + log2f(L) : -INFINITY;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+    if (p.num_splits > 1 && served) {
+      __threadfence();
+      named_bar_sync(1, 128);
+      const int ticket_idx = req * gridDim.x + blockIdx.x;
+      if (tid == 0) *s_last = (atomicAdd(&g_tickets[ticket_idx], 1) == p.num_splits - 1);
+      named_bar_sync(1, 128);
+      if (*s_last) {
+        __threadfence();
+        const int64_t sstride = p.T * p.N;
+        for (int idx = tid; idx < p.num_splits * R; idx += 128) {
+          const int s2 = idx / R, r = idx % R;
+          float v = -INFINITY;
+          if (r < rows_total) {
+            const int64_t orow = (int64_t)(qs + r / nh) * p.N + head0 + r % nh;
+            v = __ldcg(p.ws_lse + s2 * sstride + orow);
+          }
+          sLse[idx] = v;
+        }
+        named_bar_sync(1, 128);
+        for (int r = 0; r < rows_total; ++r) {
+          const int64_t orow = (int64_t)(qs + r / nh) * p.N + head0 + r % nh;
+          float M = -INFINITY;
+          for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, sLse[s2 * R + r]);
+          const float Ms = (M == -INFINITY) ? 0.f : M;
+          float den = 0.f, acc[kDV / 128] = {0.f, 0.f, 0.f, 0.f};
+          for (int s2 = 0; s2 < p.num_splits; ++s2) {
+            const float w = exp2f(sLse[s2 * R + r] - Ms);
+            den += w;
+            if (w > 0.f) {
+              const float* src = p.ws_o + (s2 * sstride + orow) * kDV + d;
+#pragma unroll
+              for (int j = 0; j < kDV / 128; ++j) acc[j] += __ldcg(src + j * 128) * w;
+            }
+          }
+          const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+          for (int j = 0; j < kDV / 128; ++j)
+            reinterpret_cast<T*>(p.out)[orow * kDV + j * 128 + d] = from_float<T>(acc[j] * inv);
+        }
+        if (tid == 0) g_tickets[ticket_idx] = 0;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T, int R>
+static int launch_r(const Params& p, const CUtensorMap& tm, int B, int head_groups, cudaStream_t st) {
+  auto kern = mla_decode_umma_kernel<T, R>;
+  const size_t smem = 1024 + (size_t)kStages * kStageBytes + kBlocks * R * 128 + 2 * R * 128 + 4096 + 16 * R * 4;
+  {
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)launch_pdl(kern, dim3(head_groups, B * p.num_splits), dim3(kThreads), smem, st, tm, p);
+}
+
+}  // namespace mlad
+}  // namespace b200
+
+// Dense paged MLA decode on tcgen05 (see the header of this file).  `tmap`: the cache as a 2-D [blocks * 64, 576]
+// 16-bit tensor with 64 x 64 boxes and 128-byte swizzle.  Serves block_size 64 and max_query_len <= 32; heads are
+// processed in groups of R / max_query_len (R = 16 or 32).  Returns 3 for shapes it does not serve.
+extern "C" int b200_mla_decode_umma(void* out, const void* q, const void* tmap, const int* block_tables,
+                                    const int* seq_lens, const int* qsl, float* ws_o, float* ws_lse, int* status,
+                                    int64_t T_, int B, int N, int block_size, int max_blocks, int64_t num_blocks,
+                                    int max_query_len, int num_splits, float scale, int early_meta, int dtype,
+                                    cudaStream_t st) {
+  using namespace b200;
+  if (B == 0 || T_ == 0) return 0;
+  if (block_size != mlad::kKeys || max_query_len < 1 || max_query_len > 32 || num_splits < 1 || num_splits > 16) return 3;
+  const int R = (N * max_query_len <= 16) ? 16 : 32;
+  const int H = R / max_query_len;  // heads per CTA
+  if (H < 1) return 3;
+  const int groups = (N + H - 1) / H;
+  if (num_splits > 1 && (ws_o == nullptr || (int64_t)B * groups > mlad::kMaxTickets)) return 2;
+  mlad::Params p;
+  p.q = q; p.out = out; p.ws_o = ws_o; p.ws_lse = ws_lse; p.block_tables = block_tables; p.seq_lens = seq_lens;
+  p.qsl = qsl; p.status = status; p.N = N; p.heads_per_cta = H; p.max_blocks = max_blocks; p.num_splits = num_splits;
+  p.early_meta = early_meta; p.num_blocks = num_blocks; p.T = T_;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const CUtensorMap& tm = *reinterpret_cast<const CUtensorMap*>(tmap);
+  if (dtype == 1) return R == 16 ? mlad::launch_r<__nv_bfloat16, 16>(p, tm, B, groups, st)
+                                 : mlad::launch_r<__nv_bfloat16, 32>(p, tm, B, groups, st);
+  if (dtype == 2) return R == 16 ? mlad::launch_r<__half, 16>(p, tm, B, groups, st)
+                                 : mlad::launch_r<__half, 32>(p, tm, B, groups, st);
+  return 3;
+}

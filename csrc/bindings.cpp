@@ -621,7 +621,8 @@ void paged_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_c
 void decode_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_cache, const at::Tensor& block_tables,
                            const at::Tensor& seq_lens, const at::Tensor& qsl, const c10::optional<at::Tensor>& sinks,
                            const c10::optional<at::Tensor>& ws_o, const c10::optional<at::Tensor>& ws_lse,
-                           int64_t max_query_len, int64_t num_splits, int64_t window, double scale) {
+                           int64_t max_query_len, int64_t num_splits, int64_t window, double scale,
+                           bool early_meta) {
   TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && kv_cache.is_contiguous() && q.dim() == 3 && kv_cache.dim() == 5);
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
   TORCH_CHECK(block_tables.stride(1) == 1 && q.scalar_type() == kv_cache.scalar_type());
@@ -645,8 +646,38 @@ void decode_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor
                                    ws_o.has_value() ? ws_o->data_ptr<float>() : nullptr,
                                    ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, gs.status.data_ptr<int>(),
                                    q.size(0), B, q.size(1), kv_cache.size(2), D, kv_cache.size(3), block_tables.stride(0),
-                                   kv_cache.size(0), max_query_len, num_splits, window, (float)scale, dtype_code(q),
-                                   stream()), "decode_attention_umma");
+                                   kv_cache.size(0), max_query_len, num_splits, window, (float)scale,
+                                   early_meta ? 1 : 0, dtype_code(q), stream()), "decode_attention_umma");
+}
+
+// Dense paged MLA decode on tcgen05: q [T, N, 576], kv [blocks, 64, 576] -> out [T, N, 512].
+void mla_decode_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, const at::Tensor& block_tables,
+                     const at::Tensor& seq_lens, const at::Tensor& qsl, const c10::optional<at::Tensor>& ws_o,
+                     const c10::optional<at::Tensor>& ws_lse, int64_t max_query_len, int64_t num_splits, double scale,
+                     bool early_meta) {
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && kv.is_contiguous() && q.dim() == 3 && kv.dim() == 3);
+  TORCH_CHECK(q.size(2) == 576 && kv.size(2) == 576 && out.size(2) == 512 && q.scalar_type() == kv.scalar_type());
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
+  TORCH_CHECK(block_tables.stride(1) == 1);
+  if (num_splits > 1) TORCH_CHECK(ws_o.has_value() && ws_lse.has_value());
+  c10::cuda::CUDAGuard guard(q.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, q.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, q.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, q.options().dtype(at::kInt));
+  }
+  at::Tensor flat = kv.view({-1, 576});
+  const Tmap& tm = get_tmap(gs, flat, 64, 2);
+  int B = seq_lens.size(0);
+  check(b200_mla_decode_umma(out.data_ptr(), q.data_ptr(), tm.b, block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(),
+                             qsl.data_ptr<int>(), ws_o.has_value() ? ws_o->data_ptr<float>() : nullptr,
+                             ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, gs.status.data_ptr<int>(),
+                             q.size(0), B, q.size(1), kv.size(1), block_tables.stride(0), kv.size(0), max_query_len,
+                             num_splits, (float)scale, early_meta ? 1 : 0, dtype_code(q), stream()),
+        "mla_decode_umma");
 }
 
 // q [T, N, 576], kv [blocks, bs, 576] -> out [T, N, 512]; dense (block tables) or sparse (indices [T, topk])
@@ -1007,6 +1038,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("merge_attn_states", &merge_attn_states);
   m.def("paged_attention", &paged_attention);
   m.def("decode_attention_umma", &decode_attention_umma);
+  m.def("mla_decode_umma", &mla_decode_umma);
   m.def("mla_attention", &mla_attention);
   m.def("indexer_logits", &indexer_logits);
   m.def("topk_rows", &topk_rows);

@@ -112,3 +112,46 @@ def test_gpt_oss_checkpoint_layout():
     assert torch.equal(m.layers["1"].self_attn.sinks.data, sinks)
     assert torch.equal(m.layers["1"].mlp.gate.weight.data, router)
     assert len(llm.generate([list(range(3, 40))], SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids) == 4
+
+
+def test_gemma_per_layer_inputs_and_multimodal():
+    """Per-layer inputs change the output and follow the reference arithmetic; the multimodal wrapper replaces
+    placeholder rows after the embedding scale and survives chunked prefill."""
+    cfg = _gemma()
+    cfg.num_kv_shared_layers = 0
+    cfg.per_layer_input_size, cfg.per_layer_vocab_size = 8, 100
+    llm = LLM(cfg, max_num_batched_tokens=64, **KW)
+    m = llm.engine.runner.model
+    L, P, H = cfg.num_layers, 8, cfg.hidden_size
+    assert m.embed_tokens_per_layer.weight.shape == (128, L * P)  # vocab padded to 64-row shards
+    assert all(float(layer.layer_scalar) == 1.0 for layer in m.layers.values())
+    ids = torch.tensor([3, 99, 120, 7])           # 120 is outside the per-layer vocabulary: looks up row 0
+    emb = torch.randn(4, H, generator=torch.Generator().manual_seed(0))
+    ple = m.per_layer_inputs(ids, emb)
+    assert ple.shape == (4, L, P)
+    tok = m.embed_tokens_per_layer.weight[torch.tensor([3, 99, 0, 7])].view(4, L, P) * P ** 0.5
+    proj = (emb @ m.per_layer_model_projection.weight.T * H ** -0.5).view(4, L, P)
+    w = m.per_layer_projection_norm.weight
+    proj = proj * torch.rsqrt(proj.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * (1 + w)
+    torch.testing.assert_close(ple, (proj + tok) * 2 ** -0.5, atol=1e-5, rtol=1e-4)
+    prompts = [list(range(3, 30))]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    a = llm.generate(prompts, sp)[0].token_ids
+    assert a == LLM(cfg, max_num_batched_tokens=8, **KW).generate(prompts, sp)[0].token_ids
+    plain = _gemma()
+    plain.num_kv_shared_layers = 0
+    assert LLM(plain, max_num_batched_tokens=64, **KW).engine.runner.model.ple == 0
+    # multimodal wrapper
+    IMG = 127
+    cfg.architecture = "Gemma4ForConditionalGeneration"
+    cfg.vision = dict(depth=2, hidden=32, heads=2, patch=2, intermediate=64, in_channels=3, image_size=8, pool=2,
+                      image_token_id=IMG)
+    vl = LLM(cfg, max_num_batched_tokens=64, **KW)
+    tower = vl.engine.runner.model.visual
+    assert tower.tokens_per_image == 4
+    px = torch.randn(1, 16, 12, generator=torch.Generator().manual_seed(1))
+    assert vl.engine.runner.model.embed_multimodal(px).shape == (4, H)
+    prompt = [5, 6] + [IMG] * 4 + [9, 10, 11]
+    o1 = vl.generate([prompt], sp, multi_modal_data={"pixel_values": px})[0].token_ids
+    o2 = LLM(cfg, max_num_batched_tokens=4, **KW).generate([prompt], sp, multi_modal_data={"pixel_values": px})[0].token_ids
+    assert o1 == o2 and len(o1) == 5

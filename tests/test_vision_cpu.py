@@ -79,3 +79,79 @@ def test_internvl_tower_and_generation():
     prompt = [5] + [IMG] * 8 + [9, 10]
     out = llm.generate([prompt], SamplingParams(max_tokens=4, ignore_eos=True), multi_modal_data={"pixel_values": px})
     assert len(out[0].token_ids) == 4
+
+
+def _qwen3_vl_moe(arch="Qwen3VLMoeForConditionalGeneration"):
+    from vllm_kunlun_b200.config import qwen3_30b_a3b
+    cfg = tiny(qwen3_30b_a3b(fp8=False), num_layers=3, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1,
+               head_dim=32, intermediate_size=128, moe_intermediate_size=32, num_experts=4, num_experts_per_tok=2,
+               max_position=512, dtype="float32")
+    cfg.architecture = arch
+    cfg.vision = dict(depth=3, hidden=32, heads=2, patch=2, temporal_patch=1, merge=2, intermediate=64, in_channels=3,
+                      norm="layernorm", image_token_id=IMG, audio_token_id=126, deepstack_indexes=[0, 1],
+                      audio=dict(hidden=32, heads=2, intermediate=64, depth=2, n_mels=8, stride=4))
+    cfg.mrope_section = (4, 6, 6)
+    return cfg
+
+
+def test_qwen3_vl_moe_deepstack_reaches_the_decoder():
+    """Qwen3-VL-MoE: MoE decoder + tower whose intermediate (deep-stack) features are added after the first decoder
+    layers; zeroing the deep-stack mergers must change the output, and chunked prefill must not."""
+    cfg = _qwen3_vl_moe()
+    grid = [(1, 8, 4)]
+    px = torch.randn(32, 3 * 1 * 2 * 2, generator=torch.Generator().manual_seed(0))
+    prompt = [5, 6, 7] + [IMG] * 8 + [9, 10, 11, 12]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    mm = {"pixel_values": px, "image_grid_thw": grid}
+    llm = LLM(cfg, max_num_batched_tokens=64, **kw)
+    model = llm.engine.runner.model
+    assert type(model.language_model).__name__ == "MoEForCausalLM" and model.num_deepstack == 2
+    emb = model.embed_multimodal(px, grid)
+    assert emb.shape == (8, 3 * cfg.hidden_size)  # main + two deep-stack features per merged token
+    a = llm.generate([prompt], sp, multi_modal_data=mm)[0].token_ids
+    b = LLM(cfg, max_num_batched_tokens=8, **kw).generate([prompt], sp, multi_modal_data=mm)[0].token_ids
+    assert a == b
+
+    def last_hidden():
+        from vllm_kunlun_b200.attention.metadata import ForwardContext, set_forward_context
+        eng = llm.engine
+        eng.add_request(prompt, SamplingParams(max_tokens=1), multi_modal_data=mm)
+        sched = eng.scheduler.schedule()
+        md, ids, _ = eng.runner.prepare(sched)
+        ctx = ForwardContext(md, eng.runner.kv_caches, eng.pstate, extras=eng.runner._step_extras)
+        with torch.inference_mode(), set_forward_context(ctx):
+            h, _ = eng.runner.model(ids)
+        eng.run_until_done()
+        return h[-1].float().clone()
+    h1 = last_hidden()
+    for m in model.visual.ds_fc2:
+        m.weight.data.zero_()
+        m.bias.data.zero_()
+    h2 = last_hidden()
+    assert (h1 - h2).abs().max() > 1e-5
+
+
+def test_qwen3_omni_thinker_takes_audio_and_images():
+    cfg = _qwen3_vl_moe("Qwen3OmniMoeForConditionalGeneration")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    model = llm.engine.runner.model
+    g = torch.Generator().manual_seed(2)
+    feats = torch.randn(10 + 7, 8, generator=g)          # two clips of 10 and 7 frames -> 3 + 2 audio tokens (stride 4)
+    assert model.audio_tower.output_lengths([10, 7]) == [3, 2]
+    px = torch.randn(16, 3 * 1 * 2 * 2, generator=g)      # one 4x4-patch image -> 4 merged tokens
+    AUD = 126
+    prompt = [5] + [AUD] * 3 + [6] + [IMG] * 4 + [7] + [AUD] * 2 + [8, 9]
+    mm = {"pixel_values": px, "image_grid_thw": [(1, 4, 4)], "input_features": feats, "feature_lens": [10, 7]}
+    sp = SamplingParams(max_tokens=4, ignore_eos=True)
+    out = llm.generate([prompt], sp, multi_modal_data=mm)[0]
+    assert len(out.token_ids) == 4
+    # the audio content reaches the output: other features, other continuation logits
+    emb, rows, pos, delta = model.encode_multimodal_data(prompt, mm)
+    assert rows == [1, 2, 3, 5, 6, 7, 8, 10, 11] and emb.shape == (9, 3 * cfg.hidden_size)
+    emb2, _, _, _ = model.encode_multimodal_data(prompt, dict(mm, input_features=feats * -2.0))
+    assert (emb[:3] - emb2[:3]).abs().max() > 1e-5 and torch.equal(emb[3:7], emb2[3:7])
+    # audio only
+    out = llm.generate([[5] + [AUD] * 3 + [6, 7]], sp,
+                       multi_modal_data={"input_features": feats[:10], "feature_lens": [10]})[0]
+    assert len(out.token_ids) == 4

@@ -104,6 +104,9 @@ class ModelConfig:
     num_kv_shared_layers: int = 0  # Gemma: trailing layers that reuse an earlier layer's KV cache
     attn_scale: Optional[float] = None  # softmax scale override (Gemma query_pre_attn_scalar)
     final_logit_softcapping: float = 0.0
+    # Gemma per-layer inputs ("PLE"): width of the per-layer embedding and the vocabulary it is looked up in
+    per_layer_input_size: int = 0
+    per_layer_vocab_size: int = 0
     attn_output_gate: bool = False  # q_proj carries a sigmoid output gate (Qwen3-Next full-attention layers)
     # quantization of the checkpoint
     quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq"
@@ -281,13 +284,17 @@ class ModelConfig:
                 act="gelu" if intern else "quick_gelu", layer_scale=intern, image_size=vcfg.get("image_size", 448),
                 downsample=cfg.get("downsample_ratio", 0.5), image_token_id=cfg.get("image_token_id", 151655),
                 text_architecture=(tc.get("architectures") or ["Qwen2ForCausalLM"])[0] if intern else
-                ("Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"))
+                ("Qwen3MoeForCausalLM" if ("Qwen3" in arch and "Moe" in arch) else
+                 "Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"),
+                deepstack_indexes=list(vcfg.get("deepstack_visual_indexes", ())))
             rsc = tc.get("rope_scaling") or {}
             kw["mrope_section"] = tuple(rsc.get("mrope_section", ()))
         if arch.startswith("Gemma"):
             kw.update(num_kv_shared_layers=cfg.get("num_kv_shared_layers", 0) or 0,
                       final_logit_softcapping=float(cfg.get("final_logit_softcapping") or 0.0),
-                      attn_scale=(float(cfg["query_pre_attn_scalar"]) ** -0.5 if cfg.get("query_pre_attn_scalar") else None))
+                      attn_scale=(float(cfg["query_pre_attn_scalar"]) ** -0.5 if cfg.get("query_pre_attn_scalar") else None),
+                      per_layer_input_size=int(cfg.get("hidden_size_per_layer_input") or 0),
+                      per_layer_vocab_size=int(cfg.get("vocab_size_per_layer_input") or cfg.get("vocab_size") or 0))
             kw.update(gemma_norm=True, hidden_act="gelu_tanh", qk_norm=True,
                       sliding_window=cfg.get("sliding_window"), sliding_window_pattern=cfg.get("sliding_window_pattern", 6),
                       tie_word_embeddings=True)

@@ -206,6 +206,10 @@ class ModelRunner:
     def encode_multimodal(self, prompt_token_ids, data: dict) -> dict:
         """Run the vision tower for one request and work out which prompt rows its embeddings replace."""
         assert self.is_vl, "the loaded model has no vision tower"
+        if hasattr(self.model, "encode_multimodal_data"):  # several modalities: the model sorts out its placeholders
+            embeds, rows, pos3, delta = self.model.encode_multimodal_data(prompt_token_ids, data)
+            return {"embeds": embeds, "rows": np.asarray(rows, dtype=np.int64),
+                    "pos3": None if pos3 is None else pos3.numpy(), "delta": int(delta)}
         grid = data.get("image_grid_thw")
         grid = [tuple(int(x) for x in g) for g in (grid.tolist() if hasattr(grid, "tolist") else grid)] if grid is not None else None
         embeds = self.model.embed_multimodal(data["pixel_values"], grid)

@@ -38,10 +38,14 @@ _REGISTRY = {
     "MiMoV2FlashForCausalLM": "mimo_v2_flash:MiMoV2FlashForCausalLM",
     # Gemma family
     "Gemma4ForCausalLM": "gemma4:Gemma4ForCausalLM",
+    "Gemma4ForConditionalGeneration": "vision:Gemma4ForConditionalGeneration",
     # vision-language wrappers (ViT tower + a registered text decoder)
     "Qwen2VLForConditionalGeneration": "vision:QwenVLForConditionalGeneration",
     "Qwen2_5_VLForConditionalGeneration": "vision:QwenVLForConditionalGeneration",
     "Qwen3VLForConditionalGeneration": "vision:QwenVLForConditionalGeneration",
+    "Qwen3VLMoeForConditionalGeneration": "vision:Qwen3VLMoeForConditionalGeneration",
+    "Qwen3OmniMoeForConditionalGeneration": "omni:Qwen3OmniMoeThinker",
+    "Qwen3OmniMoeThinkerForConditionalGeneration": "omni:Qwen3OmniMoeThinker",
     "InternVLChatModel": "vision:InternVLChatModel",
     "InternS1ForConditionalGeneration": "vision:InternVLChatModel",
 }

@@ -147,7 +147,7 @@ class MLAAttention(nn.Module):
         else:
             o = ops.mla_attention(qf.contiguous(), kv_cache, md.block_tables, md.seq_lens, md.query_start_loc,
                                   self.scale, self.rank, md.max_query_len, md.max_seq_len, md.seq_lens_cpu,
-                                  md.query_start_loc_cpu, md.workspace)
+                                  md.query_start_loc_cpu, md.workspace, stable_metadata=True)
         v = ops.bmm_heads(o, self.w_uv)  # [T, N, vdim]
         return self.o_proj(v.reshape(T, self.num_heads * self.vdim))
 

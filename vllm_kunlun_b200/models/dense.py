@@ -86,7 +86,8 @@ class GQAAttention(nn.Module):
             md.query_start_loc, self.scale, md.max_query_len, md.max_seq_len, self.window, self.sinks,
             md.seq_lens_cpu, md.query_start_loc_cpu, workspace=md.workspace,
             num_decodes=md.num_decodes, decode_query_len=1 + md.num_spec_tokens,
-            num_decode_tokens=md.num_decode_tokens)
+            num_decode_tokens=md.num_decode_tokens,
+            stable_metadata=True)  # the runner fills lengths / block tables by host copies before the step
         return self.o_proj(o.reshape(T, self.num_heads * self.head_dim))
 
 
@@ -172,6 +173,7 @@ class DenseForCausalLM(nn.Module):
     passes ``(hidden, residual)`` on, ``models/deepseek_v2.py:1102-1158``)."""
 
     layer_cls = DenseDecoderLayer
+    post_layer_hook = None  # callable(layer_idx, hidden, residual): lets a wrapper touch the stream between layers
     aux_hidden_state_layers: tuple = ()  # EAGLE-3 target interface (``models/interfaces.py`` of the reference)
     aux_hidden = None
 
@@ -213,6 +215,8 @@ class DenseForCausalLM(nn.Module):
                 aux += [self._complete(hidden, residual, partial)] * self.aux_hidden_state_layers.count(i)
             hidden, residual = self.layers[str(i)](hidden, residual, partial)
             partial = True
+            if self.post_layer_hook is not None:
+                self.post_layer_hook(i, hidden, residual)
         self.aux_hidden = torch.cat(aux, -1) if aux else None
         if self.norm is None:
             st = get_state()
@@ -251,7 +255,9 @@ class DenseForCausalLM(nn.Module):
         for name, p in self.named_parameters():
             if p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
                 continue
-            if name.endswith("norm.weight") or "layernorm.weight" in name:
+            if name.endswith("layer_scalar"):
+                p.data.fill_(1.0)
+            elif name.endswith("norm.weight") or "layernorm.weight" in name:
                 p.data.fill_(0.0 if self.cfg.gemma_norm else 1.0)
             else:
                 gen = g_rep if name in replicated else g

@@ -17,7 +17,7 @@ from ..attention.metadata import get_forward_context
 from ..config import ModelConfig
 from ..parallel.state import get_state
 from .dense import GatedMLP, GQAAttention
-from .layers import RMSNorm, reduce_add_rmsnorm
+from .layers import ReplicatedLinear, RMSNorm, VocabParallelEmbedding, param, reduce_add_rmsnorm
 from .moe import MoEForCausalLM, SparseMoEBlock
 
 
@@ -73,6 +73,21 @@ class Gemma4DecoderLayer(nn.Module):
         else:
             self.mlp = GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization, cfg.hidden_act,
                                 cfg.mlp_bias, reduce_results=False)
+        # per-layer inputs (reference gemma4.py:553-581,632-640): a gate from the stream selects from this layer's
+        # slice of the per-token embedding, which is projected back, normed and added; then the layer scalar
+        self.ple = cfg.per_layer_input_size
+        if self.ple:
+            self.per_layer_input_gate = ReplicatedLinear(cfg.hidden_size, self.ple, dtype=dtype, device=device)
+            self.per_layer_projection = ReplicatedLinear(self.ple, cfg.hidden_size, dtype=dtype, device=device)
+            self.post_per_layer_input_norm = norm()
+            self.layer_scalar = param(1, dtype=dtype, device=device)
+
+    def add_per_layer_input(self, m, residual, per_layer_input):
+        """``per_layer_input [T, ple]``: returns the complete stream (no residual left over)."""
+        h = m + residual
+        gate = torch.nn.functional.gelu(self.per_layer_input_gate(h).float(), approximate="tanh").to(h.dtype)
+        h = h + self.post_per_layer_input_norm(self.per_layer_projection(gate * per_layer_input))
+        return h * self.layer_scalar
 
     def forward(self, hidden, residual, partial: bool = False):
         """``hidden`` is the complete (already reduced and post-normed) output of the previous layer."""
@@ -95,15 +110,45 @@ class Gemma4ForCausalLM(MoEForCausalLM):
     def __init__(self, cfg: ModelConfig, device="cpu", dtype=None):
         super().__init__(cfg, device, dtype)
         self.embed_scale = cfg.hidden_size ** 0.5
+        self.ple = cfg.per_layer_input_size
+        if self.ple:
+            assert get_state().pp_size == 1, "per-layer inputs are computed from the embeddings on the first stage"
+            L = cfg.num_layers
+            self.embed_tokens_per_layer = VocabParallelEmbedding(cfg.per_layer_vocab_size or cfg.vocab_size, L * self.ple,
+                                                                 self.dtype, device)
+            self.per_layer_model_projection = ReplicatedLinear(cfg.hidden_size, L * self.ple, dtype=self.dtype,
+                                                               device=device)
+            self.per_layer_projection_norm = RMSNorm(self.ple, cfg.rms_norm_eps, self.dtype, device, cfg.gemma_norm)
+
+    def per_layer_inputs(self, input_ids, embeds):
+        """``[T, L, ple]``: (norm(proj(embeds) / sqrt(hidden)) + per-layer token embedding * sqrt(ple)) / sqrt(2);
+        tokens outside the per-layer vocabulary (multimodal placeholders) look up row 0 (reference
+        ``gemma4.py:725-775``)."""
+        L, P = self.cfg.num_layers, self.ple
+        V = self.cfg.per_layer_vocab_size or self.cfg.vocab_size
+        ids = torch.where((input_ids >= 0) & (input_ids < V), input_ids, torch.zeros_like(input_ids))
+        tok = self.embed_tokens_per_layer(ids).view(-1, L, P) * (P ** 0.5)
+        proj = (self.per_layer_model_projection(embeds) * (self.cfg.hidden_size ** -0.5)).view(-1, L, P)
+        proj = self.per_layer_projection_norm(proj.reshape(-1, P)).view(-1, L, P)
+        return (proj + tok.to(proj.dtype)) * (2.0 ** -0.5)
 
     def forward(self, input_ids, hidden=None, residual=None):
         if hidden is None:
             hidden = self.embed_tokens(input_ids)
             hidden = hidden * torch.tensor(self.embed_scale, dtype=hidden.dtype, device=hidden.device)
+            hook = getattr(self, "input_embeds_hook", None)
+            if hook is not None:  # multimodal wrapper: image rows replace the placeholder embeddings
+                hidden = hook(hidden)
+        ple = self.per_layer_inputs(input_ids, hidden) if self.ple else None
         for i in range(self.first_layer, self.last_layer):
-            hidden, residual = self.layers[str(i)](hidden, residual)
+            layer = self.layers[str(i)]
+            hidden, residual = layer(hidden, residual)
+            if ple is not None:
+                hidden, residual = layer.add_per_layer_input(hidden, residual, ple[:, i].contiguous()), None
         if self.norm is None:
             return hidden, residual
+        if residual is None:
+            return self.norm(hidden), None
         hidden, _ = self.norm(hidden, residual)  # layer outputs are complete: no reduction here
         return hidden, None
 

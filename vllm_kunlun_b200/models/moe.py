@@ -251,7 +251,9 @@ class MoEForCausalLM(DenseForCausalLM):
         for name, p in self.named_parameters():
             if name in done or p.dtype not in (torch.float32, torch.bfloat16, torch.float16):
                 continue
-            if name.endswith("norm.weight") or "layernorm.weight" in name:
+            if name.endswith("layer_scalar"):
+                p.data.fill_(1.0)
+            elif name.endswith("norm.weight") or "layernorm.weight" in name:
                 p.data.fill_(0.0 if self.cfg.gemma_norm else 1.0)
             elif name.endswith("e_score_correction_bias"):
                 p.data.zero_()

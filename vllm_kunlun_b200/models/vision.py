@@ -93,6 +93,15 @@ class QwenVisionTransformer(nn.Module):
         self.merger_fc1 = ReplicatedLinear(mh, mh, bias=True, dtype=dtype, device=device)
         self.merger_fc2 = ReplicatedLinear(mh, out_hidden, bias=True, dtype=dtype, device=device)
         self.head_dim = h // vc["heads"]
+        # Qwen3-VL "deep stack": features of intermediate blocks get their own 2x2 mergers and are later added to the
+        # decoder's stream after its first layers (models/qwen3_vl.py of the reference, deepstack_visual_indexes)
+        self.deepstack_indexes = list(vc.get("deepstack_indexes", ()))
+        self.ds_norm = nn.ModuleList([_Norm(mh, vc.get("eps", 1e-6), vc.get("norm", "layernorm"), dtype, device)
+                                      for _ in self.deepstack_indexes])
+        self.ds_fc1 = nn.ModuleList([ReplicatedLinear(mh, mh, bias=True, dtype=dtype, device=device)
+                                     for _ in self.deepstack_indexes])
+        self.ds_fc2 = nn.ModuleList([ReplicatedLinear(mh, out_hidden, bias=True, dtype=dtype, device=device)
+                                     for _ in self.deepstack_indexes])
 
     def rot_pos_emb(self, grid_thw, device):
         """Per-token (h, w) rotary angles; tokens are ordered so that each ``merge x merge`` window is contiguous."""
@@ -109,18 +118,26 @@ class QwenVisionTransformer(nn.Module):
         return ang.cos(), ang.sin()
 
     def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
-        """``pixel_values [n_patches, patch_dim]`` -> ``[n_patches / merge^2, out_hidden]``."""
+        """``pixel_values [n_patches, patch_dim]`` -> ``[n_patches / merge^2, out_hidden * (1 + n_deepstack)]``: the
+        main embedding followed by the deep-stack features of the same tokens."""
         x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
         cos, sin = self.rot_pos_emb(grid_thw, x.device)
         lens = torch.tensor([h * w for t, h, w in grid_thw for _ in range(t)], dtype=torch.int32)
         cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
         cu[1:] = lens.cumsum(0)
         cu = cu.to(x.device)
-        for blk in self.blocks:
+        deep = []
+        for li, blk in enumerate(self.blocks):
             x = blk(x, cu, cos, sin)
+            if li in self.deepstack_indexes:
+                k = self.deepstack_indexes.index(li)
+                d = self.ds_norm[k](x.reshape(-1, x.shape[-1] * self.merge ** 2))
+                d = torch.nn.functional.gelu(self.ds_fc1[k](d).float()).to(x.dtype)
+                deep.append(self.ds_fc2[k](d))
         x = self.ln_q(x).reshape(-1, x.shape[-1] * self.merge ** 2)
         x = torch.nn.functional.gelu(self.merger_fc1(x).float()).to(x.dtype)
-        return self.merger_fc2(x)
+        x = self.merger_fc2(x)
+        return torch.cat([x] + deep, -1) if deep else x
 
 
 class InternVisionModel(nn.Module):
@@ -233,6 +250,21 @@ class _VLBase(nn.Module):
         self.image_token_id = cfg.vision.get("image_token_id", cfg.vocab_size - 1)
         self.layers = self.language_model.layers
         self.first_layer, self.last_layer = self.language_model.first_layer, self.language_model.last_layer
+        self.num_deepstack = len(getattr(self.visual, "deepstack_indexes", ()))
+        if self.num_deepstack:
+            self.language_model.post_layer_hook = self._deepstack_hook
+
+    def _deepstack_hook(self, layer_idx: int, hidden, residual):
+        """After decoder layer ``i < n_deepstack`` the i-th deep-stack feature is added to the stream at the image
+        rows of this step (the stream is ``residual + hidden``; ``residual`` is complete on every TP rank)."""
+        if layer_idx >= self.num_deepstack or residual is None:
+            return
+        ex = get_forward_context().extras
+        if ex.get("mm_dst") is None:
+            return
+        H = self.cfg.hidden_size
+        feat = ex["mm_src"][:, (1 + layer_idx) * H:(2 + layer_idx) * H].to(residual.dtype)
+        residual.index_add_(0, ex["mm_dst"], feat)
 
     # ---- multimodal
     @torch.inference_mode()
@@ -253,7 +285,7 @@ class _VLBase(nn.Module):
             hidden = lm.embed_tokens(input_ids)
             ex = get_forward_context().extras
             if ex.get("mm_dst") is not None:
-                hidden.index_copy_(0, ex["mm_dst"], ex["mm_src"].to(hidden.dtype))
+                hidden.index_copy_(0, ex["mm_dst"], ex["mm_src"][:, : hidden.shape[1]].to(hidden.dtype))
         return lm(input_ids, hidden, residual)
 
     def compute_logits(self, hidden):
@@ -309,6 +341,33 @@ class QwenVLForConditionalGeneration(_VLBase):
         return n
 
 
+class Qwen3VLMoeForConditionalGeneration(QwenVLForConditionalGeneration):
+    """Qwen3-VL with the Qwen3-MoE decoder (``models/qwen3_vl_moe.py`` of the reference): the same tower with
+    deep-stack features, the text side is the sparse-MoE decoder of this package."""
+
+    _MAP = dict(QwenVLForConditionalGeneration._MAP, **{"deepstack_merger_list.": "ds_", "merger.norm.": "ln_q.",
+                                                         "merger.linear_fc1.": "merger_fc1.",
+                                                         "merger.linear_fc2.": "merger_fc2."})
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        cfg.vision.setdefault("text_architecture", "Qwen3MoeForCausalLM")
+        if cfg.vision["text_architecture"] in ("Qwen3ForCausalLM", "Qwen2ForCausalLM") and cfg.num_experts:
+            cfg.vision["text_architecture"] = "Qwen3MoeForCausalLM"
+        super().__init__(cfg, device, dtype)
+
+    def _vision_name(self, name):
+        n = super()._vision_name(name)
+        if n is None:
+            return None
+        import re
+        # deepstack_merger_list.<k>.{norm,linear_fc1,linear_fc2}.* -> ds_{norm,fc1,fc2}.<k>.*
+        m = re.match(r"ds_(\d+)\.(norm|linear_fc1|linear_fc2)\.(.*)", n)
+        if m:
+            kind = {"norm": "ds_norm", "linear_fc1": "ds_fc1", "linear_fc2": "ds_fc2"}[m.group(2)]
+            return f"{kind}.{m.group(1)}.{m.group(3)}"
+        return n
+
+
 class InternVLChatModel(_VLBase):
     """InternVL / Intern-S1: InternViT tower, pixel-shuffle projector, 1-D rotary decoder."""
 
@@ -322,6 +381,86 @@ class InternVLChatModel(_VLBase):
 
     def _vision_name(self, name):
         if not (name.startswith("vision_model.") or name.startswith("mlp1.")):
+            return None
+        n = name
+        for a, b in self._MAP.items():
+            n = n.replace(a, b)
+        return n
+
+
+class GemmaVisionTower(nn.Module):
+    """SigLIP-style tower of the Gemma multimodal models: patch embedding with a learned position table, LayerNorm
+    blocks, average pooling of ``pool x pool`` patch windows, then the (1 + w) RMSNorm + linear projector into the
+    decoder width (``models/gemma4_mm.py`` of the reference)."""
+
+    def __init__(self, vc: dict, out_hidden: int, dtype, device):
+        super().__init__()
+        self.vc = vc
+        h = vc["hidden"]
+        self.patch_dim = vc.get("in_channels", 3) * vc["patch"] ** 2
+        self.patch_embed = ReplicatedLinear(self.patch_dim, h, bias=True, dtype=dtype, device=device)
+        self.side = vc["image_size"] // vc["patch"]
+        self.pos = param(self.side ** 2, h, dtype=dtype, device=device)
+        blk = dict(vc, norm="layernorm", act="gelu")
+        self.blocks = nn.ModuleList([VisionBlock(blk, dtype, device) for _ in range(vc["depth"])])
+        self.post_norm = _Norm(h, 1e-6, "layernorm", dtype, device)
+        self.pool = vc.get("pool", 4)
+        self.soft_norm_weight = param(h, dtype=dtype, device=device)   # (1 + w) RMSNorm
+        self.proj = ReplicatedLinear(h, out_hidden, bias=False, dtype=dtype, device=device)
+        self.merge = 1
+
+    @property
+    def tokens_per_image(self) -> int:
+        return (self.side // self.pool) ** 2
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw=None) -> torch.Tensor:
+        """``pixel_values [n_images, side^2, patch_dim]`` -> ``[n_images * (side / pool)^2, out_hidden]``."""
+        n, L, _ = pixel_values.shape
+        x = self.patch_embed(pixel_values.reshape(n * L, -1).to(self.pos.dtype)).view(n, L, -1) + self.pos.unsqueeze(0)
+        x = x.reshape(n * L, -1)
+        cu = (torch.arange(n + 1, dtype=torch.int32) * L).to(x.device)
+        for blk in self.blocks:
+            x = blk(x, cu)
+        x = self.post_norm(x).view(n, self.side, self.side, -1)
+        k = self.pool
+        x = x.view(n, self.side // k, k, self.side // k, k, -1).float().mean((2, 4)).reshape(n * self.tokens_per_image, -1)
+        x = ops.rmsnorm(x.to(self.pos.dtype), self.soft_norm_weight, 1e-6, True)
+        return self.proj(x)
+
+
+class Gemma4ForConditionalGeneration(_VLBase):
+    """Gemma-4 with the vision tower (``Gemma4ForConditionalGeneration``, ``models/gemma4_mm.py`` in the reference):
+    image soft tokens replace the placeholder embeddings AFTER the embedding scale, 1-D rotary positions, and the
+    per-layer inputs of placeholder rows come from row 0 of the per-layer table."""
+
+    tower_cls = GemmaVisionTower
+    uses_mrope = False
+
+    _MAP = {"vision_tower.vision_model.embeddings.patch_embedding.": "patch_embed.",
+            "vision_tower.vision_model.embeddings.position_embedding.weight": "pos",
+            "vision_tower.vision_model.encoder.layers.": "blocks.", ".self_attn.out_proj.": ".proj.",
+            ".layer_norm1.": ".norm1.", ".layer_norm2.": ".norm2.", ".mlp.fc1.": ".fc1.", ".mlp.fc2.": ".fc2.",
+            "vision_tower.vision_model.post_layernorm.": "post_norm.",
+            "multi_modal_projector.mm_soft_emb_norm.weight": "soft_norm_weight",
+            "multi_modal_projector.mm_input_projection.": "proj."}
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        cfg.vision.setdefault("text_architecture", "Gemma4ForCausalLM")
+        super().__init__(cfg, device, dtype)
+        self.language_model.input_embeds_hook = self._inject
+
+    def _inject(self, hidden):
+        ex = get_forward_context().extras
+        if ex.get("mm_dst") is not None:
+            hidden = hidden.clone()
+            hidden.index_copy_(0, ex["mm_dst"], ex["mm_src"][:, : hidden.shape[1]].to(hidden.dtype))
+        return hidden
+
+    def forward(self, input_ids, hidden=None, residual=None):
+        return self.language_model(input_ids, hidden, residual)  # injection happens inside, after the embed scale
+
+    def _vision_name(self, name):
+        if not (name.startswith("vision_tower.") or name.startswith("multi_modal_projector.")):
             return None
         n = name
         for a, b in self._MAP.items():

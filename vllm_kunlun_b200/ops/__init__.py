@@ -188,7 +188,8 @@ def swap_blocks(src, dst, mapping):
 def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
                     max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
                     seq_lens_cpu=None, query_start_loc_cpu=None, out=None, workspace=None,
-                    num_decodes: int = 0, decode_query_len: int = 1, num_decode_tokens: int = 0):
+                    num_decodes: int = 0, decode_query_len: int = 1, num_decode_tokens: int = 0,
+                    stable_metadata: bool = False):
     """Unified varlen paged GQA attention (prefill with prefix, decode, spec-verify).
 
     The batch is decode-first: the first ``num_decodes`` requests have at most ``decode_query_len``
@@ -203,13 +204,14 @@ def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale:
             ndt = num_decode_tokens or num_decodes * decode_query_len
             paged_attention_cuda(out[:ndt], q[:ndt], kv_cache, block_tables[:num_decodes], seq_lens[:num_decodes],
                                  query_start_loc[:num_decodes + 1], scale, decode_query_len, max_seq_len,
-                                 window, sinks, workspace)
+                                 window, sinks, workspace, stable_metadata=stable_metadata)
             paged_attention_cuda(out, q, kv_cache, block_tables[num_decodes:], seq_lens[num_decodes:],
                                  query_start_loc[num_decodes:], scale, max_query_len, max_seq_len,
                                  window, sinks, workspace)
             return out
         return paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
-                                    max_query_len, max_seq_len, window, sinks, workspace)
+                                    max_query_len, max_seq_len, window, sinks, workspace,
+                                    stable_metadata=stable_metadata)
     sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
     ql = query_start_loc if query_start_loc_cpu is None else query_start_loc_cpu
     return _ra.paged_attention(q, kv_cache, block_tables, sl, ql, scale, window, sinks)
@@ -376,14 +378,15 @@ def bmm_heads(x, w):
 
 def mla_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float, kv_lora_rank: int,
                   max_query_len: int, max_seq_len: int, seq_lens_cpu=None, query_start_loc_cpu=None, workspace=None,
-                  return_lse: bool = False):
+                  return_lse: bool = False, stable_metadata: bool = False):
     """Weight-absorbed MLA attention over the latent cache (decode, spec-verify and causal prefill):
     ``q [T, N, 576]`` -> ``out [T, N, 512]`` (and the natural-log LSE ``[T, N]`` when asked; rows without any
     visible key give zeros and ``-inf``)."""
     if q.is_cuda:
         from .mla_cuda import mla_attention_cuda
         return mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank,
-                                  max_query_len, max_seq_len, workspace, return_lse=return_lse)
+                                  max_query_len, max_seq_len, workspace, return_lse=return_lse,
+                                  stable_metadata=stable_metadata)
     sl = seq_lens if seq_lens_cpu is None else seq_lens_cpu
     ql = query_start_loc if query_start_loc_cpu is None else query_start_loc_cpu
     return _ra.mla_decode(q, kv_cache, block_tables, sl, ql, scale, kv_lora_rank, return_lse=return_lse)

@@ -66,7 +66,12 @@ def plan_splits_umma(num_reqs: int, num_kv_heads: int, max_seq_len: int, device,
 
 def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_loc, scale: float,
                          max_query_len: int, max_seq_len: int, window: Optional[int] = None, sinks=None,
-                         workspace: Optional[AttnWorkspace] = None, num_splits: Optional[int] = None):
+                         workspace: Optional[AttnWorkspace] = None, num_splits: Optional[int] = None,
+                         stable_metadata: bool = False):
+    """``stable_metadata``: the caller promises that ``block_tables`` / ``seq_lens`` / ``query_start_loc`` were
+    filled by host copies before the step's first kernel (as the engine's runner does) and that the cache rows of
+    the old context come from earlier steps; the decode kernel then starts fetching KV tiles while the kernel in
+    front of it is still running."""
     T, Hq, D = q.shape
     Hkv = kv_cache.shape[2]
     g = Hq // Hkv
@@ -84,7 +89,7 @@ def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_l
             assert T <= workspace.max_tokens and num_splits <= workspace.max_splits
             ws_o, ws_lse = workspace.o, workspace.lse
         _ext.C().decode_attention_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, ws_o, ws_lse,
-                                       max_query_len, num_splits, window or 0, scale)
+                                       max_query_len, num_splits, window or 0, scale, bool(stable_metadata))
         return out
     if num_splits is None:
         if decode_layout:

@@ -24,10 +24,39 @@ def _ws(T, N, splits, device):
             torch.empty(splits * T * N, dtype=torch.float32, device=device))
 
 
+# decode / speculative-verify batches over 64-token cache blocks run on the tcgen05 kernel
+# (csrc/attention/mla_decode_umma.cu); B200_MLA_UMMA=0 keeps them on the mma.sync kernel
+import os as _os
+UMMA_DECODE = [_os.environ.get("B200_MLA_UMMA", "1") != "0"]
+_UMMA_MAX_QLEN = 4
+
+
+def mla_decode_umma(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, max_query_len, max_seq_len,
+                    num_splits=None, stable_metadata: bool = False):
+    """Dense paged MLA decode on tcgen05: every request has at most ``max_query_len`` (<= 4) query tokens."""
+    T, N, _ = q.shape
+    B = seq_lens.shape[0]
+    out = torch.empty(T, N, 512, dtype=q.dtype, device=q.device)
+    R = 16 if N * max_query_len <= 16 else 32
+    groups = -(-N // (R // max_query_len))
+    if num_splits is None:
+        tiles = max(1, -(-max_seq_len // 64))
+        num_splits = int(max(1, min(sm_count(q.device) // max(1, groups * B), 16, max(1, tiles // 2))))
+    ws_o, ws_lse = _ws(T, N, num_splits, q.device) if num_splits > 1 else (None, None)
+    _ext.C().mla_decode_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, ws_o, ws_lse, max_query_len,
+                             num_splits, scale, bool(stable_metadata))
+    return out
+
+
 def mla_attention_cuda(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank, max_query_len,
-                       max_seq_len, workspace=None, req_of_token=None, return_lse: bool = False):
+                       max_seq_len, workspace=None, req_of_token=None, return_lse: bool = False,
+                       stable_metadata: bool = False):
     assert kv_lora_rank == 512 and q.shape[-1] == 576 and kv_cache.dtype == q.dtype
     T, N, _ = q.shape
+    if (UMMA_DECODE[0] and not return_lse and 1 <= max_query_len <= _UMMA_MAX_QLEN and kv_cache.dim() == 3
+            and kv_cache.shape[1] == 64 and q.is_contiguous() and kv_cache.is_contiguous()):
+        return mla_decode_umma(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, max_query_len, max_seq_len,
+                               stable_metadata=stable_metadata)
     if req_of_token is None:
         lens = (query_start_loc[1:] - query_start_loc[:-1]).long()
         req_of_token = torch.repeat_interleave(torch.arange(lens.shape[0], device=q.device, dtype=torch.int32), lens,

@@ -41,15 +41,49 @@ class B200Platform(_VllmPlatform):
 
     @classmethod
     def get_device_capability(cls, device_id: int = 0):
+        major, minor = torch.cuda.get_device_capability(device_id) if torch.cuda.is_available() else (10, 0)
+        if _HAVE_VLLM:
+            from vllm.platforms.interface import DeviceCapability
+            return DeviceCapability(major=major, minor=minor)
+        return (major, minor)
+
+    @classmethod
+    def get_device_uuid(cls, device_id: int = 0) -> str:
+        return str(torch.cuda.get_device_properties(device_id).uuid) if torch.cuda.is_available() else "cpu"
+
+    @classmethod
+    def manual_seed_all(cls, seed: int) -> None:
         if torch.cuda.is_available():
-            return torch.cuda.get_device_capability(device_id)
-        return (10, 0)
+            torch.cuda.manual_seed_all(seed)
+
+    @classmethod
+    def num_compute_units(cls, device_id: int = 0) -> int:
+        return torch.cuda.get_device_properties(device_id).multi_processor_count if torch.cuda.is_available() else 148
+
+    @classmethod
+    def device_count(cls) -> int:
+        return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+    @classmethod
+    def stateless_init_device_torch_dist_pg(cls, backend, prefix_store, group_rank, group_size, timeout):
+        """NCCL process group without the global state of ``init_process_group`` (upstream's CUDA recipe)."""
+        from torch.distributed import ProcessGroup
+        from torch.distributed.distributed_c10d import ProcessGroupNCCL
+        pg = ProcessGroup(prefix_store, group_rank, group_size)
+        opts = ProcessGroupNCCL.Options()
+        opts._timeout = timeout
+        be = ProcessGroupNCCL(prefix_store, group_rank, group_size, opts)
+        pg._set_default_backend(ProcessGroup.BackendType.NCCL)
+        be._set_sequence_number_for_group()
+        pg._register_backend(torch.device("cuda"), ProcessGroup.BackendType.NCCL, be)
+        return pg
 
     @classmethod
     def has_device_capability(cls, capability, device_id: int = 0) -> bool:
         cap = cls.get_device_capability(device_id)
+        cap = (cap.major, cap.minor) if hasattr(cap, "major") else tuple(cap)
         want = capability if isinstance(capability, tuple) else (capability // 10, capability % 10)
-        return tuple(cap) >= tuple(want)
+        return cap >= tuple(want)
 
     @classmethod
     def get_device_total_memory(cls, device_id: int = 0) -> int:
