@@ -59,6 +59,12 @@ typedef struct GemmDecodeArgs {
   void* ll_bufs[8];     // low-latency all-reduce buffers of all ranks (peer mappings)
   const void* epoch_word;  // device word holding the number of completed all-reduce calls
   int64_t ll_slot_bytes;
+  // fp8 e4m3 operands with 128x128 weight block scales and 1x128 activation scales (fmt then names the output type;
+  // a k-block is 128 elements, so kb_per_cta counts blocks of 128)
+  int fp8;
+  const float* a_scale;    // [ceil(K/128), a_stride] transposed activation scales
+  const float* w_scale;    // [ceil(N/128), ceil(K/128)]
+  int a_stride;
 } GemmDecodeArgs;
 int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
 

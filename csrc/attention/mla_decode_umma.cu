@@ -53,6 +53,7 @@ struct Params {
   const int* qsl;
   int* status;
   int N, heads_per_cta, max_blocks, num_splits, early_meta;
+  int cluster_merge;        // the num_splits CTAs of a (request, head group) form a cluster and merge in shared memory
   int64_t num_blocks, T;
   float scale_log2;
 };
@@ -180,6 +181,11 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
             if (mbar_try_wait(&kv_full[i & 1], (i >> 1) & 1)) break;
       }
     }
+    if (p.cluster_merge) {  // the two cluster barriers of the merge count every thread of every CTA
+      __syncwarp();
+      cluster_arrive(); cluster_wait();
+      cluster_arrive(); cluster_wait();
+    }
   } else {
     griddep_wait();
     // ---- Q^T operand (warps 1-5): [9 blocks][R rows][128 B]; 16-byte chunk c of row r sits at chunk c ^ (r & 7)
@@ -248,6 +254,11 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
         umma_commit(&p_free[pb]);
         umma_commit(o_done);
       }
+    }
+    if (p.cluster_merge) {
+      __syncwarp();
+      cluster_arrive(); cluster_wait();
+      cluster_arrive(); cluster_wait();
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
@@ -377,7 +388,66 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
     }
     named_bar_sync(1, 128);
     const int d = quarter * 32 + lane;               // output dim within an O^T tile (M = 128: lane = row)
-    if (ok && served) {
+    if (p.cluster_merge) {
+      // ---- split merge inside the cluster: CTA c owns output dims [c * DS, (c + 1) * DS).  Every CTA stores its
+      // un-normalised partial O (and per row its running maximum and sum) into the owners' shared memory, which
+      // re-uses the cache-page stages once every CTA of the cluster has finished its last MMA (barrier A);
+      // barrier B publishes the stores, then each owner combines S partials for its slice.  No global workspace,
+      // no ticket, and the combine is spread over all CTAs instead of the last arriver.
+      const int S = p.num_splits, DS = kDV / S;
+      float* recv = reinterpret_cast<float*>(smem);                   // [S sources][R rows][DS dims]
+      float* recv_ml = reinterpret_cast<float*>(smem + kStageBytes);  // [S sources][R rows][max, sum]
+      cluster_arrive(); cluster_wait();  // A
+      if (served) {
+        if (tid < R) {
+          float m_mine = -INFINITY;  // m_used[tid] without a dynamically indexed register array
+#pragma unroll
+          for (int r = 0; r < R; ++r) m_mine = (tid == r) ? m_used[r] : m_mine;
+          const float L = sSum[tid] + sSum[R + tid] + sSum[2 * R + tid] + sSum[3 * R + tid];
+          const uint32_t local = smem_u32(recv_ml + (split * R + tid) * 2);
+          for (int c = 0; c < S; ++c) {
+            const uint32_t remote = mapa(local, (uint32_t)c);
+            st_cluster_f32(remote, ok ? m_mine : -INFINITY);
+            st_cluster_f32(remote + 4, ok ? L : 0.f);
+          }
+        }
+#pragma unroll 1
+        for (int j = 0; j < kDV / 128; ++j) {
+          const int dim = j * 128 + d;
+          const uint32_t remote = mapa(smem_u32(recv + (size_t)split * R * DS + dim % DS), (uint32_t)(dim / DS));
+#pragma unroll
+          for (int c = 0; c < R; c += 16) {
+            uint32_t orr[16];
+            if (ok && n_tiles > 0) {
+              tmem_ld_x16(tO + j * R + c, orr);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) orr[e] = 0;
+            }
+#pragma unroll
+            for (int e = 0; e < 16; ++e) st_cluster_f32(remote + (uint32_t)((c + e) * DS * 4), __uint_as_float(orr[e]));
+          }
+        }
+      }
+      cluster_arrive(); cluster_wait();  // B
+      if (served) {
+        for (int idx = tid; idx < rows_total * DS; idx += 128) {
+          const int r = idx / DS, dl = idx % DS;
+          float M = -INFINITY;
+          for (int s2 = 0; s2 < S; ++s2) M = fmaxf(M, recv_ml[(s2 * R + r) * 2]);
+          float den = 0.f, acc = 0.f;
+          for (int s2 = 0; s2 < S; ++s2) {
+            const float ms = recv_ml[(s2 * R + r) * 2];
+            const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            den = fmaf(recv_ml[(s2 * R + r) * 2 + 1], w, den);
+            acc = fmaf(recv[((size_t)s2 * R + r) * DS + dl], w, acc);
+          }
+          const int64_t orow = (int64_t)(qs + r / nh) * p.N + head0 + r % nh;
+          reinterpret_cast<T*>(p.out)[orow * kDV + split * DS + dl] = from_float<T>(den > 0.f ? acc / den : 0.f);
+        }
+      }
+    } else if (ok && served) {
 #pragma unroll 1
       for (int j = 0; j < kDV / 128; ++j) {
 #pragma unroll
@@ -413,7 +483,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
         }
       }
     }
-    if (p.num_splits > 1 && served) {
+    if (p.num_splits > 1 && !p.cluster_merge && served) {
       __threadfence();
       named_bar_sync(1, 128);
       const int ticket_idx = req * gridDim.x + blockIdx.x;
@@ -473,6 +543,9 @@ static int launch_r(const Params& p, const CUtensorMap& tm, int B, int head_grou
     cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
+  if (p.cluster_merge)
+    return (int)launch_pdl_cluster(kern, dim3(head_groups, B * p.num_splits), dim3(kThreads), dim3(1, p.num_splits, 1),
+                                   smem, st, tm, p);
   return (int)launch_pdl(kern, dim3(head_groups, B * p.num_splits), dim3(kThreads), smem, st, tm, p);
 }
 
@@ -494,8 +567,11 @@ extern "C" int b200_mla_decode_umma(void* out, const void* q, const void* tmap, 
   const int H = R / max_query_len;  // heads per CTA
   if (H < 1) return 3;
   const int groups = (N + H - 1) / H;
-  if (num_splits > 1 && (ws_o == nullptr || (int64_t)B * groups > mlad::kMaxTickets)) return 2;
+  // 2, 4 or 8 splits without a workspace: the splits of a (request, head group) are one cluster and merge on chip
+  const bool cluster_merge = ws_o == nullptr && (num_splits == 2 || num_splits == 4 || num_splits == 8);
+  if (num_splits > 1 && !cluster_merge && (ws_o == nullptr || (int64_t)B * groups > mlad::kMaxTickets)) return 2;
   mlad::Params p;
+  p.cluster_merge = cluster_merge ? 1 : 0;
   p.q = q; p.out = out; p.ws_o = ws_o; p.ws_lse = ws_lse; p.block_tables = block_tables; p.seq_lens = seq_lens;
   p.qsl = qsl; p.status = status; p.N = N; p.heads_per_cta = H; p.max_blocks = max_blocks; p.num_splits = num_splits;
   p.early_meta = early_meta; p.num_blocks = num_blocks; p.T = T_;

@@ -285,6 +285,59 @@ void gemm_decode(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const
   gs.launches++;
 }
 
+// fp8 block-scaled decode GEMM (T <= 32): xq [T, K] e4m3 with transposed 1x128 scales a_scale_t [K/128, stride],
+// w [N, K] e4m3 with w_scale [ceil(N/128), ceil(K/128)]; cluster split-K like gemm_decode.
+void gemm_decode_fp8(at::Tensor out, const at::Tensor& xq, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+                     const at::Tensor& a_scale_t, const at::Tensor& w_scale, int64_t splits) {
+  TORCH_CHECK(xq.is_cuda() && w.is_cuda() && out.is_cuda() && xq.dim() == 2 && w.dim() == 2 && out.dim() == 2);
+  TORCH_CHECK(xq.element_size() == 1 && w.element_size() == 1, "gemm_decode_fp8: 8-bit operands");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kHalf);
+  TORCH_CHECK(xq.stride(1) == 1 && w.is_contiguous() && out.stride(1) == 1);
+  const int T = xq.size(0), K = xq.size(1), N = w.size(0);
+  TORCH_CHECK(T <= 32 && w.size(1) == K && out.size(0) == T && out.size(1) == N);
+  TORCH_CHECK(K % 16 == 0 && xq.stride(0) % 16 == 0, "gemm_decode_fp8: K and the row stride must be multiples of 16");
+  const int total_kb = (K + 127) / 128;
+  TORCH_CHECK(a_scale_t.scalar_type() == at::kFloat && a_scale_t.dim() == 2 && a_scale_t.stride(1) == 1 &&
+              a_scale_t.size(0) >= total_kb && a_scale_t.size(1) >= T);
+  TORCH_CHECK(w_scale.scalar_type() == at::kFloat && w_scale.is_contiguous() && w_scale.numel() == (int64_t)((N + 127) / 128) * total_kb);
+  if (T == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(xq.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, out.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, out.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, out.options().dtype(at::kInt));
+  }
+  GemmDecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.out = out.data_ptr(); a.bias = opt_ptr(bias); a.status = gs.status.data_ptr<int>();
+  a.T = T; a.N = N; a.K = K;
+  a.n_tiles = (N + 127) / 128;
+  a.bn = T <= 16 ? 16 : 32;
+  a.fmt = out.scalar_type() == at::kBFloat16 ? 1 : 0;
+  a.ldo = out.stride(0);
+  a.fp8 = 1; a.a_scale = a_scale_t.data_ptr<float>(); a.w_scale = w_scale.data_ptr<float>(); a.a_stride = a_scale_t.stride(0);
+  const int max_s = a.bn == 16 ? 8 : 4;
+  int S = (int)splits;
+  if (S <= 0) {
+    // measured: a cluster of 8 only pays when each CTA still has >= 7 k-blocks (16 KB of weights each); below that
+    // the 7-way partial exchange costs more than the extra SMs bring
+    S = 1;
+    while (S * 2 <= max_s && a.n_tiles * S * 2 <= gs.num_sms && total_kb / (S * 2) >= (S * 2 == 8 ? 7 : 2)) S *= 2;
+  }
+  S = std::max(1, std::min(S, std::min(max_s, total_kb)));
+  while (S > 1 && (S - 1) * ((total_kb + S - 1) / S) >= total_kb) --S;
+  a.S = S;
+  a.kb_per_cta = (total_kb + S - 1) / S;
+  a.ctas_per_sm = a.n_tiles * S > gs.num_sms ? 2 : 1;
+  const Tmap& tw = get_tmap(gs, w, 128, 1);
+  const Tmap& tx = get_tmap(gs, xq, a.bn, 1);
+  check(b200_gemm_decode_launch(&a, tw.b, tx.b, stream()), "gemm_decode_fp8 launch");
+  gs.launches++;
+}
+
 int64_t gemm_status() {
   GemmState& gs = gemm_state();
   if (!gs.status.defined()) return 0;
@@ -659,7 +712,8 @@ void mla_decode_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, 
   TORCH_CHECK(q.size(2) == 576 && kv.size(2) == 576 && out.size(2) == 512 && q.scalar_type() == kv.scalar_type());
   TORCH_CHECK(block_tables.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
   TORCH_CHECK(block_tables.stride(1) == 1);
-  if (num_splits > 1) TORCH_CHECK(ws_o.has_value() && ws_lse.has_value());
+  if (num_splits > 8 || (num_splits & (num_splits - 1)) != 0)  // 2 / 4 / 8 splits merge inside a cluster
+    TORCH_CHECK(ws_o.has_value() && ws_lse.has_value());
   c10::cuda::CUDAGuard guard(q.device());
   GemmState& gs = gemm_state();
   std::lock_guard<std::mutex> lk(gs.mu);
@@ -996,6 +1050,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_status", &gemm_status);
   m.def("gemm_status_tensor", &gemm_status_tensor);
   m.def("gemm_decode", &gemm_decode);
+  m.def("gemm_decode_fp8", &gemm_decode_fp8);
   m.def("set_gemm_decode_comm", &set_gemm_decode_comm);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("moe_route", &moe_route);

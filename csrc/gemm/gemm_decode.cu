@@ -40,29 +40,6 @@ constexpr int kThreads = 192;
 constexpr int kStageBytesA = BM * BK * 2;
 constexpr int kTileStride = BM + 8;  // staging row (elements of OutT)
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_arrive() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_wait() {
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t cta) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -97,21 +74,32 @@ struct Comm {
   int on, rank, nranks;
 };
 
+constexpr int kAccBufs = 4;  // fp8: accumulator buffers handed to the epilogue one k-block at a time
+
 template <int BN>
 struct Cfg {
   static constexpr int kStageBytes = kStageBytesA + BN * BK * 2;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kTmemColsFp8 = kAccBufs * BN;                // 64 or 128
   static constexpr int kSlotBytes = BN * BM * 4;                    // one partial tile: [BN / 4][128 features] float4
   static constexpr int kTileBytes = BN * kTileStride * 2;
 };
 
-template <int BN, typename OutT>
+// kFp8: e4m3 operands with 128x128 weight block scales (w_scale [ceil(N/128)][ceil(K/128)]) and 1x128 activation
+// scales (a_scale [ceil(K/128)][a_stride], transposed).  A k-block is then 128 K-elements (still one 128-byte
+// swizzle row per operand row); every k-block is accumulated by the tensor core into its own TMEM buffer and the
+// epilogue warps multiply it by a_scale[kb][t] * w_scale[nt][kb] while adding it into fp32 registers, overlapped
+// with the next k-block's MMAs.
+template <int BN, typename OutT, bool kFp8>
 __global__ void __launch_bounds__(kThreads)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    OutT* __restrict__ out, const OutT* __restrict__ bias, int* __restrict__ status, int T, int N, int K,
                    int kb_per_cta, int fmt, int ldo, int num_stages, int S, int act, int l2_prefetch,
+                   const float* __restrict__ a_scale, const float* __restrict__ w_scale, int a_stride,
                    const __grid_constant__ Comm cm) {
   using C = Cfg<BN>;
+  constexpr int BKE = kFp8 ? 128 : BK;  // K elements per k-block
+  constexpr int kCols = kFp8 ? C::kTmemColsFp8 : C::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + num_stages * C::kStageBytes);
@@ -119,7 +107,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint64_t* empty_bar = bars + num_stages;
   uint64_t* tmem_full = bars + 2 * num_stages;
   uint64_t* red_bar = tmem_full + 1;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(red_bar + 1);
+  uint64_t* acc_full = red_bar + 1;             // [kAccBufs] (fp8)
+  uint64_t* acc_empty = acc_full + kAccBufs;    // [kAccBufs] (fp8)
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccBufs);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 2);  // [2]
   uint8_t* after = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tmem_base_slot + 4) + 15) & ~uintptr_t(15));
@@ -130,7 +120,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int lane = threadIdx.x & 31;
   const uint32_t crank = (S > 1) ? cluster_ctarank() : 0u;
   const int nt = blockIdx.x / S;
-  const int total_kb = (K + BK - 1) / BK;
+  const int total_kb = (K + BKE - 1) / BKE;
   const int kb0 = (int)crank * kb_per_cta;
   const int kb1 = min(total_kb, kb0 + kb_per_cta);
   const int nkb = kb1 - kb0;  // >= 1 by construction on the host
@@ -144,13 +134,14 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     mbar_init(tmem_full, 1);
     mbar_init(red_bar, (uint32_t)(S > 1 ? (S - 1) * 4 : 1));
+    for (int b = 0; b < kAccBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     mbar_fence_init();
     prefetch_tmap(&tmW);
     prefetch_tmap(&tmX);
     griddep_launch();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_base_slot, C::kTmemCols);
+    tmem_alloc(tmem_base_slot, kCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -170,9 +161,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       // weights do not depend on the previous kernel: fill the ring (and pull what follows into L2) first
       for (; pre < num_stages && pre < nkb; ++pre) {
         mbar_expect_tx(&full_bar[pre], C::kStageBytes);
-        tma_load_2d_hint(smem + pre * C::kStageBytes, &tmW, &full_bar[pre], (kb0 + pre) * BK, nt * BM, pol_w);
+        tma_load_2d_hint(smem + pre * C::kStageBytes, &tmW, &full_bar[pre], (kb0 + pre) * BKE, nt * BM, pol_w);
       }
-      for (int i = 0; i < l2_prefetch && pre + i < nkb; ++i) tma_prefetch_l2_2d(&tmW, (kb0 + pre + i) * BK, nt * BM);
+      for (int i = 0; i < l2_prefetch && pre + i < nkb; ++i) tma_prefetch_l2_2d(&tmW, (kb0 + pre + i) * BKE, nt * BM);
       griddep_wait();
       int stage = 0;
       uint32_t phase = 0;
@@ -182,12 +173,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         uint8_t* sa = smem + stage * C::kStageBytes;
         uint8_t* sb = sa + kStageBytesA;
         if (i < pre) {
-          tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BK, 0);
+          tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BKE, 0);
         } else {
           if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 121)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d_hint(sa, &tmW, &full_bar[stage], (kb0 + i) * BK, nt * BM, pol_w);
-          tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BK, 0);
+          tma_load_2d_hint(sa, &tmW, &full_bar[stage], (kb0 + i) * BKE, nt * BM, pol_w);
+          tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BKE, 0);
         }
         ++issued;
         if (++stage == num_stages) { stage = 0; phase ^= 1; }
@@ -205,25 +196,32 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = umma_idesc(BM, BN, fmt, fmt);
+      const uint32_t idesc = kFp8 ? umma_idesc(BM, BN, 0, 0) : umma_idesc(BM, BN, fmt, fmt);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int i = 0; i < nkb; ++i) {
         if (!wait_or_abort(&full_bar[stage], phase, ab, 123)) { ok = false; break; }
+        const int ab_buf = i % kAccBufs;
+        if (kFp8 && i >= kAccBufs && !wait_or_abort(&acc_empty[ab_buf], ((i / kAccBufs) - 1) & 1, ab, 126)) {
+          ok = false;
+          break;
+        }
         tc_fence_after_sync();
         uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
         uint32_t sb = sa + kStageBytesA;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          uint64_t da = umma_desc_k_sw128(sa + k * UMMA_K * 2);
-          uint64_t db = umma_desc_k_sw128(sb + k * UMMA_K * 2);
-          umma_f16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row: 16 16-bit or 32 8-bit elements each
+          uint64_t da = umma_desc_k_sw128(sa + k * 32);
+          uint64_t db = umma_desc_k_sw128(sb + k * 32);
+          if (kFp8) umma_f8(tmem_base + ab_buf * BN, da, db, idesc, k > 0 ? 1u : 0u);
+          else umma_f16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
+        if (kFp8) umma_commit(&acc_full[ab_buf]);
         if (++stage == num_stages) { stage = 0; phase ^= 1; }
       }
-      if (ok) umma_commit(tmem_full);
+      if (ok && !kFp8) umma_commit(tmem_full);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -231,11 +229,53 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int ep_tid = (warp - 2) * 32 + lane;
     const int n_local = quarter * 32 + lane;
     griddep_wait();
-    if (ep_tid == 0) ep_ok_slot[0] = wait_or_abort(tmem_full, 0, ab, 124) ? 1 : 0;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool acc_ok = ep_ok_slot[0] != 0;
     float acc[BN];
-    if (acc_ok) {
+    bool acc_ok = true;
+    if (kFp8) {
+#pragma unroll
+      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const int wkb = total_kb;  // w_scale row length
+      // the scales of a k-block are fetched one k-block ahead: no dependent global load in front of the FMAs
+      float ws_next = w_scale[(size_t)nt * wkb + kb0];
+      float as_next[BN];
+#pragma unroll
+      for (int c = 0; c < BN; ++c) as_next[c] = (c < T) ? __ldg(a_scale + (size_t)kb0 * a_stride + c) : 0.f;
+      for (int i = 0; i < nkb; ++i) {
+        const int buf = i % kAccBufs;
+        float sc[BN];
+#pragma unroll
+        for (int c = 0; c < BN; ++c) sc[c] = as_next[c] * ws_next;
+        if (i + 1 < nkb) {
+          ws_next = w_scale[(size_t)nt * wkb + kb0 + i + 1];
+#pragma unroll
+          for (int c = 0; c < BN; ++c) as_next[c] = (c < T) ? __ldg(a_scale + (size_t)(kb0 + i + 1) * a_stride + c) : 0.f;
+        }
+        if (ep_tid == 0) ep_ok_slot[i & 1] = wait_or_abort(&acc_full[buf], (i / kAccBufs) & 1, ab, 127) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ep_ok_slot[i & 1] == 0) { acc_ok = false; break; }
+        while (!mbar_try_wait(&acc_full[buf], (i / kAccBufs) & 1)) {}
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          tmem_ld_x16(taddr + buf * BN + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c + j] = fmaf(__uint_as_float(r[j]), sc[c + j], acc[c + j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      }
+    } else {
+      if (ep_tid == 0) ep_ok_slot[0] = wait_or_abort(tmem_full, 0, ab, 124) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      acc_ok = ep_ok_slot[0] != 0;
+    }
+    if (kFp8) {
+      // accumulated above
+    } else if (acc_ok) {
       while (!mbar_try_wait(tmem_full, 0)) {}
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -351,20 +391,20 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   }
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    tmem_dealloc(tmem_base, kCols);
   }
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool kFp8>
 static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const CUtensorMap& tmX, cudaStream_t st) {
   using C = Cfg<BN>;
-  auto kern = gemm_decode_kernel<BN, OutT>;
+  auto kern = gemm_decode_kernel<BN, OutT, kFp8>;
   const int fixed = 1024 /*align*/ + 512 /*barriers*/ + (a.S - 1) * C::kSlotBytes + C::kTileBytes + 64;
   {
     cudaError_t e = ensure_dynamic_smem((const void*)kern, 220 * 1024);
     if (e != cudaSuccess) return e;
   }
-  const int total_kb = (a.K + BK - 1) / BK;
+  const int total_kb = (a.K + (kFp8 ? 128 : BK) - 1) / (kFp8 ? 128 : BK);
   const int nkb = a.kb_per_cta;
   // shared memory per CTA: about half an SM when two CTAs should be resident together
   int budget = (a.ctas_per_sm >= 2 ? 112 * 1024 : 216 * 1024) - fixed;
@@ -393,7 +433,8 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.status, a.T, a.N, a.K,
-                            a.kb_per_cta, a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), cm);
+                            a.kb_per_cta, a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), a.a_scale, a.w_scale,
+                            a.a_stride, cm);
 }
 
 }  // namespace dec
@@ -404,10 +445,18 @@ extern "C" int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmW,
   const CUtensorMap& w = *reinterpret_cast<const CUtensorMap*>(tmW);
   const CUtensorMap& x = *reinterpret_cast<const CUtensorMap*>(tmX);
   if (a->S < 1 || a->S > 8 || a->T > a->bn || a->kb_per_cta < 1) return (int)cudaErrorInvalidValue;
-  if ((a->S - 1) * a->kb_per_cta >= (a->K + 63) / 64 && a->S > 1) return (int)cudaErrorInvalidValue;  // an empty CTA
+  const int bke = a->fp8 ? 128 : 64;
+  if ((a->S - 1) * a->kb_per_cta >= (a->K + bke - 1) / bke && a->S > 1) return (int)cudaErrorInvalidValue;  // an empty CTA
   if (a->bn == 32 && a->S > 4) return (int)cudaErrorInvalidValue;
+  if (a->fp8 && (a->act != 0 || a->a_scale == nullptr || a->w_scale == nullptr)) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaErrorInvalidValue;
-  if (a->bn == 16) e = (a->fmt == 1) ? dec::launch<16, __nv_bfloat16>(*a, w, x, st) : dec::launch<16, __half>(*a, w, x, st);
-  else if (a->bn == 32) e = (a->fmt == 1) ? dec::launch<32, __nv_bfloat16>(*a, w, x, st) : dec::launch<32, __half>(*a, w, x, st);
+  // fmt gives the OUTPUT type for fp8 inputs (1 = bf16, 0 = fp16)
+  if (a->fp8) {
+    if (a->bn == 16) e = (a->fmt == 1) ? dec::launch<16, __nv_bfloat16, true>(*a, w, x, st) : dec::launch<16, __half, true>(*a, w, x, st);
+    else if (a->bn == 32) e = (a->fmt == 1) ? dec::launch<32, __nv_bfloat16, true>(*a, w, x, st) : dec::launch<32, __half, true>(*a, w, x, st);
+  } else {
+    if (a->bn == 16) e = (a->fmt == 1) ? dec::launch<16, __nv_bfloat16, false>(*a, w, x, st) : dec::launch<16, __half, false>(*a, w, x, st);
+    else if (a->bn == 32) e = (a->fmt == 1) ? dec::launch<32, __nv_bfloat16, false>(*a, w, x, st) : dec::launch<32, __half, false>(*a, w, x, st);
+  }
   return (int)e;
 }

@@ -23,12 +23,16 @@ def _close(a, b, atol, rtol, name=""):
 
 
 @pytest.mark.parametrize("N,q_len", [(16, 1), (16, 2), (5, 1), (128, 1), (40, 2), (8, 4)])
-@pytest.mark.parametrize("splits", [None, 1, 3, 7])
+@pytest.mark.parametrize("splits", [None, 1, 2, 4, 8, 3, 16, -4])
 def test_mla_decode_umma(N, q_len, splits):
     """tcgen05 MLA decode (cache pages as the UMMA M side, V = first 512 dims of the same shared-memory page) vs the
-    fp32 oracle: lengths that end inside / on the edge of a page, several query tokens, head groups, split-KV merge."""
+    fp32 oracle: lengths that end inside / on the edge of a page, several query tokens, head groups, split-KV merge
+    inside a cluster (2 / 4 / 8 splits) and through the workspace (other counts; -4 = 4 splits forced that way)."""
+    from vllm_kunlun_b200.ops import mla_cuda
     from vllm_kunlun_b200.ops.gemm_cuda import check_status
     from vllm_kunlun_b200.ops.mla_cuda import mla_decode_umma
+    mla_cuda._FORCE_WORKSPACE[0] = splits is not None and splits < 0
+    splits = abs(splits) if splits is not None else None
     bs = 64
     seq_lens = [q_len, 63 + q_len, 64, 65, 129, 700, 1500]
     B = len(seq_lens)
@@ -48,6 +52,7 @@ def test_mla_decode_umma(N, q_len, splits):
     ref = ra.mla_decode(q, cache, bt, sl, qsl, 0.1)
     out = mla_decode_umma(q.to(DEV), cache.to(DEV), bt.to(DEV), sl.to(DEV), qsl.to(DEV), 0.1, q_len, max(seq_lens), splits)
     torch.cuda.synchronize()
+    mla_cuda._FORCE_WORKSPACE[0] = False
     check_status()
     _close(out, ref, 1e-2, 2e-2, f"mla umma N={N} q_len={q_len} splits={splits}")
 

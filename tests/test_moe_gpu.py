@@ -179,7 +179,36 @@ def test_router_gemm_small(T, E, K):
     torch.testing.assert_close(got, want, atol=2e-3, rtol=2e-3)
 
 
-def test_small_fp8_projection_uses_16bit_copy_for_decode_batches():
+@pytest.mark.parametrize("T,N,K,splits", [(16, 2048, 4096, 0), (1, 128, 128, 0), (7, 384, 1024, 2), (32, 520, 7168, 4),
+                                          (16, 512, 1024, 8), (24, 256, 2048, 1), (3, 1536, 640, 0)])
+def test_gemm_decode_fp8_cluster_splitk(T, N, K, splits):
+    """fp8 block-scaled decode kernel (one TMEM buffer per 128-wide k-block, scales applied in the epilogue warps)
+    against fp32 arithmetic on the SAME quantised operands."""
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    g = torch.Generator().manual_seed(T + N + K)
+    w = torch.randn(N, K, generator=g) * 0.05
+    q, s = rb.quant_fp8_block(w)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    bias = torch.randn(N, generator=g).bfloat16()
+    C = _ext.C()
+    xq, st = C.quant_fp8_group(x.to(DEV), False, None, 4)
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    C.gemm_decode_fp8(out, xq, q.to(DEV).view(torch.uint8), bias.to(DEV), st, s.to(DEV), splits)
+    torch.cuda.synchronize()
+    check_status()
+    xd = xq.view(torch.float8_e4m3fn).float().cpu() * st[:, :T].T.cpu().repeat_interleave(128, 1)[:, :K]
+    wd = q.float() * s.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    ref = xd @ wd.T + bias.float()
+    # exact products, fp32 sums: what is left is the bf16 output rounding and the order of the K sum
+    _close(out, ref, 2e-3 * (K / 64) ** 0.5, 6e-3, f"gemm_decode_fp8 {T}x{N}x{K}/{splits}")
+    out2 = torch.empty_like(out)
+    C.gemm_decode_fp8(out2, xq, q.to(DEV).view(torch.uint8), bias.to(DEV), st, s.to(DEV), splits)
+    assert torch.equal(out, out2)
+
+
+def test_fp8_projection_decode_batches_read_the_fp8_weight():
+    """A quantised layer keeps ONE copy of its weight; 16-row and 300-row calls agree with the de-quantised oracle."""
     from vllm_kunlun_b200.models.layers import ReplicatedLinear
     from vllm_kunlun_b200.models.moe import _quant_block_device
     torch.manual_seed(0)
@@ -188,13 +217,15 @@ def test_small_fp8_projection_uses_16bit_copy_for_decode_batches():
     lin.weight.data.copy_(q)
     lin.weight_scale_inv.data.copy_(s)
     lin.method.process_weights_after_loading(lin)
-    assert lin.weight_16bit.shape == (512, 1024)
+    assert not hasattr(lin, "weight_16bit")
     x = torch.randn(300, 1024, device=DEV).bfloat16()
-    big = lin(x)            # fp8 tensor-core path
-    small = lin(x[:16])     # 16-bit stream-K path over the de-quantised copy
-    ref = x.float() @ lin.weight_16bit.float().T
-    _close(small, ref[:16], 2e-2, 2e-2, "16-bit copy")
-    _close(big, ref, 0.25, 0.1, "fp8 path")  # activations are quantised to e4m3 per 128 columns on this path
+    big = lin(x)            # grouped block-scaled kernel
+    small = lin(x[:16])     # cluster split-K decode kernel
+    wd = q.float() * s.repeat_interleave(128, 0).repeat_interleave(128, 1)
+    ref = x.float() @ wd.T
+    _close(small, ref[:16], 0.25, 0.1, "fp8 decode path")  # activations are quantised to e4m3 per 128 columns
+    _close(big, ref, 0.25, 0.1, "fp8 grouped path")
+    _close(small, big[:16], 2e-2, 2e-2, "the two kernels compute the same quantised product")
 
 
 @pytest.mark.parametrize("scoring,E,k,ng,tg", [("softmax", 128, 8, 1, 1), ("sigmoid", 256, 8, 8, 4), ("softmax_after_topk", 32, 4, 1, 1)])

@@ -187,3 +187,25 @@ def test_gqa_builder_and_impl_run_on_upstreams_common_metadata():
         t += q_lens[b]
     # profiling call (no metadata) zero-fills
     assert impl.forward(None, query, key, value, cache, None, out).abs().sum() == 0
+
+
+def test_upstream_c_namespace_ops_are_defined_with_upstream_schemas():
+    """Upstream layers bind ``torch.ops._C.<op>`` in ``__init__``; the plugin defines them (its kernels on CUDA
+    tensors, plain arithmetic otherwise) when upstream's own extension is not loaded."""
+    from vllm_kunlun_b200.ops.oot_layers import define_upstream_c_ops
+    define_upstream_c_ops()
+    x = torch.randn(3, 8)
+    out = torch.empty(3, 4)
+    torch.ops._C.silu_and_mul(out, x)
+    torch.testing.assert_close(out, torch.nn.functional.silu(x[:, :4]) * x[:, 4:])
+    torch.ops._C.gelu_tanh_and_mul(out, x)
+    torch.testing.assert_close(out, torch.nn.functional.gelu(x[:, :4], approximate="tanh") * x[:, 4:])
+    r, w = torch.randn(3, 8), torch.rand(8) + 0.5
+    x0, r0 = x.clone(), r.clone()
+    torch.ops._C.fused_add_rms_norm(x, r, w, 1e-6)
+    s = x0 + r0
+    torch.testing.assert_close(r, s)
+    torch.testing.assert_close(x, s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * w)
+    res = torch.empty_like(s)
+    torch.ops._C.rms_norm(res, s, w, 1e-6)
+    torch.testing.assert_close(res, x)

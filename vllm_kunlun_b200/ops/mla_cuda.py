@@ -29,6 +29,7 @@ def _ws(T, N, splits, device):
 import os as _os
 UMMA_DECODE = [_os.environ.get("B200_MLA_UMMA", "1") != "0"]
 _UMMA_MAX_QLEN = 4
+_FORCE_WORKSPACE = [False]  # tests: merge 2/4/8 splits through the global workspace instead of the cluster
 
 
 def mla_decode_umma(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, max_query_len, max_seq_len,
@@ -41,8 +42,12 @@ def mla_decode_umma(q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
     groups = -(-N // (R // max_query_len))
     if num_splits is None:
         tiles = max(1, -(-max_seq_len // 64))
-        num_splits = int(max(1, min(sm_count(q.device) // max(1, groups * B), 16, max(1, tiles // 2))))
-    ws_o, ws_lse = _ws(T, N, num_splits, q.device) if num_splits > 1 else (None, None)
+        want = int(max(1, min(sm_count(q.device) // max(1, groups * B), 16, max(1, tiles // 2))))
+        # up to 8 splits form a thread-block cluster that merges in shared memory (powers of two only: other
+        # cluster sizes schedule badly); 16 splits - few requests with long contexts - go through a workspace
+        num_splits = 16 if want >= 16 else 1 << (want.bit_length() - 1)
+    cluster = num_splits in (2, 4, 8) and not _FORCE_WORKSPACE[0]
+    ws_o, ws_lse = _ws(T, N, num_splits, q.device) if num_splits > 1 and not cluster else (None, None)
     _ext.C().mla_decode_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, ws_o, ws_lse, max_query_len,
                              num_splits, scale, bool(stable_metadata))
     return out

@@ -125,7 +125,119 @@ def register_oot_layers() -> dict:
             return tensor_model_parallel_all_reduce(out) if self.tp_size > 1 else out
 
     _patch_unquantized_gemm()
+    define_upstream_c_ops()
     return REGISTERED
+
+
+_C_LIB: list = []
+
+
+def define_upstream_c_ops() -> list:
+    """Give ``torch.ops._C`` the element-wise ops that upstream's layers bind at construction time
+    (``SiluAndMul.__init__`` reads ``torch.ops._C.silu_and_mul`` on every CUDA-like platform, whatever
+    ``forward_*`` is dispatched later), with upstream's schemas and this package's kernels behind them.  Upstream's
+    own ``vllm._C`` is not loaded under this platform (``B200Platform.import_kernels``), so the names are free; a
+    name that IS already defined is left alone.  The reference fills the same namespace with its device's kernels
+    (``vllm_kunlun/ops/_kunlun_ops.py``, ``vllm_kunlun/vllm_utils_wrapper.py``).  Returns the names defined here."""
+    if _C_LIB:
+        return _C_LIB[1]
+    lib = torch.library.Library("_C", "FRAGMENT")
+    done: list = []
+
+    def has(name):
+        try:
+            getattr(torch.ops._C, name)
+            return True
+        except (AttributeError, RuntimeError):
+            return False
+
+    def define(name, schema, fn):
+        if has(name):
+            return
+        lib.define(f"{name}{schema}")
+        lib.impl(name, fn, "CompositeExplicitAutograd")
+        done.append(name)
+
+    def gated(act):
+        def fn(out, x):
+            if act != "gelu" and _kernel_dtype(x) and x.is_contiguous():  # erf-GELU has no kernel here
+                out.copy_(ops.act_and_mul(x, act))
+            else:
+                d = x.shape[-1] // 2
+                g = {"silu": torch.nn.functional.silu,
+                     "gelu": torch.nn.functional.gelu,
+                     "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}[act]
+                out.copy_(g(x[..., :d]) * x[..., d:])
+        return fn
+
+    def mul_and_silu(out, x):
+        d = x.shape[-1] // 2
+        out.copy_(x[..., :d] * torch.nn.functional.silu(x[..., d:]))
+
+    def fatrelu_and_mul(out, x, threshold=0.0):
+        d = x.shape[-1] // 2
+        out.copy_(torch.nn.functional.threshold(x[..., :d], threshold, 0.0) * x[..., d:])
+
+    def swigluoai_and_mul(out, x, alpha=1.702, limit=7.0):
+        g, u = x[..., ::2].clamp(max=limit), x[..., 1::2].clamp(-limit, limit)
+        out.copy_((u + 1) * g * torch.sigmoid(g * alpha))
+
+    def unary(f):
+        def fn(out, x):
+            out.copy_(f(x))
+        return fn
+
+    def gelu_new(x):
+        return 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * (x + 0.044715 * x.pow(3))))
+
+    def gelu_fast(x):
+        return 0.5 * x * (1.0 + torch.tanh(x * 0.7978845608 * (1.0 + 0.044715 * x * x)))
+
+    def gelu_quick(x):
+        return ops.quick_gelu(x) if _kernel_dtype(x) and x.is_contiguous() else x * torch.sigmoid(1.702 * x)
+
+    def rms_norm(result, x, weight, epsilon):
+        x2 = x.reshape(-1, x.shape[-1])
+        if _kernel_dtype(x) and x2.is_contiguous():
+            result.copy_(ops.rmsnorm(x2, weight.to(x.dtype), epsilon).view_as(result))
+        else:
+            v = x.float()
+            result.copy_((v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + epsilon) * weight.float()).to(x.dtype))
+
+    def fused_add_rms_norm(x, residual, weight, epsilon):
+        x2, r2 = x.view(-1, x.shape[-1]), residual.view(-1, x.shape[-1])
+        if _kernel_dtype(x) and x2.is_contiguous() and r2.is_contiguous():
+            ops.add_rmsnorm(x2, r2, weight.to(x.dtype), epsilon)
+        else:
+            v = x.float() + residual.float()
+            residual.copy_(v.to(x.dtype))
+            v = residual.float()
+            x.copy_((v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + epsilon) * weight.float()).to(x.dtype))
+
+    def rotary_embedding(positions, query, key, head_size, cos_sin_cache, is_neox):
+        T = positions.numel()
+        rot = cos_sin_cache.shape[-1]
+        assert rot == head_size and key is not None and _kernel_dtype(query), \
+            "_C::rotary_embedding on this platform: full rotary dim, 16-bit q and k"
+        ops.rope(query.view(T, -1), key.view(T, -1), positions.reshape(-1).long(),
+                 cos_sin_cache.to(torch.float32), head_size, is_neox)
+
+    for name, act in (("silu_and_mul", "silu"), ("gelu_and_mul", "gelu"), ("gelu_tanh_and_mul", "gelu_tanh")):
+        define(name, "(Tensor! out, Tensor input) -> ()", gated(act))
+    define("mul_and_silu", "(Tensor! out, Tensor input) -> ()", mul_and_silu)
+    define("fatrelu_and_mul", "(Tensor! out, Tensor input, float threshold) -> ()", fatrelu_and_mul)
+    define("swigluoai_and_mul", "(Tensor! out, Tensor input, float alpha=1.702, float limit=7.0) -> ()",
+           swigluoai_and_mul)
+    define("gelu_new", "(Tensor! out, Tensor input) -> ()", unary(gelu_new))
+    define("gelu_fast", "(Tensor! out, Tensor input) -> ()", unary(gelu_fast))
+    define("gelu_quick", "(Tensor! out, Tensor input) -> ()", unary(gelu_quick))
+    define("rms_norm", "(Tensor! result, Tensor input, Tensor weight, float epsilon) -> ()", rms_norm)
+    define("fused_add_rms_norm", "(Tensor! input, Tensor! residual, Tensor weight, float epsilon) -> ()",
+           fused_add_rms_norm)
+    define("rotary_embedding", "(Tensor positions, Tensor! query, Tensor!? key, int head_size, Tensor cos_sin_cache, "
+           "bool is_neox) -> ()", rotary_embedding)
+    _C_LIB.extend([lib, done])
+    return done
 
 
 def b200_unquantized_gemm(layer, x: torch.Tensor, weight: torch.Tensor, bias=None) -> torch.Tensor:

@@ -4,7 +4,13 @@ from __future__ import annotations
 
 import torch
 
+import os
+
 from . import _ext
+
+# decode-sized fp8 linears on the cluster split-K kernel (csrc/gemm/gemm_decode.cu); B200_DECODE_FP8=0 keeps them on
+# the grouped kernel
+DECODE_FP8 = [os.environ.get("B200_DECODE_FP8", "1") != "0"]
 
 
 def quant_fp8_group_cuda(x: torch.Tensor, group: int = 128, ue8m0: bool = False, transposed: bool = False):
@@ -31,6 +37,11 @@ def fp8_linear_cuda(x, w_fp8, w_scale_inv, bias=None, block=(128, 128), out_dtyp
     q, st = C.quant_fp8_group(x2, False, None, 4)
     N = w_fp8.shape[0]
     out = torch.empty(x2.shape[0], N, dtype=out_dtype, device=x.device)
+    if (DECODE_FP8[0] and x2.shape[0] <= 32 and w_scale_inv.dim() == 2 and x2.shape[1] % 128 == 0
+            and out_dtype in (torch.bfloat16, torch.float16)):
+        # decode-sized call: cluster split-K kernel (every SM streams weight bytes; reduction in shared memory)
+        C.gemm_decode_fp8(out, q, w_fp8.view(torch.uint8), bias, st, w_scale_inv.contiguous(), 0)
+        return out.reshape(*lead, N)
     ws = w_scale_inv if w_scale_inv.dim() == 3 else w_scale_inv.unsqueeze(0)
     C.grouped_gemm(out, q, w_fp8.view(torch.uint8), None, bias, st, ws.contiguous(), 0)
     return out.reshape(*lead, N)

@@ -29,27 +29,13 @@ class Fp8BlockLinearMethod:
     def aux_params(self):
         return {"weight_scale_inv": self.block}
 
-    # Decode-sized calls of SMALL projections (attention q/k/v/o of the MoE models) are latency-bound, and the fp8
-    # kernel has no split-K: with M <= 64 tokens a [2048 x 4096] weight gives it 16 tiles for 148 SMs.  Such layers
-    # keep a second, 16-bit copy of the weight (de-quantised once) and send small batches through the 16-bit
-    # stream-K GEMM - which also skips the activation quantiser.  Large batches stay on the fp8 tensor-core path.
-    SMALL_WEIGHT_ELEMS = 48 << 20
-    SMALL_BATCH_ROWS = 64
-
     def apply(self, layer, x: torch.Tensor) -> torch.Tensor:
-        w16 = getattr(layer, "weight_16bit", None)
-        if w16 is not None and x.is_cuda and x.numel() // x.shape[-1] <= self.SMALL_BATCH_ROWS:
-            return ops.linear(x, w16, layer.bias)
+        # decode-sized batches (<= 32 rows) run on the cluster split-K fp8 kernel, larger ones on the grouped
+        # block-scaled kernel; both read the fp8 weight itself, so no 16-bit copy of it is kept
         return ops.fp8_linear(x, layer.weight, layer.weight_scale_inv, layer.bias, self.block, layer.out_dtype)
 
     def process_weights_after_loading(self, layer):
-        w = layer.weight
-        if (w.is_cuda and w.numel() <= self.SMALL_WEIGHT_ELEMS and layer.out_dtype in (torch.bfloat16, torch.float16)
-                and w.shape[1] % 8 == 0):
-            bn, bk = self.block
-            s = layer.weight_scale_inv.data
-            sf = s.repeat_interleave(bn, 0)[: w.shape[0]].repeat_interleave(bk, 1)[:, : w.shape[1]]
-            layer.weight_16bit = (w.data.float() * sf).to(layer.out_dtype)
+        return None
 
     @staticmethod
     def quantize_(layer, w: torch.Tensor, block=(128, 128)):
