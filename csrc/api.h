@@ -148,7 +148,9 @@ int b200_decode_attention_umma(void* out, const void* q, const void* tmap, const
 int b200_mla_decode_umma(void* out, const void* q, const void* tmap, const int* block_tables, const int* seq_lens,
                          const int* qsl, float* ws_o, float* ws_lse, int* status, int64_t T, int B, int N,
                          int block_size, int max_blocks, int64_t num_blocks, int max_query_len, int num_splits,
-                         float scale, int early_meta, int dtype, cudaStream_t st);
+                         float scale, int early_meta, int dtype, unsigned long long* trace, cudaStream_t st);
+
+int b200_mla_decode_max_clusters(int R, int S, int dtype);
 
 int b200_merge_splits(void* out, const float* ws_o, const float* ws_lse, int64_t rows, int Hq, int D, int splits,
                       int64_t T, int dtype, cudaStream_t st);

@@ -117,8 +117,8 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   uint64_t* o_done = p_free + 2;                   // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
-  int* s_last = reinterpret_cast<int*>(tmem_slot + 4);
+  volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4]
+  int* s_last = reinterpret_cast<int*>(tmem_slot + 6);
   float* sMax = reinterpret_cast<float*>(tmem_slot + 8);  // [2][4 warps][16 rows]
   float* sSum = sMax + 2 * 4 * kRows;                     // [4][16]
   float* sLse = sSum + 4 * kRows;                         // [16 splits][16 rows] (merge)
@@ -247,13 +247,12 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       const uint32_t idesc_o = umma_idesc(D, kRows, fmt, fmt, 1, 0);           // A = V (MN-major), B = P (K-major)
       const uint32_t tS = tmem_base, tO = tmem_base + 2 * kRows;
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-      bool ok = true;
+      // Event-driven: S^T of the next tile and P.V of the current one do not depend on each other (the first waits
+      // for its tile to land, the second for the softmax warps), so whichever is ready is issued first; a fixed
+      // order would hold P.V(i) - and the refill of its stage - behind the load of tile i + 1.
       auto issue_s = [&](int i) {
         const int stage = i % num_stages;
-        const uint32_t ph = (i / num_stages) & 1;
         const int buf = i & 1;
-        if (!wait_or_abort(&kv_full[stage], ph, ab, 502)) return false;
-        if (i >= 2 && !wait_or_abort(&s_empty[buf], ((i >> 1) - 1) & 1, ab, 503)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(smem + stage * kStageBytes);
 #pragma unroll
@@ -264,15 +263,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
           umma_f16(tS + buf * kRows, da, db, idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[buf]);
-        return true;
       };
-      ok = issue_s(0);
-      for (int i = 0; ok && i < n_tiles; ++i) {
-        if (i + 1 < n_tiles) ok = issue_s(i + 1);
-        if (!ok) break;
-        // P.V of tile i once the softmax warps have written P[i & 1] (and rescaled O^T if they had to)
+      auto issue_pv = [&](int i) {
         const int pb = i & 1;
-        if (!wait_or_abort(&p_ready[pb], (i >> 1) & 1, ab, 504)) { ok = false; break; }
         tc_fence_after_sync();
         const int stage = i % num_stages;
         const uint32_t v_addr = smem_u32(smem + stage * kStageBytes + kOpBytes);
@@ -283,9 +276,31 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
           uint64_t db = umma_desc_k_sw128(p_addr + pb * kPBytes + (k / 4) * (kRows * 128) + (k % 4) * 32);
           umma_f16(tO, da, db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
+        // o_done first: whoever has seen p_free of this tile may rely on o_done having advanced as well
+        umma_commit(o_done);
         umma_commit(&kv_empty[stage]);
         umma_commit(&p_free[pb]);
-        umma_commit(o_done);
+      };
+      int next_s = 0, next_pv = 0;
+      uint32_t spins = 0;
+      while (next_pv < n_tiles) {
+        bool progressed = false;
+        // S^T(next_s): its tile has landed and its TMEM buffer has been read (at most one S^T ahead of P.V)
+        if (next_s < n_tiles && next_s <= next_pv + 1 &&
+            mbar_try_wait(&kv_full[next_s % num_stages], (next_s / num_stages) & 1) &&
+            (next_s < 2 || mbar_try_wait(&s_empty[next_s & 1], ((next_s >> 1) - 1) & 1))) {
+          issue_s(next_s);
+          ++next_s;
+          progressed = true;
+        }
+        if (next_pv < next_s && mbar_try_wait(&p_ready[next_pv & 1], (next_pv >> 1) & 1)) {
+          issue_pv(next_pv);
+          ++next_pv;
+          progressed = true;
+        }
+        if (progressed) { spins = 0; continue; }
+        if (++spins > (1u << 20)) { ab.raise(502); break; }
+        if ((spins & 255) == 255 && ab.aborted()) break;
       }
     }
   } else if (warp >= 2) {
@@ -307,13 +322,16 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
     // byte offset of this key's column in a P buffer row
     const int p_off = (lane_id >> 6) * (kRows * 128) + (lane_id & 7) * 2;
     const int p_ch = (lane_id & 63) >> 3;
-    bool ok = true;
-    for (int i = 0; i < n_tiles && ok; ++i) {
+    // One named barrier per tile in the common case.  Every thread polls the mbarriers itself (bounded); a thread whose
+    // wait ran out keeps walking the loop with `fail` set, and the barrier below - which also tells whether any row's
+    // reference maximum has to move - makes all 128 threads leave together.
+    bool ok = true, fail = false;
+    for (int i = 0; i < n_tiles; ++i) {
       const int buf = i & 1;
-      if (tid == 0) ok_slot[buf] = wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 505) ? 1 : 0;
-      named_bar_sync(1, 128);
-      if (ok_slot[buf] == 0) { ok = false; break; }
-      while (!mbar_try_wait(&s_full[buf], (i >> 1) & 1)) {}
+      if (!fail && !wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 505)) fail = true;
+      // P buffer i & 1 must have been consumed (P.V of tile i - 2).  Waiting here, before a possible rescale, also
+      // keeps o_done at most one phase behind, so that the parity wait on it below cannot pass two phases early.
+      if (i >= 2 && !fail && !wait_or_abort(&p_free[buf], ((i >> 1) - 1) & 1, ab, 506)) fail = true;
       tc_fence_after_sync();
       uint32_t sr[kRows];
       tmem_ld_x16(tS + buf * kRows, sr);
@@ -321,12 +339,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[buf]);
-      // ---- mask (only on tiles that touch the causal / length / window edge) + tile max per row
+      // ---- mask (only on tiles that touch the causal / length / window edge)
       const int key0 = kv_begin + (tile_lo + i) * kTileKeys;
       const int key = key0 + lane_id;
       const bool full = key0 + kTileKeys - 1 <= pos_min && key0 + kTileKeys <= kv_end &&
                         (p.window <= 0 || key0 > pos_max - p.window);
       float sc[NR];
+      bool need = fail;   // does any score exceed its row's reference maximum by more than the slack?
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
         float v = __uint_as_float(sr[r]) * p.scale_log2;
@@ -337,49 +356,53 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
           v = -INFINITY;
         }
         sc[r] = v;
-        const float wm = warp_max_redux(v);
-        if (lane == r) sMax[(buf * 4 + quarter) * kRows + r] = wm;
+        need |= v > m_used[r] + kMaxSlack;
       }
-      named_bar_sync(1, 128);
-      float alpha[NR];
-      bool rescale = false;
+      if (bar_red_or(1, 128, need)) {
+        // ---- rare after the first tiles: exchange the per-warp maxima, move the reference maxima, rescale O^T
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          const float wm = warp_max_redux(sc[r]);
+          if (lane == r) sMax[quarter * kRows + r] = wm;
+        }
+        const bool warp_failed = __any_sync(0xffffffffu, fail);
+        if (lane == 0) ok_slot[quarter] = warp_failed ? 0 : 1;
+        named_bar_sync(1, 128);
+        if ((ok_slot[0] & ok_slot[1] & ok_slot[2] & ok_slot[3]) == 0) { ok = false; break; }
+        float alpha[NR];
+        bool rescale = false;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          const float* mm = sMax + r;
+          const float tm = fmaxf(fmaxf(mm[0], mm[kRows]), fmaxf(mm[2 * kRows], mm[3 * kRows]));
+          alpha[r] = 1.f;
+          if (tm > m_used[r] + kMaxSlack) {            // also the first finite maximum (m_used = -inf)
+            alpha[r] = exp2f(m_used[r] - tm);          // exp2(-inf) = 0: nothing accumulated yet
+            m_used[r] = tm;
+            l_part[r] *= alpha[r];
+            rescale = true;
+          }
+        }
+        if (rescale && i > 0) {  // the same decision in every thread: all of them read the same maxima
+          if (!wait_or_abort(o_done, (i - 1) & 1, ab, 508)) fail = true;
+          tc_fence_after_sync();
+          uint32_t orr[kRows];
+          tmem_ld_x16(tO, orr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int r = 0; r < NR; ++r) orr[r] = __float_as_uint(__uint_as_float(orr[r]) * alpha[r]);
+          tmem_st_x16(tO, orr);
+          tmem_st_wait();
+        }
+      }
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const float* mm = sMax + buf * 4 * kRows + r;
-        const float tm = fmaxf(fmaxf(mm[0], mm[kRows]), fmaxf(mm[2 * kRows], mm[3 * kRows]));
-        alpha[r] = 1.f;
-        if (tm > m_used[r] + kMaxSlack) {            // also the first finite maximum (m_used = -inf)
-          alpha[r] = exp2f(m_used[r] - tm);          // exp2(-inf) = 0: nothing accumulated yet
-          m_used[r] = tm;
-          rescale = true;
-        }
         const float ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
         sc[r] = exp2f(sc[r] - ms);
-        l_part[r] = l_part[r] * alpha[r] + sc[r];
-      }
-      // ---- P buffer i & 1 must have been consumed (P.V of tile i - 2); a rescale needs ALL earlier P.V done
-      if (i >= 2) {
-        if (tid == 0) ok_slot[buf] = wait_or_abort(&p_free[buf], ((i >> 1) - 1) & 1, ab, 506) ? 1 : 0;
-        named_bar_sync(1, 128);
-        if (ok_slot[buf] == 0) { ok = false; break; }
-        while (!mbar_try_wait(&p_free[buf], ((i >> 1) - 1) & 1)) {}
-      }
-      if (rescale && i > 0) {  // uniform over the CTA: every thread sees the same maxima
-        if (tid == 0) ok_slot[buf] = wait_or_abort(o_done, (i - 1) & 1, ab, 508) ? 1 : 0;
-        named_bar_sync(1, 128);
-        if (ok_slot[buf] == 0) { ok = false; break; }
-        while (!mbar_try_wait(o_done, (i - 1) & 1)) {}
-        tc_fence_after_sync();
-        uint32_t orr[kRows];
-        tmem_ld_x16(tO, orr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int r = 0; r < NR; ++r) orr[r] = __float_as_uint(__uint_as_float(orr[r]) * alpha[r]);
-        tmem_st_x16(tO, orr);
-        tmem_st_wait();
+        l_part[r] += sc[r];
       }
       // ---- P^T (B operand, K-major): element (row r, this thread's key)
-      {
+      if (!fail) {
         uint8_t* base = sP + buf * kPBytes + p_off;
 #pragma unroll
         for (int r = 0; r < NR; ++r)
@@ -387,20 +410,20 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
+      const bool warp_failed = __any_sync(0xffffffffu, fail);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[buf]);
+      if (lane == 0 && !warp_failed) mbar_arrive(&p_ready[buf]);
     }
+    if (fail) ok = false;
     // ---- epilogue: O^T lane = output dim, 16 columns = query rows
     if (ok && n_tiles > 0) {
-      const int last = n_tiles - 1;
-      if (tid == 0) ok_slot[0] = wait_or_abort(o_done, last & 1, ab, 507) ? 1 : 0;
-      named_bar_sync(1, 128);
-      ok = ok_slot[0] != 0;
-      if (ok) {
-        while (!mbar_try_wait(o_done, last & 1)) {}
-        tc_fence_after_sync();
-      }
+      // A parity wait is only meaningful when the barrier is at most one phase behind the awaited one; the p_free
+      // wait of the last tile guarantees P.V(n - 3), so P.V(n - 2) is awaited first, then the last one.
+      if (n_tiles >= 2 && !wait_or_abort(o_done, (n_tiles - 2) & 1, ab, 507)) ok = false;
+      if (ok && !wait_or_abort(o_done, (n_tiles - 1) & 1, ab, 507)) ok = false;
+      tc_fence_after_sync();
     }
+    ok = bar_red_or(1, 128, !ok) == 0;   // one thread's time-out ends the tile for all
     // row sums: every thread holds the part of its own keys
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
@@ -410,9 +433,29 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       if (lane == r) sSum[quarter * kRows + r] = v;
     }
     named_bar_sync(1, 128);
-    if (ok && served) {
+    // per row, once: 1 / denominator, the output row, the log-sum-exp (instead of divisions inside the store loop)
+    float* sInv = sMax;                                                     // [16]
+    long long* sRow = reinterpret_cast<long long*>(sMax + 2 * kRows);       // [16]
+    if (served && tid < NR) {
+      const int r = tid;
+      float m_mine = -INFINITY;
+#pragma unroll
+      for (int rr = 0; rr < NR; ++rr) m_mine = (tid == rr) ? m_used[rr] : m_mine;
+      const float L = sSum[r] + sSum[kRows + r] + sSum[2 * kRows + r] + sSum[3 * kRows + r];
+      const float Ms = (m_mine == -INFINITY) ? 0.f : m_mine;
+      const int hh = kvh * g + r % g;
+      const int64_t orow = r < rows_total ? (int64_t)(qs + r / g) * p.Hq + hh : 0;
+      float den = L;
+      if (p.num_splits == 1 && p.sinks != nullptr && r < rows_total) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
+      sInv[r] = (ok && den > 0.f) ? 1.f / den : 0.f;
+      sRow[r] = orow;
+      if (p.num_splits > 1 && r < rows_total)
+        p.ws_lse[(int64_t)split * p.T * p.Hq + orow] = (ok && L > 0.f) ? Ms + log2f(L) : -INFINITY;
+    }
+    named_bar_sync(1, 128);
+    if (served) {
       uint32_t orr[kRows];
-      if (n_tiles > 0) {
+      if (ok && n_tiles > 0) {
         tmem_ld_x16(tO, orr);
         tmem_ld_wait();
       } else {
@@ -420,24 +463,20 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
         for (int r = 0; r < kRows; ++r) orr[r] = 0;
       }
       const int d = lane_id;
+      // scales and offsets into registers first: shared-memory loads do not move across the global stores below
+      float inv[NR];
+      int64_t off[NR];
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        if (r >= rows_total) break;
-        const float L = sSum[r] + sSum[kRows + r] + sSum[2 * kRows + r] + sSum[3 * kRows + r];
-        const float Ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
-        const int tok = r / g, hh = kvh * g + r % g;
-        const int64_t orow = (int64_t)(qs + tok) * p.Hq + hh;
-        const float o = __uint_as_float(orr[r]);
-        if (p.num_splits == 1) {
-          float den = L;
-          if (p.sinks != nullptr) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
-          const float inv = den > 0.f ? 1.f / den : 0.f;
-          reinterpret_cast<T*>(p.out)[orow * D + d] = from_float<T>(o * inv);
-        } else {
-          const float inv = L > 0.f ? 1.f / L : 0.f;
-          p.ws_o[((int64_t)split * p.T * p.Hq + orow) * D + d] = o * inv;
-          if (d == 0) p.ws_lse[(int64_t)split * p.T * p.Hq + orow] = (L > 0.f) ? Ms + log2f(L) : -INFINITY;
-        }
+      for (int r = 0; r < NR; ++r) { inv[r] = sInv[r]; off[r] = sRow[r] * D + d; }
+      if (p.num_splits == 1) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+          if (r < rows_total) reinterpret_cast<T*>(p.out)[off[r]] = from_float<T>(__uint_as_float(orr[r]) * inv[r]);
+      } else {
+        float* wsp = p.ws_o + (int64_t)split * p.T * p.Hq * D;
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+          if (r < rows_total) wsp[off[r]] = __uint_as_float(orr[r]) * inv[r];
       }
     }
     if (p.num_splits > 1 && served) {
@@ -450,46 +489,55 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       if (*s_last) {
         __threadfence();
         const int d = lane_id;
+        const int S = p.num_splits;
         const int64_t sstride = p.T * p.Hq;
         // all log-sum-exps of this (request, head) in one round of loads: thread t -> (split t / 16, row t % 16)
-        for (int idx = tid; idx < p.num_splits * kRows; idx += 128) {
+        for (int idx = tid; idx < S * kRows; idx += 128) {
           const int s2 = idx / kRows, r = idx % kRows;
-          float v = -INFINITY;
-          if (r < rows_total) {
-            const int64_t orow = (int64_t)(qs + r / g) * p.Hq + kvh * g + r % g;
-            v = __ldcg(p.ws_lse + s2 * sstride + orow);
+          sLse[idx] = (r < rows_total) ? __ldcg(p.ws_lse + s2 * sstride + sRow[r]) : -INFINITY;
+        }
+        named_bar_sync(1, 128);
+        // weights, already divided by the common denominator (plus the sink's share), once per row
+        float* sW = sLse;
+        if (tid < NR && tid < rows_total) {
+          const int r = tid;
+          float M = -INFINITY;
+          for (int s2 = 0; s2 < S; ++s2) M = fmaxf(M, sLse[s2 * kRows + r]);
+          const float Ms = (M == -INFINITY) ? 0.f : M;
+          float den = 0.f;
+          for (int s2 = 0; s2 < S; ++s2) {
+            const float l = sLse[s2 * kRows + r];
+            const float w = (l == -INFINITY) ? 0.f : exp2f(l - Ms);
+            den += w;
+            sW[s2 * kRows + r] = w;
           }
-          sLse[idx] = v;
+          if (p.sinks != nullptr) den += exp2f(p.sinks[kvh * g + r % g] * 1.4426950408889634f - Ms);
+          const float inv = den > 0.f ? 1.f / den : 0.f;
+          for (int s2 = 0; s2 < S; ++s2) sW[s2 * kRows + r] *= inv;
         }
         named_bar_sync(1, 128);
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
           if (r >= rows_total) break;
-          const int hh = kvh * g + r % g;
-          const int64_t orow = (int64_t)(qs + r / g) * p.Hq + hh;
-          float M = -INFINITY;
-          for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, sLse[s2 * kRows + r]);
-          const float Ms = (M == -INFINITY) ? 0.f : M;
-          float den = 0.f, acc = 0.f;
+          const float* src = p.ws_o + sRow[r] * D + d;
+          float acc = 0.f;
           int s2 = 0;
-          for (; s2 + 4 <= p.num_splits; s2 += 4) {  // four independent loads in flight
-            float v[4], w[4];
+          for (; s2 + 4 <= S; s2 += 4) {  // four independent loads in flight
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldcg(src + (s2 + u) * sstride * D);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              v[u] = __ldcg(p.ws_o + ((s2 + u) * sstride + orow) * D + d);
-              w[u] = exp2f(sLse[(s2 + u) * kRows + r] - Ms);
+              const float w = sW[(s2 + u) * kRows + r];
+              acc += w > 0.f ? v[u] * w : 0.f;   // an empty split's row may hold anything
             }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) { den += w[u]; acc += w[u] > 0.f ? v[u] * w[u] : 0.f; }
           }
-          for (; s2 < p.num_splits; ++s2) {
-            const float w = exp2f(sLse[s2 * kRows + r] - Ms);
-            den += w;
-            if (w > 0.f) acc += __ldcg(p.ws_o + (s2 * sstride + orow) * D + d) * w;
+          for (; s2 < S; ++s2) {
+            const float w = sW[s2 * kRows + r];
+            const float v = __ldcg(src + s2 * sstride * D);
+            acc += w > 0.f ? v * w : 0.f;
           }
-          if (p.sinks != nullptr) den += exp2f(p.sinks[hh] * 1.4426950408889634f - Ms);
-          const float inv = den > 0.f ? 1.f / den : 0.f;
-          reinterpret_cast<T*>(p.out)[orow * D + d] = from_float<T>(acc * inv);
+          reinterpret_cast<T*>(p.out)[sRow[r] * D + d] = from_float<T>(acc);
         }
         if (tid == 0) g_tickets[ticket_idx] = 0;
       }

@@ -29,6 +29,7 @@
 #include "../common/launch.cuh"
 #include "../common/ptx.cuh"
 #include "../gemm/gemm_common.cuh"
+#include "attn_common.cuh"
 
 namespace b200 {
 namespace mlad {
@@ -52,6 +53,7 @@ struct Params {
   const int* seq_lens;
   const int* qsl;
   int* status;
+  unsigned long long* trace;  // optional phase timestamps [CTA][24] (null = off); slots 8-12 follow tile 4 through the pipeline, 13-19 the split merge
   int N, heads_per_cta, max_blocks, num_splits, early_meta;
   int cluster_merge;        // the num_splits CTAs of a (request, head group) form a cluster and merge in shared memory
   int64_t num_blocks, T;
@@ -103,10 +105,11 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
   uint64_t* p_ready = bars + 8;                // [2]
   uint64_t* p_free = bars + 10;                // [2]
   uint64_t* o_done = bars + 12;                // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* merge_bar = bars + 13;             // [1] bulk copies of the split merge
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
-  int* s_last = reinterpret_cast<int*>(tmem_slot + 4);
+  volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4]
+  int* s_last = reinterpret_cast<int*>(tmem_slot + 6);
   float* sMax = reinterpret_cast<float*>(tmem_slot + 8);   // [2][4 warps][R]
   float* sSum = sMax + 2 * 4 * R;                          // [4][R]
   float* sAlpha = sSum + 4 * R;                            // [R]
@@ -114,6 +117,8 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Abort ab{p.status, abort_flag};
+  const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 64) trace_mark(p.trace, cta_id, 0);  // start
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -123,6 +128,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
       mbar_init(&p_ready[b], 4); mbar_init(&p_free[b], 1);
     }
     mbar_init(o_done, 1);
+    mbar_init(merge_bar, 1);
     mbar_fence_init();
     prefetch_tmap(&tmKV);
     griddep_launch();
@@ -166,6 +172,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
         const bool old_ctx = (page + 1) * kKeys <= ctx;
         if (!waited && (i >= kStages || !old_ctx)) { griddep_wait(); waited = true; }
         if (i >= kStages && !wait_or_abort(&kv_empty[stage], ((i >> 1) - 1) & 1, ab, 601)) { ok = false; break; }
+        if (i == 4) trace_mark(p.trace, cta_id, 8);    // producer: stage of tile 4 is free
         mbar_expect_tx(&kv_full[stage], kStageBytes);
         int64_t blk = page < p.max_blocks ? bt[page] : 0;
         if (blk < 0 || blk >= p.num_blocks) blk = 0;
@@ -189,21 +196,22 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
   } else {
     griddep_wait();
     // ---- Q^T operand (warps 1-5): [9 blocks][R rows][128 B]; 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+    // asynchronous 16-byte copies: every chunk of a thread is in flight at once (zero-filled past the last row)
     for (int c = threadIdx.x - 32; c < R * (kD / 8); c += kThreads - 32) {
       const int r = c / (kD / 8), ch = c % (kD / 8);
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < rows_total && served) {
-        const int tok = r / nh, hh = r % nh;
-        v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) +
-                                            ((int64_t)(qs + tok) * p.N + head0 + hh) * kD + ch * 8);
-      }
+      const bool valid = r < rows_total && served;
+      const int tok = valid ? r / nh : 0, hh = valid ? r % nh : 0;
+      const T* src = reinterpret_cast<const T*>(p.q) + ((int64_t)(qs + tok) * p.N + head0 + hh) * kD + ch * 8;
       const int kb = ch / 8, cc = ch % 8;
-      *reinterpret_cast<uint4*>(sQ + kb * (R * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+      cp_async16(sQ + kb * (R * 128) + r * 128 + ((cc ^ (r & 7)) << 4), valid ? src : p.q, valid);
     }
+    cp_async_commit();
     for (int c = threadIdx.x - 32; c < 2 * kPBytes / 16; c += kThreads - 32)
       reinterpret_cast<uint4*>(sP)[c] = make_uint4(0, 0, 0, 0);
+    cp_async_wait<0>();
     fence_proxy_async_smem();
     named_bar_sync(2, kThreads - 32);
+    if (threadIdx.x == 64) trace_mark(p.trace, cta_id, 1);  // previous kernel done, Q staged
   }
 
   if (warp == 1) {
@@ -214,11 +222,12 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
       const uint32_t idesc_o = umma_idesc(128, R, fmt, fmt, 1, 0);     // A = V page (MN-major), B = P (K-major)
       const uint32_t tS = tmem_base, tO = tmem_base + 2 * R;
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-      bool ok = true;
+      // Event-driven: S^T of the next page and P.V of the current one do not depend on each other (the first waits
+      // for its page to land, the second for the softmax warps), so whichever is ready is issued first.  Waiting
+      // for them in a fixed order would hold P.V(i) - and with it the refill of its stage - behind the load of
+      // page i + 1.
       auto issue_s = [&](int i) {
         const int stage = i & 1, buf = i & 1;
-        if (!wait_or_abort(&kv_full[stage], (i >> 1) & 1, ab, 602)) return false;
-        if (i >= 2 && !wait_or_abort(&s_empty[buf], ((i >> 1) - 1) & 1, ab, 603)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(smem + stage * kStageBytes);
 #pragma unroll
@@ -229,30 +238,46 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
           umma_f16(tS + buf * R, da, db, idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[buf]);
-        return true;
       };
-      ok = issue_s(0);
-      for (int i = 0; ok && i < n_tiles; ++i) {
-        // the next page shares its stage with page i - 1: its S^T can only be issued once that P.V has finished,
-        // which the producer's kv_empty wait already guarantees before it refills the stage
-        if (i + 1 < n_tiles) ok = issue_s(i + 1);
-        if (!ok) break;
+      auto issue_pv = [&](int i) {
         const int pb = i & 1, stage = i & 1;
-        if (!wait_or_abort(&p_ready[pb], (i >> 1) & 1, ab, 604)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(smem + stage * kStageBytes);
 #pragma unroll
-        for (int j = 0; j < kDV / 128; ++j) {       // O^T tile j: dims [128 j, 128 j + 128) = blocks 2j, 2j + 1
+        for (int k = 0; k < kKeys / 16; ++k) {      // k outer: consecutive MMAs go to four different O^T tiles
 #pragma unroll
-          for (int k = 0; k < kKeys / 16; ++k) {
+          for (int j = 0; j < kDV / 128; ++j) {     // O^T tile j: dims [128 j, 128 j + 128) = blocks 2j, 2j + 1
             uint64_t da = umma_desc_mn_sw128(v_addr + (2 * j) * kBlockBytes + k * 2048, kBlockBytes, 1024);
             uint64_t db = umma_desc_k_sw128(p_addr + pb * kPBytes + k * 32);
             umma_f16(tO + j * R, da, db, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
           }
         }
+        // o_done first: whoever has seen p_free of this tile may rely on o_done having advanced as well
+        umma_commit(o_done);
         umma_commit(&kv_empty[stage]);
         umma_commit(&p_free[pb]);
-        umma_commit(o_done);
+      };
+      int next_s = 0, next_pv = 0;
+      uint32_t spins = 0;
+      while (next_pv < n_tiles) {
+        bool progressed = false;
+        // S^T(next_s): its page has landed and its TMEM buffer has been read (at most one S^T ahead of P.V)
+        if (next_s < n_tiles && next_s <= next_pv + 1 && mbar_try_wait(&kv_full[next_s & 1], (next_s >> 1) & 1) &&
+            (next_s < 2 || mbar_try_wait(&s_empty[next_s & 1], ((next_s >> 1) - 1) & 1))) {
+          if (next_s == 4) trace_mark(p.trace, cta_id, 9);    // issuer: tile 4 has landed
+          issue_s(next_s);
+          ++next_s;
+          progressed = true;
+        }
+        if (next_pv < next_s && mbar_try_wait(&p_ready[next_pv & 1], (next_pv >> 1) & 1)) {
+          if (next_pv == 4) trace_mark(p.trace, cta_id, 12);   // issuer: P of tile 4 is in shared memory
+          issue_pv(next_pv);
+          ++next_pv;
+          progressed = true;
+        }
+        if (progressed) { spins = 0; continue; }
+        if (++spins > (1u << 20)) { ab.raise(602); break; }
+        if ((spins & 255) == 255 && ab.aborted()) break;
       }
     }
     if (p.cluster_merge) {
@@ -272,14 +297,19 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
 #pragma unroll
     for (int r = 0; r < R; ++r) { m_used[r] = -INFINITY; l_part[r] = 0.f; }
     const int p_off = (key_in_tile & 7) * 2, p_ch = (key_in_tile & 63) >> 3;
-    bool ok = true;
-    for (int i = 0; i < n_tiles && ok; ++i) {
+    // One named barrier per tile in the common case.  Every thread polls the mbarriers itself (bounded); a thread whose
+    // wait ran out keeps walking the loop with `fail` set, and the barrier below - which also tells whether any row's
+    // running maximum has to move - makes all 128 threads leave together.
+    bool ok = true, fail = false;
+    for (int i = 0; i < n_tiles; ++i) {
       const int buf = i & 1;
-      if (tid == 0) ok_slot[buf] = wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 605) ? 1 : 0;
-      named_bar_sync(1, 128);
-      if (ok_slot[buf] == 0) { ok = false; break; }
-      while (!mbar_try_wait(&s_full[buf], (i >> 1) & 1)) {}
+      if (!fail && !wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 605)) fail = true;
+      // P buffer i & 1 must have been consumed (P.V of tile i - 2).  Waiting here, before a possible rescale, also
+      // keeps o_done at most one phase behind, so that the parity wait on it below cannot pass two phases early.
+      if (i >= 2 && !fail && !wait_or_abort(&p_free[buf], ((i >> 1) - 1) & 1, ab, 606)) fail = true;
       tc_fence_after_sync();
+      if (tid == 0 && i == 0) trace_mark(p.trace, cta_id, 2);  // first S^T ready
+      if (tid == 0 && i == 4) trace_mark(p.trace, cta_id, 10);  // softmax: S^T of tile 4 ready
       float sc[R];
 #pragma unroll
       for (int c = 0; c < R; c += 16) {
@@ -295,13 +325,13 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
       const int key0 = (tile_lo + i) * kKeys;
       const int key = key0 + key_in_tile;
       const bool full = key0 + kKeys - 1 <= ctx && key0 + kKeys <= kv_end;
+      bool need = fail;   // does any score exceed its row's reference maximum by more than the slack?
       if (full) {  // every key of the page is visible to every query token: no per-row positions needed
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const float v = (key_thread && r < rows_total) ? sc[r] * p.scale_log2 : -INFINITY;
           sc[r] = v;
-          const float wm = warp_max_redux(v);
-          if (lane == (r & 31)) sMax[(buf * 4 + quarter) * R + r] = wm;
+          need |= v > m_used[r] + kMaxSlack;
         }
       } else {
         int tok = 0, hh = 0;  // row r = token tok, head hh (walked without divisions)
@@ -310,55 +340,60 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
           const bool in = key_thread && r < rows_total && key < kv_end && key <= ctx + tok;
           const float v = in ? sc[r] * p.scale_log2 : -INFINITY;
           sc[r] = v;
-          const float wm = warp_max_redux(v);
-          if (lane == (r & 31)) sMax[(buf * 4 + quarter) * R + r] = wm;
+          need |= v > m_used[r] + kMaxSlack;
           if (++hh == nh) { hh = 0; ++tok; }
         }
       }
-      named_bar_sync(1, 128);
-      bool rescale = false;
+      if (bar_red_or(1, 128, need)) {
+        // ---- rare after the first tiles: exchange the per-warp maxima, move the reference maxima, rescale O^T
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const float* mm = sMax + buf * 4 * R + r;
-        const float tm = fmaxf(fmaxf(mm[0], mm[R]), fmaxf(mm[2 * R], mm[3 * R]));
-        float alpha = 1.f;
-        if (tm > m_used[r] + kMaxSlack) {
-          alpha = exp2f(m_used[r] - tm);
-          m_used[r] = tm;
-          rescale = true;
+        for (int r = 0; r < R; ++r) {
+          const float wm = warp_max_redux(sc[r]);
+          if (lane == (r & 31)) sMax[quarter * R + r] = wm;
         }
-        if (tid == 0) sAlpha[r] = alpha;
-        const float ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
-        sc[r] = exp2f(sc[r] - ms);
-        l_part[r] = l_part[r] * alpha + sc[r];
-      }
-      if (i >= 2) {
-        if (tid == 0) ok_slot[buf] = wait_or_abort(&p_free[buf], ((i >> 1) - 1) & 1, ab, 606) ? 1 : 0;
+        const bool warp_failed = __any_sync(0xffffffffu, fail);
+        if (lane == 0) ok_slot[quarter] = warp_failed ? 0 : 1;
         named_bar_sync(1, 128);
-        if (ok_slot[buf] == 0) { ok = false; break; }
-        while (!mbar_try_wait(&p_free[buf], ((i >> 1) - 1) & 1)) {}
-      }
-      if (rescale && i > 0) {
-        if (tid == 0) ok_slot[buf] = wait_or_abort(o_done, (i - 1) & 1, ab, 608) ? 1 : 0;
-        named_bar_sync(1, 128);   // also publishes sAlpha
-        if (ok_slot[buf] == 0) { ok = false; break; }
-        while (!mbar_try_wait(o_done, (i - 1) & 1)) {}
-        tc_fence_after_sync();
-#pragma unroll 1
-        for (int j = 0; j < kDV / 128; ++j) {
+        if ((ok_slot[0] & ok_slot[1] & ok_slot[2] & ok_slot[3]) == 0) { ok = false; break; }
+        float alpha[R];
+        bool rescale = false;
 #pragma unroll
-          for (int c = 0; c < R; c += 16) {
-            uint32_t orr[16];
-            tmem_ld_x16(tO + j * R + c, orr);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * sAlpha[c + e]);
-            tmem_st_x16(tO + j * R + c, orr);
+        for (int r = 0; r < R; ++r) {
+          const float* mm = sMax + r;
+          const float tm = fmaxf(fmaxf(mm[0], mm[R]), fmaxf(mm[2 * R], mm[3 * R]));
+          alpha[r] = 1.f;
+          if (tm > m_used[r] + kMaxSlack) {
+            alpha[r] = exp2f(m_used[r] - tm);   // 0 when the row had no key yet
+            m_used[r] = tm;
+            l_part[r] *= alpha[r];
+            rescale = true;
           }
         }
-        tmem_st_wait();
+        if (rescale && i > 0) {   // same decision in every thread: all of them read the same maxima
+          if (!wait_or_abort(o_done, (i - 1) & 1, ab, 608)) fail = true;
+          tc_fence_after_sync();
+#pragma unroll 1
+          for (int j = 0; j < kDV / 128; ++j) {
+#pragma unroll
+            for (int c = 0; c < R; c += 16) {
+              uint32_t orr[16];
+              tmem_ld_x16(tO + j * R + c, orr);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * alpha[c + e]);
+              tmem_st_x16(tO + j * R + c, orr);
+            }
+          }
+          tmem_st_wait();
+        }
       }
-      if (key_thread) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
+        sc[r] = exp2f(sc[r] - ms);
+        l_part[r] += sc[r];
+      }
+      if (key_thread && !fail) {
         uint8_t* base = sP + buf * kPBytes + p_off;
 #pragma unroll
         for (int r = 0; r < R; ++r)
@@ -366,19 +401,21 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
+      const bool warp_failed = __any_sync(0xffffffffu, fail);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[buf]);
+      if (lane == 0 && !warp_failed) mbar_arrive(&p_ready[buf]);
+      if (tid == 0 && i == 4) trace_mark(p.trace, cta_id, 11);  // softmax: P of tile 4 written
     }
+    if (fail) ok = false;
+    if (tid == 0) trace_mark(p.trace, cta_id, 3);  // last P written
     if (ok && n_tiles > 0) {
-      const int last = n_tiles - 1;
-      if (tid == 0) ok_slot[0] = wait_or_abort(o_done, last & 1, ab, 607) ? 1 : 0;
-      named_bar_sync(1, 128);
-      ok = ok_slot[0] != 0;
-      if (ok) {
-        while (!mbar_try_wait(o_done, last & 1)) {}
-        tc_fence_after_sync();
-      }
+      // A parity wait is only meaningful when the barrier is at most one phase behind the awaited one; the p_free
+      // wait of the last tile guarantees P.V(n - 3), so P.V(n - 2) is awaited first, then the last one.
+      if (n_tiles >= 2 && !wait_or_abort(o_done, (n_tiles - 2) & 1, ab, 607)) ok = false;
+      if (ok && !wait_or_abort(o_done, (n_tiles - 1) & 1, ab, 607)) ok = false;
+      tc_fence_after_sync();
     }
+    ok = bar_red_or(1, 128, !ok) == 0;   // one thread's time-out ends the tile for all
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float v = l_part[r];
@@ -388,6 +425,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
     }
     named_bar_sync(1, 128);
     const int d = quarter * 32 + lane;               // output dim within an O^T tile (M = 128: lane = row)
+    if (tid == 0) trace_mark(p.trace, cta_id, 4);  // last P.V done
     if (p.cluster_merge) {
       // ---- split merge inside the cluster: CTA c owns output dims [c * DS, (c + 1) * DS).  Every CTA stores its
       // un-normalised partial O (and per row its running maximum and sum) into the owners' shared memory, which
@@ -398,6 +436,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
       float* recv = reinterpret_cast<float*>(smem);                   // [S sources][R rows][DS dims]
       float* recv_ml = reinterpret_cast<float*>(smem + kStageBytes);  // [S sources][R rows][max, sum]
       cluster_arrive(); cluster_wait();  // A
+      if (tid == 0) trace_mark(p.trace, cta_id, 5);
       if (served) {
         if (tid < R) {
           float m_mine = -INFINITY;  // m_used[tid] without a dynamically indexed register array
@@ -431,104 +470,183 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
         }
       }
       cluster_arrive(); cluster_wait();  // B
+      if (tid == 0) trace_mark(p.trace, cta_id, 6);
+      // per row: the weight of every source (already divided by the common denominator) and the output row
+      float* sW = sMax;                                   // [S][R] (the per-tile maxima are no longer needed)
+      long long* sRow = reinterpret_cast<long long*>(smem + kStageBytes + 4096);  // [R]
+      if (tid < R) {
+        const int r = tid;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < S; ++s2) M = fmaxf(M, recv_ml[(s2 * R + r) * 2]);
+        float den = 0.f;
+        for (int s2 = 0; s2 < S; ++s2) {
+          const float ms = recv_ml[(s2 * R + r) * 2];
+          const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+          den = fmaf(recv_ml[(s2 * R + r) * 2 + 1], w, den);
+          sW[s2 * R + r] = w;
+        }
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        for (int s2 = 0; s2 < S; ++s2) sW[s2 * R + r] *= inv;
+        sRow[r] = (r < rows_total && served) ? (long long)(qs + r / nh) * p.N + head0 + r % nh : 0;
+      }
+      named_bar_sync(1, 128);
       if (served) {
-        for (int idx = tid; idx < rows_total * DS; idx += 128) {
-          const int r = idx / DS, dl = idx % DS;
-          float M = -INFINITY;
-          for (int s2 = 0; s2 < S; ++s2) M = fmaxf(M, recv_ml[(s2 * R + r) * 2]);
-          float den = 0.f, acc = 0.f;
+        const int DS4 = DS / 4, sh = 31 - __clz(DS4);      // DS4 is a power of two (16, 32 or 64)
+        for (int idx = tid; idx < rows_total * DS4; idx += 128) {
+          const int r = idx >> sh, d4 = idx & (DS4 - 1);
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int s2 = 0; s2 < S; ++s2) {
-            const float ms = recv_ml[(s2 * R + r) * 2];
-            const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-            den = fmaf(recv_ml[(s2 * R + r) * 2 + 1], w, den);
-            acc = fmaf(recv[((size_t)s2 * R + r) * DS + dl], w, acc);
+            const float w = sW[s2 * R + r];
+            const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)s2 * R + r) * DS + d4 * 4);
+            acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
+            acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
           }
-          const int64_t orow = (int64_t)(qs + r / nh) * p.N + head0 + r % nh;
-          reinterpret_cast<T*>(p.out)[orow * kDV + split * DS + dl] = from_float<T>(den > 0.f ? acc / den : 0.f);
+          alignas(8) T o4[4] = {from_float<T>(acc.x), from_float<T>(acc.y), from_float<T>(acc.z), from_float<T>(acc.w)};
+          *reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.out) + sRow[r] * kDV + split * DS + d4 * 4) =
+              *reinterpret_cast<const uint2*>(o4);
         }
       }
-    } else if (ok && served) {
+    } else if (served) {
+      if (tid == 0) trace_mark(p.trace, cta_id, 5);  // row sums exchanged
+      // per row, once: 1 / sum, the output row, the log-sum-exp (instead of divisions inside the store loops)
+      float* sInv = sMax;                                                  // [R]
+      long long* sRow = reinterpret_cast<long long*>(sMax + 2 * R);        // [R]
+      if (tid < R) {
+        const int r = tid;
+        float m_mine = -INFINITY;
+#pragma unroll
+        for (int rr = 0; rr < R; ++rr) m_mine = (tid == rr) ? m_used[rr] : m_mine;
+        const float L = sSum[r] + sSum[R + r] + sSum[2 * R + r] + sSum[3 * R + r];
+        const int64_t orow = r < rows_total ? (int64_t)(qs + r / nh) * p.N + head0 + r % nh : 0;
+        sInv[r] = (ok && L > 0.f) ? 1.f / L : 0.f;
+        sRow[r] = orow;
+        if (p.num_splits > 1 && r < rows_total)
+          p.ws_lse[(int64_t)split * p.T * p.N + orow] = (ok && L > 0.f) ? m_mine + log2f(L) : -INFINITY;
+      }
+      named_bar_sync(1, 128);
+      if (tid == 0) trace_mark(p.trace, cta_id, 16);
+      T* outp = reinterpret_cast<T*>(p.out);
+      float* wsp = p.ws_o + (int64_t)split * p.T * p.N * kDV;
 #pragma unroll 1
       for (int j = 0; j < kDV / 128; ++j) {
 #pragma unroll
         for (int c = 0; c < R; c += 16) {
           uint32_t orr[16];
-          if (n_tiles > 0) {
+          if (ok && n_tiles > 0) {
             tmem_ld_x16(tO + j * R + c, orr);
             tmem_ld_wait();
           } else {
 #pragma unroll
             for (int e = 0; e < 16; ++e) orr[e] = 0;
           }
+          // row scale and offset first, into registers: the compiler cannot move shared-memory loads across the
+          // global stores below (both are generic pointers to it), and 16 load -> store chains in a row are slow
+          float inv[16];
+          int64_t off[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int r = c + e;
-            if (r < rows_total) {
-              const float L = sSum[r] + sSum[R + r] + sSum[2 * R + r] + sSum[3 * R + r];
-              const int tok = r / nh, hh = head0 + r % nh;
-              const int64_t orow = (int64_t)(qs + tok) * p.N + hh;
-              const float inv = L > 0.f ? 1.f / L : 0.f;
-              const float o = __uint_as_float(orr[e]) * inv;
-              if (p.num_splits == 1) {
-                reinterpret_cast<T*>(p.out)[orow * kDV + j * 128 + d] = from_float<T>(o);
-              } else {
-                p.ws_o[((int64_t)split * p.T * p.N + orow) * kDV + j * 128 + d] = o;
-                if (j == 0 && d == 0) {
-                  const float Ms = (m_used[r] == -INFINITY) ? 0.f : m_used[r];
-                  p.ws_lse[(int64_t)split * p.T * p.N + orow] = (L > 0.f) ? Ms + log2f(L) : -INFINITY;
-                }
-              }
-            }
+          for (int e = 0; e < 16; ++e) { inv[e] = sInv[c + e]; off[e] = sRow[c + e] * kDV + j * 128 + d; }
+          if (p.num_splits == 1) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (c + e < rows_total) outp[off[e]] = from_float<T>(__uint_as_float(orr[e]) * inv[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (c + e < rows_total) wsp[off[e]] = __uint_as_float(orr[e]) * inv[e];
           }
         }
       }
     }
     if (p.num_splits > 1 && !p.cluster_merge && served) {
+      if (tid == 0) trace_mark(p.trace, cta_id, 17);
       __threadfence();
+      if (tid == 0) trace_mark(p.trace, cta_id, 18);
       named_bar_sync(1, 128);
       const int ticket_idx = req * gridDim.x + blockIdx.x;
       if (tid == 0) *s_last = (atomicAdd(&g_tickets[ticket_idx], 1) == p.num_splits - 1);
       named_bar_sync(1, 128);
+      if (tid == 0) trace_mark(p.trace, cta_id, 6);  // partial stored, ticket taken
       if (*s_last) {
         __threadfence();
         const int64_t sstride = p.T * p.N;
-        for (int idx = tid; idx < p.num_splits * R; idx += 128) {
+        const int S = p.num_splits;
+        float* sW = sLse;                                   // [S][R]: log-sum-exps, then normalised weights
+        const long long* sRow = reinterpret_cast<const long long*>(sMax + 2 * R);  // output rows (set in the epilogue)
+        for (int idx = tid; idx < S * R; idx += 128) {
           const int s2 = idx / R, r = idx % R;
-          float v = -INFINITY;
-          if (r < rows_total) {
-            const int64_t orow = (int64_t)(qs + r / nh) * p.N + head0 + r % nh;
-            v = __ldcg(p.ws_lse + s2 * sstride + orow);
-          }
-          sLse[idx] = v;
+          sLse[idx] = r < rows_total ? __ldcg(p.ws_lse + s2 * sstride + sRow[r]) : -INFINITY;
         }
         named_bar_sync(1, 128);
-        for (int r = 0; r < rows_total; ++r) {
-          const int64_t orow = (int64_t)(qs + r / nh) * p.N + head0 + r % nh;
+        if (tid < R) {
+          const int r = tid;
           float M = -INFINITY;
-          for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, sLse[s2 * R + r]);
-          const float Ms = (M == -INFINITY) ? 0.f : M;
-          float den = 0.f, acc[kDV / 128] = {0.f, 0.f, 0.f, 0.f};
-          for (int s2 = 0; s2 < p.num_splits; ++s2) {
-            const float w = exp2f(sLse[s2 * R + r] - Ms);
+          for (int s2 = 0; s2 < S; ++s2) M = fmaxf(M, sLse[s2 * R + r]);
+          float den = 0.f;
+          for (int s2 = 0; s2 < S; ++s2) {
+            const float l = sLse[s2 * R + r];
+            const float w = (l == -INFINITY) ? 0.f : exp2f(l - M);
             den += w;
-            if (w > 0.f) {
-              const float* src = p.ws_o + (s2 * sstride + orow) * kDV + d;
-#pragma unroll
-              for (int j = 0; j < kDV / 128; ++j) acc[j] += __ldcg(src + j * 128) * w;
-            }
+            sW[s2 * R + r] = w;
           }
           const float inv = den > 0.f ? 1.f / den : 0.f;
-#pragma unroll
-          for (int j = 0; j < kDV / 128; ++j)
-            reinterpret_cast<T*>(p.out)[orow * kDV + j * 128 + d] = from_float<T>(acc[j] * inv);
+          for (int s2 = 0; s2 < S; ++s2) sW[s2 * R + r] *= inv;
+        }
+        named_bar_sync(1, 128);
+        // The partials (S x rows x 2 KB, in L2) come in with bulk copies - a few per split, all in flight at once -
+        // into the cache-page stages, G rows per pass; plain loads would keep far fewer bytes in flight from one SM.
+        if (tid == 0) trace_mark(p.trace, cta_id, 13);  // merger: weights ready
+        float* land = reinterpret_cast<float*>(smem);        // [S][G rows][512]
+        const int G = max(1, min(rows_total, (kStages * kStageBytes / (kDV * 4)) / S));
+        bool merged_ok = true;
+        int pass = 0;
+        for (int g0 = 0; g0 < rows_total; g0 += G, ++pass) {
+          const int g1 = min(rows_total, g0 + G);
+          if (warp == 2) {
+            // the other CTAs' partials were acquired through the generic proxy (ticket + fence); order the bulk
+            // copies, which read through the async proxy, behind that
+            asm volatile("fence.proxy.async;" ::: "memory");
+            if (lane == 0) mbar_expect_tx(merge_bar, (uint32_t)(S * (g1 - g0) * kDV * 4));
+            __syncwarp();
+            for (int s2 = lane; s2 < S; s2 += 32) {
+              int r = g0;
+              while (r < g1) {   // runs of consecutive output rows (one per query token) are contiguous in the workspace
+                int e = r + 1;
+                while (e < g1 && sRow[e] == sRow[e - 1] + 1) ++e;
+                bulk_load_1d(land + ((size_t)s2 * G + (r - g0)) * kDV, p.ws_o + (s2 * sstride + sRow[r]) * kDV,
+                             (uint32_t)((e - r) * kDV * 4), merge_bar);
+                r = e;
+              }
+            }
+          }
+          if (!wait_or_abort(merge_bar, pass & 1, ab, 609)) merged_ok = false;
+          if (bar_red_or(1, 128, !merged_ok)) break;
+          if (tid == 0 && pass == 0) trace_mark(p.trace, cta_id, 14);  // merger: first pass landed
+          for (int r = g0; r < g1; ++r) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int s2 = 0; s2 < S; ++s2) {
+              const float w = sW[s2 * R + r];
+              float4 v = *reinterpret_cast<const float4*>(land + ((size_t)s2 * G + (r - g0)) * kDV + tid * 4);
+              if (!(w > 0.f)) v = make_float4(0.f, 0.f, 0.f, 0.f);  // an empty split's rows may hold anything
+              acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
+              acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
+            }
+            alignas(8) T o4[4] = {from_float<T>(acc.x), from_float<T>(acc.y), from_float<T>(acc.z), from_float<T>(acc.w)};
+            *reinterpret_cast<uint2*>(reinterpret_cast<T*>(p.out) + sRow[r] * kDV + tid * 4) =
+                *reinterpret_cast<const uint2*>(o4);
+          }
+          if (tid == 0 && pass == 0) trace_mark(p.trace, cta_id, 19);
+          named_bar_sync(1, 128);   // the next pass overwrites the landing buffer
         }
         if (tid == 0) g_tickets[ticket_idx] = 0;
+        if (tid == 0) trace_mark(p.trace, cta_id, 15);  // merger: done
       }
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 64) trace_mark(p.trace, cta_id, 7);  // end
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -549,8 +667,36 @@ static int launch_r(const Params& p, const CUtensorMap& tm, int B, int head_grou
   return (int)launch_pdl(kern, dim3(head_groups, B * p.num_splits), dim3(kThreads), smem, st, tm, p);
 }
 
+template <typename T, int R>
+static int max_clusters_r(int S) {
+  auto kern = mla_decode_umma_kernel<T, R>;
+  const size_t smem = 1024 + (size_t)kStages * kStageBytes + kBlocks * R * 128 + 2 * R * 128 + 4096 + 16 * R * 4;
+  if (ensure_dynamic_smem((const void*)kern, (int)smem) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, S * 64);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = S; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+  return n;
+}
+
 }  // namespace mlad
 }  // namespace b200
+
+// How many clusters of S CTAs of the MLA decode kernel (R = 16 or 32 operand rows) the current device holds at once;
+// the host sizes the split count so that a launch is one wave.
+extern "C" int b200_mla_decode_max_clusters(int R, int S, int dtype) {
+  using namespace b200;
+  if (S < 1 || S > 8) return 0;
+  if (dtype == 2) return R == 16 ? mlad::max_clusters_r<__half, 16>(S) : mlad::max_clusters_r<__half, 32>(S);
+  return R == 16 ? mlad::max_clusters_r<__nv_bfloat16, 16>(S) : mlad::max_clusters_r<__nv_bfloat16, 32>(S);
+}
 
 // Dense paged MLA decode on tcgen05 (see the header of this file).  `tmap`: the cache as a 2-D [blocks * 64, 576]
 // 16-bit tensor with 64 x 64 boxes and 128-byte swizzle.  Serves block_size 64 and max_query_len <= 32; heads are
@@ -559,7 +705,7 @@ extern "C" int b200_mla_decode_umma(void* out, const void* q, const void* tmap, 
                                     const int* seq_lens, const int* qsl, float* ws_o, float* ws_lse, int* status,
                                     int64_t T_, int B, int N, int block_size, int max_blocks, int64_t num_blocks,
                                     int max_query_len, int num_splits, float scale, int early_meta, int dtype,
-                                    cudaStream_t st) {
+                                    unsigned long long* trace, cudaStream_t st) {
   using namespace b200;
   if (B == 0 || T_ == 0) return 0;
   if (block_size != mlad::kKeys || max_query_len < 1 || max_query_len > 32 || num_splits < 1 || num_splits > 16) return 3;
@@ -573,7 +719,7 @@ extern "C" int b200_mla_decode_umma(void* out, const void* q, const void* tmap, 
   mlad::Params p;
   p.cluster_merge = cluster_merge ? 1 : 0;
   p.q = q; p.out = out; p.ws_o = ws_o; p.ws_lse = ws_lse; p.block_tables = block_tables; p.seq_lens = seq_lens;
-  p.qsl = qsl; p.status = status; p.N = N; p.heads_per_cta = H; p.max_blocks = max_blocks; p.num_splits = num_splits;
+  p.qsl = qsl; p.status = status; p.trace = trace; p.N = N; p.heads_per_cta = H; p.max_blocks = max_blocks; p.num_splits = num_splits;
   p.early_meta = early_meta; p.num_blocks = num_blocks; p.T = T_;
   p.scale_log2 = scale * 1.4426950408889634f;
   const CUtensorMap& tm = *reinterpret_cast<const CUtensorMap*>(tmap);

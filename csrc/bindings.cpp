@@ -704,6 +704,17 @@ void decode_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor
 }
 
 // Dense paged MLA decode on tcgen05: q [T, N, 576], kv [blocks, 64, 576] -> out [T, N, 512].
+// Optional phase-trace buffer (int64 [>= CTAs * 24]) for the kernels that support it; an undefined tensor switches it off.
+at::Tensor g_kernel_trace;
+void set_kernel_trace(const c10::optional<at::Tensor>& t) {
+  if (t.has_value()) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous());
+    g_kernel_trace = *t;
+  } else {
+    g_kernel_trace = at::Tensor();
+  }
+}
+
 void mla_decode_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, const at::Tensor& block_tables,
                      const at::Tensor& seq_lens, const at::Tensor& qsl, const c10::optional<at::Tensor>& ws_o,
                      const c10::optional<at::Tensor>& ws_lse, int64_t max_query_len, int64_t num_splits, double scale,
@@ -730,7 +741,10 @@ void mla_decode_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, 
                              qsl.data_ptr<int>(), ws_o.has_value() ? ws_o->data_ptr<float>() : nullptr,
                              ws_lse.has_value() ? ws_lse->data_ptr<float>() : nullptr, gs.status.data_ptr<int>(),
                              q.size(0), B, q.size(1), kv.size(1), block_tables.stride(0), kv.size(0), max_query_len,
-                             num_splits, (float)scale, early_meta ? 1 : 0, dtype_code(q), stream()),
+                             num_splits, (float)scale, early_meta ? 1 : 0, dtype_code(q),
+                             (g_kernel_trace.defined() && g_kernel_trace.numel() >= (int64_t)B * num_splits * 64 * 24)
+                                 ? reinterpret_cast<unsigned long long*>(g_kernel_trace.data_ptr<int64_t>()) : nullptr,
+                             stream()),
         "mla_decode_umma");
 }
 
@@ -1094,6 +1108,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("decode_attention_umma", &decode_attention_umma);
   m.def("mla_decode_umma", &mla_decode_umma);
+  m.def("set_kernel_trace", &set_kernel_trace);
+  m.def("mla_decode_max_clusters", [](int64_t R, int64_t S, int64_t dtype) {
+    return (int64_t)b200_mla_decode_max_clusters((int)R, (int)S, (int)dtype);
+  });
   m.def("mla_attention", &mla_attention);
   m.def("indexer_logits", &indexer_logits);
   m.def("topk_rows", &topk_rows);

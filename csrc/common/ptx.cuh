@@ -228,6 +228,29 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// named barrier over n threads that also ORs a predicate across them
+__device__ __forceinline__ bool bar_red_or(int id, int n, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(n), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+// Untiled bulk copy global -> shared (no multicast): both addresses 16-byte aligned, size a multiple of 16 bytes;
+// completes `bytes` of transaction count on `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // ---- thread-block clusters: rank, barrier, distributed shared memory
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -254,6 +277,17 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// ---- in-kernel phase trace: nanosecond timestamps of a CTA's phases, written to a caller-provided buffer
+// ([CTA][24 slots]; null = off).  Read on the host to see where a latency-bound kernel spends its time.
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_mark(unsigned long long* trace, int cta, int slot) {
+  if (trace != nullptr) trace[(size_t)cta * 24 + slot] = globaltimer_ns();
 }
 
 }  // namespace b200

@@ -32,6 +32,41 @@ _UMMA_MAX_QLEN = 4
 _FORCE_WORKSPACE = [False]  # tests: merge 2/4/8 splits through the global workspace instead of the cluster
 
 
+_MAX_CLUSTERS: dict = {}
+
+
+def _max_clusters(R: int, S: int, dtype, device) -> int:
+    key = (R, S, dtype, str(device))
+    n = _MAX_CLUSTERS.get(key)
+    if n is None:
+        with torch.cuda.device(device):
+            n = _MAX_CLUSTERS[key] = int(_ext.C().mla_decode_max_clusters(R, S, 2 if dtype == torch.float16 else 1))
+    return n
+
+
+def plan_mla_splits(units: int, tiles: int, R: int, dtype, device):
+    """``(num_splits, merge in a cluster?)`` for ``units`` (request, head group) pairs of ``tiles`` cache pages.
+
+    Splits of one unit either form a thread-block cluster of 2 / 4 / 8 CTAs that merges in shared memory - only
+    when every cluster of the launch is resident at once (the device holds fewer clusters of 8 than SMs / 8:
+    a cluster lives inside one GPC) - or go through a workspace that the last CTA to finish combines, which costs
+    about three more pages of time.  The cheaper of the two estimates wins."""
+    sms = sm_count(device)
+    cap = max(1, tiles // 2)
+    best = (1, False, tiles)
+    for S in (2, 4, 8):
+        if S <= cap and units <= _max_clusters(R, S, dtype, device):
+            cost = -(-tiles // S)
+            if cost < best[2]:
+                best = (S, True, cost)
+    Sw = int(max(1, min(sms // max(1, units), 16, cap)))
+    if Sw > 1:
+        cost = -(-tiles // Sw) + 3
+        if cost < best[2]:
+            best = (Sw, False, cost)
+    return best[0], best[1]
+
+
 def mla_decode_umma(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, max_query_len, max_seq_len,
                     num_splits=None, stable_metadata: bool = False):
     """Dense paged MLA decode on tcgen05: every request has at most ``max_query_len`` (<= 4) query tokens."""
@@ -41,12 +76,10 @@ def mla_decode_umma(q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
     R = 16 if N * max_query_len <= 16 else 32
     groups = -(-N // (R // max_query_len))
     if num_splits is None:
-        tiles = max(1, -(-max_seq_len // 64))
-        want = int(max(1, min(sm_count(q.device) // max(1, groups * B), 16, max(1, tiles // 2))))
-        # up to 8 splits form a thread-block cluster that merges in shared memory (powers of two only: other
-        # cluster sizes schedule badly); 16 splits - few requests with long contexts - go through a workspace
-        num_splits = 16 if want >= 16 else 1 << (want.bit_length() - 1)
-    cluster = num_splits in (2, 4, 8) and not _FORCE_WORKSPACE[0]
+        num_splits, cluster = plan_mla_splits(groups * B, max(1, -(-max_seq_len // 64)), R, q.dtype, q.device)
+    else:
+        cluster = num_splits in (2, 4, 8) and groups * B <= _max_clusters(R, num_splits, q.dtype, q.device)
+    cluster = cluster and not _FORCE_WORKSPACE[0]
     ws_o, ws_lse = _ws(T, N, num_splits, q.device) if num_splits > 1 and not cluster else (None, None)
     _ext.C().mla_decode_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, ws_o, ws_lse, max_query_len,
                              num_splits, scale, bool(stable_metadata))
