@@ -261,6 +261,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
+      // The first full barrier completes only after the producer's own dependency wait (the activations come from
+      // the previous kernel).  Waiting for the dependency here, unbounded by nature, keeps the bounded wait below
+      // for what it is meant for - the copies - however long the previous kernel (say, an all-reduce that waits
+      // for a late peer) takes.
+      griddep_wait();
       const uint32_t idesc = umma_idesc(BM, BN, fmt, fmt);
       int stage = 0;
       uint32_t phase = 0;

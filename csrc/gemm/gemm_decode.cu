@@ -196,6 +196,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
+      // the first full barrier needs the activations, i.e. the previous kernel: wait for that dependency here
+      // (unbounded by nature) so that the bounded wait below covers only the copies
+      griddep_wait();
       const uint32_t idesc = kFp8 ? umma_idesc(BM, BN, 0, 0) : umma_idesc(BM, BN, fmt, fmt);
       int stage = 0;
       uint32_t phase = 0;

@@ -83,6 +83,20 @@ class DecodeGraphs:
         self.graphs[key], self.logits[key], self.hidden[key] = g, logits, sel
         if self.watcher is not None:
             self.watcher.capture(str(key), self._watched(md, input_ids))
+        self._rendezvous()
+
+    @staticmethod
+    def _rendezvous():
+        """Ranks capture the same graph at the same step, but a capture of a deep model takes seconds and not the
+        same time everywhere; without this the first replay of the fastest rank would sit in its first peer wait
+        for the difference."""
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            torch.cuda.synchronize()
+            if dist.get_backend() == "nccl":
+                dist.barrier(device_ids=[torch.cuda.current_device()])
+            else:
+                dist.barrier()
 
     @torch.inference_mode()
     def run(self, md: AttentionMetadata, input_ids, sp):

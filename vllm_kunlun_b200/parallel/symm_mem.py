@@ -11,6 +11,8 @@ All cross-GPU waits are bounded and report through a status word; nothing here u
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -52,7 +54,9 @@ class PeerBuffers:
         self.epochs = torch.zeros(C.allreduce_max_ctas(), dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.max_ctas = C.allreduce_max_ctas()
-        self.spin_limit = 1 << 22
+        # polls before a wait on a peer gives up (about 10 s): long enough for a peer that is still capturing a
+        # CUDA graph or loading a module; failure-detection tests pass their own small limit
+        self.spin_limit = int(os.environ.get("B200_PEER_SPIN_LIMIT", str(1 << 26)))
         self.one_shot_max_bytes = min(self.parity_bytes, 2 << 20)
         self.launches = 0
         torch.cuda.synchronize()
