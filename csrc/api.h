@@ -118,6 +118,11 @@ int b200_reshape_and_cache(const void* k, const void* v, void* kv_cache, const i
 int b200_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* cache, const int64_t* slots, int64_t T,
                               int rank, int rope, int64_t total_slots, int64_t kvc_stride, int64_t kpe_stride, int fp8,
                               int dtype, cudaStream_t st);
+int b200_indexer_prep(const void* q, const void* k, const void* ln_w, const void* ln_b, const int64_t* positions,
+                      const float* cos_sin, const void* head_w, float wscale, void* q_out, float* w_out, void* cache,
+                      const int64_t* slots, int64_t T, int H, int64_t max_pos, int64_t total_slots, int64_t q_stride,
+                      int64_t k_stride, int64_t hw_stride, float eps, int ue8m0, int64_t q_lo, int64_t q_hi, int dtype,
+                      cudaStream_t st);
 int b200_indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slots, int64_t T, int64_t total_slots,
                                    int ue8m0, int64_t k_stride, int dtype, cudaStream_t st);
 int b200_convert_req_index(int32_t* out, const int32_t* req_id, const int32_t* block_table, const int32_t* idx,
@@ -163,7 +168,7 @@ int b200_mla_attention(void* out, const void* q, const void* kv, const int* bloc
 // Lightning indexer: fp8 scores over the paged 132-byte key cache, then per-row top-k (unordered, -1 padded)
 int b200_indexer_logits(float* logits, const void* q_fp8, const float* w, const void* k_cache, const int* block_tables,
                         const int* seq_lens, const int* qsl, const int* req_of_token, int64_t T, int B, int block_size,
-                        int max_blocks, int64_t total_slots, int64_t ld_logits, cudaStream_t st);
+                        int max_blocks, int64_t total_slots, int64_t ld_logits, int64_t t0, cudaStream_t st);
 int b200_topk_rows(int* out, const float* logits, const int* row_len, int64_t rows, int64_t ld, int k, int64_t max_len,
                    cudaStream_t st);
 

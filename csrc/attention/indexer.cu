@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(128) indexer_logits_kernel(
     float* __restrict__ logits, const uint8_t* __restrict__ q, const float* __restrict__ w,
     const uint8_t* __restrict__ k_cache, const int* __restrict__ block_tables, const int* __restrict__ seq_lens,
     const int* __restrict__ qsl, const int* __restrict__ req_of_token, int B, int block_size, int max_blocks,
-    int64_t total_slots, int64_t ld_logits) {
+    int64_t total_slots, int64_t ld_logits, int64_t t0) {
   __shared__ __align__(16) uint8_t sQ[kIdxH * kIdxD];
   __shared__ __align__(16) uint8_t sK[4][16 * kIdxD];
   __shared__ float sW[kIdxH];
@@ -51,7 +51,8 @@ __global__ void __launch_bounds__(128) indexer_logits_kernel(
   const int req = req_of_token[t];
   if (req < 0 || req >= B) return;
   const int qs = qsl[req], q_len = qsl[req + 1] - qs;
-  const int n_keys = seq_lens[req] - q_len + (int)(t - qs) + 1;
+  // rows are tokens t0 .. t0 + gridDim.y of the batch (a rank may score a slice of the tokens only)
+  const int n_keys = seq_lens[req] - q_len + (int)(t + t0 - qs) + 1;
   const int key_lo = blockIdx.x * kIdxChunk;
   float* out = logits + t * ld_logits;
   if (key_lo >= n_keys) {
@@ -216,12 +217,12 @@ using namespace b200;
 extern "C" int b200_indexer_logits(float* logits, const void* q_fp8, const float* w, const void* k_cache,
                                    const int* block_tables, const int* seq_lens, const int* qsl,
                                    const int* req_of_token, int64_t T_, int B, int block_size, int max_blocks,
-                                   int64_t total_slots, int64_t ld_logits, cudaStream_t st) {
+                                   int64_t total_slots, int64_t ld_logits, int64_t t0, cudaStream_t st) {
   if (T_ == 0) return 0;
   dim3 grid((unsigned)((ld_logits + kIdxChunk - 1) / kIdxChunk), (unsigned)T_);
   return (int)launch_pdl(indexer_logits_kernel, grid, dim3(128), 0, st, logits, (const uint8_t*)q_fp8, w,
                          (const uint8_t*)k_cache, block_tables, seq_lens, qsl, req_of_token, B, block_size, max_blocks,
-                         total_slots, ld_logits);
+                         total_slots, ld_logits, t0);
 }
 
 extern "C" int b200_topk_rows(int* out, const float* logits, const int* row_len, int64_t rows, int64_t ld, int k,

@@ -627,6 +627,34 @@ void indexer_k_quant_and_cache(const at::Tensor& k, at::Tensor cache, const at::
                                        cache.size(0) * cache.size(1), ue8m0, k.stride(0), dtype_code(k), stream()),
         "indexer_k_quant_and_cache");
 }
+// Fused indexer operand preparation: returns (q_fp8 [T, H, 128] uint8, w [T, H] float) and writes the key rows.
+std::vector<at::Tensor> indexer_prep(const at::Tensor& q, const at::Tensor& k, const at::Tensor& ln_w, const at::Tensor& ln_b,
+                                     const at::Tensor& positions, const at::Tensor& cos_sin, const at::Tensor& head_w,
+                                     double wscale, at::Tensor cache, const at::Tensor& slots, double eps, bool ue8m0,
+                                     int64_t q_lo) {
+  // q and head_w hold tokens [q_lo, q_lo + q.size(0)) of the k.size(0) tokens in the batch
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128 && k.dim() == 2 && k.size(1) == 128 &&
+              k.stride(1) == 1 && head_w.dim() == 2 && head_w.stride(1) == 1);
+  TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == ln_w.scalar_type() &&
+              q.scalar_type() == ln_b.scalar_type() && q.scalar_type() == head_w.scalar_type());
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && cos_sin.size(-1) == 64,
+              "indexer_prep: rotary dim 64");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && slots.scalar_type() == at::kLong && positions.is_contiguous() &&
+              slots.is_contiguous());
+  TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte && cache.size(-1) == 132);
+  const int64_t T = k.size(0), Tq = q.size(0), H = q.size(1);
+  TORCH_CHECK(q_lo >= 0 && q_lo + Tq <= T && head_w.size(0) == Tq && head_w.size(1) == H && positions.numel() == T &&
+              slots.numel() >= T);
+  auto q_out = at::empty({Tq, H, 128}, q.options().dtype(at::kByte));
+  auto w_out = at::empty({Tq, H}, q.options().dtype(at::kFloat));
+  check(b200_indexer_prep(q.data_ptr(), k.data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(), positions.data_ptr<int64_t>(),
+                          cos_sin.data_ptr<float>(), head_w.data_ptr(), (float)wscale, q_out.data_ptr(),
+                          w_out.data_ptr<float>(), cache.data_ptr(), slots.data_ptr<int64_t>(), T, (int)H, cos_sin.size(0),
+                          cache.size(0) * cache.size(1), q.stride(0), k.stride(0), head_w.stride(0), (float)eps, ue8m0,
+                          q_lo, q_lo + Tq, dtype_code(q), stream()),
+        "indexer_prep");
+  return {q_out, w_out};
+}
 void convert_req_index_to_global_index(at::Tensor out, const at::Tensor& req_id, const at::Tensor& block_table,
                                        const at::Tensor& idx, int64_t block_size) {
   TORCH_CHECK(req_id.scalar_type() == at::kInt && block_table.scalar_type() == at::kInt && idx.scalar_type() == at::kInt);
@@ -779,14 +807,16 @@ void mla_attention(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, co
 // logits [T, max_len] fp32 of the lightning indexer; w already carries the per-(token, head) query scale
 void indexer_logits(at::Tensor logits, const at::Tensor& q_fp8, const at::Tensor& w, const at::Tensor& k_cache,
                     const at::Tensor& block_tables, const at::Tensor& seq_lens, const at::Tensor& qsl,
-                    const at::Tensor& req_of_token) {
+                    const at::Tensor& req_of_token, int64_t t0) {
+  // req_of_token holds the requests of rows t0 .. t0 + T (a slice of the batch's tokens); t0 = 0 for the whole batch
   TORCH_CHECK(q_fp8.is_contiguous() && q_fp8.element_size() == 1 && q_fp8.size(1) == 64 && q_fp8.size(2) == 128);
+  TORCH_CHECK(req_of_token.is_contiguous() && req_of_token.numel() >= q_fp8.size(0) && t0 >= 0);
   TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kFloat && k_cache.is_contiguous() && k_cache.size(-1) == 132);
   TORCH_CHECK(logits.is_contiguous() && logits.scalar_type() == at::kFloat && block_tables.stride(1) == 1);
   check(b200_indexer_logits(logits.data_ptr<float>(), q_fp8.data_ptr(), w.data_ptr<float>(), k_cache.data_ptr(),
                             block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), qsl.data_ptr<int>(),
                             req_of_token.data_ptr<int>(), q_fp8.size(0), seq_lens.size(0), k_cache.size(1),
-                            block_tables.stride(0), k_cache.size(0) * k_cache.size(1), logits.size(1), stream()),
+                            block_tables.stride(0), k_cache.size(0) * k_cache.size(1), logits.size(1), t0, stream()),
         "indexer_logits");
 }
 void topk_rows(at::Tensor out, const at::Tensor& logits, const c10::optional<at::Tensor>& row_len) {
@@ -1108,6 +1138,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("decode_attention_umma", &decode_attention_umma);
   m.def("mla_decode_umma", &mla_decode_umma);
+  m.def("indexer_prep", &indexer_prep);
   m.def("set_kernel_trace", &set_kernel_trace);
   m.def("mla_decode_max_clusters", [](int64_t R, int64_t S, int64_t dtype) {
     return (int64_t)b200_mla_decode_max_clusters((int)R, (int)S, (int)dtype);

@@ -196,6 +196,95 @@ __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_
   if (lane == 0) *reinterpret_cast<float*>(row + 128) = scale;
 }
 
+// Lightning-indexer operand preparation in one launch (the reference runs it as separate layer-norm, rotary,
+// concatenation, quantisation and cache-write ops, models/deepseek_v2.py:661-788).  One CTA per token, 8 warps:
+//   * every (token, head) row of q [T, H, 128]: rotary (neox halves) on the leading 64 dims, rounded to the
+//     activation type as the unfused path does, then e4m3 with one power-of-two scale per row;
+//     w[t, h] = head_weight[t, h] * wscale * q_scale  (what the logits kernel multiplies a head's ReLU'd score with);
+//   * the token's key k [T, 128]: LayerNorm (fp32 statistics, weight + bias), rotary on the leading 64 dims, e4m3 +
+//     scale into the 132-byte row of the paged indexer cache.
+// Lane l owns dims 4l .. 4l + 3; a rotary pair (d, d + 32) sits in lanes l and l ^ 8 (l < 16).
+template <typename T>
+__global__ void indexer_prep_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ ln_w,
+                                    const T* __restrict__ ln_b, const int64_t* __restrict__ positions,
+                                    const float* __restrict__ cos_sin, const T* __restrict__ head_w, float wscale,
+                                    uint8_t* __restrict__ q_out, float* __restrict__ w_out, uint8_t* __restrict__ cache,
+                                    const int64_t* __restrict__ slots, int H, int64_t max_pos, int64_t total_slots,
+                                    int64_t q_stride, int64_t k_stride, int64_t hw_stride, float eps, int ue8m0,
+                                    int64_t q_lo, int64_t q_hi) {
+  // q / head_w / q_out / w_out hold tokens [q_lo, q_hi) only (a rank may score a slice of the batch); keys: all tokens
+  constexpr int kRot = 64, kHalf = 32;
+  const int64_t t = blockIdx.x;
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  int64_t pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const float* cs = cos_sin + pos * kRot;
+  // this lane's rotary coefficients: dims 4l.. of the first half use frequency slot d, of the second half d - 32
+  float c4[4], s4[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int d = lane * 4 + j;
+    const int f = d < kHalf ? d : d - kHalf;
+    c4[j] = d < kRot ? cs[f] : 1.f;
+    s4[j] = d < kRot ? cs[kHalf + f] : 0.f;
+  }
+  auto rotate = [&](float (&v)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
+      // first half: a' = a c - b s (b = partner); second half: b' = b c + a s (a = partner)
+      const float r = lane < 8 ? v[j] * c4[j] - other * s4[j] : v[j] * c4[j] + other * s4[j];
+      if (lane < 16) v[j] = to_f(from_f<T>(r));
+    }
+  };
+  auto quantise = [&](const float (&v)[4], float& scale) -> uint32_t {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = fmaxf(warp_max(amax), 1e-10f);
+    scale = amax / 448.f;
+    if (ue8m0) scale = exp2f(ceilf(log2f(scale)));
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= (uint32_t)to_e4m3(v[j] / scale) << (8 * j);
+    return packed;
+  };
+  for (int h = wid; h <= H; h += warps) {
+    float v[4];
+    if (h < H) {
+      if (t < q_lo || t >= q_hi) continue;
+      const int64_t tq = t - q_lo;
+      const T* src = q + tq * q_stride + (int64_t)h * 128 + lane * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = to_f(src[j]);
+      rotate(v);
+      float scale;
+      const uint32_t packed = quantise(v, scale);
+      reinterpret_cast<uint32_t*>(q_out + (tq * H + h) * 128)[lane] = packed;
+      if (lane == 0) w_out[tq * H + h] = to_f(head_w[tq * hw_stride + h]) * wscale * scale;
+    } else {
+      const int64_t slot = slots[t];
+      if (slot < 0 || slot >= total_slots) continue;
+      const T* src = k + t * k_stride + lane * 4;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { v[j] = to_f(src[j]); sum += v[j]; }
+      const float mean = warp_sum(sum) * (1.f / 128.f);
+      float var = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float d = v[j] - mean; var += d * d; }
+      const float rstd = rsqrtf(warp_sum(var) * (1.f / 128.f) + eps);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        v[j] = to_f(from_f<T>((v[j] - mean) * rstd * to_f(ln_w[lane * 4 + j]) + to_f(ln_b[lane * 4 + j])));
+      rotate(v);
+      float scale;
+      const uint32_t packed = quantise(v, scale);
+      uint8_t* row = cache + slot * 132;
+      reinterpret_cast<uint32_t*>(row)[lane] = packed;
+      if (lane == 0) *reinterpret_cast<float*>(row + 128) = scale;
+    }
+  }
+}
+
 __global__ void convert_req_index_kernel(int32_t* __restrict__ out, const int32_t* __restrict__ req_id,
                                          const int32_t* __restrict__ block_table, const int32_t* __restrict__ idx,
                                          int64_t T_, int topk, int block_size, int max_blocks, int num_reqs) {
@@ -306,6 +395,20 @@ extern "C" int b200_indexer_k_quant_and_cache(const void* k, void* cache, const 
   B200_DISPATCH_DTYPE(dtype, {
     indexer_k_quant_and_cache_kernel<T><<<(T_ + 3) / 4, 128, 0, st>>>((const T*)k, (uint8_t*)cache, slots, T_,
                                                                      total_slots, ue8m0, k_stride);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int b200_indexer_prep(const void* q, const void* k, const void* ln_w, const void* ln_b, const int64_t* positions,
+                                 const float* cos_sin, const void* head_w, float wscale, void* q_out, float* w_out,
+                                 void* cache, const int64_t* slots, int64_t T_, int H, int64_t max_pos,
+                                 int64_t total_slots, int64_t q_stride, int64_t k_stride, int64_t hw_stride, float eps,
+                                 int ue8m0, int64_t q_lo, int64_t q_hi, int dtype, cudaStream_t st) {
+  if (T_ == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    indexer_prep_kernel<T><<<T_, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)ln_w, (const T*)ln_b, positions, cos_sin,
+                                               (const T*)head_w, wscale, (uint8_t*)q_out, w_out, (uint8_t*)cache, slots, H,
+                                               max_pos, total_slots, q_stride, k_stride, hw_stride, eps, ue8m0, q_lo, q_hi);
   });
   return (int)cudaGetLastError();
 }

@@ -209,6 +209,58 @@ def dcp_engine(rank, world):
     return res
 
 
+def sparse_mla_engine(rank, world):
+    """Lightning indexer under TP: every rank scores a slice of the prefill tokens against its complete key cache
+    and the selections are all-gathered.  The selections must be the same on all ranks and must match the
+    replicated scoring up to near-ties (the q projection of a 264-row slice and of the 527-row batch may differ in
+    the last bf16 bit, since the GEMM picks its split by the token count)."""
+    from vllm_kunlun_b200.attention.metadata import AttentionMetadata
+    from vllm_kunlun_b200.config import deepseek_v3, tiny
+    from vllm_kunlun_b200.models.deepseek import Indexer
+    from vllm_kunlun_b200.models.layers import get_cos_sin_cache
+    from vllm_kunlun_b200.parallel import state as ps
+    ps.init_distributed("nccl")
+    ps.initialize_model_parallel(tp=world, device=f"cuda:{rank}")
+    cfg = tiny(deepseek_v3(fp8=False, sparse=True), num_layers=1, vocab_size=1024, hidden_size=512, q_lora_rank=256,
+               max_position=2048, index_topk=64)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(11)   # the same weights and inputs on every rank
+    idx = Indexer(cfg, torch.bfloat16, dev)
+    for p_ in idx.parameters():
+        p_.data.normal_(0, 0.05)
+    idx.k_norm_weight.data.fill_(1.0)
+    lens = [300, 77, 150]
+    T, bs = sum(lens), 64
+    hidden = torch.randn(T, 512, device=dev).bfloat16()
+    q_c = torch.randn(T, 256, device=dev).bfloat16()
+    nblk = [-(-n // bs) for n in lens]
+    bt = torch.zeros(len(lens), max(nblk), dtype=torch.int32, device=dev)
+    o = 1
+    for b_, n in enumerate(nblk):
+        bt[b_, :n] = torch.arange(o, o + n, dtype=torch.int32, device=dev)
+        o += n
+    pos = torch.cat([torch.arange(n, device=dev) for n in lens]).long()
+    req = torch.cat([torch.full((n,), r, dtype=torch.int32, device=dev) for r, n in enumerate(lens)])
+    slots = (bt[req.long(), (pos // bs)].long() * bs + pos % bs).long()
+    qsl = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    cos_sin = get_cos_sin_cache(64, 2048, 10000.0, None, dev)
+    res = {}
+    for name, min_tokens in (("replicated", 1 << 30), ("sliced", 1)):
+        Indexer.SP_MIN_TOKENS = min_tokens
+        cache = torch.zeros(o, bs, 132, dtype=torch.uint8, device=dev)
+        md = AttentionMetadata(num_tokens=T, num_reqs=len(lens), positions=pos, slot_mapping=slots, block_tables=bt,
+                               seq_lens=sl, query_start_loc=qsl, max_query_len=max(lens), max_seq_len=max(lens),
+                               num_prefills=len(lens), req_id_per_token=req)
+        with torch.inference_mode():
+            out = idx(hidden, q_c, pos, cos_sin, cache, md)
+        torch.cuda.synchronize()
+        res[name] = out.sort(-1).values.cpu().tolist()
+    Indexer.SP_MIN_TOKENS = 64
+    res["rows_that_differ"] = [i for i, (a, b) in enumerate(zip(res["sliced"], res["replicated"])) if a != b]
+    return res
+
+
 def ep_block(rank, world):
     """One sparse-MoE block on replicated tokens: dispatch / combine path against the replicated-token path."""
     os.environ["B200_EP_A2A"] = "1"
@@ -274,7 +326,8 @@ if __name__ == "__main__":
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     code = 0
     try:
-        res = {"allreduce": allreduce, "engine": engine, "ep_a2a": ep_a2a, "ep_engine": ep_engine, "ep_block": ep_block, "dcp_engine": dcp_engine}[name](rank, world, *sys.argv[3:])
+        res = {"allreduce": allreduce, "engine": engine, "ep_a2a": ep_a2a, "ep_engine": ep_engine, "ep_block": ep_block, "dcp_engine": dcp_engine,
+               "sparse_mla_engine": sparse_mla_engine}[name](rank, world, *sys.argv[3:])
     except Exception:  # noqa: BLE001
         import traceback
         res = {"error": traceback.format_exc()}

@@ -223,3 +223,46 @@ def test_deepseek_mtp_speculative_engine_gpu(fp8):
         flat_a, flat_b = sum(got, []), sum(base, [])
         # q_len = 2 verification rows and q_len = 1 rows take different kernel shapes (bf16): allow rare flips
         assert sum(x == y for x, y in zip(flat_a, flat_b)) >= 0.85 * len(flat_b), (eager, got, base)
+
+
+def test_indexer_prep_fused_matches_unfused_ops():
+    """One-launch indexer preparation (K LayerNorm, rotary on q / k, e4m3 + power-of-two scales, key-cache write,
+    head weight x q scale) against the same steps as separate ops."""
+    from vllm_kunlun_b200.models.layers import get_cos_sin_cache
+    from vllm_kunlun_b200.config import RopeScaling
+    from vllm_kunlun_b200.ops import _ext
+    T, H, bs, nblk = 37, 64, 64, 6
+    g = torch.Generator(device=DEV).manual_seed(5)
+    q = torch.randn(T, H, 128, device=DEV, generator=g).bfloat16()
+    k = (torch.randn(T, 128, device=DEV, generator=g) * 2 + 0.3).bfloat16()
+    lw = (torch.rand(128, device=DEV, generator=g) + 0.5).bfloat16()
+    lb = (torch.randn(128, device=DEV, generator=g) * 0.1).bfloat16()
+    hw = torch.randn(T, H, device=DEV, generator=g).bfloat16()
+    pos = torch.randint(0, 4000, (T,), device=DEV, generator=g)
+    slots = torch.randperm(nblk * bs, device=DEV, generator=g)[:T].long()
+    slots[3] = -1  # a padded token writes nothing
+    cos_sin = get_cos_sin_cache(64, 4096, 10000.0, RopeScaling(), DEV)
+    cache = torch.zeros(nblk, bs, 132, dtype=torch.uint8, device=DEV)
+    q8, w = _ext.C().indexer_prep(q, k, lw, lb, pos, cos_sin, hw, 0.0125, cache, slots, 1e-6, True, 0)
+    # the same steps, unfused
+    kn = torch.nn.functional.layer_norm(k.float(), (128,), lw.float(), lb.float(), 1e-6).bfloat16()
+    q_pe, k_pe = ops.rope(q[..., :64].reshape(T, -1).contiguous(), kn[:, :64].contiguous(), pos, cos_sin, 64, True)
+    q2 = torch.cat([q_pe.view(T, H, 64), q[..., 64:]], -1)
+    k2 = torch.cat([k_pe.view(T, 64), kn[:, 64:]], -1)
+    cache2 = torch.zeros_like(cache)
+    ops.indexer_k_quant_and_cache(k2.contiguous(), cache2, slots, True)
+    q8r, qs = ops.quant_fp8_per_group(q2.reshape(T * H, 128).contiguous(), 128, True)
+    torch.cuda.synchronize()
+    wr = hw.float() * 0.0125 * qs.view(T, H).float()
+    # scales are powers of two: identical unless an absolute maximum sits on a rounding edge of the LayerNorm
+    deq = q8.view(torch.float8_e4m3fn).float() * (w / (hw.float() * 0.0125)).unsqueeze(-1)
+    deq_r = q8r.view(T, H, 128).view(torch.float8_e4m3fn).float() * qs.view(T, H, 1).float()
+    _close(deq, deq_r, 1e-6, 1e-6, "indexer q")
+    _close(w, wr, 1e-7, 1e-6, "indexer head weights")
+    rows, rows_r = cache.view(-1, 132), cache2.view(-1, 132)
+    kd = rows[:, :128].contiguous().view(torch.float8_e4m3fn).float() * rows[:, 128:].contiguous().view(torch.float32)
+    kd_r = rows_r[:, :128].contiguous().view(torch.float8_e4m3fn).float() * rows_r[:, 128:].contiguous().view(torch.float32)
+    # LayerNorm statistics are summed in another order: a bf16 rounding may flip, which moves one e4m3 code
+    _close(kd, kd_r, 0.07, 0.07, "indexer k rows")
+    assert (kd != kd_r).float().mean() < 0.02
+    assert torch.equal(rows[(slots[3] if slots[3] >= 0 else 0)], rows_r[(slots[3] if slots[3] >= 0 else 0)])

@@ -31,6 +31,8 @@ class Indexer(nn.Module):
     """Lightning indexer (``models/deepseek_v2.py:661-788``): 64 heads x 128 dims, LayerNorm on K, rotary
     on the first 64 dims, fp8 keys with a per-token scale in their own paged cache."""
 
+    SP_MIN_TOKENS = 64   # tokens per rank from which the scoring is split over the tensor-parallel ranks
+
     def __init__(self, cfg: ModelConfig, dtype, device):
         super().__init__()
         self.cfg = cfg
@@ -45,8 +47,43 @@ class Indexer(nn.Module):
 
     def forward(self, hidden, q_c, positions, cos_sin, k_cache, md):
         T = hidden.shape[0]
-        q = self.wq_b(q_c).view(T, self.n_heads, self.head_dim)
         k = self.wk(hidden)
+        wscale = (self.n_heads ** -0.5) * self.softmax_scale
+        if hidden.is_cuda and self.rope_dim == 64 and self.head_dim == 128:
+            # one launch: K LayerNorm, rotary on q and k, e4m3 quantisation of both, key-cache write and the
+            # per-(token, head) weight x scale product
+            from ..ops import _ext
+            from ..ops.mla_cuda import indexer_row_len, indexer_topk_cuda
+            st = get_state()
+            row_len = getattr(md, "_index_row_len", None)
+            if row_len is None or row_len.shape[0] != T:   # the same for every layer of the step
+                row_len = md._index_row_len = indexer_row_len(md.seq_lens, md.query_start_loc, md.req_id_per_token, T)
+            max_len = min(int(md.max_seq_len), md.block_tables.shape[1] * k_cache.shape[1])
+            tp = st.tp_size
+            if tp > 1 and T >= self.SP_MIN_TOKENS * tp and not st.tp_comm.disabled:
+                # prefill-sized batch: the indexer is replicated over the tensor-parallel ranks, so every rank
+                # scores its slice of the tokens against the (complete, local) key cache and the selections are
+                # all-gathered - 1 / tp of the scoring work and of the logits buffer per rank
+                per = -(-T // tp)
+                lo = min(T, st.tp_rank * per)
+                hi = min(T, lo + per)
+                ql = self.wq_b(q_c[lo:hi]).view(hi - lo, self.n_heads, self.head_dim)
+                q_fp8, w = _ext.C().indexer_prep(ql, k, self.k_norm_weight, self.k_norm_bias, positions, cos_sin,
+                                                 self.weights_proj(hidden[lo:hi]), wscale, k_cache, md.slot_mapping,
+                                                 1e-6, True, lo)
+                mine = torch.full((per, self.topk), -1, dtype=torch.int32, device=hidden.device)
+                if hi > lo:
+                    mine[: hi - lo] = indexer_topk_cuda(q_fp8, None, w, k_cache, md.block_tables, md.seq_lens,
+                                                        md.query_start_loc, self.topk,
+                                                        md.req_id_per_token[lo:hi].contiguous(), max_len,
+                                                        row_len[lo:hi].contiguous(), lo)
+                return st.tp_comm.all_gather(mine, dim=0)[:T].contiguous()
+            q = self.wq_b(q_c).view(T, self.n_heads, self.head_dim)
+            q_fp8, w = _ext.C().indexer_prep(q, k, self.k_norm_weight, self.k_norm_bias, positions, cos_sin,
+                                             self.weights_proj(hidden), wscale, k_cache, md.slot_mapping, 1e-6, True, 0)
+            return indexer_topk_cuda(q_fp8, None, w, k_cache, md.block_tables, md.seq_lens, md.query_start_loc,
+                                     self.topk, md.req_id_per_token, max_len, row_len)
+        q = self.wq_b(q_c).view(T, self.n_heads, self.head_dim)
         k = torch.nn.functional.layer_norm(k.float(), (self.head_dim,), self.k_norm_weight.float(),
                                            self.k_norm_bias.float(), 1e-6).to(hidden.dtype)
         # rotary on the leading rope_dim dims of q and k (neox halves, as the reference indexer does)
@@ -56,7 +93,7 @@ class Indexer(nn.Module):
         k = torch.cat([k_pe.view(T, self.rope_dim), k[:, self.rope_dim:]], -1)
         ops.indexer_k_quant_and_cache(k.contiguous(), k_cache, md.slot_mapping, True)
         q_fp8, q_scale = ops.quant_fp8_per_group(q.reshape(T * self.n_heads, self.head_dim).contiguous(), 128, True)
-        weights = self.weights_proj(hidden).float() * (self.n_heads ** -0.5) * self.softmax_scale
+        weights = self.weights_proj(hidden).float() * wscale
         return ops.indexer_topk(q_fp8.view(T, self.n_heads, self.head_dim), q_scale.view(T, self.n_heads), weights,
                                 k_cache, md.block_tables, md.seq_lens, md.query_start_loc, self.topk,
                                 md.seq_lens_cpu, md.query_start_loc_cpu)

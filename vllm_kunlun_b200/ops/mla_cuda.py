@@ -145,9 +145,19 @@ def bmm_heads_cuda(x, w):
     return out.view(N, T, D).transpose(0, 1)
 
 
+def indexer_row_len(seq_lens, query_start_loc, req_of_token, T):
+    """Keys visible to token ``t``: its position + 1 (int32 ``[T]``); the same for every layer of a step."""
+    rt = req_of_token.long()
+    qs = query_start_loc.long()[rt]
+    q_len = (query_start_loc[1:] - query_start_loc[:-1]).long()[rt]
+    return (seq_lens.long()[rt] - q_len + (torch.arange(T, device=seq_lens.device) - qs) + 1).to(torch.int32).contiguous()
+
+
 def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk,
-                      req_of_token=None, max_len=None):
-    """fp8 scoring (``csrc/attention/indexer.cu``) + radix-select top-k; request-local indices ``[T, topk]``."""
+                      req_of_token=None, max_len=None, row_len=None, t0: int = 0):
+    """fp8 scoring (``csrc/attention/indexer.cu``) + radix-select top-k; request-local indices ``[T, topk]``.
+    ``q_scale=None``: ``weights`` already holds ``head weight x q scale`` (``indexer_prep``).  ``t0``: the rows are
+    tokens ``t0 .. t0 + T`` of the batch (``req_of_token`` / ``row_len`` are the matching slices)."""
     T, H, D = q_fp8.shape
     assert H == 64 and D == 128, "indexer kernel is specialised for 64 heads x 128 dims"
     if req_of_token is None:
@@ -158,14 +168,12 @@ def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, 
         max_len = block_tables.shape[1] * k_cache.shape[1]
     ld = -(-max_len // 512) * 512
     logits = torch.empty(T, ld, dtype=torch.float32, device=q_fp8.device)
-    w = (weights.float() * q_scale.float()).contiguous()
+    w = weights if q_scale is None else (weights.float() * q_scale.float()).contiguous()
     C = _ext.C()
     C.indexer_logits(logits, q_fp8.view(torch.uint8).contiguous(), w, k_cache, block_tables, seq_lens,
-                     query_start_loc, req_of_token)
-    # keys visible to row t: pos(t) + 1
-    qs = query_start_loc.long()[req_of_token.long()]
-    q_len = (query_start_loc[1:] - query_start_loc[:-1]).long()[req_of_token.long()]
-    row_len = (seq_lens.long()[req_of_token.long()] - q_len + (torch.arange(T, device=q_fp8.device) - qs) + 1)
+                     query_start_loc, req_of_token, t0)
+    if row_len is None:
+        row_len = indexer_row_len(seq_lens, query_start_loc, req_of_token, T)
     out = torch.empty(T, topk, dtype=torch.int32, device=q_fp8.device)
-    C.topk_rows(out, logits, row_len.to(torch.int32).contiguous())
+    C.topk_rows(out, logits, row_len)
     return out
