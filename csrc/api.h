@@ -121,10 +121,10 @@ int b200_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* cache, c
 int b200_indexer_prep(const void* q, const void* k, const void* ln_w, const void* ln_b, const int64_t* positions,
                       const float* cos_sin, const void* head_w, float wscale, void* q_out, float* w_out, void* cache,
                       const int64_t* slots, int64_t T, int H, int64_t max_pos, int64_t total_slots, int64_t q_stride,
-                      int64_t k_stride, int64_t hw_stride, float eps, int ue8m0, int64_t q_lo, int64_t q_hi, int dtype,
+                      int64_t k_stride, int64_t hw_stride, float eps, int ue8m0, int64_t q_lo, int64_t q_hi, int block_size, int dtype,
                       cudaStream_t st);
 int b200_indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slots, int64_t T, int64_t total_slots,
-                                   int ue8m0, int64_t k_stride, int dtype, cudaStream_t st);
+                                   int ue8m0, int64_t k_stride, int block_size, int dtype, cudaStream_t st);
 int b200_convert_req_index(int32_t* out, const int32_t* req_id, const int32_t* block_table, const int32_t* idx,
                            int64_t T, int topk, int block_size, int max_blocks, int num_reqs, cudaStream_t st);
 int b200_copy_blocks(void* cache, const int64_t* src, const int64_t* dst, int64_t n_pairs, int64_t bytes_per_block,
@@ -156,6 +156,10 @@ int b200_mla_decode_umma(void* out, const void* q, const void* tmap, const int* 
                          float scale, int early_meta, int dtype, unsigned long long* trace, cudaStream_t st);
 
 int b200_mla_decode_max_clusters(int R, int S, int dtype);
+int b200_indexer_logits_umma(float* logits, const void* tmQ, const float* w, const void* cache, const void* tmK,
+                             const int* block_tables, const int* seq_lens, const int* qsl, int* status, int B,
+                             int max_query_len, int max_blocks, int64_t num_blocks, int64_t ld, int64_t t_lo, int64_t t_hi,
+                             cudaStream_t st);
 
 int b200_merge_splits(void* out, const float* ws_o, const float* ws_lse, int64_t rows, int Hq, int D, int splits,
                       int64_t T, int dtype, cudaStream_t st);
@@ -165,7 +169,7 @@ int b200_mla_attention(void* out, const void* q, const void* kv, const int* bloc
                        int64_t T, int B, int N, int block_size, int max_blocks, int64_t total_slots, int topk,
                        int num_splits, float scale, int dtype, cudaStream_t st);
 
-// Lightning indexer: fp8 scores over the paged 132-byte key cache, then per-row top-k (unordered, -1 padded)
+// Lightning indexer: fp8 scores over the paged key cache (per block: key rows, then scales), then per-row top-k (unordered, -1 padded)
 int b200_indexer_logits(float* logits, const void* q_fp8, const float* w, const void* k_cache, const int* block_tables,
                         const int* seq_lens, const int* qsl, const int* req_of_token, int64_t T, int B, int block_size,
                         int max_blocks, int64_t total_slots, int64_t ld_logits, int64_t t0, cudaStream_t st);

@@ -1,7 +1,7 @@
 // DeepSeek-V3.2 lightning indexer: fp8 scoring over the paged key cache and per-row top-k.
 //
 // logits[t, j] = k_scale[j] * sum_h w[t, h] * relu( q[t, h, :] . k[j, :] )      j <= pos(t)
-//   q  [T, H=64, 128] e4m3 (per-(token, head) scale folded into w), keys 132-byte rows (128 e4m3 | f32)
+//   q  [T, H=64, 128] e4m3 (per-(token, head) scale folded into w), keys in the page-major cache (per block: rows of 128 e4m3, then f32 scales)
 // Keys are the M side of fp8 tensor-core MMAs (mma.sync m16n8k32 e4m3), the 64 heads the N side,
 // so the head reduction is a sum along accumulator columns: 16 adds + two quad shuffles per key.
 // One CTA = 4 warps scores a 512-key chunk for one query token; the query fragments stay in
@@ -98,9 +98,10 @@ __global__ void __launch_bounds__(128) indexer_logits_kernel(
           int64_t blk = bi < max_blocks ? bt[bi] : -1;
           int64_t slot = blk >= 0 ? blk * block_size + j % block_size : -1;
           if (slot >= 0 && slot < total_slots) {
-            const uint32_t* row = reinterpret_cast<const uint32_t*>(k_cache + slot * kIdxRow);
-            word = row[lane];
-            if (lane == 0) sc = __uint_as_float(row[32]);
+            const uint8_t* blkp = k_cache + blk * ((int64_t)block_size * kIdxRow);
+            const int off = j % block_size;
+            word = reinterpret_cast<const uint32_t*>(blkp + off * kIdxD)[lane];
+            if (lane == 0) sc = reinterpret_cast<const float*>(blkp + block_size * kIdxD)[off];
           }
         }
         *reinterpret_cast<uint32_t*>(sK[warp] + swz8(r, lane >> 2) + (lane & 3) * 4) = word;

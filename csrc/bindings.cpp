@@ -624,7 +624,8 @@ void concat_and_cache_mla(const at::Tensor& kv_c, const at::Tensor& k_pe, at::Te
 void indexer_k_quant_and_cache(const at::Tensor& k, at::Tensor cache, const at::Tensor& slots, bool ue8m0) {
   TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte && cache.size(-1) == 132 && k.size(1) == 128);
   check(b200_indexer_k_quant_and_cache(k.data_ptr(), cache.data_ptr(), slots.data_ptr<int64_t>(), k.size(0),
-                                       cache.size(0) * cache.size(1), ue8m0, k.stride(0), dtype_code(k), stream()),
+                                       cache.size(0) * cache.size(1), ue8m0, k.stride(0), (int)cache.size(1), dtype_code(k),
+                                       stream()),
         "indexer_k_quant_and_cache");
 }
 // Fused indexer operand preparation: returns (q_fp8 [T, H, 128] uint8, w [T, H] float) and writes the key rows.
@@ -651,7 +652,7 @@ std::vector<at::Tensor> indexer_prep(const at::Tensor& q, const at::Tensor& k, c
                           cos_sin.data_ptr<float>(), head_w.data_ptr(), (float)wscale, q_out.data_ptr(),
                           w_out.data_ptr<float>(), cache.data_ptr(), slots.data_ptr<int64_t>(), T, (int)H, cos_sin.size(0),
                           cache.size(0) * cache.size(1), q.stride(0), k.stride(0), head_w.stride(0), (float)eps, ue8m0,
-                          q_lo, q_lo + Tq, dtype_code(q), stream()),
+                          q_lo, q_lo + Tq, (int)cache.size(1), dtype_code(q), stream()),
         "indexer_prep");
   return {q_out, w_out};
 }
@@ -818,6 +819,40 @@ void indexer_logits(at::Tensor logits, const at::Tensor& q_fp8, const at::Tensor
                             req_of_token.data_ptr<int>(), q_fp8.size(0), seq_lens.size(0), k_cache.size(1),
                             block_tables.stride(0), k_cache.size(0) * k_cache.size(1), logits.size(1), t0, stream()),
         "indexer_logits");
+}
+// The same logits for prefill-sized batches on tcgen05 (block_size 64): rows are tokens [t0, t0 + q_fp8.size(0)) of the
+// batch; only keys [0, n_keys(t)) of a row (rounded up to 128) are written.
+void indexer_logits_umma(at::Tensor logits, const at::Tensor& q_fp8, const at::Tensor& w, const at::Tensor& k_cache,
+                         const at::Tensor& block_tables, const at::Tensor& seq_lens, const at::Tensor& qsl,
+                         int64_t max_query_len, int64_t t0) {
+  TORCH_CHECK(q_fp8.is_contiguous() && q_fp8.element_size() == 1 && q_fp8.size(1) == 64 && q_fp8.size(2) == 128);
+  TORCH_CHECK(w.is_contiguous() && w.scalar_type() == at::kFloat && w.size(0) == q_fp8.size(0) && w.size(1) == 64);
+  TORCH_CHECK(k_cache.is_contiguous() && k_cache.scalar_type() == at::kByte && k_cache.dim() == 3 && k_cache.size(1) == 64 &&
+              k_cache.size(2) == 132, "indexer_logits_umma: 64-token pages");
+  TORCH_CHECK(logits.is_contiguous() && logits.scalar_type() == at::kFloat && logits.size(0) == q_fp8.size(0));
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && block_tables.stride(1) == 1 && seq_lens.scalar_type() == at::kInt &&
+              qsl.scalar_type() == at::kInt && t0 >= 0);
+  if (q_fp8.size(0) == 0) return;
+  c10::cuda::CUDAGuard guard(q_fp8.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, w.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, w.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, w.options().dtype(at::kInt));
+  }
+  at::Tensor q2 = q_fp8.view({-1, 128});
+  if (q2.scalar_type() != at::kByte) q2 = q2.view(at::kByte);
+  at::Tensor k2 = k_cache.view({-1, 128});   // a block = 66 rows: 64 key rows, then 2 rows of scales
+  const Tmap& tq = get_tmap(gs, q2, 256, 1);
+  const Tmap& tk = get_tmap(gs, k2, 64, 1);
+  check(b200_indexer_logits_umma(logits.data_ptr<float>(), tq.b, w.data_ptr<float>(), k_cache.data_ptr(), tk.b,
+                                 block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), qsl.data_ptr<int>(),
+                                 gs.status.data_ptr<int>(), (int)seq_lens.size(0), (int)max_query_len,
+                                 (int)block_tables.stride(0), k_cache.size(0), logits.size(1), t0, t0 + q_fp8.size(0),
+                                 stream()),
+        "indexer_logits_umma");
 }
 void topk_rows(at::Tensor out, const at::Tensor& logits, const c10::optional<at::Tensor>& row_len) {
   TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kInt && logits.scalar_type() == at::kFloat && logits.stride(1) == 1);
@@ -1145,6 +1180,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("mla_attention", &mla_attention);
   m.def("indexer_logits", &indexer_logits);
+  m.def("indexer_logits_umma", &indexer_logits_umma);
   m.def("topk_rows", &topk_rows);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_free", &peer_free);

@@ -3,7 +3,7 @@
 // Cache layouts (see vllm_kunlun_b200/ops/reference/attention.py):
 //   GQA     kv_cache[block][2][kv_head][slot_in_block][head_dim]
 //   MLA     kv_cache[block][slot_in_block][576]   (bf16) or uint8 [..][656] (512 e4m3 | 4 f32 | 64 bf16)
-//   indexer k_cache[block][slot_in_block][132]    (128 e4m3 | 1 f32)
+//   indexer k_cache[block]: block_size rows of 128 e4m3 bytes, then block_size f32 scales (132 bytes per slot)
 // Slot ids < 0 mark padding rows and are skipped.  Every index read from a table is range-checked
 // against the tensor bounds before it is used as an address.
 #include <cuda_fp8.h>
@@ -171,11 +171,12 @@ __global__ void __launch_bounds__(128) concat_and_cache_mla_fp8_kernel(
       __float2bfloat16(to_f(k_pe[t * kpe_stride + threadIdx.x]));
 }
 
-// 132-byte rows: 128 e4m3 | f32 scale (power of two when ue8m0).  One warp per token.
+// Page-major indexer cache: a block holds its key rows (128 e4m3 each) first and their f32 scales (powers of two
+// when ue8m0) after them, so that a page of keys is one contiguous 16-byte aligned tile.  One warp per token.
 template <typename T>
 __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_t* __restrict__ cache,
                                                  const int64_t* __restrict__ slots, int64_t T_, int64_t total_slots,
-                                                 int ue8m0, int64_t k_stride) {
+                                                 int ue8m0, int64_t k_stride, int block_size) {
   int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T_) return;
   int lane = threadIdx.x & 31;
@@ -188,12 +189,13 @@ __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_
   amax = fmaxf(warp_max(amax), 1e-10f);
   float scale = amax / 448.f;
   if (ue8m0) scale = exp2f(ceilf(log2f(scale)));
-  uint8_t* row = cache + slot * 132;
+  uint8_t* blk = cache + (slot / block_size) * ((int64_t)block_size * 132);
+  const int off = (int)(slot % block_size);
   uint32_t packed = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) packed |= (uint32_t)to_e4m3(v[j] / scale) << (8 * j);
-  reinterpret_cast<uint32_t*>(row)[lane] = packed;
-  if (lane == 0) *reinterpret_cast<float*>(row + 128) = scale;
+  reinterpret_cast<uint32_t*>(blk + off * 128)[lane] = packed;
+  if (lane == 0) reinterpret_cast<float*>(blk + block_size * 128)[off] = scale;
 }
 
 // Lightning-indexer operand preparation in one launch (the reference runs it as separate layer-norm, rotary,
@@ -202,7 +204,7 @@ __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_
 //     activation type as the unfused path does, then e4m3 with one power-of-two scale per row;
 //     w[t, h] = head_weight[t, h] * wscale * q_scale  (what the logits kernel multiplies a head's ReLU'd score with);
 //   * the token's key k [T, 128]: LayerNorm (fp32 statistics, weight + bias), rotary on the leading 64 dims, e4m3 +
-//     scale into the 132-byte row of the paged indexer cache.
+//     scale into the page-major indexer cache (key rows first, scales after them in every block).
 // Lane l owns dims 4l .. 4l + 3; a rotary pair (d, d + 32) sits in lanes l and l ^ 8 (l < 16).
 template <typename T>
 __global__ void indexer_prep_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ ln_w,
@@ -211,7 +213,7 @@ __global__ void indexer_prep_kernel(const T* __restrict__ q, const T* __restrict
                                     uint8_t* __restrict__ q_out, float* __restrict__ w_out, uint8_t* __restrict__ cache,
                                     const int64_t* __restrict__ slots, int H, int64_t max_pos, int64_t total_slots,
                                     int64_t q_stride, int64_t k_stride, int64_t hw_stride, float eps, int ue8m0,
-                                    int64_t q_lo, int64_t q_hi) {
+                                    int64_t q_lo, int64_t q_hi, int block_size) {
   // q / head_w / q_out / w_out hold tokens [q_lo, q_hi) only (a rank may score a slice of the batch); keys: all tokens
   constexpr int kRot = 64, kHalf = 32;
   const int64_t t = blockIdx.x;
@@ -278,9 +280,10 @@ __global__ void indexer_prep_kernel(const T* __restrict__ q, const T* __restrict
       rotate(v);
       float scale;
       const uint32_t packed = quantise(v, scale);
-      uint8_t* row = cache + slot * 132;
-      reinterpret_cast<uint32_t*>(row)[lane] = packed;
-      if (lane == 0) *reinterpret_cast<float*>(row + 128) = scale;
+      uint8_t* blk = cache + (slot / block_size) * ((int64_t)block_size * 132);
+      const int off = (int)(slot % block_size);
+      reinterpret_cast<uint32_t*>(blk + off * 128)[lane] = packed;
+      if (lane == 0) reinterpret_cast<float*>(blk + block_size * 128)[off] = scale;
     }
   }
 }
@@ -389,12 +392,12 @@ extern "C" int b200_concat_and_cache_mla(const void* kv_c, const void* k_pe, voi
 }
 
 extern "C" int b200_indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slots, int64_t T_,
-                                              int64_t total_slots, int ue8m0, int64_t k_stride, int dtype,
-                                              cudaStream_t st) {
+                                              int64_t total_slots, int ue8m0, int64_t k_stride, int block_size,
+                                              int dtype, cudaStream_t st) {
   if (T_ == 0) return 0;
   B200_DISPATCH_DTYPE(dtype, {
     indexer_k_quant_and_cache_kernel<T><<<(T_ + 3) / 4, 128, 0, st>>>((const T*)k, (uint8_t*)cache, slots, T_,
-                                                                     total_slots, ue8m0, k_stride);
+                                                                     total_slots, ue8m0, k_stride, block_size);
   });
   return (int)cudaGetLastError();
 }
@@ -403,12 +406,13 @@ extern "C" int b200_indexer_prep(const void* q, const void* k, const void* ln_w,
                                  const float* cos_sin, const void* head_w, float wscale, void* q_out, float* w_out,
                                  void* cache, const int64_t* slots, int64_t T_, int H, int64_t max_pos,
                                  int64_t total_slots, int64_t q_stride, int64_t k_stride, int64_t hw_stride, float eps,
-                                 int ue8m0, int64_t q_lo, int64_t q_hi, int dtype, cudaStream_t st) {
+                                 int ue8m0, int64_t q_lo, int64_t q_hi, int block_size, int dtype, cudaStream_t st) {
   if (T_ == 0) return 0;
   B200_DISPATCH_DTYPE(dtype, {
     indexer_prep_kernel<T><<<T_, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)ln_w, (const T*)ln_b, positions, cos_sin,
                                                (const T*)head_w, wscale, (uint8_t*)q_out, w_out, (uint8_t*)cache, slots, H,
-                                               max_pos, total_slots, q_stride, k_stride, hw_stride, eps, ue8m0, q_lo, q_hi);
+                                               max_pos, total_slots, q_stride, k_stride, hw_stride, eps, ue8m0, q_lo, q_hi,
+                                               block_size);
   });
   return (int)cudaGetLastError();
 }

@@ -259,10 +259,68 @@ def test_indexer_prep_fused_matches_unfused_ops():
     deq_r = q8r.view(T, H, 128).view(torch.float8_e4m3fn).float() * qs.view(T, H, 1).float()
     _close(deq, deq_r, 1e-6, 1e-6, "indexer q")
     _close(w, wr, 1e-7, 1e-6, "indexer head weights")
-    rows, rows_r = cache.view(-1, 132), cache2.view(-1, 132)
-    kd = rows[:, :128].contiguous().view(torch.float8_e4m3fn).float() * rows[:, 128:].contiguous().view(torch.float32)
-    kd_r = rows_r[:, :128].contiguous().view(torch.float8_e4m3fn).float() * rows_r[:, 128:].contiguous().view(torch.float32)
+    (kq, ks), (kq_r, ks_r) = ra.indexer_cache_views(cache), ra.indexer_cache_views(cache2)
+    kd = kq.contiguous().view(torch.float8_e4m3fn).float() * ks.unsqueeze(-1)
+    kd_r = kq_r.contiguous().view(torch.float8_e4m3fn).float() * ks_r.unsqueeze(-1)
     # LayerNorm statistics are summed in another order: a bf16 rounding may flip, which moves one e4m3 code
     _close(kd, kd_r, 0.07, 0.07, "indexer k rows")
     assert (kd != kd_r).float().mean() < 0.02
-    assert torch.equal(rows[(slots[3] if slots[3] >= 0 else 0)], rows_r[(slots[3] if slots[3] >= 0 else 0)])
+
+
+@pytest.mark.parametrize("t_lo_frac", [0.0, 0.37])
+def test_indexer_logits_umma_matches_mma_sync_kernel(t_lo_frac):
+    """tcgen05 indexer logits (keys on the UMMA M side, 4 tokens x 64 heads on the N side) against the mma.sync
+    kernel on every visible key: prefill chunks with and without cached context, a decode row, requests that end
+    inside a page, and a slice of the batch's tokens (as one tensor-parallel rank scores it)."""
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    from vllm_kunlun_b200.ops.mla_cuda import indexer_row_len
+    from vllm_kunlun_b200.ops.reference import basic as rb
+    g = torch.Generator().manual_seed(9)
+    bs, H = 64, 64
+    spec = [(300, 300), (1, 700), (77, 1100), (130, 130), (17, 64)]   # (q_len, seq_len)
+    B = len(spec)
+    seq_lens = [s for _, s in spec]
+    nblk = sum(-(-s // bs) for s in seq_lens) + 2
+    bt = torch.zeros(B, max(-(-s // bs) for s in seq_lens) + 1, dtype=torch.int32)
+    k = 1
+    for b, s in enumerate(seq_lens):
+        n = -(-s // bs)
+        bt[b, :n] = torch.arange(k, k + n)
+        k += n
+    cache = torch.zeros(nblk + 1, bs, 132, dtype=torch.uint8)
+    keys = torch.randn(sum(seq_lens), 128, generator=g)
+    slots = []
+    for b, s in enumerate(seq_lens):
+        pos = torch.arange(s)
+        slots.append(bt[b, pos // bs].long() * bs + pos % bs)
+    ra.indexer_k_quant_and_cache(keys, cache, torch.cat(slots))
+    qsl = torch.tensor([0] + list(torch.tensor([q for q, _ in spec]).cumsum(0)), dtype=torch.int32)
+    T = int(qsl[-1])
+    q = torch.randn(T, H, 128, generator=g)
+    qq, qs_ = rb.quant_fp8_per_group(q.reshape(T * H, 128), 128, True)
+    w = (torch.randn(T, H, generator=g) * 0.1 * qs_.view(T, H)).contiguous()
+    req = torch.repeat_interleave(torch.arange(B, dtype=torch.int32), (qsl[1:] - qsl[:-1]).long())
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    C = _ext.C()
+    d = lambda x: x.to(DEV)
+    lo = int(T * t_lo_frac)
+    hi = T if t_lo_frac == 0.0 else T - 5
+    ld = 1536
+    qd = d(qq.view(T, H, 128).view(torch.uint8))[lo:hi].contiguous()
+    wd = d(w)[lo:hi].contiguous()
+    a = torch.full((hi - lo, ld), float("nan"), device=DEV)
+    b_ = torch.full((hi - lo, ld), float("nan"), device=DEV)
+    C.indexer_logits(a, qd, wd, d(cache), d(bt), d(sl), d(qsl), d(req)[lo:hi].contiguous(), lo)
+    C.indexer_logits_umma(b_, qd, wd, d(cache), d(bt), d(sl), d(qsl), max(q for q, _ in spec), lo)
+    torch.cuda.synchronize()
+    check_status()
+    rl = indexer_row_len(d(sl), d(qsl), d(req), T)[lo:hi].cpu()
+    a, b_ = a.cpu(), b_.cpu()
+    for t in range(hi - lo):
+        n = int(rl[t])
+        assert torch.isfinite(b_[t, :n]).all(), (t, n)
+        # exact e4m3 products, fp32 sums in another order
+        torch.testing.assert_close(b_[t, :n], a[t, :n], atol=2e-4, rtol=2e-4)
+        up = min(ld, -(-n // 128) * 128)
+        assert (b_[t, n:up] == float("-inf")).all(), (t, n)

@@ -76,13 +76,13 @@ class Indexer(nn.Module):
                     mine[: hi - lo] = indexer_topk_cuda(q_fp8, None, w, k_cache, md.block_tables, md.seq_lens,
                                                         md.query_start_loc, self.topk,
                                                         md.req_id_per_token[lo:hi].contiguous(), max_len,
-                                                        row_len[lo:hi].contiguous(), lo)
+                                                        row_len[lo:hi].contiguous(), lo, md.max_query_len)
                 return st.tp_comm.all_gather(mine, dim=0)[:T].contiguous()
             q = self.wq_b(q_c).view(T, self.n_heads, self.head_dim)
             q_fp8, w = _ext.C().indexer_prep(q, k, self.k_norm_weight, self.k_norm_bias, positions, cos_sin,
                                              self.weights_proj(hidden), wscale, k_cache, md.slot_mapping, 1e-6, True, 0)
             return indexer_topk_cuda(q_fp8, None, w, k_cache, md.block_tables, md.seq_lens, md.query_start_loc,
-                                     self.topk, md.req_id_per_token, max_len, row_len)
+                                     self.topk, md.req_id_per_token, max_len, row_len, 0, md.max_query_len)
         q = self.wq_b(q_c).view(T, self.n_heads, self.head_dim)
         k = torch.nn.functional.layer_norm(k.float(), (self.head_dim,), self.k_norm_weight.float(),
                                            self.k_norm_bias.float(), 1e-6).to(hidden.dtype)

@@ -425,9 +425,10 @@ def indexer_topk(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query
             continue
         L = int(sl[r])
         pos = torch.arange(L)
-        rows = k_cache[block_tables[r, pos // bs].long(), pos % bs]
-        k = rows[:, :128].contiguous().view(torch.float8_e4m3fn).float()
-        ksc = rows[:, 128:132].contiguous().view(torch.float32).reshape(-1)
+        kv, sv = _ra.indexer_cache_views(k_cache)
+        blk = block_tables[r, pos // bs].long()
+        k = kv[blk, pos % bs].contiguous().view(torch.float8_e4m3fn).float()
+        ksc = sv[blk, pos % bs].reshape(-1)
         n = qe - qs
         ke = torch.arange(L - n + 1, L + 1)
         logits = _ra.indexer_logits(qf[qs:qe], k, ksc, weights[qs:qe], torch.zeros(n, dtype=torch.long), ke)

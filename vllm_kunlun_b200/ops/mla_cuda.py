@@ -153,8 +153,14 @@ def indexer_row_len(seq_lens, query_start_loc, req_of_token, T):
     return (seq_lens.long()[rt] - q_len + (torch.arange(T, device=seq_lens.device) - qs) + 1).to(torch.int32).contiguous()
 
 
+# prefill-sized batches score on the tcgen05 kernel (csrc/attention/indexer_umma.cu); B200_INDEXER_UMMA=0 keeps
+# everything on the mma.sync kernel
+INDEXER_UMMA = [_os.environ.get("B200_INDEXER_UMMA", "1") != "0"]
+_INDEXER_UMMA_MIN_ROWS = 64
+
+
 def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, query_start_loc, topk,
-                      req_of_token=None, max_len=None, row_len=None, t0: int = 0):
+                      req_of_token=None, max_len=None, row_len=None, t0: int = 0, max_query_len=None):
     """fp8 scoring (``csrc/attention/indexer.cu``) + radix-select top-k; request-local indices ``[T, topk]``.
     ``q_scale=None``: ``weights`` already holds ``head weight x q scale`` (``indexer_prep``).  ``t0``: the rows are
     tokens ``t0 .. t0 + T`` of the batch (``req_of_token`` / ``row_len`` are the matching slices)."""
@@ -170,10 +176,18 @@ def indexer_topk_cuda(q_fp8, q_scale, weights, k_cache, block_tables, seq_lens, 
     logits = torch.empty(T, ld, dtype=torch.float32, device=q_fp8.device)
     w = weights if q_scale is None else (weights.float() * q_scale.float()).contiguous()
     C = _ext.C()
-    C.indexer_logits(logits, q_fp8.view(torch.uint8).contiguous(), w, k_cache, block_tables, seq_lens,
-                     query_start_loc, req_of_token, t0)
     if row_len is None:
+        assert t0 == 0
         row_len = indexer_row_len(seq_lens, query_start_loc, req_of_token, T)
+    if (INDEXER_UMMA[0] and max_query_len is not None and T >= _INDEXER_UMMA_MIN_ROWS and k_cache.shape[1] == 64
+            and w.is_contiguous()):
+        # keys on the UMMA M side, 4 tokens x 64 heads on the N side; writes keys [0, n_keys) of every row only,
+        # which is all that the selection below reads
+        C.indexer_logits_umma(logits, q_fp8.view(torch.uint8).contiguous(), w, k_cache, block_tables, seq_lens,
+                              query_start_loc, int(max_query_len), t0)
+    else:
+        C.indexer_logits(logits, q_fp8.view(torch.uint8).contiguous(), w, k_cache, block_tables, seq_lens,
+                         query_start_loc, req_of_token, t0)
     out = torch.empty(T, topk, dtype=torch.int32, device=q_fp8.device)
     C.topk_rows(out, logits, row_len)
     return out

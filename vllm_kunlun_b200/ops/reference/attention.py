@@ -9,7 +9,8 @@ Cache layouts of this framework (chosen so a page of one KV head is one contiguo
   (``v1/attention/backends/mla/common.py:296-304``)
 * fp8_ds_mla: ``uint8[num_blocks, block_size, 656]`` = 512 e4m3 | 4 fp32 scales | 64 bf16 rope
   (``v1/attention/backends/mla/flashmla_sparse.py:357-425``)
-* indexer K: ``uint8[num_blocks, block_size, 132]`` = 128 e4m3 | 1 fp32 scale
+* indexer K: ``uint8[num_blocks, block_size, 132]`` holding, per block, ``block_size`` rows of 128 e4m3 bytes and
+  then ``block_size`` fp32 scales (page-major: a page's key rows are one contiguous, 16-byte aligned tile)
   (``models/deepseek_v2.py:714-719``)
 """
 from __future__ import annotations
@@ -87,9 +88,18 @@ def indexer_k_quant_and_cache(k, k_cache_u8, slot_mapping, ue8m0: bool = True):
         if ue8m0:
             scale = torch.exp2(torch.ceil(torch.log2(scale)))
         q = (kf / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
-        row = k_cache_u8[s // bs, s % bs]
-        row[:128] = q.view(torch.uint8)
-        row[128:132] = scale.reshape(1).to(torch.float32).view(torch.uint8)
+        kv, sv = indexer_cache_views(k_cache_u8)
+        kv[s // bs, s % bs] = q.view(torch.uint8)
+        sv[s // bs, s % bs] = scale.to(torch.float32)
+
+
+def indexer_cache_views(k_cache_u8):
+    """``(keys uint8 [blocks, block_size, 128], scales float32 [blocks, block_size])`` views of the indexer cache:
+    per block, the key rows come first and the scales after them."""
+    nb, bs, w = k_cache_u8.shape
+    assert w == 132
+    flat = k_cache_u8.view(nb, bs * 132)
+    return flat[:, : bs * 128].view(nb, bs, 128), flat[:, bs * 128:].view(torch.float32)
 
 
 def gather_indexer_k(k_cache_u8, block_table, cu_seq_lens):
@@ -100,9 +110,10 @@ def gather_indexer_k(k_cache_u8, block_table, cu_seq_lens):
     for r in range(block_table.shape[0]):
         n = int(cu_seq_lens[r + 1] - cu_seq_lens[r])
         pos = torch.arange(n)
-        rows = k_cache_u8[block_table[r, pos // bs].long(), pos % bs]
-        outs_k.append(rows[:, :128].contiguous().view(torch.float8_e4m3fn))
-        outs_s.append(rows[:, 128:132].contiguous().view(torch.float32).reshape(-1))
+        kv, sv = indexer_cache_views(k_cache_u8)
+        blk = block_table[r, pos // bs].long()
+        outs_k.append(kv[blk, pos % bs].contiguous().view(torch.float8_e4m3fn))
+        outs_s.append(sv[blk, pos % bs].reshape(-1))
     return torch.cat(outs_k), torch.cat(outs_s)
 
 
@@ -319,9 +330,10 @@ def indexer_logits_paged(q, k_cache_u8, weights, seq_lens, block_table, max_len:
         if L == 0:
             continue
         pos = torch.arange(L)
-        rows = k_cache_u8[block_table[b, pos // bs].long(), pos % bs]
-        k = rows[:, :128].contiguous().view(torch.float8_e4m3fn).float()
-        sc = rows[:, 128:132].contiguous().view(torch.float32).reshape(-1)
+        kv, sv = indexer_cache_views(k_cache_u8)
+        blk = block_table[b, pos // bs].long()
+        k = kv[blk, pos % bs].contiguous().view(torch.float8_e4m3fn).float()
+        sc = sv[blk, pos % bs].reshape(-1)
         for j in range(nn_):
             lim = L - nn_ + j + 1
             s = torch.einsum("hd,nd->hn", q[b, j].float(), k[:lim])
