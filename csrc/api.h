@@ -65,6 +65,16 @@ typedef struct GemmDecodeArgs {
   const float* a_scale;    // [ceil(K/128), a_stride] transposed activation scales
   const float* w_scale;    // [ceil(N/128), ceil(K/128)]
   int a_stride;
+  // qkv epilogue (head_dim 128): split + optional q / k RMSNorm + rotary + K / V cache write; out = q [T, Hq * 128]
+  int qk_on, qk_hq, qk_hkv, qk_neox, qk_gemma, qk_block_size;
+  float qk_eps;
+  const int64_t* qk_positions;
+  const float* qk_cos_sin;
+  const void* qk_q_w;
+  const void* qk_k_w;
+  void* qk_kv_cache;
+  const int64_t* qk_slots;
+  int64_t qk_num_blocks, qk_max_pos;
 } GemmDecodeArgs;
 int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
 

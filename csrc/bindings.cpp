@@ -285,6 +285,69 @@ void gemm_decode(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const
   gs.launches++;
 }
 
+// qkv projection of a decode-sized batch with split + optional q / k RMSNorm + rotary + K / V cache write in the GEMM
+// epilogue (head_dim 128, full rotary dim).  q_out [T, Hq * 128]; w [(Hq + 2 Hkv) * 128, K].
+void gemm_decode_qkv(at::Tensor q_out, const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+                     const at::Tensor& positions, const at::Tensor& cos_sin, const c10::optional<at::Tensor>& q_w,
+                     const c10::optional<at::Tensor>& k_w, double eps, int64_t Hq, int64_t Hkv, bool neox, bool gemma,
+                     const c10::optional<at::Tensor>& kv_cache, const at::Tensor& slots) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && q_out.is_cuda() && x.dim() == 2 && w.dim() == 2 && q_out.dim() == 2);
+  TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == q_out.scalar_type());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "gemm_decode_qkv: bf16/fp16 only");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && q_out.is_contiguous());
+  const int T = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(T <= 32 && w.size(1) == K && N == (Hq + 2 * Hkv) * 128 && q_out.size(0) == T && q_out.size(1) == Hq * 128);
+  TORCH_CHECK(K % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0);
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.numel() >= T);
+  TORCH_CHECK(slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() >= T);
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && cos_sin.size(-1) == 128,
+              "gemm_decode_qkv: rotary dim 128");
+  if (q_w.has_value()) TORCH_CHECK(q_w->scalar_type() == x.scalar_type() && q_w->numel() == 128 && q_w->is_contiguous());
+  if (k_w.has_value()) TORCH_CHECK(k_w->scalar_type() == x.scalar_type() && k_w->numel() == 128 && k_w->is_contiguous());
+  if (kv_cache.has_value())
+    TORCH_CHECK(kv_cache->is_contiguous() && kv_cache->scalar_type() == x.scalar_type() && kv_cache->dim() == 5 &&
+                kv_cache->size(1) == 2 && kv_cache->size(2) == Hkv && kv_cache->size(4) == 128);
+  if (T == 0) return;
+  c10::cuda::CUDAGuard guard(x.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, x.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, x.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, x.options().dtype(at::kInt));
+  }
+  GemmDecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.out = q_out.data_ptr(); a.bias = opt_ptr(bias); a.status = gs.status.data_ptr<int>();
+  a.T = T; a.N = N; a.K = K;
+  a.n_tiles = N / 128;
+  a.bn = T <= 16 ? 16 : 32;
+  a.fmt = x.scalar_type() == at::kBFloat16 ? 1 : 0;
+  a.ldo = q_out.stride(0);
+  const int total_kb = (K + 63) / 64;
+  const int max_s = a.bn == 16 ? 8 : 4;
+  int S = 1;
+  while (S * 2 <= max_s && a.n_tiles * S * 2 <= gs.num_sms && total_kb / (S * 2) >= 8) S *= 2;
+  while (S > 1 && (S - 1) * ((total_kb + S - 1) / S) >= total_kb) --S;
+  a.S = S;
+  a.kb_per_cta = (total_kb + S - 1) / S;
+  a.ctas_per_sm = a.n_tiles * S > gs.num_sms ? 2 : 1;
+  a.qk_on = 1; a.qk_hq = (int)Hq; a.qk_hkv = (int)Hkv; a.qk_neox = neox; a.qk_gemma = gemma; a.qk_eps = (float)eps;
+  a.qk_positions = positions.data_ptr<int64_t>(); a.qk_cos_sin = cos_sin.data_ptr<float>();
+  a.qk_q_w = q_w.has_value() ? q_w->data_ptr() : nullptr;
+  a.qk_k_w = k_w.has_value() ? k_w->data_ptr() : nullptr;
+  a.qk_kv_cache = kv_cache.has_value() ? kv_cache->data_ptr() : nullptr;
+  a.qk_slots = slots.data_ptr<int64_t>();
+  a.qk_block_size = kv_cache.has_value() ? (int)kv_cache->size(3) : 1;
+  a.qk_num_blocks = kv_cache.has_value() ? kv_cache->size(0) : 0;
+  a.qk_max_pos = cos_sin.size(0);
+  const Tmap& tw = get_tmap(gs, w, 128, 2);
+  const Tmap& tx = get_tmap(gs, x, a.bn, 2);
+  check(b200_gemm_decode_launch(&a, tw.b, tx.b, stream()), "gemm_decode_qkv launch");
+  gs.launches++;
+}
+
 // fp8 block-scaled decode GEMM (T <= 32): xq [T, K] e4m3 with transposed 1x128 scales a_scale_t [K/128, stride],
 // w [N, K] e4m3 with w_scale [ceil(N/128), ceil(K/128)]; cluster split-K like gemm_decode.
 void gemm_decode_fp8(at::Tensor out, const at::Tensor& xq, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
@@ -1130,6 +1193,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_status_tensor", &gemm_status_tensor);
   m.def("gemm_decode", &gemm_decode);
   m.def("gemm_decode_fp8", &gemm_decode_fp8);
+  m.def("gemm_decode_qkv", &gemm_decode_qkv);
   m.def("set_gemm_decode_comm", &set_gemm_decode_comm);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("moe_route", &moe_route);

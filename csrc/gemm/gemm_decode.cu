@@ -74,6 +74,22 @@ struct Comm {
   int on, rank, nranks;
 };
 
+// qkv epilogue: weight tile nt is exactly head nt (head_dim 128 = BM), so per-head q / k RMSNorm, the rotary embedding
+// and the K / V scatter into the paged cache are tile-local and run in the leader CTA's epilogue instead of in a
+// kernel of their own (the reference chains `_C::split_norm_rope_neox` and `reshape_and_cache_flash`,
+// ops/_kunlun_ops.py; the stand-alone form here is qkv_split_norm_rope_cache_kernel in cache_rope.cu).
+struct QkvEpi {
+  const int64_t* positions;   // [T]
+  const float* cos_sin;       // [max_pos][128]: cos (64) | sin (64)
+  const void* q_w;            // [128] or null
+  const void* k_w;            // [128] or null
+  void* kv_cache;             // [blocks][2][Hkv][block_size][128]
+  const int64_t* slots;       // [T]
+  int64_t num_blocks, max_pos;
+  float eps;
+  int on, Hq, Hkv, neox, gemma, block_size;
+};
+
 constexpr int kAccBufs = 4;  // fp8: accumulator buffers handed to the epilogue one k-block at a time
 
 template <int BN>
@@ -96,7 +112,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                    OutT* __restrict__ out, const OutT* __restrict__ bias, int* __restrict__ status, int T, int N, int K,
                    int kb_per_cta, int fmt, int ldo, int num_stages, int S, int act, int l2_prefetch,
                    const float* __restrict__ a_scale, const float* __restrict__ w_scale, int a_stride,
-                   const __grid_constant__ Comm cm) {
+                   const __grid_constant__ Comm cm, const __grid_constant__ QkvEpi qk) {
   using C = Cfg<BN>;
   constexpr int BKE = kFp8 ? 128 : BK;  // K elements per k-block
   constexpr int kCols = kFp8 ? C::kTmemColsFp8 : C::kTmemCols;
@@ -338,7 +354,70 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
         for (int c = 0; c < BN; ++c) tile[c * kTileStride + n_local] = from_float<OutT>(acc[c] + bv);
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (act != 0) {
+        if (qk.on) {
+          // ---- head nt of the fused qkv row: warp = token (round-robin), lane = features 4 l .. 4 l + 3.  Values are
+          // read back as OutT, i.e. rounded exactly as the stand-alone GEMM output would be.
+          const int ew = warp - 2;
+          const bool is_q = nt < qk.Hq, is_k = !is_q && nt < qk.Hq + qk.Hkv;
+          const OutT* nw = reinterpret_cast<const OutT*>(is_q ? qk.q_w : (is_k ? qk.k_w : nullptr));
+          float wv[4] = {1.f, 1.f, 1.f, 1.f};
+          if (nw != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = to_float<OutT>(nw[lane * 4 + j]) + (qk.gemma ? 1.f : 0.f);
+          }
+          for (int rr = ew; rr < T; rr += 4) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = to_float<OutT>(tile[rr * kTileStride + lane * 4 + j]);
+            if (is_q || is_k) {
+              if (nw != nullptr) {
+                float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float inv = rsqrtf(ss * (1.f / 128.f) + qk.eps);
+                // rounded to OutT between norm and rotary, as two separate kernels would
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = to_float<OutT>(from_float<OutT>(v[j] * inv * wv[j]));
+              }
+              int64_t pos = qk.positions[rr];
+              pos = pos < 0 ? 0 : (pos >= qk.max_pos ? qk.max_pos - 1 : pos);
+              const float* cs = qk.cos_sin + pos * 128;
+              if (qk.neox) {  // pairs (d, d + 64): lanes l and l ^ 16
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int f = (lane & 15) * 4 + j;
+                  const float c = cs[f], sn = cs[64 + f];
+                  const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+                  v[j] = lane < 16 ? v[j] * c - other * sn : v[j] * c + other * sn;
+                }
+              } else {        // pairs (2 i, 2 i + 1): both in this lane
+#pragma unroll
+                for (int j = 0; j < 4; j += 2) {
+                  const int f = lane * 2 + j / 2;
+                  const float c = cs[f], sn = cs[64 + f];
+                  const float a = v[j], b = v[j + 1];
+                  v[j] = a * c - b * sn;
+                  v[j + 1] = b * c + a * sn;
+                }
+              }
+            }
+            alignas(8) OutT o4[4] = {from_float<OutT>(v[0]), from_float<OutT>(v[1]), from_float<OutT>(v[2]),
+                                     from_float<OutT>(v[3])};
+            OutT* dst = nullptr;
+            if (is_q) {
+              dst = out + (size_t)rr * ldo + (size_t)nt * BM;
+            } else if (qk.kv_cache != nullptr) {
+              const int64_t slot = qk.slots[rr];
+              if (slot >= 0 && slot < qk.num_blocks * qk.block_size) {
+                const int kvh = is_k ? nt - qk.Hq : nt - qk.Hq - qk.Hkv;
+                const int64_t blk = slot / qk.block_size, off = slot % qk.block_size;
+                dst = reinterpret_cast<OutT*>(qk.kv_cache) +
+                      ((((blk * 2 + (is_k ? 0 : 1)) * qk.Hkv + kvh) * qk.block_size + off) * (int64_t)BM);
+              }
+            }
+            if (dst != nullptr) *reinterpret_cast<uint2*>(dst + lane * 4) = *reinterpret_cast<const uint2*>(o4);
+          }
+        } else if (act != 0) {
           const int n0 = nt * (BM / 2);
           const int seg = ep_tid & 7;  // 8 segments of 8 output features
           for (int rr = ep_tid >> 3; rr < BN; rr += 16) {
@@ -421,6 +500,11 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   for (int i = 0; i < 8; ++i) cm.ll_bufs[i] = a.ll_bufs[i];
   cm.epoch_word = (const uint32_t*)a.epoch_word;
   cm.slot_bytes = a.ll_slot_bytes; cm.on = a.ar_on; cm.rank = a.rank; cm.nranks = a.nranks;
+  QkvEpi qk;
+  qk.positions = a.qk_positions; qk.cos_sin = a.qk_cos_sin; qk.q_w = a.qk_q_w; qk.k_w = a.qk_k_w;
+  qk.kv_cache = a.qk_kv_cache; qk.slots = a.qk_slots; qk.num_blocks = a.qk_num_blocks; qk.max_pos = a.qk_max_pos;
+  qk.eps = a.qk_eps; qk.on = a.qk_on; qk.Hq = a.qk_hq; qk.Hkv = a.qk_hkv; qk.neox = a.qk_neox; qk.gemma = a.qk_gemma;
+  qk.block_size = a.qk_block_size;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(a.n_tiles * a.S);
   cfg.blockDim = dim3(kThreads);
@@ -437,7 +521,7 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.status, a.T, a.N, a.K,
                             a.kb_per_cta, a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), a.a_scale, a.w_scale,
-                            a.a_stride, cm);
+                            a.a_stride, cm, qk);
 }
 
 }  // namespace dec
@@ -452,6 +536,9 @@ extern "C" int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmW,
   if ((a->S - 1) * a->kb_per_cta >= (a->K + bke - 1) / bke && a->S > 1) return (int)cudaErrorInvalidValue;  // an empty CTA
   if (a->bn == 32 && a->S > 4) return (int)cudaErrorInvalidValue;
   if (a->fp8 && (a->act != 0 || a->a_scale == nullptr || a->w_scale == nullptr)) return (int)cudaErrorInvalidValue;
+  if (a->qk_on && (a->fp8 || a->act != 0 || a->ar_on || a->N != (a->qk_hq + 2 * a->qk_hkv) * 128 ||
+                   a->qk_positions == nullptr || a->qk_cos_sin == nullptr))
+    return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaErrorInvalidValue;
   // fmt gives the OUTPUT type for fp8 inputs (1 = bf16, 0 = fp16)
   if (a->fp8) {

@@ -360,3 +360,44 @@ def test_gemm_fused_gated_activation(T, act):
         _close(got, want, atol=0.01, rtol=0.02, name=f"fused {act} T={T}")
     ref = ops.act_and_mul((x.float().cpu() @ w.float().cpu().T + b.float().cpu()).to(torch.bfloat16), act)
     torch.testing.assert_close(got.float().cpu(), ref.float(), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,qk_norm,neox", [(16, 32, 8, False, True), (5, 4, 1, True, True), (32, 8, 2, True, False),
+                                                    (1, 16, 2, False, False)])
+def test_gemm_decode_qkv_epilogue(T, Hq, Hkv, qk_norm, neox):
+    """Decode qkv projection with split + q / k RMSNorm + rotary + paged-cache write in its epilogue == the projection
+    followed by the stand-alone split / norm / rope / cache kernel, bit for bit (both round the projection to bf16
+    first; the K sum is taken in the same order because the cluster size follows the same rule)."""
+    from vllm_kunlun_b200.models.layers import get_cos_sin_cache
+    from vllm_kunlun_b200.ops import _ext, gemm_cuda
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    D, K, bs, nblk = 128, 1024, 64, 5
+    g = torch.Generator(device=DEV).manual_seed(T + Hq)
+    N = (Hq + 2 * Hkv) * D
+    x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.04).bfloat16()
+    b = (torch.randn(N, device=DEV, generator=g) * 0.1).bfloat16()
+    qw = (torch.rand(D, device=DEV, generator=g) + 0.5).bfloat16() if qk_norm else None
+    kw = (torch.rand(D, device=DEV, generator=g) + 0.5).bfloat16() if qk_norm else None
+    pos = torch.randint(0, 3000, (T,), device=DEV, generator=g)
+    slots = torch.randperm(nblk * bs, device=DEV, generator=g)[:T].long()
+    if T > 2:
+        slots[2] = -1
+    cos_sin = get_cos_sin_cache(D, 4096, 10000.0, None, DEV)
+    cache = torch.zeros(nblk, 2, Hkv, bs, D, device=DEV, dtype=torch.bfloat16)
+    q = gemm_cuda.gemm_decode_qkv(x, w, b, pos, cos_sin, qw, kw, 1e-6, Hq, Hkv, neox, False, cache, slots)
+    torch.cuda.synchronize()
+    check_status()
+    qkv = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    _ext.C().gemm_decode(qkv, x, w, b, 0, 0, 0, 0)
+    cache2 = torch.zeros_like(cache)
+    q2 = ops.qkv_split_norm_rope_cache(qkv, pos, cos_sin, qw, kw, 1e-6, Hq, Hkv, D, neox, cache2, slots)
+    torch.cuda.synchronize()
+    assert torch.equal(q, q2)
+    assert torch.equal(cache, cache2)
+    # and against fp32 arithmetic on the rounded projection
+    from vllm_kunlun_b200.ops.reference import basic as rb
+    ref_qkv = (x.float().cpu() @ w.float().cpu().T + b.float().cpu()).bfloat16()
+    rq, rk, rv = rb.split_qknorm_rope(ref_qkv, pos.cpu(), cos_sin.cpu(), None if qw is None else qw.cpu(),
+                                      None if kw is None else kw.cpu(), 1e-6, Hq, Hkv, D, neox, False)
+    _close(q, rq, atol=0.06, rtol=0.03, name="qkv epilogue q")

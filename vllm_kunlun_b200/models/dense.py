@@ -19,7 +19,7 @@ from ..attention.metadata import get_forward_context
 from ..config import ModelConfig
 from ..parallel.state import get_state
 from .layers import (DTYPES, ColumnParallelLinear, ParallelLMHead, RMSNorm, RowParallelLinear,
-                     VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm, sp_sync)
+                     VocabParallelEmbedding, get_cos_sin_cache, param, reduce_add_rmsnorm, sp_sync, UnquantizedLinearMethod)
 
 
 ACT_FUSION = [os.environ.get("B200_FUSE_ACT", "1") != "0"]  # also switched off while LoRA adapters wrap gate / up
@@ -70,16 +70,32 @@ class GQAAttention(nn.Module):
     def forward(self, hidden):
         ctx = get_forward_context()
         md = ctx.attn
-        qkv = self.qkv_proj(hidden)
         kv_cache = ctx.kv_caches[self.layer_idx]
         if self.v_head_dim != self.head_dim:
             raise NotImplementedError("asymmetric V head dim goes through models.mimo")
+        proj = self.qkv_proj
+        if (hidden.is_cuda and type(proj) is ColumnParallelLinear and type(proj.method) is UnquantizedLinearMethod
+                and isinstance(kv_cache, torch.Tensor) and "forward" not in proj.__dict__):  # not wrapped (LoRA)
+            from ..ops import gemm_cuda
+            if gemm_cuda.qkv_epilogue_ok(hidden, proj.weight, self.head_dim, self.cfg.rotary_dim, kv_cache):
+                # decode-sized batch: the projection's epilogue splits, normalises, rotates and writes the cache
+                q = gemm_cuda.gemm_decode_qkv(
+                    hidden, proj.weight, proj.bias, md.positions, self.cos_sin,
+                    None if self.q_norm is None else self.q_norm.weight,
+                    None if self.k_norm is None else self.k_norm.weight,
+                    self.cfg.rms_norm_eps, self.num_heads, self.num_kv_heads, self.cfg.rope_neox, self.cfg.gemma_norm,
+                    kv_cache, md.slot_mapping)
+                return self._attend(q, kv_cache, md)
+        qkv = proj(hidden)
         q = ops.qkv_split_norm_rope_cache(
             qkv, md.positions, self.cos_sin,
             None if self.q_norm is None else self.q_norm.weight,
             None if self.k_norm is None else self.k_norm.weight,
             self.cfg.rms_norm_eps, self.num_heads, self.num_kv_heads, self.head_dim, self.cfg.rope_neox,
             kv_cache, md.slot_mapping, self.cfg.gemma_norm)
+        return self._attend(q, kv_cache, md)
+
+    def _attend(self, q, kv_cache, md):
         T = q.shape[0]
         o = ops.paged_attention(
             q.view(T, self.num_heads, self.head_dim), kv_cache, md.block_tables, md.seq_lens,

@@ -79,6 +79,32 @@ def gemm_decode_push(x: torch.Tensor, weight: torch.Tensor, peer, bias=None, out
     return out
 
 
+# qkv projection + split + q / k norm + rotary + cache write in one launch for decode-sized batches
+# (B200_QKV_EPILOGUE=0 keeps the projection and the split / rope / cache kernel apart)
+QKV_EPILOGUE = [os.environ.get("B200_QKV_EPILOGUE", "1") != "0"]
+
+
+def gemm_decode_qkv(x, weight, bias, positions, cos_sin, q_w, k_w, eps, num_heads, num_kv_heads, neox, gemma,
+                    kv_cache, slot_mapping):
+    """``q [T, Hq * 128]`` of a batch of at most 32 tokens; K and V go straight into the paged cache."""
+    global LAUNCHES
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    q = torch.empty(x2.shape[0], num_heads * 128, dtype=x.dtype, device=x.device)
+    _ext.C().gemm_decode_qkv(q, x2, weight, bias, positions, cos_sin, q_w, k_w, float(eps), num_heads, num_kv_heads,
+                             bool(neox), bool(gemma), kv_cache, slot_mapping)
+    LAUNCHES += 1
+    return q
+
+
+def qkv_epilogue_ok(x, weight, head_dim, rotary_dim, kv_cache) -> bool:
+    return (QKV_EPILOGUE[0] and DECODE_GEMM[0] and x.is_cuda and x.dim() == 2 and x.shape[0] <= 32 and head_dim == 128
+            and rotary_dim == 128 and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype
+            and weight.dim() == 2 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and x.shape[1] % 8 == 0
+            and (kv_cache is None or (kv_cache.dim() == 5 and kv_cache.is_contiguous() and kv_cache.dtype == x.dtype)))
+
+
 def check_status() -> None:
     """Raise if any GEMM CTA gave up on a bounded wait (a device-side status word, read on demand)."""
     code = _ext.C().gemm_status()
