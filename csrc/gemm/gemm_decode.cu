@@ -355,26 +355,29 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         for (int c = 0; c < BN; ++c) tile[c * kTileStride + n_local] = from_float<OutT>(acc[c] + bv);
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (qk.on) {
-          // ---- head nt of the fused qkv row: warp = token (round-robin), lane = features 4 l .. 4 l + 3.  Values are
-          // read back as OutT, i.e. rounded exactly as the stand-alone GEMM output would be.
+          // ---- head nt of the fused qkv row: warp = token (round-robin), lane = features l, l + 32, l + 64, l + 96 -
+          // the same distribution (and so the same fp32 summation order) as the stand-alone kernel.  Values are read
+          // back as OutT, i.e. rounded exactly as the stand-alone GEMM output would be.
           const int ew = warp - 2;
           const bool is_q = nt < qk.Hq, is_k = !is_q && nt < qk.Hq + qk.Hkv;
           const OutT* nw = reinterpret_cast<const OutT*>(is_q ? qk.q_w : (is_k ? qk.k_w : nullptr));
           float wv[4] = {1.f, 1.f, 1.f, 1.f};
           if (nw != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) wv[j] = to_float<OutT>(nw[lane * 4 + j]) + (qk.gemma ? 1.f : 0.f);
+            for (int j = 0; j < 4; ++j) wv[j] = to_float<OutT>(nw[lane + 32 * j]) + (qk.gemma ? 1.f : 0.f);
           }
           for (int rr = ew; rr < T; rr += 4) {
             float v[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = to_float<OutT>(tile[rr * kTileStride + lane * 4 + j]);
+            for (int j = 0; j < 4; ++j) v[j] = to_float<OutT>(tile[rr * kTileStride + lane + 32 * j]);
             if (is_q || is_k) {
               if (nw != nullptr) {
-                float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ss += v[j] * v[j];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                const float inv = rsqrtf(ss * (1.f / 128.f) + qk.eps);
+                const float inv = rsqrtf(ss / 128 + qk.eps);
                 // rounded to OutT between norm and rotary, as two separate kernels would
 #pragma unroll
                 for (int j = 0; j < 4; ++j) v[j] = to_float<OutT>(from_float<OutT>(v[j] * inv * wv[j]));
@@ -382,27 +385,25 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
               int64_t pos = qk.positions[rr];
               pos = pos < 0 ? 0 : (pos >= qk.max_pos ? qk.max_pos - 1 : pos);
               const float* cs = qk.cos_sin + pos * 128;
-              if (qk.neox) {  // pairs (d, d + 64): lanes l and l ^ 16
+              if (qk.neox) {  // pairs (d, d + 64) = (v[0], v[2]) and (v[1], v[3]) of this lane
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  const int f = lane + 32 * j;
+                  const float c = cs[f], sn = cs[64 + f];
+                  const float x0 = v[j], y0 = v[j + 2];
+                  v[j] = x0 * c - y0 * sn;
+                  v[j + 2] = y0 * c + x0 * sn;
+                }
+              } else {        // pairs (2 i, 2 i + 1): lanes l and l ^ 1
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  const int f = (lane & 15) * 4 + j;
+                  const int f = (lane + 32 * j) >> 1;
                   const float c = cs[f], sn = cs[64 + f];
-                  const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-                  v[j] = lane < 16 ? v[j] * c - other * sn : v[j] * c + other * sn;
-                }
-              } else {        // pairs (2 i, 2 i + 1): both in this lane
-#pragma unroll
-                for (int j = 0; j < 4; j += 2) {
-                  const int f = lane * 2 + j / 2;
-                  const float c = cs[f], sn = cs[64 + f];
-                  const float a = v[j], b = v[j + 1];
-                  v[j] = a * c - b * sn;
-                  v[j + 1] = b * c + a * sn;
+                  const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                  v[j] = (lane & 1) == 0 ? v[j] * c - other * sn : v[j] * c + other * sn;
                 }
               }
             }
-            alignas(8) OutT o4[4] = {from_float<OutT>(v[0]), from_float<OutT>(v[1]), from_float<OutT>(v[2]),
-                                     from_float<OutT>(v[3])};
             OutT* dst = nullptr;
             if (is_q) {
               dst = out + (size_t)rr * ldo + (size_t)nt * BM;
@@ -415,7 +416,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                       ((((blk * 2 + (is_k ? 0 : 1)) * qk.Hkv + kvh) * qk.block_size + off) * (int64_t)BM);
               }
             }
-            if (dst != nullptr) *reinterpret_cast<uint2*>(dst + lane * 4) = *reinterpret_cast<const uint2*>(o4);
+            if (dst != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = from_float<OutT>(v[j]);
+            }
           }
         } else if (act != 0) {
           const int n0 = nt * (BM / 2);
