@@ -36,6 +36,10 @@ typedef struct GemmArgs {
   const void* ag_flags;  // all-gather: local per-token-tile arrival counters
   int rs_on, rs_tloc, rs_rank, ag_on, ag_expect;
   unsigned spin_limit;
+  // signed 8-bit operands (kind::i8): per-token activation scales [T], per-channel weight scales [N]; fmt = output type
+  int i8;
+  const float* a_scale;
+  const float* w_scale;
 } GemmArgs;
 int b200_gemm_pick_bn(int T);
 int b200_gemm_launch(const GemmArgs* a, const void* tmapW, const void* tmapX, cudaStream_t st);
@@ -65,6 +69,7 @@ typedef struct GemmDecodeArgs {
   const float* a_scale;    // [ceil(K/128), a_stride] transposed activation scales
   const float* w_scale;    // [ceil(N/128), ceil(K/128)]
   int a_stride;
+  int i8;  // signed 8-bit operands (kind::i8): a_scale [T] per token, w_scale [N] per channel; fmt = output type
   // qkv epilogue (head_dim 128): split + optional q / k RMSNorm + rotary + K / V cache write; out = q [T, Hq * 128]
   int qk_on, qk_hq, qk_hkv, qk_neox, qk_gemma, qk_block_size;
   float qk_eps;
@@ -166,6 +171,8 @@ int b200_mla_decode_umma(void* out, const void* q, const void* tmap, const int* 
                          float scale, int early_meta, int dtype, unsigned long long* trace, cudaStream_t st);
 
 int b200_mla_decode_max_clusters(int R, int S, int dtype);
+int b200_quant_int8_token(void* q, float* scale, const void* x, const float* static_scale, int64_t rows, int K,
+                          int64_t x_stride, int dtype, cudaStream_t st);
 int b200_indexer_logits_umma(float* logits, const void* tmQ, const float* w, const void* cache, const void* tmK,
                              const int* block_tables, const int* seq_lens, const int* qsl, int* status, int B,
                              int max_query_len, int max_blocks, int64_t num_blocks, int64_t ld, int64_t t_lo, int64_t t_hi,

@@ -201,6 +201,85 @@ void gemm(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const c10::o
   gs.launches++;
 }
 
+// (q int8 [rows, K], scale float [rows]); static_scale: a one-element tensor for per-tensor static quantisation.
+std::vector<at::Tensor> quant_int8_token(const at::Tensor& x, const c10::optional<at::Tensor>& static_scale) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.is_cuda());
+  if (static_scale.has_value()) TORCH_CHECK(static_scale->scalar_type() == at::kFloat && static_scale->numel() >= 1);
+  auto q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kChar));
+  auto s = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  check(b200_quant_int8_token(q.data_ptr(), s.data_ptr<float>(), x.data_ptr(),
+                              static_scale.has_value() ? static_scale->data_ptr<float>() : nullptr, x.size(0),
+                              (int)x.size(1), x.stride(0), dtype_code(x), stream()),
+        "quant_int8_token");
+  return {q, s};
+}
+
+// W8A8 int8 linear on kind::i8: out[T, N] = (xq[T, K] . w[N, K]^T) * a_scale[T] * w_scale[N] (+ bias); s32 accumulation.
+// At most 32 rows go to the cluster split-K kernel, larger batches to the dense kernel in whole tiles.
+void gemm_int8(at::Tensor out, const at::Tensor& xq, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+               const at::Tensor& a_scale, const at::Tensor& w_scale) {
+  TORCH_CHECK(xq.is_cuda() && w.is_cuda() && out.is_cuda() && xq.dim() == 2 && w.dim() == 2 && out.dim() == 2);
+  TORCH_CHECK(xq.scalar_type() == at::kChar && w.scalar_type() == at::kChar, "gemm_int8: int8 operands");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kHalf);
+  TORCH_CHECK(xq.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1);
+  const int T = xq.size(0), K = xq.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == T && out.size(1) == N);
+  TORCH_CHECK(K % 16 == 0 && xq.stride(0) % 16 == 0 && w.stride(0) % 16 == 0, "gemm_int8: K and row strides: multiples of 16");
+  TORCH_CHECK(a_scale.scalar_type() == at::kFloat && a_scale.is_contiguous() && a_scale.numel() >= T);
+  TORCH_CHECK(w_scale.scalar_type() == at::kFloat && w_scale.is_contiguous() && w_scale.numel() == N);
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == out.scalar_type() && bias->numel() == N);
+  if (T == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(xq.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, out.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, out.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, out.options().dtype(at::kInt));
+  }
+  const int total_kb = (K + 127) / 128;
+  const int fmt = out.scalar_type() == at::kBFloat16 ? 1 : 0;
+  if (T <= 32) {
+    GemmDecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.out = out.data_ptr(); a.bias = opt_ptr(bias); a.status = gs.status.data_ptr<int>();
+    a.T = T; a.N = N; a.K = K;
+    a.n_tiles = (N + 127) / 128;
+    a.bn = T <= 16 ? 16 : 32;
+    a.fmt = fmt; a.ldo = out.stride(0);
+    a.i8 = 1; a.a_scale = a_scale.data_ptr<float>(); a.w_scale = w_scale.data_ptr<float>();
+    const int max_s = a.bn == 16 ? 8 : 4;
+    int S = 1;
+    while (S * 2 <= max_s && a.n_tiles * S * 2 <= gs.num_sms && total_kb / (S * 2) >= 4) S *= 2;
+    while (S > 1 && (S - 1) * ((total_kb + S - 1) / S) >= total_kb) --S;
+    a.S = S;
+    a.kb_per_cta = (total_kb + S - 1) / S;
+    a.ctas_per_sm = a.n_tiles * S > gs.num_sms ? 2 : 1;
+    const Tmap& tw = get_tmap(gs, w, 128, 1);
+    const Tmap& tx = get_tmap(gs, xq, a.bn, 1);
+    check(b200_gemm_decode_launch(&a, tw.b, tx.b, stream()), "gemm_int8 (decode) launch");
+  } else {
+    GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.spin_limit = 1u << 22;
+    a.bn = b200_gemm_pick_bn(T);
+    a.T = T; a.N = N; a.K = K;
+    a.n_tiles = (N + 127) / 128;
+    a.t_tiles = (T + a.bn - 1) / a.bn;
+    a.per_cta = 0; a.max_contrib = 1;
+    a.grid = std::min(a.n_tiles * a.t_tiles, gs.num_sms);
+    a.out = out.data_ptr(); a.bias = opt_ptr(bias); a.ws = gs.ws.data_ptr<float>();
+    a.counters = gs.counters.data_ptr<int>(); a.status = gs.status.data_ptr<int>();
+    a.fmt = fmt; a.ldo = out.stride(0); a.num_sms = gs.num_sms;
+    a.i8 = 1; a.a_scale = a_scale.data_ptr<float>(); a.w_scale = w_scale.data_ptr<float>();
+    const Tmap& tw = get_tmap(gs, w, 128, 1);
+    const Tmap& tx = get_tmap(gs, xq, a.bn, 1);
+    check(b200_gemm_launch(&a, tw.b, tx.b, stream()), "gemm_int8 launch");
+  }
+  gs.launches++;
+}
+
 // Row-parallel push epilogue for the NEXT gemm_decode() call: the output is also written, as {data, epoch} units,
 // into the low-latency all-reduce slots of every peer (consumed by ll_allreduce(..., skip_push = true)).
 struct DecCommState {
@@ -1194,6 +1273,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_decode", &gemm_decode);
   m.def("gemm_decode_fp8", &gemm_decode_fp8);
   m.def("gemm_decode_qkv", &gemm_decode_qkv);
+  m.def("gemm_int8", &gemm_int8);
+  m.def("quant_int8_token", &quant_int8_token);
   m.def("set_gemm_decode_comm", &set_gemm_decode_comm);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("moe_route", &moe_route);

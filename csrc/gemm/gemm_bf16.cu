@@ -87,6 +87,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                OutT* __restrict__ out, const OutT* __restrict__ bias, float* __restrict__ ws,
                int* __restrict__ counters, int* __restrict__ status, int T, int N, int K, int n_tiles,
                int t_tiles, int per_cta, int max_contrib, int fmt, int ldo, int num_stages, int l2_prefetch, int act,
+               const float* __restrict__ a_scale, const float* __restrict__ w_scale,
                const __grid_constant__ GemmComm cm) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -104,7 +105,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_kb = (K + BK - 1) / BK;
+  // fmt == 2: signed 8-bit operands on kind::i8 (whole tiles only; the host never splits K for them): a k-block is
+  // then 128 K-elements (still one 128-byte swizzle row), accumulators are s32, and the epilogue multiplies by the
+  // per-token activation scale a_scale [T] and the per-channel weight scale w_scale [N]
+  const bool i8 = fmt == 2;
+  const int bke = i8 ? 128 : BK;
+  const int total_kb = (K + bke - 1) / bke;
   const int num_tiles = n_tiles * t_tiles;
   Abort ab{status, abort_flag};
 
@@ -204,10 +210,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int kb = kb0; kb < kb1; ++kb) {
             if (pre < num_stages) {
               mbar_expect_tx(&full_bar[pre], Cfg::kStageBytes);
-              tma_load_2d_hint(smem + pre * Cfg::kStageBytes, &tmW, &full_bar[pre], kb * BK, nt * BM, pol_w);
+              tma_load_2d_hint(smem + pre * Cfg::kStageBytes, &tmW, &full_bar[pre], kb * bke, nt * BM, pol_w);
               ++pre;
             } else if (l2_ahead > 0) {
-              tma_prefetch_l2_2d(&tmW, kb * BK, nt * BM);
+              tma_prefetch_l2_2d(&tmW, kb * bke, nt * BM);
               --l2_ahead;
             } else {
               break;
@@ -236,12 +242,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageBytesA;
           if (issued < pre) {
-            tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
+            tma_load_2d(sb, &tmX, &full_bar[stage], kb * bke, tt * BN);
           } else {
             if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 101)) { ok = false; break; }
             mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-            tma_load_2d_hint(sa, &tmW, &full_bar[stage], kb * BK, nt * BM, pol_w);
-            tma_load_2d(sb, &tmX, &full_bar[stage], kb * BK, tt * BN);
+            tma_load_2d_hint(sa, &tmW, &full_bar[stage], kb * bke, nt * BM, pol_w);
+            tma_load_2d(sb, &tmX, &full_bar[stage], kb * bke, tt * BN);
           }
           ++issued;
           if (++stage == num_stages) { stage = 0; phase ^= 1; }
@@ -266,7 +272,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       // for what it is meant for - the copies - however long the previous kernel (say, an all-reduce that waits
       // for a late peer) takes.
       griddep_wait();
-      const uint32_t idesc = umma_idesc(BM, BN, fmt, fmt);
+      const uint32_t idesc = i8 ? umma_idesc_i8(BM, BN) : umma_idesc(BM, BN, fmt, fmt);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -288,7 +294,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t da = umma_desc_k_sw128(sa + k * UMMA_K * 2);
             uint64_t db = umma_desc_k_sw128(sb + k * UMMA_K * 2);
-            umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (i8) umma_i8(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == num_stages) { stage = 0; phase ^= 1; }
@@ -324,6 +331,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const bool n_ok = n < N;
       if (kb0 == 0 && kb1 == total_kb) {
         float bv = (bias != nullptr && n_ok) ? to_float<OutT>(bias[n]) : 0.f;
+        const float wsc = (i8 && n_ok) ? w_scale[n] : 0.f;
+        // accumulator word of token t -> real value (+ bias)
+        auto val = [&](uint32_t r, int t) -> float {
+          if (i8) return (float)(int)r * wsc * (t < T ? a_scale[t] : 0.f) + bv;
+          return __uint_as_float(r) + bv;
+        };
         // destination row of token t: the local output, or the owner rank's staging area
         auto row_ptr = [&](int t) -> OutT* {
           if (cm.rs_on) {
@@ -390,7 +403,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                  smem_ep[(c + j) * kEpStride + n_local] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+                  smem_ep[(c + j) * kEpStride + n_local] = from_float<OutT>(val(r[j], t0 + c0 + c + j));
               }
             }
             if (c0 + kEpChunk >= BN) {  // accumulator fully read: hand the TMEM buffer back
@@ -427,7 +440,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 int t = t0 + c + j;
-                if (t < T) row_ptr(t)[n] = from_float<OutT>(__uint_as_float(r[j]) + bv);
+                if (t < T) row_ptr(t)[n] = from_float<OutT>(val(r[j], t));
               }
             }
           }
@@ -548,7 +561,8 @@ static cudaError_t launch_bn(const GemmArgs& a, const CUtensorMap& tmW, const CU
   int smem = stages * Cfg::kStageBytes + 1024 + 512 + kEpBytes;
   return launch_pdl(kern, dim3(a.grid), dim3(kGemmThreads), (size_t)smem, st, tmW, tmX, (OutT*)a.out,
                     (const OutT*)a.bias, a.ws, a.counters, a.status, a.T, a.N, a.K, a.n_tiles, a.t_tiles, a.per_cta,
-                    a.max_contrib, a.fmt, a.ldo, stages, b200::gemm_l2_prefetch(), a.act, cm);
+                    a.max_contrib, a.i8 ? 2 : a.fmt, a.ldo, stages, b200::gemm_l2_prefetch(), a.act, a.a_scale, a.w_scale,
+                    cm);
 }
 
 }  // namespace b200
@@ -568,6 +582,9 @@ extern "C" int b200_gemm_launch(const GemmArgs* a, const void* tmW, const void* 
   const CUtensorMap& w = *reinterpret_cast<const CUtensorMap*>(tmW);
   const CUtensorMap& x = *reinterpret_cast<const CUtensorMap*>(tmX);
   cudaError_t e = cudaErrorInvalidValue;
+  // 8-bit integer operands: whole tiles, plain epilogue, scales required
+  if (a->i8 && (a->per_cta != 0 || a->act != 0 || a->rs_on || a->ag_on || a->a_scale == nullptr || a->w_scale == nullptr))
+    return (int)e;
 #define B200_BN_CASE(BN_)                                                                              \
   case BN_:                                                                                            \
     e = (a->fmt == 1) ? launch_bn<BN_, __nv_bfloat16>(*a, w, x, st) : launch_bn<BN_, __half>(*a, w, x, st); \

@@ -114,7 +114,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                    const float* __restrict__ a_scale, const float* __restrict__ w_scale, int a_stride,
                    const __grid_constant__ Comm cm, const __grid_constant__ QkvEpi qk) {
   using C = Cfg<BN>;
-  constexpr int BKE = kFp8 ? 128 : BK;  // K elements per k-block
+  constexpr int BKE8 = 128;             // K elements per k-block of 8-bit operands (still one 128-byte swizzle row)
+  // fmt == 2 (non-fp8 instantiation): signed 8-bit operands on kind::i8 with per-token activation scales
+  // (a_scale [T]) and per-channel weight scales (w_scale [N]) applied by the final epilogue
+  const bool i8 = !kFp8 && fmt == 2;
+  const int BKE = (kFp8 || i8) ? BKE8 : BK;  // K elements per k-block
   constexpr int kCols = kFp8 ? C::kTmemColsFp8 : C::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -215,7 +219,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       // the first full barrier needs the activations, i.e. the previous kernel: wait for that dependency here
       // (unbounded by nature) so that the bounded wait below covers only the copies
       griddep_wait();
-      const uint32_t idesc = kFp8 ? umma_idesc(BM, BN, 0, 0) : umma_idesc(BM, BN, fmt, fmt);
+      const uint32_t idesc = kFp8 ? umma_idesc(BM, BN, 0, 0) : (i8 ? umma_idesc_i8(BM, BN) : umma_idesc(BM, BN, fmt, fmt));
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -234,6 +238,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           uint64_t da = umma_desc_k_sw128(sa + k * 32);
           uint64_t db = umma_desc_k_sw128(sb + k * 32);
           if (kFp8) umma_f8(tmem_base + ab_buf * BN, da, db, idesc, k > 0 ? 1u : 0u);
+          else if (i8) umma_i8(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
           else umma_f16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
@@ -304,7 +309,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tmem_ld_x16(taddr + c, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[c + j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) acc[c + j] = i8 ? (float)(int)r[j] : __uint_as_float(r[j]);
       }
     } else {
 #pragma unroll
@@ -351,6 +356,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         // ---- final epilogue: stage [token][feature] as OutT, then 16-byte row segments
         const int n = nt * BM + n_local;
         const float bv = (bias != nullptr && n < N) ? to_float<OutT>(bias[n]) : 0.f;
+        if (i8) {  // integer sums -> real values
+          const float ws = n < N ? w_scale[n] : 0.f;
+#pragma unroll
+          for (int c = 0; c < BN; ++c) acc[c] *= ws * (c < T ? a_scale[c] : 0.f);
+        }
 #pragma unroll
         for (int c = 0; c < BN; ++c) tile[c * kTileStride + n_local] = from_float<OutT>(acc[c] + bv);
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -490,7 +500,7 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
     cudaError_t e = ensure_dynamic_smem((const void*)kern, 220 * 1024);
     if (e != cudaSuccess) return e;
   }
-  const int total_kb = (a.K + (kFp8 ? 128 : BK) - 1) / (kFp8 ? 128 : BK);
+  const int total_kb = (a.K + ((kFp8 || a.i8) ? 128 : BK) - 1) / ((kFp8 || a.i8) ? 128 : BK);
   const int nkb = a.kb_per_cta;
   // shared memory per CTA: about half an SM when two CTAs should be resident together
   int budget = (a.ctas_per_sm >= 2 ? 112 * 1024 : 216 * 1024) - fixed;
@@ -524,7 +534,7 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.status, a.T, a.N, a.K,
-                            a.kb_per_cta, a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), a.a_scale, a.w_scale,
+                            a.kb_per_cta, a.i8 ? 2 : a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), a.a_scale, a.w_scale,
                             a.a_stride, cm, qk);
 }
 
@@ -536,10 +546,12 @@ extern "C" int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmW,
   const CUtensorMap& w = *reinterpret_cast<const CUtensorMap*>(tmW);
   const CUtensorMap& x = *reinterpret_cast<const CUtensorMap*>(tmX);
   if (a->S < 1 || a->S > 8 || a->T > a->bn || a->kb_per_cta < 1) return (int)cudaErrorInvalidValue;
-  const int bke = a->fp8 ? 128 : 64;
+  const int bke = (a->fp8 || a->i8) ? 128 : 64;
   if ((a->S - 1) * a->kb_per_cta >= (a->K + bke - 1) / bke && a->S > 1) return (int)cudaErrorInvalidValue;  // an empty CTA
   if (a->bn == 32 && a->S > 4) return (int)cudaErrorInvalidValue;
   if (a->fp8 && (a->act != 0 || a->a_scale == nullptr || a->w_scale == nullptr)) return (int)cudaErrorInvalidValue;
+  if (a->i8 && (a->fp8 || a->act != 0 || a->ar_on || a->qk_on || a->a_scale == nullptr || a->w_scale == nullptr))
+    return (int)cudaErrorInvalidValue;
   if (a->qk_on && (a->fp8 || a->act != 0 || a->ar_on || a->N != (a->qk_hq + 2 * a->qk_hkv) * 128 ||
                    a->qk_positions == nullptr || a->qk_cos_sin == nullptr))
     return (int)cudaErrorInvalidValue;

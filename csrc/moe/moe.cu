@@ -532,6 +532,40 @@ extern "C" int b200_moe_unpermute(void* out, const void* y_sorted, const int* po
   return (int)cudaGetLastError();
 }
 
+// Per-token int8 quantisation of activations (compressed-tensors W8A8; reference: quantization/kernels/
+// scale_mm.py:43-90).  Dynamic: scale[t] = max|x[t]| / 127; static: the given per-tensor scale.  One warp per row.
+template <typename T>
+__global__ void quant_int8_token_kernel(int8_t* __restrict__ q, float* __restrict__ scale, const T* __restrict__ x,
+                                        const float* __restrict__ static_scale, int64_t rows, int K, int64_t x_stride) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* src = x + row * x_stride;
+  float s;
+  if (static_scale != nullptr) {
+    s = static_scale[0];
+  } else {
+    float amax = 0.f;
+    for (int i = lane; i < K; i += 32) amax = fmaxf(amax, fabsf(to_f(src[i])));
+    s = fmaxf(warp_max(amax), 1e-8f) / 127.f;
+  }
+  if (lane == 0) scale[row] = s;
+  for (int i = lane; i < K; i += 32) {
+    const float v = rintf(to_f(src[i]) / s);
+    q[row * K + i] = (int8_t)fminf(fmaxf(v, -128.f), 127.f);
+  }
+}
+
+extern "C" int b200_quant_int8_token(void* q, float* scale, const void* x, const float* static_scale, int64_t rows,
+                                     int K, int64_t x_stride, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    quant_int8_token_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>((int8_t*)q, scale, (const T*)x, static_scale,
+                                                                         rows, K, x_stride);
+  });
+  return (int)cudaGetLastError();
+}
+
 extern "C" int b200_quant_fp8_group(void* q, float* scale_t, const void* x, int64_t rows, int K, int64_t x_stride,
                                     int64_t s_stride, int ue8m0, const int* rows_valid_ptr, int dtype,
                                     cudaStream_t st) {

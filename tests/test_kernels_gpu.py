@@ -401,3 +401,40 @@ def test_gemm_decode_qkv_epilogue(T, Hq, Hkv, qk_norm, neox):
     rq, rk, rv = rb.split_qknorm_rope(ref_qkv, pos.cpu(), cos_sin.cpu(), None if qw is None else qw.cpu(),
                                       None if kw is None else kw.cpu(), 1e-6, Hq, Hkv, D, neox, False)
     _close(q, rq, atol=0.06, rtol=0.03, name="qkv epilogue q")
+
+
+@pytest.mark.parametrize("T,N,K", [(16, 512, 1024), (1, 128, 256), (32, 1000, 4096), (100, 384, 2048), (300, 1536, 7168),
+                                   (7, 2048, 11008 // 16 * 16)])
+@pytest.mark.parametrize("static", [False, True])
+def test_int8_w8a8_tensor_core_gemm(T, N, K, static):
+    """W8A8 int8 on tcgen05 kind::i8 (s32 accumulation: exact integer sums) - the activation quantiser, the cluster
+    split-K kernel (<= 32 rows) and the dense kernel - against integer arithmetic on the same quantised operands."""
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    from vllm_kunlun_b200.ops.reference import basic as rb
+    g = torch.Generator().manual_seed(T + N)
+    x = (torch.randn(T, K, generator=g) * 1.5).bfloat16()
+    wf = torch.randn(N, K, generator=g) * 0.05
+    ws = wf.abs().amax(-1, keepdim=True).clamp(min=1e-8) / 127.0
+    wq = torch.round(wf / ws).clamp(-128, 127).to(torch.int8)
+    bias = torch.randn(N, generator=g).bfloat16()
+    in_scale = torch.tensor([0.04]) if static else None
+    C = _ext.C()
+    q, s = C.quant_int8_token(x.to(DEV), None if in_scale is None else in_scale.to(DEV))
+    if static:
+        rq, rs = rb.quant_int8_static(x, in_scale), in_scale.expand(T).reshape(T, 1)
+    else:
+        rq, rs = rb.quant_int8_per_token(x)
+    torch.testing.assert_close(s.cpu(), rs.reshape(-1).float(), rtol=1e-6, atol=0)
+    assert (q.cpu().int() - rq.int()).abs().max() <= 1        # a value on a rounding edge may land on either side
+    assert (q.cpu() != rq).float().mean() < 1e-3
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    C.gemm_int8(out, q, wq.to(DEV), bias.to(DEV), s, ws.reshape(-1).to(DEV))
+    torch.cuda.synchronize()
+    check_status()
+    ref = rb.int8_scaled_mm(q.cpu(), s.cpu().reshape(T, 1), wq, ws.reshape(-1), bias, torch.float32)
+    # integer sums are exact; what is left is the bf16 rounding of the output
+    _close(out, ref, atol=1e-2, rtol=8e-3, name=f"int8 gemm {T}x{N}x{K}")
+    # and through the functional entry point
+    y = ops.int8_linear(x.to(DEV), wq.to(DEV), ws.to(DEV), bias.to(DEV), None if in_scale is None else in_scale.to(DEV))
+    assert torch.equal(y, out)

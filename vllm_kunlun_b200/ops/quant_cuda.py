@@ -47,10 +47,26 @@ def fp8_linear_cuda(x, w_fp8, w_scale_inv, bias=None, block=(128, 128), out_dtyp
     return out.reshape(*lead, N)
 
 
+# W8A8 on the int8 tensor-core path (kind::i8); B200_INT8_TC=0 de-quantises the weight once and runs the 16-bit GEMM
+INT8_TC = [os.environ.get("B200_INT8_TC", "1") != "0"]
+
+
 def int8_linear_cuda(x2, w_q, w_scale, bias, input_scale, out_dtype):
-    """W8A8 int8: weights are dequantised once into a cached bf16 copy in the GEMM layout and the
-    product runs on the 16-bit tcgen05 GEMM (per-channel weight scales fold into the cached copy;
-    activations stay in 16-bit, which is at least as accurate as the int8 path)."""
+    """W8A8 int8 (``quantization/kernels/scale_mm.py:43-90`` of the reference): activations are quantised per
+    token (dynamic) or with the checkpoint's per-tensor scale (static) by ``quant_int8_token_kernel``, the product
+    runs on ``tcgen05.mma.kind::i8`` with s32 accumulators, and the epilogue applies ``a_scale[t] * w_scale[n]``."""
+    K = x2.shape[1]
+    if (INT8_TC[0] and out_dtype in (torch.bfloat16, torch.float16) and K % 16 == 0 and w_q.dtype == torch.int8
+            and w_q.is_contiguous() and x2.dtype in (torch.bfloat16, torch.float16, torch.float32)):
+        C = _ext.C()
+        xin = x2 if x2.stride(1) == 1 else x2.contiguous()
+        st = None if input_scale is None else input_scale.float().reshape(-1).contiguous()
+        q, s = C.quant_int8_token(xin, st)
+        out = torch.empty(x2.shape[0], w_q.shape[0], dtype=out_dtype, device=x2.device)
+        ws = w_scale.float().reshape(-1).contiguous()
+        b = None if bias is None else bias.to(out_dtype)
+        C.gemm_int8(out, q, w_q, b, s, ws)
+        return out
     from .gemm_cuda import gemm_bf16
     key = "_b200_dequant"
     wd = getattr(w_q, key, None)
