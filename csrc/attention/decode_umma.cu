@@ -114,8 +114,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
   uint64_t* s_empty = s_full + 2;                  // [2]
   uint64_t* p_ready = s_empty + 2;                 // [2]
   uint64_t* p_free = p_ready + 2;                  // [2]
-  uint64_t* o_done = p_free + 2;                   // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* o_done = p_free + 2;                   // [1] one phase per P.V (rescale waits, at most one phase behind)
+  uint64_t* o_final = o_done + 1;                  // [1] committed once, after the last P.V (epilogue wait)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_final + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4]
   int* s_last = reinterpret_cast<int*>(tmem_slot + 6);
@@ -134,6 +135,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
       mbar_init(&p_ready[b], 4); mbar_init(&p_free[b], 1);
     }
     mbar_init(o_done, 1);
+    mbar_init(o_final, 1);
     mbar_fence_init();
     prefetch_tmap(&tmKV);
     griddep_launch();
@@ -280,6 +282,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
         umma_commit(o_done);
         umma_commit(&kv_empty[stage]);
         umma_commit(&p_free[pb]);
+        if (i == n_tiles - 1) umma_commit(o_final);
       };
       int next_s = 0, next_pv = 0;
       uint32_t spins = 0;
@@ -417,10 +420,9 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_consta
     if (fail) ok = false;
     // ---- epilogue: O^T lane = output dim, 16 columns = query rows
     if (ok && n_tiles > 0) {
-      // A parity wait is only meaningful when the barrier is at most one phase behind the awaited one; the p_free
-      // wait of the last tile guarantees P.V(n - 3), so P.V(n - 2) is awaited first, then the last one.
-      if (n_tiles >= 2 && !wait_or_abort(o_done, (n_tiles - 2) & 1, ab, 507)) ok = false;
-      if (ok && !wait_or_abort(o_done, (n_tiles - 1) & 1, ab, 507)) ok = false;
+      // A parity wait on o_done would be wrong here: by now the barrier may be one phase short of the last P.V, at
+      // it, or past it, and parity cannot tell the first from the last.  o_final completes exactly once.
+      if (!wait_or_abort(o_final, 0, ab, 507)) ok = false;
       tc_fence_after_sync();
     }
     ok = bar_red_or(1, 128, !ok) == 0;   // one thread's time-out ends the tile for all

@@ -106,7 +106,8 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
   uint64_t* p_free = bars + 10;                // [2]
   uint64_t* o_done = bars + 12;                // [1]
   uint64_t* merge_bar = bars + 13;             // [1] bulk copies of the split merge
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* o_final = bars + 14;               // [1] committed once, after the last P.V (epilogue wait)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* ok_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4]
   int* s_last = reinterpret_cast<int*>(tmem_slot + 6);
@@ -129,6 +130,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
     }
     mbar_init(o_done, 1);
     mbar_init(merge_bar, 1);
+    mbar_init(o_final, 1);
     mbar_fence_init();
     prefetch_tmap(&tmKV);
     griddep_launch();
@@ -256,6 +258,7 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
         umma_commit(o_done);
         umma_commit(&kv_empty[stage]);
         umma_commit(&p_free[pb]);
+        if (i == n_tiles - 1) umma_commit(o_final);
       };
       int next_s = 0, next_pv = 0;
       uint32_t spins = 0;
@@ -409,10 +412,9 @@ mla_decode_umma_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_co
     if (fail) ok = false;
     if (tid == 0) trace_mark(p.trace, cta_id, 3);  // last P written
     if (ok && n_tiles > 0) {
-      // A parity wait is only meaningful when the barrier is at most one phase behind the awaited one; the p_free
-      // wait of the last tile guarantees P.V(n - 3), so P.V(n - 2) is awaited first, then the last one.
-      if (n_tiles >= 2 && !wait_or_abort(o_done, (n_tiles - 2) & 1, ab, 607)) ok = false;
-      if (ok && !wait_or_abort(o_done, (n_tiles - 1) & 1, ab, 607)) ok = false;
+      // A parity wait on o_done would be wrong here: by now the barrier may be one phase short of the last P.V, at
+      // it, or past it, and parity cannot tell the first from the last.  o_final completes exactly once.
+      if (!wait_or_abort(o_final, 0, ab, 607)) ok = false;
       tc_fence_after_sync();
     }
     ok = bar_red_or(1, 128, !ok) == 0;   // one thread's time-out ends the tile for all
