@@ -171,6 +171,8 @@ int b200_mla_decode_umma(void* out, const void* q, const void* tmap, const int* 
                          float scale, int early_meta, int dtype, unsigned long long* trace, cudaStream_t st);
 
 int b200_mla_decode_max_clusters(int R, int S, int dtype);
+int b200_gather_mla_rows(void* out, const void* cache, const int32_t* slots, int64_t M, int64_t total_slots, int fp8,
+                         int dtype, cudaStream_t st);
 int b200_quant_int8_token(void* q, float* scale, const void* x, const float* static_scale, int64_t rows, int K,
                           int64_t x_stride, int dtype, cudaStream_t st);
 int b200_indexer_logits_umma(float* logits, const void* tmQ, const float* w, const void* cache, const void* tmK,

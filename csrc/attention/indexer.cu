@@ -145,10 +145,14 @@ __device__ __forceinline__ uint32_t f2ord(float f) {
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-// One CTA per row: indices of the k largest of logits[row, 0..n), unordered, -1 padded.
+// One CTA per row: indices of the k largest of logits[row, 0..n), unordered, -1 padded (4-pass radix select on the
+// order-preserving 32-bit keys, then two collection passes).  kResident: the row's keys are loaded into shared memory
+// once and all six passes run there (rows of up to ~55 K entries); otherwise every pass re-reads the row.
+template <bool kResident>
 __global__ void __launch_bounds__(512) topk_rows_kernel(int* __restrict__ out, const float* __restrict__ logits,
                                                         const int* __restrict__ row_len, int64_t ld, int k,
                                                         int64_t max_len) {
+  extern __shared__ uint32_t s_keys[];
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix, s_mask;
   __shared__ int s_need, s_cnt_gt, s_cnt_eq;
@@ -165,6 +169,19 @@ __global__ void __launch_bounds__(512) topk_rows_kernel(int* __restrict__ out, c
     return;
   }
   if (tid == 0) { s_prefix = 0; s_mask = 0; s_need = k; }
+  if (kResident) {
+    int i = tid * 4;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+      for (; i + 3 < n; i += 512 * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(x + i);
+        s_keys[i] = f2ord(v.x); s_keys[i + 1] = f2ord(v.y); s_keys[i + 2] = f2ord(v.z); s_keys[i + 3] = f2ord(v.w);
+      }
+      for (int j = (n & ~3) + tid; j < n; j += 512) s_keys[j] = f2ord(x[j]);
+    } else {
+      for (int j = tid; j < n; j += 512) s_keys[j] = f2ord(x[j]);
+    }
+  }
+  auto key = [&](int i) -> uint32_t { return kResident ? s_keys[i] : f2ord(x[i]); };
   __syncthreads();
   for (int pass = 3; pass >= 0; --pass) {
     for (int i = tid; i < 256; i += 512) hist[i] = 0;
@@ -172,7 +189,7 @@ __global__ void __launch_bounds__(512) topk_rows_kernel(int* __restrict__ out, c
     const uint32_t prefix = s_prefix, mask = s_mask;
     const int shift = pass * 8;
     for (int i = tid; i < n; i += 512) {
-      uint32_t u = f2ord(x[i]);
+      uint32_t u = key(i);
       if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
     }
     __syncthreads();
@@ -194,7 +211,7 @@ __global__ void __launch_bounds__(512) topk_rows_kernel(int* __restrict__ out, c
   if (tid == 0) { s_cnt_gt = 0; s_cnt_eq = 0; }
   __syncthreads();
   for (int i = tid; i < n; i += 512) {
-    uint32_t u = f2ord(x[i]);
+    uint32_t u = key(i);
     if (u > thr) {
       int p = atomicAdd(&s_cnt_gt, 1);
       if (p < k) o[p] = i;
@@ -203,7 +220,7 @@ __global__ void __launch_bounds__(512) topk_rows_kernel(int* __restrict__ out, c
   __syncthreads();
   const int base = s_cnt_gt;
   for (int i = tid; i < n; i += 512) {
-    uint32_t u = f2ord(x[i]);
+    uint32_t u = key(i);
     if (u == thr) {
       int p = atomicAdd(&s_cnt_eq, 1);
       if (p < need_eq && base + p < k) o[base + p] = i;
@@ -229,6 +246,14 @@ extern "C" int b200_indexer_logits(float* logits, const void* q_fp8, const float
 extern "C" int b200_topk_rows(int* out, const float* logits, const int* row_len, int64_t rows, int64_t ld, int k,
                               int64_t max_len, cudaStream_t st) {
   if (rows == 0) return 0;
-  return (int)launch_pdl(topk_rows_kernel, dim3((unsigned)rows), dim3(512), 0, st, out, logits, row_len, ld, k,
+  // rows of up to 220 KB of keys stay resident in shared memory for all six passes
+  const int64_t bytes = max_len * 4;
+  if (bytes <= 220 * 1024) {
+    auto kern = topk_rows_kernel<true>;
+    cudaError_t e = ensure_dynamic_smem((const void*)kern, 220 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_pdl(kern, dim3((unsigned)rows), dim3(512), (size_t)bytes, st, out, logits, row_len, ld, k, max_len);
+  }
+  return (int)launch_pdl(topk_rows_kernel<false>, dim3((unsigned)rows), dim3(512), 0, st, out, logits, row_len, ld, k,
                          max_len);
 }

@@ -798,6 +798,21 @@ std::vector<at::Tensor> indexer_prep(const at::Tensor& q, const at::Tensor& k, c
         "indexer_prep");
   return {q_out, w_out};
 }
+// out [M, 576] (bf16 / fp16) <- rows `slots` [M] (int32 global slot ids, negative = zero row) of the latent cache
+// [blocks, block_size, 576] (same dtype) or [blocks, block_size, 656] uint8 (fp8_ds_mla rows, de-quantised)
+void gather_mla_rows(at::Tensor out, const at::Tensor& cache, const at::Tensor& slots) {
+  TORCH_CHECK(out.is_contiguous() && out.dim() == 2 && out.size(1) == 576 && cache.is_contiguous() && cache.dim() == 3);
+  TORCH_CHECK(slots.scalar_type() == at::kInt && slots.is_contiguous() && slots.numel() == out.size(0));
+  const bool fp8 = cache.scalar_type() == at::kByte;
+  if (fp8) {
+    TORCH_CHECK(cache.size(2) == 656, "fp8_ds_mla rows are 656 bytes");
+  } else {
+    TORCH_CHECK(cache.size(2) == 576 && cache.scalar_type() == out.scalar_type());
+  }
+  check(b200_gather_mla_rows(out.data_ptr(), cache.data_ptr(), slots.data_ptr<int32_t>(), out.size(0),
+                             cache.size(0) * cache.size(1), fp8 ? 1 : 0, dtype_code(out), stream()),
+        "gather_mla_rows");
+}
 void convert_req_index_to_global_index(at::Tensor out, const at::Tensor& req_id, const at::Tensor& block_table,
                                        const at::Tensor& idx, int64_t block_size) {
   TORCH_CHECK(req_id.scalar_type() == at::kInt && block_table.scalar_type() == at::kInt && idx.scalar_type() == at::kInt);
@@ -1319,6 +1334,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention_umma", &decode_attention_umma);
   m.def("mla_decode_umma", &mla_decode_umma);
   m.def("indexer_prep", &indexer_prep);
+  m.def("gather_mla_rows", &gather_mla_rows);
   m.def("set_kernel_trace", &set_kernel_trace);
   m.def("mla_decode_max_clusters", [](int64_t R, int64_t S, int64_t dtype) {
     return (int64_t)b200_mla_decode_max_clusters((int)R, (int)S, (int)dtype);

@@ -138,6 +138,11 @@ __global__ void concat_and_cache_mla_kernel(const T* __restrict__ kv_c, const T*
   for (int i = threadIdx.x; i < rope; i += blockDim.x) dst[rank + i] = k_pe[t * kpe_stride + i];
 }
 
+__device__ __forceinline__ float from_e4m3(uint8_t b) {
+  __nv_fp8_e4m3 q;
+  q.__x = b;
+  return static_cast<float>(q);
+}
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
@@ -387,6 +392,54 @@ extern "C" int b200_concat_and_cache_mla(const void* kv_c, const void* k_pe, voi
       concat_and_cache_mla_kernel<T><<<T_, 128, 0, st>>>((const T*)kv_c, (const T*)k_pe, (T*)cache, slots, rank, rope,
                                                         total_slots, kvc_stride, kpe_stride);
     }
+  });
+  return (int)cudaGetLastError();
+}
+
+// Gather rows of the paged MLA latent cache by global slot index into a dense 16-bit buffer, de-quantising the
+// 656-byte fp8 rows (4 x 128 e4m3 | 4 f32 scales | 64 bf16 rope dims) on the way - the read side of the `fp8_ds_mla`
+// cache and the chunk gather of a bounded-workspace prefill context (`gather_and_maybe_dequant_cache`,
+// v1/attention/backends/mla/common.py:1557-1612 of the reference).  One warp per output row; a negative or
+// out-of-range slot gives a zero row.
+template <typename T, bool kFp8>
+__global__ void gather_mla_rows_kernel(T* __restrict__ out, const uint8_t* __restrict__ cache,
+                                       const int32_t* __restrict__ slots, int64_t M, int64_t total_slots) {
+  const int64_t m = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= M) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t slot = slots[m];
+  T* dst = out + m * 576;
+  if (slot < 0 || slot >= total_slots) {
+    for (int i = lane; i < 576 / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+    return;
+  }
+  if (kFp8) {
+    const uint8_t* row = cache + slot * 656;
+    const float* sc = reinterpret_cast<const float*>(row + 512);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t w = reinterpret_cast<const uint32_t*>(row)[g * 32 + lane];
+      const float s = sc[g];
+      T v4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v4[j] = from_f<T>(from_e4m3((uint8_t)(w >> (8 * j))) * s);
+      *reinterpret_cast<uint2*>(dst + g * 128 + lane * 4) = *reinterpret_cast<const uint2*>(v4);
+    }
+    // rope dims are stored as bf16
+    const __nv_bfloat16* pe = reinterpret_cast<const __nv_bfloat16*>(row + 528);
+    for (int i = lane; i < 64; i += 32) dst[512 + i] = from_f<T>(__bfloat162float(pe[i]));
+  } else {
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(cache + slot * (576 * sizeof(T)));
+    for (int i = lane; i < 576 / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = row[i];
+  }
+}
+
+extern "C" int b200_gather_mla_rows(void* out, const void* cache, const int32_t* slots, int64_t M, int64_t total_slots,
+                                    int fp8, int dtype, cudaStream_t st) {
+  if (M == 0) return 0;
+  B200_DISPATCH_DTYPE(dtype, {
+    if (fp8) gather_mla_rows_kernel<T, true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>((T*)out, (const uint8_t*)cache, slots, M, total_slots);
+    else gather_mla_rows_kernel<T, false><<<(unsigned)((M + 7) / 8), 256, 0, st>>>((T*)out, (const uint8_t*)cache, slots, M, total_slots);
   });
   return (int)cudaGetLastError();
 }

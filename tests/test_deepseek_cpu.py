@@ -85,3 +85,29 @@ def test_sparse_small_topk_runs():
               num_gpu_blocks=16)
     outs = llm.generate(_prompts(), SamplingParams(max_tokens=4, ignore_eos=True))
     assert all(len(o.token_ids) == 4 for o in outs)
+
+
+def test_sparse_engine_fp8_latent_cache_cpu():
+    """``kv_cache_dtype='fp8_ds_mla'`` on the sparse-attention model: 656-byte rows are allocated, written and read
+    (oracle kernels on CPU); tokens stay close to the 16-bit cache run."""
+    import torch
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    from vllm_kunlun_b200.config import deepseek_v3, tiny
+    cfg = tiny(deepseek_v3(fp8=False, sparse=True), num_layers=2, first_dense_layers=1, vocab_size=256, hidden_size=128,
+               num_heads=4, num_kv_heads=4, q_lora_rank=64, kv_lora_rank=512, qk_nope_head_dim=128,
+               qk_rope_head_dim=64, v_head_dim=128, head_dim=192, rotary_dim=64, intermediate_size=256,
+               num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, n_group=1, topk_group=1,
+               max_position=512, num_mtp_layers=0, index_topk=16)
+    prompts = [torch.randint(0, 256, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (40, 9)]
+    sp = SamplingParams(max_tokens=4, ignore_eos=True)
+    toks = {}
+    for kvd in ("auto", "fp8_ds_mla"):
+        llm = LLM(cfg, device="cpu", dtype="float32", block_size=64, max_model_len=128, max_num_seqs=2, num_gpu_blocks=8,
+                  seed=1, kv_cache_dtype=kvd)
+        caches = llm.engine.runner.kv_caches
+        first = caches[min(caches)]
+        assert (first[0].dtype == torch.uint8) == (kvd == "fp8_ds_mla")
+        if kvd == "fp8_ds_mla":
+            assert first[0].shape[-1] == 656
+        toks[kvd] = [o.token_ids for o in llm.generate(prompts, sp)]
+    assert all(len(t) == 4 for t in toks["fp8_ds_mla"])

@@ -324,3 +324,53 @@ def test_indexer_logits_umma_matches_mma_sync_kernel(t_lo_frac):
         torch.testing.assert_close(b_[t, :n], a[t, :n], atol=2e-4, rtol=2e-4)
         up = min(ld, -(-n // 128) * 128)
         assert (b_[t, n:up] == float("-inf")).all(), (t, n)
+
+
+def test_gather_mla_rows_bf16_and_fp8():
+    """Row gather out of the paged latent cache, plain and with the 656-byte fp8 rows de-quantised on the way."""
+    from vllm_kunlun_b200.ops import _ext
+    g = torch.Generator(device=DEV).manual_seed(2)
+    nblk, bs, T = 7, 64, 150
+    kvc = torch.randn(T, 512, device=DEV, generator=g).bfloat16()
+    kpe = torch.randn(T, 64, device=DEV, generator=g).bfloat16()
+    slots = torch.randperm(nblk * bs, device=DEV, generator=g)[:T].long()
+    c16 = torch.zeros(nblk, bs, 576, device=DEV, dtype=torch.bfloat16)
+    c8 = torch.zeros(nblk, bs, 656, device=DEV, dtype=torch.uint8)
+    ops.concat_and_cache_mla(kvc, kpe, c16, slots)
+    ops.concat_and_cache_mla(kvc, kpe, c8, slots)
+    pick = torch.cat([slots[:100].int(), torch.tensor([-1, nblk * bs + 5], device=DEV, dtype=torch.int32)])
+    o16 = torch.full((pick.numel(), 576), float("nan"), device=DEV, dtype=torch.bfloat16)
+    o8 = torch.full_like(o16, float("nan"))
+    _ext.C().gather_mla_rows(o16, c16, pick)
+    _ext.C().gather_mla_rows(o8, c8, pick)
+    torch.cuda.synchronize()
+    want = torch.cat([kvc, kpe], -1)[:100]
+    assert torch.equal(o16[:100], want) and (o16[100:] == 0).all() and (o8[100:] == 0).all()
+    ref8 = ra.dequant_mla_fp8_rows(c8.cpu().view(-1, 656)[pick[:100].long().cpu()]).bfloat16()
+    assert torch.equal(o8[:100].cpu(), ref8)
+    _close(o8[:100], want.float().cpu(), 0.15, 0.08, "fp8_ds_mla rows")
+
+
+def test_deepseek_sparse_engine_fp8_latent_cache():
+    """V3.2-shaped tiny model with ``kv_cache_dtype='fp8_ds_mla'``: the attention reads the quantised cache through
+    the gather + de-quantise path; greedy tokens mostly agree with the 16-bit cache (the cache is lossy)."""
+    from vllm_kunlun_b200.config import deepseek_v3
+    cfg = tiny(deepseek_v3(fp8=False, sparse=True), num_layers=2, first_dense_layers=1, vocab_size=512, hidden_size=512,
+               num_heads=16, num_kv_heads=16, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+               qk_rope_head_dim=64, v_head_dim=128, head_dim=192, rotary_dim=64, intermediate_size=1024,
+               num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256, n_group=1, topk_group=1,
+               max_position=2048, num_mtp_layers=0, index_topk=64)
+    prompts = [torch.randint(0, 512, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (200, 70)]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    toks = {}
+    for kvd in ("auto", "fp8_ds_mla"):
+        llm = LLM(cfg, device="cuda", block_size=64, max_model_len=512, max_num_seqs=4, num_gpu_blocks=24, seed=1,
+                  kv_cache_dtype=kvd)
+        caches = llm.engine.runner.kv_caches
+        first = caches[min(caches)]
+        assert (first[0].dtype == torch.uint8) == (kvd == "fp8_ds_mla")
+        toks[kvd] = [o.token_ids for o in llm.generate(prompts, sp)]
+        torch.cuda.synchronize()
+    assert all(len(t) == 6 for t in toks["fp8_ds_mla"])
+    same = sum(a == b for x, y in zip(toks["auto"], toks["fp8_ds_mla"]) for a, b in zip(x, y))
+    assert same >= 6, toks   # at least half of the 12 greedy tokens

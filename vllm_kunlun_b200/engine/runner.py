@@ -73,6 +73,7 @@ class ModelRunner:
                 self.model.load_weights(load_safetensors(cfg.weights_path))
             else:
                 self.model.init_random(cfg.seed, cfg.init_std)
+        self.model.kv_cache_dtype = cfg.cache.cache_dtype   # read by kv_cache_spec (e.g. "fp8_ds_mla")
         self.block_size = cfg.cache.block_size
         self.dcp, self.dcp_rank = self.pstate.dcp_size, self.pstate.dcp_rank
         if self.dcp > 1:

@@ -147,6 +147,32 @@ class MLAAttention(nn.Module):
         self.w_uk = w[:, : self.nope].contiguous()                    # q_nope [T,N,nope] x [N,nope,rank]
         self.w_uv = w[:, self.nope:].transpose(1, 2).contiguous()     # out [T,N,rank] x [N,rank,vdim]
 
+    FP8_GATHER_TOKENS = 256   # query tokens per pass of the fp8-cache path (scratch: tokens x top-k x 1152 bytes)
+
+    def _sparse_fp8(self, qf, kv_cache, slots):
+        """Sparse attention over the `fp8_ds_mla` cache: the selected rows of a group of query tokens are gathered
+        and de-quantised into a dense 16-bit scratch (one kernel), and the sparse kernel then runs over the scratch
+        with positional indices.  The scratch is bounded by ``FP8_GATHER_TOKENS``; long prefill chunks take several
+        passes."""
+        T, topk = slots.shape
+        out = torch.empty(T, self.num_heads, self.rank, dtype=qf.dtype, device=qf.device)
+        step = min(T, self.FP8_GATHER_TOKENS)
+        if qf.is_cuda:
+            from ..ops import _ext
+            scratch = torch.empty(step * topk, 576, dtype=qf.dtype, device=qf.device)
+            pos = torch.arange(step * topk, dtype=torch.int32, device=qf.device).view(step, topk)
+        for t0 in range(0, T, step):
+            t1 = min(T, t0 + step)
+            sl = slots[t0:t1].contiguous()
+            if qf.is_cuda:
+                rows = scratch[: (t1 - t0) * topk]
+                _ext.C().gather_mla_rows(rows, kv_cache, sl.view(-1))
+                idx = torch.where(sl >= 0, pos[: t1 - t0], torch.full_like(sl, -1))
+                out[t0:t1] = ops.sparse_mla_attention(qf[t0:t1].contiguous(), rows, idx, self.scale, self.rank)
+            else:
+                out[t0:t1] = ops.sparse_mla_attention(qf[t0:t1], kv_cache, sl, self.scale, self.rank)
+        return out
+
     def forward(self, hidden):
         ctx = get_forward_context()
         md = ctx.attn
@@ -177,7 +203,10 @@ class MLAAttention(nn.Module):
             local_idx = self.indexer(hidden, q_c, md.positions, self.cos_sin, idx_cache, md)
             slots = ops.convert_req_index_to_global_index(md.req_id_per_token, md.block_tables, local_idx,
                                                           kv_cache.shape[1])
-            o = ops.sparse_mla_attention(qf.contiguous(), kv_cache, slots, self.scale, self.rank)
+            if kv_cache.dtype == torch.uint8:
+                o = self._sparse_fp8(qf.contiguous(), kv_cache, slots)
+            else:
+                o = ops.sparse_mla_attention(qf.contiguous(), kv_cache, slots, self.scale, self.rank)
         elif ctx.pstate.dcp_size > 1:
             from ..attention.dcp import dcp_mla_attention
             o = dcp_mla_attention(qf.contiguous(), kv_cache, md, self.scale, self.rank, ctx.pstate)
@@ -215,8 +244,12 @@ class DeepseekForCausalLM(MoEForCausalLM):
         if not cfg.use_mla:
             return super().kv_cache_spec(block_size)
         spec = {}
+        # `fp8_ds_mla` (sparse-attention models only): 656-byte rows = 4 x 128 e4m3 | 4 f32 scales | 64 bf16 rope dims
+        fp8 = getattr(self, "kv_cache_dtype", "auto") == "fp8_ds_mla"
+        if fp8 and not cfg.index_topk:
+            raise ValueError("kv_cache_dtype='fp8_ds_mla' is served for sparse-attention (indexer) models only")
         for i in range(self.first_layer, self.last_layer):
-            main = ((block_size, cfg.mla_cache_dim), self.dtype)
+            main = ((block_size, 656), torch.uint8) if fp8 else ((block_size, cfg.mla_cache_dim), self.dtype)
             spec[i] = [main, ((block_size, 132), torch.uint8)] if cfg.index_topk else main
         return spec
 
