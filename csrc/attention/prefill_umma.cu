@@ -1,0 +1,397 @@
+// Paged GQA prefill / chunked-prefill attention on tcgen05 + TMEM, fed by TMA straight from the paged KV cache
+// (head_dim 128, 16-bit).  The reference's `prefill_attention` call (v1/attention/backends/kunlun_attn.py:805-947).
+//
+// One CTA = (tile of 128 query rows of one request, one query head).  Per 128-key tile:
+//     S[128 q rows, 128 keys]  = Q_tile[128, D] . K_tile^T             (A = Q, B = K tile, both K-major)
+//     O[128 q rows, D]        += P[128, 128 keys] . V_tile[128 keys, D] (A = P from shared memory, B = V tile MN-major)
+// S lives in TMEM with one lane per query row, so a softmax thread owns a whole row: row maximum, exp2 and row sum
+// need no cross-thread exchange, and the online-softmax rescale of O is a round trip through the thread's own TMEM
+// lane.  The running maximum is lazy (it moves only when a tile exceeds it by more than 8 in log2 units), so in the
+// common case O is not rescaled and the softmax warps never wait for the previous P.V.
+// 192 threads: warp 0 TMA producer (Q once; per key tile two cache pages x (K, V) x two 64-dim halves as 64 x 64
+// boxes with 128-byte swizzle, 2-stage ring), warp 1 MMA issuer (event-driven: S of the next tile and P.V of the
+// current one are issued as they become ready), warps 2-5 softmax + epilogue.  Two S buffers (2 x 128 TMEM columns)
+// + O (128 columns).  Causal masking by position (chunked prefill: row r of the request sits at ctx + r), optional
+// sliding window and attention sinks, optional log-sum-exp output.
+// TMA loads carry no cluster multicast.  Every wait is bounded; on time-out the status word is set and the CTA unwinds.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "../api.h"
+#include "../common/launch.cuh"
+#include "../common/ptx.cuh"
+#include "../gemm/gemm_common.cuh"
+
+namespace b200 {
+namespace pattn {
+
+constexpr int kThreads = 192;
+constexpr int kQTile = 128, kKTile = 128, kPage = 64, kD = 128;
+constexpr int kHalfBytes = 128 * 128;          // one 64-dim block of a 128-row operand tile
+constexpr int kOpBytes = 2 * kHalfBytes;       // Q, K, V or P tile: 32 KB
+constexpr int kStageBytes = 2 * kOpBytes;      // K + V
+constexpr int kStages = 2;
+constexpr int kTmemCols = 512;                 // 2 x 128 (S) + 128 (O)
+constexpr float kMaxSlack = 8.f;
+
+struct Params {
+  void* out;                // [T, Hq, 128]
+  float* lse;               // [T, Hq] natural-log sum-exp (optional)
+  const int* block_tables;  // [B, max_blocks]
+  const int* seq_lens;
+  const int* qsl;
+  const float* sinks;       // [Hq] or null
+  int* status;
+  int Hq, Hkv, block_size, max_blocks, window;
+  int64_t num_blocks;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+template <typename T> struct FmtOf;
+template <> struct FmtOf<__nv_bfloat16> { static constexpr uint32_t v = 1; };
+template <> struct FmtOf<__half> { static constexpr uint32_t v = 0; };
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16(a)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16(b)) << 16);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  return (uint32_t)__half_as_ushort(__float2half(a)) | ((uint32_t)__half_as_ushort(__float2half(b)) << 16);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV,
+                    const __grid_constant__ Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + kStages * kStageBytes;       // [2 dim blocks][128 rows][128 B]
+  uint8_t* sP = sQ + kOpBytes;                      // [2 key blocks][128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kOpBytes);
+  uint64_t* q_full = bars;             // [1]
+  uint64_t* kv_full = bars + 1;        // [2]
+  uint64_t* kv_empty = bars + 3;       // [2]
+  uint64_t* s_full = bars + 5;         // [2]
+  uint64_t* s_empty = bars + 7;        // [2]
+  uint64_t* p_ready = bars + 9;        // [1] 4 arrivals (one per softmax warp)
+  uint64_t* p_free = bars + 10;        // [1]
+  uint64_t* o_done = bars + 11;        // [1] one phase per P.V
+  uint64_t* o_final = bars + 12;       // [1] once, after the last P.V
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  Abort ab{p.status, abort_flag};
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&kv_full[b], 1); mbar_init(&kv_empty[b], 1);
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
+    }
+    mbar_init(p_ready, 4); mbar_init(p_free, 1); mbar_init(o_done, 1); mbar_init(o_final, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmKV);
+    griddep_launch();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();   // q and this step's cache rows come from the preceding kernels
+
+  const int head = blockIdx.y, req = blockIdx.z;
+  const int kvh = head / (p.Hq / p.Hkv);
+  const int qs = p.qsl[req], q_len = p.qsl[req + 1] - qs;
+  const int seq_len = p.seq_lens[req];
+  const int ctx = seq_len - q_len;
+  const int row0 = blockIdx.x * kQTile;                      // first query row of this tile within the request
+  const int n_rows = max(0, min(kQTile, q_len - row0));
+  // keys visible to the tile: up to the position of its last row; with a window, from the first row's window start
+  const int pos_first = ctx + row0, pos_last = ctx + row0 + n_rows - 1;
+  const int kv_end = n_rows > 0 ? min(seq_len, pos_last + 1) : 0;
+  int kv_begin = 0;
+  if (p.window > 0) kv_begin = max(0, pos_first - p.window + 1) / kKTile * kKTile;
+  const int n_tiles = n_rows > 0 ? (kv_end - kv_begin + kKTile - 1) / kKTile : 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && n_tiles > 0) {
+      mbar_expect_tx(q_full, kOpBytes);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) tma_load_2d(sQ + h * kHalfBytes, &tmQ, q_full, head * kD + h * 64, qs + row0);
+      const int* bt = p.block_tables + (int64_t)req * p.max_blocks;
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int stage = i & 1;
+        if (i >= kStages && !wait_or_abort(&kv_empty[stage], ((i >> 1) - 1) & 1, ab, 801)) { ok = false; break; }
+        mbar_expect_tx(&kv_full[stage], kStageBytes);
+        uint8_t* sK = smem + stage * kStageBytes;
+        uint8_t* sV = sK + kOpBytes;
+        const int key0 = kv_begin + i * kKTile;
+#pragma unroll
+        for (int pg = 0; pg < kKTile / kPage; ++pg) {
+          const int key = key0 + pg * kPage;
+          const int bi = key / p.block_size;
+          int64_t blk = (key < kv_end && bi < p.max_blocks) ? bt[bi] : 0;
+          if (blk < 0 || blk >= p.num_blocks) blk = 0;   // masked keys: any initialised page will do
+          const int64_t rowK = ((blk * 2) * p.Hkv + kvh) * p.block_size + (key % p.block_size);
+          const int64_t rowV = rowK + (int64_t)p.Hkv * p.block_size;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            tma_load_2d(sK + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowK);
+            tma_load_2d(sV + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowV);
+          }
+        }
+        ++issued;
+      }
+      if (!ok) {
+        for (int i = max(0, issued - kStages); i < issued; ++i)
+          for (uint32_t q2 = 0; q2 < (1u << 16); ++q2)
+            if (mbar_try_wait(&kv_full[i & 1], (i >> 1) & 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (event-driven)
+    if (elect_one() && n_tiles > 0) {
+      const uint32_t fmt = FmtOf<T>::v;
+      const uint32_t idesc_s = umma_idesc(kQTile, kKTile, fmt, fmt, 0, 0);   // A = Q, B = K tile, both K-major
+      const uint32_t idesc_o = umma_idesc(kQTile, kD, fmt, fmt, 0, 1);       // A = P (K-major), B = V tile (MN-major)
+      const uint32_t tS = tmem_base, tO = tmem_base + 2 * kKTile;
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      auto issue_s = [&](int i) {
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(smem + (i & 1) * kStageBytes);
+#pragma unroll
+        for (int k = 0; k < kD / 16; ++k) {
+          const int kb = k / 4, kk = k % 4;
+          umma_f16(tS + (i & 1) * kKTile, umma_desc_k_sw128(q_addr + kb * kHalfBytes + kk * 32),
+                   umma_desc_k_sw128(k_addr + kb * kHalfBytes + kk * 32), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[i & 1]);
+      };
+      auto issue_pv = [&](int i) {
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(smem + (i & 1) * kStageBytes + kOpBytes);
+#pragma unroll
+        for (int k = 0; k < kKTile / 16; ++k) {
+          // A: 16 keys of P (key block k / 4, 32 bytes in); B: the same 16 keys of V, 128 dims (two 64-dim blocks)
+          umma_f16(tO, umma_desc_k_sw128(p_addr + (k / 4) * kHalfBytes + (k % 4) * 32),
+                   umma_desc_mn_sw128(v_addr + k * 2048, kHalfBytes, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(o_done);   // first: whoever has seen p_free of this tile may rely on o_done having advanced
+        umma_commit(&kv_empty[i & 1]);
+        umma_commit(p_free);
+        if (i == n_tiles - 1) umma_commit(o_final);
+      };
+      bool ok = wait_or_abort(q_full, 0, ab, 802);
+      int next_s = 0, next_pv = 0;
+      uint32_t spins = 0;
+      while (ok && next_pv < n_tiles) {
+        bool progressed = false;
+        if (next_s < n_tiles && next_s <= next_pv + 1 && mbar_try_wait(&kv_full[next_s & 1], (next_s >> 1) & 1) &&
+            (next_s < 2 || mbar_try_wait(&s_empty[next_s & 1], ((next_s >> 1) - 1) & 1))) {
+          issue_s(next_s);
+          ++next_s;
+          progressed = true;
+        }
+        if (next_pv < next_s && mbar_try_wait(p_ready, next_pv & 1)) {
+          issue_pv(next_pv);
+          ++next_pv;
+          progressed = true;
+        }
+        if (progressed) { spins = 0; continue; }
+        if (++spins > (1u << 20)) { ab.raise(803); break; }
+        if ((spins & 255) == 255 && ab.aborted()) break;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue: thread = query row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off, tO = tmem_base + 2 * kKTile + lane_off;
+    const bool row_ok = r < n_rows;
+    const int pos = ctx + row0 + r;                    // position of this row's token
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool fail = false;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int buf = i & 1;
+      if (!fail && !wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 805)) fail = true;
+      tc_fence_after_sync();
+      const int key0 = kv_begin + i * kKTile;
+      const bool full_tile = key0 + kKTile - 1 <= pos_first && key0 + kKTile <= kv_end &&
+                             (p.window <= 0 || key0 > pos_last - p.window);
+      // ---- pass 1: row maximum (the scores stay in TMEM; they are read again for the exponentials)
+      float tmax = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kKTile; c += 32) {
+        uint32_t v[32];
+        tmem_ld_x32(tS + buf * kKTile + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float s = __uint_as_float(v[e]) * p.scale_log2;
+          if (!full_tile) {
+            const int key = key0 + c + e;
+            const bool in = key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
+            s = in ? s : -INFINITY;
+          }
+          tmax = fmaxf(tmax, s);
+        }
+      }
+      if (!row_ok) tmax = -INFINITY;
+      // ---- lazy running maximum; the rescale of O is warp-collective (TMEM access), so the warp decides together
+      float alpha = 1.f;
+      const bool bump = tmax > m_used + kMaxSlack;
+      if (bump) { alpha = exp2f(m_used - tmax); m_used = tmax; l_sum *= alpha; }
+      // P (one buffer): the previous P.V must have read it; this also keeps o_done within one phase
+      if (i >= 1 && !fail && !wait_or_abort(p_free, (i - 1) & 1, ab, 806)) fail = true;
+      if (__any_sync(0xffffffffu, bump) && i > 0) {
+        if (!fail && !wait_or_abort(o_done, (i - 1) & 1, ab, 808)) fail = true;
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < kD; c += 32) {
+          uint32_t o[32];
+          tmem_ld_x32(tO + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st_x32(tO + c, o);
+        }
+        tmem_st_wait();
+      }
+      // ---- pass 2: exponentials, row sum, P row (16-bit, K-major over keys, 16-byte chunks swizzled by row)
+      const float ms = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll 1
+      for (int c = 0; c < kKTile; c += 32) {
+        uint32_t v[32];
+        tmem_ld_x32(tS + buf * kKTile + c, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pe[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            float s = __uint_as_float(v[e + u]) * p.scale_log2;
+            if (!full_tile) {
+              const int key = key0 + c + e + u;
+              const bool in = key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
+              s = in ? s : -INFINITY;
+            }
+            pe[u] = row_ok ? exp2f(s - ms) : 0.f;
+            l_sum += pe[u];
+          }
+          pk[e / 2] = pack2<T>(pe[0], pe[1]);
+        }
+        if (!fail) {
+          // keys c .. c + 31 = chunks (c / 8) .. + 3 of key block c / 64
+          uint8_t* base = sP + (c >> 6) * kHalfBytes + r * 128;
+          const int ch0 = (c & 63) >> 3;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(base + (((ch0 + q4) ^ (r & 7)) << 4)) =
+                make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);
+      fence_proxy_async_smem();
+      const bool warp_failed = __any_sync(0xffffffffu, fail);
+      __syncwarp();
+      if (lane == 0 && !warp_failed) mbar_arrive(p_ready);
+    }
+    // ---- epilogue
+    bool ok = !fail;
+    if (ok && n_tiles > 0) {
+      if (!wait_or_abort(o_final, 0, ab, 807)) ok = false;
+      tc_fence_after_sync();
+    }
+    if (n_tiles > 0) {
+      const int64_t orow = (int64_t)(qs + row0 + r) * p.Hq + head;
+      float den = l_sum;
+      const float ms = (m_used == -INFINITY) ? 0.f : m_used;
+      if (p.sinks != nullptr) den += exp2f(p.sinks[head] * 1.4426950408889634f - ms);
+      const float inv = (ok && den > 0.f) ? 1.f / den : 0.f;
+      T* dst = reinterpret_cast<T*>(p.out) + orow * kD;
+#pragma unroll 1
+      for (int c = 0; c < kD; c += 32) {
+        uint32_t o[32];
+        tmem_ld_x32(tO + c, o);      // warp-collective: every lane loads, only valid rows store
+        tmem_ld_wait();
+        if (row_ok) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) pk[e / 2] = pack2<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(dst + c + q4 * 8) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        }
+      }
+      if (row_ok && p.lse != nullptr) p.lse[orow] = (ok && den > 0.f) ? (ms + log2f(den)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T>
+static int launch(const Params& p, const CUtensorMap& tmQ, const CUtensorMap& tmKV, int B, int max_query_len, cudaStream_t st) {
+  auto kern = prefill_umma_kernel<T>;
+  const size_t smem = 1024 + (size_t)kStages * kStageBytes + 2 * kOpBytes + 256;
+  cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((unsigned)((max_query_len + kQTile - 1) / kQTile), (unsigned)p.Hq, (unsigned)B);
+  return (int)launch_pdl(kern, grid, dim3(kThreads), smem, st, tmQ, tmKV, p);
+}
+
+}  // namespace pattn
+}  // namespace b200
+
+// Paged GQA prefill attention on tcgen05 (head_dim 128, block_size a multiple of 64).  `tmQ`: q as a 2-D
+// [T, Hq * 128] 16-bit tensor with 64-column x 128-row boxes; `tmKV`: the cache as [rows, 128] with 64 x 64 boxes;
+// both with 128-byte swizzle.  Returns 3 for shapes it does not serve.
+extern "C" int b200_prefill_attention_umma(void* out, float* lse, const void* tmQ, const void* tmKV,
+                                           const int* block_tables, const int* seq_lens, const int* qsl,
+                                           const float* sinks, int* status, int B, int Hq, int Hkv, int D, int block_size,
+                                           int max_blocks, int64_t num_blocks, int max_query_len, int window, float scale,
+                                           int dtype, cudaStream_t st) {
+  using namespace b200;
+  if (B == 0 || max_query_len <= 0) return 0;
+  if (D != 128 || Hq % Hkv || block_size % pattn::kPage || B > 65535 || Hq > 65535) return 3;
+  pattn::Params p;
+  p.out = out; p.lse = lse; p.block_tables = block_tables; p.seq_lens = seq_lens; p.qsl = qsl; p.sinks = sinks;
+  p.status = status; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.window = window;
+  p.num_blocks = num_blocks; p.scale_log2 = scale * 1.4426950408889634f;
+  const CUtensorMap& q = *reinterpret_cast<const CUtensorMap*>(tmQ);
+  const CUtensorMap& kv = *reinterpret_cast<const CUtensorMap*>(tmKV);
+  if (dtype == 1) return pattn::launch<__nv_bfloat16>(p, q, kv, B, max_query_len, st);
+  if (dtype == 2) return pattn::launch<__half>(p, q, kv, B, max_query_len, st);
+  return 3;
+}

@@ -889,6 +889,40 @@ void decode_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor
                                    early_meta ? 1 : 0, dtype_code(q), stream()), "decode_attention_umma");
 }
 
+// Paged GQA prefill attention on tcgen05 (head_dim 128): q [T, Hq, 128], kv_cache [blocks, 2, Hkv, block_size, 128];
+// optional lse [T, Hq] (natural log).
+void prefill_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_cache, const at::Tensor& block_tables,
+                            const at::Tensor& seq_lens, const at::Tensor& qsl, const c10::optional<at::Tensor>& sinks,
+                            const c10::optional<at::Tensor>& lse, int64_t max_query_len, int64_t window, double scale) {
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && kv_cache.is_contiguous() && q.dim() == 3 && kv_cache.dim() == 5);
+  TORCH_CHECK(q.size(2) == 128 && kv_cache.size(4) == 128 && kv_cache.size(1) == 2 && out.sizes() == q.sizes());
+  TORCH_CHECK(block_tables.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
+  TORCH_CHECK(block_tables.stride(1) == 1 && q.scalar_type() == kv_cache.scalar_type() && q.scalar_type() == out.scalar_type());
+  if (lse.has_value()) TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == q.size(0) * q.size(1));
+  if (sinks.has_value()) TORCH_CHECK(sinks->scalar_type() == at::kFloat && sinks->numel() == q.size(1));
+  if (q.size(0) == 0) return;
+  c10::cuda::CUDAGuard guard(q.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, q.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, q.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, q.options().dtype(at::kInt));
+  }
+  at::Tensor q2 = q.view({q.size(0), q.size(1) * 128});
+  at::Tensor flat = kv_cache.view({-1, 128});
+  const Tmap& tq = get_tmap(gs, q2, 128, 2);
+  const Tmap& tk = get_tmap(gs, flat, 64, 2);
+  check(b200_prefill_attention_umma(out.data_ptr(), lse.has_value() ? lse->data_ptr<float>() : nullptr, tq.b, tk.b,
+                                    block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), qsl.data_ptr<int>(),
+                                    sinks.has_value() ? sinks->data_ptr<float>() : nullptr, gs.status.data_ptr<int>(),
+                                    (int)seq_lens.size(0), (int)q.size(1), (int)kv_cache.size(2), 128, (int)kv_cache.size(3),
+                                    (int)block_tables.stride(0), kv_cache.size(0), (int)max_query_len, (int)window,
+                                    (float)scale, dtype_code(q), stream()),
+        "prefill_attention_umma");
+}
+
 // Dense paged MLA decode on tcgen05: q [T, N, 576], kv [blocks, 64, 576] -> out [T, N, 512].
 // Optional phase-trace buffer (int64 [>= CTAs * 24]) for the kernels that support it; an undefined tensor switches it off.
 at::Tensor g_kernel_trace;
@@ -1333,6 +1367,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("decode_attention_umma", &decode_attention_umma);
   m.def("mla_decode_umma", &mla_decode_umma);
+  m.def("prefill_attention_umma", &prefill_attention_umma);
   m.def("indexer_prep", &indexer_prep);
   m.def("gather_mla_rows", &gather_mla_rows);
   m.def("set_kernel_trace", &set_kernel_trace);

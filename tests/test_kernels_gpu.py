@@ -438,3 +438,58 @@ def test_int8_w8a8_tensor_core_gemm(T, N, K, static):
     # and through the functional entry point
     y = ops.int8_linear(x.to(DEV), wq.to(DEV), ws.to(DEV), bias.to(DEV), None if in_scale is None else in_scale.to(DEV))
     assert torch.equal(y, out)
+
+
+@pytest.mark.parametrize("Hq,Hkv,bs", [(8, 2, 64), (4, 4, 128), (16, 1, 64)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_attention_umma(Hq, Hkv, bs, dtype):
+    """tcgen05 prefill attention (128 query rows of one head per CTA, S and O in TMEM) vs the fp32 oracle: fresh
+    prompts, chunked continuations over a cached prefix, lengths that end inside a tile / a page, a single-row
+    request, more than one query tile per request; then a sliding window with sinks, and the log-sum-exp output."""
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.attention_cuda import UMMA_PREFILL, paged_attention_cuda
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    assert UMMA_PREFILL[0]
+    D = 128
+    spec = [(1, 40), (37, 37), (128, 128), (70, 200), (300, 300), (5, 133), (129, 1000), (450, 1500)]
+    B = len(spec)
+    seq_lens = [s for _, s in spec]
+    cache, bt = _make_paged(B, seq_lens, Hkv, D, bs, dtype=dtype, seed=3)
+    qsl = torch.tensor([0] + list(torch.tensor([q for q, _ in spec]).cumsum(0)), dtype=torch.int32)
+    T = int(qsl[-1])
+    q = (torch.randn(T, Hq, D, generator=torch.Generator().manual_seed(5)) * 0.5).to(dtype)
+    sl = torch.tensor(seq_lens, dtype=torch.int32)
+    scale = D ** -0.5
+    mq = max(qq for qq, _ in spec)
+    d = lambda x: x.to(DEV)
+    ref = ra.paged_attention(q, cache, bt, sl, qsl, scale)
+    out = torch.full((T, Hq, D), float("nan"), device=DEV, dtype=dtype)
+    paged_attention_cuda(out, d(q), d(cache), d(bt), d(sl), d(qsl), scale, mq, max(seq_lens))
+    torch.cuda.synchronize()
+    check_status()
+    _close(out, ref, 2e-2, 2e-2, "prefill umma")
+    # sliding window + sinks
+    sinks = torch.randn(Hq, generator=torch.Generator().manual_seed(6))
+    ref_w = ra.paged_attention(q, cache, bt, sl, qsl, scale, 150, sinks)
+    out_w = torch.full((T, Hq, D), float("nan"), device=DEV, dtype=dtype)
+    paged_attention_cuda(out_w, d(q), d(cache), d(bt), d(sl), d(qsl), scale, mq, max(seq_lens), 150, d(sinks))
+    torch.cuda.synchronize()
+    check_status()
+    _close(out_w, ref_w, 2e-2, 2e-2, "prefill umma window + sinks")
+    # log-sum-exp (natural log) of every row
+    lse = torch.full((T, Hq), float("nan"), device=DEV)
+    out2 = torch.empty_like(out)
+    _ext.C().prefill_attention_umma(out2, d(q), d(cache), d(bt), d(sl), d(qsl), None, lse, mq, 0, scale)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
+    want = []
+    for b, (ql, s) in enumerate(spec):
+        pos = torch.arange(s)
+        k = cache[bt[b, pos // bs].long(), 0, :, pos % bs].float()          # [s, Hkv, D]
+        g = Hq // Hkv
+        for r in range(ql):
+            qr = q[int(qsl[b]) + r].float()                                 # [Hq, D]
+            n = s - ql + r + 1
+            sc = torch.einsum("hd,nhd->hn", qr, k[:n].repeat_interleave(g, 1)) * scale
+            want.append(torch.logsumexp(sc, -1))
+    torch.testing.assert_close(lse.cpu(), torch.stack(want), atol=2e-2, rtol=2e-3)

@@ -18,6 +18,9 @@ _SM_COUNT: dict = {}
 # decode-shaped calls with head dim 128 and cache blocks of a multiple of 64 tokens run on the tcgen05 kernel
 # (csrc/attention/decode_umma.cu); B200_ATTN_UMMA=0 keeps them on the mma.sync kernel
 UMMA_DECODE = [os.environ.get("B200_ATTN_UMMA", "1") != "0"]
+# prefill-shaped calls (same head dim / block constraints) run on csrc/attention/prefill_umma.cu;
+# B200_PREFILL_UMMA=0 keeps them on the mma.sync kernel
+UMMA_PREFILL = [os.environ.get("B200_PREFILL_UMMA", "1") != "0"]
 
 
 def sm_count(device) -> int:
@@ -90,6 +93,13 @@ def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_l
             ws_o, ws_lse = workspace.o, workspace.lse
         _ext.C().decode_attention_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, ws_o, ws_lse,
                                        max_query_len, num_splits, window or 0, scale, bool(stable_metadata))
+        return out
+    if (not decode_layout and UMMA_PREFILL[0] and D == 128 and kv_cache.shape[3] % 64 == 0 and kv_cache.dim() == 5
+            and q.dtype in (torch.bfloat16, torch.float16) and q.is_contiguous() and out.is_contiguous()
+            and kv_cache.is_contiguous()):
+        # prefill / chunked prefill on tcgen05: 128 query rows of one head per CTA, S and O in TMEM
+        _ext.C().prefill_attention_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, None,
+                                        max_query_len, window or 0, scale)
         return out
     if num_splits is None:
         if decode_layout:
