@@ -44,6 +44,7 @@ struct Params {
   const int* qsl;
   const float* sinks;       // [Hq] or null
   int* status;
+  unsigned long long* trace;   // optional phase timestamps [CTA][24] (null = off)
   int Hq, Hkv, block_size, max_blocks, window;
   int64_t num_blocks;
   float scale_log2;
@@ -59,6 +60,39 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
       "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
+}
+
+// 32 consecutive TMEM columns of this thread's lane into r[0..31] (pointer form: the caller indexes one big array)
+__device__ __forceinline__ void tmem_ld_x32_p(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_x32_p(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// 2^x on the special-function unit (one instruction; -inf -> 0; -inf + -inf stays -inf, NaN cannot arise from the
+// callers' finite-or-minus-infinity inputs with a finite or minus-infinity offset)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <typename T> struct FmtOf;
@@ -95,6 +129,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Abort ab{p.status, abort_flag};
+  const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 64) trace_mark(p.trace, cta_id, 0);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
@@ -188,6 +224,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                    umma_desc_k_sw128(k_addr + kb * kHalfBytes + kk * 32), idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[i & 1]);
+        if (i == 5) trace_mark(p.trace, cta_id, 13);
       };
       auto issue_pv = [&](int i) {
         tc_fence_after_sync();
@@ -198,6 +235,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           umma_f16(tO, umma_desc_k_sw128(p_addr + (k / 4) * kHalfBytes + (k % 4) * 32),
                    umma_desc_mn_sw128(v_addr + k * 2048, kHalfBytes, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
+        if (i == 3) trace_mark(p.trace, cta_id, 12);
         umma_commit(o_done);   // first: whoever has seen p_free of this tile may rely on o_done having advanced
         umma_commit(&kv_empty[i & 1]);
         umma_commit(p_free);
@@ -215,6 +253,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           progressed = true;
         }
         if (next_pv < next_s && mbar_try_wait(p_ready, next_pv & 1)) {
+          if (next_pv == 4) trace_mark(p.trace, cta_id, 9);
           issue_pv(next_pv);
           ++next_pv;
           progressed = true;
@@ -238,90 +277,102 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int buf = i & 1;
       if (!fail && !wait_or_abort(&s_full[buf], (i >> 1) & 1, ab, 805)) fail = true;
       tc_fence_after_sync();
+      if (threadIdx.x == 64 && i == 0) trace_mark(p.trace, cta_id, 1);
+      if (threadIdx.x == 64 && i == 4) trace_mark(p.trace, cta_id, 2);
+      if (threadIdx.x == 64 && i == 5) trace_mark(p.trace, cta_id, 7);
+      if (threadIdx.x == 64 && i == 20) trace_mark(p.trace, cta_id, 8);
       const int key0 = kv_begin + i * kKTile;
       const bool full_tile = key0 + kKTile - 1 <= pos_first && key0 + kKTile <= kv_end &&
                              (p.window <= 0 || key0 > pos_last - p.window);
-      // ---- pass 1: row maximum (the scores stay in TMEM; they are read again for the exponentials)
-      float tmax = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kKTile; c += 32) {
-        uint32_t v[32];
-        tmem_ld_x32(tS + buf * kKTile + c, v);
-        tmem_ld_wait();
+      // ---- the whole row (128 scores) in one TMEM round trip: a tcgen05.ld + wait pair costs several hundred
+      // nanoseconds whatever its width, so all four 32-column loads are issued before the single wait, and the
+      // S buffer goes back to the tensor core at once
+      uint32_t v[kKTile];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float s = __uint_as_float(v[e]) * p.scale_log2;
-          if (!full_tile) {
-            const int key = key0 + c + e;
-            const bool in = key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
-            s = in ? s : -INFINITY;
-          }
-          tmax = fmaxf(tmax, s);
+      for (int c = 0; c < kKTile; c += 32) tmem_ld_x32_p(tS + buf * kKTile + c, v + c);
+      tmem_ld_wait();
+      if (threadIdx.x == 64 && i == 4) trace_mark(p.trace, cta_id, 11);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[buf]);
+      // One warp per scheduler: nothing hides instruction latency but independent work inside the thread, so the
+      // row maximum runs on four partial maxima and the exponentials in chunks of 32 with four partial sums; the
+      // raw scores are masked in place and scaled inside the exponent (one FMA + one ex2 per element).
+      if (!full_tile) {
+#pragma unroll
+        for (int e = 0; e < kKTile; ++e) {
+          const int key = key0 + e;
+          const bool in = key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
+          v[e] = in ? v[e] : 0xff800000u;   // -inf
         }
       }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int e = 0; e < kKTile; e += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(v[e + u]));
+      }
+      float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;   // scale > 0: max commutes
       if (!row_ok) tmax = -INFINITY;
+      if (threadIdx.x == 64 && i == 4) trace_mark(p.trace, cta_id, 3);
       // ---- lazy running maximum; the rescale of O is warp-collective (TMEM access), so the warp decides together
       float alpha = 1.f;
       const bool bump = tmax > m_used + kMaxSlack;
       if (bump) { alpha = exp2f(m_used - tmax); m_used = tmax; l_sum *= alpha; }
-      // P (one buffer): the previous P.V must have read it; this also keeps o_done within one phase
+      // P (one buffer): the previous P.V must have read it (it has, long ago, unless the tensor pipe is behind);
+      // this also keeps o_done within one phase
       if (i >= 1 && !fail && !wait_or_abort(p_free, (i - 1) & 1, ab, 806)) fail = true;
+      if (threadIdx.x == 64 && i == 4) trace_mark(p.trace, cta_id, 4);
       if (__any_sync(0xffffffffu, bump) && i > 0) {
         if (!fail && !wait_or_abort(o_done, (i - 1) & 1, ab, 808)) fail = true;
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < kD; c += 32) {
+        for (int c = 0; c < kD; c += 32) {   // rare path: 32 columns at a time keeps the register count down
           uint32_t o[32];
-          tmem_ld_x32(tO + c, o);
+          tmem_ld_x32_p(tO + c, o);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tmem_st_x32(tO + c, o);
+          tmem_st_x32_p(tO + c, o);
         }
         tmem_st_wait();
       }
-      // ---- pass 2: exponentials, row sum, P row (16-bit, K-major over keys, 16-byte chunks swizzled by row)
-      const float ms = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
+      // ---- exponentials, row sum and the P row (16-bit, K-major over keys, 16-byte chunks swizzled by row; keys
+      // 8 q .. 8 q + 7 = chunk q % 8 of key block q / 8), 32 keys at a time
+      const float neg_ms = (m_used == -INFINITY || !row_ok) ? -INFINITY : -m_used;   // invalid rows: P = 0
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
       for (int c = 0; c < kKTile; c += 32) {
-        uint32_t v[32];
-        tmem_ld_x32(tS + buf * kKTile + c, v);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pe[2];
+        for (int e = 0; e < 32; e += 4) {
+          float pe[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            float s = __uint_as_float(v[e + u]) * p.scale_log2;
-            if (!full_tile) {
-              const int key = key0 + c + e + u;
-              const bool in = key < kv_end && key <= pos && (p.window <= 0 || key > pos - p.window);
-              s = in ? s : -INFINITY;
-            }
-            pe[u] = row_ok ? exp2f(s - ms) : 0.f;
-            l_sum += pe[u];
+          for (int u = 0; u < 4; ++u) {
+            pe[u] = ex2_approx(fmaf(__uint_as_float(v[c + e + u]), p.scale_log2, neg_ms));
+            ls[u] += pe[u];
           }
           pk[e / 2] = pack2<T>(pe[0], pe[1]);
+          pk[e / 2 + 1] = pack2<T>(pe[2], pe[3]);
         }
         if (!fail) {
-          // keys c .. c + 31 = chunks (c / 8) .. + 3 of key block c / 64
-          uint8_t* base = sP + (c >> 6) * kHalfBytes + r * 128;
-          const int ch0 = (c & 63) >> 3;
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-            *reinterpret_cast<uint4*>(base + (((ch0 + q4) ^ (r & 7)) << 4)) =
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int q = c / 8 + q4;
+            *reinterpret_cast<uint4*>(sP + (q >> 3) * kHalfBytes + r * 128 + (((q & 7) ^ (r & 7)) << 4)) =
                 make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+          }
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[buf]);
+      l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       fence_proxy_async_smem();
+      tc_fence_before_sync();
       const bool warp_failed = __any_sync(0xffffffffu, fail);
       __syncwarp();
       if (lane == 0 && !warp_failed) mbar_arrive(p_ready);
+      if (threadIdx.x == 64 && i == 4) trace_mark(p.trace, cta_id, 5);
     }
+    if (threadIdx.x == 64) trace_mark(p.trace, cta_id, 6);
     // ---- epilogue
     bool ok = !fail;
     if (ok && n_tiles > 0) {
@@ -335,18 +386,18 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (p.sinks != nullptr) den += exp2f(p.sinks[head] * 1.4426950408889634f - ms);
       const float inv = (ok && den > 0.f) ? 1.f / den : 0.f;
       T* dst = reinterpret_cast<T*>(p.out) + orow * kD;
-#pragma unroll 1
-      for (int c = 0; c < kD; c += 32) {
-        uint32_t o[32];
-        tmem_ld_x32(tO + c, o);      // warp-collective: every lane loads, only valid rows store
-        tmem_ld_wait();
-        if (row_ok) {
-          uint32_t pk[16];
+      uint32_t o[kD];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) pk[e / 2] = pack2<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+      for (int c = 0; c < kD; c += 32) tmem_ld_x32_p(tO + c, o + c);   // warp-collective: every lane loads
+      tmem_ld_wait();
+      if (row_ok) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-            *reinterpret_cast<uint4*>(dst + c + q4 * 8) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        for (int q4 = 0; q4 < kD / 8; ++q4) {
+          uint32_t w4[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            w4[u] = pack2<T>(__uint_as_float(o[q4 * 8 + 2 * u]) * inv, __uint_as_float(o[q4 * 8 + 2 * u + 1]) * inv);
+          *reinterpret_cast<uint4*>(dst + q4 * 8) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
         }
       }
       if (row_ok && p.lse != nullptr) p.lse[orow] = (ok && den > 0.f) ? (ms + log2f(den)) * 0.6931471805599453f : -INFINITY;
@@ -355,6 +406,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 64) trace_mark(p.trace, cta_id, 10);
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -381,13 +433,13 @@ extern "C" int b200_prefill_attention_umma(void* out, float* lse, const void* tm
                                            const int* block_tables, const int* seq_lens, const int* qsl,
                                            const float* sinks, int* status, int B, int Hq, int Hkv, int D, int block_size,
                                            int max_blocks, int64_t num_blocks, int max_query_len, int window, float scale,
-                                           int dtype, cudaStream_t st) {
+                                           int dtype, unsigned long long* trace, cudaStream_t st) {
   using namespace b200;
   if (B == 0 || max_query_len <= 0) return 0;
   if (D != 128 || Hq % Hkv || block_size % pattn::kPage || B > 65535 || Hq > 65535) return 3;
   pattn::Params p;
   p.out = out; p.lse = lse; p.block_tables = block_tables; p.seq_lens = seq_lens; p.qsl = qsl; p.sinks = sinks;
-  p.status = status; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.window = window;
+  p.status = status; p.trace = trace; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.window = window;
   p.num_blocks = num_blocks; p.scale_log2 = scale * 1.4426950408889634f;
   const CUtensorMap& q = *reinterpret_cast<const CUtensorMap*>(tmQ);
   const CUtensorMap& kv = *reinterpret_cast<const CUtensorMap*>(tmKV);

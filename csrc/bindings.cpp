@@ -889,6 +889,7 @@ void decode_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor
                                    early_meta ? 1 : 0, dtype_code(q), stream()), "decode_attention_umma");
 }
 
+extern at::Tensor g_kernel_trace;
 // Paged GQA prefill attention on tcgen05 (head_dim 128): q [T, Hq, 128], kv_cache [blocks, 2, Hkv, block_size, 128];
 // optional lse [T, Hq] (natural log).
 void prefill_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv_cache, const at::Tensor& block_tables,
@@ -919,7 +920,11 @@ void prefill_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tenso
                                     sinks.has_value() ? sinks->data_ptr<float>() : nullptr, gs.status.data_ptr<int>(),
                                     (int)seq_lens.size(0), (int)q.size(1), (int)kv_cache.size(2), 128, (int)kv_cache.size(3),
                                     (int)block_tables.stride(0), kv_cache.size(0), (int)max_query_len, (int)window,
-                                    (float)scale, dtype_code(q), stream()),
+                                    (float)scale, dtype_code(q),
+                                    (g_kernel_trace.defined() &&
+                                     g_kernel_trace.numel() >= (int64_t)seq_lens.size(0) * q.size(1) * ((max_query_len + 127) / 128) * 24)
+                                        ? reinterpret_cast<unsigned long long*>(g_kernel_trace.data_ptr<int64_t>()) : nullptr,
+                                    stream()),
         "prefill_attention_umma");
 }
 
