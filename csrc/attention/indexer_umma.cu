@@ -29,6 +29,20 @@
 namespace b200 {
 namespace idxu {
 
+// 32 consecutive TMEM columns of this thread's lane into r[0..31] (pointer form: the caller indexes one big array)
+__device__ __forceinline__ void tmem_ld_x32_p(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
 constexpr int kThreads = 192;
 constexpr int kH = 64, kD = 128;             // heads, dims (bytes per e4m3 row)
 constexpr int kTok = 16, kGroupTok = 4;      // query tokens per CTA / per MMA group
@@ -190,26 +204,30 @@ indexer_logits_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         const int buf = it & 1;
         if (!wait_or_abort(&d_full[buf], (it >> 1) & 1, ab, 705)) { fail = true; break; }
         tc_fence_after_sync();
+        // A tcgen05.ld + wait pair costs a few hundred nanoseconds whatever its width: 128 columns (two tokens) per
+        // round trip; four partial sums per token so that the FMAs do not wait on one another.
         float out4[kGroupTok];
 #pragma unroll
-        for (int j = 0; j < kGroupTok; ++j) {
-          float acc = 0.f;
-          const float* wj = sW + (g * kGroupTok + j) * kH;
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[128];
 #pragma unroll
-          for (int c = 0; c < kH; c += 32) {
-            uint32_t v[32];
-            tmem_ld_x32(taddr + buf * kGroupN + j * kH + c, v);
-            tmem_ld_wait();
+          for (int c = 0; c < 128; c += 32) tmem_ld_x32_p(taddr + buf * kGroupN + half * 128 + c, v + c);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              const float4 w4 = *reinterpret_cast<const float4*>(wj + c + e);
-              acc = fmaf(fmaxf(__uint_as_float(v[e]), 0.f), w4.x, acc);
-              acc = fmaf(fmaxf(__uint_as_float(v[e + 1]), 0.f), w4.y, acc);
-              acc = fmaf(fmaxf(__uint_as_float(v[e + 2]), 0.f), w4.z, acc);
-              acc = fmaf(fmaxf(__uint_as_float(v[e + 3]), 0.f), w4.w, acc);
+          for (int jj = 0; jj < 2; ++jj) {
+            const int j = half * 2 + jj;
+            const float* wj = sW + (g * kGroupTok + j) * kH;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < kH; e += 4) {
+              const float4 w4 = *reinterpret_cast<const float4*>(wj + e);
+              acc[0] = fmaf(fmaxf(__uint_as_float(v[jj * kH + e]), 0.f), w4.x, acc[0]);
+              acc[1] = fmaf(fmaxf(__uint_as_float(v[jj * kH + e + 1]), 0.f), w4.y, acc[1]);
+              acc[2] = fmaf(fmaxf(__uint_as_float(v[jj * kH + e + 2]), 0.f), w4.z, acc[2]);
+              acc[3] = fmaf(fmaxf(__uint_as_float(v[jj * kH + e + 3]), 0.f), w4.w, acc[3]);
             }
+            out4[j] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * sc;
           }
-          out4[j] = acc * sc;
         }
         tc_fence_before_sync();
         __syncwarp();
