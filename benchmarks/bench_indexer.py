@@ -67,6 +67,6 @@ print(f"| indexer_logits_kernel (mma.sync e4m3) | {ms:.3f} | {flops / ms / 1e9:.
 ms = timeit(lambda: C.topk_rows(out, logits, row_len))
 print(f"| topk_rows_kernel (top-{a.topk}, row resident in shared memory) | {ms:.3f} | - |", flush=True)
 mask = torch.arange(S, device=dev).unsqueeze(0) < row_len.unsqueeze(1)
-d = ((a_ - b_).abs() * mask).max().item()
+d = torch.where(mask, (a_ - b_).abs(), torch.zeros_like(a_)).max().item()
 print(f"max |difference| on visible keys: {d:.4g} (values up to {b_[mask].abs().max().item():.4g})")
 check_status()
