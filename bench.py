@@ -72,6 +72,9 @@ def parse():
     ap.add_argument("--ep", action="store_true", help="expert parallelism for MoE models (whole experts per rank)")
     ap.add_argument("--spec", default=None, help="speculative method (mtp | ngram | eagle), one draft token")
     ap.add_argument("--kv-cache-dtype", default=None)
+    ap.add_argument("--tp", type=int, default=0,
+                    help="tensor-parallel size (0 = choose); the remaining ranks form data-parallel replicas that share "
+                         "the concurrent requests")
     ap.add_argument("--layers", type=int, default=0,
                     help="debugging only: run with this many layers (the JSON line then says so and is not a result)")
     a = ap.parse_args()
@@ -172,6 +175,14 @@ def main():
         raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local)
     C, IN, OUT = args.concurrency, args.in_len, args.out_len
+    # Parallel layout.  The dense 8B model at 16 concurrent requests stops gaining from tensor parallelism beyond 4
+    # ranks (64 all-reduces per step across 8 ranks cost what the smaller per-rank GEMMs save): 8 GPUs run as two
+    # replicas of 4, each serving half of the requests.  The MoE configurations keep TP = EP = all ranks.
+    tp = args.tp or (4 if (args.config == 2 and world == 8 and C % 2 == 0) else world)
+    if world % tp or C % (world // tp):
+        raise SystemExit(f"--tp {tp} does not divide {world} ranks / {C} requests")
+    dp = world // tp
+    C_local = C // dp
     spec = {"method": args.spec, "num_speculative_tokens": 1} if args.spec else None
     model = args.model
     if args.layers:
@@ -181,11 +192,12 @@ def main():
         mc = PRESETS[args.model]()
         model = dataclasses.replace(mc, num_layers=args.layers,
                                     first_dense_layers=min(mc.first_dense_layers, max(1, args.layers // 2)))
-    llm = LLM(model, tensor_parallel_size=world, device="cuda", block_size=64, max_model_len=IN + OUT + 64,
-              max_num_seqs=C, max_num_batched_tokens=8192, gpu_memory_utilization=0.9, seed=0,
-              enable_expert_parallel=args.ep and world > 1, speculative_config=spec,
+    llm = LLM(model, tensor_parallel_size=tp, data_parallel_size=dp, device="cuda", block_size=64,
+              max_model_len=IN + OUT + 64, max_num_seqs=C_local, max_num_batched_tokens=8192,
+              gpu_memory_utilization=0.9, seed=0, enable_expert_parallel=args.ep and tp > 1, speculative_config=spec,
               kv_cache_dtype=args.kv_cache_dtype)
     eng = llm.engine
+    dp_rank = eng.pstate.dp_rank if dp > 1 else 0
     vocab = eng.cfg.model.vocab_size
     g = torch.Generator().manual_seed(1234)
     # prompts live in pinned host memory; every round draws a fresh set so nothing is cached
@@ -201,7 +213,8 @@ def main():
     ttfts, tpots = [], []
 
     def one_round(i, collect=False):
-        outs = llm.generate([prompt_bank[i, c].tolist() for c in range(C)], sp)
+        # every replica serves its own share of the round's prompts
+        outs = llm.generate([prompt_bank[i, c].tolist() for c in range(dp_rank * C_local, (dp_rank + 1) * C_local)], sp)
         assert all(len(o.token_ids) == OUT for o in outs)
         if collect:
             ttfts.extend(o.ttft for o in outs)
@@ -242,6 +255,15 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_max = t.tolist()
+    if dp > 1:
+        # latencies and byte / launch counts of every replica (one reporter per replica: its first rank)
+        part = (ttfts, tpots, h2d, d2h, launches) if eng.pstate.tp_rank == 0 and eng.pstate.pp_rank == 0 else None
+        parts = [None] * world
+        dist.all_gather_object(parts, part)
+        parts = [x for x in parts if x is not None]
+        ttfts = [v for x in parts for v in x[0]]
+        tpots = [v for x in parts for v in x[1]]
+        h2d, d2h, launches = (sum(x[k] for x in parts) for k in (2, 3, 4))
     from vllm_kunlun_b200.ops.gemm_cuda import check_status
     check_status()
     # every status word of the peer-memory collectives and the expert exchange must be clean as well: a number
@@ -266,7 +288,8 @@ def main():
             "impl": "ours",
             "config": {"model": args.model, "bench_config": args.config, "global_batch": C, "seq_len": IN + OUT,
                        "in_len": IN, "out_len": OUT,
-                       "parallelism": f"tp{world}" + ("+ep" if args.ep and world > 1 else "") + (f"+{args.spec}" if args.spec else ""),
+                       "parallelism": f"tp{tp}" + (f"+dp{dp}" if dp > 1 else "") + ("+ep" if args.ep and tp > 1 else "") +
+                                      (f"+{args.spec}" if args.spec else ""),
                        "step": f"one full serving round of {C} requests",
                        **({"reduced_layers": args.layers, "valid": False} if args.layers else {}),
                        **({"spec_acceptance": round(eng.stats["spec_accepted"] / max(1, eng.stats["spec_proposed"]), 3)}

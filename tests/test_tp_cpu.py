@@ -149,3 +149,45 @@ def test_http_server_over_two_tp_ranks():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == want
+
+
+def _run_dp(rank, world, port, tp, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    from vllm_kunlun_b200 import LLM, SamplingParams
+    cfg = _cfg()
+    dp = world // tp
+    llm = LLM(cfg, device="cpu", tensor_parallel_size=tp, data_parallel_size=dp, block_size=16, max_model_len=128,
+              max_num_seqs=4, num_gpu_blocks=64)
+    with torch.inference_mode():
+        llm.engine.runner.model.load_weights(_full_state(cfg).items())
+    st = llm.engine.pstate
+    assert st.dp_size == dp and st.tp_size == tp and st.dp_rank == rank // tp
+    # every replica serves its own share of the prompts; replica 1 gets one prompt fewer (different step counts)
+    mine = _prompts()[st.dp_rank::dp]
+    outs = llm.generate(mine, SamplingParams(max_tokens=8, ignore_eos=True))
+    if st.tp_rank == tp - 1:
+        q.put((st.dp_rank, [o.token_ids for o in outs]))
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+@pytest.mark.parametrize("tp,dp", [(1, 2), (2, 2)])
+def test_data_parallel_replicas_serve_their_own_requests(tp, dp):
+    """``data_parallel_size`` replicas of ``tensor_parallel_size`` ranks schedule independently (different numbers of
+    requests and steps) and give the single-rank tokens."""
+    ref = _launch(1, 1)
+    world = tp * dp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_run_dp, args=(r, world, port, tp, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(dp))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for d in range(dp):
+        assert got[d] == ref[d::dp], d

@@ -91,12 +91,22 @@ class DecodeGraphs:
         same time everywhere; without this the first replay of the fastest rank would sit in its first peer wait
         for the difference."""
         import torch.distributed as dist
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            torch.cuda.synchronize()
-            if dist.get_backend() == "nccl":
-                dist.barrier(device_ids=[torch.cuda.current_device()])
+
+        from ..parallel.state import get_state
+        if not (dist.is_available() and dist.is_initialized()):
+            return
+        st = get_state()
+        # only the ranks of this model replica meet (tensor- and pipeline-parallel peers): data-parallel replicas
+        # schedule independently and may capture at different times
+        groups = [g for g, n in ((st.tp_group, st.tp_size), (st.pp_group, st.pp_size)) if g is not None and n > 1]
+        if not groups:
+            return
+        torch.cuda.synchronize()
+        for g in groups:
+            if dist.get_backend(g) == "nccl":
+                dist.barrier(group=g, device_ids=[torch.cuda.current_device()])
             else:
-                dist.barrier()
+                dist.barrier(group=g)
 
     @torch.inference_mode()
     def run(self, md: AttentionMetadata, input_ids, sp):

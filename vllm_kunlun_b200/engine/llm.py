@@ -243,7 +243,10 @@ class LLM:
                  enforce_eager: bool = False, speculative_config: Optional[dict] = None, seed: int = 0,
                  enable_chunked_prefill: bool = True, kv_cache_dtype: str = "auto",
                  fused_collectives: bool = True, tokenizer=None, enable_lora: bool = False, max_loras: int = 4,
-                 max_lora_rank: int = 16, decode_context_parallel_size: int = 1):
+                 max_lora_rank: int = 16, decode_context_parallel_size: int = 1, data_parallel_size: int = 1):
+        """``data_parallel_size`` > 1: the job's ranks form that many independent replicas of ``tensor_parallel_size x
+        pipeline_parallel_size`` ranks; every replica schedules and serves its own requests (the caller gives each
+        replica its share, ``engine.pstate.dp_rank`` tells which replica a rank belongs to)."""
         import os
         weights = None
         if isinstance(model, ModelConfig):
@@ -268,7 +271,7 @@ class LLM:
             cache=CacheConfig(block_size=block_size, num_blocks=num_gpu_blocks,
                               gpu_memory_utilization=gpu_memory_utilization, cache_dtype=kv_cache_dtype,
                               enable_prefix_caching=enable_prefix_caching),
-            parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size,
+            parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size, data_parallel_size,
                                     enable_expert_parallel=enable_expert_parallel,
                                     decode_context_parallel_size=decode_context_parallel_size,
                                     fused_collectives=fused_collectives),
