@@ -87,9 +87,10 @@ def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_l
                                           workspace.max_splits if workspace is not None else 16)
         ws_o = ws_lse = None
         if num_splits > 1:
-            if workspace is None:
+            if workspace is None or T > workspace.max_tokens or num_splits > workspace.max_splits:
+                # e.g. several requests whose last prefill chunk is only a few tokens long: more rows in decode
+                # layout than the step's decode batch was sized for
                 workspace = AttnWorkspace(T, Hq, D, num_splits, q.device)
-            assert T <= workspace.max_tokens and num_splits <= workspace.max_splits
             ws_o, ws_lse = workspace.o, workspace.lse
         _ext.C().decode_attention_umma(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, ws_o, ws_lse,
                                        max_query_len, num_splits, window or 0, scale, bool(stable_metadata))
@@ -109,9 +110,10 @@ def paged_attention_cuda(out, q, kv_cache, block_tables, seq_lens, query_start_l
             num_splits = 1
     ws_o = ws_lse = None
     if num_splits > 1:
-        if workspace is None:
+        if workspace is None or T > workspace.max_tokens or num_splits > workspace.max_splits:
+            # e.g. several requests whose last prefill chunk is only a few tokens long: more rows in decode
+            # layout than the step's decode batch was sized for
             workspace = AttnWorkspace(T, Hq, D, num_splits, q.device)
-        assert T <= workspace.max_tokens and num_splits <= workspace.max_splits
         ws_o, ws_lse = workspace.o, workspace.lse
     _ext.C().paged_attention(out, q, kv_cache, block_tables, seq_lens, query_start_loc, sinks, ws_o, ws_lse,
                              max_query_len, num_splits, window or 0, scale, decode_layout)
