@@ -21,7 +21,7 @@ MODULES = ["vllm_kunlun.platforms.kunlun", "vllm_kunlun.ops._custom_ops", "vllm_
 
 
 def main() -> int:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("B200_REFERENCE_DIR", "")   # a checkout of the reference
     here = os.path.dirname(os.path.abspath(__file__))
     installed = os.path.join(here, "_ref")
     work = tempfile.mkdtemp(prefix="refprobe_")

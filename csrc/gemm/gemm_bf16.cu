@@ -317,7 +317,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tile_coords(tile, nt, tt);
       int buf = local & 1;
       uint32_t acc_phase = (local >> 1) & 1;
-      // One thread does the bounded wait and publishes the verdict, so that the 128 epilogue
+      // One thread does the bounded wait and publishes the outcome, so that the 128 epilogue
       // threads always agree and none is left alone at a named barrier.
       // (two flag slots: thread 0 may already be publishing for the next item while a slow thread reads)
       if (ep_tid == 0) ep_ok_slot[local & 1] = wait_or_abort(&tmem_full[buf], acc_phase, ab, 104) ? 1 : 0;
