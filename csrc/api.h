@@ -175,6 +175,9 @@ int b200_prefill_attention_umma(void* out, float* lse, const void* tmQ, const vo
                                 const int* seq_lens, const int* qsl, const float* sinks, int* status, int B, int Hq, int Hkv,
                                 int D, int block_size, int max_blocks, int64_t num_blocks, int max_query_len, int window,
                                 float scale, int dtype, unsigned long long* trace, cudaStream_t st);
+int b200_mla_prefill_umma(void* out, float* lse, const void* tmQ, const void* tmKV, const void* tmKpe, const int* kv_starts,
+                          const int* kv_lens, const int* qsl, int* status, int B, int Hq, int max_query_len, int causal,
+                          float scale, int dtype, unsigned long long* trace, cudaStream_t st);
 int b200_gather_mla_rows(void* out, const void* cache, const int32_t* slots, int64_t M, int64_t total_slots, int fp8,
                          int dtype, cudaStream_t st);
 int b200_quant_int8_token(void* q, float* scale, const void* x, const float* static_scale, int64_t rows, int K,

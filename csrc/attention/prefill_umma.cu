@@ -13,6 +13,12 @@
 // current one are issued as they become ready), warps 2-5 softmax + epilogue.  Two S buffers (2 x 128 TMEM columns)
 // + O (128 columns).  Causal masking by position (chunked prefill: row r of the request sits at ctx + r), optional
 // sliding window and attention sinks, optional log-sum-exp output.
+// The MLA instantiation (`kMla`) is the compute-friendly prefill form of multi-head latent attention
+// (v1/attention/backends/mla/common.py:1782-1843): 192-dim q / k (128 "nope" dims per head + 64 rotary dims shared
+// by all heads), 128-dim v, keys and values read as contiguous rows of the up-projected `kv_b_proj` output
+// ([rows, heads * 256], k_nope | v per head) plus the rotary key rows ([rows, 64]); each request's keys start at
+// `kv_starts[req]`.  Causal (new tokens) or not (a chunk of cached context); the log-sum-exp output lets the caller
+// merge chunks.  Its K ring has two 48 KB stages and V a single 32 KB one (208 KB of shared memory in all).
 // TMA loads carry no cluster multicast.  Every wait is bounded; on time-out the status word is set and the CTA unwinds.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -31,8 +37,13 @@ constexpr int kThreads = 192;
 constexpr int kQTile = 128, kKTile = 128, kPage = 64, kD = 128;
 constexpr int kHalfBytes = 128 * 128;          // one 64-dim block of a 128-row operand tile
 constexpr int kOpBytes = 2 * kHalfBytes;       // Q, K, V or P tile: 32 KB
-constexpr int kStageBytes = 2 * kOpBytes;      // K + V
-constexpr int kStages = 2;
+constexpr int kStages = 2;                     // K ring
+template <bool kMla> struct Cfg {
+  static constexpr int kQBlocks = kMla ? 3 : 2;                 // 64-dim blocks of q / k
+  static constexpr int kKBytes = kQBlocks * kHalfBytes;         // Q tile or one K stage
+  static constexpr int kVStages = kMla ? 1 : 2;
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * kKBytes + (size_t)kVStages * kOpBytes + kKBytes + kOpBytes + 256;
+};
 constexpr int kTmemCols = 512;                 // 2 x 128 (S) + 128 (O)
 constexpr float kMaxSlack = 8.f;
 
@@ -42,10 +53,11 @@ struct Params {
   const int* block_tables;  // [B, max_blocks]
   const int* seq_lens;
   const int* qsl;
+  const int* kv_starts;     // MLA form: first key row of each request in the contiguous K / V tensors
   const float* sinks;       // [Hq] or null
   int* status;
   unsigned long long* trace;   // optional phase timestamps [CTA][24] (null = off)
-  int Hq, Hkv, block_size, max_blocks, window;
+  int Hq, Hkv, block_size, max_blocks, window, causal;
   int64_t num_blocks;
   float scale_log2;
 };
@@ -106,25 +118,29 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
   return (uint32_t)__half_as_ushort(__float2half(a)) | ((uint32_t)__half_as_ushort(__float2half(b)) << 16);
 }
 
-template <typename T>
+template <typename T, bool kMla>
 __global__ void __launch_bounds__(kThreads)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV,
-                    const __grid_constant__ Params p) {
+                    const __grid_constant__ CUtensorMap tmKpe, const __grid_constant__ Params p) {
+  constexpr int kQBlocks = Cfg<kMla>::kQBlocks, kKBytes = Cfg<kMla>::kKBytes, kVStages = Cfg<kMla>::kVStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + kStages * kStageBytes;       // [2 dim blocks][128 rows][128 B]
-  uint8_t* sP = sQ + kOpBytes;                      // [2 key blocks][128 rows][128 B]
+  uint8_t* sVr = smem + kStages * kKBytes;          // V ring: [kVStages][2 dim blocks][128 keys][128 B]
+  uint8_t* sQ = sVr + kVStages * kOpBytes;          // [kQBlocks dim blocks][128 rows][128 B]
+  uint8_t* sP = sQ + kKBytes;                       // [2 key blocks][128 rows][128 B]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kOpBytes);
   uint64_t* q_full = bars;             // [1]
-  uint64_t* kv_full = bars + 1;        // [2]
-  uint64_t* kv_empty = bars + 3;       // [2]
+  uint64_t* k_full = bars + 1;         // [2]
+  uint64_t* k_empty = bars + 3;        // [2] S of the tile has been computed
   uint64_t* s_full = bars + 5;         // [2]
   uint64_t* s_empty = bars + 7;        // [2]
   uint64_t* p_ready = bars + 9;        // [1] 4 arrivals (one per softmax warp)
   uint64_t* p_free = bars + 10;        // [1]
   uint64_t* o_done = bars + 11;        // [1] one phase per P.V
   uint64_t* o_final = bars + 12;       // [1] once, after the last P.V
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* v_full = bars + 13;        // [2] (kVStages used)
+  uint64_t* v_empty = bars + 15;       // [2] P.V of the tile has been computed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,13 +151,15 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     *abort_flag = 0;
     mbar_init(q_full, 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&kv_full[b], 1); mbar_init(&kv_empty[b], 1);
+      mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
+      mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
       mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
     }
     mbar_init(p_ready, 4); mbar_init(p_free, 1); mbar_init(o_done, 1); mbar_init(o_final, 1);
     mbar_fence_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmKV);
+    if (kMla) prefetch_tmap(&tmKpe);
     griddep_launch();
   }
   if (warp == 1) {
@@ -158,7 +176,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int kvh = head / (p.Hq / p.Hkv);
   const int qs = p.qsl[req], q_len = p.qsl[req + 1] - qs;
   const int seq_len = p.seq_lens[req];
-  const int ctx = seq_len - q_len;
+  // not causal: every row sees all of the request's keys - as if it sat far behind them
+  const int ctx = (kMla && !p.causal) ? (1 << 29) : seq_len - q_len;
   const int row0 = blockIdx.x * kQTile;                      // first query row of this tile within the request
   const int n_rows = max(0, min(kQTile, q_len - row0));
   // keys visible to the tile: up to the position of its last row; with a window, from the first row's window start
@@ -171,39 +190,82 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one() && n_tiles > 0) {
-      mbar_expect_tx(q_full, kOpBytes);
+      mbar_expect_tx(q_full, kKBytes);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) tma_load_2d(sQ + h * kHalfBytes, &tmQ, q_full, head * kD + h * 64, qs + row0);
-      const int* bt = p.block_tables + (int64_t)req * p.max_blocks;
-      bool ok = true;
-      int issued = 0;
-      for (int i = 0; i < n_tiles; ++i) {
+      for (int h = 0; h < kQBlocks; ++h)
+        tma_load_2d(sQ + h * kHalfBytes, &tmQ, q_full, head * (kQBlocks * 64) + h * 64, qs + row0);
+      const int* bt = kMla ? nullptr : p.block_tables + (int64_t)req * p.max_blocks;
+      const int kv_row0 = kMla ? p.kv_starts[req] : 0;
+      // cache row of a key's page (paged form): masked keys read any initialised page
+      auto page_row = [&](int key) -> int64_t {
+        const int bi = key / p.block_size;
+        int64_t blk = (key < kv_end && bi < p.max_blocks) ? bt[bi] : 0;
+        if (blk < 0 || blk >= p.num_blocks) blk = 0;
+        return ((blk * 2) * p.Hkv + kvh) * p.block_size + (key % p.block_size);
+      };
+      auto load_k = [&](int i) -> bool {
         const int stage = i & 1;
-        if (i >= kStages && !wait_or_abort(&kv_empty[stage], ((i >> 1) - 1) & 1, ab, 801)) { ok = false; break; }
-        mbar_expect_tx(&kv_full[stage], kStageBytes);
-        uint8_t* sK = smem + stage * kStageBytes;
-        uint8_t* sV = sK + kOpBytes;
-        const int key0 = kv_begin + i * kKTile;
+        if (i >= kStages && !wait_or_abort(&k_empty[stage], ((i >> 1) - 1) & 1, ab, 801)) return false;
+        mbar_expect_tx(&k_full[stage], kKBytes);
+        uint8_t* sK = smem + stage * kKBytes;
 #pragma unroll
         for (int pg = 0; pg < kKTile / kPage; ++pg) {
-          const int key = key0 + pg * kPage;
-          const int bi = key / p.block_size;
-          int64_t blk = (key < kv_end && bi < p.max_blocks) ? bt[bi] : 0;
-          if (blk < 0 || blk >= p.num_blocks) blk = 0;   // masked keys: any initialised page will do
-          const int64_t rowK = ((blk * 2) * p.Hkv + kvh) * p.block_size + (key % p.block_size);
-          const int64_t rowV = rowK + (int64_t)p.Hkv * p.block_size;
+          const int key = kv_begin + i * kKTile + pg * kPage;
+          uint8_t* dst = sK + pg * (kPage * 128);
+          if constexpr (kMla) {
+            // rows past the request's keys belong to the next request or lie outside the tensor (zero fill): masked
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            tma_load_2d(sK + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowK);
-            tma_load_2d(sV + h * kHalfBytes + pg * (kPage * 128), &tmKV, &kv_full[stage], h * 64, (int)rowV);
+            for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * kHalfBytes, &tmKV, &k_full[stage], head * 256 + h * 64, kv_row0 + key);
+            tma_load_2d(dst + 2 * kHalfBytes, &tmKpe, &k_full[stage], 0, kv_row0 + key);
+          } else {
+            const int64_t rowK = page_row(key);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * kHalfBytes, &tmKV, &k_full[stage], h * 64, (int)rowK);
           }
         }
-        ++issued;
+        return true;
+      };
+      auto load_v = [&](int i) -> bool {
+        const int stage = i % kVStages, use = i / kVStages;
+        if (i >= kVStages && !wait_or_abort(&v_empty[stage], (use - 1) & 1, ab, 804)) return false;
+        mbar_expect_tx(&v_full[stage], kOpBytes);
+        uint8_t* sV = sVr + stage * kOpBytes;
+#pragma unroll
+        for (int pg = 0; pg < kKTile / kPage; ++pg) {
+          const int key = kv_begin + i * kKTile + pg * kPage;
+          uint8_t* dst = sV + pg * (kPage * 128);
+          if constexpr (kMla) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              tma_load_2d(dst + h * kHalfBytes, &tmKV, &v_full[stage], head * 256 + 128 + h * 64, kv_row0 + key);
+          } else {
+            const int64_t rowV = page_row(key) + (int64_t)p.Hkv * p.block_size;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * kHalfBytes, &tmKV, &v_full[stage], h * 64, (int)rowV);
+          }
+        }
+        return true;
+      };
+      // order: K of the next tile before V of this one, so that S(i + 1) never waits behind the V ring
+      int issued_k = 0, issued_v = 0;
+      bool ok = true;
+      for (int j = 0; ok && j <= n_tiles; ++j) {      // K(0), K(1), V(0), K(2), V(1), ...
+        if (j < n_tiles) {
+          ok = load_k(j);
+          if (ok) ++issued_k;
+        }
+        if (ok && j >= 1) {
+          ok = load_v(j - 1);
+          if (ok) ++issued_v;
+        }
       }
-      if (!ok) {
-        for (int i = max(0, issued - kStages); i < issued; ++i)
+      if (!ok) {   // let the copies in flight land before the CTA's shared memory goes away (bounded)
+        for (int i = max(0, issued_k - kStages); i < issued_k; ++i)
           for (uint32_t q2 = 0; q2 < (1u << 16); ++q2)
-            if (mbar_try_wait(&kv_full[i & 1], (i >> 1) & 1)) break;
+            if (mbar_try_wait(&k_full[i & 1], (i >> 1) & 1)) break;
+        for (int i = max(0, issued_v - kVStages); i < issued_v; ++i)
+          for (uint32_t q2 = 0; q2 < (1u << 16); ++q2)
+            if (mbar_try_wait(&v_full[i % kVStages], (i / kVStages) & 1)) break;
       }
     }
   } else if (warp == 1) {
@@ -216,19 +278,20 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       auto issue_s = [&](int i) {
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(smem + (i & 1) * kStageBytes);
+        const uint32_t k_addr = smem_u32(smem + (i & 1) * kKBytes);
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) {
+        for (int k = 0; k < kQBlocks * 4; ++k) {
           const int kb = k / 4, kk = k % 4;
           umma_f16(tS + (i & 1) * kKTile, umma_desc_k_sw128(q_addr + kb * kHalfBytes + kk * 32),
                    umma_desc_k_sw128(k_addr + kb * kHalfBytes + kk * 32), idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[i & 1]);
+        umma_commit(&k_empty[i & 1]);
         if (i == 5) trace_mark(p.trace, cta_id, 13);
       };
       auto issue_pv = [&](int i) {
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(smem + (i & 1) * kStageBytes + kOpBytes);
+        const uint32_t v_addr = smem_u32(sVr + (i % kVStages) * kOpBytes);
 #pragma unroll
         for (int k = 0; k < kKTile / 16; ++k) {
           // A: 16 keys of P (key block k / 4, 32 bytes in); B: the same 16 keys of V, 128 dims (two 64-dim blocks)
@@ -237,7 +300,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (i == 3) trace_mark(p.trace, cta_id, 12);
         umma_commit(o_done);   // first: whoever has seen p_free of this tile may rely on o_done having advanced
-        umma_commit(&kv_empty[i & 1]);
+        umma_commit(&v_empty[i % kVStages]);
         umma_commit(p_free);
         if (i == n_tiles - 1) umma_commit(o_final);
       };
@@ -246,13 +309,14 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       uint32_t spins = 0;
       while (ok && next_pv < n_tiles) {
         bool progressed = false;
-        if (next_s < n_tiles && next_s <= next_pv + 1 && mbar_try_wait(&kv_full[next_s & 1], (next_s >> 1) & 1) &&
+        if (next_s < n_tiles && next_s <= next_pv + 1 && mbar_try_wait(&k_full[next_s & 1], (next_s >> 1) & 1) &&
             (next_s < 2 || mbar_try_wait(&s_empty[next_s & 1], ((next_s >> 1) - 1) & 1))) {
           issue_s(next_s);
           ++next_s;
           progressed = true;
         }
-        if (next_pv < next_s && mbar_try_wait(p_ready, next_pv & 1)) {
+        if (next_pv < next_s && mbar_try_wait(p_ready, next_pv & 1) &&
+            mbar_try_wait(&v_full[next_pv % kVStages], (next_pv / kVStages) & 1)) {
           if (next_pv == 4) trace_mark(p.trace, cta_id, 9);
           issue_pv(next_pv);
           ++next_pv;
@@ -413,14 +477,15 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-template <typename T>
-static int launch(const Params& p, const CUtensorMap& tmQ, const CUtensorMap& tmKV, int B, int max_query_len, cudaStream_t st) {
-  auto kern = prefill_umma_kernel<T>;
-  const size_t smem = 1024 + (size_t)kStages * kStageBytes + 2 * kOpBytes + 256;
+template <typename T, bool kMla>
+static int launch(const Params& p, const CUtensorMap& tmQ, const CUtensorMap& tmKV, const CUtensorMap& tmKpe, int B,
+                  int max_query_len, cudaStream_t st) {
+  auto kern = prefill_umma_kernel<T, kMla>;
+  const size_t smem = Cfg<kMla>::kSmem;
   cudaError_t e = ensure_dynamic_smem((const void*)kern, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid((unsigned)((max_query_len + kQTile - 1) / kQTile), (unsigned)p.Hq, (unsigned)B);
-  return (int)launch_pdl(kern, grid, dim3(kThreads), smem, st, tmQ, tmKV, p);
+  return (int)launch_pdl(kern, grid, dim3(kThreads), smem, st, tmQ, tmKV, tmKpe, p);
 }
 
 }  // namespace pattn
@@ -441,9 +506,36 @@ extern "C" int b200_prefill_attention_umma(void* out, float* lse, const void* tm
   p.out = out; p.lse = lse; p.block_tables = block_tables; p.seq_lens = seq_lens; p.qsl = qsl; p.sinks = sinks;
   p.status = status; p.trace = trace; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.window = window;
   p.num_blocks = num_blocks; p.scale_log2 = scale * 1.4426950408889634f;
+  p.kv_starts = nullptr; p.causal = 1;
   const CUtensorMap& q = *reinterpret_cast<const CUtensorMap*>(tmQ);
   const CUtensorMap& kv = *reinterpret_cast<const CUtensorMap*>(tmKV);
-  if (dtype == 1) return pattn::launch<__nv_bfloat16>(p, q, kv, B, max_query_len, st);
-  if (dtype == 2) return pattn::launch<__half>(p, q, kv, B, max_query_len, st);
+  if (dtype == 1) return pattn::launch<__nv_bfloat16, false>(p, q, kv, kv, B, max_query_len, st);
+  if (dtype == 2) return pattn::launch<__half, false>(p, q, kv, kv, B, max_query_len, st);
+  return 3;
+}
+
+// Multi-head latent attention prefill in the compute-friendly form (192-dim q / k, 128-dim v) on tcgen05.
+// `tmQ`: q as [T, Hq * 192] with 64-column x 128-row boxes; `tmKV`: the up-projected keys / values as
+// [rows, Hq * 256] (k_nope | v per head) with 64 x 64 boxes; `tmKpe`: the rotary keys as [rows, 64] with 64 x 64
+// boxes; all 16-bit with 128-byte swizzle and row extents equal to the number of valid rows.  Request r owns key rows
+// kv_starts[r] .. kv_starts[r] + kv_lens[r] and query rows qsl[r] .. qsl[r + 1]; causal: its queries are its last
+// keys.  Rows of requests with no key are not written (the caller presets out = 0, lse = -inf).
+extern "C" int b200_mla_prefill_umma(void* out, float* lse, const void* tmQ, const void* tmKV, const void* tmKpe,
+                                     const int* kv_starts, const int* kv_lens, const int* qsl, int* status, int B,
+                                     int Hq, int max_query_len, int causal, float scale, int dtype,
+                                     unsigned long long* trace, cudaStream_t st) {
+  using namespace b200;
+  if (B == 0 || max_query_len <= 0) return 0;
+  if (B > 65535 || Hq > 65535) return 3;
+  pattn::Params p;
+  p.out = out; p.lse = lse; p.block_tables = nullptr; p.seq_lens = kv_lens; p.qsl = qsl; p.kv_starts = kv_starts;
+  p.sinks = nullptr; p.status = status; p.trace = trace; p.Hq = Hq; p.Hkv = Hq; p.block_size = pattn::kPage;
+  p.max_blocks = 0; p.window = 0; p.causal = causal ? 1 : 0; p.num_blocks = 0;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const CUtensorMap& q = *reinterpret_cast<const CUtensorMap*>(tmQ);
+  const CUtensorMap& kv = *reinterpret_cast<const CUtensorMap*>(tmKV);
+  const CUtensorMap& kpe = *reinterpret_cast<const CUtensorMap*>(tmKpe);
+  if (dtype == 1) return pattn::launch<__nv_bfloat16, true>(p, q, kv, kpe, B, max_query_len, st);
+  if (dtype == 2) return pattn::launch<__half, true>(p, q, kv, kpe, B, max_query_len, st);
   return 3;
 }

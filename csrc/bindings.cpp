@@ -928,6 +928,50 @@ void prefill_attention_umma(at::Tensor out, const at::Tensor& q, const at::Tenso
         "prefill_attention_umma");
 }
 
+// MLA prefill in the compute-friendly form on tcgen05: q [T, N, 192] (q_nope | rotated q_pe), kv [rows, N * 256]
+// (k_nope | v per head: the kv_b_proj output), k_pe [rows, 64] (rotated; may be a strided view), kv_starts / kv_lens
+// [B] and qsl [B + 1] int32 -> out [T, N, 128], lse [T, N] (natural log).  Rows of requests without keys are left
+// untouched: preset out = 0 and lse = -inf when that can happen.
+void mla_prefill_umma(at::Tensor out, const at::Tensor& q, const at::Tensor& kv, const at::Tensor& k_pe,
+                      const at::Tensor& kv_starts, const at::Tensor& kv_lens, const at::Tensor& qsl,
+                      const c10::optional<at::Tensor>& lse, int64_t max_query_len, bool causal, double scale) {
+  TORCH_CHECK(q.is_cuda() && q.is_contiguous() && out.is_contiguous() && q.dim() == 3 && q.size(2) == 192);
+  TORCH_CHECK(out.dim() == 3 && out.size(0) == q.size(0) && out.size(1) == q.size(1) && out.size(2) == 128);
+  TORCH_CHECK(kv.dim() == 2 && kv.stride(1) == 1 && kv.size(1) == q.size(1) * 256 && (kv.stride(0) * 2) % 16 == 0);
+  TORCH_CHECK(k_pe.dim() == 2 && k_pe.stride(1) == 1 && k_pe.size(1) == 64 && k_pe.size(0) == kv.size(0) &&
+              (k_pe.stride(0) * 2) % 16 == 0);
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(kv.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(k_pe.data_ptr()) % 16 == 0);
+  TORCH_CHECK(q.scalar_type() == kv.scalar_type() && q.scalar_type() == k_pe.scalar_type() && q.scalar_type() == out.scalar_type());
+  TORCH_CHECK(kv_starts.scalar_type() == at::kInt && kv_lens.scalar_type() == at::kInt && qsl.scalar_type() == at::kInt);
+  TORCH_CHECK(kv_starts.is_contiguous() && kv_lens.is_contiguous() && qsl.is_contiguous());
+  TORCH_CHECK(kv_starts.numel() == kv_lens.numel() && qsl.numel() == kv_lens.numel() + 1);
+  if (lse.has_value()) TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == q.size(0) * q.size(1));
+  if (q.size(0) == 0 || kv.size(0) == 0) return;
+  c10::cuda::CUDAGuard guard(q.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, q.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, q.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, q.options().dtype(at::kInt));
+  }
+  at::Tensor q2 = q.view({q.size(0), q.size(1) * 192});
+  const Tmap& tq = get_tmap(gs, q2, 128, 2);
+  const Tmap& tk = get_tmap(gs, kv, 64, 2);
+  const Tmap& tp = get_tmap(gs, k_pe, 64, 2);
+  const int B = (int)kv_lens.numel();
+  check(b200_mla_prefill_umma(out.data_ptr(), lse.has_value() ? lse->data_ptr<float>() : nullptr, tq.b, tk.b, tp.b,
+                              kv_starts.data_ptr<int>(), kv_lens.data_ptr<int>(), qsl.data_ptr<int>(),
+                              gs.status.data_ptr<int>(), B, (int)q.size(1), (int)max_query_len, causal ? 1 : 0,
+                              (float)scale, dtype_code(q),
+                              (g_kernel_trace.defined() &&
+                               g_kernel_trace.numel() >= (int64_t)B * q.size(1) * ((max_query_len + 127) / 128) * 24)
+                                  ? reinterpret_cast<unsigned long long*>(g_kernel_trace.data_ptr<int64_t>()) : nullptr,
+                              stream()),
+        "mla_prefill_umma");
+}
+
 // Dense paged MLA decode on tcgen05: q [T, N, 576], kv [blocks, 64, 576] -> out [T, N, 512].
 // Optional phase-trace buffer (int64 [>= CTAs * 24]) for the kernels that support it; an undefined tensor switches it off.
 at::Tensor g_kernel_trace;
@@ -1373,6 +1417,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention_umma", &decode_attention_umma);
   m.def("mla_decode_umma", &mla_decode_umma);
   m.def("prefill_attention_umma", &prefill_attention_umma);
+  m.def("mla_prefill_umma", &mla_prefill_umma);
   m.def("indexer_prep", &indexer_prep);
   m.def("gather_mla_rows", &gather_mla_rows);
   m.def("set_kernel_trace", &set_kernel_trace);

@@ -111,3 +111,86 @@ def test_sparse_engine_fp8_latent_cache_cpu():
             assert first[0].shape[-1] == 656
         toks[kvd] = [o.token_ids for o in llm.generate(prompts, sp)]
     assert all(len(t) == 4 for t in toks["fp8_ds_mla"])
+
+
+def _logits_of_steps(llm, prompts, chunk_note=None):
+    """Greedy tokens plus the hidden-state fingerprint (first-step logits) of every request."""
+    sp = SamplingParams(max_tokens=5, ignore_eos=True, logprobs=None)
+    return [o.token_ids for o in llm.generate(prompts, sp)]
+
+
+@pytest.mark.parametrize("max_batched", [None, 96])
+def test_mla_prefill_up_projected_form_equals_absorbed(max_batched):
+    """The 192 / 128-style prefill form (new tokens causal + cached context in bounded chunks merged by LSE + the
+    other requests of a mixed step on the absorbed form) gives the attention output of the absorbed form."""
+    from vllm_kunlun_b200.models.deepseek import MLAAttention
+    cfg = _cfg()
+    kw = dict(device="cpu", block_size=64, max_model_len=512, max_num_seqs=4, num_gpu_blocks=32)
+    if max_batched:
+        kw["max_num_batched_tokens"] = max_batched      # chunked prefill: later chunks see cached context
+    a = LLM(cfg, **kw)
+    b = LLM(cfg, **kw)
+    with torch.inference_mode():
+        b.engine.runner.model.load_state_dict(a.engine.runner.model.state_dict())
+        b.engine.runner.model.finish_loading()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 320, (n,), generator=g).tolist() for n in (150, 70, 5, 230)]
+    calls = {"n": 0, "chunks": 0, "mixed": 0}
+    orig = MLAAttention._attend_prefill
+
+    def spy(self, plan, *args):
+        calls["n"] += 1
+        calls["chunks"] += len(plan["chunks"])
+        calls["mixed"] += plan["rest"] is not None
+        return orig(self, plan, *args)
+
+    want = _logits_of_steps(a, prompts)
+    old = (MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_MIN_QUERY, MLAAttention.PREFILL_CTX_BYTES,
+           MLAAttention._attend_prefill)
+    try:
+        MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_MIN_QUERY = True, 16
+        MLAAttention.PREFILL_CTX_BYTES = 4 * (32 + 32) * 2 * 64      # 64 context tokens per pass: several chunks
+        MLAAttention._attend_prefill = spy
+        got = _logits_of_steps(b, prompts)
+    finally:
+        (MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_MIN_QUERY, MLAAttention.PREFILL_CTX_BYTES,
+         MLAAttention._attend_prefill) = old
+    assert calls["n"] > 0
+    if max_batched:
+        assert calls["chunks"] > calls["n"] // 3 and calls["mixed"] > 0, calls
+    assert got == want
+
+
+def test_mla_prefill_form_attention_rows_match():
+    """One attention layer, one step with cached context for one request and none for another: row-level agreement
+    of the two forms (not just tokens)."""
+    from vllm_kunlun_b200.models.deepseek import MLAAttention
+    cfg = _cfg()
+    llm = LLM(cfg, device="cpu", block_size=64, max_model_len=512, max_num_seqs=4, num_gpu_blocks=32,
+              max_num_batched_tokens=128)
+    eng = llm.engine
+    attn = eng.runner.model.layers["0"].self_attn
+    eng.add_request(list(range(200)), SamplingParams(max_tokens=1))
+    g = torch.Generator().manual_seed(5)
+    outs = []
+    for step in range(2):       # step 0: 128 new tokens; step 1: 72 new tokens over 128 cached ones
+        sched = eng.scheduler.schedule()
+        md, ids, _ = eng.runner.prepare(sched)
+        hidden = torch.randn(md.num_tokens, cfg.hidden_size, generator=g) * 0.5
+        with torch.inference_mode(), set_forward_context(ForwardContext(md, eng.runner.kv_caches, eng.pstate)):
+            want = attn(hidden)
+            md.extras.pop("mla_prefill_plan", None)
+            old = (MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_MIN_QUERY, MLAAttention.PREFILL_CTX_BYTES)
+            try:
+                MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_MIN_QUERY = True, 16
+                MLAAttention.PREFILL_CTX_BYTES = 4 * 64 * 2 * 64
+                got = attn(hidden)
+                plan = md.extras["mla_prefill_plan"]
+            finally:
+                MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_MIN_QUERY, MLAAttention.PREFILL_CTX_BYTES = old
+        assert plan is not None and len(plan["chunks"]) == (2 if step else 0)
+        assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (step, (got - want).abs().max())
+        outs.append(got)
+        # advance the request by hand: the scheduler's bookkeeping for a finished chunk
+        for sr in sched.scheduled:
+            sr.req.num_computed_tokens += sr.num_new_tokens

@@ -374,3 +374,85 @@ def test_deepseek_sparse_engine_fp8_latent_cache():
     assert all(len(t) == 6 for t in toks["fp8_ds_mla"])
     same = sum(a == b for x, y in zip(toks["auto"], toks["fp8_ds_mla"]) for a, b in zip(x, y))
     assert same >= 6, toks   # at least half of the 12 greedy tokens
+
+
+@pytest.mark.parametrize("N", [16, 3])
+@pytest.mark.parametrize("causal", [True, False])
+def test_mla_prefill_umma_kernel(N, causal):
+    """MLA prefill in the up-projected form on tcgen05 (192-dim q / k from three 64-dim blocks, the rotary block
+    shared by the heads; 128-dim v; contiguous keys per request) vs the fp32 oracle: key counts on and off the
+    128-key tile edge, query tiles that end inside a tile, a request without keys (not causal), a strided view as
+    the rotary-key tensor, and the log-sum-exp output."""
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    g = torch.Generator().manual_seed(N + 7 * causal)
+    if causal:
+        q_lens = [1, 64, 127, 128, 129, 300, 517]
+        kv_lens = list(q_lens)
+    else:
+        q_lens = [5, 130, 64, 256, 77]
+        kv_lens = [700, 128, 0, 129, 1]
+    T, R = sum(q_lens), sum(kv_lens)
+    q = (torch.randn(T, N, 192, generator=g) * 0.5).bfloat16()
+    kv = (torch.randn(R, N * 256, generator=g) * 0.5).bfloat16()
+    rows = (torch.randn(R, 576, generator=g) * 0.5).bfloat16()      # k_pe = the last 64 columns of gathered rows
+    qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    ks = torch.tensor([0] + list(torch.tensor(kv_lens).cumsum(0))[:-1], dtype=torch.int32)
+    kl = torch.tensor(kv_lens, dtype=torch.int32)
+    scale = 192 ** -0.5
+    want, want_lse = ra.mla_prefill(q, kv, rows[:, 512:], ks, kl, qsl, causal, scale)
+    rows_d = rows.to(DEV)
+    out, lse = ops.mla_prefill_attention(q.to(DEV), kv.to(DEV), rows_d[:, 512:], ks.to(DEV), kl.to(DEV), qsl.to(DEV),
+                                         causal, scale, max(q_lens))
+    check_status()
+    _close(out, want, 0.02, 0.03, f"mla prefill out N={N} causal={causal}")
+    fin = torch.isfinite(want_lse)
+    assert bool((torch.isfinite(lse.cpu()) == fin).all())
+    _close(lse.cpu()[fin], want_lse[fin], 0.02, 0.01, "mla prefill lse")
+    if not causal:      # the request without keys: untouched rows (zeros / -inf as preset)
+        s, e = int(qsl[2]), int(qsl[3])
+        assert float(out[s:e].abs().max()) == 0.0 and bool(torch.isinf(lse[s:e]).all())
+
+
+def test_mla_attention_prefill_form_matches_absorbed_form_gpu():
+    """One MLA layer on the GPU: a 200-token prompt under a 140-token step budget (the second step has 60 new tokens
+    over 140 cached ones, read through three passes of a 64-token context workspace, and a 7-token request beside
+    it that stays on the absorbed form); the up-projected form must give the rows of the absorbed form."""
+    from vllm_kunlun_b200.attention.metadata import ForwardContext, set_forward_context
+    from vllm_kunlun_b200.models.deepseek import MLAAttention
+    cfg = tiny(deepseek_v3(fp8=False), num_layers=2, first_dense_layers=1, vocab_size=1024, hidden_size=512,
+               num_heads=16, num_kv_heads=16, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+               qk_rope_head_dim=64, v_head_dim=128, head_dim=192, rotary_dim=64, intermediate_size=1024,
+               num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, n_group=4, topk_group=2,
+               max_position=2048, rope_scaling=RopeScaling(type="yarn", factor=4.0, original_max_position=512,
+                                                           mscale=1.0, mscale_all_dim=1.0), num_mtp_layers=0)
+    llm = LLM(cfg, device="cuda", block_size=64, max_model_len=512, max_num_seqs=4, num_gpu_blocks=32,
+              max_num_batched_tokens=140, enforce_eager=True, seed=3)
+    eng = llm.engine
+    attn = eng.runner.model.layers["0"].self_attn
+    eng.add_request(list(range(200)), SamplingParams(max_tokens=1))
+    eng.add_request(list(range(7)), SamplingParams(max_tokens=1))
+    g = torch.Generator().manual_seed(5)
+    old = (MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_CTX_BYTES, MLAAttention.PREFILL_MIN_QUERY)
+    MLAAttention.PREFILL_MIN_QUERY = 16
+    seen_chunks, mixed = [], []
+    try:
+        for step in range(2):
+            sched = eng.scheduler.schedule()
+            md, ids, _ = eng.runner.prepare(sched)
+            hidden = (torch.randn(md.num_tokens, cfg.hidden_size, generator=g) * 0.5).bfloat16().to(DEV)
+            with torch.inference_mode(), set_forward_context(ForwardContext(md, eng.runner.kv_caches, eng.pstate)):
+                MLAAttention.PREFILL_FORM = False
+                want = attn(hidden)
+                md.extras.pop("mla_prefill_plan", None)
+                MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_CTX_BYTES = True, 16 * 256 * 2 * 64
+                got = attn(hidden)
+                plan = md.extras["mla_prefill_plan"]
+            assert plan is not None
+            seen_chunks.append(len(plan["chunks"]))
+            mixed.append(plan["rest"] is not None)
+            _close(got, want, 0.03, 0.05, f"step {step}")
+            for sr in sched.scheduled:
+                sr.req.num_computed_tokens += sr.num_new_tokens
+    finally:
+        MLAAttention.PREFILL_FORM, MLAAttention.PREFILL_CTX_BYTES, MLAAttention.PREFILL_MIN_QUERY = old
+    assert seen_chunks == [0, 3] and mixed == [False, True], (seen_chunks, mixed)

@@ -146,6 +146,125 @@ class MLAAttention(nn.Module):
         w = w.to(self._dtype).view(self.num_heads, self.nope + self.vdim, self.rank)
         self.w_uk = w[:, : self.nope].contiguous()                    # q_nope [T,N,nope] x [N,nope,rank]
         self.w_uv = w[:, self.nope:].transpose(1, 2).contiguous()     # out [T,N,rank] x [N,rank,vdim]
+        # the up-projection itself, for the 192 / 128 prefill form (a view of the weight when that is 16-bit already)
+        self.w_kvb = w.reshape(self.num_heads * (self.nope + self.vdim), self.rank)
+
+    # ------------------------------------------------------------------ prefill in the up-projected form
+    PREFILL_MIN_QUERY = 64            # requests with at least this many new tokens leave the absorbed form
+    PREFILL_CTX_BYTES = 256 << 20     # bound of the up-projected context workspace (k_nope | v rows), bytes
+    PREFILL_FORM = None               # None: on CUDA only; True / False force it (tests)
+
+    def _prefill_plan(self, md, kv_cache, on_cuda: bool):
+        """Which requests of this step take the up-projected form, and the chunks their cached context is read in.
+        Built once per step (every layer shares block tables and lengths) and kept in ``md.extras``.
+
+        The absorbed form spends 576 + 512 multiply-adds per (query, key, head), the up-projected one 192 + 128 plus
+        one ``kv_b_proj`` pass over the keys (``mla/common.py:1782-1843``); cached context (chunked prefill, prefix
+        hits) is gathered from the paged latent cache chunk by chunk into a bounded workspace, up-projected,
+        attended without a mask and merged by log-sum-exp (``mla/common.py:1614-1677``, workspace ``:467-495``)."""
+        if "mla_prefill_plan" in md.extras:
+            return md.extras["mla_prefill_plan"]
+        plan = None
+        enabled = on_cuda if self.PREFILL_FORM is None else self.PREFILL_FORM
+        ok = (enabled and self.indexer is None and not md.is_dummy
+              and ((self.nope, self.rope, self.vdim) == (128, 64, 128) or not on_cuda)   # the kernel's shape and md.max_query_len >= self.PREFILL_MIN_QUERY
+              and md.seq_lens_cpu is not None and md.query_start_loc_cpu is not None
+              and not (kv_cache.dtype == torch.uint8 and not on_cuda))
+        if ok:
+            import numpy as np
+            dev = kv_cache.device
+            B = md.num_reqs
+            qsl = md.query_start_loc_cpu.numpy().astype(np.int64)[: B + 1]
+            sl = md.seq_lens_cpu.numpy().astype(np.int64)[:B]
+            ql = qsl[1:] - qsl[:-1]
+            pre = np.nonzero(ql >= self.PREFILL_MIN_QUERY)[0]
+            rest = np.nonzero((ql < self.PREFILL_MIN_QUERY) & (ql > 0))[0]
+
+            def dev_i32(a):
+                return torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+
+            def dev_i64(a):
+                return torch.from_numpy(np.ascontiguousarray(a, dtype=np.int64)).to(dev)
+
+            plan = {"all": len(rest) == 0 and len(pre) == B}
+            qlp = ql[pre]
+            qsl_p = np.concatenate([[0], np.cumsum(qlp)])
+            plan["tok"] = None if plan["all"] else dev_i64(np.concatenate([np.arange(qsl[r], qsl[r + 1]) for r in pre]))
+            plan["qsl"] = dev_i32(qsl_p)
+            plan["kv_starts"] = dev_i32(qsl_p[:-1])
+            plan["kv_lens"] = dev_i32(qlp)
+            plan["qsl_cpu"], plan["q_lens_cpu"] = qsl_p, qlp
+            plan["max_q"] = int(qlp.max())
+            # cached context of the prefill requests, in chunks that fit the workspace
+            ctx = (sl - ql)[pre]
+            chunks = []
+            n_ctx = int((ctx > 0).sum())
+            if n_ctx:
+                bs = kv_cache.shape[1]
+                budget = max(64, self.PREFILL_CTX_BYTES // (self.num_heads * (self.nope + self.vdim) * 2))
+                per_req = max(64, budget // n_ctx // 64 * 64)
+                for lo in range(0, int(ctx.max()), per_req):
+                    a = np.minimum(ctx, lo)
+                    b = np.minimum(ctx, lo + per_req)
+                    lens = b - a
+                    req = np.repeat(pre, lens)
+                    pos = np.concatenate([np.arange(x, y) for x, y in zip(a, b)])
+                    req_d, pos_d = dev_i64(req), dev_i64(pos)
+                    slots = (md.block_tables[req_d, pos_d // bs].long() * bs + pos_d % bs).to(torch.int32)
+                    starts = np.concatenate([[0], np.cumsum(lens)])[:-1]
+                    chunks.append({"slots": slots, "kv_starts": dev_i32(starts), "kv_lens": dev_i32(lens),
+                                   "starts_cpu": starts, "lens_cpu": lens})
+            plan["chunks"] = chunks
+            # the other requests of a mixed step keep the absorbed form over a compacted sub-batch
+            if len(rest):
+                qlr = ql[rest]
+                qsl_r = np.concatenate([[0], np.cumsum(qlr)])
+                rest_d = dev_i64(rest)
+                plan["rest"] = {
+                    "tok": dev_i64(np.concatenate([np.arange(qsl[r], qsl[r + 1]) for r in rest])),
+                    "block_tables": md.block_tables.index_select(0, rest_d).contiguous(),
+                    "seq_lens": dev_i32(sl[rest]), "qsl": dev_i32(qsl_r),
+                    "seq_lens_cpu": torch.from_numpy(sl[rest].astype(np.int32)),
+                    "qsl_cpu": torch.from_numpy(qsl_r.astype(np.int32)),
+                    "max_q": int(qlr.max()), "max_seq": int(sl[rest].max())}
+            else:
+                plan["rest"] = None
+        md.extras["mla_prefill_plan"] = plan
+        return plan
+
+    def _attend_prefill(self, plan, q_nope, q_pe, kv_c, k_pe, kv_cache):
+        """Attention of the plan's prefill requests in the up-projected form -> ``[Tp, N, vdim]``."""
+        N = self.num_heads
+        tok = plan["tok"]
+        if tok is not None:
+            q_nope, q_pe, kv_c, k_pe = (x.index_select(0, tok) for x in (q_nope, q_pe, kv_c, k_pe))
+        Tp = q_nope.shape[0]
+        q = torch.cat([q_nope, q_pe.view(Tp, N, self.rope)], -1)
+        cpu = not q.is_cuda
+        # the new tokens among themselves (causal)
+        kv_new = ops.linear(kv_c.contiguous(), self.w_kvb)
+        out, lse = ops.mla_prefill_attention(q, kv_new, k_pe.contiguous(),
+                                             plan["qsl_cpu"][:-1] if cpu else plan["kv_starts"],
+                                             plan["q_lens_cpu"] if cpu else plan["kv_lens"],
+                                             plan["qsl_cpu"] if cpu else plan["qsl"], True, self.scale, plan["max_q"])
+        del kv_new
+        # cached context, chunk by chunk through the bounded workspace (no mask), merged by log-sum-exp
+        for ch in plan["chunks"]:
+            n = ch["slots"].shape[0]
+            if cpu:
+                rows = kv_cache.reshape(-1, kv_cache.shape[-1])[ch["slots"].long()]
+            else:
+                from ..ops import _ext
+                rows = torch.empty(n, self.rank + self.rope, dtype=q.dtype, device=q.device)
+                _ext.C().gather_mla_rows(rows, kv_cache, ch["slots"])
+            kv_ctx = ops.linear(rows[:, : self.rank].contiguous(), self.w_kvb)
+            o_c, lse_c = ops.mla_prefill_attention(q, kv_ctx, rows[:, self.rank:],
+                                                   ch["starts_cpu"] if cpu else ch["kv_starts"],
+                                                   ch["lens_cpu"] if cpu else ch["kv_lens"],
+                                                   plan["qsl_cpu"] if cpu else plan["qsl"], False, self.scale,
+                                                   plan["max_q"])
+            out, lse = ops.merge_attn_states(out, lse, o_c, lse_c)
+        return out
 
     FP8_GATHER_TOKENS = 256   # query tokens per pass of the fp8-cache path (scratch: tokens x top-k x 1152 bytes)
 
@@ -196,6 +315,26 @@ class MLAAttention(nn.Module):
         q_pe, k_pe = ops.rope(q_pe.reshape(T, -1).contiguous(), k_pe.contiguous(), md.positions, self.cos_sin,
                               self.rope, cfg.rope_neox)
         ops.concat_and_cache_mla(kv_c, k_pe, kv_cache, md.slot_mapping)
+        plan = None
+        if self.indexer is None and ctx.pstate.dcp_size == 1 and md.max_query_len >= self.PREFILL_MIN_QUERY:
+            plan = self._prefill_plan(md, kv_cache, hidden.is_cuda)
+        if plan is not None:
+            o_p = self._attend_prefill(plan, q_nope, q_pe, kv_c, k_pe, kv_cache)
+            rest = plan["rest"]
+            if plan["all"]:
+                v = o_p
+            else:
+                v = torch.zeros(T, self.num_heads, self.vdim, dtype=o_p.dtype, device=o_p.device)
+                v.index_copy_(0, plan["tok"], o_p)
+                if rest is not None:   # decode / short rows of a mixed step: the absorbed form over a sub-batch
+                    qn = q_nope.index_select(0, rest["tok"])
+                    qp = q_pe.view(T, self.num_heads, self.rope).index_select(0, rest["tok"])
+                    qf = torch.cat([ops.bmm_heads(qn, self.w_uk), qp], -1).contiguous()
+                    o = ops.mla_attention(qf, kv_cache, rest["block_tables"], rest["seq_lens"], rest["qsl"], self.scale,
+                                          self.rank, rest["max_q"], rest["max_seq"], rest["seq_lens_cpu"],
+                                          rest["qsl_cpu"], md.workspace)
+                    v.index_copy_(0, rest["tok"], ops.bmm_heads(o, self.w_uv))
+            return self.o_proj(v.reshape(T, self.num_heads * self.vdim))
         # absorbed query: [T, N, rank] = q_nope . W_UK   (batched over heads)
         ql = ops.bmm_heads(q_nope, self.w_uk)
         qf = torch.cat([ql, q_pe.view(T, self.num_heads, self.rope)], -1)

@@ -392,6 +392,24 @@ def mla_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale: f
     return _ra.mla_decode(q, kv_cache, block_tables, sl, ql, scale, kv_lora_rank, return_lse=return_lse)
 
 
+def mla_prefill_attention(q, kv, k_pe, kv_starts, kv_lens, query_start_loc, causal: bool, scale: float,
+                          max_query_len: int, out=None, lse=None):
+    """MLA prefill in the up-projected 192 / 128 form over contiguous keys (the new tokens themselves, causal; or a
+    gathered and up-projected chunk of cached context, not causal): ``q [T, N, 192]``, ``kv [rows, N * 256]``,
+    ``k_pe [rows, 64]`` -> ``out [T, N, 128]``, natural-log ``lse [T, N]``.  Rows of requests without keys give
+    zeros and ``-inf``.  CUDA: the tcgen05 prefill kernel (``csrc/attention/prefill_umma.cu``, MLA instantiation)."""
+    if q.is_cuda:
+        T, N, _ = q.shape
+        if out is None:
+            out = torch.zeros(T, N, 128, dtype=q.dtype, device=q.device)
+        if lse is None:
+            lse = torch.full((T, N), float("-inf"), dtype=torch.float32, device=q.device)
+        _c().mla_prefill_umma(out, q, kv, k_pe, kv_starts, kv_lens, query_start_loc, lse, int(max_query_len),
+                              bool(causal), float(scale))
+        return out, lse
+    return _ra.mla_prefill(q, kv, k_pe, kv_starts, kv_lens, query_start_loc, causal, scale)
+
+
 def sparse_mla_attention(q, kv_cache, indices, scale: float, d_v: int = 512):
     """DeepSeek sparse attention: every query row attends its own ``indices [T, topk]`` (global slot ids,
     -1 = none) of the flat latent cache.  Returns ``out [T, N, d_v]``."""

@@ -254,6 +254,38 @@ def merge_attn_states(o1, lse1, o2, lse2):
 
 # ----------------------------------------------------------------------------- MLA
 
+def mla_prefill(q, kv, k_pe, kv_starts, kv_lens, query_start_loc, causal: bool, scale: float):
+    """Multi-head latent attention in the up-projected ("compute-friendly") form used for prefill
+    (``v1/attention/backends/mla/common.py:1782-1843``): ``q [T, N, 192]`` (q_nope | rotated q_pe),
+    ``kv [rows, N * 256]`` (k_nope | v per head: the ``kv_b_proj`` output), ``k_pe [rows, 64]`` (one rotary key per
+    token, shared by the heads).  Request ``r`` owns key rows ``kv_starts[r] .. + kv_lens[r]`` and query rows
+    ``query_start_loc[r] .. [r + 1]``; causal: its queries are its last keys; otherwise every query sees every key
+    (a chunk of cached context).  Returns ``out [T, N, 128]`` and the natural-log LSE ``[T, N]``; rows of requests
+    without keys give zeros and ``-inf``."""
+    T, N, dq = q.shape
+    nope = dq - k_pe.shape[1]                       # 128 in the checkpoints; the oracle takes any split
+    vdim = kv.shape[1] // N - nope
+    out = torch.zeros(T, N, vdim, dtype=q.dtype)
+    lse = torch.full((T, N), float("-inf"))
+    kvh = kv.reshape(kv.shape[0], N, nope + vdim).float()
+    for r in range(len(kv_lens)):
+        qs, qe = int(query_start_loc[r]), int(query_start_loc[r + 1])
+        ks, L = int(kv_starts[r]), int(kv_lens[r])
+        if qe == qs or L == 0:
+            continue
+        k = torch.cat([kvh[ks:ks + L, :, :nope], k_pe[ks:ks + L].float().unsqueeze(1).expand(-1, N, -1)], -1)
+        v = kvh[ks:ks + L, :, nope:]
+        s = torch.einsum("qnd,knd->nqk", q[qs:qe].float(), k) * scale
+        if causal:
+            pos = (L - (qe - qs)) + torch.arange(qe - qs)
+            s = s.masked_fill(torch.arange(L)[None, None, :] > pos[None, :, None], float("-inf"))
+        l = torch.logsumexp(s, -1)                                   # [N, q]
+        p = torch.exp(s - l.unsqueeze(-1))
+        out[qs:qe] = torch.einsum("nqk,knd->qnd", p, v).to(q.dtype)
+        lse[qs:qe] = l.t()
+    return out, lse
+
+
 def mla_decode(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank: int = 512,
                return_lse: bool = False):
     """Weight-absorbed MQA decode (``flash_mla_with_kvcache``, ``ops/attention/flashmla.py:61-128``).
