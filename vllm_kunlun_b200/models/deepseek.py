@@ -5,10 +5,11 @@ sigmoid group routing ``:149-308``, the sparse-attention indexer ``:475-788``, M
 weight loading (``fused_qkv_a_proj``, expert mapping, MTP layers skipped) ``:1285-1413`` - and the MLA
 backends ``v1/attention/backends/mla/{common,flashmla,flashmla_sparse}.py``.
 
-Attention here always runs in the weight-absorbed form over the latent cache
-(``q_nope . W_UK`` -> 576-d MQA -> ``. W_UV``), for decode, speculative verify and prefill alike; the
-cache row is ``[kv_c (512) | k_pe (64)]``.  With ``index_topk > 0`` (V3.2) a lightning indexer
-selects the top-k context tokens per query and attention is restricted to them.
+Decode, speculative verify and short prefill rows run in the weight-absorbed form over the latent cache
+(``q_nope . W_UK`` -> 576-d MQA -> ``. W_UV``); requests with at least ``PREFILL_MIN_QUERY`` new tokens run in the
+up-projected 192 / 128 form (``kv_b_proj`` applied to the keys, cached context read chunk by chunk through a bounded
+workspace and merged by log-sum-exp).  The cache row is ``[kv_c (512) | k_pe (64)]``.  With ``index_topk > 0``
+(V3.2) a lightning indexer selects the top-k context tokens per query and attention is restricted to them.
 """
 from __future__ import annotations
 
