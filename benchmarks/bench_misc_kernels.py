@@ -110,13 +110,16 @@ def case_lora(small):
     x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
     A = torch.randn(L, r, K, device="cuda").to(torch.bfloat16)
     Bm = torch.randn(L, N, r, device="cuda").to(torch.bfloat16)
-    ids = torch.randint(0, L, (T,), device="cuda", dtype=torch.int32)
     out = torch.zeros(T, N, device="cuda", dtype=torch.bfloat16)
-    sec = timeit(lambda: ops.lora_shrink(x, A, ids, 1.0))
-    report("lora_shrink_kernel", sec, T * K * 2 + T * r * 4, f"T={T} K={K} r={r}")
-    h = ops.lora_shrink(x, A, ids, 1.0)
-    sec = timeit(lambda: ops.lora_expand(h, Bm, ids, out, 0, True))
-    report("lora_expand_kernel", sec, 2 * T * N * 2 + T * r * 4, f"T={T} N={N} r={r}")
+    # prefill: runs of 512 tokens per adapter; decode-like: an adapter drawn per token
+    patterns = (("segments of 512", (torch.arange(T, device="cuda") // 512 % L).int()),
+                ("adapter per token", torch.randint(0, L, (T,), device="cuda", dtype=torch.int32)))
+    for name, ids in patterns:
+        sec = timeit(lambda: ops.lora_shrink(x, A, ids, 1.0))
+        report("lora_shrink_kernel", sec, T * K * 2 + T * r * 4, f"T={T} K={K} r={r}, {name}")
+        h = ops.lora_shrink(x, A, ids, 1.0)
+        sec = timeit(lambda: ops.lora_expand(h, Bm, ids, out, 0, True))
+        report("lora_expand_kernel", sec, 2 * T * N * 2 + T * r * 4, f"T={T} N={N} r={r}, {name}")
 
 
 def case_gemm_splits(small):

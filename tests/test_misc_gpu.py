@@ -151,21 +151,31 @@ def test_gated_delta_rule_varlen(Dk, Dv, Hk, Hv):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_lora_shrink_expand(dtype):
+@pytest.mark.parametrize("pattern", ["random", "segments"])
+@pytest.mark.parametrize("N,offset,r", [(640, 128, 16), (333, 5, 8), (1030, 0, 12)])
+def test_lora_shrink_expand(dtype, pattern, N, offset, r):
+    """Token-tiled shrink / expand kernels vs the oracle: tiles whose tokens share an adapter (prefill segments), tiles
+    with several adapters and base-model rows (-1), whole tiles of base-model rows, a token count off the tile sizes,
+    odd column counts / offsets (no paired 4-byte stores), ranks that are not a multiple of the vector width,
+    accumulate and overwrite."""
     torch.manual_seed(6)
-    T, K, N, r, L = 37, 1024, 640, 16, 3
+    T, K, L = 77, 1024, 3
     x = torch.randn(T, K).to(dtype)
     A = (torch.randn(L, r, K) * 0.05).to(dtype)
     Bm = (torch.randn(L, N, r) * 0.05).to(dtype)
-    ids = torch.randint(-1, L, (T,), dtype=torch.int32)
+    if pattern == "random":
+        ids = torch.randint(-1, L, (T,), dtype=torch.int32)
+    else:   # runs of one adapter: 20 tokens of adapter 1, 20 base-model rows, 30 of adapter 0, 7 of adapter 2
+        ids = torch.tensor([1] * 20 + [-1] * 20 + [0] * 30 + [2] * 7, dtype=torch.int32)
     h_ref = ref.bgmv_shrink(x, A, ids, 0.5)
     h = ops.lora_shrink(x.to(DEV), A.to(DEV), ids.to(DEV), 0.5)
     torch.testing.assert_close(h.cpu(), h_ref, atol=2e-3, rtol=2e-3)
-    out0 = torch.randn(T, N + 128).to(dtype)
-    want = ref.bgmv_expand(h_ref, Bm, ids, out0.clone(), offset=128, add=True)
-    got = ops.lora_expand(h, Bm.to(DEV), ids.to(DEV), out0.to(DEV), offset=128, add=True)
     tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-4, rtol=1e-4)
-    torch.testing.assert_close(got.cpu().float(), want.float(), **tol)
+    for add in (True, False):
+        out0 = torch.randn(T, N + offset + 3).to(dtype)
+        want = ref.bgmv_expand(h_ref, Bm, ids, out0.clone(), offset=offset, add=add)
+        got = ops.lora_expand(h, Bm.to(DEV), ids.to(DEV), out0.to(DEV), offset=offset, add=add)
+        torch.testing.assert_close(got.cpu().float(), want.float(), **tol)
 
 
 def test_mtp_concat_norm_and_sigmoid_gate():

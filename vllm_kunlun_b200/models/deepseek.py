@@ -153,7 +153,7 @@ class MLAAttention(nn.Module):
     # ------------------------------------------------------------------ prefill in the up-projected form
     PREFILL_MIN_QUERY = 64            # requests with at least this many new tokens leave the absorbed form
     PREFILL_CTX_BYTES = 256 << 20     # bound of the up-projected context workspace (k_nope | v rows), bytes
-    PREFILL_FORM = None               # None: on CUDA only; True / False force it (tests)
+    PREFILL_FORM = None               # None: on CUDA unless B200_MLA_PREFILL_FORM=0; True / False force it (tests)
 
     def _prefill_plan(self, md, kv_cache, on_cuda: bool):
         """Which requests of this step take the up-projected form, and the chunks their cached context is read in.
@@ -166,7 +166,11 @@ class MLAAttention(nn.Module):
         if "mla_prefill_plan" in md.extras:
             return md.extras["mla_prefill_plan"]
         plan = None
-        enabled = on_cuda if self.PREFILL_FORM is None else self.PREFILL_FORM
+        if self.PREFILL_FORM is None:
+            from .. import envs
+            enabled = on_cuda and envs.B200_MLA_PREFILL_FORM
+        else:
+            enabled = self.PREFILL_FORM
         ok = (enabled and self.indexer is None and not md.is_dummy
               and ((self.nope, self.rope, self.vdim) == (128, 64, 128) or not on_cuda)   # the kernel's shape and md.max_query_len >= self.PREFILL_MIN_QUERY
               and md.seq_lens_cpu is not None and md.query_start_loc_cpu is not None
