@@ -70,6 +70,11 @@ typedef struct GemmDecodeArgs {
   const float* w_scale;    // [ceil(N/128), ceil(K/128)]
   int a_stride;
   int i8;  // signed 8-bit operands (kind::i8): a_scale [T] per token, w_scale [N] per channel; fmt = output type
+  // 4-bit weights (AWQ / GPTQ after repacking): the weight tensor map covers the packed bytes [N, K / 2] (32-byte x
+  // 128-row boxes, no swizzle); scale / zero [N, K / group] in the activation type; group a multiple of 64
+  int w4, w4_group;
+  const void* w4_scale;
+  const void* w4_zero;
   // qkv epilogue (head_dim 128): split + optional q / k RMSNorm + rotary + K / V cache write; out = q [T, Hq * 128]
   int qk_on, qk_hq, qk_hkv, qk_neox, qk_gemma, qk_block_size;
   float qk_eps;
@@ -104,6 +109,14 @@ int b200_grouped_gemm_launch(const GroupedGemmArgs* a, const void* tmapW, const 
 // swizzle into `out` (128 bytes).  elem_bytes = 1 or 2.
 int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
                         uint32_t box_rows, uint32_t box_cols, int elem_bytes);
+
+// Same for a plain (unswizzled) byte tensor: [rows, row_bytes] with a [box_rows, box_bytes] box; box_bytes a multiple
+// of 16.
+int b200_encode_tmap_2d_raw(void* out, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t row_stride_bytes,
+                            uint32_t box_rows, uint32_t box_bytes);
+// out [N, K] (bf16 / fp16) = (q - zero) * scale of 4-bit weights packed as [N, K / 2] (see quantization/int4.py)
+int b200_dequant_w4(void* out, const void* packed, const void* scale, const void* zero, int64_t N, int K, int group,
+                    int dtype, cudaStream_t st);
 
 // ---- elementwise ----------------------------------------------------------------------------
 int b200_rmsnorm(void* out, const void* x, void* residual, const void* w, int64_t rows, int H, float eps, int gemma,

@@ -88,6 +88,18 @@ const Tmap& get_tmap(GemmState& gs, const at::Tensor& t, int box_rows, int elem_
   return gs.cache.emplace(key, tm).first->second;
 }
 
+// Plain (unswizzled) byte tensor map with a [box_rows, box_bytes] box; cached under elem_bytes = -box_bytes.
+const Tmap& get_tmap_raw(GemmState& gs, const at::Tensor& t, int box_rows, int box_bytes) {
+  TmapKey key{t.data_ptr(), t.size(0), t.size(1), t.stride(0), box_rows, -box_bytes};
+  auto it = gs.cache.find(key);
+  if (it != gs.cache.end()) return it->second;
+  if (gs.cache.size() > 4096) gs.cache.clear();
+  Tmap tm;
+  int rc = b200_encode_tmap_2d_raw(tm.b, t.data_ptr(), t.size(0), t.size(1), t.stride(0), box_rows, box_bytes);
+  TORCH_CHECK(rc == 0, "tensor map encode failed: ", rc);
+  return gs.cache.emplace(key, tm).first->second;
+}
+
 // Collective-fusion arguments for the NEXT gemm() call (consumed by it).
 struct GemmCommState {
   bool active = false;
@@ -362,6 +374,78 @@ void gemm_decode(at::Tensor out, const at::Tensor& x, const at::Tensor& w, const
   const Tmap& tx = get_tmap(gs, x, a.bn, 2);
   check(b200_gemm_decode_launch(&a, tw.b, tx.b, stream()), "gemm_decode launch");
   gs.launches++;
+}
+
+// Decode-sized linear over 4-bit weights (AWQ / GPTQ after repacking, see quantization/int4.py::pack_w4):
+// out [T <= 32, N] = x [T, K] . W^T with W[n, k] = (q[n, k] - zero[n, k / group]) * scale[n, k / group], the packed bytes
+// streamed from HBM and de-quantised inside the kernel.  act as in gemm_decode (interleaved gate / up rows).
+void gemm_decode_w4(at::Tensor out, const at::Tensor& x, const at::Tensor& packed, const at::Tensor& scale, const at::Tensor& zero,
+                    const c10::optional<at::Tensor>& bias, int64_t group, int64_t splits, int64_t act) {
+  TORCH_CHECK(x.is_cuda() && packed.is_cuda() && out.is_cuda() && x.dim() == 2 && packed.dim() == 2 && out.dim() == 2);
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "gemm_decode_w4: bf16/fp16 activations");
+  TORCH_CHECK(packed.scalar_type() == at::kByte && packed.is_contiguous() && x.stride(1) == 1 && out.stride(1) == 1);
+  TORCH_CHECK(scale.scalar_type() == x.scalar_type() && zero.scalar_type() == x.scalar_type() && out.scalar_type() == x.scalar_type());
+  const int T = x.size(0), K = x.size(1), N = packed.size(0);
+  TORCH_CHECK(T <= 32, "gemm_decode_w4: at most 32 rows");
+  TORCH_CHECK(packed.size(1) * 2 == K && out.size(0) == T && out.size(1) == (act ? N / 2 : N));
+  TORCH_CHECK(K % 64 == 0 && group >= 64 && group % 64 == 0 && K % group == 0 && x.stride(0) % 8 == 0,
+              "gemm_decode_w4: K and the group size must be multiples of 64");
+  TORCH_CHECK(scale.is_contiguous() && zero.is_contiguous() && scale.dim() == 2 && scale.size(0) == N &&
+              scale.size(1) == K / group && zero.sizes() == scale.sizes());
+  if (act) TORCH_CHECK(N % 128 == 0 && out.stride(0) % 8 == 0, "fused gate/up activation needs whole [64 | 64] weight tiles");
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == out.scalar_type() && bias->numel() == N);
+  if (T == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(x.device());
+  GemmState& gs = gemm_state();
+  std::lock_guard<std::mutex> lk(gs.mu);
+  if (gs.num_sms == 0) {
+    gs.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    gs.ws = at::empty({16 << 20}, x.options().dtype(at::kFloat));
+    gs.counters = at::zeros({1 << 16}, x.options().dtype(at::kInt));
+    gs.status = at::zeros({1}, x.options().dtype(at::kInt));
+  }
+  GemmDecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.out = out.data_ptr(); a.bias = opt_ptr(bias); a.status = gs.status.data_ptr<int>();
+  a.T = T; a.N = N; a.K = K;
+  a.n_tiles = (N + 127) / 128;
+  a.bn = T <= 16 ? 16 : 32;
+  a.fmt = x.scalar_type() == at::kBFloat16 ? 1 : 0;
+  a.ldo = out.stride(0);
+  a.act = (int)act;
+  a.w4 = 1; a.w4_group = (int)group; a.w4_scale = scale.data_ptr(); a.w4_zero = zero.data_ptr();
+  const int total_kb = K / 64;
+  const int max_s = a.bn == 16 ? 8 : 4;
+  int S = (int)splits;
+  if (S <= 0) {
+    // the de-quantising warps of a CTA bound its throughput, so more CTAs help where 16-bit weights would already be
+    // bandwidth-bound: clusters of up to 4 may fill the SMs twice (two CTAs fit per SM), larger ones once
+    S = 1;
+    while (S * 2 <= max_s && total_kb / (S * 2) >= 8 && a.n_tiles * S * 2 <= (S * 2 <= 4 ? 2 : 1) * gs.num_sms) S *= 2;
+  }
+  S = std::max(1, std::min(S, std::min(max_s, total_kb)));
+  while (S > 1 && (S - 1) * ((total_kb + S - 1) / S) >= total_kb) --S;
+  a.S = S;
+  a.kb_per_cta = (total_kb + S - 1) / S;
+  a.ctas_per_sm = a.n_tiles * S > gs.num_sms ? 2 : 1;
+  const Tmap& tw = get_tmap_raw(gs, packed, 128, 32);
+  const Tmap& tx = get_tmap(gs, x, a.bn, 2);
+  check(b200_gemm_decode_launch(&a, tw.b, tx.b, stream()), "gemm_decode_w4 launch");
+  gs.launches++;
+}
+
+// 4-bit weights -> a 16-bit [N, K] matrix (for batches the decode kernel does not take).
+void dequant_w4(at::Tensor out, const at::Tensor& packed, const at::Tensor& scale, const at::Tensor& zero, int64_t group) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.dim() == 2 && packed.is_contiguous() && packed.scalar_type() == at::kByte);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kHalf);
+  TORCH_CHECK(scale.scalar_type() == out.scalar_type() && zero.scalar_type() == out.scalar_type());
+  const int64_t N = out.size(0);
+  const int K = out.size(1);
+  TORCH_CHECK(packed.size(0) == N && packed.size(1) * 2 == K && scale.is_contiguous() && zero.is_contiguous());
+  TORCH_CHECK(K % group == 0 && scale.numel() == N * (K / group) && zero.numel() == scale.numel());
+  c10::cuda::CUDAGuard guard(out.device());
+  check(b200_dequant_w4(out.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(), N, K, (int)group,
+                        dtype_code(out), stream()), "dequant_w4");
 }
 
 // qkv projection of a decode-sized batch with split + optional q / k RMSNorm + rotary + K / V cache write in the GEMM
@@ -1371,6 +1455,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_decode", &gemm_decode);
   m.def("gemm_decode_fp8", &gemm_decode_fp8);
   m.def("gemm_decode_qkv", &gemm_decode_qkv);
+  m.def("gemm_decode_w4", &gemm_decode_w4);
+  m.def("dequant_w4", &dequant_w4);
   m.def("gemm_int8", &gemm_int8);
   m.def("quant_int8_token", &quant_int8_token);
   m.def("set_gemm_decode_comm", &set_gemm_decode_comm);

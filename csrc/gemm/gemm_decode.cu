@@ -37,6 +37,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
+constexpr int kThreadsW4 = 320;   // 4-bit weights: four more warps de-quantise
 constexpr int kStageBytesA = BM * BK * 2;
 constexpr int kTileStride = BM + 8;  // staging row (elements of OutT)
 
@@ -92,6 +93,48 @@ struct QkvEpi {
 
 constexpr int kAccBufs = 4;  // fp8: accumulator buffers handed to the epilogue one k-block at a time
 
+// 4-bit weights: the TMA ring then carries, per k-block, the activation tile and the PACKED weight tile (128 rows x
+// 32 bytes) - 6 or 8 KB a stage, so the ring is deep enough to keep HBM busy - and the 16-bit A tiles live in a ring
+// of their own (kW4Tiles x 16 KB): the four epilogue warps (one thread per weight row), idle during the main loop
+// otherwise, turn each packed tile into a 128-byte-swizzled A tile and hand it to the MMA issuer through `deq_bar`;
+// the tensor core's commit frees the A tile (`afree_bar`) and the ring stage.
+constexpr int kPackedBytes = BM * (BK / 2);
+constexpr int kW4Tiles = 3;
+struct W4 {
+  const void* scale;   // [N, K / group], activation type
+  const void* zero;    // [N, K / group], activation type (integer-valued)
+  int group, on;
+};
+
+// Eight 4-bit values of a packed word -> four pairs of 16-bit floats (q - zero) * scale.  The nibbles of a word are
+// stored in the order 0, 2, 4, 6, 1, 3, 5, 7 of its eight consecutive k positions, so that `(w >> 4 j) & 0x000F000F`
+// is the pair (2 j, 2 j + 1); or-ing the exponent of 128 (bf16) / 1024 (fp16) makes each half the exact value
+// 128 + q / 1024 + q, and one subtraction of (128 + zero) and one multiplication finish the job - the same value
+// as rounding (q - zero) * scale once from fp32.
+template <typename OutT> struct W4Cvt;
+template <> struct W4Cvt<__nv_bfloat16> {
+  using V2 = __nv_bfloat162;
+  static constexpr uint32_t kMagic = 0x43004300u;
+  static constexpr float kBase = 128.f;
+};
+template <> struct W4Cvt<__half> {
+  using V2 = __half2;
+  static constexpr uint32_t kMagic = 0x64006400u;
+  static constexpr float kBase = 1024.f;
+};
+template <typename OutT>
+__device__ __forceinline__ uint4 w4_convert(uint32_t w, typename W4Cvt<OutT>::V2 off, typename W4Cvt<OutT>::V2 sc) {
+  using V2 = typename W4Cvt<OutT>::V2;
+  uint32_t r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t t = ((w >> (4 * j)) & 0x000F000Fu) | W4Cvt<OutT>::kMagic;
+    V2 v = __hmul2(__hsub2(*reinterpret_cast<V2*>(&t), off), sc);
+    r[j] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 template <int BN>
 struct Cfg {
   static constexpr int kStageBytes = kStageBytesA + BN * BK * 2;
@@ -107,29 +150,36 @@ struct Cfg {
 // epilogue warps multiply it by a_scale[kb][t] * w_scale[nt][kb] while adding it into fp32 registers, overlapped
 // with the next k-block's MMAs.
 template <int BN, typename OutT, bool kFp8>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreadsW4)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    OutT* __restrict__ out, const OutT* __restrict__ bias, int* __restrict__ status, int T, int N, int K,
                    int kb_per_cta, int fmt, int ldo, int num_stages, int S, int act, int l2_prefetch,
                    const float* __restrict__ a_scale, const float* __restrict__ w_scale, int a_stride,
-                   const __grid_constant__ Comm cm, const __grid_constant__ QkvEpi qk) {
+                   const __grid_constant__ Comm cm, const __grid_constant__ QkvEpi qk, const __grid_constant__ W4 w4p) {
   using C = Cfg<BN>;
   constexpr int BKE8 = 128;             // K elements per k-block of 8-bit operands (still one 128-byte swizzle row)
   // fmt == 2 (non-fp8 instantiation): signed 8-bit operands on kind::i8 with per-token activation scales
   // (a_scale [T]) and per-channel weight scales (w_scale [N]) applied by the final epilogue
   const bool i8 = !kFp8 && fmt == 2;
   const int BKE = (kFp8 || i8) ? BKE8 : BK;  // K elements per k-block
+  const bool w4 = !kFp8 && w4p.on != 0;      // 4-bit weights, de-quantised into the stage's A tile by the epilogue warps
+  const int stage_bytes = w4 ? BN * BK * 2 + kPackedBytes : C::kStageBytes;   // 4-bit: [x tile | packed weight tile]
+  const uint32_t stage_tx = (uint32_t)stage_bytes;
   constexpr int kCols = kFp8 ? C::kTmemColsFp8 : C::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + num_stages * C::kStageBytes);
+  uint8_t* smem_al = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* a_ring = smem_al;                                             // 4-bit: kW4Tiles de-quantised A tiles
+  uint8_t* smem = smem_al + (w4 ? kW4Tiles * kStageBytesA : 0);          // the TMA ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + num_stages * stage_bytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + num_stages;
   uint64_t* tmem_full = bars + 2 * num_stages;
   uint64_t* red_bar = tmem_full + 1;
   uint64_t* acc_full = red_bar + 1;             // [kAccBufs] (fp8)
   uint64_t* acc_empty = acc_full + kAccBufs;    // [kAccBufs] (fp8)
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccBufs);
+  uint64_t* deq_bar = acc_empty + kAccBufs;     // [kW4Tiles] (4-bit weights): 4 arrivals, one per epilogue warp
+  uint64_t* afree_bar = deq_bar + 4;            // [kW4Tiles] the MMAs that read the A tile are complete
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(deq_bar + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* ep_ok_slot = reinterpret_cast<volatile int*>(tmem_base_slot + 2);  // [2]
   uint8_t* after = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tmem_base_slot + 4) + 15) & ~uintptr_t(15));
@@ -152,6 +202,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
+    for (int b = 0; b < kW4Tiles; ++b) { mbar_init(&deq_bar[b], 4); mbar_init(&afree_bar[b], 1); }
     mbar_init(tmem_full, 1);
     mbar_init(red_bar, (uint32_t)(S > 1 ? (S - 1) * 4 : 1));
     for (int b = 0; b < kAccBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
@@ -173,6 +224,72 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   }
   const uint32_t tmem_base = *tmem_base_slot;
 
+  // ---- 4-bit weights: a group of four warps (one thread per weight row) turns the packed tile of every ndg-th k-block
+  // into a 16-bit A tile (128-byte swizzle).  Group 0 = the epilogue warps, group 1 = warps 6 - 9 when the block was
+  // launched with 320 threads; the groups alternate over the k-blocks.
+  const int ndg = (int)(blockDim.x - 64) / 128;
+  auto dequant_rows = [&](int grp, int n_local) {
+    using V2 = typename W4Cvt<OutT>::V2;
+    const int row = nt * BM + n_local;
+    const int groups = K / w4p.group;                         // scale / zero row length
+    const OutT* sc_row = reinterpret_cast<const OutT*>(w4p.scale) + (size_t)row * groups;
+    const OutT* zr_row = reinterpret_cast<const OutT*>(w4p.zero) + (size_t)row * groups;
+    const bool row_in = row < N;
+    const int kpg = w4p.group / BK;                           // k-blocks per quantisation group
+    const int kshift = (kpg & (kpg - 1)) == 0 ? __ffs(kpg) - 1 : -1;
+    auto group_of = [&](int kb) { return kshift >= 0 ? (kb >> kshift) : kb / kpg; };
+    uint32_t coff[8];                                         // swizzled position of 16-byte chunk j of this row
+#pragma unroll
+    for (int j = 0; j < 8; ++j) coff[j] = (uint32_t)((j ^ (n_local & 7)) << 4);
+    const uint8_t* pk_base = smem + BN * BK * 2 + n_local * (BK / 2);
+    uint8_t* a_base = a_ring + n_local * 128;
+    int stage = grp % num_stages, slot = grp % kW4Tiles;
+    uint32_t phase = (uint32_t)((grp / num_stages) & 1), sph = (uint32_t)((grp / kW4Tiles) & 1);
+    // group parameters are fetched one step ahead: no dependent global load in front of the conversion
+    int g_cur = -1, g_nxt = group_of(kb0 + grp);
+    OutT s_nxt = from_float<OutT>(0.f), z_nxt = from_float<OutT>(0.f);
+    if (row_in && grp < nkb) { s_nxt = sc_row[g_nxt]; z_nxt = zr_row[g_nxt]; }
+    V2 off = V2(s_nxt, s_nxt), sc = off;
+    for (int i = grp; i < nkb; i += ndg) {
+      const int gi = g_nxt;
+      if (gi != g_cur) {
+        g_cur = gi;
+        const OutT o1 = from_float<OutT>(W4Cvt<OutT>::kBase + to_float<OutT>(z_nxt));
+        sc = V2(s_nxt, s_nxt);
+        off = V2(o1, o1);
+      }
+      if (i + ndg < nkb) {
+        g_nxt = group_of(kb0 + i + ndg);
+        if (g_nxt != gi && row_in) { s_nxt = sc_row[g_nxt]; z_nxt = zr_row[g_nxt]; }
+      }
+      // every warp waits by itself (lane 0 with the bound, the others once the phase is known to be complete)
+      int ok_w = 1;
+      if (lane == 0) {
+        ok_w = (i < kW4Tiles || wait_or_abort(&afree_bar[slot], sph ^ 1u, ab, 130)) &&
+               wait_or_abort(&full_bar[stage], phase, ab, 128);
+      }
+      ok_w = __shfl_sync(0xffffffffu, ok_w, 0);
+      if (!ok_w) break;
+      while (!mbar_try_wait(&full_bar[stage], phase)) {}
+      if (i >= kW4Tiles) { while (!mbar_try_wait(&afree_bar[slot], sph ^ 1u)) {} }
+      tc_fence_after_sync();
+      const uint4* pk = reinterpret_cast<const uint4*>(pk_base + stage * stage_bytes);
+      const uint4 p0 = pk[0], p1 = pk[1];
+      const uint32_t wds[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+      uint8_t* arow = a_base + slot * kStageBytesA;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)   // word j = k positions 8 j .. 8 j + 7 = 16-byte chunk j of the row
+        *reinterpret_cast<uint4*>(arow + coff[j]) = w4_convert<OutT>(wds[j], off, sc);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&deq_bar[slot]);
+      stage += ndg;
+      if (stage >= num_stages) { stage -= num_stages; phase ^= 1u; }
+      slot += ndg;
+      if (slot >= kW4Tiles) { slot -= kW4Tiles; sph ^= 1u; }
+    }
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
@@ -180,24 +297,26 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int pre = 0;
       // weights do not depend on the previous kernel: fill the ring (and pull what follows into L2) first
       for (; pre < num_stages && pre < nkb; ++pre) {
-        mbar_expect_tx(&full_bar[pre], C::kStageBytes);
-        tma_load_2d_hint(smem + pre * C::kStageBytes, &tmW, &full_bar[pre], (kb0 + pre) * BKE, nt * BM, pol_w);
+        mbar_expect_tx(&full_bar[pre], stage_tx);
+        if (w4) tma_load_2d_hint(smem + pre * stage_bytes + BN * BK * 2, &tmW, &full_bar[pre], (kb0 + pre) * (BK / 2), nt * BM, pol_w);
+        else tma_load_2d_hint(smem + pre * stage_bytes, &tmW, &full_bar[pre], (kb0 + pre) * BKE, nt * BM, pol_w);
       }
-      for (int i = 0; i < l2_prefetch && pre + i < nkb; ++i) tma_prefetch_l2_2d(&tmW, (kb0 + pre + i) * BKE, nt * BM);
+      for (int i = 0; i < l2_prefetch && pre + i < nkb && !w4; ++i) tma_prefetch_l2_2d(&tmW, (kb0 + pre + i) * BKE, nt * BM);
       griddep_wait();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int issued = 0;
       for (int i = 0; i < nkb; ++i) {
-        uint8_t* sa = smem + stage * C::kStageBytes;
-        uint8_t* sb = sa + kStageBytesA;
+        uint8_t* sa = smem + stage * stage_bytes;
+        uint8_t* sb = w4 ? sa : sa + kStageBytesA;
         if (i < pre) {
           tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BKE, 0);
         } else {
           if (!wait_or_abort(&empty_bar[stage], phase ^ 1, ab, 121)) { ok = false; break; }
-          mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d_hint(sa, &tmW, &full_bar[stage], (kb0 + i) * BKE, nt * BM, pol_w);
+          mbar_expect_tx(&full_bar[stage], stage_tx);
+          if (w4) tma_load_2d_hint(sa + BN * BK * 2, &tmW, &full_bar[stage], (kb0 + i) * (BK / 2), nt * BM, pol_w);
+          else tma_load_2d_hint(sa, &tmW, &full_bar[stage], (kb0 + i) * BKE, nt * BM, pol_w);
           tma_load_2d(sb, &tmX, &full_bar[stage], (kb0 + i) * BKE, 0);
         }
         ++issued;
@@ -225,14 +344,19 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       bool ok = true;
       for (int i = 0; i < nkb; ++i) {
         if (!wait_or_abort(&full_bar[stage], phase, ab, 123)) { ok = false; break; }
+        if (w4 && !wait_or_abort(&deq_bar[i % kW4Tiles], (i / kW4Tiles) & 1, ab, 129)) { ok = false; break; }
         const int ab_buf = i % kAccBufs;
         if (kFp8 && i >= kAccBufs && !wait_or_abort(&acc_empty[ab_buf], ((i / kAccBufs) - 1) & 1, ab, 126)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+        uint32_t sa = smem_u32(smem + stage * stage_bytes);
         uint32_t sb = sa + kStageBytesA;
+        if (w4) {
+          sb = sa;
+          sa = smem_u32(a_ring + (i % kW4Tiles) * kStageBytesA);
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row: 16 16-bit or 32 8-bit elements each
           uint64_t da = umma_desc_k_sw128(sa + k * 32);
@@ -242,17 +366,23 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           else umma_f16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
+        if (w4) umma_commit(&afree_bar[i % kW4Tiles]);
         if (kFp8) umma_commit(&acc_full[ab_buf]);
         if (++stage == num_stages) { stage = 0; phase ^= 1; }
       }
       if (ok && !kFp8) umma_commit(tmem_full);
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ second de-quantising group (4-bit weights)
+    griddep_wait();
+    if (w4) dequant_rows(1, (warp - 6) * 32 + lane);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;
     const int ep_tid = (warp - 2) * 32 + lane;
     const int n_local = quarter * 32 + lane;
     griddep_wait();
+    if (w4) dequant_rows(0, n_local);
     float acc[BN];
     bool acc_ok = true;
     if (kFp8) {
@@ -496,6 +626,8 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   using C = Cfg<BN>;
   auto kern = gemm_decode_kernel<BN, OutT, kFp8>;
   const int fixed = 1024 /*align*/ + 512 /*barriers*/ + (a.S - 1) * C::kSlotBytes + C::kTileBytes + 64;
+  const int stage_bytes = a.w4 ? BN * BK * 2 + kPackedBytes : C::kStageBytes;
+  const int a_ring = a.w4 ? kW4Tiles * kStageBytesA : 0;
   {
     cudaError_t e = ensure_dynamic_smem((const void*)kern, 220 * 1024);
     if (e != cudaSuccess) return e;
@@ -503,12 +635,12 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   const int total_kb = (a.K + ((kFp8 || a.i8) ? 128 : BK) - 1) / ((kFp8 || a.i8) ? 128 : BK);
   const int nkb = a.kb_per_cta;
   // shared memory per CTA: about half an SM when two CTAs should be resident together
-  int budget = (a.ctas_per_sm >= 2 ? 112 * 1024 : 216 * 1024) - fixed;
-  int stages = a.stages > 0 ? a.stages : budget / C::kStageBytes;
+  int budget = (a.ctas_per_sm >= 2 ? 112 * 1024 : 216 * 1024) - fixed - a_ring;
+  int stages = a.stages > 0 ? a.stages : budget / stage_bytes;
   if (stages > nkb) stages = nkb;
-  if (stages > 12) stages = 12;
+  if (stages > (a.w4 ? 16 : 12)) stages = a.w4 ? 16 : 12;
   if (stages < 2) stages = 2;
-  const size_t smem = (size_t)stages * C::kStageBytes + fixed;
+  const size_t smem = (size_t)stages * stage_bytes + fixed + a_ring;
   (void)total_kb;
   Comm cm;
   for (int i = 0; i < 8; ++i) cm.ll_bufs[i] = a.ll_bufs[i];
@@ -519,9 +651,11 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   qk.kv_cache = a.qk_kv_cache; qk.slots = a.qk_slots; qk.num_blocks = a.qk_num_blocks; qk.max_pos = a.qk_max_pos;
   qk.eps = a.qk_eps; qk.on = a.qk_on; qk.Hq = a.qk_hq; qk.Hkv = a.qk_hkv; qk.neox = a.qk_neox; qk.gemma = a.qk_gemma;
   qk.block_size = a.qk_block_size;
+  W4 w4p;
+  w4p.scale = a.w4_scale; w4p.zero = a.w4_zero; w4p.group = a.w4_group; w4p.on = a.w4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(a.n_tiles * a.S);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(a.w4 ? kThreadsW4 : kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -535,7 +669,7 @@ static cudaError_t launch(const GemmDecodeArgs& a, const CUtensorMap& tmW, const
   cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, (OutT*)a.out, (const OutT*)a.bias, a.status, a.T, a.N, a.K,
                             a.kb_per_cta, a.i8 ? 2 : a.fmt, a.ldo, stages, a.S, a.act, gemm_l2_prefetch(), a.a_scale, a.w_scale,
-                            a.a_stride, cm, qk);
+                            a.a_stride, cm, qk, w4p);
 }
 
 }  // namespace dec
@@ -551,6 +685,9 @@ extern "C" int b200_gemm_decode_launch(const GemmDecodeArgs* a, const void* tmW,
   if (a->bn == 32 && a->S > 4) return (int)cudaErrorInvalidValue;
   if (a->fp8 && (a->act != 0 || a->a_scale == nullptr || a->w_scale == nullptr)) return (int)cudaErrorInvalidValue;
   if (a->i8 && (a->fp8 || a->act != 0 || a->ar_on || a->qk_on || a->a_scale == nullptr || a->w_scale == nullptr))
+    return (int)cudaErrorInvalidValue;
+  if (a->w4 && (a->fp8 || a->i8 || a->K % 64 != 0 || a->w4_group < 64 || a->w4_group % 64 != 0 || a->K % a->w4_group != 0 ||
+                a->w4_scale == nullptr || a->w4_zero == nullptr))
     return (int)cudaErrorInvalidValue;
   if (a->qk_on && (a->fp8 || a->act != 0 || a->ar_on || a->N != (a->qk_hq + 2 * a->qk_hkv) * 128 ||
                    a->qk_positions == nullptr || a->qk_cos_sin == nullptr))

@@ -44,6 +44,25 @@ extern "C" int b200_encode_tmap_2d(void* out, const void* base, uint64_t rows, u
   return 0;
 }
 
+extern "C" int b200_encode_tmap_2d_raw(void* out, const void* base, uint64_t rows, uint64_t row_bytes,
+                                       uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_bytes) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return 1001;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15)) return 1002;
+  if (box_bytes == 0 || (box_bytes & 15) || box_bytes > 256 || box_rows > 256) return 1003;
+  CUtensorMap tm;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 2000 + (int)r;
+  memcpy(out, &tm, sizeof(tm));
+  return 0;
+}
+
 // ---- PDL switch (see common/launch.cuh) ----
 #include <stdlib.h>
 

@@ -493,3 +493,50 @@ def test_prefill_attention_umma(Hq, Hkv, bs, dtype):
             sc = torch.einsum("hd,nhd->hn", qr, k[:n].repeat_interleave(g, 1)) * scale
             want.append(torch.logsumexp(sc, -1))
     torch.testing.assert_close(lse.cpu(), torch.stack(want), atol=2e-2, rtol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,N,K,group,splits", [(1, 256, 512, 128, 0), (16, 300, 1024, 64, 0), (16, 4096, 4096, 128, 0),
+                                                (32, 1024, 2048, 128, 0), (5, 384, 4096, 128, 4), (16, 128, 4096, 4096, 8),
+                                                (16, 6144, 4096, 128, 1)])
+def test_gemm_decode_w4(dtype, T, N, K, group, splits):
+    """Decode GEMM over 4-bit weights (packed bytes streamed by TMA, de-quantised by the epilogue warps into the
+    swizzled A tile, then tcgen05): against the fp32 oracle over the de-quantised weight, and - with the same cluster
+    size - bit for bit against the 16-bit decode GEMM over that weight (the kernel computes (q - zero) * scale with one
+    rounding, as the oracle does).  Covers a partial last weight tile, groups of 64 / 128 / K, bias, both 16-bit types."""
+    from vllm_kunlun_b200.ops import _ext
+    from vllm_kunlun_b200.ops.gemm_cuda import check_status
+    from vllm_kunlun_b200.quantization.int4 import dequant_w4, pack_w4
+    g = torch.Generator().manual_seed(T + N + K + group)
+    q = torch.randint(0, 16, (N, K), generator=g)
+    zero = torch.randint(0, 17, (N, K // group), generator=g).to(dtype)          # GPTQ's +1 convention reaches 16
+    scale = (torch.rand(N, K // group, generator=g) * 0.02 + 0.005).to(dtype)
+    packed = pack_w4(q)
+    w = dequant_w4(packed, scale, zero, group)                                    # [N, K] in dtype
+    x = torch.randn(T, K, generator=g).to(dtype)
+    bias = torch.randn(N, generator=g).to(dtype)
+    C = _ext.C()
+    pd, sd, zd, xd, bd = packed.to(DEV), scale.to(DEV), zero.to(DEV), x.to(DEV), bias.to(DEV)
+    out = torch.empty(T, N, dtype=dtype, device=DEV)
+    C.gemm_decode_w4(out, xd, pd, sd, zd, bd, group, splits, 0)
+    check_status()
+    want = x.float() @ w.float().T + bias.float()
+    _close(out, want, 0.02 * math.sqrt(K / 512), 0.02, f"w4 decode {T}x{N}x{K} g{group}")
+    # the de-quantising kernel for large batches: exact
+    wd = torch.empty(N, K, dtype=dtype, device=DEV)
+    C.dequant_w4(wd, pd, sd, zd, group)
+    assert torch.equal(wd.cpu(), w)
+    if splits > 0:   # same cluster size -> same sequence of MMAs and the same reduction order
+        ref = torch.empty(T, N, dtype=dtype, device=DEV)
+        C.gemm_decode(ref, xd, wd, bd, splits, 0, 0, 0)
+        check_status()
+        assert torch.equal(out, ref)
+    # the op wrapper: decode-sized and larger batches
+    y = ops.w4_linear(xd, pd, sd, zd, group, bd)
+    if splits == 0:
+        assert torch.equal(y, out)
+    else:   # the wrapper lets the library choose the cluster size: another reduction order
+        _close(y, want, 0.02 * math.sqrt(K / 512), 0.02, "w4 wrapper")
+    xl = torch.randn(70, K, generator=g).to(dtype)
+    yl = ops.w4_linear(xl.to(DEV), pd, sd, zd, group, bd)
+    _close(yl, xl.float() @ w.float().T + bias.float(), 0.02 * math.sqrt(K / 512), 0.02, "w4 large batch")

@@ -142,6 +142,9 @@ class MLAAttention(nn.Module):
         """Absorb ``kv_b_proj`` (``mla/common.py:1423-1555``): ``W_UK [N, nope, rank]``, ``W_UV [N, rank, vdim]``."""
         m = self.kv_b_proj
         w = m.weight
+        if w is None and getattr(m, "w4_packed", None) is not None:    # 4-bit checkpoint: the absorbed factors are 16-bit
+            from ..quantization.int4 import dequant_w4
+            w = dequant_w4(m.w4_packed.cpu(), m.w4_scale.cpu(), m.w4_zero.cpu(), m.w4_group).to(m.w4_packed.device)
         if w.dtype == torch.float8_e4m3fn:
             w = ops.reference_basic.dequant_fp8_block(w.cpu(), m.weight_scale_inv.cpu(), m.method.block).to(w.device)
         w = w.to(self._dtype).view(self.num_heads, self.nope + self.vdim, self.rank)

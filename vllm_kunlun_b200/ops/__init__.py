@@ -297,6 +297,33 @@ def fp8_linear(x, w_fp8, w_scale_inv, bias=None, block=(128, 128), out_dtype=tor
     return y.to(out_dtype if out_dtype != torch.float8_e4m3fn else torch.bfloat16).reshape(*lead, -1)
 
 
+W4_DECODE_ROWS = 32   # batches up to this many rows stream the packed weights through the decode GEMM
+
+
+def w4_linear(x, packed, scale, zero, group: int, bias=None):
+    """Linear over 4-bit weights in the packed layout of ``quantization/int4.py`` (``packed [N, K / 2]`` uint8,
+    ``scale`` / ``zero [N, K / group]``): ``y = x @ ((q - zero) * scale).T (+ b)``.  CUDA: at most 32 rows run on the
+    decode GEMM, which streams the packed bytes and de-quantises in the kernel; larger batches de-quantise into a
+    temporary 16-bit matrix and run the 16-bit GEMM (``quantization/awq.py:124-168`` of the reference)."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x.is_cuda:
+        N, K = packed.shape[0], packed.shape[1] * 2
+        if x2.dtype != scale.dtype:
+            x2 = x2.to(scale.dtype)
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        if 0 < x2.shape[0] <= W4_DECODE_ROWS:
+            out = torch.empty(x2.shape[0], N, dtype=x2.dtype, device=x2.device)
+            _c().gemm_decode_w4(out, x2, packed, scale, zero, bias, int(group), 0, 0)
+            return out.reshape(*lead, N)
+        w = torch.empty(N, K, dtype=scale.dtype, device=x2.device)
+        _c().dequant_w4(w, packed, scale, zero, int(group))
+        return linear(x2, w, bias).reshape(*lead, N)
+    from ..quantization.int4 import dequant_w4
+    return _rb.linear(x2, dequant_w4(packed, scale, zero, group), bias).reshape(*lead, -1)
+
+
 def int8_linear(x, w_q, w_scale, bias=None, input_scale=None, out_dtype=torch.bfloat16):
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
