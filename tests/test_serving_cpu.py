@@ -25,18 +25,24 @@ def test_qwen3_reasoning_whole_and_streaming():
     assert (r, c) == ("reason", "answer")
 
 
+_WEATHER_TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+    "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"},
+                                     "opts": {"type": "object"}, "note": {"type": ["string", "null"]},
+                                     "unit": {"enum": ["C", "F"]}, "when": {"anyOf": [{"type": "integer"}, {"type": "string"}]},
+                                     "tags": {"items": {"type": "string"}}, "flag": {"type": "boolean"}}}}}]
+
+
 def test_glm47_tool_parser():
-    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
-        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"},
-                                         "opts": {"type": "object"}}}}}]
+    tools = _WEATHER_TOOLS
     out = ("I will call.<tool_call>get_weather\n<arg_key>city</arg_key><arg_value>Paris</arg_value>"
-           "<arg_key>days</arg_key><arg_value>3</arg_value><arg_key>opts</arg_key>"
+           "<arg_key>days</arg_key><arg_value>3</arg_value>\n<arg_key>opts</arg_key>"
            "<arg_value>{\"units\": \"C\"}</arg_value></tool_call>")
     p = Glm47ToolParser()
     ex = p.extract_tool_calls(out, tools)
     assert ex.tools_called and ex.content == "I will call."
     assert ex.tool_calls[0].name == "get_weather"
     assert json.loads(ex.tool_calls[0].arguments) == {"city": "Paris", "days": 3, "opts": {"units": "C"}}
+    assert ex.tool_calls[0].arguments == json.dumps({"city": "Paris", "days": 3, "opts": {"units": "C"}})
     assert not p.extract_tool_calls("no tools here").tools_called
     # streaming: name first, then argument text that concatenates to the final JSON
     sp = Glm47ToolParser()
@@ -48,6 +54,88 @@ def test_glm47_tool_parser():
     for d in sp.extract_tool_calls_streaming(out, tools):
         args += d.get("arguments", "")
     assert name == "get_weather" and json.loads(args) == {"city": "Paris", "days": 3, "opts": {"units": "C"}}
+
+
+def test_glm47_schema_types():
+    from vllm_kunlun_b200.entrypoints.tool_parsers.glm47 import argument_type, convert_value, infer_schema_type
+    t = _WEATHER_TOOLS
+    assert [argument_type(t, "get_weather", k) for k in ("city", "days", "opts", "note", "unit", "when", "tags", "flag")] == \
+        ["string", "integer", "object", "string", "string", "string", "array", "boolean"]
+    assert argument_type(t, "get_weather", "missing") is None and argument_type(t, "other", "city") is None
+    assert infer_schema_type({"anyOf": [{"type": "integer"}, {"type": "null"}]}) == "integer"
+    assert infer_schema_type({"enum": [1, 2]}) == "integer" and infer_schema_type({"enum": [1, "a"]}) == "string"
+    assert infer_schema_type({"allOf": [{"type": "string"}, {"type": "object"}]}) == "object"
+    assert infer_schema_type({"properties": {}}) == "object" and infer_schema_type({}) is None
+    assert convert_value("3", "integer") == 3 and convert_value("2.5", "number") == 2.5 and convert_value("7", "number") == 7
+    assert convert_value("True", "boolean") is True and convert_value("no", "boolean") is False
+    assert convert_value("{'a': True}", "object") == {"a": True}            # python-literal spelling
+    assert convert_value("[1, 2]", None) == [1, 2] and convert_value("plain", None) == "plain"
+    assert convert_value("12x", "integer") == "12x"
+
+
+def test_glm47_streaming_any_split_multiple_calls_and_string_values_flow():
+    """Whatever the split of the text into increments: the events rebuild the same calls; a string value is forwarded
+    before its closing tag arrives; text around calls stays content; a call without arguments gives ``{}``; a call the
+    model never closed is closed at the end of the stream."""
+    from vllm_kunlun_b200.entrypoints.tool_parsers.glm47 import Glm47Scanner
+    text = ("Let me check. <tool_call>get_weather\n<arg_key>city</arg_key><arg_value>San \"Quoted\" José\nline2</arg_value>"
+            "<arg_key>flag</arg_key><arg_value>true</arg_value><arg_key>tags</arg_key><arg_value>[\"a\", \"b\"]</arg_value>"
+            "</tool_call>\n<tool_call>ping</tool_call> done <not a tag> "
+            "<tool_call>get_weather\n<arg_key>city</arg_key><arg_value>Oslo")
+    want = [("get_weather", {"city": "San \"Quoted\" José\nline2", "flag": True, "tags": ["a", "b"]}), ("ping", {}),
+            ("get_weather", {"city": "Oslo"})]
+
+    def run(step):
+        sc = Glm47Scanner(_WEATHER_TOOLS)
+        events = []
+        for i in range(0, len(text), step):
+            events += sc.feed(text[i:i + step])
+        events += sc.finish()
+        names, args, content = {}, {}, ""
+        for e in events:
+            if "content" in e:
+                content += e["content"]
+            else:
+                if "name" in e:
+                    names[e["index"]] = e["name"]
+                    assert e["id"].startswith("call_")
+                args[e["index"]] = args.get(e["index"], "") + e.get("arguments", "")
+        return [(names[i], json.loads(args[i])) for i in sorted(names)], content, events
+
+    for step in (1, 2, 3, 5, 11, 64, len(text)):
+        calls, content, _ = run(step)
+        assert calls == want, step
+        assert content == "Let me check. \n done <not a tag> ", (step, content)
+    # the string value streams: with one character per increment, argument pieces of call 0 arrive before the closing tag
+    sc = Glm47Scanner(_WEATHER_TOOLS)
+    seen = ""
+    upto = text.index("line2")
+    for ch in text[:upto]:
+        for e in sc.feed(ch):
+            seen += e.get("arguments", "")
+    assert seen.startswith('{"city": "San \\"Quoted\\" Jos') and not seen.endswith('"')
+
+
+def test_chat_stream_delta_assembles_tool_call_chunks():
+    from vllm_kunlun_b200.entrypoints.openai_server import ChatPostProcessor
+    post = ChatPostProcessor(None, "glm47", _WEATHER_TOOLS)
+    text = "ok <tool_call>get_weather\n<arg_key>days</arg_key><arg_value>2</arg_value></tool_call>"
+    deltas, fin = [], None
+    for i in range(0, len(text), 9):
+        d, f = post.stream_delta(text[i:i + 9], None)
+        deltas.append(d)
+    d, fin = post.stream_delta("", "stop")
+    deltas.append(d)
+    assert fin == "tool_calls"
+    assert "".join(d.get("content", "") for d in deltas) == "ok "
+    calls = [c for d in deltas for c in d.get("tool_calls", [])]
+    assert calls[0]["function"]["name"] == "get_weather" and calls[0]["type"] == "function" and calls[0]["index"] == 0
+    assert json.loads("".join(c["function"]["arguments"] for c in calls)) == {"days": 2}
+    # no tool call: content passes through and the finish reason stays
+    post = ChatPostProcessor(None, "glm47", _WEATHER_TOOLS)
+    d1, _ = post.stream_delta("plain <text", None)
+    d2, fin = post.stream_delta("", "stop")
+    assert d1.get("content", "") + d2.get("content", "") == "plain <text" and fin == "stop"
 
 
 def test_plugin_entry_points_and_platform():

@@ -30,7 +30,7 @@ def test_entry_points_load_through_upstreams_plugin_loader():
     assert "b200" in plat, f"platform plugin not discovered: {sorted(plat)}"
     assert plat["b200"]() == "vllm_kunlun_b200.platforms.b200.B200Platform"
     general = load_plugins_by_group("vllm.general_plugins")
-    for name in ("b200_model", "b200_quant", "b200_ops", "b200_reasoning_parser"):
+    for name in ("b200_model", "b200_quant", "b200_ops", "b200_reasoning_parser", "b200_tool_parser"):
         assert name in general, name
         general[name]()  # each registration runs against the installed vLLM
 
@@ -209,3 +209,44 @@ def test_upstream_c_namespace_ops_are_defined_with_upstream_schemas():
     res = torch.empty_like(s)
     torch.ops._C.rms_norm(res, s, w, 1e-6)
     torch.testing.assert_close(res, x)
+
+
+def test_glm47_tool_parser_is_an_upstream_tool_parser():
+    """`--tool-call-parser glm47` resolves through upstream's manager to a `ToolParser` subclass with upstream's method
+    signatures; complete and streaming extraction return upstream's protocol objects."""
+    import inspect
+    import json
+    from types import SimpleNamespace
+
+    from vllm.tool_parsers.abstract_tool_parser import ToolParser, ToolParserManager
+
+    import vllm_kunlun_b200 as pkg
+    pkg.register_tool_parser()
+    cls = ToolParserManager.get_tool_parser("glm47")
+    assert issubclass(cls, ToolParser)
+    for name in ("extract_tool_calls", "extract_tool_calls_streaming"):
+        assert list(inspect.signature(getattr(cls, name)).parameters) == \
+            list(inspect.signature(getattr(ToolParser, name)).parameters)
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {
+        "n": {"type": "integer"}, "s": {"type": "string"}}}}}]
+    req = SimpleNamespace(tools=tools)
+    tok = SimpleNamespace(get_vocab=lambda: {}, vocab={})
+    text = "hi <tool_call>f\n<arg_key>n</arg_key><arg_value>4</arg_value><arg_key>s</arg_key><arg_value>x y</arg_value></tool_call>"
+    p = cls(tok)
+    info = p.extract_tool_calls(text, req)
+    assert info.tools_called and info.content == "hi"
+    assert info.tool_calls[0].function.name == "f" and json.loads(info.tool_calls[0].function.arguments) == {"n": 4, "s": "x y"}
+    p = cls(tok)
+    name, args, content, prev = None, "", "", ""
+    for i in range(0, len(text), 5):
+        piece = text[i:i + 5]
+        d = p.extract_tool_calls_streaming(prev, prev + piece, piece, [], [], [], req)
+        prev += piece
+        if d is None:
+            continue
+        content += d.content or ""
+        for tc in d.tool_calls:
+            if tc.function.name:
+                name = tc.function.name
+            args += tc.function.arguments or ""
+    assert name == "f" and content == "hi " and json.loads(args) == {"n": 4, "s": "x y"}

@@ -45,6 +45,16 @@ def register_reasoning_parser() -> None:
     register_reasoning_parsers()
 
 
+def register_tool_parser() -> None:
+    """``vllm.general_plugins`` entry point: the GLM-4.7 tool-call parser under upstream's ``--tool-call-parser glm47``
+    (the reference ships the parser as a file for ``--tool-parser-plugin``)."""
+    if "tool_parser" in _completed_steps:
+        return
+    _completed_steps.add("tool_parser")
+    from .entrypoints.tool_parsers.vllm_adapter import register_with_vllm
+    register_with_vllm()
+
+
 def register_quant_method() -> None:
     if "quant" in _completed_steps:
         return

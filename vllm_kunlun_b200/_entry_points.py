@@ -12,6 +12,7 @@ ENTRY_POINTS = {
         "b200_quant = vllm_kunlun_b200:register_quant_method",
         "b200_ops = vllm_kunlun_b200:register_custom_ops",
         "b200_reasoning_parser = vllm_kunlun_b200:register_reasoning_parser",
+        "b200_tool_parser = vllm_kunlun_b200:register_tool_parser",
     ],
     "console_scripts": ["vllm-kunlun-b200 = vllm_kunlun_b200.entrypoints.cli:main"],
 }

@@ -38,6 +38,43 @@ class ChatPostProcessor:
             from .tool_parsers import TOOL_PARSERS
             self.tool = TOOL_PARSERS[tool_parser]()
 
+    def stream_delta(self, text: str, fin: Optional[str]):
+        """The ``delta`` object of a streamed chat chunk for the next piece of generated text, and the finish reason
+        to report (``tool_calls`` when the model called tools).  Reasoning is split off first; the remaining content
+        goes through the tool-call scanner: text outside calls stays content, calls stream as OpenAI tool-call deltas
+        (the name first, then pieces of the arguments JSON)."""
+        delta: dict = {}
+        if text:
+            if self.reasoning is not None:
+                d = self.reasoning.extract_reasoning_streaming(text)
+                if d is not None:
+                    if d.reasoning:
+                        delta["reasoning_content"] = d.reasoning
+                    if d.content:
+                        delta["content"] = d.content
+            else:
+                delta["content"] = text
+        if self.tool is not None:
+            content_in = delta.pop("content", "")
+            events = self.tool.feed(content_in, self.tools) if content_in else []
+            if fin is not None:
+                events = events + self.tool.finish()
+            content = "".join(e["content"] for e in events if "content" in e)
+            calls = []
+            for e in events:
+                if "name" in e:
+                    calls.append({"index": e["index"], "id": e["id"], "type": "function",
+                                  "function": {"name": e["name"], "arguments": ""}})
+                elif "arguments" in e:
+                    calls.append({"index": e["index"], "function": {"arguments": e["arguments"]}})
+            if content:
+                delta["content"] = content
+            if calls:
+                delta["tool_calls"] = calls
+            if fin is not None and fin != "length" and self.tool.tools_called:
+                fin = "tool_calls"
+        return delta, fin
+
     def finalize(self, text: str) -> dict:
         reasoning, content = (None, text)
         if self.reasoning is not None:
@@ -380,17 +417,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
         post = ChatPostProcessor(reasoning_parser, tool_parser, body.get("tools"), body.get("chat_template_kwargs"))
 
         def chunk(rid, created, text, fin):
-            delta = {}
-            if text:
-                if post.reasoning is not None:
-                    d = post.reasoning.extract_reasoning_streaming(text)
-                    if d is not None:
-                        if d.reasoning:
-                            delta["reasoning_content"] = d.reasoning
-                        if d.content:
-                            delta["content"] = d.content
-                else:
-                    delta["content"] = text
+            delta, fin = post.stream_delta(text, fin)
             return {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model_name,
                     "choices": [{"index": 0, "delta": delta, "finish_reason": fin}]}
 
