@@ -109,7 +109,8 @@ class ModelConfig:
     per_layer_vocab_size: int = 0
     attn_output_gate: bool = False  # q_proj carries a sigmoid output gate (Qwen3-Next full-attention layers)
     # quantization of the checkpoint
-    quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq"
+    quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq" | "w4a16"
+    quantization_kw: dict = field(default_factory=dict)  # constructor arguments of the linear method (group size, bits, ...)
     attn_quantization: Optional[str] = "same"  # "same" = follow ``quantization``; None = keep attention projections unquantised
     weight_block_size: tuple = (128, 128)
     dtype: str = "bfloat16"
@@ -202,6 +203,7 @@ class ModelConfig:
             rope = RopeScaling(type="linear", factor=float(rs.get("factor", 1.0)))
         qc = cfg.get("quantization_config") or {}
         quant = None
+        qkw: dict = {}
         wbs = (128, 128)
         if qc:
             method = qc.get("quant_method")
@@ -210,8 +212,18 @@ class ModelConfig:
                 wbs = tuple(qc.get("weight_block_size") or (128, 128))
             elif method in ("awq", "gptq"):
                 quant = method
+                qkw = {"group_size": int(qc.get("q_group_size", qc.get("group_size", 128))),
+                       "bits": int(qc.get("w_bit", qc.get("bits", 4)))}
+                if method == "gptq":
+                    qkw["desc_act"] = bool(qc.get("desc_act", False))
             elif method == "compressed-tensors":
                 quant = "int8"
+                groups = qc.get("config_groups") or {}
+                wq = next((g.get("weights") for g in groups.values() if isinstance(g, dict) and g.get("weights")), None)
+                if isinstance(wq, dict) and int(wq.get("num_bits", 8)) == 4:      # W4A16, pack-quantized
+                    quant = "w4a16"
+                    qkw = {"group_size": int(wq.get("group_size") or -1), "bits": 4,
+                           "symmetric": bool(wq.get("symmetric", True))}
         use_mla = "kv_lora_rank" in cfg and cfg.get("kv_lora_rank")
         kw: dict[str, Any] = dict(
             architecture=arch, name=cfg.get("_name_or_path", arch),
@@ -226,7 +238,7 @@ class ModelConfig:
             qkv_bias=bool(cfg.get("attention_bias", arch.startswith("Qwen2"))),
             qk_norm=arch.startswith("Qwen3"),
             sliding_window=cfg.get("sliding_window") if cfg.get("use_sliding_window", True) else None,
-            quantization=quant, weight_block_size=wbs,
+            quantization=quant, quantization_kw=qkw, weight_block_size=wbs,
             dtype=str(cfg.get("torch_dtype", "bfloat16")),
         )
         if arch.startswith("Qwen2") or arch.startswith("Qwen3"):

@@ -69,4 +69,7 @@ def resolve_model_cls(arch: str):
 
 
 def build_model(cfg: ModelConfig, device="cpu", dtype=None):
+    if cfg.quantization and cfg.quantization_kw:      # group size, bits, ... of the checkpoint's quantization_config
+        from .layers import set_quant_defaults
+        set_quant_defaults(cfg.quantization, cfg.quantization_kw)
     return resolve_model_cls(cfg.architecture)(cfg, device=device, dtype=dtype)

@@ -52,10 +52,28 @@ def register_linear_method(name: str, cls) -> None:
     _QUANT_METHODS[name] = cls
 
 
+_QUANT_DEFAULTS: dict = {}   # method name -> constructor arguments taken from the checkpoint's quantization_config
+
+
+def set_quant_defaults(name: Optional[str], kw: Optional[dict]) -> None:
+    """Arguments (group size, bits, ...) for the layers of the model about to be built (``build_model``)."""
+    if name:
+        _QUANT_DEFAULTS[name] = dict(kw or {})
+
+
 def get_linear_method(name: Optional[str], **kw):
     if name not in _QUANT_METHODS:
         from .. import quantization  # noqa: F401  (registers the methods)
+    if not kw and name in _QUANT_DEFAULTS:
+        kw = _QUANT_DEFAULTS[name]
     return _QUANT_METHODS[name](**kw)
+
+
+def _kn_spec(method, name: str):
+    """``(k_div, n_div)`` of an input-major checkpoint tensor ``[K / k_div, N / n_div]`` (AWQ / GPTQ ``qweight``,
+    ``qzeros``, ``scales``; ``g_idx [K]`` has ``n_div`` None), else None."""
+    fn = getattr(method, "kn_params", None)
+    return fn().get(name) if fn is not None else None
 
 
 class LinearBase(nn.Module):
@@ -117,8 +135,31 @@ class ColumnParallelLinear(LinearBase):
                         src0 // row_div, i))
         return out
 
+    def _load_kn(self, name: str, w: torch.Tensor, shard_id: Optional[int], kn, kv_head_shard=None):
+        """Input-major tensor ``[K / k_div, N / n_div]``: the output partitions lie along dim 1."""
+        p = getattr(self, name)
+        n_div = kn[1]
+        if n_div is None:               # per-input vector (g_idx): the same on every rank
+            p.data.copy_(w.reshape(p.shape))
+            return
+        if shard_id is None and len(self.output_sizes) > 1:
+            offs = 0
+            for i, s in enumerate(self.output_sizes):
+                self._load_kn(name, w[:, offs // n_div:(offs + s) // n_div], i, kn, kv_head_shard)
+                offs += s
+            return
+        for dst0, ln, src0, i in self._shard_rows(shard_id if shard_id is not None else 0):
+            if kv_head_shard is not None and self.replicate[i]:
+                src0 = kv_head_shard(i)
+            assert dst0 % n_div == 0 and ln % n_div == 0 and src0 % n_div == 0, \
+                f"{name}: partition of {ln} columns at {src0} does not fall on the packing of {n_div}"
+            p.data[:, dst0 // n_div:(dst0 + ln) // n_div].copy_(w[:, src0 // n_div:(src0 + ln) // n_div])
+
     def load(self, name: str, w: torch.Tensor, shard_id: Optional[int] = None, kv_head_shard=None):
         p = getattr(self, name)
+        kn = _kn_spec(self.method, name)
+        if kn is not None:
+            return self._load_kn(name, w, shard_id, kn, kv_head_shard)
         aux = self.method.aux_params().get(name)
         row_div = aux[0] if aux else 1
         if shard_id is None and len(self.output_sizes) > 1:
@@ -184,6 +225,17 @@ class RowParallelLinear(LinearBase):
 
     def load(self, name: str, w: torch.Tensor, shard_id=None):
         p = getattr(self, name)
+        kn = _kn_spec(self.method, name)
+        if kn is not None:      # input-major tensor [K / k_div, ...]: this rank's inputs are a block of rows
+            k_div = kn[0]
+            assert (self.tp_rank * self.in_local) % k_div == 0 and self.in_local % k_div == 0, \
+                f"{name}: {self.in_local} inputs per rank do not fall on the packing / group size of {k_div}"
+            r0 = (self.tp_rank * self.in_local) // k_div
+            rows = w[r0:r0 + self.in_local // k_div]
+            if kn[1] is None:   # g_idx: group numbers restart at this rank's first group
+                rows = rows - (rows.min() if rows.numel() else 0)
+            p.data.copy_(rows.reshape(p.shape))
+            return
         if name == "bias" or p.dim() < 2:
             p.data.copy_(w.reshape(p.shape))
             return

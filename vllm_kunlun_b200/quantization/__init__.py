@@ -8,12 +8,13 @@ format of the DeepSeek-V3 / Qwen3-MoE fp8 checkpoints.
 """
 from ..models.layers import register_linear_method
 from .fp8 import Fp8BlockLinearMethod
-from .int4 import AWQLinearMethod, GPTQLinearMethod
+from .int4 import AWQLinearMethod, CompressedTensorsW4A16LinearMethod, GPTQLinearMethod
 from .int8 import Int8LinearMethod
 
 register_linear_method("fp8", Fp8BlockLinearMethod)
 register_linear_method("int8", Int8LinearMethod)
 register_linear_method("awq", AWQLinearMethod)
 register_linear_method("gptq", GPTQLinearMethod)
+register_linear_method("w4a16", CompressedTensorsW4A16LinearMethod)
 
 QUANTIZATION_METHODS = ["fp8", "int8", "compressed-tensors", "awq", "gptq"]

@@ -60,9 +60,9 @@ def packed_ok(K: int, group: int) -> bool:
 class _W4Method:
     """Shared tail of the two checkpoint formats: keep the packed form when the kernels take it."""
 
-    def _finish(self, layer, q, scale_kn, zero_gn, group, contiguous_groups: bool, dense_fallback):
+    def _finish(self, layer, q, scale_kn, zero_gn, group, contiguous_groups: bool, dense_fallback, dev=None):
         """``q [K, N]`` ints, ``scale_kn [K / g, N]``, ``zero_gn [K / g, N]`` (values), all on the CPU."""
-        dev = layer.scales.device
+        dev = layer.scales.device if dev is None else dev
         K = q.shape[0]
         if contiguous_groups and packed_ok(K, group) and scale_kn.dtype in (torch.bfloat16, torch.float16):
             layer.w4_packed = pack_w4(q.T.contiguous()).to(dev)
@@ -88,6 +88,7 @@ class AWQLinearMethod(_W4Method):
 
     def create_weights(self, layer, out_local: int, in_local: int, dtype, device):
         g = self.group_size if self.group_size > 0 else in_local
+        self._g = g
         layer.qweight = param(in_local, out_local // 8, dtype=torch.int32, device=device)
         layer.qzeros = param(in_local // g, out_local // 8, dtype=torch.int32, device=device)
         layer.scales = param(in_local // g, out_local, dtype=dtype, device=device)
@@ -95,6 +96,11 @@ class AWQLinearMethod(_W4Method):
 
     def aux_params(self):
         return {}
+
+    def kn_params(self):
+        """Input-major checkpoint tensors ``[K / k_div, N / n_div]`` (how the parallel layers shard them)."""
+        g = self._g
+        return {"qweight": (1, 8), "qzeros": (g, 8), "scales": (g, 1)}
 
     def process_weights_after_loading(self, layer):
         if layer.qweight is None:
@@ -113,9 +119,14 @@ class GPTQLinearMethod(_W4Method):
     def __init__(self, group_size: int = 128, bits: int = 4, desc_act: bool = False):
         self.group_size, self.bits, self.desc_act = group_size, bits, desc_act
 
+    def kn_params(self):
+        pack = 32 // self.bits
+        return {"qweight": (pack, 1), "qzeros": (self._g, pack), "scales": (self._g, 1), "g_idx": (1, None)}
+
     def create_weights(self, layer, out_local: int, in_local: int, dtype, device):
         pack = 32 // self.bits
         g = self.group_size if self.group_size > 0 else in_local
+        self._g = g
         layer.qweight = param(in_local // pack, out_local, dtype=torch.int32, device=device)
         layer.qzeros = param(in_local // g, out_local // pack, dtype=torch.int32, device=device)
         layer.scales = param(in_local // g, out_local, dtype=dtype, device=device)
@@ -141,3 +152,45 @@ class GPTQLinearMethod(_W4Method):
         q = ((qw.unsqueeze(1) >> shifts.view(1, -1, 1)) & 0xF).reshape(-1, qw.shape[1])          # [K, N]
         z = ((qz.unsqueeze(-1) >> shifts) & 0xF).reshape(qz.shape[0], -1) + 1                    # [K / g, N]
         self._finish(layer, q, sc, z, g, in_order, dense)
+
+
+class CompressedTensorsW4A16LinearMethod(_W4Method):
+    """compressed-tensors ``pack-quantized`` int4 weights with 16-bit activations (W4A16; the reference lists the
+    format in ``docs/source/user_guide/feature_guide/quantization.md:4-44``): ``weight_packed [N, K / 8]`` int32
+    (eight values per word along k, value ``i`` in bits ``4 i``), ``weight_scale [N, K / g]``, and for asymmetric
+    checkpoints ``weight_zero_point [N / 8, K / g]`` int32 (packed along n); symmetric values are stored with an
+    offset of 8.  Output-major tensors: the parallel layers shard them like an ordinary weight."""
+    name = "w4a16"
+
+    def __init__(self, group_size: int = 128, bits: int = 4, symmetric: bool = True):
+        self.group_size, self.bits, self.symmetric = group_size, bits, symmetric
+
+    def create_weights(self, layer, out_local: int, in_local: int, dtype, device):
+        g = self.group_size if self.group_size > 0 else in_local
+        self._g = g
+        layer.weight_packed = param(out_local, in_local // 8, dtype=torch.int32, device=device)
+        layer.weight_scale = param(out_local, in_local // g, dtype=dtype, device=device)
+        layer.weight_zero_point = None if self.symmetric else param(out_local // 8, in_local // g, dtype=torch.int32,
+                                                                    device=device)
+        layer.weight = None
+
+    def aux_params(self):
+        """(row divisor, column divisor) of the tensors that are smaller than the weight."""
+        return {"weight_packed": (1, 8), "weight_scale": (1, self._g), "weight_zero_point": (8, self._g)}
+
+    def process_weights_after_loading(self, layer):
+        if layer.weight_packed is None:
+            return
+        dev = layer.weight_scale.device
+        wp, sc = layer.weight_packed.data.cpu(), layer.weight_scale.data.cpu()
+        shifts = torch.arange(0, 32, 4, dtype=torch.int32)
+        q = ((wp.unsqueeze(-1) >> shifts) & 0xF).reshape(wp.shape[0], -1)                      # [N, K]
+        if layer.weight_zero_point is None:
+            z = torch.full(sc.shape, 8, dtype=torch.int32)
+        else:
+            zp = layer.weight_zero_point.data.cpu()                                              # [N / 8, K / g]
+            z = ((zp.unsqueeze(1) >> shifts.view(1, -1, 1)) & 0xF).reshape(-1, zp.shape[1])      # [N, K / g]
+        g = self._g
+        dense = lambda: ((q - z.repeat_interleave(g, 1)).float() * sc.float().repeat_interleave(g, 1)).to(sc.dtype).T  # noqa: E731
+        self._finish(layer, q.T.contiguous(), sc.T.contiguous(), z.T.contiguous(), g, True, dense, dev)
+        layer.weight_packed = layer.weight_zero_point = layer.weight_scale = None
