@@ -317,3 +317,32 @@ def test_awq_dense_model_loads_per_projection_tensors_and_matches_dequantised_mo
             h, _ = m(ids)
             res.append(m.compute_logits(h).float())
     torch.testing.assert_close(res[1], res[0], atol=0.05, rtol=0.05)
+
+
+def test_int8_checkpoints_shard_over_tensor_parallel_ranks():
+    """compressed-tensors W8A8: merged column-parallel layers take rows of `weight` and `weight_scale` per partition;
+    row-parallel layers take columns of `weight` and the whole per-channel `weight_scale`."""
+    torch.manual_seed(10)
+    K, parts = 64, [32, 16]
+    N = sum(parts)
+    w = torch.randn(N, K)
+    s = w.abs().amax(1, keepdim=True) / 127
+    q = (w / s).round().clamp(-127, 127).to(torch.int8)
+    x = torch.randn(3, K)
+    want = x @ (q.float() * s).T
+    outs = []
+    for rank in range(2):
+        lin = ColumnParallelLinear(K, parts, dtype=torch.float32, device="cpu", quant="int8", tp_size=2, tp_rank=rank)
+        lin.load("weight", q); lin.load("weight_scale", s)          # fused checkpoint tensors
+        lin.method.process_weights_after_loading(lin)
+        outs.append(lin(x))
+    got = torch.cat([outs[0][:, :16], outs[1][:, :16], outs[0][:, 32 - 16:], outs[1][:, 16:]], 1)
+    torch.testing.assert_close(got, want, atol=0.3, rtol=0.05)      # dynamic per-token activation quantisation
+    total = 0
+    for rank in range(2):
+        lin = RowParallelLinear(K, N, dtype=torch.float32, device="cpu", quant="int8", tp_size=2, tp_rank=rank,
+                                reduce_results=False)
+        lin.load("weight", q); lin.load("weight_scale", s)
+        lin.method.process_weights_after_loading(lin)
+        total = total + lin(x[:, rank * 32:(rank + 1) * 32].contiguous())
+    torch.testing.assert_close(total, want, atol=0.3, rtol=0.05)

@@ -239,6 +239,9 @@ class RowParallelLinear(LinearBase):
         if name == "bias" or p.dim() < 2:
             p.data.copy_(w.reshape(p.shape))
             return
+        if w.dim() == 2 and w.shape[1] == 1 and p.shape[1] == 1:
+            p.data.copy_(w)     # one value per output channel (int8 weight scales): the same on every rank
+            return
         aux = self.method.aux_params().get(name)
         col_div = aux[1] if aux else 1
         n = p.shape[1]
