@@ -117,3 +117,18 @@ def test_int8_and_awq_expert_checkpoints_dequantise_on_load():
         dense = rb.awq_dequantize(qw, sc, qz, 32).T
         got = ex.w2.data[1] if which == "down_proj" else ex.w13.data[1, (0 if which == "gate_proj" else I):][:I]
         torch.testing.assert_close(got, dense)
+    # compressed-tensors W4A16 (pack-quantized, symmetric: values stored with an offset of 8), group 32
+    ex = FusedExperts(dataclasses.replace(base, quantization="w4a16", quantization_kw={"group_size": 32, "symmetric": True}),
+                      torch.float32, "cpu")
+    for which, (N, K) in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+        qv = torch.randint(0, 16, (N, K), generator=g)
+        sc = torch.rand(N, K // 32, generator=g) * 0.1
+        wp = torch.zeros(N, K // 8, dtype=torch.int64)
+        for j in range(8):
+            wp |= qv[:, j::8].long() << (4 * j)
+        wp = torch.where(wp >= 2 ** 31, wp - 2 ** 32, wp).to(torch.int32)
+        for pname, t in (("weight_shape", torch.tensor([N, K])), ("weight_packed", wp), ("weight_scale", sc)):
+            ex.load_expert(0, which, pname, t)
+        dense = (qv.float() - 8) * sc.repeat_interleave(32, 1)
+        got = ex.w2.data[0] if which == "down_proj" else ex.w13.data[0, (0 if which == "gate_proj" else I):][:I]
+        torch.testing.assert_close(got, dense)

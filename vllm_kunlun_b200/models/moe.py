@@ -78,13 +78,14 @@ class FusedExperts(nn.Module):
     # the pieces of one projection are collected and de-quantised ONCE into the 16-bit grouped-GEMM layout (the
     # reference de-quantises int4 experts to dense weights on every call).
     _QUANT_PIECES = {"weight_scale": ("weight", "weight_scale"), "weight_packed": ("weight_packed", "weight_scale"),
+                     "weight_zero_point": ("weight_packed", "weight_scale", "weight_zero_point"),
                      "qweight": ("qweight", "scales", "qzeros"), "scales": ("qweight", "scales", "qzeros"),
                      "qzeros": ("qweight", "scales", "qzeros")}
 
     def _load_quantised(self, e: int, which: str, pname: str, w: torch.Tensor) -> bool:
         """Returns True when ``pname`` belongs to an int8 / int4 format (and was consumed)."""
         q = self.cfg.quantization
-        if q not in ("int8", "awq", "gptq", "wna16"):
+        if q not in ("int8", "awq", "gptq", "wna16", "w4a16"):
             return False
         if pname in ("bias", "g_idx", "weight_shape", "input_scale"):
             return True  # not needed by the de-quantised layout
@@ -95,6 +96,19 @@ class FusedExperts(nn.Module):
         dense = None
         if q == "int8" and "weight" in slot and "weight_scale" in slot:
             dense = slot["weight"].float() * slot["weight_scale"].float().reshape(-1, 1)
+        elif q == "w4a16" and "weight_packed" in slot and "weight_scale" in slot and (
+                self.cfg.quantization_kw.get("symmetric", True) or "weight_zero_point" in slot):
+            # compressed-tensors pack-quantized int4: eight values per word along k; symmetric values carry an offset of 8
+            wp, sc = slot["weight_packed"], slot["weight_scale"].float()
+            shifts = torch.arange(0, 32, 4, dtype=torch.int32)
+            qv = ((wp.unsqueeze(-1) >> shifts) & 0xF).reshape(wp.shape[0], -1).float()          # [N, K]
+            g = qv.shape[1] // sc.shape[1]
+            if "weight_zero_point" in slot:
+                zp = slot["weight_zero_point"]
+                z = ((zp.unsqueeze(1) >> shifts.view(1, -1, 1)) & 0xF).reshape(-1, zp.shape[1]).float()
+            else:
+                z = torch.full_like(sc, 8.0)
+            dense = (qv - z.repeat_interleave(g, 1)) * sc.repeat_interleave(g, 1)
         elif q in ("awq", "gptq", "wna16") and all(k in slot for k in ("qweight", "scales", "qzeros")):
             g = slot["qweight"].shape[0] * (1 if q == "awq" else 8) // slot["scales"].shape[0]
             if q == "awq":
