@@ -1,5 +1,7 @@
 """Reasoning parser, tool parser, plugin entry points, platform, env registry, loader, utils."""
 import json
+
+import pytest
 import os
 
 import torch
@@ -447,3 +449,40 @@ def test_openai_server_stop_string_and_stop_token_abort_the_request():
         assert [int(t) for t in again] == toks
         assert app.state.engine_loop.stats["aborted"] >= 1
     assert not llm.engine.has_unfinished()
+
+
+def test_openai_server_returns_logprobs_when_asked():
+    from fastapi.testclient import TestClient
+
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    cfg = tiny(qwen2_0_5b(), num_layers=1, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+               intermediate_size=128, max_position=256, dtype="float32")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    app = build_app(llm, "tiny")
+    body = {"prompt": [5, 6, 7, 8], "max_tokens": 5, "temperature": 0, "ignore_eos": True}
+    with TestClient(app) as c:
+        plain = c.post("/v1/completions", json=body).json()
+        assert "logprobs" not in plain["choices"][0]
+        r = c.post("/v1/completions", json=dict(body, logprobs=1)).json()
+        lp = r["choices"][0]["logprobs"]
+        assert r["choices"][0]["text"] == plain["choices"][0]["text"]
+        assert len(lp["tokens"]) == 5 and " ".join(lp["tokens"]) == r["choices"][0]["text"]
+        assert len(lp["token_logprobs"]) == 5 and all(v <= 0.0 for v in lp["token_logprobs"])
+        assert lp["text_offset"][0] == 0 and lp["text_offset"] == sorted(lp["text_offset"])
+        # greedy: the sampled token is the most likely one, so its probability is at least 1 / vocab
+        import math
+        assert all(v >= math.log(1 / 128) for v in lp["token_logprobs"])
+        chat = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "1 2 3"}], "max_tokens": 3,
+                                                    "temperature": 0, "ignore_eos": True, "logprobs": True}).json()
+        entries = chat["choices"][0]["logprobs"]["content"]
+        assert len(entries) == 3 and all(e["logprob"] <= 0 and e["top_logprobs"] == [] for e in entries)
+        # streamed: the chunks carry the same values
+        with c.stream("POST", "/v1/completions", json=dict(body, logprobs=1, stream=True)) as s:
+            got = []
+            for line in s.iter_lines():
+                if line.startswith("data: {"):
+                    ch = json.loads(line[6:])["choices"][0]
+                    got += (ch.get("logprobs") or {}).get("token_logprobs", [])
+        assert got == pytest.approx(lp["token_logprobs"], abs=1e-5)

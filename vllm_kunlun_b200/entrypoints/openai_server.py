@@ -250,6 +250,8 @@ class EngineLoop:
                     new_toks = req.output_token_ids[sent[rid]:n]
                     self.stats["tokens"] += len(new_toks)
                     sent[rid] = n
+                    if req.sampling.logprobs:   # log p of every new token, ahead of the tokens themselves
+                        loop.call_soon_threadsafe(out_q.put_nowait, ("logprobs", list(req.output_logprobs[n - len(new_toks):n])))
                     loop.call_soon_threadsafe(out_q.put_nowait, ("tokens", new_toks))
                 if req.status.finished:
                     reason = "length" if req.status.name.endswith("LENGTH") else "stop"
@@ -278,6 +280,19 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
 
     def decode(ids):
         return " ".join(map(str, ids)) if tok is None else tok.decode(ids)
+
+    def logprob_block(ids, lps, obj: str):
+        """The ``logprobs`` object of a choice for these tokens: the chat form (``content`` entries) or the completions
+        form (parallel lists).  Only the sampled token's log-probability is reported (``top_logprobs`` stays empty)."""
+        toks = [decode([t]) for t in ids]
+        if obj.startswith("chat"):
+            return {"content": [{"token": t, "logprob": lp, "bytes": list(t.encode("utf-8")), "top_logprobs": []}
+                                for t, lp in zip(toks, lps)]}
+        offs, pos = [], 0
+        for t in toks:
+            offs.append(pos)
+            pos += len(t)
+        return {"tokens": toks, "token_logprobs": list(lps), "top_logprobs": None, "text_offset": offs}
 
     def sampling(body):
         """Request body -> SamplingParams, or an error string (answered with HTTP 400)."""
@@ -342,14 +357,21 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
         if stream:
             async def gen():
                 ids = []
+                lps = None
                 try:
                     while True:
                         kind, val = await out_q.get()
-                        if kind == "tokens":
+                        if kind == "logprobs":
+                            lps = val
+                        elif kind == "tokens":
                             ids += val
                             piece, hit = cut.feed(decode(val))
-                            if piece:
-                                yield f"data: {json.dumps(make_chunk(rid, created, piece, None))}\n\n"
+                            if piece or lps:
+                                ch = make_chunk(rid, created, piece, None)
+                                if lps:     # the tokens of this step (their text may still be held back by a stop string)
+                                    ch["choices"][0]["logprobs"] = logprob_block(val, lps, ch["object"])
+                                    lps = None
+                                yield f"data: {json.dumps(ch)}\n\n"
                             if hit:
                                 loop_obj.abort(rid)
                                 yield f"data: {json.dumps(make_chunk(rid, created, '', 'stop'))}\n\n"
@@ -370,10 +392,12 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                     loop_obj.abort(rid)
                     raise
             return StreamingResponse(gen(), media_type="text/event-stream")
-        ids, reason, text = [], None, ""
+        ids, reason, text, all_lps = [], None, "", []
         while reason is None:
             kind, val = await out_q.get()
-            if kind == "tokens":
+            if kind == "logprobs":
+                all_lps += val
+            elif kind == "tokens":
                 ids += val
                 if stops:
                     piece, hit = cut.feed(decode(val))
@@ -386,8 +410,10 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
             else:
                 reason = val
                 text += cut.flush()
-        return JSONResponse(make_final(rid, created, text if stops else decode(ids), reason, len(prompt_ids),
-                                       len(ids)))
+        out = make_final(rid, created, text if stops else decode(ids), reason, len(prompt_ids), len(ids))
+        if all_lps:
+            out["choices"][0]["logprobs"] = logprob_block(ids[:len(all_lps)], all_lps, out["object"])
+        return JSONResponse(out)
 
     @app.post("/v1/completions")
     async def completions(req: Request):
