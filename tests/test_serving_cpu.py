@@ -486,3 +486,60 @@ def test_openai_server_returns_logprobs_when_asked():
                     ch = json.loads(line[6:])["choices"][0]
                     got += (ch.get("logprobs") or {}).get("token_logprobs", [])
         assert got == pytest.approx(lp["token_logprobs"], abs=1e-5)
+
+
+_HARMONY = ("<|channel|>analysis<|message|>The user wants weather. I should call the tool.<|end|>"
+            "<|start|>assistant<|channel|>commentary<|message|>Checking the forecast.<|end|>"
+            "<|start|>assistant<|channel|>commentary to=functions.get_weather <|constrain|>json<|message|>"
+            "{\"city\": \"Paris\", \"days\": 2}<|call|>")
+_HARMONY_ANSWER = ("<|channel|>analysis<|message|>Simple sum.<|end|><|start|>assistant<|channel|>final<|message|>"
+                   "2 + 2 = 4<|return|>")
+
+
+def test_gpt_oss_harmony_channels_whole_and_streaming():
+    """analysis -> reasoning, final / commentary preamble -> content, commentary to=functions.X -> a tool call whose
+    body is the arguments JSON; any split of the stream gives the same result."""
+    from vllm_kunlun_b200.reasoning import get_reasoning_parser
+    cls = get_reasoning_parser("gpt_oss")
+    assert get_reasoning_parser("openai_gptoss") is cls
+    r, c, calls = cls().extract_all(_HARMONY)
+    assert r == "The user wants weather. I should call the tool." and c == "Checking the forecast."
+    assert [(n, json.loads(a)) for _, n, a in calls] == [("get_weather", {"city": "Paris", "days": 2})]
+    assert cls().extract_reasoning(_HARMONY_ANSWER) == ("Simple sum.", "2 + 2 = 4")
+    assert cls().extract_reasoning("no markers at all") == (None, "no markers at all")
+    for step in (1, 2, 3, 7, 16, len(_HARMONY)):
+        p = cls()
+        r, c, name, args = "", "", None, ""
+        for i in range(0, len(_HARMONY), step):
+            d = p.extract_reasoning_streaming(_HARMONY[i:i + step], final=i + step >= len(_HARMONY))
+            if d is None:
+                continue
+            r += d.reasoning or ""
+            c += d.content or ""
+            for e in d.tool_events or []:
+                name = e.get("name", name)
+                args += e.get("arguments", "")
+        assert (r, c, name) == ("The user wants weather. I should call the tool.", "Checking the forecast.", "get_weather"), step
+        assert json.loads(args) == {"city": "Paris", "days": 2} and p.tools_called
+
+
+def test_chat_post_processor_with_harmony_parser():
+    from vllm_kunlun_b200.entrypoints.openai_server import ChatPostProcessor
+    msg = ChatPostProcessor("gpt_oss").finalize(_HARMONY)
+    assert msg["reasoning_content"].startswith("The user wants") and msg["content"] == "Checking the forecast."
+    assert msg["tool_calls"][0]["function"]["name"] == "get_weather"
+    assert json.loads(msg["tool_calls"][0]["function"]["arguments"]) == {"city": "Paris", "days": 2}
+    post = ChatPostProcessor("gpt_oss")
+    deltas = [post.stream_delta(_HARMONY[i:i + 11], None)[0] for i in range(0, len(_HARMONY), 11)]
+    last, fin = post.stream_delta("", "stop")
+    deltas.append(last)
+    assert fin == "tool_calls"
+    assert "".join(d.get("reasoning_content", "") for d in deltas) == "The user wants weather. I should call the tool."
+    assert "".join(d.get("content", "") for d in deltas) == "Checking the forecast."
+    calls = [c for d in deltas for c in d.get("tool_calls", [])]
+    assert calls[0]["function"]["name"] == "get_weather"
+    assert json.loads("".join(c["function"]["arguments"] for c in calls)) == {"city": "Paris", "days": 2}
+    post = ChatPostProcessor("gpt_oss")
+    deltas = [post.stream_delta(_HARMONY_ANSWER[i:i + 5], None)[0] for i in range(0, len(_HARMONY_ANSWER), 5)]
+    last, fin = post.stream_delta("", "stop")
+    assert fin == "stop" and "".join(d.get("content", "") for d in deltas + [last]) == "2 + 2 = 4"

@@ -44,16 +44,29 @@ class ChatPostProcessor:
         goes through the tool-call scanner: text outside calls stays content, calls stream as OpenAI tool-call deltas
         (the name first, then pieces of the arguments JSON)."""
         delta: dict = {}
-        if text:
+        harmony = getattr(self.reasoning, "handles_tools", False)   # the parser reports tool calls of the same stream
+        if text or (harmony and fin is not None):
             if self.reasoning is not None:
-                d = self.reasoning.extract_reasoning_streaming(text)
+                d = (self.reasoning.extract_reasoning_streaming(text, final=fin is not None) if harmony
+                     else self.reasoning.extract_reasoning_streaming(text))
                 if d is not None:
                     if d.reasoning:
                         delta["reasoning_content"] = d.reasoning
                     if d.content:
                         delta["content"] = d.content
+                    calls = []
+                    for e in (getattr(d, "tool_events", None) or []):
+                        if "name" in e:
+                            calls.append({"index": e["index"], "id": e["id"], "type": "function",
+                                          "function": {"name": e["name"], "arguments": ""}})
+                        else:
+                            calls.append({"index": e["index"], "function": {"arguments": e["arguments"]}})
+                    if calls:
+                        delta["tool_calls"] = calls
             else:
                 delta["content"] = text
+        if harmony and fin is not None and fin != "length" and self.reasoning.tools_called:
+            fin = "tool_calls"
         if self.tool is not None:
             content_in = delta.pop("content", "")
             events = self.tool.feed(content_in, self.tools) if content_in else []
@@ -77,11 +90,17 @@ class ChatPostProcessor:
 
     def finalize(self, text: str) -> dict:
         reasoning, content = (None, text)
-        if self.reasoning is not None:
+        calls = []
+        if getattr(self.reasoning, "handles_tools", False):
+            reasoning, content, calls = self.reasoning.extract_all(text)
+        elif self.reasoning is not None:
             reasoning, content = self.reasoning.extract_reasoning(text)
         msg = {"role": "assistant", "content": content}
         if reasoning:
             msg["reasoning_content"] = reasoning
+        if calls:
+            msg["tool_calls"] = [{"id": cid, "type": "function", "function": {"name": name, "arguments": args}}
+                                 for cid, name, args in calls]
         if self.tool is not None and content:
             ex = self.tool.extract_tool_calls(content, self.tools)
             if ex.tools_called:
