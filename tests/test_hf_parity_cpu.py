@@ -1,0 +1,122 @@
+"""Model families against the Hugging Face reference implementations (CPU, fp32, tiny random-weight instances).
+
+For every family: build the ``transformers`` model from a small config, randomise its weights, take the logits of a
+prompt; build this package's model from the SAME config dict (``ModelConfig.from_hf_config``), load the SAME state
+dict through the model's checkpoint loader, run the prompt through the engine's prefill path and compare the logits.
+This checks the config parsing, the checkpoint name mapping / stacking / expert layouts and the model mathematics
+(attention variants, rotary variants, routing rules, activations) in one go.
+"""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from vllm_kunlun_b200 import LLM, SamplingParams  # noqa: E402
+from vllm_kunlun_b200.attention.metadata import ForwardContext, set_forward_context  # noqa: E402
+from vllm_kunlun_b200.config import ModelConfig  # noqa: E402
+
+COMMON = dict(vocab_size=160, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=256, max_position_embeddings=256, rms_norm_eps=1e-5)
+DS = dict(vocab_size=160, hidden_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+          intermediate_size=256, moe_intermediate_size=64, n_routed_experts=8, num_experts_per_tok=2,
+          first_k_dense_replace=1, kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+          max_position_embeddings=256, rms_norm_eps=1e-5)
+GPT_OSS = dict(vocab_size=160, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=32, intermediate_size=64, num_local_experts=4, num_experts_per_tok=2, max_position_embeddings=256)
+YARN = {"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 64,
+        "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0}
+
+# (id, transformers config class, transformers model class, architecture string, config arguments, tolerance)
+CASES = [
+    ("llama", "LlamaConfig", "LlamaForCausalLM", "LlamaForCausalLM", dict(COMMON, rope_theta=500000.0), 1e-4),
+    ("llama3_rope_scaling", "LlamaConfig", "LlamaForCausalLM", "LlamaForCausalLM",
+     dict(COMMON, rope_theta=500000.0, rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                     "high_freq_factor": 4.0, "original_max_position_embeddings": 64}), 1e-4),
+    ("mistral_sliding_window", "MistralConfig", "MistralForCausalLM", "MistralForCausalLM", dict(COMMON, sliding_window=8), 1e-4),
+    ("qwen2_bias", "Qwen2Config", "Qwen2ForCausalLM", "Qwen2ForCausalLM", dict(COMMON), 1e-4),
+    ("qwen3_qk_norm", "Qwen3Config", "Qwen3ForCausalLM", "Qwen3ForCausalLM", dict(COMMON, head_dim=48), 1e-4),
+    ("seed_oss", "SeedOssConfig", "SeedOssForCausalLM", "SeedOssForCausalLM", dict(COMMON, head_dim=32), 1e-4),
+    ("mixtral", "MixtralConfig", "MixtralForCausalLM", "MixtralForCausalLM",
+     dict(COMMON, num_local_experts=4, num_experts_per_tok=2), 1e-4),
+    ("qwen3_moe", "Qwen3MoeConfig", "Qwen3MoeForCausalLM", "Qwen3MoeForCausalLM",
+     dict(COMMON, head_dim=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
+          decoder_sparse_step=1, mlp_only_layers=[]), 1e-4),
+    ("qwen2_moe_shared_expert", "Qwen2MoeConfig", "Qwen2MoeForCausalLM", "Qwen2MoeForCausalLM",
+     dict(COMMON, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
+          norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[]), 1e-4),
+    ("glm4_moe", "Glm4MoeConfig", "Glm4MoeForCausalLM", "Glm4MoeForCausalLM",
+     dict(vocab_size=160, hidden_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+          intermediate_size=256, attention_bias=True, partial_rotary_factor=0.5, use_qk_norm=True, n_routed_experts=8,
+          n_shared_experts=1, num_experts_per_tok=2, moe_intermediate_size=64, first_k_dense_replace=1, n_group=1,
+          topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True, max_position_embeddings=256, rms_norm_eps=1e-5), 1e-4),
+    ("deepseek_v3_mla_sigmoid_groups", "DeepseekV3Config", "DeepseekV3ForCausalLM", "DeepseekV3ForCausalLM",
+     dict(DS, q_lora_rank=64, n_shared_experts=1, n_group=2, topk_group=1, routed_scaling_factor=2.5, norm_topk_prob=True), 5e-4),
+    ("deepseek_v3_yarn", "DeepseekV3Config", "DeepseekV3ForCausalLM", "DeepseekV3ForCausalLM",
+     dict(DS, q_lora_rank=64, n_shared_experts=1, n_group=2, topk_group=1, routed_scaling_factor=2.5, norm_topk_prob=True,
+          rope_parameters=YARN), 5e-4),
+    ("deepseek_v3_plain_q_proj", "DeepseekV3Config", "DeepseekV3ForCausalLM", "DeepseekV3ForCausalLM",
+     dict(DS, q_lora_rank=None, n_shared_experts=1, n_group=2, topk_group=1, routed_scaling_factor=2.5, norm_topk_prob=True), 5e-4),
+    ("deepseek_v2_softmax_routing", "DeepseekV2Config", "DeepseekV2ForCausalLM", "DeepseekV2ForCausalLM",
+     dict(DS, q_lora_rank=None, n_shared_experts=2, n_group=1, topk_group=1, routed_scaling_factor=1.0, norm_topk_prob=False,
+          topk_method="greedy"), 5e-4),
+    ("gpt_oss_sinks_swa_yarn", "GptOssConfig", "GptOssForCausalLM", "GptOssForCausalLM",
+     dict(GPT_OSS, sliding_window=8, layer_types=["sliding_attention", "full_attention"]), 1e-4),
+    ("gpt_oss_plain_rope", "GptOssConfig", "GptOssForCausalLM", "GptOssForCausalLM",
+     dict(GPT_OSS, sliding_window=64, rope_parameters={"rope_type": "default", "rope_theta": 150000.0},
+          layer_types=["full_attention", "full_attention"]), 1e-4),
+    ("qwen3_next_gated_delta_net", "Qwen3NextConfig", "Qwen3NextForCausalLM", "Qwen3NextForCausalLM",
+     dict(vocab_size=160, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+          intermediate_size=256, moe_intermediate_size=64, shared_expert_intermediate_size=64, num_experts=4,
+          num_experts_per_tok=2, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+          linear_value_head_dim=32, linear_conv_kernel_dim=4, full_attention_interval=4, partial_rotary_factor=0.25,
+          max_position_embeddings=256, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]), 5e-4),
+]
+
+
+def _randomise(model):
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if "norm" in name and p.dim() == 1:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            elif p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.05)
+            else:
+                p.copy_(torch.randn_like(p) * 0.1)      # biases, sinks, router correction biases
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_logits_match_the_transformers_implementation(case):
+    _, cfg_name, cls_name, arch, kwargs, tol = case
+    if not (hasattr(transformers, cfg_name) and hasattr(transformers, cls_name)):
+        pytest.skip(f"transformers {transformers.__version__} has no {cls_name}")
+    torch.manual_seed(0)
+    hf_cfg = getattr(transformers, cfg_name)(**kwargs)
+    hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
+    _randomise(hf)
+    ids = torch.randint(1, hf_cfg.vocab_size - 1, (1, 19))
+    with torch.no_grad():
+        want = hf(ids).logits[0].float()
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = [arch], "float32"
+    cfg = ModelConfig.from_hf_config(d)
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    model = llm.engine.runner.model
+    with torch.inference_mode():
+        loaded = model.load_weights(list(hf.state_dict().items()))
+    assert len(loaded) >= len(hf.state_dict()) - 8, "most checkpoint tensors must find their parameter"
+    eng = llm.engine
+    eng.add_request(ids[0].tolist(), SamplingParams(max_tokens=1))
+    md, tok, _ = eng.runner.prepare(eng.scheduler.schedule())
+    with torch.inference_mode(), set_forward_context(ForwardContext(md, eng.runner.kv_caches, eng.pstate)):
+        h, _ = model(tok)
+        got = model.compute_logits(h).float()
+    err = (got - want).abs().max().item()
+    assert err <= tol * max(1.0, want.abs().max().item()), f"{case[0]}: max |logit difference| {err:.3g}"
+    # and the engine's own path (scheduler, KV cache, sampler): greedy continuation = the reference's argmax chain
+    out = llm.generate([ids[0].tolist()], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))[0].token_ids
+    seq = ids.clone()
+    with torch.no_grad():
+        for _ in range(3):
+            nxt = hf(seq).logits[0, -1].argmax().view(1, 1)
+            seq = torch.cat([seq, nxt], 1)
+    assert out == seq[0, -3:].tolist()

@@ -105,8 +105,9 @@ def test_gpt_oss_checkpoint_layout():
     h = x @ gu[e] + gub[e]                                   # checkpoint semantics: interleaved gate / up
     gate, up = h[:, 0::2], h[:, 1::2]
     mine = x @ ex.w13.data[e].T + ex.b13.data[e]
-    torch.testing.assert_close(mine[:, :I], gate, atol=1e-5, rtol=1e-5)
-    torch.testing.assert_close(mine[:, I:], up, atol=1e-5, rtol=1e-5)
+    # the expert weights keep the interleaved order the family's activation reads
+    torch.testing.assert_close(mine[:, 0::2], gate, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(mine[:, 1::2], up, atol=1e-5, rtol=1e-5)
     a = torch.randn(3, I, generator=g)
     torch.testing.assert_close(a @ ex.w2.data[e].T + ex.b2.data[e], a @ dn[e] + dnb[e], atol=1e-5, rtol=1e-5)
     assert torch.equal(m.layers["1"].self_attn.sinks.data, sinks)

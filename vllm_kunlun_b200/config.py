@@ -30,6 +30,7 @@ class RopeScaling:
     mscale_all_dim: float = 0.0
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
+    truncate: bool = True   # YaRN: round the correction range to whole dimensions (gpt-oss checkpoints say False)
 
 
 @dataclass
@@ -68,7 +69,9 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     num_shared_experts: int = 0
-    shared_expert_gate: bool = False  # Qwen3-Next sigmoid gate on the shared expert
+    shared_expert_gate: bool = False  # Qwen2-MoE / Qwen3-Next sigmoid gate on the shared expert
+    shared_intermediate_size: Optional[int] = None  # width of the shared expert when the checkpoint names it (else
+    # num_shared_experts x moe_intermediate_size)
     first_dense_layers: int = 0
     moe_layer_freq: int = 1
     scoring_func: str = "softmax"  # "softmax" | "sigmoid"
@@ -192,7 +195,8 @@ class ModelConfig:
                 type="yarn", factor=float(rs.get("factor", 1.0)),
                 original_max_position=int(rs.get("original_max_position_embeddings", 4096)),
                 beta_fast=float(rs.get("beta_fast", 32)), beta_slow=float(rs.get("beta_slow", 1)),
-                mscale=float(rs.get("mscale", 1.0)), mscale_all_dim=float(rs.get("mscale_all_dim", 0.0)))
+                mscale=float(rs.get("mscale", 1.0)), mscale_all_dim=float(rs.get("mscale_all_dim", 0.0)),
+                truncate=bool(rs.get("truncate", True)))
         elif rtype == "llama3":
             rope = RopeScaling(
                 type="llama3", factor=float(rs.get("factor", 8.0)),
@@ -232,7 +236,9 @@ class ModelConfig:
             head_dim=cfg.get("head_dim") or h // nh,
             intermediate_size=cfg.get("intermediate_size", 4 * h),
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
-            rope_theta=float(cfg.get("rope_theta", 10000.0)), rope_scaling=rope,
+            # transformers 5 writes rope_theta (and partial_rotary_factor) inside rope_parameters
+            rope_theta=float(cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
+            rope_scaling=rope,
             max_position=cfg.get("max_position_embeddings", 8192),
             tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
             qkv_bias=bool(cfg.get("attention_bias", arch.startswith("Qwen2"))),
@@ -244,6 +250,7 @@ class ModelConfig:
         if arch.startswith("Qwen2") or arch.startswith("Qwen3"):
             kw["sliding_window"] = None
         n_exp = cfg.get("num_experts") or cfg.get("n_routed_experts") or cfg.get("num_local_experts") or 0
+        v3_like = arch in ("DeepseekV3ForCausalLM", "DeepseekV32ForCausalLM", "KimiK2ForCausalLM", "GlmMoeDsaForCausalLM")
         if n_exp:
             kw.update(
                 num_experts=n_exp,
@@ -252,11 +259,13 @@ class ModelConfig:
                 num_shared_experts=cfg.get("n_shared_experts", 0) or 0,
                 first_dense_layers=cfg.get("first_k_dense_replace", 0),
                 moe_layer_freq=cfg.get("moe_layer_freq", 1) or 1,
-                scoring_func=cfg.get("scoring_func", "softmax"),
+                # DeepSeek-V3 and its descendants score with a sigmoid and a correction bias; configs written by
+                # transformers 5 no longer carry the two keys that said so
+                scoring_func=cfg.get("scoring_func", "sigmoid" if v3_like else "softmax"),
                 norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
                 n_group=cfg.get("n_group", 1) or 1, topk_group=cfg.get("topk_group", 1) or 1,
                 routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0)),
-                router_bias=cfg.get("topk_method") == "noaux_tc",
+                router_bias=(cfg.get("topk_method") == "noaux_tc") if "topk_method" in cfg else v3_like,
             )
         if use_mla:
             kw.update(
@@ -268,6 +277,16 @@ class ModelConfig:
                 index_head_dim=cfg.get("index_head_dim", 0) or 0,
                 num_mtp_layers=cfg.get("num_nextn_predict_layers", 0) or 0,
             )
+        if n_exp and cfg.get("shared_expert_intermediate_size"):
+            # Qwen2-MoE / Qwen3-Next: one shared expert of its own width behind a sigmoid gate
+            kw.update(num_shared_experts=1, shared_expert_gate=True,
+                      shared_intermediate_size=int(cfg["shared_expert_intermediate_size"]))
+        if arch == "Glm4MoeForCausalLM":
+            # GLM-4.5 / 4.6 / 4.7: GQA attention with partial rotary embedding and optional per-head q / k norm,
+            # DeepSeek-V3 style MoE (sigmoid scores + correction bias, grouped top-k, shared experts, dense first layers)
+            kw.update(scoring_func="sigmoid", router_bias=True, qk_norm=bool(cfg.get("use_qk_norm", False)),
+                      rotary_dim=int(kw["head_dim"] * float(cfg.get("partial_rotary_factor") or (cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or 0.5)),
+                      num_mtp_layers=cfg.get("num_nextn_predict_layers", 0) or 0)
         if arch == "GptOssForCausalLM":
             kw.update(attention_sinks=True, sliding_window_pattern=2, hidden_act="swigluoai",
                       moe_bias=True, qkv_bias=True, o_bias=True,
@@ -279,7 +298,7 @@ class ModelConfig:
                 gdn_num_v_heads=tc.get("linear_num_value_heads", 32), gdn_head_k_dim=tc.get("linear_key_head_dim", 128),
                 gdn_head_v_dim=tc.get("linear_value_head_dim", 128), gdn_conv_kernel=tc.get("linear_conv_kernel_dim", 4),
                 attn_output_gate=True, gemma_norm=True, qk_norm=True,
-                rotary_dim=int(kw["head_dim"] * float(tc.get("partial_rotary_factor", 0.25))),
+                rotary_dim=int(kw["head_dim"] * float(tc.get("partial_rotary_factor") or (tc.get("rope_parameters") or {}).get("partial_rotary_factor") or 0.25)),
                 num_shared_experts=1 if tc.get("shared_expert_intermediate_size") else 0, shared_expert_gate=True)
         vcfg = cfg.get("vision_config")
         if vcfg and ("VL" in arch or arch.startswith("Intern")):

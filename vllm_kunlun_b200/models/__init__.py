@@ -28,6 +28,7 @@ _REGISTRY = {
     "DeepseekV3ForCausalLM": "deepseek:DeepseekForCausalLM",
     "DeepseekV32ForCausalLM": "deepseek:DeepseekForCausalLM",
     "GlmMoeDsaForCausalLM": "deepseek:DeepseekForCausalLM",
+    "Glm4MoeForCausalLM": "deepseek:DeepseekForCausalLM",     # GQA attention + DeepSeek-V3 style MoE
     "KimiK2ForCausalLM": "deepseek:DeepseekForCausalLM",
     "DeepSeekMTPModel": "deepseek_mtp:DeepSeekMTP",
     # hybrid linear attention

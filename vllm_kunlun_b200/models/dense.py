@@ -301,10 +301,14 @@ class DenseForCausalLM(nn.Module):
         """Checkpoint tensor name -> (module, param name, shard id) or None when not on this stage."""
         name = name.removeprefix("model.")
         shard = None
+        plain = name
         for ck, fused, sid in STACKED:
             if ck in name:
                 name, shard = name.replace(ck, fused), sid
                 break
+        if shard is not None and self._walk(name.split(".")) is None and self._walk(plain.split(".")) is not None:
+            # the module keeps this projection on its own (MLA without a low-rank query: ``self_attn.q_proj``)
+            name, shard = plain, None
         parts = name.split(".")
         mod = self
         for i, p in enumerate(parts[:-1]):
@@ -319,6 +323,22 @@ class DenseForCausalLM(nn.Module):
                 return None
             mod = getattr(mod, p)
         return mod, parts[-1], shard
+
+    def _walk(self, parts):
+        """The module that owns parameter path ``parts`` on this stage, or None."""
+        mod = self
+        for i, p in enumerate(parts[:-1]):
+            if p == "layers":
+                continue
+            if i > 0 and parts[i - 1] == "layers":
+                if p not in self.layers:
+                    return None
+                mod = self.layers[p]
+                continue
+            if not hasattr(mod, p) or getattr(mod, p) is None:
+                return None
+            mod = getattr(mod, p)
+        return mod
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
         loaded = set()

@@ -34,12 +34,15 @@ class GptOssForCausalLM(MoEForCausalLM):
                 sel = slice(ex.first, ex.first + ex.num_local)
                 key = parts[4]
                 if key == "gate_up_proj":
+                    # the clamped SwiGLU of this family (``ops.act_and_mul(..., "swigluoai")``) reads its input as
+                    # interleaved (gate_0, up_0, gate_1, up_1, ...), the checkpoint's own order: keep it, taking this
+                    # rank's slice of the intermediate dimension pair by pair
                     gate, up = w[sel, :, 0::2], w[sel, :, 1::2]  # [E, H, I_total]
-                    ex.w13.data[:, :I].copy_(gate[:, :, lo:lo + I].transpose(1, 2))
-                    ex.w13.data[:, I:].copy_(up[:, :, lo:lo + I].transpose(1, 2))
+                    g, u = gate[:, :, lo:lo + I].transpose(1, 2), up[:, :, lo:lo + I].transpose(1, 2)   # [E, I, H]
+                    ex.w13.data.copy_(torch.stack([g, u], 2).reshape(g.shape[0], 2 * I, -1))
                 elif key == "gate_up_proj_bias":
-                    ex.b13.data[:, :I].copy_(w[sel, 0::2][:, lo:lo + I])
-                    ex.b13.data[:, I:].copy_(w[sel, 1::2][:, lo:lo + I])
+                    g, u = w[sel, 0::2][:, lo:lo + I], w[sel, 1::2][:, lo:lo + I]
+                    ex.b13.data.copy_(torch.stack([g, u], 2).reshape(g.shape[0], 2 * I))
                 elif key == "down_proj":
                     ex.w2.data.copy_(w[sel, lo:lo + I, :].transpose(1, 2))
                 elif key == "down_proj_bias":

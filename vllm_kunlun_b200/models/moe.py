@@ -156,8 +156,9 @@ class SparseMoEBlock(nn.Module):
         self.experts = FusedExperts(cfg, dtype, device)
         self.shared_experts = None
         if cfg.num_shared_experts:
-            self.shared_experts = GatedMLP(cfg.hidden_size, cfg.moe_intermediate_size * cfg.num_shared_experts, dtype,
-                                           device, cfg.quantization, "silu", reduce_results=False)
+            self.shared_experts = GatedMLP(cfg.hidden_size,
+                                           cfg.shared_intermediate_size or cfg.moe_intermediate_size * cfg.num_shared_experts,
+                                           dtype, device, cfg.quantization, "silu", reduce_results=False)
         self.shared_expert_gate = (ReplicatedLinear(cfg.hidden_size, 1, dtype=dtype, device=device)
                                    if cfg.shared_expert_gate else None)
 
@@ -282,6 +283,21 @@ class MoEForCausalLM(DenseForCausalLM):
             if ".mlp.experts." in name and ".shared" not in name:
                 # model.layers.L.mlp.experts.E.{gate,up,down}_proj.{weight,weight_scale_inv}
                 parts = name.removeprefix("model.").split(".")
+                if parts[4] in ("gate_up_proj", "down_proj") and w.dim() == 3:
+                    # stacked form (checkpoints saved by transformers 5: experts.gate_up_proj [E, 2 I, H] with the gate
+                    # rows first, experts.down_proj [E, H, I])
+                    li = parts[1]
+                    if li in self.layers and isinstance(self.layers[li].mlp, SparseMoEBlock):
+                        ex = self.layers[li].mlp.experts
+                        for e in range(w.shape[0]):
+                            if parts[4] == "down_proj":
+                                ex.load_expert(e, "down_proj", "weight", w[e])
+                            else:
+                                half = w.shape[1] // 2
+                                ex.load_expert(e, "gate_proj", "weight", w[e, :half])
+                                ex.load_expert(e, "up_proj", "weight", w[e, half:])
+                        loaded.add(name)
+                    continue
                 li, e, which, pname = parts[1], int(parts[4]), parts[5], parts[6]
                 if li in self.layers and isinstance(self.layers[li].mlp, SparseMoEBlock):
                     self.layers[li].mlp.experts.load_expert(e, which, pname, w)
@@ -289,6 +305,7 @@ class MoEForCausalLM(DenseForCausalLM):
                 continue
             name = name.replace(".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias")
             name = name.replace(".block_sparse_moe.", ".mlp.")
+            name = name.replace(".mlp.shared_expert.", ".mlp.shared_experts.")      # Qwen2-MoE spelling
             rest.append((name, w))
         loaded |= super().load_weights(rest)
         return loaded

@@ -138,9 +138,11 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling=None) -> tuple[torch.Te
         out = torch.where(mid, (1 - smooth) * inv / scaling.factor + smooth * inv, out)
         return out, mscale
     if scaling.type == "yarn":
-        lo = max(math.floor(_yarn_find_dim(scaling.beta_fast, rotary_dim, theta, scaling.original_max_position)), 0)
-        hi = min(math.ceil(_yarn_find_dim(scaling.beta_slow, rotary_dim, theta, scaling.original_max_position)),
-                 rotary_dim - 1)
+        lo = _yarn_find_dim(scaling.beta_fast, rotary_dim, theta, scaling.original_max_position)
+        hi = _yarn_find_dim(scaling.beta_slow, rotary_dim, theta, scaling.original_max_position)
+        if getattr(scaling, "truncate", True):      # whole dimensions (DeepSeek); gpt-oss keeps the fractions
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, rotary_dim - 1)
         if lo == hi:
             hi += 0.001
         ramp = ((torch.arange(rotary_dim // 2, dtype=torch.float32) - lo) / (hi - lo)).clamp(0, 1)
