@@ -120,3 +120,79 @@ def test_logits_match_the_transformers_implementation(case):
             nxt = hf(seq).logits[0, -1].argmax().view(1, 1)
             seq = torch.cat([seq, nxt], 1)
     assert out == seq[0, -3:].tolist()
+
+
+_TOK = dict(image_token_id=150, video_token_id=151, vision_start_token_id=152, vision_end_token_id=153)
+VL_CASES = [
+    # Qwen2-VL: LayerNorm blocks, quick-GELU MLP, full attention per frame, M-RoPE decoder
+    ("qwen2_vl", "Qwen2VLConfig", "Qwen2VLForConditionalGeneration", "Qwen2VLForConditionalGeneration",
+     dict(rope_scaling={"type": "mrope", "mrope_section": [4, 6, 6]}),
+     dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, patch_size=4, spatial_merge_size=2,
+          temporal_patch_size=2, in_channels=3)),
+    # Qwen2.5-VL: RMSNorm blocks, gated MLP (gate / up / down tensors), windowed attention except in listed blocks
+    ("qwen2_5_vl_windows", "Qwen2_5_VLConfig", "Qwen2_5_VLForConditionalGeneration", "Qwen2_5_VLForConditionalGeneration",
+     dict(rope_scaling={"type": "mrope", "mrope_section": [4, 6, 6]}),
+     dict(depth=3, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
+          spatial_merge_size=2, temporal_patch_size=2, in_channels=3, window_size=16, fullatt_block_indexes=[1])),
+    # Qwen3-VL: patch bias, interpolated position table, tanh-GELU MLP, deep-stack features, interleaved M-RoPE
+    ("qwen3_vl_deepstack", "Qwen3VLConfig", "Qwen3VLForConditionalGeneration", "Qwen3VLForConditionalGeneration",
+     dict(head_dim=32, rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True}),
+     dict(depth=3, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
+          spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=64,
+          deepstack_visual_indexes=[0, 1])),
+]
+
+
+@pytest.mark.parametrize("case", VL_CASES, ids=[c[0] for c in VL_CASES])
+def test_vision_language_models_match_the_transformers_implementation(case):
+    """Two images of different grids in one prompt: the vision tower's embeddings (and deep-stack features) equal the
+    reference's, and greedy decoding through the engine (placeholder rows replaced during prefill, M-RoPE positions,
+    deep-stack injection) gives the reference's tokens."""
+    _, cfg_name, cls_name, arch, text_kw, vis_kw = case
+    if not (hasattr(transformers, cfg_name) and hasattr(transformers, cls_name)):
+        pytest.skip(f"transformers {transformers.__version__} has no {cls_name}")
+    torch.manual_seed(0)
+    tc = dict(vocab_size=200, hidden_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=256, max_position_embeddings=512, rms_norm_eps=1e-5, **text_kw)
+    hf_cfg = getattr(transformers, cfg_name)(text_config=tc, vision_config=vis_kw, **_TOK)
+    hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
+    _randomise(hf)
+    vc = hf_cfg.vision_config
+    grids = [(1, 8, 12), (1, 4, 6)]
+    patch_dim = 3 * vc.temporal_patch_size * vc.patch_size ** 2
+    px = torch.randn(sum(t * h * w for t, h, w in grids), patch_dim)
+    m2 = vc.spatial_merge_size ** 2
+    img = hf_cfg.image_token_id
+    ids = [5, 6, 7] + [img] * (8 * 12 // m2) + [8, 9] + [img] * (4 * 6 // m2) + [10, 11, 12]
+    gthw = torch.tensor(grids)
+
+    def hf_logits(seq):
+        with torch.no_grad():
+            return hf(input_ids=seq, pixel_values=px, image_grid_thw=gthw, mm_token_type_ids=(seq == img).long()).logits[0]
+
+    seq = torch.tensor([ids])
+    want = []
+    for _ in range(3):
+        want.append(hf_logits(seq)[-1].argmax().item())
+        seq = torch.cat([seq, torch.tensor([[want[-1]]])], 1)
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = [arch], "float32"
+    cfg = ModelConfig.from_hf_config(d)
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=32)
+    model = llm.engine.runner.model
+    with torch.inference_mode():
+        loaded = model.load_weights(list(hf.state_dict().items()))
+    assert len(loaded) == len(hf.state_dict())
+    with torch.no_grad():
+        ref = hf.model.visual(px, grid_thw=gthw)
+    ref_main = ref.pooler_output if hasattr(ref, "pooler_output") else (ref[0] if isinstance(ref, tuple) else ref)
+    deep = getattr(ref, "deepstack_features", None) if not isinstance(ref, tuple) else (ref[1] if len(ref) > 1 else None)
+    with torch.inference_mode():
+        mine = model.embed_multimodal(px, [list(g) for g in grids]).float()
+    H = ref_main.shape[-1]
+    assert (mine[:, :H] - ref_main.float()).abs().max().item() < 1e-4
+    for k, f in enumerate(deep or []):
+        assert (mine[:, (k + 1) * H:(k + 2) * H] - f.float()).abs().max().item() < 1e-4
+    out = llm.generate([ids], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True),
+                       multi_modal_data={"pixel_values": px, "image_grid_thw": [list(g) for g in grids]})[0].token_ids
+    assert out == want

@@ -312,13 +312,21 @@ class ModelConfig:
                 intermediate=vcfg.get("intermediate_size", int(vcfg.get("embed_dim", 1280) * vcfg.get("mlp_ratio", 4))),
                 in_channels=vcfg.get("in_channels", vcfg.get("in_chans", 3)),
                 norm="rmsnorm" if "2_5" in arch else "layernorm", gated_mlp="2_5" in arch,
-                act="gelu" if intern else "quick_gelu", layer_scale=intern, image_size=vcfg.get("image_size", 448),
+                act="gelu" if intern else ("gelu_tanh" if "Qwen3" in arch else "quick_gelu"), layer_scale=intern,
+                image_size=vcfg.get("image_size", 448),
+                # Qwen2.5-VL: windowed attention in all blocks but the listed ones (window in pixels); Qwen3-VL: a
+                # learned position table interpolated to the image grid, a bias on the patch projection, exact GELU
+                # in the mergers
+                window_size=int(vcfg.get("window_size") or 0) if "2_5" in arch else 0,
+                fullatt_blocks=list(vcfg.get("fullatt_block_indexes") or ()),
+                num_pos=int(vcfg.get("num_position_embeddings") or 0) if "Qwen3" in arch else 0,
+                patch_bias="Qwen3" in arch,
                 downsample=cfg.get("downsample_ratio", 0.5), image_token_id=cfg.get("image_token_id", 151655),
                 text_architecture=(tc.get("architectures") or ["Qwen2ForCausalLM"])[0] if intern else
                 ("Qwen3MoeForCausalLM" if ("Qwen3" in arch and "Moe" in arch) else
                  "Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"),
                 deepstack_indexes=list(vcfg.get("deepstack_visual_indexes", ())))
-            rsc = tc.get("rope_scaling") or {}
+            rsc = tc.get("rope_scaling") or tc.get("rope_parameters") or {}
             kw["mrope_section"] = tuple(rsc.get("mrope_section", ()))
         if arch.startswith("Gemma"):
             kw.update(num_kv_shared_layers=cfg.get("num_kv_shared_layers", 0) or 0,

@@ -71,6 +71,8 @@ class VisionBlock(nn.Module):
             m = ops.act_and_mul(m, "silu")
         elif self.act == "quick_gelu":
             m = ops.quick_gelu(m)
+        elif self.act == "gelu_tanh":
+            m = torch.nn.functional.gelu(m.float(), approximate="tanh").to(m.dtype)
         else:
             m = torch.nn.functional.gelu(m.float()).to(m.dtype)
         m = self.fc2(m)
@@ -85,7 +87,13 @@ class QwenVisionTransformer(nn.Module):
         self.vc = vc
         h = vc["hidden"]
         self.patch_dim = vc.get("in_channels", 3) * vc.get("temporal_patch", 2) * vc["patch"] ** 2
-        self.patch_embed = ReplicatedLinear(self.patch_dim, h, bias=False, dtype=dtype, device=device)
+        self.patch_embed = ReplicatedLinear(self.patch_dim, h, bias=bool(vc.get("patch_bias")), dtype=dtype, device=device)
+        # Qwen3-VL: learned positions on a square table, interpolated bilinearly to every image's grid
+        self.num_pos = int(vc.get("num_pos") or 0)
+        self.pos_embed = param(self.num_pos, h, dtype=dtype, device=device) if self.num_pos else None
+        # Qwen2.5-VL: attention inside windows of window_size pixels, except in the listed blocks
+        self.window = int(vc.get("window_size") or 0) // self.merge_of(vc) // vc["patch"] if vc.get("window_size") else 0
+        self.fullatt = set(vc.get("fullatt_blocks") or ())
         self.blocks = nn.ModuleList([VisionBlock(vc, dtype, device) for _ in range(vc["depth"])])
         self.merge = vc.get("merge", 2)
         self.ln_q = _Norm(h, vc.get("eps", 1e-6), vc.get("norm", "layernorm"), dtype, device)
@@ -102,6 +110,54 @@ class QwenVisionTransformer(nn.Module):
                                      for _ in self.deepstack_indexes])
         self.ds_fc2 = nn.ModuleList([ReplicatedLinear(mh, out_hidden, bias=True, dtype=dtype, device=device)
                                      for _ in self.deepstack_indexes])
+
+    @staticmethod
+    def merge_of(vc: dict) -> int:
+        return vc.get("merge", 2)
+
+    def window_order(self, grid_thw):
+        """Qwen2.5-VL windowed attention: the order of the merged tokens (groups of ``merge^2`` patches) that puts
+        every ``window x window`` tile of merged tokens of a frame together, and the cumulative PATCH counts of the
+        tiles.  Tiles at the right / bottom edge are partial; like the upstream model, a grid that is an exact
+        multiple of the window still gets a (then empty) extra tile row and column, which changes nothing."""
+        wz, unit = self.window, self.merge ** 2
+        order, cu, base = [], [0], 0
+        for t, h, w in grid_thw:
+            lh, lw = h // self.merge, w // self.merge
+            idx = torch.arange(t * lh * lw).reshape(t, lh, lw)
+            ph, pw = wz - lh % wz, wz - lw % wz
+            pad = torch.nn.functional.pad(idx, (0, pw, 0, ph), value=-1)
+            nh, nw = (lh + ph) // wz, (lw + pw) // wz
+            tiles = pad.reshape(t, nh, wz, nw, wz).permute(0, 1, 3, 2, 4).reshape(t * nh * nw, wz * wz)
+            counts = (tiles >= 0).sum(1)
+            flat = tiles.reshape(-1)
+            order.append(flat[flat >= 0] + base)
+            for c in counts.tolist():
+                if c:
+                    cu.append(cu[-1] + c * unit)
+            base += t * lh * lw
+        return torch.cat(order), torch.tensor(cu, dtype=torch.int32)
+
+    def interpolated_positions(self, grid_thw, device, dtype):
+        """Qwen3-VL: the position table (a ``side x side`` square) sampled bilinearly on each image's ``h x w`` grid,
+        in the tower's token order (``merge x merge`` windows contiguous), repeated for every frame."""
+        side = int(round(self.num_pos ** 0.5))
+        table = self.pos_embed.float()
+        out = []
+        for t, h, w in grid_thw:
+            ys = torch.linspace(0, side - 1, h, device=device)
+            xs = torch.linspace(0, side - 1, w, device=device)
+            y0, x0 = ys.floor().long(), xs.floor().long()
+            y1, x1 = (y0 + 1).clamp(max=side - 1), (x0 + 1).clamp(max=side - 1)
+            fy, fx = (ys - y0).unsqueeze(1), (xs - x0).unsqueeze(0)                    # [h, 1], [1, w]
+            def at(yy, xx):
+                return table[(yy.unsqueeze(1) * side + xx.unsqueeze(0)).reshape(-1)].reshape(h, w, -1)
+            pe = (at(y0, x0) * ((1 - fy) * (1 - fx)).unsqueeze(-1) + at(y0, x1) * ((1 - fy) * fx).unsqueeze(-1)
+                  + at(y1, x0) * (fy * (1 - fx)).unsqueeze(-1) + at(y1, x1) * (fy * fx).unsqueeze(-1))
+            m = self.merge
+            pe = pe.reshape(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(pe.repeat(t, 1))
+        return torch.cat(out, 0).to(dtype)
 
     def rot_pos_emb(self, grid_thw, device):
         """Per-token (h, w) rotary angles; tokens are ordered so that each ``merge x merge`` window is contiguous."""
@@ -120,15 +176,29 @@ class QwenVisionTransformer(nn.Module):
     def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
         """``pixel_values [n_patches, patch_dim]`` -> ``[n_patches / merge^2, out_hidden * (1 + n_deepstack)]``: the
         main embedding followed by the deep-stack features of the same tokens."""
+        grid_thw = [tuple(int(v) for v in g) for g in grid_thw]
         x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        if self.pos_embed is not None:
+            x = x + self.interpolated_positions(grid_thw, x.device, x.dtype)
         cos, sin = self.rot_pos_emb(grid_thw, x.device)
         lens = torch.tensor([h * w for t, h, w in grid_thw for _ in range(t)], dtype=torch.int32)
         cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
         cu[1:] = lens.cumsum(0)
         cu = cu.to(x.device)
+        cu_win, order = None, None
+        if self.window:
+            # tokens travel through the blocks in window order (whole merge groups move together)
+            order, cu_win = self.window_order(grid_thw)
+            unit = self.merge ** 2
+            order = order.to(x.device)
+
+            def reorder(t):
+                return t.reshape(-1, unit, t.shape[-1])[order].reshape(t.shape)
+            x, cos, sin = reorder(x), reorder(cos), reorder(sin)
+            cu_win = cu_win.to(x.device)
         deep = []
         for li, blk in enumerate(self.blocks):
-            x = blk(x, cu, cos, sin)
+            x = blk(x, cu if (cu_win is None or li in self.fullatt) else cu_win, cos, sin)
             if li in self.deepstack_indexes:
                 k = self.deepstack_indexes.index(li)
                 d = self.ds_norm[k](x.reshape(-1, x.shape[-1] * self.merge ** 2))
@@ -137,6 +207,8 @@ class QwenVisionTransformer(nn.Module):
         x = self.ln_q(x).reshape(-1, x.shape[-1] * self.merge ** 2)
         x = torch.nn.functional.gelu(self.merger_fc1(x).float()).to(x.dtype)
         x = self.merger_fc2(x)
+        if order is not None:
+            x = x[torch.argsort(order)]      # back to the image order the prompt's placeholders follow
         return torch.cat([x] + deep, -1) if deep else x
 
 
@@ -312,10 +384,23 @@ class _VLBase(nn.Module):
         text, loaded = [], set()
         vis = dict(self.visual.named_parameters())
         for name, w in weights:
+            # checkpoints written by transformers 5 nest both halves under ``model.``: ``model.visual.*`` and
+            # ``model.language_model.*`` (older ones: ``visual.*`` and ``model.*`` / ``language_model.model.*``)
+            if name.startswith("model.visual."):
+                name = name[len("model."):]
+            elif name.startswith("model.language_model."):
+                name = "model." + name[len("model.language_model."):]
             v = self._vision_name(name)
             if v is not None:
+                half = None
+                if isinstance(v, tuple):        # (parameter, which half of its rows): gate / up of a gated MLP
+                    v, half = v
                 if v in vis:
-                    vis[v].data.copy_(w.reshape(vis[v].shape))
+                    if half is None:
+                        vis[v].data.copy_(w.reshape(vis[v].shape))
+                    else:
+                        n = vis[v].shape[0] // 2
+                        vis[v].data[half * n:(half + 1) * n].copy_(w)
                     loaded.add(name)
                 continue
             text.append((name.replace("language_model.model.", "model.").replace("language_model.", ""), w))
@@ -328,37 +413,22 @@ class _VLBase(nn.Module):
 class QwenVLForConditionalGeneration(_VLBase):
     """Qwen2-VL / Qwen2.5-VL / Qwen3-VL."""
 
-    _MAP = {"patch_embed.proj.weight": "patch_embed.weight", "attn.qkv.": "qkv.", "attn.proj.": "proj.",
-            "mlp.fc1.": "fc1.", "mlp.fc2.": "fc2.", "merger.ln_q.": "ln_q.", "merger.mlp.0.": "merger_fc1.",
-            "merger.mlp.2.": "merger_fc2."}
+    _MAP = {"patch_embed.proj.weight": "patch_embed.weight", "patch_embed.proj.bias": "patch_embed.bias",
+            "pos_embed.weight": "pos_embed", "attn.qkv.": "qkv.", "attn.proj.": "proj.",
+            "mlp.fc1.": "fc1.", "mlp.fc2.": "fc2.", "mlp.linear_fc1.": "fc1.", "mlp.linear_fc2.": "fc2.",
+            "mlp.down_proj.": "fc2.", "merger.ln_q.": "ln_q.", "merger.mlp.0.": "merger_fc1.",
+            "merger.mlp.2.": "merger_fc2.", "deepstack_merger_list.": "ds_", "merger.norm.": "ln_q.",
+            "merger.linear_fc1.": "merger_fc1.", "merger.linear_fc2.": "merger_fc2."}
 
     def _vision_name(self, name):
         if not name.startswith("visual."):
             return None
         n = name[len("visual."):]
+        for half, key in enumerate(("mlp.gate_proj.", "mlp.up_proj.")):     # Qwen2.5-VL: gate | up stacked in fc1
+            if key in n:
+                return n.replace(key, "fc1."), half
         for a, b in self._MAP.items():
             n = n.replace(a, b)
-        return n
-
-
-class Qwen3VLMoeForConditionalGeneration(QwenVLForConditionalGeneration):
-    """Qwen3-VL with the Qwen3-MoE decoder (``models/qwen3_vl_moe.py`` of the reference): the same tower with
-    deep-stack features, the text side is the sparse-MoE decoder of this package."""
-
-    _MAP = dict(QwenVLForConditionalGeneration._MAP, **{"deepstack_merger_list.": "ds_", "merger.norm.": "ln_q.",
-                                                         "merger.linear_fc1.": "merger_fc1.",
-                                                         "merger.linear_fc2.": "merger_fc2."})
-
-    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
-        cfg.vision.setdefault("text_architecture", "Qwen3MoeForCausalLM")
-        if cfg.vision["text_architecture"] in ("Qwen3ForCausalLM", "Qwen2ForCausalLM") and cfg.num_experts:
-            cfg.vision["text_architecture"] = "Qwen3MoeForCausalLM"
-        super().__init__(cfg, device, dtype)
-
-    def _vision_name(self, name):
-        n = super()._vision_name(name)
-        if n is None:
-            return None
         import re
         # deepstack_merger_list.<k>.{norm,linear_fc1,linear_fc2}.* -> ds_{norm,fc1,fc2}.<k>.*
         m = re.match(r"ds_(\d+)\.(norm|linear_fc1|linear_fc2)\.(.*)", n)
@@ -366,6 +436,17 @@ class Qwen3VLMoeForConditionalGeneration(QwenVLForConditionalGeneration):
             kind = {"norm": "ds_norm", "linear_fc1": "ds_fc1", "linear_fc2": "ds_fc2"}[m.group(2)]
             return f"{kind}.{m.group(1)}.{m.group(3)}"
         return n
+
+
+class Qwen3VLMoeForConditionalGeneration(QwenVLForConditionalGeneration):
+    """Qwen3-VL with the Qwen3-MoE decoder (``models/qwen3_vl_moe.py`` of the reference): the same tower with
+    deep-stack features, the text side is the sparse-MoE decoder of this package."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        cfg.vision.setdefault("text_architecture", "Qwen3MoeForCausalLM")
+        if cfg.vision["text_architecture"] in ("Qwen3ForCausalLM", "Qwen2ForCausalLM") and cfg.num_experts:
+            cfg.vision["text_architecture"] = "Qwen3MoeForCausalLM"
+        super().__init__(cfg, device, dtype)
 
 
 class InternVLChatModel(_VLBase):
