@@ -23,6 +23,9 @@ DS = dict(vocab_size=160, hidden_size=128, num_hidden_layers=3, num_attention_he
           max_position_embeddings=256, rms_norm_eps=1e-5)
 GPT_OSS = dict(vocab_size=160, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                head_dim=32, intermediate_size=64, num_local_experts=4, num_experts_per_tok=2, max_position_embeddings=256)
+Q35 = dict(vocab_size=160, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+           intermediate_size=256, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+           linear_value_head_dim=32, linear_conv_kernel_dim=4, full_attention_interval=4, max_position_embeddings=256)
 YARN = {"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 64,
         "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0}
 
@@ -70,6 +73,14 @@ CASES = [
           num_experts_per_tok=2, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
           linear_value_head_dim=32, linear_conv_kernel_dim=4, full_attention_interval=4, partial_rotary_factor=0.25,
           max_position_embeddings=256, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]), 5e-4),
+    ("qwen3_5_dense_hybrid", "Qwen3_5TextConfig", "Qwen3_5ForCausalLM", "Qwen3_5ForCausalLM", dict(Q35), 5e-4),
+    ("qwen3_5_moe_hybrid", "Qwen3_5MoeTextConfig", "Qwen3_5MoeForCausalLM", "Qwen3_5MoeForCausalLM",
+     dict(Q35, moe_intermediate_size=64, shared_expert_intermediate_size=64, num_experts=4, num_experts_per_tok=2), 5e-4),
+    # GLM-MoE-DSA (DeepSeek-V3.2 style sparse attention): with a top-k above the prompt length every key is selected,
+    # so the whole path (indexer, index conversion, sparse MLA) must reproduce dense attention
+    ("glm_moe_dsa_indexer", "GlmMoeDsaConfig", "GlmMoeDsaForCausalLM", "GlmMoeDsaForCausalLM",
+     dict(DS, q_lora_rank=64, n_shared_experts=1, n_group=1, topk_group=1, index_topk=64, index_n_heads=4,
+          index_head_dim=128, mlp_layer_types=["dense", "sparse", "sparse"]), 5e-4),
 ]
 
 
@@ -91,6 +102,7 @@ def test_logits_match_the_transformers_implementation(case):
         pytest.skip(f"transformers {transformers.__version__} has no {cls_name}")
     torch.manual_seed(0)
     hf_cfg = getattr(transformers, cfg_name)(**kwargs)
+    hf_cfg._attn_implementation = "eager"      # the plain-PyTorch attention of the reference implementation
     hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
     _randomise(hf)
     ids = torch.randint(1, hf_cfg.vocab_size - 1, (1, 19))
@@ -99,11 +111,12 @@ def test_logits_match_the_transformers_implementation(case):
     d = hf_cfg.to_dict()
     d["architectures"], d["torch_dtype"] = [arch], "float32"
     cfg = ModelConfig.from_hf_config(d)
-    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
+    llm = LLM(cfg, device="cpu", block_size=64 if cfg.index_topk else 16, max_model_len=128, max_num_seqs=4,
+              num_gpu_blocks=32)
     model = llm.engine.runner.model
     with torch.inference_mode():
         loaded = model.load_weights(list(hf.state_dict().items()))
-    assert len(loaded) >= len(hf.state_dict()) - 8, "most checkpoint tensors must find their parameter"
+    assert len(loaded) >= len(hf.state_dict()) - 12, "most checkpoint tensors must find their parameter"
     eng = llm.engine
     eng.add_request(ids[0].tolist(), SamplingParams(max_tokens=1))
     md, tok, _ = eng.runner.prepare(eng.scheduler.schedule())

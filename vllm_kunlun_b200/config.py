@@ -257,7 +257,7 @@ class ModelConfig:
                 num_experts_per_tok=cfg.get("num_experts_per_tok", 8),
                 moe_intermediate_size=cfg.get("moe_intermediate_size", cfg.get("intermediate_size")),
                 num_shared_experts=cfg.get("n_shared_experts", 0) or 0,
-                first_dense_layers=cfg.get("first_k_dense_replace", 0),
+                first_dense_layers=_leading_dense(cfg),
                 moe_layer_freq=cfg.get("moe_layer_freq", 1) or 1,
                 # DeepSeek-V3 and its descendants score with a sigmoid and a correction bias; configs written by
                 # transformers 5 no longer carry the two keys that said so
@@ -272,7 +272,9 @@ class ModelConfig:
                 use_mla=True, q_lora_rank=cfg.get("q_lora_rank"), kv_lora_rank=cfg["kv_lora_rank"],
                 qk_nope_head_dim=cfg["qk_nope_head_dim"], qk_rope_head_dim=cfg["qk_rope_head_dim"],
                 v_head_dim=cfg["v_head_dim"], head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
-                rope_neox=False, index_topk=cfg.get("index_topk", 0) or 0,
+                # DeepSeek rotates q_pe / k_pe as interleaved pairs; GLM-MoE-DSA as split halves (as its indexer does)
+                rope_neox=arch == "GlmMoeDsaForCausalLM" or not bool(cfg.get("rope_interleave", True)),
+                index_topk=cfg.get("index_topk", 0) or 0,
                 index_n_heads=cfg.get("index_n_heads", 0) or 0,
                 index_head_dim=cfg.get("index_head_dim", 0) or 0,
                 num_mtp_layers=cfg.get("num_nextn_predict_layers", 0) or 0,
@@ -346,6 +348,18 @@ class ModelConfig:
     def from_pretrained(cls, path: str) -> "ModelConfig":
         with open(os.path.join(path, "config.json")) as f:
             return cls.from_hf_config(json.load(f))
+
+
+def _leading_dense(cfg: dict) -> int:
+    """Number of dense MLP layers in front of the MoE layers: ``first_k_dense_replace``, or the leading ``"dense"``
+    entries of ``mlp_layer_types`` (how configs written by transformers 5 spell it)."""
+    types = cfg.get("mlp_layer_types")
+    if isinstance(types, (list, tuple)) and types:
+        n = 0
+        while n < len(types) and types[n] == "dense":
+            n += 1
+        return n
+    return cfg.get("first_k_dense_replace", 0) or 0
 
 
 @dataclass

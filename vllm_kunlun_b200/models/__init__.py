@@ -35,6 +35,8 @@ _REGISTRY = {
     "Qwen3NextForCausalLM": "qwen3_next:Qwen3NextForCausalLM",
     "Qwen3_5ForConditionalGeneration": "qwen3_next:Qwen3NextForCausalLM",
     "Qwen3_5MoeForConditionalGeneration": "qwen3_next:Qwen3NextForCausalLM",
+    "Qwen3_5ForCausalLM": "qwen3_next:Qwen3NextForCausalLM",          # the text-only classes of the same checkpoints
+    "Qwen3_5MoeForCausalLM": "qwen3_next:Qwen3NextForCausalLM",
     # asymmetric V / sliding window with sinks
     "MiMoV2FlashForCausalLM": "mimo_v2_flash:MiMoV2FlashForCausalLM",
     # Gemma family

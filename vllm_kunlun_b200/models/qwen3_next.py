@@ -225,6 +225,17 @@ class Qwen3NextForCausalLM(MoEForCausalLM):
                     gdn.load_qkvz(w, parts[-1])
                 elif key == "in_proj_ba.weight":
                     gdn.load_ba(w)
+                elif key.startswith("in_proj_qkv."):
+                    # Qwen3.5 keeps the projections apart and in plain order: [q | k | v] rows, then z, b and a
+                    kd = self.cfg.gdn_num_k_heads * gdn.dk
+                    for i, part in enumerate((w[:kd], w[kd:2 * kd], w[2 * kd:])):
+                        gdn.in_proj.load(parts[-1], part, i)
+                elif key.startswith("in_proj_z."):
+                    gdn.in_proj.load(parts[-1], w, 3)
+                elif key == "in_proj_b.weight":
+                    gdn.in_proj_ba.load("weight", w, 0)
+                elif key == "in_proj_a.weight":
+                    gdn.in_proj_ba.load("weight", w, 1)
                 elif key == "conv1d.weight":
                     gdn.load_conv(w)
                 elif key in ("A_log", "dt_bias"):
