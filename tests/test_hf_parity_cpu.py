@@ -26,6 +26,9 @@ GPT_OSS = dict(vocab_size=160, hidden_size=128, num_hidden_layers=2, num_attenti
 Q35 = dict(vocab_size=160, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
            intermediate_size=256, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
            linear_value_head_dim=32, linear_conv_kernel_dim=4, full_attention_interval=4, max_position_embeddings=256)
+GEMMA4 = dict(vocab_size=160, hidden_size=128, num_hidden_layers=6, layer_types=["sliding_attention", "full_attention"] * 3,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=32, intermediate_size=256, max_position_embeddings=256,
+              sliding_window=8)
 YARN = {"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 64,
         "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0}
 
@@ -76,6 +79,17 @@ CASES = [
     ("qwen3_5_dense_hybrid", "Qwen3_5TextConfig", "Qwen3_5ForCausalLM", "Qwen3_5ForCausalLM", dict(Q35), 5e-4),
     ("qwen3_5_moe_hybrid", "Qwen3_5MoeTextConfig", "Qwen3_5MoeForCausalLM", "Qwen3_5MoeForCausalLM",
      dict(Q35, moe_intermediate_size=64, shared_expert_intermediate_size=64, num_experts=4, num_experts_per_tok=2), 5e-4),
+    # Gemma-4: sandwich norms with plain weights, softmax scale 1, V norm, layer scalars, per-type rotary parameters
+    ("gemma4_basic", "Gemma4TextConfig", "Gemma4ForCausalLM", "Gemma4ForCausalLM",
+     dict(GEMMA4, global_head_dim=32, hidden_size_per_layer_input=0, num_kv_shared_layers=0), 1e-4),
+    # ... plus proportional rotary embedding and a larger head on the full-attention layers whose values are their keys,
+    # per-layer inputs, cross-layer KV sharing with double-wide MLPs
+    ("gemma4_full_featured", "Gemma4TextConfig", "Gemma4ForCausalLM", "Gemma4ForCausalLM",
+     dict(GEMMA4, global_head_dim=64, attention_k_eq_v=True, num_global_key_value_heads=1, hidden_size_per_layer_input=64,
+          vocab_size_per_layer_input=160, num_kv_shared_layers=2, use_double_wide_mlp=True,
+          rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                           "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25,
+                                              "rope_theta": 1000000.0}}), 1e-4),
     # GLM-MoE-DSA (DeepSeek-V3.2 style sparse attention): with a top-k above the prompt length every key is selected,
     # so the whole path (indexer, index conversion, sparse MLA) must reproduce dense attention
     ("glm_moe_dsa_indexer", "GlmMoeDsaConfig", "GlmMoeDsaForCausalLM", "GlmMoeDsaForCausalLM",

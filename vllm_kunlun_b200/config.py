@@ -31,6 +31,7 @@ class RopeScaling:
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
     truncate: bool = True   # YaRN: round the correction range to whole dimensions (gpt-oss checkpoints say False)
+    partial: float = 1.0    # "proportional": fraction of the head's angle pairs that rotate (the rest keep angle 0)
 
 
 @dataclass
@@ -110,6 +111,14 @@ class ModelConfig:
     # Gemma per-layer inputs ("PLE"): width of the per-layer embedding and the vocabulary it is looked up in
     per_layer_input_size: int = 0
     per_layer_vocab_size: int = 0
+    layer_types: tuple = ()  # explicit "sliding_attention" / "full_attention" per layer (else sliding_window_pattern)
+    rope_per_type: dict = field(default_factory=dict)  # layer type -> (theta, RopeScaling) when the types differ
+    v_norm: bool = False  # RMS-normalise V per head, without a weight (Gemma-4)
+    layer_scalar: bool = False  # a learned scalar multiplies the stream at the end of every layer (Gemma-4)
+    double_wide_mlp: bool = False  # KV-shared layers have an MLP of twice the width (Gemma-4)
+    global_head_dim: Optional[int] = None  # head size of the full-attention layers when it differs (Gemma-4)
+    num_global_kv_heads: Optional[int] = None  # their KV head count when values are the keys (attention_k_eq_v)
+    attention_k_eq_v: bool = False  # full-attention layers have no v_proj: V is the (un-normalised, un-rotated) K
     attn_output_gate: bool = False  # q_proj carries a sigmoid output gate (Qwen3-Next full-attention layers)
     # quantization of the checkpoint
     quantization: Optional[str] = None  # None | "fp8" | "int8" | "awq" | "gptq" | "w4a16"
@@ -147,6 +156,8 @@ class ModelConfig:
     def layer_is_sliding(self, i: int) -> bool:
         if self.sliding_window is None:
             return False
+        if self.layer_types:
+            return self.layer_types[i] == "sliding_attention"
         if self.sliding_window_pattern <= 0:
             return True
         return (i + 1) % self.sliding_window_pattern != 0
@@ -339,6 +350,24 @@ class ModelConfig:
             kw.update(gemma_norm=True, hidden_act="gelu_tanh", qk_norm=True,
                       sliding_window=cfg.get("sliding_window"), sliding_window_pattern=cfg.get("sliding_window_pattern", 6),
                       tie_word_embeddings=True)
+            if arch.startswith("Gemma4"):
+                # Gemma-4: norm weights multiply directly (no 1 + w), softmax scale 1 (q / k are normalised), V is
+                # RMS-normalised, a scalar per layer, rotary parameters per layer type ("proportional" on the full-
+                # attention layers: only a fraction of the angle pairs rotates)
+                rp = cfg.get("rope_parameters") or {}
+                per_type = {}
+                for lt, key in (("sliding_attention", "sliding"), ("full_attention", "full")):
+                    r = rp.get(lt) if isinstance(rp.get(lt), dict) else None
+                    if r:
+                        sc = RopeScaling(type="proportional", partial=float(r.get("partial_rotary_factor", 1.0)),
+                                         factor=float(r.get("factor", 1.0))) if r.get("rope_type") == "proportional" else RopeScaling()
+                        per_type[key] = (float(r.get("rope_theta", 10000.0)), sc)
+                kw.update(gemma_norm=False, attn_scale=1.0, v_norm=True, layer_scalar=True, rope_per_type=per_type,
+                          layer_types=tuple(cfg.get("layer_types") or ()),
+                          double_wide_mlp=bool(cfg.get("use_double_wide_mlp", False)),
+                          global_head_dim=cfg.get("global_head_dim") or None,
+                          attention_k_eq_v=bool(cfg.get("attention_k_eq_v", False)),
+                          num_global_kv_heads=cfg.get("num_global_key_value_heads") or None)
         if arch == "MiMoV2FlashForCausalLM":
             kw.update(v_head_dim=cfg.get("v_head_dim", kw["head_dim"]), attention_sinks=bool(cfg.get("add_swa_attention_sink_bias", True)),
                       sliding_window=cfg.get("sliding_window", 128), sliding_window_pattern=cfg.get("hybrid_block_size", 0) or 0)

@@ -33,16 +33,50 @@ def kv_source_layer(cfg: ModelConfig, i: int) -> int:
     return i
 
 
+def layer_attention_config(cfg: ModelConfig, i: int) -> ModelConfig:
+    """The configuration as layer ``i``'s attention sees it: Gemma-4 full-attention layers may have their own head
+    size and, when their values are their keys, their own KV head count."""
+    if cfg.layer_is_sliding(i) or not (cfg.global_head_dim or cfg.attention_k_eq_v):
+        return cfg
+    import dataclasses
+    hd = cfg.global_head_dim or cfg.head_dim
+    kvh = cfg.num_global_kv_heads if (cfg.attention_k_eq_v and cfg.num_global_kv_heads) else cfg.num_kv_heads
+    return dataclasses.replace(cfg, head_dim=hd, v_head_dim=hd, rotary_dim=hd, num_kv_heads=kvh)
+
+
 class Gemma4Attention(GQAAttention):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        cfg = layer_attention_config(cfg, layer_idx)
         super().__init__(cfg, layer_idx, dtype, device)
+        self.k_eq_v = cfg.attention_k_eq_v and not cfg.layer_is_sliding(layer_idx)
         self.kv_layer = kv_source_layer(cfg, layer_idx)
         if cfg.attn_scale is not None:
             self.scale = cfg.attn_scale
+        kind = "sliding" if cfg.layer_is_sliding(layer_idx) else "full"
+        if kind in cfg.rope_per_type:       # rotary parameters of this layer's type
+            from .layers import get_cos_sin_cache
+            theta, scaling = cfg.rope_per_type[kind]
+            self.cos_sin = get_cos_sin_cache(self.head_dim, cfg.max_position, theta, scaling, device)
 
     def forward(self, hidden):
         if self.kv_layer == self.layer_idx:
-            return super().forward(hidden)
+            if not self.cfg.v_norm:
+                return super().forward(hidden)
+            # V is RMS-normalised per head (no weight) before it goes to the cache
+            ctx = get_forward_context()
+            md, cfg = ctx.attn, self.cfg
+            kv_cache = ctx.kv_caches[self.layer_idx]
+            qkv = self.qkv_proj(hidden)
+            T = qkv.shape[0]
+            v0 = (self.num_heads + self.num_kv_heads) * self.head_dim
+            v = qkv[:, v0:].reshape(T * self.num_kv_heads, self.head_dim).float()
+            v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps)
+            qkv = torch.cat([qkv[:, :v0], v.to(qkv.dtype).view(T, -1)], -1)
+            q = ops.qkv_split_norm_rope_cache(
+                qkv, md.positions, self.cos_sin, None if self.q_norm is None else self.q_norm.weight,
+                None if self.k_norm is None else self.k_norm.weight, cfg.rms_norm_eps, self.num_heads, self.num_kv_heads,
+                self.head_dim, cfg.rope_neox, kv_cache, md.slot_mapping, cfg.gemma_norm)
+            return self._attend(q, kv_cache, md)
         # KV-shared layer: only the query is used; keys / values come from the source layer's cache
         ctx = get_forward_context()
         md, cfg = ctx.attn, self.cfg
@@ -71,7 +105,9 @@ class Gemma4DecoderLayer(nn.Module):
         if cfg.layer_is_moe(layer_idx):
             self.mlp = SparseMoEBlock(cfg, dtype, device)
         else:
-            self.mlp = GatedMLP(cfg.hidden_size, cfg.intermediate_size, dtype, device, cfg.quantization, cfg.hidden_act,
+            shared = cfg.num_kv_shared_layers > 0 and layer_idx >= cfg.num_layers - cfg.num_kv_shared_layers
+            inter = cfg.intermediate_size * (2 if cfg.double_wide_mlp and shared else 1)
+            self.mlp = GatedMLP(cfg.hidden_size, inter, dtype, device, cfg.quantization, cfg.hidden_act,
                                 cfg.mlp_bias, reduce_results=False)
         # per-layer inputs (reference gemma4.py:553-581,632-640): a gate from the stream selects from this layer's
         # slice of the per-token embedding, which is projected back, normed and added; then the layer scalar
@@ -80,6 +116,7 @@ class Gemma4DecoderLayer(nn.Module):
             self.per_layer_input_gate = ReplicatedLinear(cfg.hidden_size, self.ple, dtype=dtype, device=device)
             self.per_layer_projection = ReplicatedLinear(self.ple, cfg.hidden_size, dtype=dtype, device=device)
             self.post_per_layer_input_norm = norm()
+        if self.ple or cfg.layer_scalar:
             self.layer_scalar = param(1, dtype=dtype, device=device)
 
     def add_per_layer_input(self, m, residual, per_layer_input):
@@ -145,6 +182,8 @@ class Gemma4ForCausalLM(MoEForCausalLM):
             hidden, residual = layer(hidden, residual)
             if ple is not None:
                 hidden, residual = layer.add_per_layer_input(hidden, residual, ple[:, i].contiguous()), None
+            elif self.cfg.layer_scalar:
+                hidden, residual = (hidden + residual) * layer.layer_scalar, None
         if self.norm is None:
             return hidden, residual
         if residual is None:
@@ -161,6 +200,22 @@ class Gemma4ForCausalLM(MoEForCausalLM):
 
     def kv_cache_spec(self, block_size: int):
         st = get_state()
-        kvh = max(1, self.cfg.num_kv_heads // st.tp_size)
-        return {i: ((2, kvh, block_size, self.cfg.head_dim), self.dtype)
-                for i in range(self.first_layer, self.last_layer) if kv_source_layer(self.cfg, i) == i}
+        spec = {}
+        for i in range(self.first_layer, self.last_layer):
+            if kv_source_layer(self.cfg, i) != i:
+                continue
+            lc = layer_attention_config(self.cfg, i)
+            spec[i] = ((2, max(1, lc.num_kv_heads // st.tp_size), block_size, lc.head_dim), self.dtype)
+        return spec
+
+    def load_weights(self, weights):
+        # full-attention layers whose values are their keys have no v_proj tensor: the fused projection's V rows
+        # take the K weight (V = k_proj(x), before the key's norm and rotation)
+        out = []
+        for name, w in weights:
+            out.append((name, w))
+            if self.cfg.attention_k_eq_v and ".self_attn.k_proj." in name:
+                parts = name.removeprefix("model.").split(".")
+                if parts[0] == "layers" and parts[1].isdigit() and not self.cfg.layer_is_sliding(int(parts[1])):
+                    out.append((name.replace(".k_proj.", ".v_proj."), w))
+        return super().load_weights(out)

@@ -137,6 +137,13 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling=None) -> tuple[torch.Te
         mid = (wavelen <= low) & (wavelen >= high)
         out = torch.where(mid, (1 - smooth) * inv / scaling.factor + smooth * inv, out)
         return out, mscale
+    if scaling.type == "proportional":
+        # the first ``partial`` of the head's angle pairs rotate with exponents relative to the whole head; the other
+        # pairs keep angle 0 (cos 1, sin 0: they pass through)
+        n_rot = int(scaling.partial * rotary_dim // 2)
+        out = torch.zeros(rotary_dim // 2, dtype=torch.float32)
+        out[:n_rot] = 1.0 / (theta ** (torch.arange(0, 2 * n_rot, 2, dtype=torch.float32) / rotary_dim))
+        return out / scaling.factor, mscale
     if scaling.type == "yarn":
         lo = _yarn_find_dim(scaling.beta_fast, rotary_dim, theta, scaling.original_max_position)
         hi = _yarn_find_dim(scaling.beta_slow, rotary_dim, theta, scaling.original_max_position)
