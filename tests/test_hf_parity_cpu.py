@@ -156,14 +156,25 @@ VL_CASES = [
      dict(rope_scaling={"type": "mrope", "mrope_section": [4, 6, 6]}),
      dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, patch_size=4, spatial_merge_size=2,
           temporal_patch_size=2, in_channels=3)),
-    # Qwen2.5-VL: RMSNorm blocks, gated MLP (gate / up / down tensors), windowed attention except in listed blocks
+    # Qwen2.5-VL: RMSNorm blocks, gated MLP (gate / up / down tensors), windowed attention except in listed blocks.
+    # tokens_per_second=1: transformers 5 multiplies an image's temporal position by tokens_per_second (the model's
+    # own rule, followed here, scales only the frame index of a video, so an image keeps its start position).
     ("qwen2_5_vl_windows", "Qwen2_5_VLConfig", "Qwen2_5_VLForConditionalGeneration", "Qwen2_5_VLForConditionalGeneration",
      dict(rope_scaling={"type": "mrope", "mrope_section": [4, 6, 6]}),
      dict(depth=3, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
-          spatial_merge_size=2, temporal_patch_size=2, in_channels=3, window_size=16, fullatt_block_indexes=[1])),
+          spatial_merge_size=2, temporal_patch_size=2, in_channels=3, window_size=16, fullatt_block_indexes=[1],
+          tokens_per_second=1)),
     # Qwen3-VL: patch bias, interpolated position table, tanh-GELU MLP, deep-stack features, interleaved M-RoPE
     ("qwen3_vl_deepstack", "Qwen3VLConfig", "Qwen3VLForConditionalGeneration", "Qwen3VLForConditionalGeneration",
      dict(head_dim=32, rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True}),
+     dict(depth=3, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
+          spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=64,
+          deepstack_visual_indexes=[0, 1])),
+    # Qwen3-VL-MoE: the same tower over a sparse decoder with stacked expert tensors
+    ("qwen3_vl_moe", "Qwen3VLMoeConfig", "Qwen3VLMoeForConditionalGeneration", "Qwen3VLMoeForConditionalGeneration",
+     dict(head_dim=32, moe_intermediate_size=64, num_experts=4, num_experts_per_tok=2, norm_topk_prob=True,
+          decoder_sparse_step=1, mlp_only_layers=[],
+          rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True}),
      dict(depth=3, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
           spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=64,
           deepstack_visual_indexes=[0, 1])),
@@ -173,8 +184,8 @@ VL_CASES = [
 @pytest.mark.parametrize("case", VL_CASES, ids=[c[0] for c in VL_CASES])
 def test_vision_language_models_match_the_transformers_implementation(case):
     """Two images of different grids in one prompt: the vision tower's embeddings (and deep-stack features) equal the
-    reference's, and greedy decoding through the engine (placeholder rows replaced during prefill, M-RoPE positions,
-    deep-stack injection) gives the reference's tokens."""
+    reference's; the logits after the prompt (placeholder rows replaced during prefill, M-RoPE positions, deep-stack
+    injection) equal the reference's, and so do eight greedily decoded tokens."""
     _, cfg_name, cls_name, arch, text_kw, vis_kw = case
     if not (hasattr(transformers, cfg_name) and hasattr(transformers, cls_name)):
         pytest.skip(f"transformers {transformers.__version__} has no {cls_name}")
@@ -199,8 +210,11 @@ def test_vision_language_models_match_the_transformers_implementation(case):
 
     seq = torch.tensor([ids])
     want = []
-    for _ in range(3):
-        want.append(hf_logits(seq)[-1].argmax().item())
+    want_logits = None
+    for _ in range(8):
+        lg = hf_logits(seq)[-1].float()
+        want_logits = lg if want_logits is None else want_logits
+        want.append(lg.argmax().item())
         seq = torch.cat([seq, torch.tensor([[want[-1]]])], 1)
     d = hf_cfg.to_dict()
     d["architectures"], d["torch_dtype"] = [arch], "float32"
@@ -220,6 +234,15 @@ def test_vision_language_models_match_the_transformers_implementation(case):
     assert (mine[:, :H] - ref_main.float()).abs().max().item() < 1e-4
     for k, f in enumerate(deep or []):
         assert (mine[:, (k + 1) * H:(k + 2) * H] - f.float()).abs().max().item() < 1e-4
-    out = llm.generate([ids], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True),
+    seen, compute_logits = [], model.compute_logits
+
+    def recording(h):
+        out = compute_logits(h)
+        seen.append(out.detach().float().clone())
+        return out
+
+    model.compute_logits = recording
+    out = llm.generate([ids], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True),
                        multi_modal_data={"pixel_values": px, "image_grid_thw": [list(g) for g in grids]})[0].token_ids
+    assert (seen[0][-1] - want_logits).abs().max().item() < 1e-4
     assert out == want

@@ -341,6 +341,9 @@ class ModelConfig:
                 deepstack_indexes=list(vcfg.get("deepstack_visual_indexes", ())))
             rsc = tc.get("rope_scaling") or tc.get("rope_parameters") or {}
             kw["mrope_section"] = tuple(rsc.get("mrope_section", ()))
+            # Qwen3-VL interleaves the three position axes over the rotary pairs (t h w t h w ...); Qwen2-VL / 2.5-VL
+            # give each axis a contiguous section
+            kw["mrope_interleaved"] = bool(rsc.get("mrope_interleaved", arch.startswith("Qwen3VL") or arch.startswith("Qwen3Omni")))
         if arch.startswith("Gemma"):
             kw.update(num_kv_shared_layers=cfg.get("num_kv_shared_layers", 0) or 0,
                       final_logit_softcapping=float(cfg.get("final_logit_softcapping") or 0.0),

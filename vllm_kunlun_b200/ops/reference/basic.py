@@ -205,7 +205,7 @@ def apply_mrope(x, positions3, cos_sin_cache, head_dim, sections, interleaved: b
         sel = torch.zeros(half, dtype=torch.long)
         for axis in (1, 2):
             idx = torch.arange(axis, sections[axis] * 3, 3)
-            sel[idx] = axis
+            sel[idx[idx < half]] = axis      # slots past the rotary width do not exist (small heads)
     else:
         sel = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(sections)])
     ar = torch.arange(half)
