@@ -246,3 +246,44 @@ def test_vision_language_models_match_the_transformers_implementation(case):
                        multi_modal_data={"pixel_values": px, "image_grid_thw": [list(g) for g in grids]})[0].token_ids
     assert (seen[0][-1] - want_logits).abs().max().item() < 1e-4
     assert out == want
+
+
+def test_qwen3_vl_image_and_video_prompt_matches_the_transformers_implementation():
+    """One image and one two-frame video in a prompt (Qwen3-VL: one video placeholder run per temporal patch, with
+    text in between): the logits after the prompt equal the reference's."""
+    _, cfg_name, cls_name, arch, text_kw, vis_kw = VL_CASES[2]
+    if not (hasattr(transformers, cfg_name) and hasattr(transformers, cls_name)):
+        pytest.skip(f"transformers {transformers.__version__} has no {cls_name}")
+    torch.manual_seed(0)
+    tc = dict(vocab_size=200, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=256, max_position_embeddings=512, rms_norm_eps=1e-5, **text_kw)
+    hf_cfg = getattr(transformers, cfg_name)(text_config=tc, vision_config=vis_kw, **_TOK)
+    hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
+    _randomise(hf)
+    img, vid = hf_cfg.image_token_id, hf_cfg.video_token_id
+    patch_dim = 3 * hf_cfg.vision_config.temporal_patch_size * hf_cfg.vision_config.patch_size ** 2
+    px, pv = torch.randn(1 * 4 * 6, patch_dim), torch.randn(2 * 4 * 4, patch_dim)
+    ids = [5, 6] + [img] * 6 + [7, 30, 31] + [vid] * 4 + [32, 33] + [vid] * 4 + [8, 9, 10]
+    seq = torch.tensor([ids])
+    with torch.no_grad():
+        want = hf(input_ids=seq, pixel_values=px, image_grid_thw=torch.tensor([[1, 4, 6]]), pixel_values_videos=pv,
+                  video_grid_thw=torch.tensor([[2, 4, 4]]),
+                  mm_token_type_ids=(seq == img).long() + 2 * (seq == vid).long()).logits[0, -1].float()
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = [arch], "float32"
+    llm = LLM(ModelConfig.from_hf_config(d), device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=32)
+    model = llm.engine.runner.model
+    with torch.inference_mode():
+        model.load_weights(list(hf.state_dict().items()))
+    seen, compute_logits = [], model.compute_logits
+
+    def recording(h):
+        out = compute_logits(h)
+        seen.append(out.detach().float().clone())
+        return out
+
+    model.compute_logits = recording
+    llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
+                 multi_modal_data={"pixel_values": px, "image_grid_thw": [[1, 4, 6]], "pixel_values_videos": pv,
+                                   "video_grid_thw": [[2, 4, 4]]})
+    assert (seen[0][-1] - want).abs().max().item() < 1e-4

@@ -543,3 +543,82 @@ def test_chat_post_processor_with_harmony_parser():
     deltas = [post.stream_delta(_HARMONY_ANSWER[i:i + 5], None)[0] for i in range(0, len(_HARMONY_ANSWER), 5)]
     last, fin = post.stream_delta("", "stop")
     assert fin == "stop" and "".join(d.get("content", "") for d in deltas + [last]) == "2 + 2 = 4"
+
+
+def test_image_preprocessor_matches_the_transformers_processor():
+    """Same grid and patch order as ``Qwen2VLImageProcessor``; pixel values within one intensity level (the two
+    bicubic resamplers round differently)."""
+    np = pytest.importorskip("numpy")
+    transformers = pytest.importorskip("transformers")
+    from PIL import Image
+
+    from vllm_kunlun_b200.multimodal import QwenImagePreprocessor, expand_placeholders, smart_resize
+    assert smart_resize(37, 91, 28, 56 * 56, 28 * 28 * 64) == (56, 112)
+    rng = np.random.default_rng(0)
+    mine = QwenImagePreprocessor(14, 2, 2, 56 * 56, 28 * 28 * 64)
+    hp = transformers.Qwen2VLImageProcessor(patch_size=14, temporal_patch_size=2, merge_size=2,
+                                            size={"shortest_edge": 56 * 56, "longest_edge": 28 * 28 * 64})
+    for H, W in ((120, 200), (37, 91), (600, 300)):
+        # smooth content: both resamplers agree to rounding (on noise they differ by design)
+        yy, xx = np.mgrid[0:H, 0:W]
+        arr = np.stack([(yy * 255 // H), (xx * 255 // W), ((yy + xx) * 255 // (H + W))], -1).astype(np.uint8)
+        im = Image.fromarray(arr)
+        want = hp(images=[im], return_tensors="pt")
+        px, grid = mine([im])
+        assert grid == want["image_grid_thw"].tolist()
+        assert px.shape == want["pixel_values"].shape
+        assert (px - want["pixel_values"]).abs().max().item() <= 2.1 / 255 / 0.26
+        assert mine.tokens_per_image(grid[0]) == grid[0][1] * grid[0][2] // 4
+    assert expand_placeholders([1, 9, 2, 9, 9, 3], 9, [3, 2]) == [1, 9, 9, 9, 2, 9, 9, 3]
+    with pytest.raises(ValueError):
+        expand_placeholders([1, 9, 2], 9, [3, 2])
+
+
+def test_openai_server_chat_with_an_image_part():
+    """An ``image_url`` part (data: URI) reaches the engine as pixel values + grid with the placeholder expanded; the
+    answer depends on the image; a text-only model answers 400."""
+    import base64
+    import io
+
+    from fastapi.testclient import TestClient
+    from PIL import Image
+
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.config import qwen2_0_5b, tiny
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    base = dict(num_layers=2, vocab_size=128, hidden_size=64, num_heads=2, num_kv_heads=1, head_dim=32,
+                intermediate_size=128, max_position=512, dtype="float32")
+    cfg = tiny(qwen2_0_5b(), **base)
+    cfg.architecture = "Qwen2VLForConditionalGeneration"
+    cfg.mrope_section = (4, 6, 6)
+    cfg.vision = dict(depth=1, hidden=32, heads=2, patch=14, temporal_patch=2, merge=2, intermediate=64, in_channels=3,
+                      norm="layernorm", gated_mlp=False, image_token_id=127, text_architecture="Qwen2ForCausalLM")
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=64)
+
+    def uri(color):
+        buf = io.BytesIO()
+        Image.new("RGB", (60, 90), color).save(buf, format="PNG")
+        return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+    def ask(c, color):
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "text", "text": "3 4 5"}, {"type": "image_url", "image_url": {"url": uri(color)}},
+            {"type": "text", "text": "6 7"}]}], "max_tokens": 6, "temperature": 0, "ignore_eos": True, "logprobs": True})
+        assert r.status_code == 200, r.text
+        return r.json()
+
+    with TestClient(build_app(llm, "vl")) as c:
+        a, b = ask(c, (250, 10, 10)), ask(c, (10, 10, 250))
+        # 60 x 90 -> 56 x 84 pixels -> 4 x 6 patches -> 6 placeholder tokens + 5 text tokens
+        assert a["usage"]["prompt_tokens"] == 11
+        lp = lambda d: [e["logprob"] for e in d["choices"][0]["logprobs"]["content"]]  # noqa: E731
+        assert lp(a) != lp(b)
+        assert lp(ask(c, (250, 10, 10))) == lp(a)
+        bad = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]}], "max_tokens": 2})
+        assert bad.status_code == 400
+    text_llm = LLM(tiny(qwen2_0_5b(), **base), device="cpu", block_size=16, max_model_len=128, max_num_seqs=2, num_gpu_blocks=32)
+    with TestClient(build_app(text_llm, "text")) as c:
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": uri((1, 2, 3))}}]}], "max_tokens": 2})
+        assert r.status_code == 400

@@ -37,6 +37,21 @@ def test_mrope_positions():
     assert pos[:, 6].tolist() == [4, 4, 4] and delta == 6 - 8
 
 
+def test_mrope_positions_of_a_video():
+    """Two temporal patches of 2 x 2 merged patches: frame-major order, the temporal axis steps by 1 per patch
+    (Qwen2-VL) or by seconds-per-patch x tokens_per_second truncated (Qwen2.5-VL); text continues after the largest
+    position used."""
+    VID = IMG + 1
+    ids = [1, IMG, IMG, 2] + [VID] * 8 + [3]
+    pos, delta = get_mrope_positions(ids, [(1, 2, 4)], IMG, 2, VID, [(2, 4, 4)])
+    assert pos[:, 1:3].tolist() == [[1, 1], [1, 1], [1, 2]] and pos[:, 3].tolist() == [3, 3, 3]
+    assert pos[0, 4:12].tolist() == [4, 4, 4, 4, 5, 5, 5, 5]
+    assert pos[1, 4:12].tolist() == [4, 4, 5, 5, 4, 4, 5, 5] and pos[2, 4:12].tolist() == [4, 5, 4, 5, 4, 5, 4, 5]
+    assert pos[:, 12].tolist() == [6, 6, 6] and delta == 7 - 13
+    pos, delta = get_mrope_positions(ids, [(1, 2, 4)], IMG, 2, VID, [(2, 4, 4)], [2.5 * 2])
+    assert pos[0, 4:12].tolist() == [4, 4, 4, 4, 9, 9, 9, 9] and pos[:, 12].tolist() == [10, 10, 10] and delta == 11 - 13
+
+
 def test_qwen_vl_generation_uses_the_image_and_survives_chunking():
     cfg = _qwen_vl()
     grid = [(1, 8, 4)]  # 32 patches -> 8 merged tokens

@@ -335,6 +335,11 @@ class ModelConfig:
                 num_pos=int(vcfg.get("num_position_embeddings") or 0) if "Qwen3" in arch else 0,
                 patch_bias="Qwen3" in arch,
                 downsample=cfg.get("downsample_ratio", 0.5), image_token_id=cfg.get("image_token_id", 151655),
+                # videos: Qwen2.5-VL spaces temporal positions by seconds x tokens_per_second; Qwen3-VL prompts hold
+                # one placeholder run per temporal patch
+                video_token_id=cfg.get("video_token_id"),
+                tokens_per_second=vcfg.get("tokens_per_second", 4) if "2_5" in arch else 0,
+                video_frame_runs="Qwen3" in arch,
                 text_architecture=(tc.get("architectures") or ["Qwen2ForCausalLM"])[0] if intern else
                 ("Qwen3MoeForCausalLM" if ("Qwen3" in arch and "Moe" in arch) else
                  "Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"),

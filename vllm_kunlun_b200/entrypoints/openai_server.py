@@ -21,6 +21,7 @@ import uuid
 from typing import Optional
 
 from ..engine.request import SamplingParams
+from ..multimodal import QwenImagePreprocessor, collect_images, expand_placeholders, load_image
 
 
 class ChatPostProcessor:
@@ -176,9 +177,10 @@ class EngineLoop:
             self.thread = threading.Thread(target=self._run, daemon=True)
             self.thread.start()
 
-    def submit(self, prompt_ids, sp: SamplingParams, loop, out_q, lora_id: int = -1):
+    def submit(self, prompt_ids, sp: SamplingParams, loop, out_q, lora_id: int = -1, mm: Optional[dict] = None):
+        """``mm``: the request's ``multi_modal_data`` (host tensors), or None."""
         rid = f"cmpl-{uuid.uuid4().hex}"
-        self.inbox.put((rid, prompt_ids, sp, loop, out_q, lora_id))
+        self.inbox.put((rid, prompt_ids, sp, loop, out_q, lora_id, mm))
         return rid
 
     def abort(self, rid: str):
@@ -206,9 +208,10 @@ class EngineLoop:
                 return
             for rid in aborts:
                 eng.abort(rid)
-            for rid, ids, sp, lora_id in new:
+            for rid, ids, sp, lora_id, mm in new:
                 try:
-                    eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                    eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id,
+                                    multi_modal_data=mm)
                 except Exception:  # rank 0 validated the request; a failure here is reported there as well
                     log.exception("follower: add_request failed for %s", rid)
             if eng.has_unfinished():
@@ -233,12 +236,13 @@ class EngineLoop:
             while not self.aborts.empty():
                 aborts.append(self.aborts.get_nowait())
             if self.multi:
-                self._broadcast(("step", [(rid, ids, sp, lora_id) for rid, ids, sp, _, _, lora_id in new], aborts))
+                self._broadcast(("step", [(rid, ids, sp, lora_id, mm) for rid, ids, sp, _, _, lora_id, mm in new], aborts))
             for rid in aborts:
                 self.stats["aborted"] += int(eng.abort(rid))
-            for rid, ids, sp, loop, out_q, lora_id in new:
+            for rid, ids, sp, loop, out_q, lora_id, mm in new:
                 try:
-                    req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id)
+                    req = eng.add_request(ids, sp, request_id=rid, eos_token_id=self.llm.eos_token_id, lora_id=lora_id,
+                                          multi_modal_data=mm)
                 except Exception as e:  # an unservable request fails alone; the loop and the other streams go on
                     loop.call_soon_threadsafe(out_q.put_nowait, ("error", f"{type(e).__name__}: {e}"))
                     self.stats["failed"] = self.stats.get("failed", 0) + 1
@@ -288,6 +292,11 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
     app = FastAPI()
+    # image inputs: models with a Qwen-VL tower (patch / merge geometry in the configuration) take image_url parts
+    vision = getattr(llm.engine.cfg.model, "vision", None) or {}
+    image_pre = (QwenImagePreprocessor.from_config(vision, getattr(llm, "preprocessor_config", None))
+                 if vision.get("merge") and vision.get("temporal_patch") and not vision.get("layer_scale") else None)
+    image_token_id = vision.get("image_token_id")
     loop_obj = EngineLoop(llm)
     app.state.engine_loop = loop_obj
     tok = llm.tokenizer
@@ -357,7 +366,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
         kind = "BadRequestError" if code == 400 else "InternalServerError"
         return JSONResponse({"error": {"message": msg, "type": kind, "code": code}}, status_code=code)
 
-    async def run(prompt_ids, sp, stream, make_chunk, make_final, requested_model=None, stops=()):
+    async def run(prompt_ids, sp, stream, make_chunk, make_final, requested_model=None, stops=(), mm=None):
         if isinstance(sp, str):  # the sampling parameters did not parse
             return bad_request(sp)
         # the name selects an adapter; with no adapters loaded every name is served by the base model
@@ -370,7 +379,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
             return bad_request(str(e))
         loop = asyncio.get_running_loop()
         out_q: asyncio.Queue = asyncio.Queue()
-        rid = loop_obj.submit(prompt_ids, sp, loop, out_q, lora_modules.get(requested_model, -1))
+        rid = loop_obj.submit(prompt_ids, sp, loop, out_q, lora_modules.get(requested_model, -1), mm)
         created = int(time.time())
         cut = StopStrings(stops)
         if stream:
@@ -454,11 +463,30 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
     async def chat(req: Request):
         body = await req.json()
         msgs = body.get("messages", [])
+        urls = collect_images(msgs)
+        if urls and image_pre is None:
+            return bad_request("this model takes no image input")
         if tok is not None and hasattr(tok, "apply_chat_template"):
             ids = tok.apply_chat_template(msgs, add_generation_prompt=True, tools=body.get("tools"),
                                           **(body.get("chat_template_kwargs") or {}))
+            ids = ids["input_ids"] if hasattr(ids, "keys") else ids
         else:
-            ids = encode(" ".join(str(m.get("content", "")) for m in msgs))
+            ids = []
+            for m in msgs:      # no tokenizer: text parts are lists of ids, every image part is one placeholder
+                c = m.get("content", "")
+                for part in (c if isinstance(c, list) else [{"type": "text", "text": c}]):
+                    if isinstance(part, dict) and ("image_url" in part or part.get("type") in ("image", "image_url")):
+                        ids.append(image_token_id)
+                    else:
+                        ids += encode(str(part.get("text", "")) if isinstance(part, dict) else str(part))
+        mm = None
+        if urls:
+            try:
+                px, grids = image_pre([load_image(u) for u in urls])
+                ids = expand_placeholders(list(ids), image_token_id, [image_pre.tokens_per_image(g) for g in grids])
+            except (ValueError, OSError) as e:
+                return bad_request(f"image input: {e}")
+            mm = {"pixel_values": px, "image_grid_thw": grids}
         post = ChatPostProcessor(reasoning_parser, tool_parser, body.get("tools"), body.get("chat_template_kwargs"))
 
         def chunk(rid, created, text, fin):
@@ -472,7 +500,8 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                     "choices": [{"index": 0, "message": msg,
                                  "finish_reason": "tool_calls" if msg.get("tool_calls") else fin}],
                     "usage": {"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out}}
-        return await run(list(ids), sampling(body), bool(body.get("stream")), chunk, final, body.get("model"), stop_list(body))
+        return await run(list(ids), sampling(body), bool(body.get("stream")), chunk, final, body.get("model"),
+                         stop_list(body), mm)
 
     return app
 
@@ -561,6 +590,10 @@ def main(argv=None):
         except Exception:
             tokenizer = None
     llm = LLM(a.model, tokenizer=tokenizer, **llm_kwargs(a))
+    pre = os.path.join(a.model, "preprocessor_config.json")
+    if os.path.isfile(pre):     # pixel budget and normalisation statistics of the checkpoint's image processor
+        with open(pre) as f:
+            llm.preprocessor_config = json.load(f)
     lora_ids = {}
     if a.lora_modules:
         from ..lora import LoRARequest

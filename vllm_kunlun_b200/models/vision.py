@@ -278,25 +278,36 @@ class MRopeAttention(GQAAttention):
         return self.o_proj(o.reshape(T, qs))
 
 
-def get_mrope_positions(token_ids, grid_thw, image_token_id: int, merge: int):
+def get_mrope_positions(token_ids, grid_thw, image_token_id: int, merge: int, video_token_id: Optional[int] = None,
+                        video_grid_thw=(), video_t_steps=()):
     """``[3, L]`` (t, h, w) positions and the delta ``next_position - L`` for a prompt whose image placeholders
-    (runs of ``image_token_id``) correspond to ``grid_thw`` in order."""
+    (runs of ``image_token_id``) correspond to ``grid_thw`` in order and whose video placeholders (runs of
+    ``video_token_id``) to ``video_grid_thw``.  Within a placeholder the height / width axes count merged patches
+    and the temporal axis advances by 1 per temporal patch - for a video by ``video_t_steps[i]`` (Qwen2.5-VL:
+    seconds per temporal patch x ``tokens_per_second``, truncated after the multiplication); text after it continues
+    from the largest position used plus one."""
     L = len(token_ids)
     pos = torch.zeros(3, L, dtype=torch.long)
-    i, nxt, img = 0, 0, 0
+    grids = {image_token_id: [(g, 1.0) for g in grid_thw or ()]}
+    if video_token_id is not None:
+        steps = list(video_t_steps) or [1.0] * len(video_grid_thw)
+        grids[video_token_id] = list(zip(video_grid_thw, steps))
+    used = {k: 0 for k in grids}
+    i, nxt = 0, 0
     while i < L:
-        if token_ids[i] == image_token_id and img < len(grid_thw):
-            t, h, w = grid_thw[img]
+        tok = token_ids[i]
+        if tok in grids and used[tok] < len(grids[tok]):
+            (t, h, w), step = grids[tok][used[tok]]
             gh, gw = h // merge, w // merge
             n = t * gh * gw
-            tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).reshape(-1)
+            tt = (torch.arange(t) * step).long().view(t, 1, 1).expand(t, gh, gw).reshape(-1)
             hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).reshape(-1)
             ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).reshape(-1)
             n = min(n, L - i)
             pos[:, i:i + n] = torch.stack([tt, hh, ww])[:, :n] + nxt
-            nxt += max(t, gh, gw)
+            nxt += max(int(tt[-1]) + 1, gh, gw)
             i += n
-            img += 1
+            used[tok] += 1
         else:
             pos[:, i] = nxt
             nxt += 1
@@ -412,6 +423,40 @@ class _VLBase(nn.Module):
 
 class QwenVLForConditionalGeneration(_VLBase):
     """Qwen2-VL / Qwen2.5-VL / Qwen3-VL."""
+
+    @torch.inference_mode()
+    def encode_multimodal_data(self, token_ids, data: dict):
+        """Images (``pixel_values`` + ``image_grid_thw``) and videos (``pixel_values_videos`` + ``video_grid_thw``,
+        optionally ``second_per_grid_ts``) of one request: embeddings, the prompt rows they replace, M-RoPE
+        positions and the position delta.  Video placeholders are runs of ``video_token_id``; Qwen3-VL prompts carry
+        one run per temporal patch (timestamps in between), so each run is a one-frame grid."""
+        def grids(key):
+            g = data.get(key)
+            return [tuple(int(x) for x in r) for r in (g.tolist() if hasattr(g, "tolist") else g)] if g is not None else []
+
+        vc = self.cfg.vision
+        ig, vg = grids("image_grid_thw"), grids("video_grid_thw")
+        vid_tok = vc.get("video_token_id")
+        embeds, rows = [], []
+        if data.get("pixel_values") is not None:
+            embeds.append(self.visual(data["pixel_values"].to(self.device), ig))
+            rows += [i for i, t in enumerate(token_ids) if t == self.image_token_id]
+        if data.get("pixel_values_videos") is not None:
+            assert vid_tok is not None, "the configuration names no video_token_id"
+            embeds.append(self.visual(data["pixel_values_videos"].to(self.device), vg))
+            rows += [i for i, t in enumerate(token_ids) if t == vid_tok]
+        embeds = torch.cat(embeds) if embeds else torch.zeros(0, self.cfg.hidden_size * (1 + self.num_deepstack),
+                                                               dtype=self.dtype, device=self.device)
+        assert len(rows) == embeds.shape[0], f"{len(rows)} placeholder tokens but {embeds.shape[0]} embeddings"
+        steps = []
+        if vc.get("video_frame_runs"):
+            vg = [(1, h, w) for t, h, w in vg for _ in range(t)]
+        elif vc.get("tokens_per_second"):
+            sec = data.get("second_per_grid_ts")
+            sec = [float(x) for x in sec] if sec is not None else [1.0] * len(vg)
+            steps = [x * vc["tokens_per_second"] for x in sec]
+        pos, delta = get_mrope_positions(token_ids, ig, self.image_token_id, self.visual.merge, vid_tok, vg, steps)
+        return embeds, rows, pos, delta
 
     _MAP = {"patch_embed.proj.weight": "patch_embed.weight", "patch_embed.proj.bias": "patch_embed.bias",
             "pos_embed.weight": "pos_embed", "attn.qkv.": "qkv.", "attn.proj.": "proj.",
