@@ -287,3 +287,68 @@ def test_qwen3_vl_image_and_video_prompt_matches_the_transformers_implementation
                  multi_modal_data={"pixel_values": px, "image_grid_thw": [[1, 4, 6]], "pixel_values_videos": pv,
                                    "video_grid_thw": [[2, 4, 4]]})
     assert (seen[0][-1] - want).abs().max().item() < 1e-4
+
+
+def test_qwen3_omni_thinker_matches_the_transformers_implementation():
+    """Audio clip + image in one prompt through the Qwen3-Omni thinker: the audio tower's rows (three-convolution
+    stem over 100-frame chunks, tail chunk shorter), and the logits after the prompt (audio rows, image rows with
+    deep-stack features, interleaved M-RoPE, sparse decoder) equal the reference's.  The clip fits one attention
+    window: the library's non-flash attention paths ignore the window boundaries of longer clips."""
+    if not hasattr(transformers, "Qwen3OmniMoeThinkerForConditionalGeneration"):
+        pytest.skip(f"transformers {transformers.__version__} has no Qwen3-Omni")
+    torch.manual_seed(0)
+    tc = dict(vocab_size=200, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=32, intermediate_size=256, moe_intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+              norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], max_position_embeddings=512,
+              rms_norm_eps=1e-5, rope_scaling={"rope_type": "default", "mrope_section": [4, 6, 6], "mrope_interleaved": True})
+    vc = dict(depth=3, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
+              spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=64,
+              deepstack_visual_indexes=[0, 1])
+    ac = dict(num_mel_bins=16, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, d_model=64,
+              max_source_positions=100, n_window=50, output_dim=128, n_window_infer=200, conv_chunksize=3,
+              downsample_hidden_size=8)
+    AUD, AUD_START, AUD_END = 154, 155, 156
+    hf_cfg = transformers.Qwen3OmniMoeThinkerConfig(
+        text_config=tc, vision_config=vc, audio_config=ac, audio_token_id=AUD, audio_start_token_id=AUD_START,
+        audio_end_token_id=AUD_END, position_id_per_seconds=25, **_TOK)
+    hf_cfg._attn_implementation = "eager"
+    hf = transformers.Qwen3OmniMoeThinkerForConditionalGeneration(hf_cfg).eval().float()
+    _randomise(hf)
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = ["Qwen3OmniMoeThinkerForConditionalGeneration"], "float32"
+    # the complete checkpoint nests the thinker's configuration
+    cfg = ModelConfig.from_hf_config({"architectures": ["Qwen3OmniMoeForConditionalGeneration"], "thinker_config": d})
+    llm = LLM(cfg, device="cpu", block_size=16, max_model_len=512, max_num_seqs=2, num_gpu_blocks=64)
+    model = llm.engine.runner.model
+    sd = {"thinker." + k: v for k, v in hf.state_dict().items()}
+    with torch.inference_mode():
+        loaded = model.load_weights(list(sd.items()))
+    assert len(loaded) == len(sd)
+    frames = 150                                                   # chunks of 100 and 50 frames -> 13 + 7 rows
+    feats = torch.randn(frames, 16)
+    with torch.no_grad():
+        want_audio = hf.audio_tower(feats.T, feature_lens=torch.tensor([frames])).last_hidden_state.float()
+    with torch.inference_mode():
+        got_audio = model.audio_tower(feats, [frames]).float()
+    assert model.audio_tower.output_lengths([frames]) == [20] and got_audio.shape == want_audio.shape
+    assert (got_audio - want_audio).abs().max().item() < 1e-5
+    img = hf_cfg.image_token_id
+    px = torch.randn(1 * 4 * 6, 3 * 2 * 16)
+    ids = [5, 6, AUD_START] + [AUD] * 20 + [AUD_END, 7, _TOK["vision_start_token_id"]] + [img] * 6 + \
+          [_TOK["vision_end_token_id"], 8, 9]
+    seq = torch.tensor([ids])
+    with torch.no_grad():
+        want = hf(input_ids=seq, input_features=feats.T[None], feature_attention_mask=torch.ones(1, frames, dtype=torch.long),
+                  pixel_values=px, image_grid_thw=torch.tensor([[1, 4, 6]]), attention_mask=torch.ones_like(seq)).logits[0, -1].float()
+    seen, compute_logits = [], model.compute_logits
+
+    def recording(h):
+        out = compute_logits(h)
+        seen.append(out.detach().float().clone())
+        return out
+
+    model.compute_logits = recording
+    llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
+                 multi_modal_data={"pixel_values": px, "image_grid_thw": [[1, 4, 6]], "input_features": feats,
+                                   "feature_lens": [frames]})
+    assert (seen[0][-1] - want).abs().max().item() < 1e-4

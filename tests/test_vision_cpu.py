@@ -104,7 +104,8 @@ def _qwen3_vl_moe(arch="Qwen3VLMoeForConditionalGeneration"):
     cfg.architecture = arch
     cfg.vision = dict(depth=3, hidden=32, heads=2, patch=2, temporal_patch=1, merge=2, intermediate=64, in_channels=3,
                       norm="layernorm", image_token_id=IMG, audio_token_id=126, deepstack_indexes=[0, 1],
-                      audio=dict(hidden=32, heads=2, intermediate=64, depth=2, n_mels=8, stride=4))
+                      audio=dict(hidden=32, heads=2, intermediate=64, depth=2, n_mels=8, n_window=4, n_window_infer=16,
+                                 downsample_hidden=4))
     cfg.mrope_section = (4, 6, 6)
     return cfg
 
@@ -152,21 +153,25 @@ def test_qwen3_omni_thinker_takes_audio_and_images():
     llm = LLM(cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, num_gpu_blocks=32)
     model = llm.engine.runner.model
     g = torch.Generator().manual_seed(2)
-    feats = torch.randn(10 + 7, 8, generator=g)          # two clips of 10 and 7 frames -> 3 + 2 audio tokens (stride 4)
-    assert model.audio_tower.output_lengths([10, 7]) == [3, 2]
+    # chunks of 2 * n_window = 8 frames, each shrunk 8x by the convolutions: 10 frames -> 1 + 1, 17 frames -> 1 + 1 + 1
+    feats = torch.randn(17 + 10, 8, generator=g)
+    assert model.audio_tower.output_lengths([17, 10]) == [3, 2]
     px = torch.randn(16, 3 * 1 * 2 * 2, generator=g)      # one 4x4-patch image -> 4 merged tokens
     AUD = 126
     prompt = [5] + [AUD] * 3 + [6] + [IMG] * 4 + [7] + [AUD] * 2 + [8, 9]
-    mm = {"pixel_values": px, "image_grid_thw": [(1, 4, 4)], "input_features": feats, "feature_lens": [10, 7]}
+    mm = {"pixel_values": px, "image_grid_thw": [(1, 4, 4)], "input_features": feats, "feature_lens": [17, 10]}
     sp = SamplingParams(max_tokens=4, ignore_eos=True)
     out = llm.generate([prompt], sp, multi_modal_data=mm)[0]
     assert len(out.token_ids) == 4
-    # the audio content reaches the output: other features, other continuation logits
+    # the audio content reaches the output: other features, other embeddings (the random 0.02-scale convolution
+    # weights are scaled up so that the signal is not lost under the position table)
+    for w in (model.audio_tower.conv1_w, model.audio_tower.conv2_w, model.audio_tower.conv3_w):
+        w.data.mul_(20.0)
     emb, rows, pos, delta = model.encode_multimodal_data(prompt, mm)
-    assert rows == [1, 2, 3, 5, 6, 7, 8, 10, 11] and emb.shape == (9, 3 * cfg.hidden_size)
+    assert rows == [5, 6, 7, 8, 1, 2, 3, 10, 11] and emb.shape == (9, 3 * cfg.hidden_size)     # images, then audio
     emb2, _, _, _ = model.encode_multimodal_data(prompt, dict(mm, input_features=feats * -2.0))
-    assert (emb[:3] - emb2[:3]).abs().max() > 1e-5 and torch.equal(emb[3:7], emb2[3:7])
+    assert (emb[4:7] - emb2[4:7]).abs().max() > 1e-5 and torch.equal(emb[:4], emb2[:4])
     # audio only
     out = llm.generate([[5] + [AUD] * 3 + [6, 7]], sp,
-                       multi_modal_data={"input_features": feats[:10], "feature_lens": [10]})[0]
+                       multi_modal_data={"input_features": feats[:17], "feature_lens": [17]})[0]
     assert len(out.token_ids) == 4

@@ -192,6 +192,8 @@ class ModelConfig:
     def from_hf_config(cls, cfg: dict) -> "ModelConfig":
         """Build from a Hugging Face ``config.json`` dict (same checkpoints the reference serves)."""
         arch = (cfg.get("architectures") or ["LlamaForCausalLM"])[0]
+        if isinstance(cfg.get("thinker_config"), dict):     # Qwen3-Omni: the served part is the "thinker"
+            cfg = {**cfg["thinker_config"], "architectures": [arch], "quantization_config": cfg.get("quantization_config")}
         if "hidden_size" not in cfg and isinstance(cfg.get("text_config"), dict):
             # nested layouts (Qwen3.5, vision-language wrappers): the decoder's fields live under text_config
             cfg = {**cfg["text_config"], **{k: v for k, v in cfg.items() if k != "text_config"},
@@ -314,7 +316,7 @@ class ModelConfig:
                 rotary_dim=int(kw["head_dim"] * float(tc.get("partial_rotary_factor") or (tc.get("rope_parameters") or {}).get("partial_rotary_factor") or 0.25)),
                 num_shared_experts=1 if tc.get("shared_expert_intermediate_size") else 0, shared_expert_gate=True)
         vcfg = cfg.get("vision_config")
-        if vcfg and ("VL" in arch or arch.startswith("Intern")):
+        if vcfg and ("VL" in arch or "Omni" in arch or arch.startswith("Intern")):
             tc = cfg.get("text_config") or cfg.get("llm_config") or cfg
             intern = arch.startswith("Intern")
             kw["vision"] = dict(
@@ -338,12 +340,22 @@ class ModelConfig:
                 # videos: Qwen2.5-VL spaces temporal positions by seconds x tokens_per_second; Qwen3-VL prompts hold
                 # one placeholder run per temporal patch
                 video_token_id=cfg.get("video_token_id"),
-                tokens_per_second=vcfg.get("tokens_per_second", 4) if "2_5" in arch else 0,
-                video_frame_runs="Qwen3" in arch,
+                tokens_per_second=(vcfg.get("tokens_per_second", 4) if "2_5" in arch else
+                                   cfg.get("position_id_per_seconds", 25) if "Omni" in arch else 0),
+                video_frame_runs="Qwen3VL" in arch,
                 text_architecture=(tc.get("architectures") or ["Qwen2ForCausalLM"])[0] if intern else
                 ("Qwen3MoeForCausalLM" if ("Qwen3" in arch and "Moe" in arch) else
                  "Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"),
                 deepstack_indexes=list(vcfg.get("deepstack_visual_indexes", ())))
+            acfg = cfg.get("audio_config")
+            if acfg and "Omni" in arch:
+                kw["vision"]["audio"] = dict(
+                    hidden=acfg.get("d_model", 1280), heads=acfg.get("encoder_attention_heads", 20),
+                    intermediate=acfg.get("encoder_ffn_dim", 5120), depth=acfg.get("encoder_layers", 32),
+                    n_mels=acfg.get("num_mel_bins", 128), n_window=acfg.get("n_window", 50),
+                    n_window_infer=acfg.get("n_window_infer", 400), conv_chunksize=acfg.get("conv_chunksize", 500),
+                    downsample_hidden=acfg.get("downsample_hidden_size", 480))
+                kw["vision"]["audio_token_id"] = cfg.get("audio_token_id", 151646)
             rsc = tc.get("rope_scaling") or tc.get("rope_parameters") or {}
             kw["mrope_section"] = tuple(rsc.get("mrope_section", ()))
             # Qwen3-VL interleaves the three position axes over the rotary pairs (t h w t h w ...); Qwen2-VL / 2.5-VL

@@ -476,9 +476,11 @@ class QwenVLForConditionalGeneration(_VLBase):
             n = n.replace(a, b)
         import re
         # deepstack_merger_list.<k>.{norm,linear_fc1,linear_fc2}.* -> ds_{norm,fc1,fc2}.<k>.*
-        m = re.match(r"ds_(\d+)\.(norm|linear_fc1|linear_fc2)\.(.*)", n)
+        # (Qwen3-Omni: merger_list.<k>.{ln_q,mlp.0,mlp.2}.*)
+        m = re.match(r"(?:ds_|merger_list\.)(\d+)\.(norm|linear_fc1|linear_fc2|ln_q|mlp\.0|mlp\.2)\.(.*)", n)
         if m:
-            kind = {"norm": "ds_norm", "linear_fc1": "ds_fc1", "linear_fc2": "ds_fc2"}[m.group(2)]
+            kind = {"norm": "ds_norm", "linear_fc1": "ds_fc1", "linear_fc2": "ds_fc2", "ln_q": "ds_norm",
+                    "mlp.0": "ds_fc1", "mlp.2": "ds_fc2"}[m.group(2)]
             return f"{kind}.{m.group(1)}.{m.group(3)}"
         return n
 
