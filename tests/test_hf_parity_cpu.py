@@ -90,6 +90,10 @@ CASES = [
           rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
                            "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25,
                                               "rope_theta": 1000000.0}}), 1e-4),
+    # ... and the sparse block beside every dense MLP (own router: scale-free norm, per-channel and per-expert scales)
+    ("gemma4_moe_block", "Gemma4TextConfig", "Gemma4ForCausalLM", "Gemma4ForCausalLM",
+     dict(GEMMA4, global_head_dim=32, hidden_size_per_layer_input=0, num_kv_shared_layers=0, enable_moe_block=True,
+          num_experts=4, top_k_experts=2, moe_intermediate_size=64), 1e-4),
     # GLM-MoE-DSA (DeepSeek-V3.2 style sparse attention): with a top-k above the prompt length every key is selected,
     # so the whole path (indexer, index conversion, sparse MLA) must reproduce dense attention
     ("glm_moe_dsa_indexer", "GlmMoeDsaConfig", "GlmMoeDsaForCausalLM", "GlmMoeDsaForCausalLM",

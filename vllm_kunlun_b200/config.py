@@ -371,6 +371,13 @@ class ModelConfig:
                       sliding_window=cfg.get("sliding_window"), sliding_window_pattern=cfg.get("sliding_window_pattern", 6),
                       tie_word_embeddings=True)
             if arch.startswith("Gemma4"):
+                # sparse block beside the dense MLP of every layer (26B-A4B): top_k_experts of num_experts
+                if cfg.get("enable_moe_block") and cfg.get("num_experts"):
+                    kw.update(num_experts=int(cfg["num_experts"]), num_experts_per_tok=int(cfg.get("top_k_experts") or 8),
+                              moe_intermediate_size=int(cfg.get("moe_intermediate_size") or cfg["intermediate_size"]),
+                              first_dense_layers=0, moe_layer_freq=1, scoring_func="softmax", norm_topk_prob=True)
+                else:
+                    kw["num_experts"] = 0
                 # Gemma-4: norm weights multiply directly (no 1 + w), softmax scale 1 (q / k are normalised), V is
                 # RMS-normalised, a scalar per layer, rotary parameters per layer type ("proportional" on the full-
                 # attention layers: only a fraction of the angle pairs rotates)

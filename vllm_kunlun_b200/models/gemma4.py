@@ -18,7 +18,7 @@ from ..config import ModelConfig
 from ..parallel.state import get_state
 from .dense import GatedMLP, GQAAttention
 from .layers import ReplicatedLinear, RMSNorm, VocabParallelEmbedding, param, reduce_add_rmsnorm
-from .moe import MoEForCausalLM, SparseMoEBlock
+from .moe import FusedExperts, MoEForCausalLM
 
 
 def kv_source_layer(cfg: ModelConfig, i: int) -> int:
@@ -94,6 +94,28 @@ class Gemma4Attention(GQAAttention):
         return self.o_proj(o.reshape(T, self.num_heads * self.head_dim))
 
 
+class Gemma4Router(nn.Module):
+    """RMS-normalise (no weight), multiply by a learned per-channel scale and ``hidden ** -0.5``, project to expert
+    scores; softmax over ALL experts, keep the top k, renormalise them to sum 1, then multiply each by its expert's
+    learned scale."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.scale = param(cfg.hidden_size, dtype=dtype, device=device)
+        self.proj = ReplicatedLinear(cfg.hidden_size, cfg.num_experts, dtype=dtype, device=device)
+        self.per_expert_scale = param(cfg.num_experts, dtype=dtype, device=device)
+
+    def forward(self, x):
+        cfg = self.cfg
+        xf = x.float()
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps)
+        xf = (xf * self.scale.float() * cfg.hidden_size ** -0.5).to(x.dtype)
+        w, ids = ops.moe_route(ops.router_gemm(xf, self.proj.weight, None), cfg.num_experts_per_tok, "softmax", True,
+                               None, 1, 1, 1.0)
+        return w * self.per_expert_scale.float()[ids.long()], ids
+
+
 class Gemma4DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
         super().__init__()
@@ -102,13 +124,18 @@ class Gemma4DecoderLayer(nn.Module):
         self.input_layernorm, self.post_attention_layernorm = norm(), norm()
         self.pre_feedforward_layernorm, self.post_feedforward_layernorm = norm(), norm()
         self.self_attn = Gemma4Attention(cfg, layer_idx, dtype, device)
-        if cfg.layer_is_moe(layer_idx):
-            self.mlp = SparseMoEBlock(cfg, dtype, device)
-        else:
-            shared = cfg.num_kv_shared_layers > 0 and layer_idx >= cfg.num_layers - cfg.num_kv_shared_layers
-            inter = cfg.intermediate_size * (2 if cfg.double_wide_mlp and shared else 1)
-            self.mlp = GatedMLP(cfg.hidden_size, inter, dtype, device, cfg.quantization, cfg.hidden_act,
-                                cfg.mlp_bias, reduce_results=False)
+        shared = cfg.num_kv_shared_layers > 0 and layer_idx >= cfg.num_layers - cfg.num_kv_shared_layers
+        inter = cfg.intermediate_size * (2 if cfg.double_wide_mlp and shared else 1)
+        self.mlp = GatedMLP(cfg.hidden_size, inter, dtype, device, cfg.quantization, cfg.hidden_act,
+                            cfg.mlp_bias, reduce_results=False)
+        # sparse block BESIDE the dense MLP (reference gemma4.py:131-252,520-535,612-630): the router reads the
+        # stream before the MLP; both branches are normed on their own, added, and normed once more
+        self.moe = cfg.layer_is_moe(layer_idx)
+        if self.moe:
+            self.router = Gemma4Router(cfg, dtype, device)
+            self.experts = FusedExperts(cfg, dtype, device)
+            self.post_feedforward_layernorm_1, self.post_feedforward_layernorm_2 = norm(), norm()
+            self.pre_feedforward_layernorm_2 = norm()
         # per-layer inputs (reference gemma4.py:553-581,632-640): a gate from the stream selects from this layer's
         # slice of the per-token embedding, which is projected back, normed and added; then the layer scalar
         self.ple = cfg.per_layer_input_size
@@ -137,6 +164,12 @@ class Gemma4DecoderLayer(nn.Module):
         a, _ = reduce_add_rmsnorm(a, None, self.post_attention_layernorm, True)
         h, residual = self.pre_feedforward_layernorm(a, residual)
         m = self.mlp(h)
+        if self.moe:
+            m, _ = reduce_add_rmsnorm(m, None, self.post_feedforward_layernorm_1, True)
+            w, ids = self.router(residual)
+            e = self.experts(self.pre_feedforward_layernorm_2(residual), w, ids)
+            e, _ = reduce_add_rmsnorm(e, None, self.post_feedforward_layernorm_2, True)
+            return self.post_feedforward_layernorm(m + e), residual
         m, _ = reduce_add_rmsnorm(m, None, self.post_feedforward_layernorm, True)
         return m, residual
 
@@ -211,11 +244,26 @@ class Gemma4ForCausalLM(MoEForCausalLM):
     def load_weights(self, weights):
         # full-attention layers whose values are their keys have no v_proj tensor: the fused projection's V rows
         # take the K weight (V = k_proj(x), before the key's norm and rotation)
-        out = []
+        out, loaded = [], set()
         for name, w in weights:
+            if ".experts." in name and w.dim() == 3:
+                # layers.L.experts.{gate_up_proj [E, 2 I, H] (gate rows first), down_proj [E, H, I]}; the multimodal
+                # checkpoints spell it layers.L.moe.experts.*
+                parts = name.removeprefix("model.").split(".")
+                layer = self.layers[parts[1]] if parts[1] in self.layers else None
+                if layer is not None and getattr(layer, "moe", False):
+                    for e in range(w.shape[0]):
+                        if parts[-1] == "down_proj":
+                            layer.experts.load_expert(e, "down_proj", "weight", w[e])
+                        else:
+                            half = w.shape[1] // 2
+                            layer.experts.load_expert(e, "gate_proj", "weight", w[e, :half])
+                            layer.experts.load_expert(e, "up_proj", "weight", w[e, half:])
+                    loaded.add(name)
+                continue
             out.append((name, w))
             if self.cfg.attention_k_eq_v and ".self_attn.k_proj." in name:
                 parts = name.removeprefix("model.").split(".")
                 if parts[0] == "layers" and parts[1].isdigit() and not self.cfg.layer_is_sliding(int(parts[1])):
                     out.append((name.replace(".k_proj.", ".v_proj."), w))
-        return super().load_weights(out)
+        return loaded | super().load_weights(out)

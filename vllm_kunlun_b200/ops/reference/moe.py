@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import torch
 
-from .basic import dequant_fp8_block, quant_fp8_per_group, silu_and_mul, swigluoai_and_mul
+from .basic import dequant_fp8_block, gelu_tanh_and_mul, quant_fp8_per_group, silu_and_mul, swigluoai_and_mul
 
 
 def route_softmax_topk(logits, k: int, renormalize: bool = True):
@@ -108,6 +108,6 @@ def fused_moe(x, w13, w2, topk_weights, topk_ids, act: str = "silu", b13=None, b
         return (q.float().reshape(*s.shape, block[1]) * s.unsqueeze(-1)).reshape(t.shape).to(t.dtype)
 
     h = grouped_gemm(_q(xs), w13f, lod, b13)
-    h = swigluoai_and_mul(h) if act == "swigluoai" else silu_and_mul(h)
+    h = {"swigluoai": swigluoai_and_mul, "gelu_tanh": gelu_tanh_and_mul}.get(act, silu_and_mul)(h)
     y = grouped_gemm(_q(h), w2f, lod, b2)
     return moe_unpermute(y, order, wts, T)
