@@ -356,3 +356,68 @@ def test_qwen3_omni_thinker_matches_the_transformers_implementation():
                  multi_modal_data={"pixel_values": px, "image_grid_thw": [[1, 4, 6]], "input_features": feats,
                                    "feature_lens": [frames]})
     assert (seen[0][-1] - want).abs().max().item() < 1e-4
+
+
+def test_gemma4_with_images_matches_the_transformers_implementation():
+    """Gemma-4 vision tower (position rows looked up by x and y, 2-D rotary embedding, clipped linears, pooling,
+    standardisation) on two images of different grids, and the logits after a prompt holding both: soft tokens after
+    the embedding scale, per-layer inputs of placeholder rows from the padding token."""
+    if not hasattr(transformers, "Gemma4ForConditionalGeneration"):
+        pytest.skip(f"transformers {transformers.__version__} has no Gemma-4")
+    torch.manual_seed(0)
+    IMG, BOI, EOI = 150, 151, 152
+    tc = dict(vocab_size=200, hidden_size=128, num_hidden_layers=4, layer_types=["sliding_attention", "full_attention"] * 2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=32, global_head_dim=32, intermediate_size=256,
+              max_position_embeddings=256, sliding_window=8, hidden_size_per_layer_input=32,
+              vocab_size_per_layer_input=200, num_kv_shared_layers=0)
+    vc = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, patch_size=4, position_embedding_size=32, pooling_kernel_size=2, standardize=True,
+              use_clipped_linears=True)
+    hf_cfg = transformers.Gemma4Config(text_config=tc, vision_config=vc, audio_config=None, image_token_id=IMG,
+                                       boi_token_id=BOI, eoi_token_id=EOI, video_token_id=153, audio_token_id=154)
+    hf_cfg._attn_implementation = "eager"
+    hf = transformers.Gemma4ForConditionalGeneration(hf_cfg).eval().float()
+    _randomise(hf)
+    with torch.no_grad():
+        hf.model.vision_tower.std_bias.copy_(torch.randn(64) * 0.1)
+        hf.model.vision_tower.std_scale.copy_(1 + 0.1 * torch.randn(64))
+        for name, buf in hf.model.vision_tower.named_buffers():
+            if name.endswith("_min"):
+                buf.fill_(-0.8)
+            elif name.endswith("_max"):
+                buf.fill_(0.9)
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = ["Gemma4ForConditionalGeneration"], "float32"
+    llm = LLM(ModelConfig.from_hf_config(d), device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=64)
+    model = llm.engine.runner.model
+    sd = hf.state_dict()
+    with torch.inference_mode():
+        loaded = model.load_weights(list(sd.items()))
+    assert [k for k in sd if k not in loaded] == ["lm_head.weight"]         # tied to the embedding
+    grids = [(1, 4, 6), (1, 6, 4)]
+    px = torch.rand(sum(h * w for _, h, w in grids), 3 * 16)
+
+    def positions(h, w):
+        return torch.stack([torch.arange(w).repeat(h), torch.arange(h).repeat_interleave(w)], -1)
+
+    # the reference takes one padded batch row per image: both images have 24 patches
+    pos = torch.stack([positions(h, w) for _, h, w in grids])
+    with torch.no_grad():
+        want_v = hf.model.get_image_features(px.view(2, 24, -1), pos).pooler_output.float()
+    with torch.inference_mode():
+        got_v = model.embed_multimodal(px, grids).float()
+    assert got_v.shape == (12, 128) and (got_v - want_v.reshape(12, 128)).abs().max().item() < 1e-4
+    ids = [5, 6, BOI] + [IMG] * 6 + [EOI, 7, BOI] + [IMG] * 6 + [EOI, 8, 9]
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([ids]), pixel_values=px.view(2, 24, -1), image_position_ids=pos).logits[0, -1].float()
+    seen, compute_logits = [], model.compute_logits
+
+    def recording(h):
+        out = compute_logits(h)
+        seen.append(out.detach().float().clone())
+        return out
+
+    model.compute_logits = recording
+    llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
+                 multi_modal_data={"pixel_values": px, "image_grid_thw": [list(g) for g in grids]})
+    assert (seen[0][-1] - want).abs().max().item() < 2e-4

@@ -145,12 +145,12 @@ def test_gemma_per_layer_inputs_and_multimodal():
     # multimodal wrapper
     IMG = 127
     cfg.architecture = "Gemma4ForConditionalGeneration"
-    cfg.vision = dict(depth=2, hidden=32, heads=2, patch=2, intermediate=64, in_channels=3, image_size=8, pool=2,
-                      image_token_id=IMG)
+    cfg.vision = dict(depth=2, hidden=32, heads=2, patch=2, intermediate=64, in_channels=3, pool=2,
+                      position_embedding_size=16, image_token_id=IMG)
     vl = LLM(cfg, max_num_batched_tokens=64, **KW)
     tower = vl.engine.runner.model.visual
-    assert tower.tokens_per_image == 4
-    px = torch.randn(1, 16, 12, generator=torch.Generator().manual_seed(1))
+    assert tower.tokens_per_image((1, 4, 4)) == 4
+    px = torch.rand(1, 16, 12, generator=torch.Generator().manual_seed(1))      # a 4 x 4 grid of 2 x 2-pixel patches
     assert vl.engine.runner.model.embed_multimodal(px).shape == (4, H)
     prompt = [5, 6] + [IMG] * 4 + [9, 10, 11]
     o1 = vl.generate([prompt], sp, multi_modal_data={"pixel_values": px})[0].token_ids

@@ -361,6 +361,18 @@ class ModelConfig:
             # Qwen3-VL interleaves the three position axes over the rotary pairs (t h w t h w ...); Qwen2-VL / 2.5-VL
             # give each axis a contiguous section
             kw["mrope_interleaved"] = bool(rsc.get("mrope_interleaved", arch.startswith("Qwen3VL") or arch.startswith("Qwen3Omni")))
+        if vcfg and arch.startswith("Gemma"):
+            rp = vcfg.get("rope_parameters") or {}
+            kw["vision"] = dict(
+                depth=vcfg.get("num_hidden_layers", 16), hidden=vcfg.get("hidden_size", 768),
+                heads=vcfg.get("num_attention_heads", 12), kv_heads=vcfg.get("num_key_value_heads"),
+                head_dim=vcfg.get("head_dim"), patch=vcfg.get("patch_size", 16),
+                intermediate=vcfg.get("intermediate_size", 3072), in_channels=3,
+                position_embedding_size=vcfg.get("position_embedding_size", 10240),
+                pool=vcfg.get("pooling_kernel_size", 3), standardize=bool(vcfg.get("standardize")),
+                eps=vcfg.get("rms_norm_eps", 1e-6), rope_theta=float(rp.get("rope_theta", 100.0)),
+                image_token_id=cfg.get("image_token_id", 258880), text_architecture="Gemma4ForCausalLM",
+                pad_token_id=int((cfg.get("text_config") or {}).get("pad_token_id") or 0))
         if arch.startswith("Gemma"):
             kw.update(num_kv_shared_layers=cfg.get("num_kv_shared_layers", 0) or 0,
                       final_logit_softcapping=float(cfg.get("final_logit_softcapping") or 0.0),

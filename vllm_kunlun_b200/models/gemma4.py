@@ -207,9 +207,16 @@ class Gemma4ForCausalLM(MoEForCausalLM):
             hidden = self.embed_tokens(input_ids)
             hidden = hidden * torch.tensor(self.embed_scale, dtype=hidden.dtype, device=hidden.device)
             hook = getattr(self, "input_embeds_hook", None)
+            ple_ids = input_ids
             if hook is not None:  # multimodal wrapper: image rows replace the placeholder embeddings
-                hidden = hook(hidden)
-        ple = self.per_layer_inputs(input_ids, hidden) if self.ple else None
+                hidden, rows = hook(hidden)
+                if rows is not None and self.ple:
+                    # the per-layer token embedding of a placeholder row is the padding token's; the projected part
+                    # is computed from the soft token itself
+                    ple_ids = input_ids.index_fill(0, rows, int((self.cfg.vision or {}).get("pad_token_id", 0)))
+        else:
+            ple_ids = input_ids
+        ple = self.per_layer_inputs(ple_ids, hidden) if self.ple else None
         for i in range(self.first_layer, self.last_layer):
             layer = self.layers[str(i)]
             hidden, residual = layer(hidden, residual)

@@ -516,61 +516,162 @@ class InternVLChatModel(_VLBase):
         return n
 
 
+class _ClippedLinear(nn.Module):
+    """Bias-free linear whose input and output are clamped to learned ranges (checkpoint buffers ``input_min`` /
+    ``input_max`` / ``output_min`` / ``output_max``; infinite when the checkpoint has none)."""
+
+    def __init__(self, n_in: int, n_out: int, dtype, device):
+        super().__init__()
+        self.linear = ReplicatedLinear(n_in, n_out, bias=False, dtype=dtype, device=device)
+        self.register_buffer("clip", torch.tensor([-math.inf, math.inf, -math.inf, math.inf], dtype=torch.float32,
+                                                  device=device), persistent=False)
+        self.clipped = False
+
+    def forward(self, x):
+        if not self.clipped:
+            return self.linear(x)
+        c = self.clip.tolist()
+        return self.linear(x.clamp(c[0], c[1])).clamp(c[2], c[3])
+
+
+class Gemma4VisionBlock(nn.Module):
+    """Encoder layer of the Gemma-4 tower: sandwich RMSNorms (weights multiply directly), q / k RMSNorm per head, V
+    RMS-normalised without a weight, softmax scale 1, rotary embedding over the patch's (x, y) position - the first
+    half of a head rotates with x, the second with y - and a gated tanh-GELU MLP."""
+
+    def __init__(self, vc: dict, dtype, device):
+        super().__init__()
+        h, self.heads, self.kv_heads = vc["hidden"], vc["heads"], vc.get("kv_heads") or vc["heads"]
+        self.head_dim = vc.get("head_dim") or h // self.heads
+        eps = self.eps = vc.get("eps", 1e-6)
+        lin = lambda a, b: _ClippedLinear(a, b, dtype, device)  # noqa: E731
+        self.q_proj, self.k_proj = lin(h, self.heads * self.head_dim), lin(h, self.kv_heads * self.head_dim)
+        self.v_proj, self.o_proj = lin(h, self.kv_heads * self.head_dim), lin(self.heads * self.head_dim, h)
+        self.q_norm = RMSNorm(self.head_dim, eps, dtype, device)
+        self.k_norm = RMSNorm(self.head_dim, eps, dtype, device)
+        self.gate_proj, self.up_proj = lin(h, vc["intermediate"]), lin(h, vc["intermediate"])
+        self.down_proj = lin(vc["intermediate"], h)
+        self.input_layernorm, self.post_attention_layernorm = RMSNorm(h, eps, dtype, device), RMSNorm(h, eps, dtype, device)
+        self.pre_feedforward_layernorm = RMSNorm(h, eps, dtype, device)
+        self.post_feedforward_layernorm = RMSNorm(h, eps, dtype, device)
+
+    @staticmethod
+    def _rope2d(x, cos, sin):
+        """``x [T, heads, D]``; ``cos`` / ``sin [T, D]``: two halves of ``D / 2`` channels, each rotated split-half."""
+        D = x.shape[-1]
+        part = 2 * (D // 4)
+        out = []
+        for k in range(2):
+            xp = x[..., k * part:(k + 1) * part].float()
+            c, s_ = cos[:, None, k * part:(k + 1) * part], sin[:, None, k * part:(k + 1) * part]
+            x1, x2 = xp[..., :part // 2], xp[..., part // 2:]
+            out.append(xp * c + torch.cat([-x2, x1], -1) * s_)
+        if 2 * part < D:
+            out.append(x[..., 2 * part:].float())
+        return torch.cat(out, -1).to(x.dtype)
+
+    def forward(self, x, cu_seqlens, cos, sin):
+        T = x.shape[0]
+        h = self.input_layernorm(x)
+        q = self.q_norm(self.q_proj(h).view(T * self.heads, self.head_dim)).view(T, self.heads, self.head_dim)
+        k = self.k_norm(self.k_proj(h).view(T * self.kv_heads, self.head_dim)).view(T, self.kv_heads, self.head_dim)
+        v = self.v_proj(h).view(T, self.kv_heads, self.head_dim).float()
+        v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
+        q, k = self._rope2d(q, cos, sin), self._rope2d(k, cos, sin)
+        if self.kv_heads != self.heads:
+            rep = self.heads // self.kv_heads
+            k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+        a = ops.varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, 1.0)
+        x = x + self.post_attention_layernorm(self.o_proj(a.reshape(T, -1)))
+        h = self.pre_feedforward_layernorm(x)
+        m = torch.nn.functional.gelu(self.gate_proj(h).float(), approximate="tanh").to(h.dtype) * self.up_proj(h)
+        return x + self.post_feedforward_layernorm(self.down_proj(m))
+
+
 class GemmaVisionTower(nn.Module):
-    """SigLIP-style tower of the Gemma multimodal models: patch embedding with a learned position table, LayerNorm
-    blocks, average pooling of ``pool x pool`` patch windows, then the (1 + w) RMSNorm + linear projector into the
-    decoder width (``models/gemma4_mm.py`` of the reference)."""
+    """Gemma-4 vision tower (``models/gemma4_mm.py`` of the reference drives upstream's tower of the same design):
+    patches (values in [0, 1], rescaled to [-1, 1]) are projected without a bias and get the sum of two learned
+    position rows - one looked up by the patch's x, one by its y; encoder layers with 2-D rotary embedding;
+    ``pool x pool`` patches are averaged into one soft token, scaled by ``sqrt(hidden)``, optionally standardised
+    with learned statistics; then an RMS norm without a weight and the projection into the decoder width."""
 
     def __init__(self, vc: dict, out_hidden: int, dtype, device):
         super().__init__()
         self.vc = vc
         h = vc["hidden"]
         self.patch_dim = vc.get("in_channels", 3) * vc["patch"] ** 2
-        self.patch_embed = ReplicatedLinear(self.patch_dim, h, bias=True, dtype=dtype, device=device)
-        self.side = vc["image_size"] // vc["patch"]
-        self.pos = param(self.side ** 2, h, dtype=dtype, device=device)
-        blk = dict(vc, norm="layernorm", act="gelu")
-        self.blocks = nn.ModuleList([VisionBlock(blk, dtype, device) for _ in range(vc["depth"])])
-        self.post_norm = _Norm(h, 1e-6, "layernorm", dtype, device)
-        self.pool = vc.get("pool", 4)
-        self.soft_norm_weight = param(h, dtype=dtype, device=device)   # (1 + w) RMSNorm
+        self.input_proj = ReplicatedLinear(self.patch_dim, h, bias=False, dtype=dtype, device=device)
+        self.position_embedding_table = param(2, vc.get("position_embedding_size", 10240), h, dtype=dtype, device=device)
+        self.blocks = nn.ModuleList([Gemma4VisionBlock(vc, dtype, device) for _ in range(vc["depth"])])
+        self.pool = vc.get("pool", 3)
+        self.standardize = bool(vc.get("standardize"))
+        if self.standardize:
+            self.std_bias, self.std_scale = param(h, dtype=dtype, device=device), param(h, dtype=dtype, device=device)
         self.proj = ReplicatedLinear(h, out_hidden, bias=False, dtype=dtype, device=device)
+        self.eps = vc.get("eps", 1e-6)
+        self.theta = float(vc.get("rope_theta", 100.0))
+        self.head_dim = vc.get("head_dim") or h // vc["heads"]
         self.merge = 1
 
-    @property
-    def tokens_per_image(self) -> int:
-        return (self.side // self.pool) ** 2
+    def tokens_per_image(self, grid) -> int:
+        _, gh, gw = grid
+        return (gh // self.pool) * (gw // self.pool)
 
     def forward(self, pixel_values: torch.Tensor, grid_thw=None) -> torch.Tensor:
-        """``pixel_values [n_images, side^2, patch_dim]`` -> ``[n_images * (side / pool)^2, out_hidden]``."""
-        n, L, _ = pixel_values.shape
-        x = self.patch_embed(pixel_values.reshape(n * L, -1).to(self.pos.dtype)).view(n, L, -1) + self.pos.unsqueeze(0)
-        x = x.reshape(n * L, -1)
-        cu = (torch.arange(n + 1, dtype=torch.int32) * L).to(x.device)
+        """``pixel_values [sum(h * w), patch_dim]`` (patches of every image row-major, values in [0, 1]) and the
+        patch grids ``[(1, h, w), ...]`` (``h``, ``w`` multiples of the pooling size) -> ``[sum(h * w / pool^2),
+        out_hidden]``."""
+        if pixel_values.dim() == 3:      # [n_images, patches, patch_dim] of equal square images
+            n, L, _ = pixel_values.shape
+            side = int(math.isqrt(L))
+            grid_thw = grid_thw or [(1, side, side)] * n
+            pixel_values = pixel_values.reshape(n * L, -1)
+        dt, dev = self.input_proj.weight.dtype, pixel_values.device
+        xs, ys = [], []
+        for _, gh, gw in grid_thw:
+            ys.append(torch.arange(gh, device=dev).repeat_interleave(gw))
+            xs.append(torch.arange(gw, device=dev).repeat(gh))
+        px, py = torch.cat(xs), torch.cat(ys)
+        x = self.input_proj((2.0 * (pixel_values.float() - 0.5)).to(dt))
+        x = x + self.position_embedding_table[0, px] + self.position_embedding_table[1, py]
+        half = self.head_dim // 2        # channels per axis; frequencies as for a head of that size
+        inv = 1.0 / (self.theta ** (torch.arange(0, half, 2, dtype=torch.float32, device=dev) / half))
+        fx, fy = px[:, None].float() * inv[None], py[:, None].float() * inv[None]
+        ang = torch.cat([fx, fx, fy, fy], -1)
+        cos, sin = ang.cos(), ang.sin()
+        lens = [gh * gw for _, gh, gw in grid_thw]
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(lens).cumsum(0)
+        cu = cu.to(dev)
         for blk in self.blocks:
-            x = blk(x, cu)
-        x = self.post_norm(x).view(n, self.side, self.side, -1)
-        k = self.pool
-        x = x.view(n, self.side // k, k, self.side // k, k, -1).float().mean((2, 4)).reshape(n * self.tokens_per_image, -1)
-        x = ops.rmsnorm(x.to(self.pos.dtype), self.soft_norm_weight, 1e-6, True)
-        return self.proj(x)
+            x = blk(x, cu, cos, sin)
+        k, outs, o = self.pool, [], 0
+        for (_, gh, gw), n in zip(grid_thw, lens):
+            img = x[o:o + n].view(gh // k, k, gw // k, k, -1).float().mean((1, 3))
+            outs.append(img.reshape((gh // k) * (gw // k), -1))
+            o += n
+        x = torch.cat(outs) * (x.shape[-1] ** 0.5)
+        if self.standardize:
+            x = (x - self.std_bias.float()) * self.std_scale.float()
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
+        return self.proj(x.to(dt))
 
 
 class Gemma4ForConditionalGeneration(_VLBase):
     """Gemma-4 with the vision tower (``Gemma4ForConditionalGeneration``, ``models/gemma4_mm.py`` in the reference):
     image soft tokens replace the placeholder embeddings AFTER the embedding scale, 1-D rotary positions, and the
-    per-layer inputs of placeholder rows come from row 0 of the per-layer table."""
+    per-layer token embedding of a placeholder row is the padding token's.  Image rows attend causally, as in
+    the reference (the training-time mask lets the soft tokens of one image see each other in the sliding layers).
+    The audio tower of the any-to-any checkpoints is not built: their audio tensors are skipped."""
 
     tower_cls = GemmaVisionTower
     uses_mrope = False
 
-    _MAP = {"vision_tower.vision_model.embeddings.patch_embedding.": "patch_embed.",
-            "vision_tower.vision_model.embeddings.position_embedding.weight": "pos",
-            "vision_tower.vision_model.encoder.layers.": "blocks.", ".self_attn.out_proj.": ".proj.",
-            ".layer_norm1.": ".norm1.", ".layer_norm2.": ".norm2.", ".mlp.fc1.": ".fc1.", ".mlp.fc2.": ".fc2.",
-            "vision_tower.vision_model.post_layernorm.": "post_norm.",
-            "multi_modal_projector.mm_soft_emb_norm.weight": "soft_norm_weight",
-            "multi_modal_projector.mm_input_projection.": "proj."}
+    _MAP = {"vision_tower.patch_embedder.input_proj.": "input_proj.",
+            "vision_tower.patch_embedder.position_embedding_table": "position_embedding_table",
+            "vision_tower.encoder.layers.": "blocks.", ".self_attn.": ".", ".mlp.": ".",
+            "vision_tower.std_bias": "std_bias", "vision_tower.std_scale": "std_scale",
+            "embed_vision.embedding_projection.": "proj."}
 
     def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
         cfg.vision.setdefault("text_architecture", "Gemma4ForCausalLM")
@@ -578,19 +679,47 @@ class Gemma4ForConditionalGeneration(_VLBase):
         self.language_model.input_embeds_hook = self._inject
 
     def _inject(self, hidden):
+        """-> (embeddings with the soft tokens in place, the rows they went to or None)."""
         ex = get_forward_context().extras
-        if ex.get("mm_dst") is not None:
-            hidden = hidden.clone()
-            hidden.index_copy_(0, ex["mm_dst"], ex["mm_src"][:, : hidden.shape[1]].to(hidden.dtype))
-        return hidden
+        if ex.get("mm_dst") is None:
+            return hidden, None
+        hidden = hidden.clone()
+        hidden.index_copy_(0, ex["mm_dst"], ex["mm_src"][:, : hidden.shape[1]].to(hidden.dtype))
+        return hidden, ex["mm_dst"]
 
     def forward(self, input_ids, hidden=None, residual=None):
         return self.language_model(input_ids, hidden, residual)  # injection happens inside, after the embed scale
 
     def _vision_name(self, name):
-        if not (name.startswith("vision_tower.") or name.startswith("multi_modal_projector.")):
+        if not (name.startswith("vision_tower.") or name.startswith("embed_vision.")):
             return None
         n = name
         for a, b in self._MAP.items():
             n = n.replace(a, b)
         return n
+
+    def load_weights(self, weights):
+        """Besides the tensors: the clipping ranges of the tower's linears (scalars ``*.input_min`` ...), kept in each
+        linear's ``clip`` buffer; audio tensors are skipped.  Returns the checkpoint names that were used."""
+        slot = {"input_min": 0, "input_max": 1, "output_min": 2, "output_max": 3}
+        mods = dict(self.visual.named_modules())
+        keep, original, loaded = [], {}, set()
+        for name, w in weights:
+            n = name.removeprefix("model.")
+            if n.startswith("audio_tower.") or n.startswith("embed_audio."):
+                continue
+            stem, _, leaf = n.rpartition(".")
+            if n.startswith("vision_tower.") and leaf in slot:
+                m = mods.get(self._vision_name(stem))
+                if m is not None:
+                    m.clip[slot[leaf]] = float(w)
+                    m.clipped = bool(torch.isfinite(m.clip).any())
+                    loaded.add(name)
+                continue
+            if n.startswith("language_model."):
+                n = "model." + n[len("language_model."):]
+            elif not (n.startswith("vision_tower.") or n.startswith("embed_vision.")):
+                n = name
+            original[n] = name
+            keep.append((n, w))
+        return loaded | {original.get(g, g) for g in super().load_weights(keep)}
