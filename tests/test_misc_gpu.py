@@ -327,3 +327,4 @@ def test_qwen_vl_engine_on_gpu():
     assert cos > 0.99, cos
     out = LLM(cfg, device="cuda", **kw).generate([prompt], SamplingParams(max_tokens=5, ignore_eos=True), multi_modal_data=mm)
     assert len(out[0].token_ids) == 5
+

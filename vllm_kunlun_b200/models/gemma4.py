@@ -179,7 +179,10 @@ class Gemma4ForCausalLM(MoEForCausalLM):
 
     def __init__(self, cfg: ModelConfig, device="cpu", dtype=None):
         super().__init__(cfg, device, dtype)
-        self.embed_scale = cfg.hidden_size ** 0.5
+        # sqrt(hidden) rounded to the model's dtype, as a device scalar (creating it inside forward would be a
+        # host-to-device copy, which a CUDA-graph capture does not allow)
+        self.register_buffer("embed_scale", torch.tensor(cfg.hidden_size ** 0.5, dtype=self.dtype, device=device),
+                             persistent=False)
         self.ple = cfg.per_layer_input_size
         if self.ple:
             assert get_state().pp_size == 1, "per-layer inputs are computed from the embeddings on the first stage"
@@ -205,7 +208,7 @@ class Gemma4ForCausalLM(MoEForCausalLM):
     def forward(self, input_ids, hidden=None, residual=None):
         if hidden is None:
             hidden = self.embed_tokens(input_ids)
-            hidden = hidden * torch.tensor(self.embed_scale, dtype=hidden.dtype, device=hidden.device)
+            hidden = hidden * self.embed_scale
             hook = getattr(self, "input_embeds_hook", None)
             ple_ids = input_ids
             if hook is not None:  # multimodal wrapper: image rows replace the placeholder embeddings

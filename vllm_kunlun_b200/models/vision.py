@@ -523,14 +523,13 @@ class _ClippedLinear(nn.Module):
     def __init__(self, n_in: int, n_out: int, dtype, device):
         super().__init__()
         self.linear = ReplicatedLinear(n_in, n_out, bias=False, dtype=dtype, device=device)
-        self.register_buffer("clip", torch.tensor([-math.inf, math.inf, -math.inf, math.inf], dtype=torch.float32,
-                                                  device=device), persistent=False)
+        self.clip = [-math.inf, math.inf, -math.inf, math.inf]      # host floats: no device read in forward
         self.clipped = False
 
     def forward(self, x):
         if not self.clipped:
             return self.linear(x)
-        c = self.clip.tolist()
+        c = self.clip
         return self.linear(x.clamp(c[0], c[1])).clamp(c[2], c[3])
 
 
@@ -713,7 +712,7 @@ class Gemma4ForConditionalGeneration(_VLBase):
                 m = mods.get(self._vision_name(stem))
                 if m is not None:
                     m.clip[slot[leaf]] = float(w)
-                    m.clipped = bool(torch.isfinite(m.clip).any())
+                    m.clipped = any(math.isfinite(v) for v in m.clip)
                     loaded.add(name)
                 continue
             if n.startswith("language_model."):
