@@ -50,3 +50,49 @@ def test_hybrid_decode_consistent_with_prefill():
     out = llm.generate([prompt], SamplingParams(max_tokens=5, ignore_eos=True))[0].token_ids
     again = llm.generate([prompt + out[:4]], SamplingParams(max_tokens=1, ignore_eos=True))[0].token_ids
     assert again[0] == out[4]
+
+
+def test_batched_chunked_form_and_its_dispatch(monkeypatch):
+    """The all-chunks-at-once form equals the token-by-token rule (length not a multiple of the chunk, grouped heads,
+    an initial state); with ``B200_GDN_CHUNKED=1`` the varlen op sends long requests through it and the others through
+    the recurrent pass, and leaves the same outputs and states as without the switch."""
+    from vllm_kunlun_b200 import ops
+    torch.manual_seed(1)
+    L, Hk, Hv, Dk, Dv = 150, 2, 4, 16, 32
+    q, k, v = torch.randn(L, Hk, Dk), torch.randn(L, Hk, Dk), torch.randn(L, Hv, Dv)
+    g, beta = -torch.rand(L, Hv) * 0.5, torch.rand(L, Hv)
+    S0 = torch.randn(Hv, Dv, Dk) * 0.1
+    o1, s1 = ref.recurrent_gated_delta_rule(q, k, v, g, beta, S0)
+    o2, s2 = ref.chunk_gated_delta_rule_batched(q, k, v, g, beta, S0, chunk=64)
+    torch.testing.assert_close(o1, o2, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(s1, s2, atol=2e-4, rtol=2e-4)
+    # three requests: 100 tokens with a state, 1 token (decode) with a state, 49 tokens without
+    cu = torch.tensor([0, 100, 101, 150], dtype=torch.int32)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32)
+    has = torch.tensor([True, True, False])
+    base = torch.randn(5, Hv, Dv, Dk) * 0.1
+
+    def run():
+        st = base.clone()
+        return ops.gated_delta_rule(q, k, v, g, beta, st, cu, slots, has, None, True, cu.clone()), st
+
+    calls, inner = [], ref.chunk_gated_delta_rule_batched
+    monkeypatch.setattr(ref, "chunk_gated_delta_rule_batched", lambda *a, **kw: (calls.append(a[0].shape[0]), inner(*a, **kw))[1])
+    monkeypatch.setenv("B200_GDN_CHUNKED", "0")
+    want, want_st = run()
+    assert calls == []
+    monkeypatch.setenv("B200_GDN_CHUNKED", "1")
+    got, got_st = run()
+    assert calls == [100]                   # only the 100-token request took the chunked form
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(got_st, want_st, atol=2e-4, rtol=2e-4)
+    assert torch.equal(got_st[1], base[1]) and torch.equal(got_st[4], base[4])      # untouched slots
+    # and the model: same tokens either way
+    cfg = _cfg()
+    prompts = [list(range(3, 100)), list(range(50, 61))]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    kw = dict(device="cpu", block_size=16, max_model_len=160, max_num_seqs=4, num_gpu_blocks=48, max_num_batched_tokens=160)
+    b = [o.token_ids for o in LLM(cfg, **kw).generate(prompts, sp)]
+    monkeypatch.setenv("B200_GDN_CHUNKED", "0")
+    a = [o.token_ids for o in LLM(cfg, **kw).generate(prompts, sp)]
+    assert a == b

@@ -82,3 +82,32 @@ def test_qwen3_omni_audio_tower_on_gpu():
         got = gpu(feats.to(DEV), lens).float().cpu()
     assert got.shape == want.shape == (sum(cpu.output_lengths(lens)), 256)
     assert torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0) > 0.99
+
+
+def test_chunked_gated_delta_rule_on_gpu(monkeypatch):
+    """``B200_GDN_CHUNKED=1``: a 300-token request takes the chunked form (batched products on the GPU), a decode
+    row and a short request keep the recurrent kernel; outputs and states equal the fp32 token-by-token rule."""
+    from vllm_kunlun_b200 import ops
+    from vllm_kunlun_b200.ops.reference import misc as ref
+    torch.manual_seed(0)
+    lens = [300, 1, 40]
+    L, Hk, Hv, Dk, Dv = sum(lens), 2, 4, 128, 128
+    q, k = torch.randn(L, Hk, Dk).bfloat16(), torch.randn(L, Hk, Dk).bfloat16()
+    v = torch.randn(L, Hv, Dv).bfloat16()
+    g, beta = -torch.rand(L, Hv) * 0.3, torch.rand(L, Hv)
+    cu = torch.tensor([0, 300, 301, 341], dtype=torch.int32)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32)
+    has = torch.tensor([True, True, False])
+    base = torch.randn(5, Hv, Dv, Dk) * 0.1
+    want, want_st = torch.empty(L, Hv, Dv), base.clone()
+    for r in range(3):
+        s, e, slot = int(cu[r]), int(cu[r + 1]), int(slots[r])
+        S0 = base[slot] if bool(has[r]) else torch.zeros_like(base[slot])
+        o, S = ref.recurrent_gated_delta_rule(q[s:e], k[s:e], v[s:e], g[s:e], beta[s:e], S0)
+        want[s:e], want_st[slot] = o.float(), S
+    monkeypatch.setenv("B200_GDN_CHUNKED", "1")
+    st = base.to(DEV)
+    got = ops.gated_delta_rule(q.to(DEV), k.to(DEV), v.to(DEV), g.to(DEV), beta.to(DEV), st, cu.to(DEV), slots.to(DEV),
+                               has.to(DEV), None, True, cu.clone())
+    torch.testing.assert_close(got.float().cpu(), want, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(st.cpu(), want_st, atol=2e-2, rtol=2e-2)

@@ -48,6 +48,8 @@ _ENV: dict[str, Callable[[], Any]] = {
     "B200_EP_A2A_MAX_TOKENS": lambda: int(os.environ.get("B200_EP_A2A_MAX_TOKENS", "8192")),
     # MLA prefill in the up-projected 192 / 128 form for requests with many new tokens (0: absorbed form everywhere)
     "B200_MLA_PREFILL_FORM": lambda: os.environ.get("B200_MLA_PREFILL_FORM", "1") != "0",
+    # gated delta rule of requests with >= 64 new tokens in the chunked form (batched products per 64-token chunk)
+    "B200_GDN_CHUNKED": lambda: os.environ.get("B200_GDN_CHUNKED", "0") == "1",
     # the chat endpoint fetches http(s) image URLs (off: only data: URIs and local files are read)
     "B200_ALLOW_REMOTE_IMAGES": lambda: os.environ.get("B200_ALLOW_REMOTE_IMAGES", "0") == "1",
     # bounded-wait budget of cross-GPU spins (iterations)

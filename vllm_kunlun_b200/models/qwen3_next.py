@@ -75,7 +75,7 @@ class GatedDeltaNet(nn.Module):
         k = mixed[:, self.key_dim:2 * self.key_dim].view(T, self.hk, self.dk)
         v = mixed[:, 2 * self.key_dim:].view(T, self.hv, self.dv)
         o = ops.gated_delta_rule(q, k, v, g, beta, ssm_state, md.query_start_loc, md.state_indices, md.has_initial_state,
-                                 self.dk ** -0.5, True)
+                                 self.dk ** -0.5, True, md.query_start_loc_cpu)
         o = ops.rms_norm_gated(o.reshape(T * self.hv, self.dv), z.reshape(T * self.hv, self.dv), self.norm.weight,
                                self.cfg.rms_norm_eps, True)
         return self.out_proj(o.reshape(T, self.value_dim))

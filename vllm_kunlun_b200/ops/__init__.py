@@ -570,27 +570,51 @@ def fused_gdn_gating(A_log, a, b, dt_bias):
     return g, torch.sigmoid(b.float())
 
 
+GDN_CHUNK_MIN = 64      # new tokens of a request from which the chunked form is used (when it is enabled)
+
+
 def gated_delta_rule(q, k, v, g, beta, states, cu_seqlens, state_indices, has_initial_state, scale=None,
-                     use_qk_l2norm=True):
+                     use_qk_l2norm=True, cu_seqlens_cpu=None):
     """Varlen gated delta rule over a state cache ``[slots, Hv, Dv, Dk]`` (fp32, updated in place).
-    ``q, k [T, Hk, Dk]``, ``v [T, Hv, Dv]``, ``g, beta [T, Hv]`` fp32.  Serves prefill (chunked form in the
-    reference) and decode (recurrent form) alike."""
+    ``q, k [T, Hk, Dk]``, ``v [T, Hv, Dv]``, ``g, beta [T, Hv]`` fp32.  Serves prefill and decode alike with the
+    recurrent kernel (one dependent step per token).  With ``B200_GDN_CHUNKED=1`` and the host copy of the segment
+    offsets, requests with at least ``GDN_CHUNK_MIN`` new tokens take the chunked form instead (the reference's
+    prefill path, ``ops/fla/chunk.py:23-140``): batched matrix products per 64-token chunk and one state update per
+    chunk; the other requests of the step keep the recurrent kernel."""
     scale = q.shape[-1] ** -0.5 if scale is None else scale
-    if q.is_cuda:
-        out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-        _c().gdn_recurrent(out, q, k, v, g, beta, states, cu_seqlens.int(), state_indices.int(),
-                           has_initial_state.to(torch.uint8), scale, use_qk_l2norm)
-        return out
-    out = torch.empty_like(v)
-    for r in range(len(cu_seqlens) - 1):
-        s, e = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
-        slot = int(state_indices[r])
-        if e == s or slot < 0:
-            continue
-        S0 = states[slot] if bool(has_initial_state[r]) else torch.zeros_like(states[slot])
-        o, S = _rx.recurrent_gated_delta_rule(q[s:e], k[s:e], v[s:e], g[s:e], beta[s:e], S0, scale, use_qk_l2norm)
+    long_rows = []
+    if cu_seqlens_cpu is not None:
+        from .. import envs
+        if envs.B200_GDN_CHUNKED:
+            lens = (cu_seqlens_cpu[1:] - cu_seqlens_cpu[:-1]).tolist()
+            long_rows = [r for r, n in enumerate(lens) if n >= GDN_CHUNK_MIN]
+    out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    slots = state_indices
+    if long_rows:
+        rows_t = torch.tensor(long_rows, dtype=torch.long).to(v.device, non_blocking=True)
+        slots = state_indices.clone()
+        slots[rows_t] = -1          # the recurrent pass skips them
+    if len(long_rows) < len(cu_seqlens) - 1:
+        if q.is_cuda:
+            _c().gdn_recurrent(out, q, k, v, g, beta, states, cu_seqlens.int(), slots.int(),
+                               has_initial_state.to(torch.uint8), scale, use_qk_l2norm)
+        else:
+            for r in range(len(cu_seqlens) - 1):
+                s, e = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+                slot = int(slots[r])
+                if e == s or slot < 0:
+                    continue
+                S0 = states[slot] if bool(has_initial_state[r]) else torch.zeros_like(states[slot])
+                o, S = _rx.recurrent_gated_delta_rule(q[s:e], k[s:e], v[s:e], g[s:e], beta[s:e], S0, scale, use_qk_l2norm)
+                out[s:e] = o
+                states[slot] = S
+    for r in long_rows:             # offsets from the host copy; slot and initial-state flag stay on the device
+        s, e = int(cu_seqlens_cpu[r]), int(cu_seqlens_cpu[r + 1])
+        slot = state_indices[r].view(1).long()
+        S0 = states.index_select(0, slot)[0] * has_initial_state[r].to(states.dtype)
+        o, S = _rx.chunk_gated_delta_rule_batched(q[s:e], k[s:e], v[s:e], g[s:e], beta[s:e], S0, 64, scale, use_qk_l2norm)
         out[s:e] = o
-        states[slot] = S
+        states.index_copy_(0, slot, S.unsqueeze(0).to(states.dtype))
     return out
 
 

@@ -207,6 +207,58 @@ def chunk_gated_delta_rule(q, k, v, g, beta, state, chunk: int = 64, scale=None,
     return out.permute(1, 0, 2).to(v.dtype), S
 
 
+def chunk_gated_delta_rule_batched(q, k, v, g, beta, state, chunk: int = 64, scale=None, use_qk_l2norm=True):
+    """The chunked form with everything that does not depend on the running state computed for ALL chunks at once
+    (decays, the unit-lower-triangular solve, ``u`` / ``w``, the intra-chunk attention: batched matrix products on the
+    tensors' own device), followed by one short loop over the chunks that carries the state - three small products
+    per chunk instead of one dependent step per token.  The sequence is padded to a multiple of ``chunk`` with steps
+    that change nothing (``g = 0``, ``beta = 0``).  Same arguments and results as
+    :func:`recurrent_gated_delta_rule`; fp32 inside."""
+    L, Hk, Dk = q.shape
+    Hv, Dv = v.shape[1], v.shape[2]
+    rep, dev = Hv // Hk, q.device
+    qf, kf = q.float(), k.float()
+    if use_qk_l2norm:
+        qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6)
+        kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
+    qf = qf * (scale if scale is not None else Dk ** -0.5)
+    pad = (-L) % chunk
+    N = (L + pad) // chunk
+
+    def blocks(x, heads_from_k):            # [L, H, D] -> [Hv, N, chunk, D]
+        if pad:
+            x = torch.cat([x, x.new_zeros(pad, *x.shape[1:])])
+        if heads_from_k and rep > 1:
+            x = x.repeat_interleave(rep, 1)
+        return x.permute(1, 0, 2).reshape(Hv, N, chunk, x.shape[-1])
+
+    qc, kc, vc = blocks(qf, True), blocks(kf, True), blocks(v.float(), False)
+    gc = blocks(g.float().unsqueeze(-1), False).squeeze(-1).cumsum(-1)        # [Hv, N, chunk] log decay inside a chunk
+    bc = blocks(beta.float().unsqueeze(-1), False).squeeze(-1)
+    lower = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=dev))
+    diff = gc.unsqueeze(-1) - gc.unsqueeze(-2)                                  # g_i - g_j
+    decay = torch.exp(diff.masked_fill(~lower, float("-inf")))                  # 0 above the diagonal
+    kk = kc @ kc.transpose(-1, -2)
+    eye = torch.eye(chunk, device=dev)
+    A = kk * decay * bc.unsqueeze(-1) * (~eye.bool())                           # strictly lower
+    Tm = torch.linalg.solve_triangular(eye + A, eye.expand(Hv, N, chunk, chunk).contiguous(), upper=False)
+    u = Tm @ (vc * bc.unsqueeze(-1))
+    w = Tm @ (kc * (bc * torch.exp(gc)).unsqueeze(-1))
+    attn = (qc @ kc.transpose(-1, -2)) * decay
+    qg = qc * torch.exp(gc).unsqueeze(-1)
+    glast = gc[..., -1]
+    kdec = kc * torch.exp(glast.unsqueeze(-1) - gc).unsqueeze(-1)
+    eg = torch.exp(glast)
+    S = state.float().clone()                                                   # [Hv, Dv, Dk]
+    out = torch.empty(Hv, N, chunk, Dv, dtype=torch.float32, device=dev)
+    for n in range(N):
+        St = S.transpose(-1, -2)
+        v_new = u[:, n] - w[:, n] @ St
+        out[:, n] = qg[:, n] @ St + attn[:, n] @ v_new
+        S = S * eg[:, n].reshape(Hv, 1, 1) + v_new.transpose(-1, -2) @ kdec[:, n]
+    return out.reshape(Hv, N * chunk, Dv)[:, :L].permute(1, 0, 2).to(v.dtype), S
+
+
 # ----------------------------------------------------------------------------- LoRA
 
 def sgmv_shrink(x, lora_a, seq_lod, lora_ids, scale: float):
