@@ -421,3 +421,51 @@ def test_gemma4_with_images_matches_the_transformers_implementation():
     llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
                  multi_modal_data={"pixel_values": px, "image_grid_thw": [list(g) for g in grids]})
     assert (seen[0][-1] - want).abs().max().item() < 2e-4
+
+
+@pytest.mark.parametrize("qk_norm", [False, True], ids=["layernorm", "rmsnorm_qk_norm"])
+def test_internvl_matches_the_transformers_implementation(qk_norm):
+    """InternVL in the transformers-native layout: InternViT tower (class token, position table, layer scale; the
+    large towers' RMSNorm with q / k normalisation), pixel shuffle, projector; logits after a two-image prompt."""
+    if not hasattr(transformers, "InternVLForConditionalGeneration"):
+        pytest.skip(f"transformers {transformers.__version__} has no InternVL")
+    torch.manual_seed(0)
+    IMG = 150
+    tc = dict(model_type="qwen2", vocab_size=200, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, intermediate_size=256, max_position_embeddings=512, rms_norm_eps=1e-5)
+    vc = dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, image_size=[32, 32],
+              patch_size=[8, 8], num_channels=3, use_qk_norm=qk_norm, norm_type="rms_norm" if qk_norm else "layer_norm",
+              attention_bias=qk_norm)
+    hf_cfg = transformers.InternVLConfig(text_config=tc, vision_config=vc, image_token_id=IMG, downsample_ratio=0.5)
+    hf_cfg._attn_implementation = "eager"
+    hf = transformers.InternVLForConditionalGeneration(hf_cfg).eval().float()
+    _randomise(hf)
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = ["InternVLForConditionalGeneration"], "float32"
+    llm = LLM(ModelConfig.from_hf_config(d), device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=32)
+    model = llm.engine.runner.model
+    sd = hf.state_dict()
+    with torch.inference_mode():
+        loaded = model.load_weights(list(sd.items()))
+    assert [k for k in sd if k not in loaded] == ["lm_head.weight"]         # tied to the embedding
+    images = torch.randn(2, 3, 32, 32)
+    # patches row-major, each flattened as (channel, y, x)
+    px = images.view(2, 3, 4, 8, 4, 8).permute(0, 2, 4, 1, 3, 5).reshape(2, 16, 3 * 64)
+    with torch.no_grad():
+        want_v = hf.model.get_image_features(images).pooler_output.float()
+    with torch.inference_mode():
+        got_v = model.embed_multimodal(px).float()
+    assert got_v.shape == (8, 128) and (got_v - want_v.reshape(8, 128)).abs().max().item() < 1e-4
+    ids = [5, 6] + [IMG] * 4 + [7, 8] + [IMG] * 4 + [9, 10, 11]
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([ids]), pixel_values=images).logits[0, -1].float()
+    seen, compute_logits = [], model.compute_logits
+
+    def recording(h):
+        out = compute_logits(h)
+        seen.append(out.detach().float().clone())
+        return out
+
+    model.compute_logits = recording
+    llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True), multi_modal_data={"pixel_values": px})
+    assert (seen[0][-1] - want).abs().max().item() < 1e-4

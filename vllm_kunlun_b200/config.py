@@ -319,14 +319,22 @@ class ModelConfig:
         if vcfg and ("VL" in arch or "Omni" in arch or arch.startswith("Intern")):
             tc = cfg.get("text_config") or cfg.get("llm_config") or cfg
             intern = arch.startswith("Intern")
+            if intern:      # the transformers-native layout writes sizes as [h, w] and names the decoder by model_type
+                vcfg = {**vcfg, **{k: (v[0] if isinstance(v, (list, tuple)) else v) for k, v in vcfg.items()
+                                   if k in ("image_size", "patch_size")}}
+                if not tc.get("architectures") and tc.get("model_type"):
+                    tc = {**tc, "architectures": [{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                                                   "llama": "LlamaForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+                                                   "gpt_oss": "GptOssForCausalLM"}.get(tc["model_type"], "Qwen2ForCausalLM")]}
             kw["vision"] = dict(
                 depth=vcfg.get("depth", vcfg.get("num_hidden_layers", 32)),
                 hidden=vcfg.get("embed_dim", vcfg.get("hidden_size", 1280)),
                 heads=vcfg.get("num_heads", vcfg.get("num_attention_heads", 16)), patch=vcfg.get("patch_size", 14),
                 temporal_patch=vcfg.get("temporal_patch_size", 2), merge=vcfg.get("spatial_merge_size", 2),
                 intermediate=vcfg.get("intermediate_size", int(vcfg.get("embed_dim", 1280) * vcfg.get("mlp_ratio", 4))),
-                in_channels=vcfg.get("in_channels", vcfg.get("in_chans", 3)),
-                norm="rmsnorm" if "2_5" in arch else "layernorm", gated_mlp="2_5" in arch,
+                in_channels=vcfg.get("in_channels", vcfg.get("in_chans", vcfg.get("num_channels", 3))),
+                norm="rmsnorm" if ("2_5" in arch or vcfg.get("norm_type") == "rms_norm") else "layernorm",
+                gated_mlp="2_5" in arch, qk_norm=bool(intern and (vcfg.get("use_qk_norm") or vcfg.get("qk_normalization"))),
                 act="gelu" if intern else ("gelu_tanh" if "Qwen3" in arch else "quick_gelu"), layer_scale=intern,
                 image_size=vcfg.get("image_size", 448),
                 # Qwen2.5-VL: windowed attention in all blocks but the listed ones (window in pixels); Qwen3-VL: a
@@ -410,7 +418,19 @@ class ModelConfig:
         if arch == "MiMoV2FlashForCausalLM":
             kw.update(v_head_dim=cfg.get("v_head_dim", kw["head_dim"]), attention_sinks=bool(cfg.get("add_swa_attention_sink_bias", True)),
                       sliding_window=cfg.get("sliding_window", 128), sliding_window_pattern=cfg.get("hybrid_block_size", 0) or 0)
-        return cls(**kw)
+        out = cls(**kw)
+        if arch.startswith("Intern") and isinstance(cfg.get("text_config") or cfg.get("llm_config"), dict):
+            # the decoder's traits (q/k/v biases, q/k norms, routing, ...) follow ITS architecture, not the wrapper's
+            tcfg = dict(cfg.get("text_config") or cfg.get("llm_config"))
+            tcfg["architectures"] = [out.vision["text_architecture"]]
+            tcfg.setdefault("torch_dtype", cfg.get("torch_dtype", "bfloat16"))
+            if cfg.get("quantization_config") and not tcfg.get("quantization_config"):
+                tcfg["quantization_config"] = cfg["quantization_config"]
+            text = cls.from_hf_config(tcfg)
+            text.architecture, text.name, text.vision = arch, out.name, out.vision
+            text.tie_word_embeddings = out.tie_word_embeddings
+            return text
+        return out
 
     @classmethod
     def from_pretrained(cls, path: str) -> "ModelConfig":

@@ -50,6 +50,7 @@ _REGISTRY = {
     "Qwen3OmniMoeForConditionalGeneration": "omni:Qwen3OmniMoeThinker",
     "Qwen3OmniMoeThinkerForConditionalGeneration": "omni:Qwen3OmniMoeThinker",
     "InternVLChatModel": "vision:InternVLChatModel",
+    "InternVLForConditionalGeneration": "vision:InternVLChatModel",
     "InternS1ForConditionalGeneration": "vision:InternVLChatModel",
 }
 

@@ -56,11 +56,17 @@ class VisionBlock(nn.Module):
         self.act = vc.get("act", "quick_gelu")
         self.ls1 = param(h, dtype=dtype, device=device) if vc.get("layer_scale") else None
         self.ls2 = param(h, dtype=dtype, device=device) if vc.get("layer_scale") else None
+        # InternViT-6B: RMSNorm of the whole q and k rows (all heads together) before the split
+        self.q_norm = RMSNorm(h, vc.get("eps", 1e-6), dtype, device) if vc.get("qk_norm") else None
+        self.k_norm = RMSNorm(h, vc.get("eps", 1e-6), dtype, device) if vc.get("qk_norm") else None
 
     def forward(self, x, cu_seqlens, cos=None, sin=None):
         T = x.shape[0]
         qkv = self.qkv(self.norm1(x)).view(T, 3, self.heads, self.head_dim)
         q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+        if self.q_norm is not None:
+            q = self.q_norm(q.reshape(T, -1)).view(T, self.heads, self.head_dim)
+            k = self.k_norm(k.reshape(T, -1)).view(T, self.heads, self.head_dim)
         if cos is not None:
             q, k = ops.rope_vit(q, k, cos, sin)
         a = ops.varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, self.head_dim ** -0.5)
@@ -505,15 +511,54 @@ class InternVLChatModel(_VLBase):
     _MAP = {"vision_model.embeddings.patch_embedding.": "patch_embed.", "vision_model.embeddings.class_embedding": "cls",
             "vision_model.embeddings.position_embedding": "pos", "vision_model.encoder.layers.": "blocks.",
             ".attn.qkv.": ".qkv.", ".attn.proj.": ".proj.", ".mlp.fc1.": ".fc1.", ".mlp.fc2.": ".fc2.",
-            "mlp1.0.": "proj_norm.", "mlp1.1.": "proj_fc1.", "mlp1.3.": "proj_fc2."}
+            "mlp1.0.": "proj_norm.", "mlp1.1.": "proj_fc1.", "mlp1.3.": "proj_fc2.",
+            # checkpoints in the transformers-native layout (InternVLForConditionalGeneration)
+            "vision_tower.embeddings.cls_token": "cls", "vision_tower.embeddings.position_embeddings": "pos",
+            "vision_tower.embeddings.patch_embeddings.projection.": "patch_embed.",
+            "vision_tower.encoder.layer.": "blocks.", ".attention.qkv.": ".qkv.",
+            ".attention.projection_layer.": ".proj.", ".attention.q_norm.": ".q_norm.", ".attention.k_norm.": ".k_norm.",
+            ".layernorm_before.": ".norm1.", ".layernorm_after.": ".norm2.", ".lambda_1": ".ls1", ".lambda_2": ".ls2",
+            "multi_modal_projector.layer_norm.": "proj_norm.", "multi_modal_projector.linear_1.": "proj_fc1.",
+            "multi_modal_projector.linear_2.": "proj_fc2."}
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        super().__init__(cfg, device, dtype)
+        for n, p_ in self.visual.named_parameters():     # checkpoints without attention biases leave these at zero
+            if n.endswith(".bias"):
+                p_.data.zero_()
 
     def _vision_name(self, name):
-        if not (name.startswith("vision_model.") or name.startswith("mlp1.")):
+        if not name.startswith(("vision_model.", "mlp1.", "vision_tower.", "multi_modal_projector.")):
             return None
         n = name
         for a, b in self._MAP.items():
             n = n.replace(a, b)
         return n
+
+    def load_weights(self, weights):
+        """The transformers-native layout keeps q / k / v of the tower apart: they are stacked into ``qkv`` here;
+        ``model.vision_tower.*`` / ``model.multi_modal_projector.*`` / ``model.language_model.*`` lose the prefix."""
+        out, parts, original = [], {}, {}
+        for name, w in weights:
+            n = name
+            if n.startswith("model.") and not n.startswith("model.layers.") and not n.startswith("model.embed_tokens.") \
+                    and not n.startswith("model.norm."):
+                n = n[len("model."):]
+                if n.startswith("language_model."):
+                    n = "model." + n[len("language_model."):]
+            hit = next((x for x in (".attention.q_proj.", ".attention.k_proj.", ".attention.v_proj.") if x in n), None)
+            if hit is not None and n.startswith("vision_tower."):
+                key = n.replace(hit, ".attention.qkv.")
+                got = parts.setdefault(key, {})
+                got[hit] = (name, w)
+                if len(got) == 3:
+                    out.append((key, torch.cat([got[x][1] for x in (".attention.q_proj.", ".attention.k_proj.", ".attention.v_proj.")])))
+                    original[key] = [got[x][0] for x in got]
+                continue
+            original[n] = [name]
+            out.append((n, w))
+        loaded = super().load_weights(out)
+        return {o for g in loaded for o in original.get(g, [g])}
 
 
 class _ClippedLinear(nn.Module):
