@@ -469,3 +469,56 @@ def test_internvl_matches_the_transformers_implementation(qk_norm):
     model.compute_logits = recording
     llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True), multi_modal_data={"pixel_values": px})
     assert (seen[0][-1] - want).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("moe", [False, True], ids=["dense", "moe"])
+def test_qwen3_5_with_images_matches_the_transformers_implementation(moe):
+    """Qwen3.5 / Qwen3.5-MoE with two images: Qwen3-VL tower in front of the hybrid decoder, interleaved M-RoPE on the
+    rotated half of each head in the gated full-attention layers; logits after the prompt and four greedy tokens."""
+    names = ("Qwen3_5MoeConfig", "Qwen3_5MoeForConditionalGeneration") if moe else ("Qwen3_5Config", "Qwen3_5ForConditionalGeneration")
+    if not all(hasattr(transformers, n) for n in names):
+        pytest.skip(f"transformers {transformers.__version__} has no {names[1]}")
+    torch.manual_seed(0)
+    tc = dict(Q35, vocab_size=200, max_position_embeddings=512,
+              rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                               "mrope_section": [3, 3, 2], "mrope_interleaved": True})
+    if moe:
+        tc.update(moe_intermediate_size=64, shared_expert_intermediate_size=64, num_experts=4, num_experts_per_tok=2)
+    vc = dict(depth=2, hidden_size=64, out_hidden_size=128, num_heads=4, intermediate_size=128, patch_size=4,
+              spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=64,
+              deepstack_visual_indexes=[])
+    hf_cfg = getattr(transformers, names[0])(text_config=tc, vision_config=vc, **_TOK)
+    hf_cfg._attn_implementation = "eager"
+    hf = getattr(transformers, names[1])(hf_cfg).eval().float()
+    _randomise(hf)
+    d = hf_cfg.to_dict()
+    d["architectures"], d["torch_dtype"] = [names[1]], "float32"
+    llm = LLM(ModelConfig.from_hf_config(d), device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=32)
+    model = llm.engine.runner.model
+    with torch.inference_mode():
+        loaded = model.load_weights(list(hf.state_dict().items()))
+    assert len(loaded) == len(hf.state_dict())
+    grids = [(1, 8, 12), (1, 4, 6)]
+    px = torch.randn(sum(t * h * w for t, h, w in grids), 3 * 2 * 16)
+    img = hf_cfg.image_token_id
+    ids = [5, 6, 7] + [img] * 24 + [8, 9] + [img] * 6 + [10, 11, 12]
+    gthw = torch.tensor(grids)
+    seq, want, want_logits = torch.tensor([ids]), [], None
+    for _ in range(4):
+        with torch.no_grad():
+            lg = hf(input_ids=seq, pixel_values=px, image_grid_thw=gthw, mm_token_type_ids=(seq == img).long()).logits[0, -1].float()
+        want_logits = lg if want_logits is None else want_logits
+        want.append(lg.argmax().item())
+        seq = torch.cat([seq, torch.tensor([[want[-1]]])], 1)
+    seen, compute_logits = [], model.compute_logits
+
+    def recording(h):
+        out = compute_logits(h)
+        seen.append(out.detach().float().clone())
+        return out
+
+    model.compute_logits = recording
+    out = llm.generate([ids], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True),
+                       multi_modal_data={"pixel_values": px, "image_grid_thw": [list(g) for g in grids]})[0].token_ids
+    assert (seen[0][-1] - want_logits).abs().max().item() < 2e-4
+    assert out == want

@@ -300,7 +300,7 @@ class ModelConfig:
             # GLM-4.5 / 4.6 / 4.7: GQA attention with partial rotary embedding and optional per-head q / k norm,
             # DeepSeek-V3 style MoE (sigmoid scores + correction bias, grouped top-k, shared experts, dense first layers)
             kw.update(scoring_func="sigmoid", router_bias=True, qk_norm=bool(cfg.get("use_qk_norm", False)),
-                      rotary_dim=int(kw["head_dim"] * float(cfg.get("partial_rotary_factor") or (cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or 0.5)),
+                      rotary_dim=int(kw["head_dim"] * float((cfg.get("rope_parameters") or {}).get("partial_rotary_factor") or cfg.get("partial_rotary_factor") or 0.5)),
                       num_mtp_layers=cfg.get("num_nextn_predict_layers", 0) or 0)
         if arch == "GptOssForCausalLM":
             kw.update(attention_sinks=True, sliding_window_pattern=2, hidden_act="swigluoai",
@@ -313,10 +313,14 @@ class ModelConfig:
                 gdn_num_v_heads=tc.get("linear_num_value_heads", 32), gdn_head_k_dim=tc.get("linear_key_head_dim", 128),
                 gdn_head_v_dim=tc.get("linear_value_head_dim", 128), gdn_conv_kernel=tc.get("linear_conv_kernel_dim", 4),
                 attn_output_gate=True, gemma_norm=True, qk_norm=True,
-                rotary_dim=int(kw["head_dim"] * float(tc.get("partial_rotary_factor") or (tc.get("rope_parameters") or {}).get("partial_rotary_factor") or 0.25)),
+                rotary_dim=int(kw["head_dim"] * float((tc.get("rope_parameters") or {}).get("partial_rotary_factor") or tc.get("partial_rotary_factor") or 0.25)),
                 num_shared_experts=1 if tc.get("shared_expert_intermediate_size") else 0, shared_expert_gate=True)
         vcfg = cfg.get("vision_config")
-        if vcfg and ("VL" in arch or "Omni" in arch or arch.startswith("Intern")):
+        q35_vl = arch.startswith("Qwen3_5") and "ConditionalGeneration" in arch
+        if q35_vl and not vcfg:      # a text-only export of the checkpoint: the decoder alone
+            kw["architecture"] = arch = arch.replace("ForConditionalGeneration", "ForCausalLM")
+            q35_vl = False
+        if vcfg and ("VL" in arch or "Omni" in arch or arch.startswith("Intern") or q35_vl):
             tc = cfg.get("text_config") or cfg.get("llm_config") or cfg
             intern = arch.startswith("Intern")
             if intern:      # the transformers-native layout writes sizes as [h, w] and names the decoder by model_type
@@ -350,9 +354,10 @@ class ModelConfig:
                 video_token_id=cfg.get("video_token_id"),
                 tokens_per_second=(vcfg.get("tokens_per_second", 4) if "2_5" in arch else
                                    cfg.get("position_id_per_seconds", 25) if "Omni" in arch else 0),
-                video_frame_runs="Qwen3VL" in arch,
+                video_frame_runs="Qwen3VL" in arch or q35_vl,
                 text_architecture=(tc.get("architectures") or ["Qwen2ForCausalLM"])[0] if intern else
-                ("Qwen3MoeForCausalLM" if ("Qwen3" in arch and "Moe" in arch) else
+                (arch.replace("ForConditionalGeneration", "ForCausalLM") if q35_vl else
+                 "Qwen3MoeForCausalLM" if ("Qwen3" in arch and "Moe" in arch) else
                  "Qwen3ForCausalLM" if "Qwen3" in arch else "Qwen2ForCausalLM"),
                 deepstack_indexes=list(vcfg.get("deepstack_visual_indexes", ())))
             acfg = cfg.get("audio_config")
@@ -368,7 +373,7 @@ class ModelConfig:
             kw["mrope_section"] = tuple(rsc.get("mrope_section", ()))
             # Qwen3-VL interleaves the three position axes over the rotary pairs (t h w t h w ...); Qwen2-VL / 2.5-VL
             # give each axis a contiguous section
-            kw["mrope_interleaved"] = bool(rsc.get("mrope_interleaved", arch.startswith("Qwen3VL") or arch.startswith("Qwen3Omni")))
+            kw["mrope_interleaved"] = bool(rsc.get("mrope_interleaved", arch.startswith("Qwen3VL") or arch.startswith("Qwen3Omni") or q35_vl))
         if vcfg and arch.startswith("Gemma"):
             rp = vcfg.get("rope_parameters") or {}
             kw["vision"] = dict(

@@ -33,8 +33,8 @@ _REGISTRY = {
     "DeepSeekMTPModel": "deepseek_mtp:DeepSeekMTP",
     # hybrid linear attention
     "Qwen3NextForCausalLM": "qwen3_next:Qwen3NextForCausalLM",
-    "Qwen3_5ForConditionalGeneration": "qwen3_next:Qwen3NextForCausalLM",
-    "Qwen3_5MoeForConditionalGeneration": "qwen3_next:Qwen3NextForCausalLM",
+    "Qwen3_5ForConditionalGeneration": "vision:Qwen3_5ForConditionalGeneration",
+    "Qwen3_5MoeForConditionalGeneration": "vision:Qwen3_5ForConditionalGeneration",
     "Qwen3_5ForCausalLM": "qwen3_next:Qwen3NextForCausalLM",          # the text-only classes of the same checkpoints
     "Qwen3_5MoeForCausalLM": "qwen3_next:Qwen3NextForCausalLM",
     # asymmetric V / sliding window with sinks

@@ -142,11 +142,22 @@ class GatedAttention(GQAAttention):
         fused = self.qkv_proj(hidden)
         gate = fused[:, : self.q_local]
         kv_cache = ctx.kv_caches[self.layer_idx]
-        q = ops.qkv_split_norm_rope_cache(
-            fused[:, self.q_local:], md.positions, self.cos_sin,
-            None if self.q_norm is None else self.q_norm.weight, None if self.k_norm is None else self.k_norm.weight,
-            self.cfg.rms_norm_eps, self.num_heads, self.num_kv_heads, self.head_dim, self.cfg.rope_neox,
-            kv_cache, md.slot_mapping, self.cfg.gemma_norm)
+        pos3 = ctx.extras.get("mrope_positions") if ctx.extras else None
+        if pos3 is not None:
+            # Qwen3.5 with images in this step: three-axis rotary positions over the rotated part of each head
+            cfg, T = self.cfg, fused.shape[0]
+            qs, ks = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+            q = fused[:, self.q_local:self.q_local + qs].contiguous()
+            k = fused[:, self.q_local + qs:self.q_local + qs + ks].contiguous()
+            v = fused[:, self.q_local + qs + ks:].contiguous()
+            if self.q_norm is not None:
+                q = self.q_norm(q.view(-1, self.head_dim)).view(T, qs)
+                k = self.k_norm(k.view(-1, self.head_dim)).view(T, ks)
+            q, k = ops.mrope(q, k, pos3, self.cos_sin, self.head_dim, list(cfg.mrope_section), cfg.mrope_interleaved)
+            ops.reshape_and_cache(k.view(T, self.num_kv_heads, self.head_dim), v.view(T, self.num_kv_heads, self.head_dim),
+                                  kv_cache, md.slot_mapping)
+        else:
+            q = self._split_norm_rope_cache(fused, md, kv_cache)
         T = q.shape[0]
         o = ops.paged_attention(
             q.view(T, self.num_heads, self.head_dim), kv_cache, md.block_tables, md.seq_lens, md.query_start_loc,
@@ -155,6 +166,13 @@ class GatedAttention(GQAAttention):
             decode_query_len=1 + md.num_spec_tokens, num_decode_tokens=md.num_decode_tokens)
         o = ops.sigmoid_gate_mul(o.reshape(T, self.q_local), gate)
         return self.o_proj(o)
+
+    def _split_norm_rope_cache(self, fused, md, kv_cache):
+        return ops.qkv_split_norm_rope_cache(
+            fused[:, self.q_local:], md.positions, self.cos_sin,
+            None if self.q_norm is None else self.q_norm.weight, None if self.k_norm is None else self.k_norm.weight,
+            self.cfg.rms_norm_eps, self.num_heads, self.num_kv_heads, self.head_dim, self.cfg.rope_neox,
+            kv_cache, md.slot_mapping, self.cfg.gemma_norm)
 
     def load_q_and_gate(self, w: torch.Tensor, pname: str = "weight"):
         """Checkpoint ``q_proj`` rows are ``[head][q(D) | gate(D)]``."""

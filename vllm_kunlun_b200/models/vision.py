@@ -334,7 +334,10 @@ class _VLBase(nn.Module):
         self.dtype, self.device = self.language_model.dtype, self.language_model.device
         if self.uses_mrope:
             for layer in self.language_model.layers.values():
-                layer.self_attn.__class__ = MRopeAttention
+                # plain attention layers get the three-axis rotary variant; the gated attention of the hybrid decoders
+                # handles the positions itself, linear-attention layers have no rotary embedding
+                if type(getattr(layer, "self_attn", None)) is GQAAttention:
+                    layer.self_attn.__class__ = MRopeAttention
         self.visual = self.tower_cls(cfg.vision, cfg.hidden_size, self.dtype, device)
         self.image_token_id = cfg.vision.get("image_token_id", cfg.vocab_size - 1)
         self.layers = self.language_model.layers
@@ -489,6 +492,23 @@ class QwenVLForConditionalGeneration(_VLBase):
                     "mlp.0": "ds_fc1", "mlp.2": "ds_fc2"}[m.group(2)]
             return f"{kind}.{m.group(1)}.{m.group(3)}"
         return n
+
+
+class Qwen3_5ForConditionalGeneration(QwenVLForConditionalGeneration):
+    """Qwen3.5 / Qwen3.5-MoE with images and videos (``models/qwen3_5.py:627-700`` of the reference): the Qwen3-VL tower
+    (no deep-stack features) in front of the hybrid gated-delta-net decoder; interleaved M-RoPE over the rotated
+    quarter of each head in the full-attention layers."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None):
+        cfg.vision.setdefault("text_architecture", "Qwen3_5MoeForCausalLM" if cfg.num_experts else "Qwen3_5ForCausalLM")
+        super().__init__(cfg, device, dtype)
+
+    def state_cache_spec(self):
+        return self.language_model.state_cache_spec()
+
+    @property
+    def uses_state_cache(self) -> bool:
+        return self.language_model.uses_state_cache
 
 
 class Qwen3VLMoeForConditionalGeneration(QwenVLForConditionalGeneration):
