@@ -249,6 +249,11 @@ def test_openai_server_completions_and_chat_stream():
     with TestClient(app) as c:
         assert c.get("/health").text == "ok"
         assert c.get("/v1/models").json()["data"][0]["id"] == "tiny"
+        assert c.get("/version").json()["version"]
+        t = c.post("/tokenize", json={"prompt": "5 6 7"}).json()
+        assert t["tokens"] == [5, 6, 7] and t["count"] == 3 and t["max_model_len"] > 0
+        assert c.post("/detokenize", json={"tokens": [5, 6, 7]}).json()["prompt"] == "5 6 7"
+        assert c.post("/detokenize", json={"tokens": ["x"]}).status_code == 400
         r = c.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 4, "temperature": 0, "ignore_eos": True})
         body = r.json()
         assert body["usage"]["completion_tokens"] == 4 and body["choices"][0]["finish_reason"] == "length"

@@ -353,6 +353,33 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                  for n in lora_modules]
         return {"object": "list", "data": data}
 
+    @app.get("/version")
+    async def version():
+        from .. import __version__
+        return {"version": __version__}
+
+    @app.post("/tokenize")
+    async def tokenize(req: Request):
+        """``{"prompt": text}`` or ``{"messages": [...]}`` -> token ids (upstream's helper endpoint)."""
+        body = await req.json()
+        if "messages" in body and tok is not None and hasattr(tok, "apply_chat_template"):
+            ids = tok.apply_chat_template(body["messages"], add_generation_prompt=bool(body.get("add_generation_prompt", True)),
+                                          **(body.get("chat_template_kwargs") or {}))
+            ids = ids["input_ids"] if hasattr(ids, "keys") else ids
+        else:
+            ids = encode(body.get("prompt", ""))
+        ids = list(ids)
+        return {"tokens": ids, "count": len(ids), "max_model_len": llm.engine.cfg.scheduler.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(req: Request):
+        body = await req.json()
+        try:
+            ids = [int(t) for t in body.get("tokens", [])]
+        except (TypeError, ValueError):
+            return bad_request("tokens must be a list of integers")
+        return {"prompt": decode(ids)}
+
     @app.get("/metrics")
     async def metrics():
         s, e = loop_obj.stats, llm.engine.stats

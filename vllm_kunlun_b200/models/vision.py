@@ -401,9 +401,10 @@ class _VLBase(nn.Module):
         self.language_model.finish_loading()
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]):
-        text, loaded = [], set()
+        text, loaded, original = [], set(), {}
         vis = dict(self.visual.named_parameters())
-        for name, w in weights:
+        for ckpt_name, w in weights:
+            name = ckpt_name
             # checkpoints written by transformers 5 nest both halves under ``model.``: ``model.visual.*`` and
             # ``model.language_model.*`` (older ones: ``visual.*`` and ``model.*`` / ``language_model.model.*``)
             if name.startswith("model.visual."):
@@ -421,10 +422,13 @@ class _VLBase(nn.Module):
                     else:
                         n = vis[v].shape[0] // 2
                         vis[v].data[half * n:(half + 1) * n].copy_(w)
-                    loaded.add(name)
+                    loaded.add(ckpt_name)
                 continue
-            text.append((name.replace("language_model.model.", "model.").replace("language_model.", ""), w))
-        return loaded | self.language_model.load_weights(text)
+            tname = name.replace("language_model.model.", "model.").replace("language_model.", "")
+            original[tname] = ckpt_name
+            text.append((tname, w))
+        # report the checkpoint's own names
+        return loaded | {original.get(n, n) for n in self.language_model.load_weights(text)}
 
     def _vision_name(self, name: str) -> Optional[str]:
         raise NotImplementedError
