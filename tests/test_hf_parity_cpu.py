@@ -423,16 +423,21 @@ def test_gemma4_with_images_matches_the_transformers_implementation():
     assert (seen[0][-1] - want).abs().max().item() < 2e-4
 
 
-@pytest.mark.parametrize("qk_norm", [False, True], ids=["layernorm", "rmsnorm_qk_norm"])
-def test_internvl_matches_the_transformers_implementation(qk_norm):
+@pytest.mark.parametrize("qk_norm,text_type,arch", [
+    (False, "qwen2", "InternVLForConditionalGeneration"), (True, "qwen2", "InternVLForConditionalGeneration"),
+    # Intern-S1 checkpoints use the same tensor layout over a Qwen3 decoder (q / k norms, no q/k/v biases)
+    (True, "qwen3", "InternS1ForConditionalGeneration")], ids=["layernorm", "rmsnorm_qk_norm", "intern_s1_qwen3_decoder"])
+def test_internvl_matches_the_transformers_implementation(qk_norm, text_type, arch):
     """InternVL in the transformers-native layout: InternViT tower (class token, position table, layer scale; the
     large towers' RMSNorm with q / k normalisation), pixel shuffle, projector; logits after a two-image prompt."""
     if not hasattr(transformers, "InternVLForConditionalGeneration"):
         pytest.skip(f"transformers {transformers.__version__} has no InternVL")
     torch.manual_seed(0)
     IMG = 150
-    tc = dict(model_type="qwen2", vocab_size=200, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+    tc = dict(model_type=text_type, vocab_size=200, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, intermediate_size=256, max_position_embeddings=512, rms_norm_eps=1e-5)
+    if text_type == "qwen3":
+        tc["head_dim"] = 32
     vc = dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, image_size=[32, 32],
               patch_size=[8, 8], num_channels=3, use_qk_norm=qk_norm, norm_type="rms_norm" if qk_norm else "layer_norm",
               attention_bias=qk_norm)
@@ -441,7 +446,7 @@ def test_internvl_matches_the_transformers_implementation(qk_norm):
     hf = transformers.InternVLForConditionalGeneration(hf_cfg).eval().float()
     _randomise(hf)
     d = hf_cfg.to_dict()
-    d["architectures"], d["torch_dtype"] = ["InternVLForConditionalGeneration"], "float32"
+    d["architectures"], d["torch_dtype"] = [arch], "float32"
     llm = LLM(ModelConfig.from_hf_config(d), device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=32)
     model = llm.engine.runner.model
     sd = hf.state_dict()
