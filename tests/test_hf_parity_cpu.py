@@ -356,6 +356,21 @@ def test_qwen3_omni_thinker_matches_the_transformers_implementation():
                  multi_modal_data={"pixel_values": px, "image_grid_thw": [[1, 4, 6]], "input_features": feats,
                                    "feature_lens": [frames]})
     assert (seen[0][-1] - want).abs().max().item() < 1e-4
+    # a three-frame video (2 s per temporal patch: positions 50 apart) and an image
+    vid = hf_cfg.video_token_id
+    pv = torch.randn(3 * 4 * 4, 3 * 2 * 16)
+    ids = [5, 6, _TOK["vision_start_token_id"]] + [vid] * 12 + [_TOK["vision_end_token_id"], 7, 8,
+           _TOK["vision_start_token_id"]] + [img] * 6 + [_TOK["vision_end_token_id"], 9]
+    seq = torch.tensor([ids])
+    with torch.no_grad():
+        want = hf(input_ids=seq, pixel_values_videos=pv, video_grid_thw=torch.tensor([[3, 4, 4]]),
+                  video_second_per_grid=torch.tensor([2.0]), pixel_values=px, image_grid_thw=torch.tensor([[1, 4, 6]]),
+                  attention_mask=torch.ones_like(seq)).logits[0, -1].float()
+    seen.clear()
+    llm.generate([ids], SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
+                 multi_modal_data={"pixel_values": px, "image_grid_thw": [[1, 4, 6]], "pixel_values_videos": pv,
+                                   "video_grid_thw": [[3, 4, 4]], "second_per_grid_ts": [2.0]})
+    assert (seen[0][-1] - want).abs().max().item() < 1e-4
 
 
 def test_gemma4_with_images_matches_the_transformers_implementation():
