@@ -627,3 +627,34 @@ def test_openai_server_chat_with_an_image_part():
         r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
             {"type": "image_url", "image_url": {"url": uri((1, 2, 3))}}]}], "max_tokens": 2})
         assert r.status_code == 400
+
+
+def test_openai_server_chat_with_an_image_part_internvl_tiles():
+    """InternVL: the image is cut into tiles of the tower's size plus a thumbnail; the single placeholder grows to
+    tiles x tokens-per-tile."""
+    import base64
+    import io
+    import sys
+
+    from fastapi.testclient import TestClient
+    from PIL import Image
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from test_vision_cpu import _intern
+    from vllm_kunlun_b200 import LLM
+    from vllm_kunlun_b200.entrypoints.openai_server import build_app
+    from vllm_kunlun_b200.multimodal import InternImagePreprocessor
+    pre = InternImagePreprocessor(448, 14, 0.5, 1, 12, True)
+    assert pre.tile_grid(800, 400) == (2, 1) and pre.tile_grid(448, 448) == (1, 1) and pre.tile_grid(300, 1200) == (1, 4)
+    assert pre.tokens_per_tile == 256
+    llm = LLM(_intern(), device="cpu", block_size=16, max_model_len=256, max_num_seqs=2, num_gpu_blocks=64)
+    buf = io.BytesIO()
+    Image.new("RGB", (16, 8), (200, 30, 30)).save(buf, format="PNG")
+    uri = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    with TestClient(build_app(llm, "intern")) as c:
+        r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+            {"type": "text", "text": "3 4"}, {"type": "image_url", "image_url": {"url": uri}}]}],
+            "max_tokens": 3, "temperature": 0, "ignore_eos": True})
+        assert r.status_code == 200, r.text
+        # 16 x 8 pixels on an 8-pixel tower: a 2 x 1 grid of tiles + thumbnail, 4 tokens each, + 2 text tokens
+        assert r.json()["usage"]["prompt_tokens"] == 3 * 4 + 2

@@ -21,7 +21,8 @@ import uuid
 from typing import Optional
 
 from ..engine.request import SamplingParams
-from ..multimodal import QwenImagePreprocessor, collect_images, expand_placeholders, load_image
+from ..multimodal import (InternImagePreprocessor, QwenImagePreprocessor, collect_images, expand_placeholders,
+                          load_image)
 
 
 class ChatPostProcessor:
@@ -294,8 +295,13 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
     app = FastAPI()
     # image inputs: models with a Qwen-VL tower (patch / merge geometry in the configuration) take image_url parts
     vision = getattr(llm.engine.cfg.model, "vision", None) or {}
-    image_pre = (QwenImagePreprocessor.from_config(vision, getattr(llm, "preprocessor_config", None))
-                 if vision.get("merge") and vision.get("temporal_patch") and not vision.get("layer_scale") else None)
+    pre_cfg = getattr(llm, "preprocessor_config", None)
+    if vision.get("layer_scale") and vision.get("image_size"):          # InternViT tower: tiles + thumbnail
+        image_pre = InternImagePreprocessor.from_config(vision, pre_cfg)
+    elif vision.get("merge") and vision.get("temporal_patch"):
+        image_pre = QwenImagePreprocessor.from_config(vision, pre_cfg)
+    else:
+        image_pre = None
     image_token_id = vision.get("image_token_id")
     loop_obj = EngineLoop(llm)
     app.state.engine_loop = loop_obj
@@ -513,7 +519,7 @@ def build_app(llm, model_name: str, reasoning_parser=None, tool_parser=None, lor
                 ids = expand_placeholders(list(ids), image_token_id, [image_pre.tokens_per_image(g) for g in grids])
             except (ValueError, OSError) as e:
                 return bad_request(f"image input: {e}")
-            mm = {"pixel_values": px, "image_grid_thw": grids}
+            mm = image_pre.mm_data(px, grids)
         post = ChatPostProcessor(reasoning_parser, tool_parser, body.get("tools"), body.get("chat_template_kwargs"))
 
         def chunk(rid, created, text, fin):

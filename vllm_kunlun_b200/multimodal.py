@@ -9,6 +9,7 @@ layout).  This module does the same work without a processor object:
 * :func:`smart_resize` - the target height / width;
 * :class:`QwenImagePreprocessor` - images -> ``pixel_values [sum(t*h*w), C * temporal_patch * patch * patch]`` and
   ``image_grid_thw``;
+* :class:`InternImagePreprocessor` - InternVL's tile grid + thumbnail;
 * :func:`expand_placeholders` - a chat template writes ONE placeholder token per image; the engine wants one per
   merged patch;
 * :func:`collect_images` - the ``image_url`` / ``image`` parts of an OpenAI ``messages`` list, in order.
@@ -119,6 +120,80 @@ class QwenImagePreprocessor:
     def tokens_per_image(self, grid) -> int:
         t, h, w = grid
         return t * h * w // (self.merge * self.merge)
+
+    def mm_data(self, pixel_values, grids) -> dict:
+        return {"pixel_values": pixel_values, "image_grid_thw": grids}
+
+
+IMAGENET_MEAN = (0.485, 0.456, 0.406)
+IMAGENET_STD = (0.229, 0.224, 0.225)
+
+
+class InternImagePreprocessor:
+    """InternVL's tiling: the image is resized to the grid of ``image_size`` tiles (at most ``max_tiles``) whose
+    aspect ratio is closest to its own, cut into tiles, and - when there is more than one tile - a thumbnail of the
+    whole image is appended; every tile is normalised with the ImageNet statistics and flattened into patches
+    ``[tiles, (image_size / patch)^2, 3 * patch * patch]`` (row-major patches, each as (channel, y, x)).  One tile
+    becomes ``(image_size / patch * downsample)^2`` placeholder tokens."""
+
+    def __init__(self, image_size: int = 448, patch: int = 14, downsample: float = 0.5, min_tiles: int = 1,
+                 max_tiles: int = 12, use_thumbnail: bool = True):
+        self.image_size, self.patch, self.downsample = image_size, patch, downsample
+        self.min_tiles, self.max_tiles, self.use_thumbnail = min_tiles, max_tiles, use_thumbnail
+        self.mean = torch.tensor(IMAGENET_MEAN, dtype=torch.float32).view(3, 1, 1)
+        self.std = torch.tensor(IMAGENET_STD, dtype=torch.float32).view(3, 1, 1)
+        self.tokens_per_tile = int(image_size // patch * downsample) ** 2
+
+    @classmethod
+    def from_config(cls, vision: dict, processor: Optional[dict] = None):
+        p = processor or {}
+        return cls(image_size=vision.get("image_size", 448), patch=vision["patch"], downsample=vision.get("downsample", 0.5),
+                   min_tiles=int(p.get("min_dynamic_patch", p.get("min_patches", 1))),
+                   max_tiles=int(p.get("max_dynamic_patch", p.get("max_patches", 12))),
+                   use_thumbnail=bool(p.get("use_thumbnail", True)))
+
+    def tile_grid(self, width: int, height: int) -> tuple[int, int]:
+        """(columns, rows) of the tile grid: the admissible ratio closest to the image's; on a tie the larger grid
+        wins when the image has more than half of that grid's pixels."""
+        ratios = sorted({(i, j) for n in range(self.min_tiles, self.max_tiles + 1) for i in range(1, n + 1)
+                         for j in range(1, n + 1) if self.min_tiles <= i * j <= self.max_tiles}, key=lambda r: r[0] * r[1])
+        aspect, best, best_diff = width / height, (1, 1), float("inf")
+        for i, j in ratios:
+            diff = abs(aspect - i / j)
+            if diff < best_diff:
+                best, best_diff = (i, j), diff
+            elif diff == best_diff and width * height > 0.5 * self.image_size ** 2 * i * j:
+                best = (i, j)
+        return best
+
+    def _tile(self, image) -> torch.Tensor:
+        import numpy as np
+        arr = np.asarray(image, dtype=np.uint8)
+        x = (torch.from_numpy(arr.copy()).permute(2, 0, 1).float() / 255.0 - self.mean) / self.std
+        g, p = self.image_size // self.patch, self.patch
+        return x.view(3, g, p, g, p).permute(1, 3, 0, 2, 4).reshape(g * g, 3 * p * p)
+
+    def one(self, image) -> torch.Tensor:
+        from PIL import Image
+        W, H = image.size
+        cols, rows = self.tile_grid(W, H)
+        s = self.image_size
+        big = image.resize((s * cols, s * rows), resample=Image.Resampling.BICUBIC)
+        tiles = [big.crop((c * s, r * s, (c + 1) * s, (r + 1) * s)) for r in range(rows) for c in range(cols)]
+        if self.use_thumbnail and len(tiles) > 1:
+            tiles.append(image.resize((s, s), resample=Image.Resampling.BICUBIC))
+        return torch.stack([self._tile(t) for t in tiles])
+
+    def __call__(self, images) -> tuple[torch.Tensor, list]:
+        """-> (``[sum(tiles), patches, patch_dim]``, tiles per image)."""
+        outs = [self.one(im) for im in images]
+        return torch.cat(outs), [int(o.shape[0]) for o in outs]
+
+    def tokens_per_image(self, tiles: int) -> int:
+        return tiles * self.tokens_per_tile
+
+    def mm_data(self, pixel_values, tiles) -> dict:
+        return {"pixel_values": pixel_values}
 
 
 def expand_placeholders(token_ids: Sequence[int], token_id: int, counts: Sequence[int]) -> list:
