@@ -346,3 +346,22 @@ def test_int8_checkpoints_shard_over_tensor_parallel_ranks():
         lin.method.process_weights_after_loading(lin)
         total = total + lin(x[:, rank * 32:(rank + 1) * 32].contiguous())
     torch.testing.assert_close(total, want, atol=0.3, rtol=0.05)
+
+
+def test_internvl_own_config_layout_parses_with_the_decoders_traits():
+    """InternVL's own checkpoints name the decoder section ``llm_config``; q / k norms, biases and rope base follow
+    the architecture named there, the tower's options (RMSNorm, q / k normalisation) come from ``vision_config``."""
+    from vllm_kunlun_b200.config import ModelConfig
+    d = dict(architectures=["InternVLChatModel"], downsample_ratio=0.5, torch_dtype="bfloat16",
+             llm_config=dict(architectures=["Qwen3ForCausalLM"], vocab_size=1000, hidden_size=256, num_hidden_layers=2,
+                             num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512,
+                             rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=4096, tie_word_embeddings=False),
+             vision_config=dict(hidden_size=128, num_hidden_layers=2, num_attention_heads=2, intermediate_size=256,
+                                image_size=448, patch_size=14, qk_normalization=True, norm_type="rms_norm", qkv_bias=False))
+    c = ModelConfig.from_hf_config(d)
+    assert (c.architecture, c.vision["text_architecture"]) == ("InternVLChatModel", "Qwen3ForCausalLM")
+    assert c.qk_norm and not c.qkv_bias and c.head_dim == 64 and c.rope_theta == 1e6 and not c.tie_word_embeddings
+    assert c.vision["qk_norm"] and c.vision["norm"] == "rmsnorm" and (c.vision["patch"], c.vision["image_size"]) == (14, 448)
+    d["llm_config"] = dict(d["llm_config"], architectures=["Qwen2ForCausalLM"])
+    c = ModelConfig.from_hf_config(d)
+    assert c.qkv_bias and not c.qk_norm

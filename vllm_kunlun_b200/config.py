@@ -194,6 +194,8 @@ class ModelConfig:
         arch = (cfg.get("architectures") or ["LlamaForCausalLM"])[0]
         if isinstance(cfg.get("thinker_config"), dict):     # Qwen3-Omni: the served part is the "thinker"
             cfg = {**cfg["thinker_config"], "architectures": [arch], "quantization_config": cfg.get("quantization_config")}
+        if "hidden_size" not in cfg and "text_config" not in cfg and isinstance(cfg.get("llm_config"), dict):
+            cfg = {**cfg, "text_config": cfg["llm_config"]}        # InternVL's own layout names the decoder llm_config
         if "hidden_size" not in cfg and isinstance(cfg.get("text_config"), dict):
             # nested layouts (Qwen3.5, vision-language wrappers): the decoder's fields live under text_config
             cfg = {**cfg["text_config"], **{k: v for k, v in cfg.items() if k != "text_config"},
